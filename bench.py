@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the TurboQuant KV-cache decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c3|small]
+
+One *step* is one full decode step of the named workload: for every attention layer, append the new K/V token
+of every sequence to the packed cache (normalise, rotate, quantise, pack) and run GQA decode attention over
+the whole context.  Default workload `c1`: 28 layers, 16 query / 8 KV heads, head_dim 128, 64 sequences
+(16 prompts x 4 rollouts, rollouts share their first 100 tokens) at context 4096, kv_bits=4 -- 7.75 GB of cache
+per GPU, read once per step.  Inputs are seeded synthetic tensors with the reference configuration's shapes
+and value distributions (no model weights or datasets are available offline).
+
+Reported on ONE JSON line (rank 0): `value` = algorithmic cache+I/O bytes of a step over all GPUs / device
+time of a step with inputs resident in HBM; `e2e` = the same through the host-buffer C-ABI call
+(pinned host q/k/v in, attention outputs back out, both copies inside the timed region); `roofline` for the
+attention kernel alone (its own CUDA-event timing over every layer); `cpu_baseline` = the CPU oracle (a port of
+the reference's kernel arithmetic -- the reference has no CPU implementation) on a bounded sample.
+
+With N > 1 (torchrun) every rank owns its own 64 sequences (sequences are independent: weak scaling, no
+data-path collective) and the per-sequence outputs are all-gathered once per step over NCCL inside the timed
+region.  `--impl reference` times the CPU port with all host threads on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: layers, H, Hkv, G, context, bits, prompt
+    "c1": dict(layers=28, H=16, Hkv=8, G=64, L=4096, bits=4, prompt=100,
+               desc="Qwen3-0.6B shape decode step: 28 layers, 64 seq x ctx 4096, kv_bits=4"),
+    "c3": dict(layers=36, H=32, Hkv=8, G=32, L=8192, bits=2, prompt=100,
+               desc="Qwen3-8B shape decode step: 36 layers, 32 seq per GPU x ctx 8192, kv_bits=2"),
+    "small": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=100,
+                  desc="reduced case for profiler captures: 4 layers, 16 seq x ctx 2048, kv_bits=4"),
+}
+D = 128
+METRIC = "decode-attn HBM GB/s over 4-bit KV (% of ~8 TB/s); append tokens/s"
+
+
+def algorithmic_bytes(w, attention_only=False):
+    """Bytes one step must move, per GPU: every cache byte of the context once (GQA sharing does not count
+    twice), q in / out out, R once per layer; plus, for the append, the new K/V vectors in and codes+norm out."""
+    vpb = 4 if w["bits"] == 2 else 2
+    kvp = w["Hkv"] * D // vpb
+    per_layer_attn = w["G"] * w["L"] * (2 * kvp + 4 * w["Hkv"]) + 4 * w["G"] * w["H"] * D + 32768
+    per_vec = 256 + D // vpb + 2
+    per_layer_append = w["G"] * w["Hkv"] * 2 * per_vec
+    if attention_only:
+        return per_layer_attn
+    return w["layers"] * (per_layer_attn + per_layer_append)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region (read-only queries)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(self.gpu_index)], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.f.name)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (a port of the reference kernels' arithmetic) on the host cores
+# ------------------------------------------------------------------------------------------------------------------------
+class CpuPort:
+    """Decode steps of ONE layer of the workload on the CPU oracle (all host threads OpenMP gives it)."""
+
+    def __init__(self, w, seed=0):
+        from oracle import tqo
+        from triebwerk_b200 import synth
+        self.tqo, self.synth, self.w = tqo, synth, w
+        self.cores = tqo.num_threads()
+        G, L, Hkv, bits = w["G"], w["L"], w["Hkv"], w["bits"]
+        kv_dim = Hkv * D
+        self.rng = rng = np.random.default_rng(seed)
+        self.R, _ = tqo.rotation()
+        vpb = 4 if bits == 2 else 2
+        # The sample's cache holds random code bytes and plausible norms: the CPU cost of attention does not depend
+        # on the values, and quantising 64 x 4096 tokens on the CPU first would take longer than the sample itself.
+        self.ck = rng.integers(0, 256, (G * L, kv_dim // vpb), dtype=np.uint8)
+        self.cv = rng.integers(0, 256, (G * L, kv_dim // vpb), dtype=np.uint8)
+        self.kn = (11.3 + rng.standard_normal((G * L, Hkv), dtype=np.float32)).astype(np.float16)
+        self.vn = (11.3 + rng.standard_normal((G * L, Hkv), dtype=np.float32)).astype(np.float16)
+        self.scales = synth.channel_scales(kv_dim)
+        self.pos = np.full(G, L - 1, np.int32)
+
+    def run(self, seconds):
+        """Returns (GB/s by the GPU arm's algorithmic-byte formula, description, seconds per layer-step)."""
+        w, tqo = self.w, self.tqo
+        G, L, H, Hkv, bits = w["G"], w["L"], w["H"], w["Hkv"], w["bits"]
+        per_layer = algorithmic_bytes(w) / w["layers"]
+        t_total, n = 0.0, 0
+        while t_total < seconds or n < 1:
+            k, v = self.synth.kv_batch(self.rng, G, Hkv * D, self.scales)
+            q = self.synth.q_batch(self.rng, G, H * D)
+            t0 = time.perf_counter()
+            tqo.append_batch(self.ck, self.kn, k, self.R, self.pos, L, Hkv, D, bits)
+            tqo.append_batch(self.cv, self.vn, v, self.R, self.pos, L, Hkv, D, bits)
+            tqo.attention_batch(q, self.ck, self.cv, self.kn, self.vn, self.R, self.pos, L, H, Hkv, D, bits)
+            t_total += time.perf_counter() - t0
+            n += 1
+        sec = t_total / n
+        sample = f"1 of {w['layers']} layers x all {G} sequences at context {L}: {n} layer-steps in {t_total:.1f} s"
+        return per_layer / sec / 1e9, sample, sec
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    port = CpuPort(w)
+    for _ in range(min(1, args.warmup)):
+        port.run(0.0)  # pages the library and the cache in; CPU timings need no more warm-up than that
+    vals, secs, sample = [], [], ""
+    for _ in range(max(1, args.steps)):  # each step of this arm is a bounded sample: one layer of the workload
+        gbs, sample, sec = port.run(0.0)
+        vals.append(gbs)
+        secs.append(sec)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(secs)) * w["layers"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 codes, f32 math",
+        "data": "synthetic", "config": {"workload": w["desc"], "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": port.cores, "kind": "port",
+                         "sample": "CPU port of the reference kernels' arithmetic (the reference ships no CPU "
+                                   "implementation of this path); each step = " + sample.split(":")[0] +
+                                   "; ms_per_step extrapolates one layer to all layers"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------------------
+def build_engine(w, device_seed):
+    import torch
+    import triebwerk_b200 as tq
+    from triebwerk_b200 import synth
+    G, L, H, Hkv, bits, NL = w["G"], w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
+    kv_dim = Hkv * D
+    eng = tq.Engine(L, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, L)
+    gen = torch.Generator(device="cuda").manual_seed(device_seed)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    prompt = w["prompt"]
+    # The cache is produced by the library's own append (prefill form), not filled with random bytes.
+    for layer in range(NL):
+        for g0 in range(0, G, 4):
+            kp, vp = synth.torch_kv(gen, prompt, kv_dim, scales)  # prompt shared by the 4 rollouts
+            for g in range(g0, min(g0 + 4, G)):
+                eng.prefill_append(layer, g, kp, vp, 0)
+                kd, vd = synth.torch_kv(gen, L - 1 - prompt, kv_dim, scales)
+                eng.prefill_append(layer, g, kd, vd, prompt)
+    eng.set_positions([L - 1] * G)
+    torch.cuda.synchronize()
+    return eng, gen, scales
+
+
+def run_ours(args, w, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import triebwerk_b200 as tq
+    from triebwerk_b200 import synth
+
+    torch.cuda.set_device(local_rank)
+    G, L, H, Hkv, bits, NL = w["G"], w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
+    kv_dim, q_dim = Hkv * D, H * D
+    eng, gen, scales = build_engine(w, 1234 + rank)
+
+    # step inputs: resident copies for `value`, pinned host copies for `e2e`
+    k_dev = torch.empty(NL, G, kv_dim, dtype=torch.float16, device="cuda")
+    v_dev = torch.empty_like(k_dev)
+    for layer in range(NL):
+        k_dev[layer], v_dev[layer] = synth.torch_kv(gen, G, kv_dim, scales)
+    q_dev = torch.randn(NL, G, q_dim, generator=gen, device="cuda").to(torch.float16)
+    out_dev = torch.empty_like(q_dev)
+    q_host, k_host, v_host = (t.cpu().pin_memory() for t in (q_dev, k_dev, v_dev))
+    out_host = torch.empty(NL, G, q_dim, dtype=torch.float16).pin_memory()
+    gather_buf = torch.empty(world, NL, G, q_dim, dtype=torch.float16, device="cuda") if world > 1 else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device():
+        eng.decode_step(q_dev, k_dev, v_dev, out_dev)
+        if world > 1:  # the one exchange of the path: gather per-sequence outputs
+            dist.all_gather_into_tensor(gather_buf, out_dev)
+
+    def step_host():
+        eng.decode_step_host(q_host, k_host, v_host, out_host)
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    for _ in range(max(3, args.warmup)):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_step = timed(step_device, args.steps)
+
+    # the attention kernel alone, every layer, on the launching stream
+    def attn_only():
+        for layer in range(NL):
+            eng.attend_layer(layer, out_dev[layer])
+    attn_only()
+    ms_attn_pass = timed(attn_only, max(1, args.steps))
+    clocks = sampler.stop() if sampler else None
+
+    for _ in range(2):
+        step_host()
+    ms_e2e = timed(step_host, max(1, args.steps))
+
+    status = eng.status()
+    assert status == 0, f"device status word is {status}: a kernel gave up on a bounded wait or saw a bad position"
+    if rank != 0:
+        return
+    bytes_step = algorithmic_bytes(w)
+    value = world * bytes_step / (ms_step * 1e-3) / 1e9
+    e2e = world * bytes_step / (ms_e2e * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    attn_bytes = algorithmic_bytes(w, attention_only=True)
+    attn_ms = ms_attn_pass / NL
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+    tokens_per_s = world * G / (ms_step * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 codes, f16 mma, f32 accumulate", "data": "synthetic",
+        "config": {"workload": w["desc"], "kv_bits": bits, "sequences_per_gpu": G, "context": L, "layers": NL,
+                   "l2": "inputs larger than L2 (one layer's cache is %.0f MB, 126 MB L2)" % (attn_bytes / 1e6),
+                   "parallelism": f"sequence-sharded x{world}" if world > 1 else "1 GPU"},
+        "pct_of_8TBs": 100.0 * value / world / 8000.0,
+        "append_tokens_per_s": tokens_per_s,
+        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(NL * G * (q_dim + 2 * kv_dim) * 2), "d2h_bytes_per_step": int(NL * G * q_dim * 2)},
+        "gpu_launches": int(args.steps * NL * 2),
+        "roofline": {"kernel": f"decode_attention_kernel<{bits}>", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     "us_per_launch": attn_ms * 1e3, "algorithmic_bytes_per_launch": attn_bytes,
+                     "traffic": TRAFFIC.get(args.workload)},
+        "clocks": clocks,
+    }
+    if args.cpu_seconds > 0 and world == 1:
+        port = CpuPort(w)
+        gbs, sample, _ = port.run(args.cpu_seconds)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": port.cores, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per attention launch from the committed ncu capture (profiles/), or
+# None while no capture of that workload exists.
+TRAFFIC = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="length of the CPU-baseline sample (0 = skip)")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, w, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

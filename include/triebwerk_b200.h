@@ -1,0 +1,247 @@
+/* triebwerk_b200 -- C ABI of the B200 (sm_100a) TurboQuant KV-cache hot path.
+ *
+ * Two layers, both plain C (pointers and sizes only; no torch, no C++ types):
+ *
+ *  1. The reference's own launcher symbols (BY571/triebwerk, engine/kernels.cu, all inside its
+ *     extern "C" block) with identical parameter lists, so that the reference's engine.cpp links against
+ *     this library instead of its own kernels for this path.  Every pointer is a DEVICE pointer owned by
+ *     the caller; calls are asynchronous on the given stream and return nothing, like the reference's.
+ *
+ *  2. The native tq_* entry points: the same operations with explicit workspaces, fused launches and an
+ *     int status (0 = ok, <0 = argument/capacity error, >0 = CUDA error code), plus the KV arena
+ *     (sizing, slot table, reset, sleep/wake, external memory) that the reference keeps inside
+ *     InferenceEngine (engine/engine.cpp:1338-1560, 1609-1620, 893-1022).
+ *
+ * Where a declaration below replaces a reference interface, the comment cites it as file:line inside the
+ * reference project.  `half` data crosses as void* / uint16 bits; the cache byte layout is the reference's
+ * (engine/kernels.cu:1618-1635): codes [row][kv_dim/vpb] uint8, norms [row][num_kv_heads] fp16, row =
+ * g*max_seq_len + position.  head_dim must be 128.  kv_bits is 0 (fp16 cache), 2 or 4.
+ */
+#ifndef TRIEBWERK_B200_H_
+#define TRIEBWERK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* An opaque CUDA stream handle (cudaStream_t).  NULL is the legacy default stream, as in the reference's
+ * single-sequence path. */
+typedef struct CUstream_st* tq_stream_t;
+
+/* ---- status codes of the tq_* entry points ------------------------------------------------------------------ */
+enum {
+    TQ_OK = 0,
+    TQ_ERR_ARG = -1,         /* null pointer, bad kv_bits, head_dim != 128, heads not divisible ... */
+    TQ_ERR_CAPACITY = -2,    /* position / sequence count beyond what was reserved */
+    TQ_ERR_WORKSPACE = -3,   /* workspace missing or too small */
+    TQ_ERR_UNSUPPORTED = -4, /* shape outside what the kernels are built for */
+    TQ_ERR_STATE = -5,       /* engine asleep, arena not set ... */
+    TQ_ERR_DEVICE = -6,      /* a kernel reported a device-side status (bounded wait ran out) */
+    TQ_ERR_NOMEM = -7
+};
+
+const char* tq_status_string(int status);
+/* Library version as major*10000 + minor*100 + patch. */
+int tq_version(void);
+
+/* ===================================================================================================================
+ * 1. Reference-compatible launchers.
+ *
+ * Differences a caller can observe: `as` / `attn_scratch` (the reference's fp32 score buffer,
+ * engine/engine.cpp:1371,1467) is accepted and ignored -- scores never leave the SM; a small per-device
+ * workspace (pre-rotated queries, split-K partials) is allocated inside the library the first time a
+ * launcher needs it and when a later call needs a larger one, so the first call of a given size must come
+ * before any stream capture (the reference warms up before it captures, engine/engine.cpp:2369-2387).
+ * Errors cannot be returned through these signatures; they are kept for tq_last_compat_status().
+ * =================================================================================================================== */
+
+/* engine/kernels.cu:1963-1973 (kernel :1482-1560).  Token-form append into a single-sequence cache:
+ * token t of kv_buf [num_tokens][kv_dim] goes to row positions[t]. */
+void launch_turbo_kv_quantize(uint8_t* cache_q, void* cache_norms, const void* kv_buf, const void* rotation,
+                              const int* positions, int max_seq_len, int num_tokens, int num_kv_heads,
+                              int head_dim, int kv_dim, int bits, tq_stream_t s);
+
+/* engine/kernels.cu:1975-1984 (kernel :1563-1636).  One new token per sequence g at row
+ * g*max_seq_len + positions[g]; kv_buf is [G][kv_dim]. */
+void launch_turbo_kv_quantize_batch(uint8_t* cache_q, void* cache_norms, const void* kv_buf,
+                                    const void* rotation, const int* positions, int max_seq_len, int G,
+                                    int num_kv_heads, int head_dim, int kv_dim, int bits, tq_stream_t s);
+
+/* engine/kernels.cu:1986-1999 (kernel :1641-1776).  Batched GQA decode attention over the packed cache,
+ * positions 0..positions[g] inclusive; q and out are [G][q_dim]. */
+void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
+                                      const void* k_norms, const void* v_norms, const void* rotation,
+                                      float* as, const int* pos, int msl, int G, int num_heads,
+                                      int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits,
+                                      tq_stream_t s);
+
+/* engine/kernels.cu:2001-2013 (kernel :1779-1870).  Single-sequence form, `pos` by value. */
+void launch_turbo_gqa_attention(const void* q, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms,
+                                const void* v_norms, const void* rotation, void* output, float* as, int pos,
+                                int msl, int num_heads, int num_kv_heads, int head_dim, int bits,
+                                tq_stream_t s);
+
+/* engine/kernels.cu:2015-2028 (kernel :1874-1960).  Causal prefill attention over a single-sequence
+ * packed cache: query row tq of q [T][q_dim] attends to positions 0..tq. */
+void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
+                                        const void* k_norms, const void* v_norms, const void* rotation,
+                                        float* as, int T, int msl, int num_heads, int num_kv_heads,
+                                        int head_dim, int q_dim, int kv_dim, int bits, tq_stream_t s);
+
+/* engine/kernels.cu:1351-1353 (kernel :964-977).  kv_bits = 0 cache write. */
+void launch_kv_cache_write_batch(void* ck, void* cv, const void* k, const void* v, const int* pos, int msl,
+                                 int G, int kv_dim, tq_stream_t s);
+
+/* engine/kernels.cu:1354-1357 (kernel :981-1066).  kv_bits = 0 batched decode attention. */
+void launch_gqa_attention_batch(void* out, const void* q, const void* ck, const void* cv, float* as,
+                                const int* pos, int msl, int G, int num_heads, int num_kv_heads, int head_dim,
+                                int q_dim, int kv_dim, tq_stream_t s);
+
+/* engine/kernels.cu:737-752 (kernel :244-345).  kv_bits = 0 single-sequence decode attention. */
+void launch_gqa_attention(const void* q, const void* k_cache, const void* v_cache, void* output,
+                          float* attn_scratch, int pos, int max_seq_len, int num_heads, int num_kv_heads,
+                          int head_dim, tq_stream_t stream);
+
+/* Status of the most recent compat launcher call on this host thread (TQ_OK or an error above). */
+int tq_last_compat_status(void);
+
+/* ===================================================================================================================
+ * 2. Native entry points.
+ * =================================================================================================================== */
+
+/* Rotation matrix of the reference (engine/engine.cpp:364-392): mt19937(seed) normal fill, row-wise
+ * modified Gram-Schmidt in fp32, fp16 rounding.  host_out receives 128*128 fp16 values (32 KB, HOST
+ * memory).  The reference uses seed 42. */
+int tq_rotation_generate(uint32_t seed, void* host_out_half);
+
+/* Bytes of device workspace tq_decode_attention / tq_append_decode need for G sequences and num_heads
+ * query heads on the current device (pre-rotated queries, tile table, split-K partials, tickets). */
+size_t tq_workspace_bytes(int G, int num_heads);
+
+/* Fused decode-step append (replaces the two launch_turbo_kv_quantize_batch calls of
+ * engine/engine.cpp:1985-1990 and phase 1 of the attention kernel, engine/kernels.cu:1676-1680): for every
+ * sequence g, quantise k_buf[g] into the K cache and v_buf[g] into the V cache at row
+ * row(g) + positions[g], and rotate q[g] into the workspace for tq_decode_attention.  Any of
+ * {k_buf, v_buf, q} may be NULL to skip that part.  kv_bits must be 2 or 4 here.
+ * row(g) = g*max_seq_len, or row_base[g] when row_base (device, int64[G]) is not NULL. */
+int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf,
+                     const void* v_buf, const void* q, const void* rotation, const int* positions,
+                     const long long* row_base, int max_seq_len, int G, int num_heads, int num_kv_heads,
+                     int head_dim, int q_dim, int kv_dim, int bits, void* workspace, size_t workspace_bytes,
+                     tq_stream_t s);
+
+/* Split-K GQA decode attention over the packed cache (replaces launch_turbo_gqa_attention_batch,
+ * engine/kernels.cu:1986-1999).  Reads the queries that tq_append_decode rotated into `workspace` on the
+ * same stream.  total_rows is the number of rows of the cache arrays (G*max_seq_len for the dense layout).
+ * positions may be NULL when pos_value >= 0 gives one position for every sequence. */
+int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms,
+                        const void* v_norms, const void* rotation, const int* positions, int pos_value,
+                        const long long* row_base, long long total_rows, int max_seq_len, int G, int num_heads,
+                        int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
+                        size_t workspace_bytes, tq_stream_t s);
+
+/* kv_bits = 0 twins with the same slot addressing (replace launch_kv_cache_write_batch and
+ * launch_gqa_attention_batch, engine/kernels.cu:1351-1357). */
+int tq_fp16_append_decode(void* ck, void* cv, const void* k_buf, const void* v_buf, const int* positions,
+                          const long long* row_base, int max_seq_len, int G, int kv_dim, tq_stream_t s);
+int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const void* cv, const int* positions,
+                             int pos_value, const long long* row_base, long long total_rows, int max_seq_len,
+                             int G, int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim,
+                             void* workspace, size_t workspace_bytes, tq_stream_t s);
+
+/* Reads (and clears) the device status word kept in `workspace`: 0, or a code saying which bounded wait
+ * gave up.  Synchronises the stream. */
+int tq_workspace_status(void* workspace, tq_stream_t s);
+
+/* ---- KV arena / engine state ----------------------------------------------------------------------------------------
+ * The part of InferenceEngine that owns the cache: constructor arguments (engine/engine.cpp:300-317),
+ * KV_DIM_PACKED (:292-294), alloc_batch sizing and carving (:1338-1560), set_arena (:1609-1620), reset
+ * (:893-916), sleep / wake (:922-1022) and the per-layer call sites (:1979-2006).  One handle per device. */
+typedef struct tq_engine tq_engine;
+
+typedef struct tq_model_shape {
+    int num_layers;   /* attention layers that own a KV cache */
+    int num_heads;    /* query heads */
+    int num_kv_heads; /* KV heads */
+    int head_dim;     /* must be 128 */
+} tq_model_shape;
+
+/* Like Engine(max_seq_len, kv_bits): an unsupported kv_bits falls back to 0 with a warning on stderr
+ * (engine/engine.cpp:310-313).  Allocates nothing on the device yet. */
+int tq_engine_create(const tq_model_shape* shape, int max_seq_len, int kv_bits, tq_engine** out);
+void tq_engine_destroy(tq_engine* e);
+int tq_engine_kv_bits(const tq_engine* e);
+
+/* Bytes of arena needed for G sequences.  capacities == NULL: dense slots of max_seq_len rows each (the
+ * reference's layout, row(g) = g*max_seq_len).  Otherwise sequence g gets capacities[g] rows (rounded up
+ * to 32) and row(g) is the running sum. */
+size_t tq_engine_arena_bytes(const tq_engine* e, int G, int max_seq_len, const int* capacities);
+
+/* Use caller-owned device memory as the arena (Engine.set_arena, engine/engine.cpp:1609-1620).  The
+ * library never frees it. */
+int tq_engine_set_arena(tq_engine* e, void* device_ptr, size_t bytes);
+
+/* Reserve and carve the arena for a batch (alloc_batch, engine/engine.cpp:1338-1560).  Reuses the current
+ * carving when it is large enough; grows an internally owned arena; fails with TQ_ERR_CAPACITY when an
+ * external arena is too small.  Positions are set to 0. */
+int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capacities);
+
+/* Forget all sequences: positions = 0 (engine reset()).  With zero_cache != 0 also clears the cache
+ * bytes as the reference does (engine/engine.cpp:2262-2283); attention never reads rows past a position,
+ * so this is only needed by callers that inspect the raw cache. */
+int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s);
+
+/* Release (sleep) and re-create (wake) the internally owned arena; contents are not kept, as in the
+ * reference (engine/engine.cpp:922-1022).  An external arena is detached by sleep and must be set again. */
+int tq_engine_sleep(tq_engine* e);
+int tq_engine_wake(tq_engine* e);
+
+/* Reads and clears the engine's device status word (0 = fine; 1 = a bounded wait on a TMA barrier gave up;
+ * 2 = shared-memory layout refused; 3 = a position outside its slot).  Synchronises the stream. */
+int tq_engine_status(tq_engine* e, tq_stream_t s);
+
+/* Positions of the G sequences (device int32[G], advanced by the caller or by tq_engine_advance). */
+int* tq_engine_positions(tq_engine* e);
+int tq_engine_set_positions(tq_engine* e, const int* host_positions, int G, tq_stream_t s);
+int tq_engine_advance(tq_engine* e, tq_stream_t s); /* positions[g] += 1 on the device */
+
+/* Raw device pointers of one layer's cache (for tests and for callers that keep using the compat
+ * launchers).  kv_bits != 0: k_codes/v_codes uint8, k_norms/v_norms fp16.  kv_bits == 0: k_codes/v_codes
+ * are the fp16 K/V arrays and the norm pointers are NULL. */
+int tq_engine_layer_ptrs(tq_engine* e, int layer, void** k_codes, void** v_codes, void** k_norms,
+                         void** v_norms, long long* total_rows);
+const long long* tq_engine_row_base(tq_engine* e); /* device int64[G], NULL for the dense layout */
+const void* tq_engine_rotation(tq_engine* e);      /* device fp16 [128][128] */
+int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s);
+
+/* One layer of a decode step on device buffers (steps 4-5 of forward_layer_batch,
+ * engine/engine.cpp:1979-2006): append k/v at the current positions, then attend.  q/out [G][q_dim], k/v
+ * [G][kv_dim], all fp16 on the device. */
+int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
+                           tq_stream_t s);
+
+/* The attention half of tq_engine_decode_layer alone, on the queries the last tq_engine_decode_layer of
+ * this engine rotated (packed modes only).  Used to time the attention kernel by itself. */
+int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s);
+
+/* Every layer of a decode step on DEVICE buffers: q/out [layers][G][q_dim], k/v [layers][G][kv_dim]. */
+int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
+
+/* Token-form append of T tokens of sequence `seq` (prefill, engine/engine.cpp:2121-2130): k/v
+ * [T][kv_dim] fp16 on the device, written at positions first_pos .. first_pos+T-1. */
+int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos,
+                             int T, tq_stream_t s);
+
+/* A whole decode step from HOST buffers: q_host [layers][G][q_dim], k_host/v_host [layers][G][kv_dim],
+ * out_host [layers][G][q_dim], fp16, ideally pinned.  Copies the inputs in, runs every layer, copies the
+ * outputs back and waits.  This is the end-to-end call bench.py times. */
+int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_host, const void* v_host,
+                               void* out_host, tq_stream_t s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIEBWERK_B200_H_ */

@@ -1,0 +1,203 @@
+"""GPU parity of the GQA decode attention over the packed cache, through the C ABI launchers, against the CPU
+oracle on oracle-built caches (so that only the attention is under test) and against the committed outputs of
+the reference's own kernels.  Tolerance: max-abs 2e-3 and relative 1e-2 in fp16 (tests/helpers.py)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tqo
+from tests import helpers as hp
+
+pytestmark = pytest.mark.gpu
+gu = pytest.importorskip("tests.gpu_util")
+
+EDGE_LENGTHS = [1, 2, 31, 32, 33, 127, 128, 129, 511, 512, 513, 1000]
+
+
+def _scales(kv_dim):
+    return np.exp(np.random.default_rng(1).normal(0, 0.5, kv_dim)).astype(np.float32)
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("H", [16, 32])
+def test_ragged_batch_edge_lengths(bits, H):
+    rng = np.random.default_rng(10 + bits + H)
+    R, _ = tqo.rotation()
+    Hkv, D, msl = 8, 128, 1024
+    lengths = EDGE_LENGTHS
+    G = len(lengths)
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R, _scales(Hkv * D))
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    worst, rel = hp.assert_attention_close(got, ref, H, D, f"tq{bits} H={H}")
+    print(f"tq{bits} H={H}: max-abs {worst:.2e}, rel {rel:.2e}")
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_rows_past_the_position_are_ignored(bits):
+    """Rows after positions[g] hold other data (here: random bytes and NaN norms): they must not leak in."""
+    rng = np.random.default_rng(20)
+    R, _ = tqo.rotation()
+    G, H, Hkv, D, msl = 3, 16, 8, 128, 96
+    lengths = [5, 40, 70]
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R)
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    for g, n in enumerate(lengths):
+        sl = slice(g * msl + n, (g + 1) * msl)
+        ck[sl] = rng.integers(0, 256, ck[sl].shape, dtype=np.uint8)
+        cv[sl] = rng.integers(0, 256, cv[sl].shape, dtype=np.uint8)
+        kn[sl] = np.float16(np.nan)
+        vn[sl] = np.float16(np.inf)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got, ref, H, D, f"tq{bits} garbage tail")
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_long_context_split_over_many_ctas(bits):
+    # 8 sequences x 4096 tokens: every sequence is cut across several CTAs and merged by the last one to arrive
+    rng = np.random.default_rng(30)
+    R, _ = tqo.rotation()
+    G, H, Hkv, D, msl = 8, 16, 8, 128, 4096
+    lengths = [4096, 4096, 4095, 4065, 3000, 4096, 17, 4096]
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R, _scales(Hkv * D))
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    worst, rel = hp.assert_attention_close(got, ref, H, D, f"tq{bits} long")
+    print(f"tq{bits} long: max-abs {worst:.2e}, rel {rel:.2e}")
+    # run it again: tickets and workspace must be reusable as they are
+    got2 = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    assert (got2.view(np.uint16) == got.view(np.uint16)).all()
+
+
+def test_peaked_and_flat_softmax():
+    """One key aligned with the query (weight ~1 on one position) and an all-equal cache (uniform weights)."""
+    rng = np.random.default_rng(40)
+    R, _ = tqo.rotation()
+    G, H, Hkv, D, msl, bits = 2, 16, 8, 128, 256, 4
+    kv_dim = Hkv * D
+    L = 200
+    k = rng.standard_normal((L, kv_dim), dtype=np.float32)
+    v = rng.standard_normal((L, kv_dim), dtype=np.float32)
+    q = rng.standard_normal((G, H * D), dtype=np.float32)
+    k[77] = np.tile(q[0].reshape(H, D)[::2], 1).reshape(-1) * 8.0  # KV head h aligned with query head 2h, large norm
+    ck, kn = tqo.alloc_cache(G, msl, Hkv, D, bits)
+    cv, vn = tqo.alloc_cache(G, msl, Hkv, D, bits)
+    posl = np.arange(L, dtype=np.int32)
+    tqo.append_tokens(ck, kn, k.astype(np.float16), R, posl, msl, Hkv, D, bits)
+    tqo.append_tokens(cv, vn, v.astype(np.float16), R, posl, msl, Hkv, D, bits)
+    same_k = np.tile(k[:1], (L, 1)).astype(np.float16)
+    tqo.append_tokens(ck[msl:], kn[msl:], same_k, R, posl, msl, Hkv, D, bits)
+    tqo.append_tokens(cv[msl:], vn[msl:], v.astype(np.float16), R, posl, msl, Hkv, D, bits)
+    q16 = q.astype(np.float16)
+    pos = np.array([L - 1, L - 1], np.int32)
+    ref, _ = tqo.attention_batch(q16, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    got = gu.gpu_attention_batch(q16, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got, ref, H, D, "peaked/flat")
+
+
+def test_identical_sequences_and_permutation():
+    rng = np.random.default_rng(50)
+    R, _ = tqo.rotation()
+    H, Hkv, D, msl, bits, L = 16, 8, 128, 320, 4, 300
+    ck1, kn1, cv1, vn1 = hp.build_cache_oracle(rng, 1, [L], msl, Hkv, D, bits, R)
+    G = 4
+    ck, cv = np.tile(ck1, (G, 1)), np.tile(cv1, (G, 1))
+    kn, vn = np.tile(kn1, (G, 1)), np.tile(vn1, (G, 1))
+    q = np.tile(rng.standard_normal((1, H * D), dtype=np.float32).astype(np.float16), (G, 1))
+    pos = np.full(G, L - 1, np.int32)
+    out = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    assert (out.view(np.uint16) == out[0].view(np.uint16)).all(), "identical sequences gave different outputs"
+    # permuting sequences permutes outputs (different lengths, different slices of the CTA partition)
+    lengths = [300, 10, 150, 299]
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R)
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    a = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    perm = np.array([2, 0, 3, 1])
+    rows = np.concatenate([np.arange(g * msl, (g + 1) * msl) for g in perm])
+    b = gu.gpu_attention_batch(q[perm], ck[rows], cv[rows], kn[rows], vn[rows], R, pos[perm], msl, H, Hkv, D, bits)
+    hp.assert_attention_close(b, a[perm], H, D, "permutation")
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_single_sequence_and_prefill_forms(bits):
+    rng = np.random.default_rng(60)
+    R, _ = tqo.rotation()
+    H, Hkv, D, msl, L = 16, 8, 128, 192, 150
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, 1, [L], msl, Hkv, D, bits, R)
+    q = rng.standard_normal(H * D, dtype=np.float32).astype(np.float16)
+    for pos in (0, 31, 32, L - 1):
+        ref, _ = tqo.attention_single(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+        got = gu.gpu_attention_single(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+        hp.assert_attention_close(got[None], ref[None], H, D, f"single pos={pos}")
+    T = 70
+    qp = rng.standard_normal((T, H * D), dtype=np.float32).astype(np.float16)
+    ref, _ = tqo.prefill_attention(qp, ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    got = gu.gpu_prefill_attention(qp, ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got, ref, H, D, "prefill")
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_attention_on_reference_cache_bytes_vs_reference_outputs(bits):
+    g = hp.load_golden(f"ref_kernels_tq{bits}.npz")
+    if g is None:
+        pytest.skip("fixture not generated yet")
+    H, Hkv, D, msl = int(g["H"]), int(g["Hkv"]), int(g["D"]), int(g["msl"])
+    R = hp.h(g["R"])
+    got = gu.gpu_attention_batch(hp.h(g["q"]), g["ck"], g["cv"], hp.h(g["kn"]), hp.h(g["vn"]), R, g["final_pos"], msl, H,
+                                 Hkv, D, bits)
+    hp.assert_attention_close(got, hp.h(g["out"]), H, D, "vs reference kernels (batched)")
+    sl = slice(2 * msl, 3 * msl)
+    got1 = gu.gpu_attention_single(hp.h(g["q"])[2], g["ck"][sl], g["cv"][sl], hp.h(g["kn"])[sl], hp.h(g["vn"])[sl], R,
+                                   int(g["final_pos"][2]), msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got1[None], hp.h(g["out_single"])[None], H, D, "vs reference kernels (single)")
+    gotp = gu.gpu_prefill_attention(hp.h(g["q_prefill"]), g["ck"][sl], g["cv"][sl], hp.h(g["kn"])[sl],
+                                    hp.h(g["vn"])[sl], R, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(gotp, hp.h(g["out_prefill"]), H, D, "vs reference kernels (prefill)")
+
+
+def test_attention_equals_reference_kernels_live():
+    if not os.path.exists(gu.REF_SO):
+        pytest.skip("reference kernel library not present in this snapshot")
+    ref = C.CDLL(gu.REF_SO)
+    ref.launch_turbo_gqa_attention_batch.restype = None
+    rng = np.random.default_rng(70)
+    R, _ = tqo.rotation()
+    G, H, Hkv, D, msl, bits = 4, 16, 8, 128, 640, 4
+    lengths = [101, 300, 612, 612]  # the reference configuration's context range
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R, _scales(Hkv * D))
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    d = [gu.dev(x) for x in (q, ck, cv, kn, vn, R, pos)]
+    out = torch.zeros(G, H * D, dtype=torch.float16, device="cuda")
+    scratch = torch.zeros(G * H * msl, dtype=torch.float32, device="cuda")
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    i = C.c_int
+    ref.launch_turbo_gqa_attention_batch(vp(out), vp(d[0]), vp(d[1]), vp(d[2]), vp(d[3]), vp(d[4]), vp(d[5]), vp(scratch),
+                                         vp(d[6]), i(msl), i(G), i(H), i(Hkv), i(D), i(H * D), i(Hkv * D), i(bits),
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    want = gu.host(out)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    worst, rel = hp.assert_attention_close(got, want, H, D, "vs live reference kernels")
+    print(f"vs live reference kernels: max-abs {worst:.2e}, rel {rel:.2e}")
+
+
+def test_unsupported_shapes_are_refused():
+    import triebwerk_b200 as tq
+    R, _ = tqo.rotation()
+    rng = np.random.default_rng(80)
+    H, Hkv, D, msl, bits = 6, 3, 128, 32, 4  # 3 KV heads: outside what the kernel is built for
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, 1, [4], msl, Hkv, D, bits, R)
+    q = rng.standard_normal((1, H * D), dtype=np.float32).astype(np.float16)
+    with pytest.raises(tq.TqError) as e:
+        gu.gpu_attention_batch(q, ck, cv, kn, vn, R, [3], msl, H, Hkv, D, bits)
+    assert e.value.status == -4

@@ -1,0 +1,223 @@
+"""GPU tests of the engine handle (KV arena, slots, per-layer decode step, host-buffer step, CUDA graph replay)
+and of the properties that hold at the benchmark's full size."""
+import numpy as np
+import pytest
+import torch
+
+import triebwerk_b200 as tq
+from triebwerk_b200 import synth
+from oracle import tqo
+from tests import helpers as hp
+
+pytestmark = pytest.mark.gpu
+gu = pytest.importorskip("tests.gpu_util")
+
+
+def test_c0_generation_loop_against_oracle():
+    """The reference's CPU-runnable configuration: 16/8 heads, G=4, a 100-token prompt and decoded tokens up to
+    context 612, kv_bits=4, one layer; every decode step is compared with the oracle run on its own cache."""
+    H, Hkv, D, G, bits = 16, 8, 128, 4, 4
+    prompt, new_tokens, msl = 100, 512, 640
+    kv_dim, q_dim = Hkv * D, H * D
+    rng = np.random.default_rng(0)
+    scales = synth.channel_scales(kv_dim)
+    R = tq.ops.rotation_matrix().numpy()
+    eng = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, msl)
+    ock, okn = tqo.alloc_cache(G, msl, Hkv, D, bits)
+    ocv, ovn = tqo.alloc_cache(G, msl, Hkv, D, bits)
+    # all G sequences share the prompt (GRPO rollouts of one prompt)
+    k, v = synth.kv_batch(rng, prompt, kv_dim, scales)
+    for g in range(G):
+        eng.prefill_append(0, g, gu.dev(k), gu.dev(v), 0)
+        tqo.append_tokens(ock[g * msl:], okn[g * msl:], k, R, np.arange(prompt, dtype=np.int32), msl, Hkv, D, bits)
+        tqo.append_tokens(ocv[g * msl:], ovn[g * msl:], v, R, np.arange(prompt, dtype=np.int32), msl, Hkv, D, bits)
+    eng.set_positions([prompt] * G)
+    worst = 0.0
+    for step in range(new_tokens):
+        pos = np.full(G, prompt + step, np.int32)
+        k, v = synth.kv_batch(rng, G, kv_dim, scales)
+        q = synth.q_batch(rng, G, q_dim)
+        out = gu.host(eng.decode_layer(0, gu.dev(q), gu.dev(k), gu.dev(v)))
+        eng.advance()
+        tqo.append_batch(ock, okn, k, R, pos, msl, Hkv, D, bits)
+        tqo.append_batch(ocv, ovn, v, R, pos, msl, Hkv, D, bits)
+        if step % 8 == 0 or step == new_tokens - 1:  # the oracle is the slow side
+            ref, _ = tqo.attention_batch(q, ock, ocv, okn, ovn, R, pos, msl, H, Hkv, D, bits)
+            w, _ = hp.assert_attention_close(out, ref, H, D, f"step {step}")
+            worst = max(worst, w)
+    assert (eng.positions().numpy() == prompt + new_tokens).all()
+    gk, gv, gkn, gvn = (gu.host(t) for t in eng.layer_cache(0))
+    a = hp.unpack_codes(gk.reshape(G * msl, Hkv, -1), bits)
+    b = hp.unpack_codes(ock.reshape(G * msl, Hkv, -1), bits)
+    n_bad = int((a != b).sum())
+    print(f"C0 loop: worst attention max-abs {worst:.2e}; {n_bad} of {G * (prompt + new_tokens) * Hkv * D} K coordinates differ from the oracle")
+    assert n_bad <= 8
+    assert np.abs(gkn.view(np.uint16).astype(np.int32) - okn.view(np.uint16).astype(np.int32)).max() <= 1
+
+
+@pytest.mark.parametrize("bits", [4, 2, 0])
+def test_ragged_slots_external_arena_and_host_step(bits):
+    H, Hkv, D, NL = 32, 8, 128, 3
+    kv_dim, q_dim = Hkv * D, H * D
+    lengths = [130, 1, 64, 700, 33]
+    caps = [n + 4 for n in lengths]
+    G = len(lengths)
+    rng = np.random.default_rng(1)
+    R = tq.ops.rotation_matrix().numpy()
+    eng = tq.Engine(1024, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    need = eng.arena_bytes(G, 1024, caps)
+    assert need < eng.arena_bytes(G, 1024)
+    arena = torch.empty(need + 4096, dtype=torch.uint8, device="cuda")
+    canary = arena[need:]
+    canary.fill_(0xA5)
+    eng.set_arena(arena.data_ptr(), need, keep_alive=arena)
+    eng.alloc_batch(G, 1024, caps)
+    # an arena that is too small is refused, and caller memory is never replaced
+    small = tq.Engine(1024, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    small.set_arena(arena.data_ptr(), 4096, keep_alive=arena)
+    with pytest.raises(tq.TqError) as e:
+        small.alloc_batch(G, 1024, caps)
+    assert e.value.status == -2
+    # fill the prompts, keep an oracle copy per sequence
+    o = []
+    for layer in range(NL):
+        per_seq = []
+        for g, n in enumerate(lengths):
+            k = rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16)
+            v = rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16)
+            if n > 1:
+                eng.prefill_append(layer, g, gu.dev(k[:-1]), gu.dev(v[:-1]), 0)
+            per_seq.append((k, v))
+        o.append(per_seq)
+    with pytest.raises(tq.TqError):
+        eng.prefill_append(0, 1, gu.dev(np.zeros((10, kv_dim), np.float16)), gu.dev(np.zeros((10, kv_dim), np.float16)), 0)
+    with pytest.raises(tq.TqError):
+        eng.set_positions([c for c in caps[:-1]] + [10 ** 6])
+    eng.set_positions([n - 1 for n in lengths])
+    # one decode step from host buffers: the last token of every sequence is appended by the step itself
+    qh = torch.from_numpy(rng.standard_normal((NL, G, q_dim), dtype=np.float32).astype(np.float16)).pin_memory()
+    kh = torch.from_numpy(np.stack([np.stack([o[l][g][0][-1] for g in range(G)]) for l in range(NL)])).pin_memory()
+    vh = torch.from_numpy(np.stack([np.stack([o[l][g][1][-1] for g in range(G)]) for l in range(NL)])).pin_memory()
+    outh = torch.empty(NL, G, q_dim, dtype=torch.float16).pin_memory()
+    eng.decode_step_host(qh, kh, vh, outh)
+    for layer in range(NL):
+        for g, n in enumerate(lengths):
+            k, v = o[layer][g]
+            q = qh[layer, g].numpy()
+            if bits == 0:
+                ref, _ = tqo.fp16_attention_single(q, k, v, n - 1, n, H, Hkv, D)
+            else:
+                cq, cn = tqo.alloc_cache(1, n, Hkv, D, bits)
+                vq, vn = tqo.alloc_cache(1, n, Hkv, D, bits)
+                tqo.append_tokens(cq, cn, k, R, np.arange(n, dtype=np.int32), n, Hkv, D, bits)
+                tqo.append_tokens(vq, vn, v, R, np.arange(n, dtype=np.int32), n, Hkv, D, bits)
+                ref, _ = tqo.attention_single(q, cq, vq, cn, vn, R, n - 1, n, H, Hkv, D, bits)
+            hp.assert_attention_close(outh[layer, g].numpy()[None], ref[None], H, D, f"bits={bits} layer {layer} seq {g}")
+    torch.cuda.synchronize()
+    assert (canary.cpu().numpy() == 0xA5).all(), "wrote past the end of the caller's arena"
+    # sleep drops the arena, wake + alloc brings an internal one back
+    eng.sleep()
+    with pytest.raises(tq.TqError) as e:
+        eng.alloc_batch(G, 64)
+    assert e.value.status == -5
+    eng.wake()
+    eng.alloc_batch(2, 64)
+    assert (eng.positions().numpy() == 0).all()
+    eng.reset()
+
+
+def test_graph_replay_equals_eager():
+    """Append + attention + position increment captured once and replayed: the launch geometry does not depend
+    on the (device-side) positions, as the reference's captured decode loop requires."""
+    H, Hkv, D, G, bits, msl, steps = 16, 8, 128, 4, 4, 256, 48
+    kv_dim, q_dim = Hkv * D, H * D
+    rng = np.random.default_rng(2)
+    ks = gu.dev(rng.standard_normal((steps, G, kv_dim), dtype=np.float32).astype(np.float16))
+    vs = gu.dev(rng.standard_normal((steps, G, kv_dim), dtype=np.float32).astype(np.float16))
+    qs = gu.dev(rng.standard_normal((steps, G, q_dim), dtype=np.float32).astype(np.float16))
+    start = [0, 5, 40, 100]
+
+    def run(use_graph):
+        eng = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+        eng.alloc_batch(G, msl)
+        eng.reset(zero_cache=True)
+        eng.set_positions(start)
+        k, v, q = torch.empty_like(ks[0]), torch.empty_like(vs[0]), torch.empty_like(qs[0])
+        out = torch.empty_like(q)
+        outs = []
+        side = torch.cuda.Stream()
+        graph = None
+        if use_graph:
+            k.copy_(ks[0]); v.copy_(vs[0]); q.copy_(qs[0])
+            torch.cuda.synchronize()
+            # warm-up outside the capture (module load, attribute set), then rewind the positions
+            eng.decode_layer(0, q, k, v, out)
+            eng.set_positions(start)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                eng.decode_layer(0, q, k, v, out)
+                eng.advance()
+        for s in range(steps):
+            k.copy_(ks[s]); v.copy_(vs[s]); q.copy_(qs[s])
+            if use_graph:
+                graph.replay()
+            else:
+                eng.decode_layer(0, q, k, v, out)
+                eng.advance()
+            torch.cuda.synchronize()
+            outs.append(out.clone())
+        cache = [t.clone() for t in eng.layer_cache(0)]
+        return torch.stack(outs), cache, eng.positions()
+
+    o_e, c_e, p_e = run(False)
+    o_g, c_g, p_g = run(True)
+    assert (p_e == p_g).all() and (p_e.numpy() == np.array(start) + steps).all()
+    for a, b in zip(c_e, c_g):
+        assert torch.equal(a, b), "cache bytes differ between eager and graph replay"
+    assert torch.equal(o_e.view(torch.int16), o_g.view(torch.int16)), "outputs differ between eager and graph replay"
+
+
+def test_full_size_layer_properties():
+    """One layer at the benchmark's size (64 sequences x 4096 tokens, 4-bit): sequences come in groups of four
+    identical rollouts -> outputs identical within a group; two sampled sequences are checked against the oracle;
+    appending the same token twice is idempotent."""
+    H, Hkv, D, G, bits, msl = 16, 8, 128, 64, 4, 4096
+    kv_dim, q_dim = Hkv * D, H * D
+    L = 4096
+    R = tq.ops.rotation_matrix().numpy()
+    eng = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, msl)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    keep = {}
+    for p in range(G // 4):
+        k, v = synth.torch_kv(gen, L - 1, kv_dim, scales)
+        for j in range(4):
+            eng.prefill_append(0, 4 * p + j, k, v, 0)
+        if p in (0, 9):
+            keep[p] = (gu.host(k), gu.host(v))
+    eng.set_positions([L - 1] * G)
+    k_new, v_new = synth.torch_kv(gen, G // 4, kv_dim, scales)
+    k_new, v_new = k_new.repeat_interleave(4, 0).contiguous(), v_new.repeat_interleave(4, 0).contiguous()
+    q = torch.randn(G // 4, q_dim, generator=gen, device="cuda").to(torch.float16).repeat_interleave(4, 0).contiguous()
+    out = gu.host(eng.decode_layer(0, q, k_new, v_new))
+    cache1 = [t.clone() for t in eng.layer_cache(0)]
+    out2 = gu.host(eng.decode_layer(0, q, k_new, v_new))  # same token at the same position again
+    for a, b in zip(cache1, eng.layer_cache(0)):
+        assert torch.equal(a, b), "re-appending the same token changed the cache"
+    assert (out.view(np.uint16) == out2.view(np.uint16)).all()
+    o4 = out.reshape(G // 4, 4, q_dim)
+    assert (o4.view(np.uint16) == o4[:, :1].view(np.uint16)).all(), "identical rollouts gave different outputs"
+    for p, (kh, vh) in keep.items():
+        g = 4 * p
+        kk = np.concatenate([kh, gu.host(k_new[g:g + 1])])
+        vv = np.concatenate([vh, gu.host(v_new[g:g + 1])])
+        cq, cn = tqo.alloc_cache(1, L, Hkv, D, bits)
+        vq, vn = tqo.alloc_cache(1, L, Hkv, D, bits)
+        tqo.append_tokens(cq, cn, kk, R, np.arange(L, dtype=np.int32), L, Hkv, D, bits)
+        tqo.append_tokens(vq, vn, vv, R, np.arange(L, dtype=np.int32), L, Hkv, D, bits)
+        ref, _ = tqo.attention_single(gu.host(q[g]), cq, vq, cn, vn, R, L - 1, L, H, Hkv, D, bits)
+        w, r = hp.assert_attention_close(out[g][None], ref[None], H, D, f"full-size sequence {g}")
+        print(f"full-size sequence {g}: max-abs {w:.2e}, rel {r:.2e}")

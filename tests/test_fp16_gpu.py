@@ -1,0 +1,83 @@
+"""GPU parity of the kv_bits = 0 twin (fp16 cache write + GQA decode attention) against the oracle and the
+committed outputs of the reference's own kernels."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import tqo
+from tests import helpers as hp
+
+pytestmark = pytest.mark.gpu
+gu = pytest.importorskip("tests.gpu_util")
+from triebwerk_b200 import ops  # noqa: E402
+
+
+def _fill(rng, G, lengths, msl, kv_dim):
+    ck = np.zeros((G * msl, kv_dim), np.float16)
+    cv = np.zeros_like(ck)
+    for g, n in enumerate(lengths):
+        ck[g * msl:g * msl + n] = rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16)
+        cv[g * msl:g * msl + n] = rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16)
+    return ck, cv
+
+
+def test_cache_write_is_a_row_copy():
+    rng = np.random.default_rng(0)
+    G, kv_dim, msl = 5, 1024, 40
+    k = rng.standard_normal((G, kv_dim), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((G, kv_dim), dtype=np.float32).astype(np.float16)
+    pos = np.array([0, 39, 7, 20, 1], np.int32)
+    dck = torch.zeros(G * msl, kv_dim, dtype=torch.float16, device="cuda")
+    dcv = torch.zeros_like(dck)
+    ops.launch_kv_cache_write_batch(dck, dcv, gu.dev(k), gu.dev(v), gu.dev(pos), msl, G, kv_dim)
+    ock = np.zeros((G * msl, kv_dim), np.float16)
+    ocv = np.zeros_like(ock)
+    tqo.fp16_write_batch(ock, ocv, k, v, pos, msl)
+    assert (gu.host(dck).view(np.uint16) == ock.view(np.uint16)).all()
+    assert (gu.host(dcv).view(np.uint16) == ocv.view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("H", [8, 16, 32])
+def test_fp16_attention_ragged(H):
+    rng = np.random.default_rng(1 + H)
+    Hkv, D, msl = 8, 128, 1100
+    lengths = [1, 2, 31, 32, 33, 511, 512, 513, 1024, 1100]
+    G = len(lengths)
+    ck, cv = _fill(rng, G, lengths, msl, Hkv * D)
+    # rows past the position must be ignored even when they hold NaN
+    for g, n in enumerate(lengths):
+        ck[g * msl + n:(g + 1) * msl] = np.float16(np.nan)
+        cv[g * msl + n:(g + 1) * msl] = np.float16(np.nan)
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    ref, _ = tqo.fp16_attention_batch(q, ck, cv, pos, msl, H, Hkv, D)
+    out = torch.zeros(G, H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_attention_batch(out, gu.dev(q), gu.dev(ck), gu.dev(cv), None, gu.dev(pos), msl, G, H, Hkv, D, H * D,
+                                   Hkv * D)
+    worst, rel = hp.assert_attention_close(gu.host(out), ref, H, D, f"fp16 H={H}")
+    print(f"fp16 H={H}: max-abs {worst:.2e}, rel {rel:.2e}")
+    g = G - 1
+    o1 = torch.zeros(H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_attention(gu.dev(q[g]), gu.dev(ck[g * msl:(g + 1) * msl]), gu.dev(cv[g * msl:(g + 1) * msl]), o1, None,
+                             int(pos[g]), msl, H, Hkv, D)
+    r1, _ = tqo.fp16_attention_single(q[g], ck[g * msl:(g + 1) * msl], cv[g * msl:(g + 1) * msl], int(pos[g]), msl, H,
+                                      Hkv, D)
+    hp.assert_attention_close(gu.host(o1)[None], r1[None], H, D, "fp16 single")
+
+
+def test_fp16_against_reference_kernel_outputs():
+    g = hp.load_golden("ref_kernels_fp16.npz")
+    if g is None:
+        pytest.skip("fixture not generated yet")
+    H, Hkv, D, msl = int(g["H"]), int(g["Hkv"]), int(g["D"]), int(g["msl"])
+    k_steps, v_steps = hp.h(g["k_steps"]), hp.h(g["v_steps"])
+    G = k_steps.shape[1]
+    dck = torch.zeros(G * msl, Hkv * D, dtype=torch.float16, device="cuda")
+    dcv = torch.zeros_like(dck)
+    for s in range(k_steps.shape[0]):
+        ops.launch_kv_cache_write_batch(dck, dcv, gu.dev(k_steps[s]), gu.dev(v_steps[s]), gu.dev(g["pos_steps"][s]), msl,
+                                        G, Hkv * D)
+    out = torch.zeros(G, H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_attention_batch(out, gu.dev(hp.h(g["q"])), dck, dcv, None, gu.dev(g["final_pos"]), msl, G, H, Hkv, D,
+                                   H * D, Hkv * D)
+    hp.assert_attention_close(gu.host(out), hp.h(g["out"]), H, D, "fp16 vs reference kernels")

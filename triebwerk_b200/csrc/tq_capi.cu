@@ -1,0 +1,712 @@
+// extern "C" surface of libtriebwerk_b200.so (declared in include/triebwerk_b200.h).
+// The whole library is this one translation unit; kernels live in the .cuh files it includes.
+
+#include "tq_host.cuh"
+
+using namespace tq;
+
+static thread_local int g_compat_status = TQ_OK;
+
+static inline cudaStream_t cs(tq_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+const char* tq_status_string(int status) {
+    switch (status) {
+        case TQ_OK: return "ok";
+        case TQ_ERR_ARG: return "bad argument";
+        case TQ_ERR_CAPACITY: return "capacity exceeded";
+        case TQ_ERR_WORKSPACE: return "workspace missing or too small";
+        case TQ_ERR_UNSUPPORTED: return "unsupported shape";
+        case TQ_ERR_STATE: return "engine in the wrong state";
+        case TQ_ERR_DEVICE: return "device-side status set";
+        case TQ_ERR_NOMEM: return "out of memory";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int tq_version(void) { return 100; }
+
+int tq_last_compat_status(void) { return g_compat_status; }
+
+// ---- rotation ---------------------------------------------------------------------------------------------------------
+// Restates engine/engine.cpp:364-392.  An x86-64 build of the reference rounds after every multiply and
+// every add (no FMA contraction); the volatile temporaries below keep that whatever flags build this file.
+int tq_rotation_generate(uint32_t seed, void* host_out_half) {
+    if (!host_out_half) return TQ_ERR_ARG;
+    const int d = HEAD_DIM;
+    std::mt19937 gen(seed);
+    std::normal_distribution<float> dist(0.0f, 1.0f);
+    std::vector<float> m((size_t)d * d);
+    for (auto& x : m) x = dist(gen);
+    for (int i = 0; i < d; ++i) {
+        float* ri = &m[(size_t)i * d];
+        for (int j = 0; j < i; ++j) {
+            const float* rj = &m[(size_t)j * d];
+            volatile float dot = 0.0f;  // volatile: keep every rounding step, whatever the host flags
+            for (int k = 0; k < d; ++k) {
+                volatile float prod = ri[k] * rj[k];
+                dot = dot + prod;
+            }
+            for (int k = 0; k < d; ++k) {
+                volatile float prod = dot * rj[k];
+                ri[k] = ri[k] - prod;
+            }
+        }
+        volatile float nrm = 0.0f;
+        for (int k = 0; k < d; ++k) {
+            volatile float prod = ri[k] * ri[k];
+            nrm = nrm + prod;
+        }
+        const float inv = 1.0f / sqrtf(nrm);
+        for (int k = 0; k < d; ++k) ri[k] *= inv;
+    }
+    __half* out = reinterpret_cast<__half*>(host_out_half);
+    for (int i = 0; i < d * d; ++i) out[i] = __float2half_rn(m[i]);
+    return TQ_OK;
+}
+
+size_t tq_workspace_bytes(int G, int num_heads) {
+    if (G <= 0 || num_heads <= 0) return 0;
+    return carve_full(nullptr, G, num_heads).bytes;
+}
+
+int tq_workspace_status(void* workspace, tq_stream_t s) {
+    if (!workspace) return TQ_ERR_WORKSPACE;
+    int st = 0;
+    TQ_CUDA(cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, cs(s)));
+    TQ_CUDA(cudaStreamSynchronize(cs(s)));
+    if (st != 0) {
+        TQ_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), cs(s)));
+        TQ_CUDA(cudaStreamSynchronize(cs(s)));
+    }
+    return st;
+}
+
+// ---- packed path ---------------------------------------------------------------------------------------------------------
+static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf, const void* v_buf,
+                       const void* q, const void* rotation, const int* positions, int pos_value,
+                       const long long* row_base, int token_mode, long long token_row0, int max_seq_len, int n_src,
+                       int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
+                       size_t workspace_bytes, bool build_tiles, cudaStream_t s) {
+    if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
+    if (bits != 2 && bits != 4) return TQ_ERR_ARG;
+    if (n_src <= 0 || num_kv_heads <= 0 || kv_dim != num_kv_heads * head_dim || !rotation) return TQ_ERR_ARG;
+    if ((k_buf && (!ck_q || !k_norms)) || (v_buf && (!cv_q || !v_norms))) return TQ_ERR_ARG;
+    if (q && (num_heads <= 0 || q_dim < num_heads * head_dim)) return TQ_ERR_ARG;
+    if (!workspace) return TQ_ERR_WORKSPACE;
+    const int Hws = num_heads > 0 ? num_heads : 1;
+    FullWorkspace fw = carve_full(workspace, n_src, Hws);
+    if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
+    AppendParams p{};
+    p.ck = ck_q; p.kn = (__half*)k_norms; p.cv = cv_q; p.vn = (__half*)v_norms;
+    p.k_buf = (const __half*)k_buf; p.v_buf = (const __half*)v_buf; p.q = (const __half*)q;
+    p.rotation = (const __half*)rotation;
+    p.positions = positions; p.row_base = row_base;
+    p.q_rot = fw.w.q_rot;
+    p.tile_start = build_tiles ? fw.w.tile_start : nullptr;
+    p.tickets = build_tiles ? fw.w.tickets : nullptr;
+    p.total_tiles = fw.w.total_tiles;
+    p.status = fw.w.status;
+    p.token_row0 = token_row0; p.token_mode = token_mode;
+    p.max_seq_len = max_seq_len; p.capacity_rows = max_seq_len;
+    p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
+    p.pos_value = pos_value;
+    return launch_append(p, s);
+}
+
+int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf, const void* v_buf,
+                     const void* q, const void* rotation, const int* positions, const long long* row_base,
+                     int max_seq_len, int G, int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim,
+                     int bits, void* workspace, size_t workspace_bytes, tq_stream_t s) {
+    if (!positions) return TQ_ERR_ARG;
+    return append_impl(ck_q, k_norms, cv_q, v_norms, k_buf, v_buf, q, rotation, positions, 0, row_base, 0, 0,
+                       max_seq_len, G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, workspace,
+                       workspace_bytes, true, cs(s));
+}
+
+static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* k_norms,
+                          const void* v_norms, const void* rotation, const int* positions, int pos_value,
+                          const long long* row_base, int max_seq_len, int G, int num_heads, int num_kv_heads,
+                          int q_dim, int bits, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+    FullWorkspace fw = carve_full(workspace, G, num_heads);
+    if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
+    AttnParams p{};
+    p.kn = (const __half*)k_norms; p.vn = (const __half*)v_norms;
+    p.q_rot = fw.w.q_rot; p.rotation = (const __half*)rotation; p.out = (__half*)out;
+    p.positions = positions; p.row_base = row_base;
+    p.tile_start = fw.w.tile_start; p.tickets = fw.w.tickets; p.partials = fw.w.partials; p.status = fw.w.status;
+    p.pos_value = pos_value; p.max_seq_len = max_seq_len;
+    p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim;
+    return launch_attention(bits, tmK, tmV, p, attention_workers(G, max_seq_len), s);
+}
+
+int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms, const void* v_norms,
+                        const void* rotation, const int* positions, int pos_value, const long long* row_base,
+                        long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int head_dim,
+                        int q_dim, int kv_dim, int bits, void* workspace, size_t workspace_bytes, tq_stream_t s) {
+    int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    if (r != TQ_OK) return r;
+    if (!out || !ck_q || !cv_q || !k_norms || !v_norms || !rotation) return TQ_ERR_ARG;
+    if (!positions && pos_value < 0) return TQ_ERR_ARG;
+    if (!workspace) return TQ_ERR_WORKSPACE;
+    const int vpb = bits == 2 ? 4 : 2;
+    CUtensorMap tmK, tmV;
+    r = cached_code_map(&tmK, ck_q, total_rows, kv_dim / vpb, head_dim / vpb);
+    if (r != TQ_OK) return r;
+    r = cached_code_map(&tmV, cv_q, total_rows, kv_dim / vpb, head_dim / vpb);
+    if (r != TQ_OK) return r;
+    return attention_impl(out, tmK, tmV, k_norms, v_norms, rotation, positions, pos_value, row_base, max_seq_len, G,
+                          num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
+}
+
+// ---- fp16 twin ---------------------------------------------------------------------------------------------------------
+int tq_fp16_append_decode(void* ck, void* cv, const void* k_buf, const void* v_buf, const int* positions,
+                          const long long* row_base, int max_seq_len, int G, int kv_dim, tq_stream_t s) {
+    if (!ck || !cv || !k_buf || !v_buf || !positions || G <= 0 || kv_dim <= 0 || kv_dim % 8 != 0) return TQ_ERR_ARG;
+    fp16_cache_write_kernel<<<G, 128, 0, cs(s)>>>((__half*)ck, (__half*)cv, (const __half*)k_buf, (const __half*)v_buf,
+                                                  positions, row_base, max_seq_len, max_seq_len, G, kv_dim, nullptr);
+    return cuda_status(cudaGetLastError());
+}
+
+int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const void* cv, const int* positions,
+                             int pos_value, const long long* row_base, long long total_rows, int max_seq_len, int G,
+                             int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, void* workspace,
+                             size_t workspace_bytes, tq_stream_t s) {
+    (void)total_rows;
+    int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
+    if (r != TQ_OK) return r;
+    if (!out || !q || !ck || !cv) return TQ_ERR_ARG;
+    if (!positions && pos_value < 0) return TQ_ERR_ARG;
+    if (!workspace) return TQ_ERR_WORKSPACE;
+    // fp16 layout of the workspace: [0,256) header, tickets int[G*Hkv], partials
+    const size_t tick_bytes = align_up((size_t)G * num_kv_heads * sizeof(int), 256);
+    const size_t need = 256 + tick_bytes + fp16_partials_bytes(G, num_heads, max_seq_len);
+    if (need > workspace_bytes) return TQ_ERR_WORKSPACE;
+    char* base = (char*)workspace;
+    Fp16AttnParams p{};
+    p.q = (const __half*)q; p.ck = (const __half*)ck; p.cv = (const __half*)cv; p.out = (__half*)out;
+    p.positions = positions; p.row_base = row_base;
+    p.tickets = (int*)(base + 256); p.partials = (float*)(base + 256 + tick_bytes); p.status = (int*)base;
+    p.pos_value = pos_value; p.max_seq_len = max_seq_len;
+    p.nchunk_max = (max_seq_len + FP16_CHUNK - 1) / FP16_CHUNK;
+    p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim;
+    TQ_CUDA(cudaMemsetAsync(p.tickets, 0, (size_t)G * num_kv_heads * sizeof(int), cs(s)));
+    return launch_fp16_attention(p, cs(s));
+}
+
+static size_t fp16_workspace_bytes(int G, int H, int Hkv, int max_seq_len) {
+    return 256 + align_up((size_t)G * Hkv * sizeof(int), 256) + fp16_partials_bytes(G, H, max_seq_len);
+}
+
+// ===================================================================================================================
+// Reference-compatible launchers
+// ===================================================================================================================
+void launch_turbo_kv_quantize(uint8_t* cache_q, void* cache_norms, const void* kv_buf, const void* rotation,
+                              const int* positions, int max_seq_len, int num_tokens, int num_kv_heads, int head_dim,
+                              int kv_dim, int bits, tq_stream_t s) {
+    void* ws = nullptr;
+    const size_t need = carve_full(nullptr, num_tokens > 0 ? num_tokens : 1, 1).bytes;
+    int r = compat_workspace(need, &ws, cs(s));
+    if (r == TQ_OK)
+        r = append_impl(cache_q, cache_norms, nullptr, nullptr, kv_buf, nullptr, nullptr, rotation, positions, 0,
+                        nullptr, 1, 0, max_seq_len, num_tokens, 0, num_kv_heads, head_dim, 0, kv_dim,
+                        bits == 4 ? 4 : 2, ws, need, false, cs(s));
+    g_compat_status = r;
+}
+
+void launch_turbo_kv_quantize_batch(uint8_t* cache_q, void* cache_norms, const void* kv_buf, const void* rotation,
+                                    const int* positions, int max_seq_len, int G, int num_kv_heads, int head_dim,
+                                    int kv_dim, int bits, tq_stream_t s) {
+    void* ws = nullptr;
+    const size_t need = carve_full(nullptr, G > 0 ? G : 1, 1).bytes;
+    int r = compat_workspace(need, &ws, cs(s));
+    if (r == TQ_OK)
+        r = append_impl(cache_q, cache_norms, nullptr, nullptr, kv_buf, nullptr, nullptr, rotation, positions, 0,
+                        nullptr, 0, 0, max_seq_len, G, 0, num_kv_heads, head_dim, 0, kv_dim, bits == 4 ? 4 : 2, ws,
+                        need, false, cs(s));
+    g_compat_status = r;
+}
+
+void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
+                                      const void* k_norms, const void* v_norms, const void* rotation, float* as,
+                                      const int* pos, int msl, int G, int num_heads, int num_kv_heads, int head_dim,
+                                      int q_dim, int kv_dim, int bits, tq_stream_t s) {
+    (void)as;
+    bits = bits == 4 ? 4 : 2;  // the reference treats anything that is not 4 as 2-bit
+    int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    void* ws = nullptr;
+    size_t need = 0;
+    if (r == TQ_OK) {
+        need = carve_full(nullptr, G, num_heads).bytes;
+        r = compat_workspace(need, &ws, cs(s));
+    }
+    if (r == TQ_OK)
+        r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, pos, 0, nullptr, 0, 0, msl, G,
+                        num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
+    if (r == TQ_OK)
+        r = tq_decode_attention(out, ck_q, cv_q, k_norms, v_norms, rotation, pos, -1, nullptr, (long long)G * msl, msl,
+                                G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, s);
+    g_compat_status = r;
+}
+
+void launch_turbo_gqa_attention(const void* q, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms,
+                                const void* v_norms, const void* rotation, void* output, float* as, int pos, int msl,
+                                int num_heads, int num_kv_heads, int head_dim, int bits, tq_stream_t s) {
+    (void)as;
+    bits = bits == 4 ? 4 : 2;
+    const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
+    int r = check_shape(1, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    if (r == TQ_OK && (pos < 0 || pos >= msl)) r = TQ_ERR_CAPACITY;
+    void* ws = nullptr;
+    size_t need = 0;
+    if (r == TQ_OK) {
+        need = carve_full(nullptr, 1, num_heads).bytes;
+        r = compat_workspace(need, &ws, cs(s));
+    }
+    if (r == TQ_OK)
+        r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, nullptr, pos, nullptr, 0, 0,
+                        msl, 1, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
+    if (r == TQ_OK)
+        r = tq_decode_attention(output, ck_q, cv_q, k_norms, v_norms, rotation, nullptr, pos, nullptr, msl, msl, 1,
+                                num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, s);
+    g_compat_status = r;
+}
+
+void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
+                                        const void* k_norms, const void* v_norms, const void* rotation, float* as,
+                                        int T, int msl, int num_heads, int num_kv_heads, int head_dim, int q_dim,
+                                        int kv_dim, int bits, tq_stream_t s) {
+    (void)as;
+    // Query tq attends to rows 0..tq of ONE sequence: run the decode kernel with T "sequences" that all start
+    // at row 0 and have positions 0..T-1.
+    bits = bits == 4 ? 4 : 2;
+    int r = check_shape(T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    if (r == TQ_OK && T > msl) r = TQ_ERR_CAPACITY;
+    void* ws = nullptr;
+    size_t need = 0;
+    if (r == TQ_OK) {
+        need = carve_full(nullptr, T, num_heads).bytes;
+        r = compat_workspace(need, &ws, cs(s));
+    }
+    if (r == TQ_OK) {
+        FullWorkspace fw = carve_full(ws, T, num_heads);
+        iota_rows_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(fw.aux_pos, fw.aux_rows, T, 0);
+        r = cuda_status(cudaGetLastError());
+        if (r == TQ_OK)
+            r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, fw.aux_pos, 0, fw.aux_rows,
+                            0, 0, msl, T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
+        if (r == TQ_OK)
+            r = tq_decode_attention(out, ck_q, cv_q, k_norms, v_norms, rotation, fw.aux_pos, -1, fw.aux_rows, msl, msl, T,
+                                    num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, s);
+    }
+    g_compat_status = r;
+}
+
+void launch_kv_cache_write_batch(void* ck, void* cv, const void* k, const void* v, const int* pos, int msl, int G,
+                                 int kv_dim, tq_stream_t s) {
+    g_compat_status = tq_fp16_append_decode(ck, cv, k, v, pos, nullptr, msl, G, kv_dim, s);
+}
+
+void launch_gqa_attention_batch(void* out, const void* q, const void* ck, const void* cv, float* as, const int* pos,
+                                int msl, int G, int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim,
+                                tq_stream_t s) {
+    (void)as;
+    void* ws = nullptr;
+    int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
+    size_t need = 0;
+    if (r == TQ_OK) {
+        need = fp16_workspace_bytes(G, num_heads, num_kv_heads, msl);
+        r = compat_workspace(need, &ws, cs(s));
+    }
+    if (r == TQ_OK)
+        r = tq_fp16_decode_attention(out, q, ck, cv, pos, -1, nullptr, (long long)G * msl, msl, G, num_heads,
+                                     num_kv_heads, head_dim, q_dim, kv_dim, ws, need, s);
+    g_compat_status = r;
+}
+
+void launch_gqa_attention(const void* q, const void* k_cache, const void* v_cache, void* output, float* attn_scratch,
+                          int pos, int max_seq_len, int num_heads, int num_kv_heads, int head_dim, tq_stream_t stream) {
+    (void)attn_scratch;
+    const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
+    void* ws = nullptr;
+    int r = check_shape(1, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
+    if (r == TQ_OK && (pos < 0 || pos >= max_seq_len)) r = TQ_ERR_CAPACITY;
+    size_t need = 0;
+    if (r == TQ_OK) {
+        need = fp16_workspace_bytes(1, num_heads, num_kv_heads, max_seq_len);
+        r = compat_workspace(need, &ws, cs(stream));
+    }
+    if (r == TQ_OK)
+        r = tq_fp16_decode_attention(output, q, k_cache, v_cache, nullptr, pos, nullptr, max_seq_len, max_seq_len, 1,
+                                     num_heads, num_kv_heads, head_dim, q_dim, kv_dim, ws, need, stream);
+    g_compat_status = r;
+}
+
+// ===================================================================================================================
+// Engine / arena
+// ===================================================================================================================
+int tq_engine_create(const tq_model_shape* shape, int max_seq_len, int kv_bits, tq_engine** out) {
+    if (!shape || !out) return TQ_ERR_ARG;
+    if (shape->num_layers <= 0 || shape->num_heads <= 0 || shape->num_kv_heads <= 0 ||
+        shape->num_heads % shape->num_kv_heads != 0 || max_seq_len <= 0)
+        return TQ_ERR_ARG;
+    if (shape->head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
+    if (kv_bits != 0 && kv_bits != 2 && kv_bits != 4) {
+        fprintf(stderr, "WARNING: kv_bits=%d not supported, using 0 (fp16)\n", kv_bits);
+        kv_bits = 0;
+    }
+    tq_engine* e = new (std::nothrow) tq_engine();
+    if (!e) return TQ_ERR_NOMEM;
+    e->shape = *shape;
+    e->ctor_max_seq_len = max_seq_len;
+    e->kv_bits = kv_bits;
+    cudaGetDevice(&e->device);
+    e->h_rotation.resize((size_t)HEAD_DIM * HEAD_DIM);
+    tq_rotation_generate(42, e->h_rotation.data());
+    e->layers.resize(shape->num_layers);
+    *out = e;
+    return TQ_OK;
+}
+
+static void engine_release_arena(tq_engine* e) {
+    if (e->arena && !e->arena_external) cudaFree(e->arena);
+    e->arena = nullptr;
+    e->arena_cap = 0;
+    e->arena_external = false;
+    e->G = 0;
+    e->total_rows = 0;
+    e->d_positions = nullptr;
+    e->d_row_base = nullptr;
+    e->workspace = nullptr;
+    for (auto& l : e->layers) l = tq_engine::Layer();
+}
+
+void tq_engine_destroy(tq_engine* e) {
+    if (!e) return;
+    engine_release_arena(e);
+    if (e->d_rotation) cudaFree(e->d_rotation);
+    delete e;
+}
+
+int tq_engine_kv_bits(const tq_engine* e) { return e ? e->kv_bits : TQ_ERR_ARG; }
+
+// One walk of the arena; with base == nullptr it only measures.
+static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long rows, bool ragged, bool assign) {
+    size_t off = 0;
+    const size_t code_bytes = (size_t)rows * e->code_row_bytes();
+    const size_t norm_bytes = (size_t)rows * e->shape.num_kv_heads * 2;
+    for (int l = 0; l < e->shape.num_layers; ++l) {
+        size_t ok = bump(off, code_bytes);
+        size_t ov = bump(off, code_bytes);
+        size_t okn = 0, ovn = 0;
+        if (e->kv_bits != 0) {
+            okn = bump(off, norm_bytes);
+            ovn = bump(off, norm_bytes);
+        }
+        if (assign) {
+            tq_engine::Layer& L = e->layers[l];
+            L.k = base + ok;
+            L.v = base + ov;
+            L.kn = e->kv_bits ? base + okn : nullptr;
+            L.vn = e->kv_bits ? base + ovn : nullptr;
+        }
+    }
+    size_t opos = bump(off, (size_t)G * sizeof(int));
+    size_t orb = bump(off, (size_t)G * sizeof(long long));
+    size_t ws_bytes = e->kv_bits ? carve_full(nullptr, G, e->shape.num_heads).bytes
+                                 : fp16_workspace_bytes(G, e->shape.num_heads, e->shape.num_kv_heads, msl);
+    size_t ows = bump(off, ws_bytes);
+    const size_t qb = (size_t)e->shape.num_layers * G * e->q_dim() * 2;
+    const size_t kb = (size_t)e->shape.num_layers * G * e->kv_dim() * 2;
+    size_t oq = bump(off, qb), okk = bump(off, kb), ovv = bump(off, kb), oo = bump(off, qb);
+    if (assign) {
+        e->d_positions = (int*)(base + opos);
+        e->d_row_base = ragged ? (long long*)(base + orb) : nullptr;
+        e->workspace = base + ows;
+        e->ws_bytes = ws_bytes;
+        e->stage_q = base + oq;
+        e->stage_k = base + okk;
+        e->stage_v = base + ovv;
+        e->stage_out = base + oo;
+    }
+    return (off + 255) & ~(size_t)255;
+}
+
+size_t tq_engine_arena_bytes(const tq_engine* e, int G, int max_seq_len, const int* capacities) {
+    if (!e || G <= 0 || max_seq_len <= 0) return 0;
+    long long rows = plan_rows(G, max_seq_len, capacities, nullptr, nullptr);
+    return engine_carve(const_cast<tq_engine*>(e), nullptr, G, max_seq_len, rows, capacities != nullptr, false);
+}
+
+int tq_engine_set_arena(tq_engine* e, void* device_ptr, size_t bytes) {
+    if (!e || !device_ptr || bytes == 0) return TQ_ERR_ARG;
+    if (((uintptr_t)device_ptr & 255u) != 0) return TQ_ERR_ARG;
+    engine_release_arena(e);  // frees only memory this library allocated
+    e->arena = (char*)device_ptr;
+    e->arena_cap = bytes;
+    e->arena_external = true;
+    e->asleep = false;
+    return TQ_OK;
+}
+
+int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capacities) {
+    if (!e || G <= 0 || max_seq_len <= 0) return TQ_ERR_ARG;
+    if (e->asleep) return TQ_ERR_STATE;
+    int r = check_shape(G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim, e->q_dim(), e->kv_dim(),
+                        e->kv_bits, e->kv_bits != 0);
+    if (r != TQ_OK) return r;
+    const bool ragged = capacities != nullptr;
+    // Like alloc_batch (engine/engine.cpp:1338-1443) the arena is re-carved for every new batch shape and
+    // only re-allocated when it is too small.
+    std::vector<int> caps;
+    std::vector<long long> bases;
+    long long rows = plan_rows(G, max_seq_len, capacities, &caps, &bases);
+    if (rows >= (1ll << 31)) return TQ_ERR_CAPACITY;
+    int msl = max_seq_len;
+    if (ragged)
+        for (int c : caps) msl = c > msl ? c : msl;
+    size_t need = engine_carve(e, nullptr, G, msl, rows, ragged, false);
+    if (need > e->arena_cap) {
+        if (e->arena_external) return TQ_ERR_CAPACITY;  // never free or replace caller-owned memory
+        if (e->arena) {
+            cudaDeviceSynchronize();
+            cudaFree(e->arena);
+            e->arena = nullptr;
+            e->arena_cap = 0;
+        }
+        void* p = nullptr;
+        cudaError_t ce = cudaMalloc(&p, need);
+        if (ce != cudaSuccess) {
+            cudaGetLastError();
+            return TQ_ERR_NOMEM;
+        }
+        e->arena = (char*)p;
+        e->arena_cap = need;
+    }
+    e->G = G;
+    e->msl = msl;
+    e->ragged = ragged;
+    e->total_rows = rows;
+    e->capacities = caps;
+    e->h_row_base = bases;
+    engine_carve(e, e->arena, G, msl, rows, ragged, true);
+    TQ_CUDA(cudaMemset(e->d_positions, 0, (size_t)G * sizeof(int)));
+    TQ_CUDA(cudaMemset(e->workspace, 0, e->ws_bytes));
+    if (ragged) TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
+    if (!e->d_rotation) {
+        TQ_CUDA(cudaMalloc(&e->d_rotation, e->h_rotation.size() * 2));
+        TQ_CUDA(cudaMemcpy(e->d_rotation, e->h_rotation.data(), e->h_rotation.size() * 2, cudaMemcpyHostToDevice));
+    }
+    if (e->kv_bits != 0) {
+        const int kvp = e->kv_dim() / e->vpb(), bph = HEAD_DIM / e->vpb();
+        for (auto& L : e->layers) {
+            r = make_code_map(&L.tmK, L.k, rows, kvp, bph);
+            if (r != TQ_OK) return r;
+            r = make_code_map(&L.tmV, L.v, rows, kvp, bph);
+            if (r != TQ_OK) return r;
+        }
+    }
+    return TQ_OK;
+}
+
+int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s) {
+    if (!e) return TQ_ERR_ARG;
+    if (!e->arena || e->G == 0) return TQ_OK;
+    TQ_CUDA(cudaMemsetAsync(e->d_positions, 0, (size_t)e->G * sizeof(int), cs(s)));
+    if (zero_cache) {
+        const size_t code_bytes = (size_t)e->total_rows * e->code_row_bytes();
+        const size_t norm_bytes = (size_t)e->total_rows * e->shape.num_kv_heads * 2;
+        for (auto& L : e->layers) {
+            TQ_CUDA(cudaMemsetAsync(L.k, 0, code_bytes, cs(s)));
+            TQ_CUDA(cudaMemsetAsync(L.v, 0, code_bytes, cs(s)));
+            if (L.kn) TQ_CUDA(cudaMemsetAsync(L.kn, 0, norm_bytes, cs(s)));
+            if (L.vn) TQ_CUDA(cudaMemsetAsync(L.vn, 0, norm_bytes, cs(s)));
+        }
+    }
+    return TQ_OK;
+}
+
+int tq_engine_sleep(tq_engine* e) {
+    if (!e) return TQ_ERR_ARG;
+    TQ_CUDA(cudaDeviceSynchronize());
+    engine_release_arena(e);
+    e->asleep = true;
+    return TQ_OK;
+}
+
+int tq_engine_wake(tq_engine* e) {
+    if (!e) return TQ_ERR_ARG;
+    e->asleep = false;  // the arena comes back lazily with the next tq_engine_alloc_batch, as in the reference
+    return TQ_OK;
+}
+
+int tq_engine_status(tq_engine* e, tq_stream_t s) {
+    if (!e) return TQ_ERR_ARG;
+    if (!e->arena || !e->workspace) return TQ_OK;
+    return tq_workspace_status(e->workspace, s);
+}
+
+int* tq_engine_positions(tq_engine* e) { return e ? e->d_positions : nullptr; }
+
+int tq_engine_set_positions(tq_engine* e, const int* host_positions, int G, tq_stream_t s) {
+    if (!e || !host_positions) return TQ_ERR_ARG;
+    if (!e->arena || G != e->G) return TQ_ERR_STATE;
+    for (int g = 0; g < G; ++g) {
+        int cap = e->ragged ? e->capacities[g] : e->msl;
+        if (host_positions[g] < 0 || host_positions[g] >= cap) return TQ_ERR_CAPACITY;
+    }
+    TQ_CUDA(cudaMemcpyAsync(e->d_positions, host_positions, (size_t)G * sizeof(int), cudaMemcpyHostToDevice, cs(s)));
+    return TQ_OK;
+}
+
+__global__ void advance_positions_kernel(int* pos, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) pos[i] += 1;
+}
+
+int tq_engine_advance(tq_engine* e, tq_stream_t s) {
+    if (!e || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    advance_positions_kernel<<<(e->G + 127) / 128, 128, 0, cs(s)>>>(e->d_positions, e->G);
+    return cuda_status(cudaGetLastError());
+}
+
+int tq_engine_layer_ptrs(tq_engine* e, int layer, void** k_codes, void** v_codes, void** k_norms, void** v_norms,
+                         long long* total_rows) {
+    if (!e || layer < 0 || layer >= e->shape.num_layers) return TQ_ERR_ARG;
+    if (!e->arena || e->G == 0) return TQ_ERR_STATE;
+    const tq_engine::Layer& L = e->layers[layer];
+    if (k_codes) *k_codes = L.k;
+    if (v_codes) *v_codes = L.v;
+    if (k_norms) *k_norms = L.kn;
+    if (v_norms) *v_norms = L.vn;
+    if (total_rows) *total_rows = e->total_rows;
+    return TQ_OK;
+}
+
+const long long* tq_engine_row_base(tq_engine* e) { return e ? e->d_row_base : nullptr; }
+const void* tq_engine_rotation(tq_engine* e) { return e ? e->d_rotation : nullptr; }
+
+int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s) {
+    if (!e || !host_half) return TQ_ERR_ARG;
+    memcpy(e->h_rotation.data(), host_half, e->h_rotation.size() * 2);
+    if (!e->d_rotation) TQ_CUDA(cudaMalloc(&e->d_rotation, e->h_rotation.size() * 2));
+    TQ_CUDA(cudaMemcpyAsync(e->d_rotation, e->h_rotation.data(), e->h_rotation.size() * 2, cudaMemcpyHostToDevice, cs(s)));
+    TQ_CUDA(cudaStreamSynchronize(cs(s)));
+    return TQ_OK;
+}
+
+int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
+                           tq_stream_t s) {
+    if (!e || layer < 0 || layer >= e->shape.num_layers || !q || !k || !v || !out) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    const tq_engine::Layer& L = e->layers[layer];
+    const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, D = e->shape.head_dim;
+    if (e->kv_bits == 0) {
+        fp16_cache_write_kernel<<<e->G, 128, 0, cs(s)>>>((__half*)L.k, (__half*)L.v, (const __half*)k, (const __half*)v,
+                                                         e->d_positions, e->d_row_base, e->msl, e->msl, e->G,
+                                                         e->kv_dim(), (int*)e->workspace);
+        int r = cuda_status(cudaGetLastError());
+        if (r != TQ_OK) return r;
+        return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->d_row_base, e->total_rows, e->msl, e->G,
+                                        H, Hkv, D, e->q_dim(), e->kv_dim(), e->workspace, e->ws_bytes, s);
+    }
+    int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
+                        e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
+                        e->ws_bytes, true, cs(s));
+    if (r != TQ_OK) return r;
+    return attention_impl(out, L.tmK, L.tmV, L.kn, L.vn, e->d_rotation, e->d_positions, -1, e->d_row_base, e->msl, e->G,
+                          H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s));
+}
+
+int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
+    if (!e || layer < 0 || layer >= e->shape.num_layers || !out) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
+    const tq_engine::Layer& L = e->layers[layer];
+    return attention_impl(out, L.tmK, L.tmV, L.kn, L.vn, e->d_rotation, e->d_positions, -1, e->d_row_base, e->msl, e->G,
+                          e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
+                          cs(s));
+}
+
+int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {
+    if (!e || !q || !k || !v || !out) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
+    for (int l = 0; l < e->shape.num_layers; ++l) {
+        int r = tq_engine_decode_layer(e, l, (const char*)q + qb * l, (const char*)k + kb * l, (const char*)v + kb * l,
+                                       (char*)out + qb * l, s);
+        if (r != TQ_OK) return r;
+    }
+    return TQ_OK;
+}
+
+__global__ void iota_from_kernel(int* pos, int n, int first) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) pos[i] = first + i;
+}
+
+int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos, int T,
+                             tq_stream_t s) {
+    if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (seq < 0 || seq >= e->G) return TQ_ERR_ARG;
+    const int cap = e->ragged ? e->capacities[seq] : e->msl;
+    if (first_pos + T > cap) return TQ_ERR_CAPACITY;
+    const long long row0 = e->ragged ? e->h_row_base[seq] : (long long)seq * e->msl;
+    const tq_engine::Layer& L = e->layers[layer];
+    if (e->kv_bits == 0) {
+        const size_t row_bytes = (size_t)e->kv_dim() * 2;
+        TQ_CUDA(cudaMemcpyAsync((char*)L.k + (size_t)(row0 + first_pos) * row_bytes, k, (size_t)T * row_bytes,
+                                cudaMemcpyDeviceToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync((char*)L.v + (size_t)(row0 + first_pos) * row_bytes, v, (size_t)T * row_bytes,
+                                cudaMemcpyDeviceToDevice, cs(s)));
+        return TQ_OK;
+    }
+    // token form: positions are first_pos + t; pass them by value through a per-token iota kept in a scratch
+    // allocation sized on demand (outside the arena so that prompt length is not bounded by the batch size).
+    static thread_local int* d_iota = nullptr;
+    static thread_local int iota_cap = 0;
+    if (iota_cap < T) {
+        if (d_iota) cudaFree(d_iota);
+        TQ_CUDA(cudaMalloc(&d_iota, (size_t)T * sizeof(int)));
+        iota_cap = T;
+    }
+    iota_from_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(d_iota, T, first_pos);
+    int r = cuda_status(cudaGetLastError());
+    if (r != TQ_OK) return r;
+    // the append kernel only needs the header of the workspace here (status word)
+    AppendParams p{};
+    p.ck = (uint8_t*)L.k; p.kn = (__half*)L.kn; p.cv = (uint8_t*)L.v; p.vn = (__half*)L.vn;
+    p.k_buf = (const __half*)k; p.v_buf = (const __half*)v; p.q = nullptr;
+    p.rotation = (const __half*)e->d_rotation;
+    p.positions = d_iota; p.row_base = nullptr; p.q_rot = nullptr;
+    p.tile_start = nullptr; p.tickets = nullptr; p.total_tiles = nullptr;
+    p.status = (int*)e->workspace;
+    p.token_row0 = row0; p.token_mode = 1;
+    p.max_seq_len = e->msl; p.capacity_rows = cap;
+    p.n_src = T; p.H = e->shape.num_heads; p.Hkv = e->shape.num_kv_heads; p.q_dim = e->q_dim(); p.kv_dim = e->kv_dim();
+    p.bits = e->kv_bits; p.pos_value = 0;
+    return launch_append(p, cs(s));
+}
+
+int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_host, const void* v_host, void* out_host,
+                               tq_stream_t s) {
+    if (!e || !q_host || !k_host || !v_host || !out_host) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    const int NL = e->shape.num_layers;
+    const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
+    TQ_CUDA(cudaMemcpyAsync(e->stage_q, q_host, qb * NL, cudaMemcpyHostToDevice, cs(s)));
+    TQ_CUDA(cudaMemcpyAsync(e->stage_k, k_host, kb * NL, cudaMemcpyHostToDevice, cs(s)));
+    TQ_CUDA(cudaMemcpyAsync(e->stage_v, v_host, kb * NL, cudaMemcpyHostToDevice, cs(s)));
+    for (int l = 0; l < NL; ++l) {
+        int r = tq_engine_decode_layer(e, l, (char*)e->stage_q + qb * l, (char*)e->stage_k + kb * l,
+                                       (char*)e->stage_v + kb * l, (char*)e->stage_out + qb * l, s);
+        if (r != TQ_OK) return r;
+    }
+    TQ_CUDA(cudaMemcpyAsync(out_host, e->stage_out, qb * NL, cudaMemcpyDeviceToHost, cs(s)));
+    TQ_CUDA(cudaStreamSynchronize(cs(s)));
+    return TQ_OK;
+}
+
+}  // extern "C"

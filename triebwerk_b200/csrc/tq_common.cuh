@@ -1,0 +1,185 @@
+// Shared device helpers for the sm_100a TurboQuant kernels: code books, PTX wrappers (mbarrier, TMA,
+// mma.sync, prmt), the workspace layout and the status word.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tq {
+
+constexpr int HEAD_DIM = 128;
+constexpr int TILE_TOKENS = 32;  // tokens per attention tile (one lane per token when norms are loaded)
+
+// Lloyd-Max code books for N(0, 1/128): the reference's literals (engine/kernels.cu:1426-1445).
+__device__ __constant__ float kCent4[16] = {-0.24155f, -0.18293f, -0.14304f, -0.11099f, -0.08330f, -0.05806f,
+                                            -0.03432f, -0.01135f, 0.01135f,  0.03432f,  0.05806f,  0.08330f,
+                                            0.11099f,  0.14304f,  0.18293f,  0.24155f};
+__device__ __constant__ float kBnd4[15] = {-0.21224f, -0.16299f, -0.12701f, -0.09715f, -0.07068f,
+                                           -0.04619f, -0.02284f, 0.00000f,  0.02284f,  0.04619f,
+                                           0.07068f,  0.09715f,  0.12701f,  0.16299f,  0.21224f};
+__device__ __constant__ float kCent2[4] = {-0.13351f, -0.04003f, 0.04003f, 0.13351f};
+__device__ __constant__ float kBnd2[3] = {-0.08677f, 0.0f, 0.08677f};
+
+// Device status word values (written with atomicMax; 0 = fine).
+enum : int {
+    ST_OK = 0,
+    ST_TMA_WAIT_TIMEOUT = 1,   // a bounded wait on a TMA mbarrier ran out
+    ST_SMEM_LAYOUT = 2,        // dynamic shared memory does not start where the kernel needs it
+    ST_BAD_POSITION = 3        // a position outside [0, capacity)
+};
+
+// ---- workspace layout ---------------------------------------------------------------------------------------
+// [0,256)                       header: int status; int total_tiles; ...
+// q_rot      float [G][H][128]  pre-rotated queries, already multiplied by log2(e)/sqrt(128)
+// tile_start int   [G+1]        exclusive prefix of ceil(L_g / TILE_TOKENS)
+// tickets    int   [G]          arrivals per sequence (zeroed by the append/rotate kernel)
+// partials   float [W+G][H][PART_STRIDE]  acc[128], m, l, pad
+constexpr int PART_STRIDE = 132;
+constexpr int MAX_WORKERS = 1024;  // upper bound on attention CTAs assumed by the workspace size
+
+struct Workspace {
+    int* status;
+    int* total_tiles;
+    float* q_rot;
+    int* tile_start;
+    int* tickets;
+    float* partials;
+    size_t bytes;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ inline Workspace carve_workspace(void* base, int G, int H) {
+    Workspace w;
+    char* p = (char*)base;
+    size_t off = 0;
+    w.status = (int*)(p + off);
+    w.total_tiles = (int*)(p + off + 4);
+    off += 256;
+    w.q_rot = (float*)(p + off);
+    off += align_up((size_t)G * H * HEAD_DIM * sizeof(float), 256);
+    w.tile_start = (int*)(p + off);
+    off += align_up((size_t)(G + 1) * sizeof(int), 256);
+    w.tickets = (int*)(p + off);
+    off += align_up((size_t)G * sizeof(int), 256);
+    w.partials = (float*)(p + off);
+    off += align_up((size_t)(MAX_WORKERS + G) * H * PART_STRIDE * sizeof(float), 256);
+    w.bytes = off;
+    return w;
+}
+
+// ---- small PTX wrappers ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ float rsqrt_approx_ftz(float x) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float sqrt_approx_ftz(float x) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float fma_ftz(float a, float b, float c) {
+    float r;
+    asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float mul_ftz(float a, float b) {
+    float r;
+    asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float add_ftz(float a, float b) {
+    float r;
+    asm("add.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t r;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- mbarrier / TMA ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself block for a hardware-defined short
+// time).  Returns false on give-up; the caller records ST_TMA_WAIT_TIMEOUT and stops using the pipeline.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 20)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
+// 2-D tiled TMA load global -> shared of this CTA (no multicast), completion on an mbarrier.
+// x = innermost coordinate in elements (bytes here; must be a multiple of 16), y = row.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+}  // namespace tq

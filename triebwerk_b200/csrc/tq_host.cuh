@@ -1,0 +1,320 @@
+// Host side of the library: tensor-map encoding, launch wrappers with argument checks, the per-device
+// workspace used by the reference-compatible launchers, and the KV arena / engine state that the
+// reference keeps inside InferenceEngine (engine/engine.cpp:292-409, 893-1022, 1338-1620).
+#pragma once
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <random>
+#include <tuple>
+#include <vector>
+
+#include <cudaTypedefs.h>
+
+#include "../../include/triebwerk_b200.h"
+#include "tq_append.cuh"
+#include "tq_attention.cuh"
+#include "tq_common.cuh"
+#include "tq_fp16.cuh"
+
+namespace tq {
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? TQ_OK : (int)e; }
+
+#define TQ_CUDA(call)                                  \
+    do {                                               \
+        cudaError_t _e = (call);                       \
+        if (_e != cudaSuccess) return (int)_e;         \
+    } while (0)
+
+struct DeviceProps {
+    int sm_count = 0;
+    bool attn4_attr = false, attn2_attr = false;
+};
+
+inline DeviceProps& device_props() {
+    static std::mutex mu;
+    static std::map<int, DeviceProps> props;
+    std::lock_guard<std::mutex> lock(mu);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    DeviceProps& d = props[dev];
+    if (d.sm_count == 0) {
+        cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (d.sm_count <= 0) d.sm_count = 1;
+    }
+    return d;
+}
+
+// ---- TMA descriptors ----------------------------------------------------------------------------------------------
+inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+// Code array viewed as uint8 [rows][kvp]; box = one head's bytes (bph) x TILE_TOKENS rows.
+inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int kvp, int bph) {
+    auto fn = encode_fn();
+    if (!fn) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31)) return TQ_ERR_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)kvp, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)kvp};
+    cuuint32_t box[2] = {(cuuint32_t)bph, (cuuint32_t)TILE_TOKENS};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
+}
+
+// ---- workspace ------------------------------------------------------------------------------------------------------
+// The carve of tq_common.cuh plus two helper arrays used by the prefill form (positions 0..T-1 and a
+// constant row base) and the fp16 twin's ticket/partial area, which aliases the packed path's partials.
+struct FullWorkspace {
+    Workspace w;
+    int* aux_pos;          // [G]
+    long long* aux_rows;   // [G]
+    size_t bytes;
+};
+
+inline FullWorkspace carve_full(void* base, int G, int H) {
+    FullWorkspace f;
+    f.w = carve_workspace(base, G, H);
+    size_t off = f.w.bytes;
+    char* p = (char*)base;
+    f.aux_pos = (int*)(p + off);
+    off += align_up((size_t)G * sizeof(int), 256);
+    f.aux_rows = (long long*)(p + off);
+    off += align_up((size_t)G * sizeof(long long), 256);
+    f.bytes = off;
+    return f;
+}
+
+inline size_t fp16_partials_bytes(int G, int H, int max_seq_len) {
+    int nchunk = (max_seq_len + FP16_CHUNK - 1) / FP16_CHUNK;
+    return (size_t)G * H * nchunk * PART_STRIDE * sizeof(float);
+}
+
+// ---- shape checks -------------------------------------------------------------------------------------------------------
+inline int check_shape(int G, int H, int Hkv, int head_dim, int q_dim, int kv_dim, int bits, bool packed) {
+    if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
+    if (G <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return TQ_ERR_ARG;
+    if (kv_dim != Hkv * head_dim || q_dim < H * head_dim) return TQ_ERR_ARG;
+    if (packed) {
+        if (bits != 2 && bits != 4) return TQ_ERR_ARG;
+        if (Hkv % 4 != 0 || Hkv > 8 || H / Hkv > 8 || H > ATTN_MAX_HEADS) return TQ_ERR_UNSUPPORTED;
+    } else {
+        int grp = H / Hkv;
+        if (grp != 1 && grp != 2 && grp != 4 && grp != 8) return TQ_ERR_UNSUPPORTED;
+    }
+    return TQ_OK;
+}
+
+// ---- launches -------------------------------------------------------------------------------------------------------------
+inline int launch_append(const AppendParams& p, cudaStream_t s) {
+    const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
+    const long long total = (long long)p.n_src * (nk + nv + nq);
+    if (total <= 0 && p.tile_start == nullptr) return TQ_OK;
+    long long groups = (total + APPEND_NV - 1) / APPEND_NV;
+    long long cap = (long long)device_props().sm_count * 3;
+    int grid = (int)(groups < 1 ? 1 : (groups < cap ? groups : cap));
+    append_rotate_kernel<<<grid, 128, 0, s>>>(p);
+    return cuda_status(cudaGetLastError());
+}
+
+inline int attention_workers(int G, int max_seq_len) {
+    long long tiles = (long long)G * ((max_seq_len + TILE_TOKENS - 1) / TILE_TOKENS);
+    long long w = device_props().sm_count;
+    if (w > MAX_WORKERS) w = MAX_WORKERS;
+    if (tiles < w) w = tiles;
+    return (int)(w < 1 ? 1 : w);
+}
+
+inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int workers,
+                            cudaStream_t s) {
+    DeviceProps& d = device_props();
+    if (bits == 4) {
+        if (!d.attn4_attr) {
+            TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)ATTN_DYN_SMEM));
+            d.attn4_attr = true;
+        }
+        decode_attention_kernel<4><<<workers, 32 * p.Hkv, ATTN_DYN_SMEM, s>>>(tmK, tmV, p);
+    } else {
+        if (!d.attn2_attr) {
+            TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)ATTN_DYN_SMEM));
+            d.attn2_attr = true;
+        }
+        decode_attention_kernel<2><<<workers, 32 * p.Hkv, ATTN_DYN_SMEM, s>>>(tmK, tmV, p);
+    }
+    return cuda_status(cudaGetLastError());
+}
+
+inline int launch_fp16_attention(const Fp16AttnParams& p, cudaStream_t s) {
+    const int grp = p.H / p.Hkv;
+    dim3 grid(p.nchunk_max, p.Hkv, p.G);
+    dim3 block(FP16_WARPS * 32);
+    switch (grp) {
+        case 1: fp16_decode_attention_kernel<1><<<grid, block, 0, s>>>(p); break;
+        case 2: fp16_decode_attention_kernel<2><<<grid, block, 0, s>>>(p); break;
+        case 4: fp16_decode_attention_kernel<4><<<grid, block, 0, s>>>(p); break;
+        case 8: fp16_decode_attention_kernel<8><<<grid, block, 0, s>>>(p); break;
+        default: return TQ_ERR_UNSUPPORTED;
+    }
+    return cuda_status(cudaGetLastError());
+}
+
+__global__ void iota_rows_kernel(int* pos, long long* rows, int n, long long row0) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        pos[i] = i;
+        rows[i] = row0;
+    }
+}
+
+// ---- per-device workspace of the compat launchers + descriptor cache ----------------------------------------------------------
+struct CompatState {
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> maps;
+};
+
+inline CompatState& compat_state() {
+    static std::mutex mu;
+    static std::map<int, CompatState> st;
+    std::lock_guard<std::mutex> lock(mu);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return st[dev];
+}
+
+inline int compat_workspace(size_t need, void** out, cudaStream_t s) {
+    CompatState& c = compat_state();
+    if (c.ws_bytes < need) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(s, &cs);
+        if (cs != cudaStreamCaptureStatusNone) return TQ_ERR_WORKSPACE;  // cannot allocate while capturing
+        if (c.ws) {
+            cudaDeviceSynchronize();
+            cudaFree(c.ws);
+            c.ws = nullptr;
+            c.ws_bytes = 0;
+        }
+        TQ_CUDA(cudaMalloc(&c.ws, need));
+        TQ_CUDA(cudaMemset(c.ws, 0, need));
+        c.ws_bytes = need;
+    }
+    *out = c.ws;
+    return TQ_OK;
+}
+
+inline int cached_code_map(CUtensorMap* out, const void* base, long long rows, int kvp, int bph) {
+    CompatState& c = compat_state();
+    auto key = std::make_tuple(base, rows, kvp, bph);
+    auto it = c.maps.find(key);
+    if (it == c.maps.end()) {
+        CUtensorMap m;
+        int r = make_code_map(&m, base, rows, kvp, bph);
+        if (r != TQ_OK) return r;
+        if (c.maps.size() > 4096) c.maps.clear();
+        it = c.maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return TQ_OK;
+}
+
+}  // namespace tq
+
+// =====================================================================================================================
+// Engine state (opaque to C callers)
+// =====================================================================================================================
+struct tq_engine {
+    tq_model_shape shape{};
+    int ctor_max_seq_len = 0;
+    int kv_bits = 0;
+    int device = 0;
+
+    // arena
+    char* arena = nullptr;
+    size_t arena_cap = 0;
+    bool arena_external = false;
+    bool asleep = false;
+
+    // current carving
+    int G = 0;
+    int msl = 0;          // dense slot size, or the largest capacity in ragged mode
+    bool ragged = false;
+    long long total_rows = 0;
+    std::vector<int> capacities;       // ragged mode, rounded up
+    std::vector<long long> h_row_base; // ragged mode
+
+    struct Layer {
+        void* k = nullptr;
+        void* v = nullptr;
+        void* kn = nullptr;
+        void* vn = nullptr;
+        CUtensorMap tmK{}, tmV{};
+    };
+    std::vector<Layer> layers;
+
+    int* d_positions = nullptr;
+    long long* d_row_base = nullptr;
+    void* workspace = nullptr;
+    size_t ws_bytes = 0;
+    void* stage_q = nullptr;   // [layers][G][q_dim]
+    void* stage_k = nullptr;   // [layers][G][kv_dim]
+    void* stage_v = nullptr;
+    void* stage_out = nullptr; // [layers][G][q_dim]
+
+    // rotation: host copy kept across sleep, device copy outside the arena (32 KB)
+    std::vector<uint16_t> h_rotation;
+    void* d_rotation = nullptr;
+
+    int q_dim() const { return shape.num_heads * shape.head_dim; }
+    int kv_dim() const { return shape.num_kv_heads * shape.head_dim; }
+    int vpb() const { return kv_bits == 2 ? 4 : 2; }
+    // bytes per cache row (all KV heads) of one of K / V: engine/engine.cpp:292-294 for the packed modes
+    size_t code_row_bytes() const { return kv_bits == 0 ? (size_t)kv_dim() * 2 : (size_t)kv_dim() / vpb(); }
+};
+
+namespace tq {
+
+// Walks the arena exactly as tq_engine_alloc_batch carves it.  base == nullptr only measures.
+struct ArenaPlan {
+    size_t bytes = 0;
+    long long total_rows = 0;
+};
+
+inline size_t bump(size_t& off, size_t bytes) {
+    off = (off + 255) & ~(size_t)255;  // 256-byte alignment, as GpuArena::alloc (engine/model.h:264-279)
+    size_t at = off;
+    off += bytes;
+    return at;
+}
+
+inline long long plan_rows(int G, int max_seq_len, const int* capacities, std::vector<int>* caps_out,
+                           std::vector<long long>* base_out) {
+    long long rows = 0;
+    if (capacities == nullptr) return (long long)G * max_seq_len;
+    for (int g = 0; g < G; ++g) {
+        int c = capacities[g] < 1 ? 1 : capacities[g];
+        c = (c + TILE_TOKENS - 1) / TILE_TOKENS * TILE_TOKENS;
+        if (caps_out) caps_out->push_back(c);
+        if (base_out) base_out->push_back(rows);
+        rows += c;
+    }
+    return rows;
+}
+
+}  // namespace tq
