@@ -227,6 +227,9 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
  * this engine rotated (packed modes only).  Used to time the attention kernel by itself. */
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s);
 
+/* tq_engine_attend_layer for every layer in turn: out [layers][G][q_dim] on the device. */
+int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s);
+
 /* Every layer of a decode step on DEVICE buffers: q/out [layers][G][q_dim], k/v [layers][G][kv_dim]. */
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
 

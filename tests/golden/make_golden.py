@@ -143,19 +143,21 @@ def main():
     ckf = torch.zeros(G * msl, kv_dim, dtype=torch.float16, device="cuda")
     cvf = torch.zeros_like(ckf)
     for s in range(S):
-        ref.launch_kv_cache_write_batch(p(ckf), p(cvf), p(dev(k_steps[s])), p(dev(v_steps[s])), p(dev(pos_steps[s])),
-                                        i(msl), i(G), i(kv_dim), null)
-    torch.cuda.synchronize()
+        dk, dv, dpos = dev(k_steps[s]), dev(v_steps[s]), dev(pos_steps[s])  # named: they must outlive the launch
+        ref.launch_kv_cache_write_batch(p(ckf), p(cvf), p(dk), p(dv), p(dpos), i(msl), i(G), i(kv_dim), null)
+        torch.cuda.synchronize()
     outf = torch.zeros(G, q_dim, dtype=torch.float16, device="cuda")
     scratch = torch.zeros(G * H * msl, dtype=torch.float32, device="cuda")
     dq = dev(q)
-    ref.launch_gqa_attention_batch(p(outf), p(dq), p(ckf), p(cvf), p(scratch), p(dev(final_pos)), i(msl), i(G), i(H),
+    dfinal = dev(final_pos)
+    ref.launch_gqa_attention_batch(p(outf), p(dq), p(ckf), p(cvf), p(scratch), p(dfinal), i(msl), i(G), i(H),
                                    i(Hkv), i(D), i(q_dim), i(kv_dim), null)
     g2 = 2
     outf1 = torch.zeros(q_dim, dtype=torch.float16, device="cuda")
     ck1 = ckf[g2 * msl:(g2 + 1) * msl].contiguous()
     cv1 = cvf[g2 * msl:(g2 + 1) * msl].contiguous()
-    ref.launch_gqa_attention(p(dq[g2].contiguous()), p(ck1), p(cv1), p(outf1), p(scratch), i(int(final_pos[g2])),
+    dq1 = dq[g2].contiguous()
+    ref.launch_gqa_attention(p(dq1), p(ck1), p(cv1), p(outf1), p(scratch), i(int(final_pos[g2])),
                              i(msl), i(H), i(Hkv), i(D), null)
     torch.cuda.synchronize()
     np.savez_compressed(os.path.join(args.out, "ref_kernels_fp16.npz"), H=H, Hkv=Hkv, D=D, msl=msl,

@@ -24,7 +24,7 @@ SYMBOLS = [
     "tq_engine_alloc_batch", "tq_engine_reset", "tq_engine_sleep", "tq_engine_wake", "tq_engine_positions",
     "tq_engine_set_positions", "tq_engine_advance", "tq_engine_layer_ptrs", "tq_engine_row_base",
     "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append",
-    "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status",
+    "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
 ]
 
 
@@ -93,6 +93,7 @@ def lib() -> C.CDLL:
     sig("tq_engine_attend_layer", i, [vp, i, vp, vp])
     sig("tq_engine_decode_step", i, [vp, vp, vp, vp, vp, vp])
     sig("tq_engine_status", i, [vp, vp])
+    sig("tq_engine_attend_step", i, [vp, vp, vp])
     _lib = L
     return L
 

@@ -35,6 +35,8 @@ struct AppendParams {
     float* q_rot;                // [G][H][128]
     int* tile_start;             // [G+1], optional (written by block 0 in batch mode)
     int* tickets;                // [G], optional (zeroed by block 0)
+    int* worker_g;               // [n_workers], optional: first sequence of each attention worker's slice
+    int n_workers;               // attention workers the tile list will be cut into
     int* total_tiles;
     int* status;
     long long token_row0;        // token mode: first row of the sequence the tokens belong to
@@ -66,7 +68,29 @@ __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p
     const int d = threadIdx.x;
     const int lane = d & 31, wid = d >> 5;
 
-    // Block 0 also prepares the attention kernel's tables: tickets = 0, tile_start = prefix of tiles.
+    pdl_launch_dependents();
+
+    // Row d of R into registers as fp32 (exact: fp16 -> fp32).  R is never written by a kernel, so this may run
+    // while the previous kernel in the stream is still finishing.
+    float r[HEAD_DIM];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM);
+#pragma unroll
+        for (int i = 0; i < HEAD_DIM / 8; ++i) {
+            uint4 u = __ldg(src + i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __half22float2(h2[j]);
+                r[8 * i + 2 * j] = f.x;
+                r[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+    pdl_wait();  // inputs come from earlier kernels; the workspace may still be read by the previous attention
+
+    // Block 0 also prepares the attention kernel's tables: tickets = 0, tile_start = prefix of tiles, and the
+    // first sequence of every worker's slice of the flat tile list.
     if (blockIdx.x == 0 && p.tile_start != nullptr && !p.token_mode) {
         __shared__ int scan[128];
         const int G = p.n_src;
@@ -100,9 +124,23 @@ __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p
                 run += (pos + 1 + TILE_TOKENS - 1) / TILE_TOKENS;
             }
         }
+        const int N = scan[127];
         if (d == 127) {
-            p.tile_start[G] = scan[127];
-            if (p.total_tiles) *p.total_tiles = scan[127];
+            p.tile_start[G] = N;
+            if (p.total_tiles) *p.total_tiles = N;
+        }
+        __syncthreads();  // tile_start is complete and visible to this block
+        if (p.worker_g) {
+            const int W = p.n_workers < N ? p.n_workers : N;
+            for (int w = d; w < W; w += 128) {
+                const long long lo = (long long)w * N / W;
+                int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
+                while (b - a > 1) {
+                    int mid = (a + b) >> 1;
+                    if ((long long)p.tile_start[mid] <= lo) a = mid; else b = mid;
+                }
+                p.worker_g[w] = a;
+            }
         }
         __syncthreads();
     }
@@ -113,23 +151,6 @@ __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p
     const int per_src = nk + nv + nq;
     const long long total = (long long)p.n_src * per_src;
     if ((long long)blockIdx.x * APPEND_NV >= total) return;
-
-    // Row d of R into registers as fp32 (exact: fp16 -> fp32).
-    float r[HEAD_DIM];
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM);
-#pragma unroll
-        for (int i = 0; i < HEAD_DIM / 8; ++i) {
-            uint4 u = __ldg(src + i);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 f = __half22float2(h2[j]);
-                r[8 * i + 2 * j] = f.x;
-                r[8 * i + 2 * j + 1] = f.y;
-            }
-        }
-    }
 
     const int vpb = (p.bits == 2) ? 4 : 2;
     const int bph = HEAD_DIM / vpb;

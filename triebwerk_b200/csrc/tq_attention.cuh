@@ -9,123 +9,183 @@
 // Decomposition
 //   * The (sequence, 32-token tile) pairs of the whole batch form one flat list (lengths come from the
 //     device-side positions, so the launch geometry never depends on them and the launch can be captured in
-//     a CUDA graph).  CTA i of W takes the contiguous slice [i*N/W, (i+1)*N/W) of that list: every SM gets
-//     the same number of bytes whatever the mix of sequence lengths.
-//   * Inside a CTA warp w owns KV head w and all of its query heads (2 for Qwen3-0.6B, 4 for Qwen3-8B): every
-//     cache byte is fetched from HBM once, not once per query head as in the reference.
-//   * Each warp runs its own TMA pipeline: lane 0 issues cp.async.bulk.tensor.2d (no multicast) for a
-//     [32 tokens][64 B] K box and V box of its head into a 4-deep ring of shared-memory stages, completion on
-//     one mbarrier per stage.  Warps never wait for one another inside a sequence.
+//     a CUDA graph).  The list is cut into equal contiguous slices, one per WORKER; a CTA holds two workers
+//     (16 warps on the SM for latency hiding), each a group of Hkv warps with its own named barrier.  Every SM
+//     gets the same number of bytes whatever the mix of sequence lengths.
+//   * Inside a worker warp w owns KV head w and all of its query heads (2 for Qwen3-0.6B, 4 for Qwen3-8B):
+//     every cache byte is fetched from HBM once, not once per query head as in the reference.
+//   * A worker streams its tiles through a ring of shared-memory stages filled by the TMA engine with plain
+//     contiguous bulk copies (cp.async.bulk, no multicast): one 16 KB copy for the K codes of 32 token rows (all
+//     heads), one for V, and two small ones for the fp16 norms, completion on one mbarrier per stage; tiles
+//     further ahead are pulled into L2 with cp.async.bulk.prefetch.L2 so that HBM stays busy beyond what shared
+//     memory can hold.  The last warp of the worker to finish a stage (one shared-memory atomic per warp and
+//     tile) re-arms it: nobody ever waits for a slower warp.
 //   * Codes are turned into fp16 centroids one BYTE at a time (2 codes for 4-bit, 4 for 2-bit) through a
 //     shared-memory table with one private column per lane (bank-conflict free); the table sits at shared
 //     address 0x10000 so that a single PRMT builds the lookup address from the packed word.
 //   * The dot products run on the tensor cores with warp-level mma.sync.m16n8k16 (fp16 in, fp32 accumulate):
 //     scores as Q(16 x 16) * K^T(16 x 8 tokens) with the query split into an fp16 high part (rows 0-7) and
 //     low part (rows 8-15) so that no query precision is lost, and the value sum in transposed form
-//     V^T(16 coords x 16 tokens) * P^T(16 tokens x 8 heads).  Scalar fp32 FMAs cannot keep up with HBM3e on
-//     this path: 512 FMAs per 132-byte row would need more than the SMs can issue.
-//   * A CTA that finishes its part of a sequence writes (acc[128], m, l) per query head to the workspace and
-//     takes a ticket; the last arrival merges all parts, divides, multiplies by R^T and writes fp16.  Nobody
-//     spins on anybody: the ticket is a single atomicAdd.
+//     V^T(16 coords x 16 tokens) * P^T(16 tokens x 8 heads); the token pairs the V^T fragment needs are
+//     formed by interleaving the nibbles of two tokens' words BEFORE the table lookup.  Scalar fp32 FMAs cannot
+//     keep up with HBM3e on this path: 512 FMAs per 132-byte row is more than the SMs can issue.
+//   * A worker that finishes its part of a sequence writes (acc[128], m, l) per query head to the workspace
+//     and takes a ticket; the last arrival merges all parts, and multiplies by R^T on the tensor cores
+//     (normalised accumulators split into fp16 high + low parts as the A operand, R^T as B).  Nobody spins on
+//     anybody: the ticket is a single atomicAdd.
 #pragma once
 
 #include "tq_common.cuh"
 
 namespace tq {
 
-constexpr int ATTN_STAGES = 4;
 constexpr uint32_t LUT_ABS = 0x10000u;        // absolute shared address of the byte -> centroid table
-constexpr uint32_t LUT_BYTES = 0x10000u;      // 256 entries x 256 B
-constexpr uint32_t REGION_B_ABS = 0x20000u;   // stages 1.. live above the table
-constexpr int ATTN_MAX_HEADS = 32;            // merge buffer is 128 x 32 floats
+constexpr uint32_t REGION_B_ABS = 0x20000u;   // more stage blocks live above the table
+constexpr int ATTN_MAX_HEADS = 32;
 constexpr size_t ATTN_DYN_SMEM = 226 * 1024;  // requested dynamic shared memory
+constexpr int ATTN_GROUPS = 2;                // workers per CTA
+constexpr int ATTN_MAX_STAGES = 4;            // shared-memory stages per worker (as many as fit, at most this)
+constexpr int ATTN_L2_AHEAD = 4;              // tiles prefetched into L2 beyond the shared-memory ring
+constexpr int MERGE_ROW = 136;                // halves per row of the merge A-operand (padded: conflict-free)
 
 struct AttnParams {
-    const __half* kn;
+    const uint8_t* ck;         // packed K codes [rows][kvp]
+    const uint8_t* cv;
+    const __half* kn;          // norms [rows][Hkv]
     const __half* vn;
-    const float* q_rot;       // [G][H][128], pre-scaled by log2(e)/sqrt(128)
-    const __half* rotation;   // [128][128]
-    __half* out;              // [G][q_dim]
-    const int* positions;     // device [G] or null
+    const float* q_rot;        // [G][H][128], pre-scaled by log2(e)/sqrt(128)
+    const __half* rotation_t;  // R transposed: rotation_t[d][k] = R[k][d]
+    __half* out;               // [G][q_dim]
+    const int* positions;      // device [G] or null
     const long long* row_base;
-    const int* tile_start;    // [G+1]
-    int* tickets;             // [G]
-    float* partials;          // [W+G][H][PART_STRIDE]
+    const int* tile_start;     // [G+1]
+    const int* worker_g;       // first sequence of each worker's slice, or null (then it is searched for)
+    int* tickets;              // [G]
+    float* partials;           // [workers+G][H][PART_STRIDE]
     int* status;
+    long long total_rows;      // rows of the cache arrays (copies are clipped to it)
     int pos_value;
     int max_seq_len;
     int G, H, Hkv, q_dim;
+    int debug;                 // measurement switches (TQ_ATTN_DEBUG): bit 0 = skip the math, bit 1 = skip the loads
 };
 
 template <int BITS>
 struct AttnGeom {
-    static constexpr int BPH = (BITS == 4) ? 64 : 32;         // code bytes per head per token
-    static constexpr int TILE_BYTES = TILE_TOKENS * BPH;      // one K (or V) box
-    static constexpr int WARP_STAGE_BYTES = 2 * TILE_BYTES;   // K box + V box
+    static constexpr int BPH = (BITS == 4) ? 64 : 32;  // code bytes per head per token
 };
 
-// Region A (below the table): barriers, norm stash, merge buffer, stage 0.
+// Region A (below the table): barriers, control words, merge operands, then stage blocks.
 struct RegionA {
-    static constexpr uint32_t BAR_OFF = 0;                                   // up to 16 warps x 4 stages x 8 B
-    static constexpr uint32_t NORM_OFF = 512;                                // 16 warps x 2 x 32 floats = 4 KB
-    static constexpr uint32_t CTRL_OFF = NORM_OFF + 16 * 2 * 32 * 4;         // flags
-    static constexpr uint32_t MERGE_OFF = CTRL_OFF + 256;                    // 128 x 32 floats = 16 KB
-    static constexpr uint32_t STAGE0_OFF = MERGE_OFF + HEAD_DIM * ATTN_MAX_HEADS * 4;  // 21248 -> align 1024
+    static constexpr uint32_t BAR_OFF = 0;       // per group: full[ATTN_MAX_STAGES] mbarriers (8 B each)
+    static constexpr uint32_t CNT_OFF = 128;     // per group: done-counters, one u32 per stage
+    static constexpr uint32_t CTRL_OFF = 256;    // one word per group
+    static constexpr uint32_t MERGE_OFF = 512;   // per group: hi + lo [16][MERGE_ROW] halves
+    static constexpr uint32_t MERGE_GROUP_BYTES = 2 * 16 * MERGE_ROW * 2;  // 8704
+    static constexpr uint32_t BLOCKS_OFF = MERGE_OFF + ATTN_GROUPS * MERGE_GROUP_BYTES;
 };
 
-template <int BITS>
-__global__ void __launch_bounds__(256, 1)
-decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const AttnParams p) {
+__device__ __forceinline__ void group_barrier(int group, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(nthreads) : "memory");
+}
+
+// Contiguous bulk copy global -> shared of this CTA, completion on an mbarrier.  Addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t atom_add_shared(uint32_t addr, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
+}
+// Loads whose ordering is carried by data dependence (their address derives from a value produced after the
+// barrier wait), so the compiler may schedule them freely among the arithmetic of a tile.
+__device__ __forceinline__ uint32_t ldsp32(uint32_t addr) {
+    uint32_t r;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint2 ldsp64(uint32_t addr) {
+    uint2 r;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint4 ldsp128(uint32_t addr) {
+    uint4 r;
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from shared memory as float
+    unsigned short h;
+    asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+    return __half2float(__ushort_as_half(h));
+}
+
+template <int BITS, bool QSPLIT>
+__global__ void __launch_bounds__(512, 1)
+decode_attention_kernel(const AttnParams p) {
     using Geo = AttnGeom<BITS>;
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-    const int warp = tid >> 5;           // = KV head
+    const int warp = tid >> 5;
+    const int Hkv = p.Hkv;
+    const int group = warp / Hkv;        // worker within the CTA
+    const int head = warp - group * Hkv; // KV head of this warp
     const int gl = lane >> 2;            // mma "group id": token (K side), coordinate row (V side), head (S layout)
     const int t4 = lane & 3;             // mma "thread in group"
-    const int grp = p.H / p.Hkv;         // query heads per KV head (<= 8)
-    const int nthreads = blockDim.x;
+    const int grp = p.H / Hkv;           // query heads per KV head (<= 8)
+    const int gthreads = 32 * Hkv;       // threads of a worker
+    const int gtid = tid - group * gthreads;
+    const uint32_t kvp = (uint32_t)Hkv * Geo::BPH;               // code bytes per token row (all heads)
+    const uint32_t code_tile = TILE_TOKENS * kvp;                // one K (or V) tile
+    const uint32_t norm_tile = TILE_TOKENS * (uint32_t)Hkv * 2u; // one norm tile
+    const uint32_t stage_bytes = 2u * code_tile + 2u * norm_tile;
 
     // ---- shared memory map (absolute shared addresses) ----
     const uint32_t dyn_base = smem_u32(dyn_smem);
     const uint32_t a_base = (dyn_base + 1023u) & ~1023u;
-    const uint32_t stage0 = (a_base + RegionA::STAGE0_OFF + 1023u) & ~1023u;
-    const uint32_t set_bytes = (uint32_t)p.Hkv * Geo::WARP_STAGE_BYTES;
-    {
-        bool ok = (stage0 + set_bytes <= LUT_ABS) &&
-                  (REGION_B_ABS + (ATTN_STAGES - 1) * set_bytes <= dyn_base + (uint32_t)ATTN_DYN_SMEM);
-        if (!ok) {
-            if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
-            return;
-        }
+    const uint32_t blocks_a = (a_base + RegionA::BLOCKS_OFF + 1023u) & ~1023u;
+    const uint32_t n_a = blocks_a < LUT_ABS ? (LUT_ABS - blocks_a) / stage_bytes : 0u;
+    const uint32_t dyn_end = dyn_base + (uint32_t)ATTN_DYN_SMEM;
+    const uint32_t n_b = dyn_end > REGION_B_ABS ? (dyn_end - REGION_B_ABS) / stage_bytes : 0u;
+    const int s_fit = (int)((n_a + n_b) / ATTN_GROUPS);
+    const int S = s_fit >= 4 ? 4 : 2;       // a power of two: stage index and parity are masks and shifts
+    const int s_log = s_fit >= 4 ? 2 : 1;
+    if (blocks_a >= LUT_ABS || s_fit < 2 || dyn_end < REGION_B_ABS) {
+        if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
+        return;
     }
-    const uint32_t bar0 = a_base + RegionA::BAR_OFF + (uint32_t)warp * ATTN_STAGES * 8u;
-    const uint32_t norm_s = a_base + RegionA::NORM_OFF + (uint32_t)warp * 256u;  // kn[32] floats, vn[32] floats
-    const uint32_t ctrl_s = a_base + RegionA::CTRL_OFF;
-    const uint32_t merge_s = a_base + RegionA::MERGE_OFF;
+    const uint32_t bar0 = a_base + RegionA::BAR_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 8u);
+    const uint32_t cnt0 = a_base + RegionA::CNT_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 4u);
+    const uint32_t ctrl_s = a_base + RegionA::CTRL_OFF + (uint32_t)group * 16u;
+    const uint32_t merge_s = a_base + RegionA::MERGE_OFF + (uint32_t)group * RegionA::MERGE_GROUP_BYTES;
     auto stage_addr = [&](int s) -> uint32_t {
-        return (s == 0 ? stage0 : REGION_B_ABS + (uint32_t)(s - 1) * set_bytes) + (uint32_t)warp * Geo::WARP_STAGE_BYTES;
+        const uint32_t blk = (uint32_t)(group * S + s);
+        return blk < n_a ? blocks_a + blk * stage_bytes : REGION_B_ABS + (blk - n_a) * stage_bytes;
     };
 
-    // ---- work slice ----
-    const int W = gridDim.x;
+    pdl_launch_dependents();
+    if (p.debug & 32) { pdl_wait(); return; }
     const int G = p.G;
-    const long long N = p.tile_start[G];
-    const long long lo = (long long)blockIdx.x * N / W;
-    const long long hi = (long long)(blockIdx.x + 1) * N / W;
-    if (lo >= hi) return;  // uniform for the CTA
 
     // ---- byte -> centroid table, one column per lane ----
-    if (BITS == 4) {
-        for (int idx = tid; idx < 256 * 32; idx += nthreads) {
+    if (p.debug & 16) {
+    } else if (BITS == 4) {
+        for (int idx = tid; idx < 256 * 32; idx += blockDim.x) {
             int v = idx >> 5, l = idx & 31;
             uint32_t val = pack_half2(kCent4[v & 15], kCent4[v >> 4]);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(LUT_ABS + (uint32_t)v * 256u + (uint32_t)l * 4u), "r"(val) : "memory");
         }
     } else {
-        for (int idx = tid; idx < 256 * 32; idx += nthreads) {
+        for (int idx = tid; idx < 256 * 32; idx += blockDim.x) {
             int v = idx >> 5, l = idx & 31;
             uint32_t lo2 = pack_half2(kCent2[v & 3], kCent2[(v >> 2) & 3]);
             uint32_t hi2 = pack_half2(kCent2[(v >> 4) & 3], kCent2[(v >> 6) & 3]);
@@ -133,16 +193,34 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                          "r"(lo2), "r"(hi2) : "memory");
         }
     }
-    if (lane == 0) {
-        for (int s = 0; s < ATTN_STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
+    if (gtid == 0) {
+        for (int s = 0; s < ATTN_MAX_STAGES; ++s) {
+            mbar_init(bar0 + 8u * s, 1);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
+        }
         fence_mbar_init();
         fence_proxy_async_smem();
     }
+    // Everything above touches only shared memory and may overlap the tail of the previous kernel in the stream.
+    pdl_wait();
+    const long long N = p.tile_start[G];
     __syncthreads();
+
+    // ---- work slice of this worker ----
+    // Only min(workers, N) workers take part, so that every participant owns at least one tile: the ticket
+    // count of a sequence is then simply (last owner - first owner + 1).
+    const long long w_all = (long long)gridDim.x * ATTN_GROUPS;
+    const int W = w_all < N ? (int)w_all : (int)N;
+    const int wid = blockIdx.x * ATTN_GROUPS + group;
+    if (wid >= W) return;  // uniform for the worker; no CTA-wide barrier follows
+    const long long lo = (long long)wid * N / W;
+    const long long hi = (long long)(wid + 1) * N / W;
 
     // first sequence of the slice: largest g with tile_start[g] <= lo
     int g;
-    {
+    if (p.worker_g) {
+        g = p.worker_g[wid];
+    } else {
         int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
         while (b - a > 1) {
             int mid = (a + b) >> 1;
@@ -151,36 +229,70 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         g = a;
     }
 
-    // ---- producer cursor (warp-uniform) ----
-    long long ptile = lo;
-    int pg = g;
-    long long pg_end = p.tile_start[pg + 1];
-    int issued = 0, consumed = 0;
-    bool dead = false;  // a bounded wait gave up: keep the control flow, stop touching the pipeline
-    const int xcoord = warp * Geo::BPH;
-
-    auto issue_one = [&]() {
-        while (ptile >= pg_end) {
-            ++pg;
-            pg_end = p.tile_start[pg + 1];
+    // ---- load cursor over the flat tile list (warp-uniform, advanced in step by every warp of the worker) ----
+    // Tile counts and row numbers fit 32 bits (the host refuses caches of 2^31 rows or more).
+    const int lo_i = (int)lo, hi_i = (int)hi;
+    int cl_tile = lo_i;                         // next tile to load into shared memory
+    int cl_g = g;
+    int cl_gend = p.tile_start[g + 1];
+    int cl_row = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - p.tile_start[g]) * TILE_TOKENS;
+    auto cursor_advance = [&]() {
+        ++cl_tile;
+        cl_row += TILE_TOKENS;
+        if (cl_tile == cl_gend && cl_tile < hi_i) {
+            ++cl_g;
+            cl_gend = p.tile_start[cl_g + 1];
+            cl_row = (int)(p.row_base ? p.row_base[cl_g] : (long long)cl_g * p.max_seq_len);
         }
-        const long long local = ptile - p.tile_start[pg];
-        const long long row = (p.row_base ? p.row_base[pg] : (long long)pg * p.max_seq_len) + local * TILE_TOKENS;
-        const int s = issued % ATTN_STAGES;
-        if (lane == 0) {
-            const uint32_t bar = bar0 + 8u * s;
-            const uint32_t dst = stage_addr(s);
-            mbar_arrive_expect_tx(bar, Geo::WARP_STAGE_BYTES);
-            tma_load_2d(dst, &tmK, bar, xcoord, (int)row);
-            tma_load_2d(dst + Geo::TILE_BYTES, &tmV, bar, xcoord, (int)row);
-        }
-        ++issued;
-        ++ptile;
     };
-    for (int s = 0; s < ATTN_STAGES; ++s)
-        if (ptile < hi) issue_one();
+    int consumed = 0;
+    bool dead = false;  // a bounded wait gave up: keep the control flow, stop touching the pipeline
+    const bool loads_on = !(p.debug & 2);
+    const int total_rows_i = (int)p.total_rows;
 
+    // One elected thread issues the four copies of a tile (K codes, V codes, K norms, V norms), clipped to the
+    // end of the arrays; rows past a sequence's position only ever reach masked tokens.
+    auto issue_tile = [&](int row, int s) {
+        int nrows = total_rows_i - row;
+        if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
+        if (nrows < 0) nrows = 0;
+        const uint32_t cb = (uint32_t)nrows * kvp, nb = (uint32_t)nrows * (uint32_t)Hkv * 2u;
+        const uint32_t bar = bar0 + 8u * s;
+        const uint32_t dst = stage_addr(s);
+        mbar_arrive_expect_tx(bar, 2u * cb + 2u * nb);
+        if (nrows > 0) {
+            bulk_load(dst, p.ck + (size_t)row * kvp, cb, bar);
+            bulk_load(dst + code_tile, p.cv + (size_t)row * kvp, cb, bar);
+            bulk_load(dst + 2u * code_tile, p.kn + (size_t)row * Hkv, nb, bar);
+            bulk_load(dst + 2u * code_tile + norm_tile, p.vn + (size_t)row * Hkv, nb, bar);
+        }
+    };
+    // L2 prefetch of the tile ATTN_L2_AHEAD further on, when it belongs to the same sequence (rows are then contiguous)
+    auto prefetch_ahead = [&](int row, int tile_idx, int gend) {
+        if (tile_idx + ATTN_L2_AHEAD < gend) {
+            const int prow = row + ATTN_L2_AHEAD * TILE_TOKENS;
+            int nrows = total_rows_i - prow;
+            if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
+            if (nrows > 0) {
+                bulk_prefetch_l2(p.ck + (size_t)prow * kvp, (uint32_t)nrows * kvp);
+                bulk_prefetch_l2(p.cv + (size_t)prow * kvp, (uint32_t)nrows * kvp);
+            }
+        }
+    };
+    // prologue: fill the ring (and prefetch a few tiles beyond each)
+    for (int s = 0; s < S; ++s) {
+        if (cl_tile < hi_i) {
+            if (gtid == 0 && loads_on) {
+                issue_tile(cl_row, s);
+                prefetch_ahead(cl_row, cl_tile, cl_gend);
+            }
+            cursor_advance();
+        }
+    }
+
+    if (p.debug & 64) return;
     const uint32_t lutlane = LUT_ABS | ((uint32_t)lane << (BITS == 4 ? 2 : 3));
+    const uint32_t head_off = (uint32_t)head * Geo::BPH;
 
     long long tile = lo;
     while (tile < hi) {
@@ -190,15 +302,14 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const long long seg_end = hi < ts_g1 ? hi : ts_g1;
         const int pos = p.positions ? p.positions[g] : p.pos_value;
         const int L = (pos < 0 ? 0 : pos) + 1;
-        const long long row0 = p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len;
 
-        // query fragments: lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head warp*grp + gl
-        uint32_t qa[8][4];
+        // query fragments: lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head  head*grp + gl
+        uint32_t qa[8][QSPLIT ? 4 : 2];
         {
             float qv[32];
-            if (gl < grp) {
+            if (gl < grp && !(p.debug & 8)) {
                 const float4* src =
-                    reinterpret_cast<const float4*>(p.q_rot + ((size_t)g * p.H + (size_t)warp * grp + gl) * HEAD_DIM + 32 * t4);
+                    reinterpret_cast<const float4*>(p.q_rot + ((size_t)g * p.H + (size_t)head * grp + gl) * HEAD_DIM + 32 * t4);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float4 f = __ldg(src + i);
@@ -212,11 +323,13 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             for (int j = 0; j < 8; ++j) {
                 __half2 h01 = __floats2half2_rn(qv[4 * j], qv[4 * j + 1]);
                 __half2 h23 = __floats2half2_rn(qv[4 * j + 2], qv[4 * j + 3]);
-                float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
                 qa[j][0] = *reinterpret_cast<uint32_t*>(&h01);
-                qa[j][2] = *reinterpret_cast<uint32_t*>(&h23);
-                qa[j][1] = pack_half2(qv[4 * j] - f01.x, qv[4 * j + 1] - f01.y);
-                qa[j][3] = pack_half2(qv[4 * j + 2] - f23.x, qv[4 * j + 3] - f23.y);
+                qa[j][QSPLIT ? 2 : 1] = *reinterpret_cast<uint32_t*>(&h23);
+                if (QSPLIT) {
+                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                    qa[j][1] = pack_half2(qv[4 * j] - f01.x, qv[4 * j + 1] - f01.y);
+                    qa[j][3] = pack_half2(qv[4 * j + 2] - f23.x, qv[4 * j + 3] - f23.y);
+                }
             }
         }
 
@@ -225,42 +338,28 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
         for (int b = 0; b < 8; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
 
-        // norm prefetch ring: lane <-> token of the tile
-        auto load_norms = [&](long long tl, float& kf, float& vf) {
-            kf = 0.0f; vf = 0.0f;
-            if (tl < seg_end) {
-                const long long tok = (tl - ts_g) * TILE_TOKENS + lane;
-                if (tok < L) {
-                    const size_t off = (size_t)(row0 + tok) * p.Hkv + warp;
-                    kf = __half2float(p.kn[off]);
-                    vf = __half2float(p.vn[off]);
-                }
-            }
-        };
-        float kn0, vn0, kn1, vn1;
-        load_norms(tile, kn0, vn0);
-        load_norms(tile + 1, kn1, vn1);
-
         for (; tile < seg_end; ++tile) {
             const int t0 = (int)(tile - ts_g) * TILE_TOKENS;
-            // stash this tile's norms, fetch the ones two tiles ahead
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(norm_s + 4u * lane), "f"(kn0) : "memory");
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(norm_s + 128u + 4u * lane), "f"(vn0) : "memory");
-            kn0 = kn1; vn0 = vn1;
-            load_norms(tile + 2, kn1, vn1);
-            __syncwarp();
-
-            const int s = consumed % ATTN_STAGES;
-            if (!dead) {
-                if (!mbar_wait_bounded(bar0 + 8u * s, (uint32_t)(consumed / ATTN_STAGES) & 1u)) {
+            const bool full = t0 + TILE_TOKENS <= L;  // warp-uniform: no token of the tile is masked
+            const int s = consumed & (S - 1);
+            uint32_t token = 0;  // 0 at run time; produced by the wait, so that the tile's loads cannot move above it
+            if (!dead && loads_on) {
+                const uint32_t bar = bar0 + 8u * s, parity = (uint32_t)(consumed >> s_log) & 1u;
+                uint32_t ok = 0;
+                for (uint32_t it = 0; it < (1u << 20) && !ok; ++it) ok = mbar_try_wait(bar, parity);
+                if (!ok) {
                     dead = true;
                     if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
                 }
+                dead = __any_sync(0xffffffffu, dead);
+                token = ok ^ 1u;
             }
-            dead = __any_sync(0xffffffffu, dead);
-            if (!dead) {
-                const uint32_t kt = stage_addr(s);
-                const uint32_t vt = kt + Geo::TILE_BYTES;
+            if (!dead && !(p.debug & 1)) {
+                const uint32_t kt = stage_addr(s) + token + head_off;  // this head's bytes of token row 0
+                const uint32_t vt = kt + code_tile;
+                const uint32_t kns = stage_addr(s) + token + 2u * code_tile + (uint32_t)head * 2u;
+                const uint32_t vns = kns + norm_tile;
+                const uint32_t nstride = (uint32_t)Hkv * 2u;
 
                 // ---------------- scores: 4 blocks of 8 tokens ----------------
                 float sv[8];
@@ -268,50 +367,51 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 for (int blk = 0; blk < 4; ++blk) {
                     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                     if (BITS == 4) {
-                        const uint4 kw = lds128(kt + (uint32_t)(8 * blk + gl) * 64u + (uint32_t)t4 * 16u);
+                        const uint4 kw = ldsp128(kt + (uint32_t)(8 * blk + gl) * kvp + (uint32_t)t4 * 16u);
                         const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const uint32_t word = w[j >> 1];
-                            const uint32_t b0 = lds32(prmt(word, lutlane, (j & 1) ? 0x7624u : 0x7604u));
-                            const uint32_t b1 = lds32(prmt(word, lutlane, (j & 1) ? 0x7634u : 0x7614u));
-                            mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], b0, b1);
+                            const uint32_t b0 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7624u : 0x7604u));
+                            const uint32_t b1 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7634u : 0x7614u));
+                            if (QSPLIT) mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], b0, b1);
+                            else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, b0, b1);
                         }
                     } else {
-                        const uint2 kw = lds64(kt + (uint32_t)(8 * blk + gl) * 32u + (uint32_t)t4 * 8u);
+                        const uint2 kw = ldsp64(kt + (uint32_t)(8 * blk + gl) * kvp + (uint32_t)t4 * 8u);
                         const uint32_t w[2] = {kw.x, kw.y};
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const uint32_t word = w[j >> 2];
-                            const uint2 bb = lds64(prmt(word, lutlane, 0x7604u | ((uint32_t)(j & 3) << 4)));
-                            mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], bb.x, bb.y);
+                            const uint2 bb = ldsp64(prmt(word, lutlane, 0x7604u | ((uint32_t)(j & 3) << 4)));
+                            if (QSPLIT) mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], bb.x, bb.y);
+                            else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, bb.x, bb.y);
                         }
                     }
-                    float2 kn2;
-                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(kn2.x), "=f"(kn2.y)
-                                 : "r"(norm_s + 4u * (uint32_t)(8 * blk + 2 * t4)));
-                    sv[2 * blk] = (c[0] + c[2]) * kn2.x;
-                    sv[2 * blk + 1] = (c[1] + c[3]) * kn2.y;
+                    const float k0 = ldsp_h2f(kns + (uint32_t)(8 * blk + 2 * t4) * nstride);
+                    const float k1 = ldsp_h2f(kns + (uint32_t)(8 * blk + 2 * t4 + 1) * nstride);
+                    sv[2 * blk] = (QSPLIT ? c[0] + c[2] : c[0]) * k0;
+                    sv[2 * blk + 1] = (QSPLIT ? c[1] + c[3] : c[1]) * k1;
                 }
 
-                // ---------------- online softmax (rows = heads gl < grp) ----------------
-                float tmax = -1e30f;
+                // ---------------- online softmax (row = head gl; rows >= grp carry zeros and are never read) ----
+                if (!full) {  // rows past the position may hold anything (even NaN norms): force them out
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
-                    if (tok >= L) sv[i] = -1e30f;
-                    tmax = fmaxf(tmax, sv[i]);
+                    for (int i = 0; i < 8; ++i) {
+                        const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
+                        if (tok >= L) sv[i] = -1e30f;
+                    }
                 }
+                float tmax = fmaxf(fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])), fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7])));
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
                 const float m_new = fmaxf(m_run, tmax);
-                const bool grew = (gl < grp) && (m_new > m_run);
-                if (__any_sync(0xffffffffu, grew)) {
+                if (__any_sync(0xffffffffu, m_new > m_run)) {
                     const float corr = ex2_approx(m_run - m_new);  // 1 when unchanged, 0 at the first tile
                     l_run *= corr;
                     // accumulators of head (2*t4 + e) live in lanes with this t4; its corr lives in lanes gl' = 2*t4 + e
                     const float c0 = __shfl_sync(0xffffffffu, corr, (2 * t4) * 4);
-                    const float c1 = __shfl_sync(0xffffffffu, corr, ((2 * t4 + 1) & 7) * 4);
+                    const float c1 = __shfl_sync(0xffffffffu, corr, (2 * t4 + 1) * 4);
 #pragma unroll
                     for (int b = 0; b < 8; ++b) {
                         acc[b][0] *= c0; acc[b][2] *= c0;
@@ -321,51 +421,67 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
                 float pv[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
-                    const float e = ex2_approx(sv[i] - m_run);
-                    pv[i] = (tok < L && gl < grp) ? e : 0.0f;
-                    l_run += pv[i];
+                for (int i = 0; i < 8; ++i) pv[i] = ex2_approx(sv[i] - m_run);
+                if (!full) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
+                        if (tok >= L) pv[i] = 0.0f;
+                    }
                 }
+                l_run += ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
 
                 // ---------------- values: 2 blocks of 16 tokens ----------------
 #pragma unroll
                 for (int gam = 0; gam < 2; ++gam) {
-                    float2 va, vb;
-                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(va.x), "=f"(va.y)
-                                 : "r"(norm_s + 128u + 4u * (uint32_t)(16 * gam + 2 * t4)));
-                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(vb.x), "=f"(vb.y)
-                                 : "r"(norm_s + 128u + 4u * (uint32_t)(16 * gam + 8 + 2 * t4)));
-                    const uint32_t pb0 = pack_half2(pv[4 * gam] * va.x, pv[4 * gam + 1] * va.y);
-                    const uint32_t pb1 = pack_half2(pv[4 * gam + 2] * vb.x, pv[4 * gam + 3] * vb.y);
                     const uint32_t rowA = (uint32_t)(16 * gam + 2 * t4);
+                    float v0 = ldsp_h2f(vns + (rowA + 0) * nstride), v1 = ldsp_h2f(vns + (rowA + 1) * nstride);
+                    float v8 = ldsp_h2f(vns + (rowA + 8) * nstride), v9 = ldsp_h2f(vns + (rowA + 9) * nstride);
+                    if (!full) {  // 0 * NaN would poison the accumulators
+                        if (t0 + (int)rowA + 0 >= L) v0 = 0.0f;
+                        if (t0 + (int)rowA + 1 >= L) v1 = 0.0f;
+                        if (t0 + (int)rowA + 8 >= L) v8 = 0.0f;
+                        if (t0 + (int)rowA + 9 >= L) v9 = 0.0f;
+                    }
+                    const uint32_t pb0 = pack_half2(pv[4 * gam] * v0, pv[4 * gam + 1] * v1);
+                    const uint32_t pb1 = pack_half2(pv[4 * gam + 2] * v8, pv[4 * gam + 3] * v9);
                     if (BITS == 4) {
-                        const uint2 xa = lds64(vt + (rowA + 0) * 64u + (uint32_t)gl * 8u);
-                        const uint2 xb = lds64(vt + (rowA + 1) * 64u + (uint32_t)gl * 8u);
-                        const uint2 xc = lds64(vt + (rowA + 8) * 64u + (uint32_t)gl * 8u);
-                        const uint2 xd = lds64(vt + (rowA + 9) * 64u + (uint32_t)gl * 8u);
+                        // lane reads bytes 8*gl .. 8*gl+7 (coordinates 16*gl .. 16*gl+15) of tokens rowA, +1, +8, +9
+                        const uint2 xa = ldsp64(vt + (rowA + 0) * kvp + (uint32_t)gl * 8u);
+                        const uint2 xb = ldsp64(vt + (rowA + 1) * kvp + (uint32_t)gl * 8u);
+                        const uint2 xc = ldsp64(vt + (rowA + 8) * kvp + (uint32_t)gl * 8u);
+                        const uint2 xd = ldsp64(vt + (rowA + 9) * kvp + (uint32_t)gl * 8u);
+                        // Interleave the nibbles of two tokens: byte b of `ev` = (code of token A, code of token B) for the
+                        // EVEN coordinate of byte b, `od` for the odd one.  The table then returns the (A, B) pair directly.
+                        const uint32_t wa[2] = {xa.x, xa.y}, wb[2] = {xb.x, xb.y}, wc[2] = {xc.x, xc.y}, wd[2] = {xd.x, xd.y};
 #pragma unroll
-                        for (int b = 0; b < 8; ++b) {
-                            const uint32_t sel = 0x7604u | ((uint32_t)(b & 3) << 4);
-                            const uint32_t la = lds32(prmt(b < 4 ? xa.x : xa.y, lutlane, sel));
-                            const uint32_t lb = lds32(prmt(b < 4 ? xb.x : xb.y, lutlane, sel));
-                            const uint32_t lc = lds32(prmt(b < 4 ? xc.x : xc.y, lutlane, sel));
-                            const uint32_t ld = lds32(prmt(b < 4 ? xd.x : xd.y, lutlane, sel));
-                            mma16816(acc[b], prmt(la, lb, 0x5410u), prmt(la, lb, 0x7632u), prmt(lc, ld, 0x5410u),
-                                     prmt(lc, ld, 0x7632u), pb0, pb1);
+                        for (int w2 = 0; w2 < 2; ++w2) {
+                            const uint32_t ev_ab = (wa[w2] & 0x0f0f0f0fu) | ((wb[w2] << 4) & 0xf0f0f0f0u);
+                            const uint32_t od_ab = ((wa[w2] >> 4) & 0x0f0f0f0fu) | (wb[w2] & 0xf0f0f0f0u);
+                            const uint32_t ev_cd = (wc[w2] & 0x0f0f0f0fu) | ((wd[w2] << 4) & 0xf0f0f0f0u);
+                            const uint32_t od_cd = ((wc[w2] >> 4) & 0x0f0f0f0fu) | (wd[w2] & 0xf0f0f0f0u);
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const uint32_t sel = 0x7604u | ((uint32_t)b << 4);
+                                const uint32_t a0 = ldsp32(prmt(ev_ab, lutlane, sel));
+                                const uint32_t a1 = ldsp32(prmt(od_ab, lutlane, sel));
+                                const uint32_t a2 = ldsp32(prmt(ev_cd, lutlane, sel));
+                                const uint32_t a3 = ldsp32(prmt(od_cd, lutlane, sel));
+                                mma16816(acc[4 * w2 + b], a0, a1, a2, a3, pb0, pb1);
+                            }
                         }
                     } else {
-                        const uint32_t xa = lds32(vt + (rowA + 0) * 32u + (uint32_t)gl * 4u);
-                        const uint32_t xb = lds32(vt + (rowA + 1) * 32u + (uint32_t)gl * 4u);
-                        const uint32_t xc = lds32(vt + (rowA + 8) * 32u + (uint32_t)gl * 4u);
-                        const uint32_t xd = lds32(vt + (rowA + 9) * 32u + (uint32_t)gl * 4u);
+                        const uint32_t xa = ldsp32(vt + (rowA + 0) * kvp + (uint32_t)gl * 4u);
+                        const uint32_t xb = ldsp32(vt + (rowA + 1) * kvp + (uint32_t)gl * 4u);
+                        const uint32_t xc = ldsp32(vt + (rowA + 8) * kvp + (uint32_t)gl * 4u);
+                        const uint32_t xd = ldsp32(vt + (rowA + 9) * kvp + (uint32_t)gl * 4u);
 #pragma unroll
                         for (int bb = 0; bb < 4; ++bb) {
                             const uint32_t sel = 0x7604u | ((uint32_t)bb << 4);
-                            const uint2 la = lds64(prmt(xa, lutlane, sel));
-                            const uint2 lb = lds64(prmt(xb, lutlane, sel));
-                            const uint2 lc = lds64(prmt(xc, lutlane, sel));
-                            const uint2 ld = lds64(prmt(xd, lutlane, sel));
+                            const uint2 la = ldsp64(prmt(xa, lutlane, sel));
+                            const uint2 lb = ldsp64(prmt(xb, lutlane, sel));
+                            const uint2 lc = ldsp64(prmt(xc, lutlane, sel));
+                            const uint2 ld = ldsp64(prmt(xd, lutlane, sel));
                             mma16816(acc[2 * bb], prmt(la.x, lb.x, 0x5410u), prmt(la.x, lb.x, 0x7632u),
                                      prmt(lc.x, ld.x, 0x5410u), prmt(lc.x, ld.x, 0x7632u), pb0, pb1);
                             mma16816(acc[2 * bb + 1], prmt(la.y, lb.y, 0x5410u), prmt(la.y, lb.y, 0x7632u),
@@ -374,19 +490,33 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     }
                 }
             }
-            __syncwarp();
+            // Everything this warp read from the stage has been consumed by the (ordered) mma instructions above.
+            // The last warp of the worker to get here re-arms the stage with the tile S ahead; nobody waits.
             ++consumed;
-            if (!dead && ptile < hi) issue_one();
+            const int next_row = cl_row, next_tile = cl_tile, next_gend = cl_gend;
+            const bool more = cl_tile < hi_i;
+            if (more) cursor_advance();
+            __syncwarp();
+            if (lane == 0 && more && !dead && loads_on) {
+                __threadfence_block();  // this warp's reads of the stage are ordered before the hand-over below
+                const uint32_t old = atom_add_shared(cnt0 + 4u * s, 1u);
+                if (old == (uint32_t)Hkv - 1u) {
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
+                    fence_proxy_async_smem();
+                    issue_tile(next_row, s);
+                    prefetch_ahead(next_row, next_tile, next_gend);
+                }
+            }
         }
 
         // ================= end of segment: publish the partial, maybe merge =================
-        const int slot = blockIdx.x + g;
-        {
+        const int slot = wid + g;
+        if (!(p.debug & 8)) {
             float lsum = l_run;
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
             if (gl < grp && t4 == 0) {
-                float* dst = p.partials + ((size_t)slot * p.H + (size_t)warp * grp + gl) * PART_STRIDE;
+                float* dst = p.partials + ((size_t)slot * p.H + (size_t)head * grp + gl) * PART_STRIDE;
                 dst[HEAD_DIM] = m_run;
                 dst[HEAD_DIM + 1] = lsum;
             }
@@ -394,7 +524,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             for (int e = 0; e < 2; ++e) {
                 const int hq = 2 * t4 + e;
                 if (hq < grp) {
-                    float* dst = p.partials + ((size_t)slot * p.H + (size_t)warp * grp + hq) * PART_STRIDE + 16 * gl;
+                    float* dst = p.partials + ((size_t)slot * p.H + (size_t)head * grp + hq) * PART_STRIDE + 16 * gl;
 #pragma unroll
                     for (int b2 = 0; b2 < 4; ++b2) {
                         float4 o;
@@ -405,64 +535,123 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             }
         }
-        __threadfence();
-        __syncthreads();
-        // number of CTAs that hold a part of sequence g
+        if (p.debug & 4) { ++g; continue; }
+        // number of workers that hold a part of sequence g
         const int first_w = (int)(((ts_g + 1) * W - 1) / N);
         const int last_w = (int)((ts_g1 * W - 1) / N);
-        if (tid == 0) {
-            const int parts = last_w - first_w + 1;
-            const int old = atomicAdd(p.tickets + g, 1);
-            const uint32_t flag = (old == parts - 1) ? 1u : 0u;
-            if (flag) p.tickets[g] = 0;  // everybody has arrived: leave the ticket ready for the next launch
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(ctrl_s), "r"(flag) : "memory");
+        const int parts = last_w - first_w + 1;
+        group_barrier(group, gthreads);  // every warp's partial is written (happens-before the fence below)
+        uint32_t is_last = 1u;
+        if (parts > 1) {
+            if (gtid == 0) {
+                __threadfence();  // cumulative: orders the whole worker's partials before the ticket
+                const int old = atomicAdd(p.tickets + g, 1);
+                const uint32_t flag = (old == parts - 1) ? 1u : 0u;
+                if (flag) {
+                    p.tickets[g] = 0;  // everybody has arrived: leave the ticket ready for the next launch
+                    __threadfence();
+                }
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(ctrl_s), "r"(flag) : "memory");
+            }
+            group_barrier(group, gthreads);
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(is_last) : "r"(ctrl_s) : "memory");
         }
-        __syncthreads();
-        uint32_t is_last;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(is_last) : "r"(ctrl_s) : "memory");
         if (is_last) {
-            __threadfence();
             const int H = p.H;
-            const int Hp = (H + 7) & ~7;
-            // phase A: combine the parts, normalise -> merge[k][head]
-            for (int idx = tid; idx < H * HEAD_DIM; idx += nthreads) {
-                const int hq = idx >> 7, k = idx & 127;
-                float M = -1e30f;
-                for (int wk = first_w; wk <= last_w; ++wk)
-                    M = fmaxf(M, __ldcg(p.partials + ((size_t)(wk + g) * H + hq) * PART_STRIDE + HEAD_DIM));
-                float Z = 0.0f, a = 0.0f;
-                for (int wk = first_w; wk <= last_w; ++wk) {
-                    const float* src = p.partials + ((size_t)(wk + g) * H + hq) * PART_STRIDE;
-                    const float wgt = ex2_approx(__ldcg(src + HEAD_DIM) - M);
-                    Z += __ldcg(src + HEAD_DIM + 1) * wgt;
-                    a += __ldcg(src + k) * wgt;
-                }
-                const float val = a / (Z + 1e-8f);
-                asm volatile("st.shared.f32 [%0], %1;" ::"r"(merge_s + 4u * (uint32_t)(k * Hp + hq)), "f"(val) : "memory");
-            }
-            __syncthreads();
-            // phase B: out[head][d] = sum_k R[k][d] * merge[k][head]
-            const int d = tid & 127;
-            const int part = tid >> 7, nparts = nthreads >> 7;
-            for (int h0 = part * 8; h0 < H; h0 += nparts * 8) {
-                float o[8];
+            for (int hb = 0; hb < H; hb += 16) {
+                // ---- phase A: heads hb .. hb+15, one warp per head in turn: combine the parts, normalise,
+                //      split into fp16 high + low, store as the A operand [16][MERGE_ROW]
+                for (int hh = head; hh < 16; hh += Hkv) {
+                    const int hq = hb + hh;
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (hq < H) {
+                        const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
+                        const size_t pstride = (size_t)H * PART_STRIDE;
+                        if (parts <= 8) {
+                            // common case: all loads go out together (one round trip), weights afterwards
+                            float4 v[8];
+                            float2 ml = make_float2(-1e30f, 0.0f);
+                            if (lane < parts) ml = __ldcg(reinterpret_cast<const float2*>(base + lane * pstride + HEAD_DIM));
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = 0.0f;
-#pragma unroll 4
-                for (int k = 0; k < HEAD_DIM; ++k) {
-                    const float r = __half2float(__ldg(p.rotation + k * HEAD_DIM + d));
-                    const uint4 u0 = lds128(merge_s + 4u * (uint32_t)(k * Hp + h0));
-                    const uint4 u1 = lds128(merge_s + 4u * (uint32_t)(k * Hp + h0 + 4));
-                    o[0] = fmaf(r, __uint_as_float(u0.x), o[0]); o[1] = fmaf(r, __uint_as_float(u0.y), o[1]);
-                    o[2] = fmaf(r, __uint_as_float(u0.z), o[2]); o[3] = fmaf(r, __uint_as_float(u0.w), o[3]);
-                    o[4] = fmaf(r, __uint_as_float(u1.x), o[4]); o[5] = fmaf(r, __uint_as_float(u1.y), o[5]);
-                    o[6] = fmaf(r, __uint_as_float(u1.z), o[6]); o[7] = fmaf(r, __uint_as_float(u1.w), o[7]);
-                }
+                            for (int j = 0; j < 8; ++j)
+                                v[j] = j < parts ? __ldcg(reinterpret_cast<const float4*>(base + j * pstride) + lane)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                            float M = ml.x;
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (h0 + i < H) p.out[(size_t)g * p.q_dim + (size_t)(h0 + i) * HEAD_DIM + d] = __float2half_rn(o[i]);
+                            for (int o = 4; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                            M = __shfl_sync(0xffffffffu, M, 0);
+                            const float e = lane < parts ? ex2_approx(ml.x - M) : 0.0f;
+                            float Z = ml.y * e;
+#pragma unroll
+                            for (int o = 4; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
+                            Z = __shfl_sync(0xffffffffu, Z, 0);
+                            const float sc = e / (Z + 1e-8f);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float wj = __shfl_sync(0xffffffffu, sc, j);
+                                a.x = fmaf(wj, v[j].x, a.x); a.y = fmaf(wj, v[j].y, a.y);
+                                a.z = fmaf(wj, v[j].z, a.z); a.w = fmaf(wj, v[j].w, a.w);
+                            }
+                        } else {
+                            float M = -1e30f;
+                            for (int j = lane; j < parts; j += 32) M = fmaxf(M, __ldcg(base + j * pstride + HEAD_DIM));
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                            float Z = 0.0f;
+                            for (int j = lane; j < parts; j += 32)
+                                Z += __ldcg(base + j * pstride + HEAD_DIM + 1) * ex2_approx(__ldcg(base + j * pstride + HEAD_DIM) - M);
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
+                            const float inv = 1.0f / (Z + 1e-8f);
+                            for (int j0 = 0; j0 < parts; j0 += 32) {
+                                const int jn = parts - j0 < 32 ? parts - j0 : 32;
+                                float sc = 0.0f;
+                                if (lane < jn) sc = ex2_approx(__ldcg(base + (j0 + lane) * pstride + HEAD_DIM) - M) * inv;
+                                for (int j = 0; j < jn; ++j) {
+                                    const float wj = __shfl_sync(0xffffffffu, sc, j);
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (j0 + j) * pstride) + lane);
+                                    a.x = fmaf(wj, v.x, a.x); a.y = fmaf(wj, v.y, a.y);
+                                    a.z = fmaf(wj, v.z, a.z); a.w = fmaf(wj, v.w, a.w);
+                                }
+                            }
+                        }
+                    }
+                    __half2 h01 = __floats2half2_rn(a.x, a.y), h23 = __floats2half2_rn(a.z, a.w);
+                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                    const uint32_t dst = merge_s + (uint32_t)(hh * MERGE_ROW + 4 * lane) * 2u;
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h01)),
+                                 "r"(*reinterpret_cast<uint32_t*>(&h23)) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + 16u * MERGE_ROW * 2u),
+                                 "r"(pack_half2(a.x - f01.x, a.y - f01.y)), "r"(pack_half2(a.z - f23.x, a.w - f23.y)) : "memory");
+                }
+                group_barrier(group, gthreads);
+                // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k]
+                for (int nb = head; nb < 16; nb += Hkv) {
+                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    const __half* rt = p.rotation_t + (size_t)(8 * nb + gl) * HEAD_DIM + 2 * t4;
+                    uint32_t bfrag[8][2];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        bfrag[j][0] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j));
+                        bfrag[j][1] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j + 8));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t r0 = merge_s + (uint32_t)(gl * MERGE_ROW + 16 * j + 2 * t4) * 2u;
+                        const uint32_t r8 = r0 + 8u * MERGE_ROW * 2u;
+                        const uint32_t lo_off = 16u * MERGE_ROW * 2u;
+                        mma16816(c, lds32(r0), lds32(r8), lds32(r0 + 16u), lds32(r8 + 16u), bfrag[j][0], bfrag[j][1]);
+                        mma16816(c, lds32(r0 + lo_off), lds32(r8 + lo_off), lds32(r0 + lo_off + 16u), lds32(r8 + lo_off + 16u),
+                                 bfrag[j][0], bfrag[j][1]);
+                    }
+                    const int d = 8 * nb + 2 * t4;
+                    if (hb + gl < H)
+                        *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl) * HEAD_DIM + d) = __floats2half2_rn(c[0], c[1]);
+                    if (hb + gl + 8 < H)
+                        *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl + 8) * HEAD_DIM + d) = __floats2half2_rn(c[2], c[3]);
+                }
+                group_barrier(group, gthreads);
             }
-            __syncthreads();
         }
         ++g;
     }
@@ -470,8 +659,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     // A warp that gave up on a wait may still have copies in flight: give them a bounded chance to land
     // before the CTA (and its shared memory) goes away.
     if (dead) {
-        for (int n = consumed; n < issued; ++n)
-            mbar_wait_bounded(bar0 + 8u * (n % ATTN_STAGES), (uint32_t)(n / ATTN_STAGES) & 1u, 1u << 16);
+        for (int n = consumed; n < consumed + S && lo + n < hi; ++n)
+            mbar_wait_bounded(bar0 + 8u * (n & (S - 1)), (uint32_t)(n >> s_log) & 1u, 1u << 16);
     }
 }
 

@@ -9,6 +9,12 @@ static thread_local int g_compat_status = TQ_OK;
 
 static inline cudaStream_t cs(tq_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// The engine's own launches overlap each other's tails (programmatic dependent launch); TQ_PDL=0 turns it off.
+static inline bool use_pdl() {
+    static const bool on = !(getenv("TQ_PDL") && atoi(getenv("TQ_PDL")) == 0);
+    return on;
+}
+
 extern "C" {
 
 const char* tq_status_string(int status) {
@@ -88,7 +94,7 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
                        const void* q, const void* rotation, const int* positions, int pos_value,
                        const long long* row_base, int token_mode, long long token_row0, int max_seq_len, int n_src,
                        int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
-                       size_t workspace_bytes, bool build_tiles, cudaStream_t s) {
+                       size_t workspace_bytes, bool build_tiles, cudaStream_t s, bool pdl = false) {
     if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
     if (bits != 2 && bits != 4) return TQ_ERR_ARG;
     if (n_src <= 0 || num_kv_heads <= 0 || kv_dim != num_kv_heads * head_dim || !rotation) return TQ_ERR_ARG;
@@ -106,13 +112,15 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.q_rot = fw.w.q_rot;
     p.tile_start = build_tiles ? fw.w.tile_start : nullptr;
     p.tickets = build_tiles ? fw.w.tickets : nullptr;
+    p.worker_g = build_tiles ? fw.w.worker_g : nullptr;
+    p.n_workers = attention_ctas(n_src, max_seq_len) * ATTN_GROUPS;
     p.total_tiles = fw.w.total_tiles;
     p.status = fw.w.status;
     p.token_row0 = token_row0; p.token_mode = token_mode;
     p.max_seq_len = max_seq_len; p.capacity_rows = max_seq_len;
     p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
     p.pos_value = pos_value;
-    return launch_append(p, s);
+    return launch_append(p, s, pdl);
 }
 
 int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf, const void* v_buf,
@@ -125,20 +133,29 @@ int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms,
                        workspace_bytes, true, cs(s));
 }
 
-static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* k_norms,
-                          const void* v_norms, const void* rotation, const int* positions, int pos_value,
-                          const long long* row_base, int max_seq_len, int G, int num_heads, int num_kv_heads,
-                          int q_dim, int bits, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+static int attention_impl(void* out, const void* ck_q, const void* cv_q, const void* k_norms, const void* v_norms,
+                          const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
+                          long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
+                          int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false) {
     FullWorkspace fw = carve_full(workspace, G, num_heads);
     if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
+    // bulk copies need 16-byte aligned sources: rows are 512/256 B (codes) and 2*Hkv B (norms, Hkv % 4 == 0 -> 8|16 B)
+    if ((((uintptr_t)ck_q | (uintptr_t)cv_q | (uintptr_t)k_norms | (uintptr_t)v_norms) & 15u) != 0) return TQ_ERR_ARG;
+    // norm rows are 2*Hkv bytes: with 4 KV heads (8 B) every slot and the array end must fall on an even row
+    if (num_kv_heads % 8 != 0 && ((max_seq_len & 1) || (total_rows & 1))) return TQ_ERR_UNSUPPORTED;
     AttnParams p{};
+    p.ck = (const uint8_t*)ck_q; p.cv = (const uint8_t*)cv_q;
     p.kn = (const __half*)k_norms; p.vn = (const __half*)v_norms;
-    p.q_rot = fw.w.q_rot; p.rotation = (const __half*)rotation; p.out = (__half*)out;
+    p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)rotation_t; p.out = (__half*)out;
     p.positions = positions; p.row_base = row_base;
-    p.tile_start = fw.w.tile_start; p.tickets = fw.w.tickets; p.partials = fw.w.partials; p.status = fw.w.status;
+    p.tile_start = fw.w.tile_start; p.worker_g = fw.w.worker_g; p.tickets = fw.w.tickets; p.partials = fw.w.partials;
+    p.status = fw.w.status;
+    p.total_rows = total_rows;
     p.pos_value = pos_value; p.max_seq_len = max_seq_len;
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim;
-    return launch_attention(bits, tmK, tmV, p, attention_workers(G, max_seq_len), s);
+    static const int debug_mode = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
+    p.debug = debug_mode;
+    return launch_attention(bits, p, attention_ctas(G, max_seq_len), s, pdl);
 }
 
 int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms, const void* v_norms,
@@ -150,14 +167,14 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
     if (!out || !ck_q || !cv_q || !k_norms || !v_norms || !rotation) return TQ_ERR_ARG;
     if (!positions && pos_value < 0) return TQ_ERR_ARG;
     if (!workspace) return TQ_ERR_WORKSPACE;
-    const int vpb = bits == 2 ? 4 : 2;
-    CUtensorMap tmK, tmV;
-    r = cached_code_map(&tmK, ck_q, total_rows, kv_dim / vpb, head_dim / vpb);
+    // this entry point only receives R: transpose it into the workspace for the merge's tensor-core product
+    FullWorkspace fw = carve_full(workspace, G, num_heads);
+    if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
+    transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation);
+    r = cuda_status(cudaGetLastError());
     if (r != TQ_OK) return r;
-    r = cached_code_map(&tmV, cv_q, total_rows, kv_dim / vpb, head_dim / vpb);
-    if (r != TQ_OK) return r;
-    return attention_impl(out, tmK, tmV, k_norms, v_norms, rotation, positions, pos_value, row_base, max_seq_len, G,
-                          num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
+    return attention_impl(out, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, pos_value, row_base, total_rows,
+                          max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
 }
 
 // ---- fp16 twin ---------------------------------------------------------------------------------------------------------
@@ -369,6 +386,20 @@ int tq_engine_create(const tq_model_shape* shape, int max_seq_len, int kv_bits, 
     return TQ_OK;
 }
 
+// R and its transpose (for the merge's tensor-core product) to the device; both live outside the arena.
+static int engine_upload_rotation(tq_engine* e, cudaStream_t s) {
+    const size_t bytes = e->h_rotation.size() * 2;
+    if (!e->d_rotation) TQ_CUDA(cudaMalloc(&e->d_rotation, bytes));
+    if (!e->d_rotation_t) TQ_CUDA(cudaMalloc(&e->d_rotation_t, bytes));
+    std::vector<uint16_t> t(e->h_rotation.size());
+    for (int k = 0; k < HEAD_DIM; ++k)
+        for (int d = 0; d < HEAD_DIM; ++d) t[(size_t)d * HEAD_DIM + k] = e->h_rotation[(size_t)k * HEAD_DIM + d];
+    TQ_CUDA(cudaMemcpyAsync(e->d_rotation, e->h_rotation.data(), bytes, cudaMemcpyHostToDevice, s));
+    TQ_CUDA(cudaMemcpyAsync(e->d_rotation_t, t.data(), bytes, cudaMemcpyHostToDevice, s));
+    TQ_CUDA(cudaStreamSynchronize(s));  // t and h_rotation are pageable host memory
+    return TQ_OK;
+}
+
 static void engine_release_arena(tq_engine* e) {
     if (e->arena && !e->arena_external) cudaFree(e->arena);
     e->arena = nullptr;
@@ -386,6 +417,7 @@ void tq_engine_destroy(tq_engine* e) {
     if (!e) return;
     engine_release_arena(e);
     if (e->d_rotation) cudaFree(e->d_rotation);
+    if (e->d_rotation_t) cudaFree(e->d_rotation_t);
     delete e;
 }
 
@@ -495,17 +527,8 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
     TQ_CUDA(cudaMemset(e->workspace, 0, e->ws_bytes));
     if (ragged) TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
     if (!e->d_rotation) {
-        TQ_CUDA(cudaMalloc(&e->d_rotation, e->h_rotation.size() * 2));
-        TQ_CUDA(cudaMemcpy(e->d_rotation, e->h_rotation.data(), e->h_rotation.size() * 2, cudaMemcpyHostToDevice));
-    }
-    if (e->kv_bits != 0) {
-        const int kvp = e->kv_dim() / e->vpb(), bph = HEAD_DIM / e->vpb();
-        for (auto& L : e->layers) {
-            r = make_code_map(&L.tmK, L.k, rows, kvp, bph);
-            if (r != TQ_OK) return r;
-            r = make_code_map(&L.tmV, L.v, rows, kvp, bph);
-            if (r != TQ_OK) return r;
-        }
+        int ur = engine_upload_rotation(e, nullptr);
+        if (ur != TQ_OK) return ur;
     }
     return TQ_OK;
 }
@@ -590,10 +613,7 @@ const void* tq_engine_rotation(tq_engine* e) { return e ? e->d_rotation : nullpt
 int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s) {
     if (!e || !host_half) return TQ_ERR_ARG;
     memcpy(e->h_rotation.data(), host_half, e->h_rotation.size() * 2);
-    if (!e->d_rotation) TQ_CUDA(cudaMalloc(&e->d_rotation, e->h_rotation.size() * 2));
-    TQ_CUDA(cudaMemcpyAsync(e->d_rotation, e->h_rotation.data(), e->h_rotation.size() * 2, cudaMemcpyHostToDevice, cs(s)));
-    TQ_CUDA(cudaStreamSynchronize(cs(s)));
-    return TQ_OK;
+    return engine_upload_rotation(e, cs(s));
 }
 
 int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
@@ -613,10 +633,10 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
-                        e->ws_bytes, true, cs(s));
+                        e->ws_bytes, true, cs(s), use_pdl());
     if (r != TQ_OK) return r;
-    return attention_impl(out, L.tmK, L.tmV, L.kn, L.vn, e->d_rotation, e->d_positions, -1, e->d_row_base, e->msl, e->G,
-                          H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s));
+    return attention_impl(out, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
+                          e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl());
 }
 
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
@@ -624,9 +644,20 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
     const tq_engine::Layer& L = e->layers[layer];
-    return attention_impl(out, L.tmK, L.tmV, L.kn, L.vn, e->d_rotation, e->d_positions, -1, e->d_row_base, e->msl, e->G,
-                          e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
-                          cs(s));
+    return attention_impl(out, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
+                          e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace,
+                          e->ws_bytes, cs(s), use_pdl());
+}
+
+int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s) {
+    if (!e || !out) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    const size_t qb = (size_t)e->G * e->q_dim() * 2;
+    for (int l = 0; l < e->shape.num_layers; ++l) {
+        int r = tq_engine_attend_layer(e, l, (char*)out + qb * l, s);
+        if (r != TQ_OK) return r;
+    }
+    return TQ_OK;
 }
 
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {

@@ -2,7 +2,6 @@
 // mma.sync, prmt), the workspace layout and the status word.
 #pragma once
 
-#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -35,6 +34,7 @@ enum : int {
 // q_rot      float [G][H][128]  pre-rotated queries, already multiplied by log2(e)/sqrt(128)
 // tile_start int   [G+1]        exclusive prefix of ceil(L_g / TILE_TOKENS)
 // tickets    int   [G]          arrivals per sequence (zeroed by the append/rotate kernel)
+// worker_g   int   [MAX_WORKERS] first sequence of each attention worker's slice
 // partials   float [W+G][H][PART_STRIDE]  acc[128], m, l, pad
 constexpr int PART_STRIDE = 132;
 constexpr int MAX_WORKERS = 1024;  // upper bound on attention CTAs assumed by the workspace size
@@ -45,6 +45,7 @@ struct Workspace {
     float* q_rot;
     int* tile_start;
     int* tickets;
+    int* worker_g;     // [MAX_WORKERS] first sequence of every attention worker (written with tile_start)
     float* partials;
     size_t bytes;
 };
@@ -64,6 +65,8 @@ __host__ inline Workspace carve_workspace(void* base, int G, int H) {
     off += align_up((size_t)(G + 1) * sizeof(int), 256);
     w.tickets = (int*)(p + off);
     off += align_up((size_t)G * sizeof(int), 256);
+    w.worker_g = (int*)(p + off);
+    off += align_up((size_t)MAX_WORKERS * sizeof(int), 256);
     w.partials = (float*)(p + off);
     off += align_up((size_t)(MAX_WORKERS + G) * H * PART_STRIDE * sizeof(float), 256);
     w.bytes = off;
@@ -137,6 +140,12 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// ---- programmatic dependent launch: a kernel launched with the programmatic-serialisation attribute may start
+// while its predecessor in the stream is still running; everything that depends on the predecessor's writes (or
+// that overwrites something the predecessor still reads) comes after pdl_wait().  No-ops otherwise.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier / TMA ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -171,15 +180,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
     }
     return false;
-}
-
-// 2-D tiled TMA load global -> shared of this CTA (no multicast), completion on an mbarrier.
-// x = innermost coordinate in elements (bytes here; must be a multiple of 16), y = row.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst_smem), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
 }
 
 }  // namespace tq

@@ -11,8 +11,6 @@
 #include <tuple>
 #include <vector>
 
-#include <cudaTypedefs.h>
-
 #include "../../include/triebwerk_b200.h"
 #include "tq_append.cuh"
 #include "tq_attention.cuh"
@@ -31,7 +29,6 @@ inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? TQ_OK : (int)e
 
 struct DeviceProps {
     int sm_count = 0;
-    bool attn4_attr = false, attn2_attr = false;
 };
 
 inline DeviceProps& device_props() {
@@ -48,35 +45,6 @@ inline DeviceProps& device_props() {
     return d;
 }
 
-// ---- TMA descriptors ----------------------------------------------------------------------------------------------
-inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
-    });
-    return fn;
-}
-
-// Code array viewed as uint8 [rows][kvp]; box = one head's bytes (bph) x TILE_TOKENS rows.
-inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int kvp, int bph) {
-    auto fn = encode_fn();
-    if (!fn) return TQ_ERR_UNSUPPORTED;
-    if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31)) return TQ_ERR_ARG;
-    cuuint64_t dims[2] = {(cuuint64_t)kvp, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kvp};
-    cuuint32_t box[2] = {(cuuint32_t)bph, (cuuint32_t)TILE_TOKENS};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
-}
-
 // ---- workspace ------------------------------------------------------------------------------------------------------
 // The carve of tq_common.cuh plus two helper arrays used by the prefill form (positions 0..T-1 and a
 // constant row base) and the fp16 twin's ticket/partial area, which aliases the packed path's partials.
@@ -84,6 +52,7 @@ struct FullWorkspace {
     Workspace w;
     int* aux_pos;          // [G]
     long long* aux_rows;   // [G]
+    __half* rot_t;         // [128][128] transposed rotation (for callers that only hand over R)
     size_t bytes;
 };
 
@@ -96,6 +65,8 @@ inline FullWorkspace carve_full(void* base, int G, int H) {
     off += align_up((size_t)G * sizeof(int), 256);
     f.aux_rows = (long long*)(p + off);
     off += align_up((size_t)G * sizeof(long long), 256);
+    f.rot_t = (__half*)(p + off);
+    off += (size_t)HEAD_DIM * HEAD_DIM * sizeof(__half);
     f.bytes = off;
     return f;
 }
@@ -121,44 +92,71 @@ inline int check_shape(int G, int H, int Hkv, int head_dim, int q_dim, int kv_di
 }
 
 // ---- launches -------------------------------------------------------------------------------------------------------------
-inline int launch_append(const AppendParams& p, cudaStream_t s) {
+// Launch with the programmatic-serialisation attribute: the kernel may start while the previous kernel of the
+// stream is still running; the kernels themselves wait (griddepcontrol.wait) before touching dependent data.
+template <typename Kernel, typename Params>
+inline int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, const Params& p) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, p));
+}
+
+inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
     const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
     const long long total = (long long)p.n_src * (nk + nv + nq);
     if (total <= 0 && p.tile_start == nullptr) return TQ_OK;
     long long groups = (total + APPEND_NV - 1) / APPEND_NV;
     long long cap = (long long)device_props().sm_count * 3;
     int grid = (int)(groups < 1 ? 1 : (groups < cap ? groups : cap));
-    append_rotate_kernel<<<grid, 128, 0, s>>>(p);
-    return cuda_status(cudaGetLastError());
+    return launch_kernel(append_rotate_kernel, dim3(grid), dim3(128), 0, s, pdl, p);
 }
 
-inline int attention_workers(int G, int max_seq_len) {
+// Number of attention CTAs: one per SM (each holds ATTN_GROUPS workers), fewer when the cache cannot hold that
+// many tiles.
+inline int attention_ctas(int G, int max_seq_len) {
     long long tiles = (long long)G * ((max_seq_len + TILE_TOKENS - 1) / TILE_TOKENS);
     long long w = device_props().sm_count;
-    if (w > MAX_WORKERS) w = MAX_WORKERS;
-    if (tiles < w) w = tiles;
+    if (w * ATTN_GROUPS > MAX_WORKERS) w = MAX_WORKERS / ATTN_GROUPS;
+    long long need = (tiles + ATTN_GROUPS - 1) / ATTN_GROUPS;
+    if (need < w) w = need;
     return (int)(w < 1 ? 1 : w);
 }
 
-inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int workers,
-                            cudaStream_t s) {
-    DeviceProps& d = device_props();
-    if (bits == 4) {
-        if (!d.attn4_attr) {
-            TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)ATTN_DYN_SMEM));
-            d.attn4_attr = true;
-        }
-        decode_attention_kernel<4><<<workers, 32 * p.Hkv, ATTN_DYN_SMEM, s>>>(tmK, tmV, p);
-    } else {
-        if (!d.attn2_attr) {
-            TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)ATTN_DYN_SMEM));
-            d.attn2_attr = true;
-        }
-        decode_attention_kernel<2><<<workers, 32 * p.Hkv, ATTN_DYN_SMEM, s>>>(tmK, tmV, p);
+template <int BITS, bool QSPLIT>
+inline int launch_attention_t(const AttnParams& p, int ctas, cudaStream_t s, bool pdl) {
+    static std::map<int, bool> attr_set;  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)ATTN_DYN_SMEM));
+        attr_set[dev] = true;
     }
-    return cuda_status(cudaGetLastError());
+    return launch_kernel(decode_attention_kernel<BITS, QSPLIT>, dim3(ctas), dim3(ATTN_GROUPS * 32 * p.Hkv), ATTN_DYN_SMEM, s,
+                         pdl, p);
+}
+
+inline int launch_attention(int bits, const AttnParams& p, int ctas, cudaStream_t s, bool pdl = false) {
+    // TQ_ATTN_QSPLIT=0 selects the variant that feeds the query to the tensor cores as plain fp16 (no high/low split)
+    static const bool qsplit = !(getenv("TQ_ATTN_QSPLIT") && atoi(getenv("TQ_ATTN_QSPLIT")) == 0);
+    if (bits == 4) return qsplit ? launch_attention_t<4, true>(p, ctas, s, pdl) : launch_attention_t<4, false>(p, ctas, s, pdl);
+    return qsplit ? launch_attention_t<2, true>(p, ctas, s, pdl) : launch_attention_t<2, false>(p, ctas, s, pdl);
+}
+
+__global__ void transpose_rotation_kernel(__half* dst, const __half* src) {
+    // dst[d][k] = src[k][d]; one block per 32x32 tile would be overkill for 32 KB: a plain strided copy
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < HEAD_DIM * HEAD_DIM; i += gridDim.x * blockDim.x) {
+        const int d = i >> 7, k = i & 127;
+        dst[i] = src[k * HEAD_DIM + d];
+    }
 }
 
 inline int launch_fp16_attention(const Fp16AttnParams& p, cudaStream_t s) {
@@ -187,7 +185,6 @@ __global__ void iota_rows_kernel(int* pos, long long* rows, int n, long long row
 struct CompatState {
     void* ws = nullptr;
     size_t ws_bytes = 0;
-    std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> maps;
 };
 
 inline CompatState& compat_state() {
@@ -216,21 +213,6 @@ inline int compat_workspace(size_t need, void** out, cudaStream_t s) {
         c.ws_bytes = need;
     }
     *out = c.ws;
-    return TQ_OK;
-}
-
-inline int cached_code_map(CUtensorMap* out, const void* base, long long rows, int kvp, int bph) {
-    CompatState& c = compat_state();
-    auto key = std::make_tuple(base, rows, kvp, bph);
-    auto it = c.maps.find(key);
-    if (it == c.maps.end()) {
-        CUtensorMap m;
-        int r = make_code_map(&m, base, rows, kvp, bph);
-        if (r != TQ_OK) return r;
-        if (c.maps.size() > 4096) c.maps.clear();
-        it = c.maps.emplace(key, m).first;
-    }
-    *out = it->second;
     return TQ_OK;
 }
 
@@ -264,7 +246,6 @@ struct tq_engine {
         void* v = nullptr;
         void* kn = nullptr;
         void* vn = nullptr;
-        CUtensorMap tmK{}, tmV{};
     };
     std::vector<Layer> layers;
 
@@ -277,9 +258,10 @@ struct tq_engine {
     void* stage_v = nullptr;
     void* stage_out = nullptr; // [layers][G][q_dim]
 
-    // rotation: host copy kept across sleep, device copy outside the arena (32 KB)
+    // rotation: host copy kept across sleep, device copies (R and R transposed, 32 KB each) outside the arena
     std::vector<uint16_t> h_rotation;
     void* d_rotation = nullptr;
+    void* d_rotation_t = nullptr;
 
     int q_dim() const { return shape.num_heads * shape.head_dim; }
     int kv_dim() const { return shape.num_kv_heads * shape.head_dim; }

@@ -115,6 +115,11 @@ class Engine:
         check(lib().tq_engine_attend_layer(self._h, layer, out.data_ptr(), self._stream()), "attend_layer")
         return out
 
+    def attend_step(self, out: torch.Tensor) -> torch.Tensor:
+        """attend_layer for every layer, out [layers, G, q_dim] (one C call, used to time the attention kernel)."""
+        check(lib().tq_engine_attend_step(self._h, out.data_ptr(), self._stream()), "attend_step")
+        return out
+
     def decode_step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """All layers of one decode step on device buffers [layers, G, dim]."""
         for t in (q, k, v, out):
