@@ -42,6 +42,8 @@ WORKLOADS = {
                desc="Qwen3-0.6B shape decode step: 28 layers, 64 seq x ctx 4096, kv_bits=4"),
     "c3": dict(layers=36, H=32, Hkv=8, G=32, L=8192, bits=2, prompt=100,
                desc="Qwen3-8B shape decode step: 36 layers, 32 seq per GPU x ctx 8192, kv_bits=2"),
+    "c1l4": dict(layers=4, H=16, Hkv=8, G=64, L=4096, bits=4, prompt=100,
+                 desc="4 of the 28 layers of c1 (same per-layer shape; for profiler captures): 64 seq x ctx 4096, kv_bits=4"),
     "small": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=100,
                   desc="reduced case for profiler captures: 4 layers, 16 seq x ctx 2048, kv_bits=4"),
 }

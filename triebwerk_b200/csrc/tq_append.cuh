@@ -7,17 +7,19 @@
 //   * inv = rsqrt.approx.ftz(ss + 1e-12f); xh = v * inv (mul.ftz);
 //   * rot[d] = fma.rn.ftz chain over k = 0..127 of float(R[d][k]) * xh[k], starting from 0;
 //   * code = number of bounds <= rot (NaN -> 15 for 4-bit, 0 for 2-bit); norm = half(sqrt.approx.ftz(ss + 1e-12f)).
-// What changes is the data movement: one CTA keeps row d of R in the registers of thread d and streams
-// many head vectors through it (the reference re-reads all 32 KB of R for every single vector), K, V and
-// the query rotation share one launch, and NV vectors are in flight per thread for instruction-level
-// parallelism along the 128-long dependent FMA chain.
+// What changes is the data movement: a CTA stages R once in shared memory as fp32, laid out so that thread d
+// (output coordinate d) fetches R[d][k..k+3] with one conflict-free 16-byte load, and streams many head vectors
+// through it (the reference re-reads all 32 KB of R, uncoalesced, for every single vector); K, V and the query
+// rotation share one launch; NV vectors advance together, step by step, for instruction-level parallelism along
+// the 128-long dependent FMA chain; the chain is a short rolled loop (a fully unrolled one is instruction-fetch
+// bound, every warp runs it once).
 #pragma once
 
 #include "tq_common.cuh"
 
 namespace tq {
 
-constexpr int APPEND_NV = 4;  // head vectors processed together by one CTA
+constexpr int APPEND_MAX_NV = 8;  // head vectors processed together by one CTA: 2, 4 or 8 (chosen per launch)
 
 struct AppendParams {
     // destinations (K cache, V cache); either pair may be null
@@ -46,6 +48,7 @@ struct AppendParams {
     int n_src;                   // G (batch mode) or T (token mode)
     int H, Hkv, q_dim, kv_dim, bits;
     int pos_value;               // used when positions == nullptr
+    long long* stamps;           // optional (measurement): 16 clock stamps, 8 from block 0 and 8 from block 1
 };
 
 __device__ __forceinline__ int quantize_code(float v, int bits) {
@@ -59,39 +62,57 @@ __device__ __forceinline__ int quantize_code(float v, int bits) {
     return ((v >= kBnd2[0]) ? 1 : 0) + ((v >= kBnd2[1]) ? 1 : 0) + ((v >= kBnd2[2]) ? 1 : 0);
 }
 
-// One CTA = 128 threads; thread d owns output coordinate d and row d of R.
+// One CTA = 128 threads; thread d owns output coordinate d and row d of R.  When the launch also has to build the
+// attention kernel's tables, block 0 does only that and the head vectors start at block 1.
+template <int NV>
 __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p) {
-    __shared__ __align__(16) float xs[APPEND_NV][HEAD_DIM];
-    __shared__ float warp_part[APPEND_NV][4];
-    __shared__ uint8_t codes[APPEND_NV][HEAD_DIM];
+    __shared__ __align__(16) float xs[NV][HEAD_DIM];
+    __shared__ float warp_part[NV][4];
+    __shared__ __align__(16) uint8_t codes[NV][HEAD_DIM];
+    __shared__ long long dest_row[NV];
+    __shared__ int dest_meta[NV];
 
     const int d = threadIdx.x;
     const int lane = d & 31, wid = d >> 5;
 
     pdl_launch_dependents();
+    const bool has_tables = p.tile_start != nullptr && !p.token_mode;
+    long long* stamp = (p.stamps && blockIdx.x < 2 && d == 0) ? p.stamps + 8 * blockIdx.x : nullptr;
+    auto mark = [&](int i) {
+        if (stamp) {
+            long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            stamp[i] = t;
+        }
+    };
+    mark(0);
 
-    // Row d of R into registers as fp32 (exact: fp16 -> fp32).  R is never written by a kernel, so this may run
-    // while the previous kernel in the stream is still finishing.
-    float r[HEAD_DIM];
-    {
+    // R into shared memory as fp32, Rs[k/4][d][k%4]: thread d later reads R[d][4j..4j+3] as one float4, consecutive
+    // threads 16 bytes apart.  R is never written by a kernel, so this may run while the previous kernel in the
+    // stream is still finishing.
+    extern __shared__ __align__(16) float Rs[];
+    if (!(blockIdx.x == 0 && has_tables)) {
         const uint4* src = reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM);
+        uint4 rr[HEAD_DIM / 8];
+#pragma unroll
+        for (int i = 0; i < HEAD_DIM / 8; ++i) rr[i] = __ldg(src + i);  // all 16 loads in flight together
 #pragma unroll
         for (int i = 0; i < HEAD_DIM / 8; ++i) {
-            uint4 u = __ldg(src + i);
+            const uint4 u = rr[i];
             const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 f = __half22float2(h2[j]);
-                r[8 * i + 2 * j] = f.x;
-                r[8 * i + 2 * j + 1] = f.y;
-            }
+            const float2 f0 = __half22float2(h2[0]), f1 = __half22float2(h2[1]);
+            const float2 f2 = __half22float2(h2[2]), f3 = __half22float2(h2[3]);
+            *reinterpret_cast<float4*>(&Rs[((2 * i) * HEAD_DIM + d) * 4]) = make_float4(f0.x, f0.y, f1.x, f1.y);
+            *reinterpret_cast<float4*>(&Rs[((2 * i + 1) * HEAD_DIM + d) * 4]) = make_float4(f2.x, f2.y, f3.x, f3.y);
         }
     }
+    mark(1);
     pdl_wait();  // inputs come from earlier kernels; the workspace may still be read by the previous attention
+    mark(2);
 
     // Block 0 also prepares the attention kernel's tables: tickets = 0, tile_start = prefix of tiles, and the
     // first sequence of every worker's slice of the flat tile list.
-    if (blockIdx.x == 0 && p.tile_start != nullptr && !p.token_mode) {
+    if (blockIdx.x == 0 && has_tables) {
         __shared__ int scan[128];
         const int G = p.n_src;
         const int per = (G + 127) / 128;
@@ -115,89 +136,83 @@ __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p
             __syncthreads();
         }
         int run = scan[d] - local;  // exclusive
+        const int N = scan[127];
+        const int W = p.n_workers < N ? p.n_workers : N;
         for (int i = 0; i < per; ++i) {
             int g = d * per + i;
             if (g < G) {
                 p.tile_start[g] = run;
                 int pos = p.positions ? p.positions[g] : p.pos_value;
                 if (pos < 0) pos = 0;
-                run += (pos + 1 + TILE_TOKENS - 1) / TILE_TOKENS;
+                const int next = run + (pos + 1 + TILE_TOKENS - 1) / TILE_TOKENS;
+                if (p.worker_g) {
+                    // worker w starts at tile floor(w*N/W); it starts inside sequence g iff ceil(run*W/N) <= w < ceil(next*W/N)
+                    const int w0 = (int)(((long long)run * W + N - 1) / N);
+                    const int w1 = (int)(((long long)next * W + N - 1) / N);
+                    for (int w = w0; w < w1; ++w) p.worker_g[w] = g;
+                }
+                run = next;
             }
         }
-        const int N = scan[127];
         if (d == 127) {
             p.tile_start[G] = N;
             if (p.total_tiles) *p.total_tiles = N;
         }
-        __syncthreads();  // tile_start is complete and visible to this block
-        if (p.worker_g) {
-            const int W = p.n_workers < N ? p.n_workers : N;
-            for (int w = d; w < W; w += 128) {
-                const long long lo = (long long)w * N / W;
-                int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
-                while (b - a > 1) {
-                    int mid = (a + b) >> 1;
-                    if ((long long)p.tile_start[mid] <= lo) a = mid; else b = mid;
-                }
-                p.worker_g[w] = a;
-            }
-        }
-        __syncthreads();
+        mark(3);
+        return;
     }
 
     const int nk = p.k_buf ? p.Hkv : 0;
     const int nv = p.v_buf ? p.Hkv : 0;
     const int nq = p.q ? p.H : 0;
     const int per_src = nk + nv + nq;
-    const long long total = (long long)p.n_src * per_src;
-    if ((long long)blockIdx.x * APPEND_NV >= total) return;
+    const int total = p.n_src * per_src;  // the host refuses launches with 2^31 vectors or more
+    const int vblock = (int)blockIdx.x - (has_tables ? 1 : 0);  // index among the blocks that process vectors
+    const int vblocks = (int)gridDim.x - (has_tables ? 1 : 0);
+    if (vblock * NV >= total) return;
 
     const int vpb = (p.bits == 2) ? 4 : 2;
     const int bph = HEAD_DIM / vpb;
     const int kvp = p.kv_dim / vpb;
 
-    for (long long base = (long long)blockIdx.x * APPEND_NV; base < total; base += (long long)gridDim.x * APPEND_NV) {
-        // ---- load, sum of squares, normalise ----
-        float val[APPEND_NV];
-        int kind[APPEND_NV];  // 0 = K, 1 = V, 2 = Q, -1 = none
-        int srcid[APPEND_NV], head[APPEND_NV];
+    for (int base = vblock * NV; base < total; base += vblocks * NV) {
+        // ---- decode the NV work items without branches, then issue every load at once ----
+        int kind[NV];  // 0 = K, 1 = V, 2 = Q, -1 = none
+        int srcid[NV], head[NV];
+        const __half* src[NV];
 #pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) {
-            long long item = base + v;
-            kind[v] = -1;
-            val[v] = 0.0f;
-            srcid[v] = 0;
-            head[v] = 0;
-            if (item < total) {
-                int s = (int)(item / per_src);
-                int w = (int)(item - (long long)s * per_src);
-                srcid[v] = s;
-                if (w < nk) {
-                    kind[v] = 0;
-                    head[v] = w;
-                    val[v] = __half2float(p.k_buf[(size_t)s * p.kv_dim + (size_t)w * HEAD_DIM + d]);
-                } else if (w < nk + nv) {
-                    kind[v] = 1;
-                    head[v] = w - nk;
-                    val[v] = __half2float(p.v_buf[(size_t)s * p.kv_dim + (size_t)(w - nk) * HEAD_DIM + d]);
-                } else {
-                    kind[v] = 2;
-                    head[v] = w - nk - nv;
-                    val[v] = __half2float(p.q[(size_t)s * p.q_dim + (size_t)(w - nk - nv) * HEAD_DIM + d]);
-                }
-            }
+        for (int v = 0; v < NV; ++v) {
+            const int item = base + v;
+            const bool live = item < total;
+            const int s = live ? item / per_src : 0;
+            const int w = live ? item - s * per_src : 0;
+            srcid[v] = s;
+            const bool is_k = w < nk, is_v = !is_k && w < nk + nv;
+            kind[v] = !live ? -1 : (is_k ? 0 : (is_v ? 1 : 2));
+            head[v] = is_k ? w : (is_v ? w - nk : w - nk - nv);
+            const __half* basep = is_k ? p.k_buf : (is_v ? p.v_buf : p.q);
+            const int stride = (is_k || is_v) ? p.kv_dim : p.q_dim;
+            src[v] = basep + (size_t)s * stride + (size_t)head[v] * HEAD_DIM + d;
         }
+        float val[NV];
+        int posv[NV];
 #pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) {
+        for (int v = 0; v < NV; ++v) {
+            val[v] = kind[v] >= 0 ? __half2float(*src[v]) : 0.0f;
+            posv[v] = (kind[v] >= 0 && p.positions) ? p.positions[srcid[v]] : p.pos_value;
+        }
+        // ---- sum of squares (reference order), normalise ----
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
             float sq = mul_ftz(val[v], val[v]);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) sq = add_ftz(sq, __shfl_down_sync(0xffffffffu, sq, off));
             if (lane == 0) warp_part[v][wid] = sq;
         }
         __syncthreads();
-        float t[APPEND_NV];
+        float t[NV];
 #pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) {
+        for (int v = 0; v < NV; ++v) {
             float ss = add_ftz(add_ftz(warp_part[v][0], warp_part[v][2]), add_ftz(warp_part[v][1], warp_part[v][3]));
             t[v] = add_ftz(ss, 1e-12f);
             float inv = rsqrt_approx_ftz(t[v]);
@@ -205,65 +220,92 @@ __global__ void __launch_bounds__(128) append_rotate_kernel(const AppendParams p
             xs[v][d] = (kind[v] == 2) ? val[v] : mul_ftz(val[v], inv);
         }
         __syncthreads();
+        mark(3);
 
-        // ---- rotation: k-ascending fused chain per output coordinate ----
-        float acc[APPEND_NV];
+        // ---- rotation: k-ascending fused chain per output coordinate, the NV chains interleaved step by step ----
+        float acc[NV];
 #pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) acc[v] = 0.0f;
+        for (int v = 0; v < NV; ++v) acc[v] = 0.0f;
+#pragma unroll 4
+        for (int j = 0; j < HEAD_DIM / 4; ++j) {
+            const float4 r = *reinterpret_cast<const float4*>(&Rs[(j * HEAD_DIM + d) * 4]);
+            float4 x[NV];
 #pragma unroll
-        for (int k = 0; k < HEAD_DIM; k += 4) {
+            for (int v = 0; v < NV; ++v) x[v] = *reinterpret_cast<const float4*>(&xs[v][4 * j]);
 #pragma unroll
-            for (int v = 0; v < APPEND_NV; ++v) {
-                float4 x = *reinterpret_cast<const float4*>(&xs[v][k]);
-                acc[v] = fma_ftz(r[k + 0], x.x, acc[v]);
-                acc[v] = fma_ftz(r[k + 1], x.y, acc[v]);
-                acc[v] = fma_ftz(r[k + 2], x.z, acc[v]);
-                acc[v] = fma_ftz(r[k + 3], x.w, acc[v]);
-            }
+            for (int v = 0; v < NV; ++v) acc[v] = fma_ftz(r.x, x[v].x, acc[v]);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = fma_ftz(r.y, x[v].y, acc[v]);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = fma_ftz(r.z, x[v].z, acc[v]);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = fma_ftz(r.w, x[v].w, acc[v]);
         }
+        mark(4);
 
-        // ---- quantise / store ----
+        // ---- quantise; rotated queries go straight out ----
 #pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) {
-            if (kind[v] == 2) {
-                // log2(e) / sqrt(128): the attention kernel works with exp2 and folds the softmax scale here
-                p.q_rot[((size_t)srcid[v] * p.H + head[v]) * HEAD_DIM + d] = acc[v] * 0.12751743074602467f;
-            } else if (kind[v] >= 0) {
-                codes[v][d] = (uint8_t)quantize_code(acc[v], p.bits);
+        for (int v = 0; v < NV; ++v) {
+            codes[v][d] = (uint8_t)quantize_code(acc[v], p.bits);
+            // log2(e) / sqrt(128): the attention kernel works with exp2 and folds the softmax scale here
+            if (kind[v] == 2) p.q_rot[((size_t)srcid[v] * p.H + head[v]) * HEAD_DIM + d] = acc[v] * 0.12751743074602467f;
+        }
+        // per-vector destination row and norm, published by thread 0 for the packing threads
+        if (d == 0) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const int pos = posv[v];
+                const bool kv = kind[v] == 0 || kind[v] == 1;
+                const bool ok = pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows);
+                long long row = -1;
+                if (kv && ok) {
+                    row = p.token_mode ? p.token_row0 + pos
+                                       : (p.row_base ? p.row_base[srcid[v]] : (long long)srcid[v] * p.max_seq_len) + pos;
+                    __half* cn = (kind[v] == 0) ? p.kn : p.vn;
+                    cn[(size_t)row * p.Hkv + head[v]] = __float2half_rn(sqrt_approx_ftz(t[v]));
+                } else if (kv) {
+                    atomicMax(p.status, ST_BAD_POSITION);
+                }
+                dest_row[v] = row;
+                dest_meta[v] = (kind[v] << 8) | head[v];
             }
         }
         __syncthreads();
-#pragma unroll
-        for (int v = 0; v < APPEND_NV; ++v) {
-            if (kind[v] == 0 || kind[v] == 1) {
-                int pos = p.positions ? p.positions[srcid[v]] : p.pos_value;
-                bool ok = pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows);
-                if (!ok) {
-                    if (d == 0) atomicMax(p.status, ST_BAD_POSITION);
-                    continue;
-                }
-                long long row;
-                if (p.token_mode) {
-                    row = p.token_row0 + pos;
-                } else {
-                    row = (p.row_base ? p.row_base[srcid[v]] : (long long)srcid[v] * p.max_seq_len) + pos;
-                }
-                uint8_t* cq = (kind[v] == 0) ? p.ck : p.cv;
-                __half* cn = (kind[v] == 0) ? p.kn : p.vn;
-                if (d < bph) {
-                    uint8_t packed;
+        // ---- pack: one 32-bit word (8 four-bit or 16 two-bit codes) per thread, NV * bph / 4 words in all ----
+        {
+            const int words_per_vec = bph / 4;
+            for (int wi = d; wi < NV * words_per_vec; wi += 128) {
+                const int v = wi / words_per_vec, wv = wi - v * words_per_vec;
+                const long long row = dest_row[v];
+                if (row >= 0) {
+                    const int meta = dest_meta[v];
+                    uint32_t word = 0;
                     if (p.bits == 2) {
-                        packed = (uint8_t)(codes[v][4 * d] | (codes[v][4 * d + 1] << 2) | (codes[v][4 * d + 2] << 4) |
-                                           (codes[v][4 * d + 3] << 6));
+                        const uint4 c4 = *reinterpret_cast<const uint4*>(&codes[v][16 * wv]);
+                        const uint32_t cw[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {  // 4 code bytes -> one packed byte
+                            const uint32_t x = cw[b];
+                            const uint32_t pk = (x & 3u) | ((x >> 6) & 0xcu) | ((x >> 12) & 0x30u) | ((x >> 18) & 0xc0u);
+                            word |= pk << (8 * b);
+                        }
                     } else {
-                        packed = (uint8_t)(codes[v][2 * d] | (codes[v][2 * d + 1] << 4));
+                        const uint2 c2 = *reinterpret_cast<const uint2*>(&codes[v][8 * wv]);
+                        const uint32_t cw[2] = {c2.x, c2.y};
+#pragma unroll
+                        for (int hbyte = 0; hbyte < 2; ++hbyte) {  // 4 code bytes -> two packed bytes
+                            const uint32_t x = cw[hbyte];
+                            const uint32_t pk = (x & 0xfu) | ((x >> 4) & 0xf0u) | ((x >> 8) & 0xf00u) | ((x >> 12) & 0xf000u);
+                            word |= pk << (16 * hbyte);
+                        }
                     }
-                    cq[(size_t)row * kvp + (size_t)head[v] * bph + d] = packed;
+                    uint8_t* cq = ((meta >> 8) == 0) ? p.ck : p.cv;
+                    *reinterpret_cast<uint32_t*>(cq + (size_t)row * kvp + (size_t)(meta & 0xff) * bph + 4 * wv) = word;
                 }
-                if (d == 0) cn[(size_t)row * p.Hkv + head[v]] = __float2half_rn(sqrt_approx_ftz(t[v]));
             }
         }
         __syncthreads();
+        mark(5);
     }
 }
 

@@ -120,6 +120,8 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.max_seq_len = max_seq_len; p.capacity_rows = max_seq_len;
     p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
     p.pos_value = pos_value;
+    static const bool stamps = getenv("TQ_APPEND_STAMPS") != nullptr;  // measurement: clock stamps in the header's spare words
+    p.stamps = stamps ? reinterpret_cast<long long*>(reinterpret_cast<char*>(workspace) + 64) : nullptr;
     return launch_append(p, s, pdl);
 }
 

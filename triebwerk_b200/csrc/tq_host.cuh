@@ -109,14 +109,38 @@ inline int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cuda
     return cuda_status(cudaLaunchKernelEx(&cfg, kernel, p));
 }
 
+constexpr size_t APPEND_SMEM = (size_t)HEAD_DIM * HEAD_DIM * sizeof(float);  // R as fp32
+
+template <int NV>
+inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, bool pdl) {
+    static std::map<int, bool> attr_set;  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(append_rotate_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)APPEND_SMEM));
+        attr_set[dev] = true;
+    }
+    return launch_kernel(append_rotate_kernel<NV>, grid, dim3(128), APPEND_SMEM, s, pdl, p);
+}
+
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
     const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
     const long long total = (long long)p.n_src * (nk + nv + nq);
-    if (total <= 0 && p.tile_start == nullptr) return TQ_OK;
-    long long groups = (total + APPEND_NV - 1) / APPEND_NV;
-    long long cap = (long long)device_props().sm_count * 3;
-    int grid = (int)(groups < 1 ? 1 : (groups < cap ? groups : cap));
-    return launch_kernel(append_rotate_kernel, dim3(grid), dim3(128), 0, s, pdl, p);
+    const bool tables = p.tile_start != nullptr && !p.token_mode;
+    if (total <= 0 && !tables) return TQ_OK;
+    if (total >= (1ll << 31)) return TQ_ERR_CAPACITY;
+    // As few vectors per CTA as still fit the whole launch into one wave (3 CTAs of 64 KB shared memory per SM):
+    // short dependent chains when the batch is small, amortised staging of R when it is large.
+    const long long slots = (long long)device_props().sm_count * 3 - 1;
+    int nvec = 2;
+    while (nvec < APPEND_MAX_NV && (total + nvec - 1) / nvec > slots) nvec *= 2;
+    long long groups = (total + nvec - 1) / nvec;
+    if (groups > slots) groups = slots;
+    if (groups < 1) groups = 1;
+    const dim3 grid((unsigned)(groups + (tables ? 1 : 0)));
+    if (nvec == 2) return launch_append_t<2>(p, grid, s, pdl);
+    if (nvec == 4) return launch_append_t<4>(p, grid, s, pdl);
+    return launch_append_t<8>(p, grid, s, pdl);
 }
 
 // Number of attention CTAs: one per SM (each holds ATTN_GROUPS workers), fewer when the cache cannot hold that
