@@ -14,12 +14,14 @@
 //     gets the same number of bytes whatever the mix of sequence lengths.
 //   * Inside a worker warp w owns KV head w and all of its query heads (2 for Qwen3-0.6B, 4 for Qwen3-8B):
 //     every cache byte is fetched from HBM once, not once per query head as in the reference.
-//   * A worker streams its tiles through a ring of shared-memory stages filled by the TMA engine with plain
-//     contiguous bulk copies (cp.async.bulk, no multicast): one 16 KB copy for the K codes of 32 token rows (all
-//     heads), one for V, and two small ones for the fp16 norms, completion on one mbarrier per stage; tiles
-//     further ahead are pulled into L2 with cp.async.bulk.prefetch.L2 so that HBM stays busy beyond what shared
-//     memory can hold.  The last warp of the worker to finish a stage (one shared-memory atomic per warp and
-//     tile) re-arms it: nobody ever waits for a slower warp.
+//   * A worker streams its tiles through a ring of shared-memory stages filled by the TMA engine (no multicast):
+//     the K codes of 32 token rows arrive as [32 rows][128 B] boxes (two heads' bytes per row, four boxes for eight
+//     heads) through a 2-D tensor map with the 128-byte swizzle, likewise V, and the fp16 norms as two small
+//     contiguous bulk copies; completion on one mbarrier per stage.  (An optional cp.async.bulk.prefetch.L2 of tiles
+//     further ahead exists, TQ_ATTN_L2_AHEAD; it is off by default because it did not pay on B200.)  The last warp of the
+//     worker to finish a stage (one shared-memory atomic per warp and tile) re-arms it: nobody waits for a slower
+//     warp.  With the swizzle, and with the eight tokens of a score block taken in the order 0,5,2,7,4,1,6,3, every
+//     16-, 8- and 4-byte read of packed codes is free of bank conflicts.
 //   * Codes are turned into fp16 centroids one BYTE at a time (2 codes for 4-bit, 4 for 2-bit) through a
 //     shared-memory table with one private column per lane (bank-conflict free); the table sits at shared
 //     address 0x10000 so that a single PRMT builds the lookup address from the packed word.
@@ -45,7 +47,7 @@ constexpr int ATTN_MAX_HEADS = 32;
 constexpr size_t ATTN_DYN_SMEM = 226 * 1024;  // requested dynamic shared memory
 constexpr int ATTN_GROUPS = 2;                // workers per CTA
 constexpr int ATTN_MAX_STAGES = 4;            // shared-memory stages per worker (as many as fit, at most this)
-constexpr int ATTN_L2_AHEAD = 4;              // tiles prefetched into L2 beyond the shared-memory ring
+constexpr int ATTN_L2_AHEAD = 0;              // tiles prefetched into L2 beyond the ring; 0 = off (measured: no gain on B200)
 constexpr int MERGE_ROW = 136;                // halves per row of the merge A-operand (padded: conflict-free)
 
 struct AttnParams {
@@ -67,6 +69,7 @@ struct AttnParams {
     int pos_value;
     int max_seq_len;
     int G, H, Hkv, q_dim;
+    int l2_ahead;              // tiles prefetched into L2 beyond the shared-memory ring
     int debug;                 // measurement switches (TQ_ATTN_DEBUG): bit 0 = skip the math, bit 1 = skip the loads
 };
 
@@ -129,7 +132,8 @@ __device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from sha
 
 template <int BITS, bool QSPLIT>
 __global__ void __launch_bounds__(512, 1)
-decode_attention_kernel(const AttnParams p) {
+decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const AttnParams p) {
     using Geo = AttnGeom<BITS>;
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
 
@@ -252,25 +256,29 @@ decode_attention_kernel(const AttnParams p) {
 
     // One elected thread issues the four copies of a tile (K codes, V codes, K norms, V norms), clipped to the
     // end of the arrays; rows past a sequence's position only ever reach masked tokens.
+    const int nbox = (int)(kvp / 128u);  // 128-byte boxes per token row
     auto issue_tile = [&](int row, int s) {
         int nrows = total_rows_i - row;
         if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
         if (nrows < 0) nrows = 0;
-        const uint32_t cb = (uint32_t)nrows * kvp, nb = (uint32_t)nrows * (uint32_t)Hkv * 2u;
+        const uint32_t nb = (uint32_t)nrows * (uint32_t)Hkv * 2u;
         const uint32_t bar = bar0 + 8u * s;
         const uint32_t dst = stage_addr(s);
-        mbar_arrive_expect_tx(bar, 2u * cb + 2u * nb);
+        // a tensor-map box always delivers its full size (rows past the end of the array arrive as zeros)
+        mbar_arrive_expect_tx(bar, 2u * code_tile + 2u * nb);
+        for (int b = 0; b < nbox; ++b) {
+            tma_load_2d(dst + (uint32_t)b * 4096u, &tmK, bar, b * 128, row);
+            tma_load_2d(dst + code_tile + (uint32_t)b * 4096u, &tmV, bar, b * 128, row);
+        }
         if (nrows > 0) {
-            bulk_load(dst, p.ck + (size_t)row * kvp, cb, bar);
-            bulk_load(dst + code_tile, p.cv + (size_t)row * kvp, cb, bar);
             bulk_load(dst + 2u * code_tile, p.kn + (size_t)row * Hkv, nb, bar);
             bulk_load(dst + 2u * code_tile + norm_tile, p.vn + (size_t)row * Hkv, nb, bar);
         }
     };
     // L2 prefetch of the tile ATTN_L2_AHEAD further on, when it belongs to the same sequence (rows are then contiguous)
     auto prefetch_ahead = [&](int row, int tile_idx, int gend) {
-        if (tile_idx + ATTN_L2_AHEAD < gend) {
-            const int prow = row + ATTN_L2_AHEAD * TILE_TOKENS;
+        if (tile_idx + p.l2_ahead < gend && tile_idx + p.l2_ahead < hi_i) {  // own slice only: others fetch theirs
+            const int prow = row + p.l2_ahead * TILE_TOKENS;
             int nrows = total_rows_i - prow;
             if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
             if (nrows > 0) {
@@ -292,7 +300,26 @@ decode_attention_kernel(const AttnParams p) {
 
     if (p.debug & 64) return;
     const uint32_t lutlane = LUT_ABS | ((uint32_t)lane << (BITS == 4 ? 2 : 3));
-    const uint32_t head_off = (uint32_t)head * Geo::BPH;
+    // ---- swizzled addressing.  A box holds [32 rows][128 B]; the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
+    // Tokens of an 8-token score block are taken in the order tau(n) = n ^ ((n & 1) << 2), which keeps both the
+    // K reads (lane <-> token tau(gl)) and the V reads (lane <-> tokens tau(2*t4), tau(2*t4+1)) conflict free.
+    const uint32_t hbyte = (uint32_t)head * Geo::BPH;          // this head's first byte within the token row
+    const uint32_t box_off = (hbyte >> 7) * 4096u;              // which box
+    const uint32_t hchunk = (hbyte & 127u) >> 4;                // first 16-byte chunk of the head inside the box row
+    const uint32_t tauK = (uint32_t)gl ^ (((uint32_t)gl & 1u) << 2);
+    const uint32_t tokA = 2u * (uint32_t)t4, tokB = (2u * (uint32_t)t4 + 1u) ^ 4u;   // tau(2*t4), tau(2*t4+1)
+    uint32_t k_off, vA_off, vB_off;
+    if (BITS == 4) {
+        k_off = box_off + tauK * 128u + (((hchunk + (uint32_t)t4) ^ tauK) << 4);
+        const uint32_t vch = hchunk + ((uint32_t)gl >> 1), vsub = ((uint32_t)gl & 1u) * 8u;
+        vA_off = box_off + tokA * 128u + ((vch ^ tokA) << 4) + vsub;
+        vB_off = box_off + tokB * 128u + ((vch ^ tokB) << 4) + vsub;
+    } else {
+        k_off = box_off + tauK * 128u + (((hchunk + ((uint32_t)t4 >> 1)) ^ tauK) << 4) + ((uint32_t)t4 & 1u) * 8u;
+        const uint32_t vch = hchunk + ((uint32_t)gl >> 2), vsub = ((uint32_t)gl & 3u) * 4u;
+        vA_off = box_off + tokA * 128u + ((vch ^ tokA) << 4) + vsub;
+        vB_off = box_off + tokB * 128u + ((vch ^ tokB) << 4) + vsub;
+    }
 
     long long tile = lo;
     while (tile < hi) {
@@ -355,7 +382,7 @@ decode_attention_kernel(const AttnParams p) {
                 token = ok ^ 1u;
             }
             if (!dead && !(p.debug & 1)) {
-                const uint32_t kt = stage_addr(s) + token + head_off;  // this head's bytes of token row 0
+                const uint32_t kt = stage_addr(s) + token;
                 const uint32_t vt = kt + code_tile;
                 const uint32_t kns = stage_addr(s) + token + 2u * code_tile + (uint32_t)head * 2u;
                 const uint32_t vns = kns + norm_tile;
@@ -367,7 +394,7 @@ decode_attention_kernel(const AttnParams p) {
                 for (int blk = 0; blk < 4; ++blk) {
                     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                     if (BITS == 4) {
-                        const uint4 kw = ldsp128(kt + (uint32_t)(8 * blk + gl) * kvp + (uint32_t)t4 * 16u);
+                        const uint4 kw = ldsp128(kt + (uint32_t)blk * 1024u + k_off);
                         const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -378,7 +405,7 @@ decode_attention_kernel(const AttnParams p) {
                             else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, b0, b1);
                         }
                     } else {
-                        const uint2 kw = ldsp64(kt + (uint32_t)(8 * blk + gl) * kvp + (uint32_t)t4 * 8u);
+                        const uint2 kw = ldsp64(kt + (uint32_t)blk * 1024u + k_off);
                         const uint32_t w[2] = {kw.x, kw.y};
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -388,8 +415,8 @@ decode_attention_kernel(const AttnParams p) {
                             else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, bb.x, bb.y);
                         }
                     }
-                    const float k0 = ldsp_h2f(kns + (uint32_t)(8 * blk + 2 * t4) * nstride);
-                    const float k1 = ldsp_h2f(kns + (uint32_t)(8 * blk + 2 * t4 + 1) * nstride);
+                    const float k0 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokA) * nstride);
+                    const float k1 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokB) * nstride);
                     sv[2 * blk] = (QSPLIT ? c[0] + c[2] : c[0]) * k0;
                     sv[2 * blk + 1] = (QSPLIT ? c[1] + c[3] : c[1]) * k1;
                 }
@@ -398,7 +425,7 @@ decode_attention_kernel(const AttnParams p) {
                 if (!full) {  // rows past the position may hold anything (even NaN norms): force them out
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
+                        const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
                         if (tok >= L) sv[i] = -1e30f;
                     }
                 }
@@ -425,7 +452,7 @@ decode_attention_kernel(const AttnParams p) {
                 if (!full) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const int tok = t0 + 8 * (i >> 1) + 2 * t4 + (i & 1);
+                        const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
                         if (tok >= L) pv[i] = 0.0f;
                     }
                 }
@@ -434,23 +461,25 @@ decode_attention_kernel(const AttnParams p) {
                 // ---------------- values: 2 blocks of 16 tokens ----------------
 #pragma unroll
                 for (int gam = 0; gam < 2; ++gam) {
-                    const uint32_t rowA = (uint32_t)(16 * gam + 2 * t4);
-                    float v0 = ldsp_h2f(vns + (rowA + 0) * nstride), v1 = ldsp_h2f(vns + (rowA + 1) * nstride);
-                    float v8 = ldsp_h2f(vns + (rowA + 8) * nstride), v9 = ldsp_h2f(vns + (rowA + 9) * nstride);
+                    // token rows of this lane: A, B from score block 2*gam, C, D from block 2*gam+1
+                    const uint32_t rA = (uint32_t)(16 * gam) + tokA, rB = (uint32_t)(16 * gam) + tokB;
+                    float v0 = ldsp_h2f(vns + rA * nstride), v1 = ldsp_h2f(vns + rB * nstride);
+                    float v8 = ldsp_h2f(vns + (rA + 8u) * nstride), v9 = ldsp_h2f(vns + (rB + 8u) * nstride);
                     if (!full) {  // 0 * NaN would poison the accumulators
-                        if (t0 + (int)rowA + 0 >= L) v0 = 0.0f;
-                        if (t0 + (int)rowA + 1 >= L) v1 = 0.0f;
-                        if (t0 + (int)rowA + 8 >= L) v8 = 0.0f;
-                        if (t0 + (int)rowA + 9 >= L) v9 = 0.0f;
+                        if (t0 + (int)rA >= L) v0 = 0.0f;
+                        if (t0 + (int)rB >= L) v1 = 0.0f;
+                        if (t0 + (int)rA + 8 >= L) v8 = 0.0f;
+                        if (t0 + (int)rB + 8 >= L) v9 = 0.0f;
                     }
                     const uint32_t pb0 = pack_half2(pv[4 * gam] * v0, pv[4 * gam + 1] * v1);
                     const uint32_t pb1 = pack_half2(pv[4 * gam + 2] * v8, pv[4 * gam + 3] * v9);
                     if (BITS == 4) {
-                        // lane reads bytes 8*gl .. 8*gl+7 (coordinates 16*gl .. 16*gl+15) of tokens rowA, +1, +8, +9
-                        const uint2 xa = ldsp64(vt + (rowA + 0) * kvp + (uint32_t)gl * 8u);
-                        const uint2 xb = ldsp64(vt + (rowA + 1) * kvp + (uint32_t)gl * 8u);
-                        const uint2 xc = ldsp64(vt + (rowA + 8) * kvp + (uint32_t)gl * 8u);
-                        const uint2 xd = ldsp64(vt + (rowA + 9) * kvp + (uint32_t)gl * 8u);
+                        // lane reads bytes 8*gl .. 8*gl+7 (coordinates 16*gl .. 16*gl+15) of token rows A, B, C = A+8, D = B+8
+                        const uint32_t vg = vt + (uint32_t)gam * 2048u;
+                        const uint2 xa = ldsp64(vg + vA_off);
+                        const uint2 xb = ldsp64(vg + vB_off);
+                        const uint2 xc = ldsp64(vg + vA_off + 1024u);
+                        const uint2 xd = ldsp64(vg + vB_off + 1024u);
                         // Interleave the nibbles of two tokens: byte b of `ev` = (code of token A, code of token B) for the
                         // EVEN coordinate of byte b, `od` for the odd one.  The table then returns the (A, B) pair directly.
                         const uint32_t wa[2] = {xa.x, xa.y}, wb[2] = {xb.x, xb.y}, wc[2] = {xc.x, xc.y}, wd[2] = {xd.x, xd.y};
@@ -471,10 +500,11 @@ decode_attention_kernel(const AttnParams p) {
                             }
                         }
                     } else {
-                        const uint32_t xa = ldsp32(vt + (rowA + 0) * kvp + (uint32_t)gl * 4u);
-                        const uint32_t xb = ldsp32(vt + (rowA + 1) * kvp + (uint32_t)gl * 4u);
-                        const uint32_t xc = ldsp32(vt + (rowA + 8) * kvp + (uint32_t)gl * 4u);
-                        const uint32_t xd = ldsp32(vt + (rowA + 9) * kvp + (uint32_t)gl * 4u);
+                        const uint32_t vg = vt + (uint32_t)gam * 2048u;
+                        const uint32_t xa = ldsp32(vg + vA_off);
+                        const uint32_t xb = ldsp32(vg + vB_off);
+                        const uint32_t xc = ldsp32(vg + vA_off + 1024u);
+                        const uint32_t xd = ldsp32(vg + vB_off + 1024u);
 #pragma unroll
                         for (int bb = 0; bb < 4; ++bb) {
                             const uint32_t sel = 0x7604u | ((uint32_t)bb << 4);

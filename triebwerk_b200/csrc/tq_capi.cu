@@ -135,7 +135,8 @@ int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms,
                        workspace_bytes, true, cs(s));
 }
 
-static int attention_impl(void* out, const void* ck_q, const void* cv_q, const void* k_norms, const void* v_norms,
+static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* ck_q, const void* cv_q,
+                          const void* k_norms, const void* v_norms,
                           const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
                           long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
                           int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false) {
@@ -157,7 +158,9 @@ static int attention_impl(void* out, const void* ck_q, const void* cv_q, const v
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim;
     static const int debug_mode = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
     p.debug = debug_mode;
-    return launch_attention(bits, p, attention_ctas(G, max_seq_len), s, pdl);
+    static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
+    p.l2_ahead = l2_ahead > 0 ? l2_ahead : (1 << 28);  // 0 switches the prefetch off
+    return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl);
 }
 
 int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms, const void* v_norms,
@@ -175,7 +178,13 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
     transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation);
     r = cuda_status(cudaGetLastError());
     if (r != TQ_OK) return r;
-    return attention_impl(out, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, pos_value, row_base, total_rows,
+    const int kvp = kv_dim / (bits == 2 ? 4 : 2);
+    CUtensorMap tmK, tmV;
+    r = cached_code_map(&tmK, ck_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
+    r = cached_code_map(&tmV, cv_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
+    return attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, pos_value, row_base, total_rows,
                           max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
 }
 
@@ -532,6 +541,15 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
         int ur = engine_upload_rotation(e, nullptr);
         if (ur != TQ_OK) return ur;
     }
+    if (e->kv_bits != 0) {
+        const int kvp = e->kv_dim() / e->vpb();
+        for (auto& L : e->layers) {
+            r = make_code_map(&L.tmK, L.k, rows, kvp);
+            if (r != TQ_OK) return r;
+            r = make_code_map(&L.tmV, L.v, rows, kvp);
+            if (r != TQ_OK) return r;
+        }
+    }
     return TQ_OK;
 }
 
@@ -637,7 +655,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
                         e->ws_bytes, true, cs(s), use_pdl());
     if (r != TQ_OK) return r;
-    return attention_impl(out, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
+    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
                           e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl());
 }
 
@@ -646,7 +664,7 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
     const tq_engine::Layer& L = e->layers[layer];
-    return attention_impl(out, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
+    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
                           e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace,
                           e->ws_bytes, cs(s), use_pdl());
 }

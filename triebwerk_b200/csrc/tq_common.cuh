@@ -2,6 +2,7 @@
 // mma.sync, prmt), the workspace layout and the status word.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -180,6 +181,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
     }
     return false;
+}
+
+// 2-D tiled TMA load global -> shared of this CTA (no multicast), completion on an mbarrier.
+// x = innermost coordinate in elements (bytes here; must be a multiple of 16), y = row.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
 }
 
 }  // namespace tq

@@ -11,6 +11,8 @@
 #include <tuple>
 #include <vector>
 
+#include <cudaTypedefs.h>
+
 #include "../../include/triebwerk_b200.h"
 #include "tq_append.cuh"
 #include "tq_attention.cuh"
@@ -43,6 +45,35 @@ inline DeviceProps& device_props() {
         if (d.sm_count <= 0) d.sm_count = 1;
     }
     return d;
+}
+
+// ---- TMA descriptors ----------------------------------------------------------------------------------------------
+inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+// Code array viewed as uint8 [rows][kvp]; box = 128 bytes x TILE_TOKENS rows, 128-byte swizzle in shared memory.
+inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int kvp) {
+    auto fn = encode_fn();
+    if (!fn) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31) || kvp % 128 != 0) return TQ_ERR_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)kvp, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)kvp};
+    cuuint32_t box[2] = {128u, (cuuint32_t)TILE_TOKENS};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
 }
 
 // ---- workspace ------------------------------------------------------------------------------------------------------
@@ -155,7 +186,8 @@ inline int attention_ctas(int G, int max_seq_len) {
 }
 
 template <int BITS, bool QSPLIT>
-inline int launch_attention_t(const AttnParams& p, int ctas, cudaStream_t s, bool pdl) {
+inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas, cudaStream_t s,
+                              bool pdl) {
     static std::map<int, bool> attr_set;  // per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -164,15 +196,26 @@ inline int launch_attention_t(const AttnParams& p, int ctas, cudaStream_t s, boo
                                      (int)ATTN_DYN_SMEM));
         attr_set[dev] = true;
     }
-    return launch_kernel(decode_attention_kernel<BITS, QSPLIT>, dim3(ctas), dim3(ATTN_GROUPS * 32 * p.Hkv), ATTN_DYN_SMEM, s,
-                         pdl, p);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(ATTN_GROUPS * 32 * p.Hkv);
+    cfg.dynamicSmemBytes = ATTN_DYN_SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT>, tmK, tmV, p));
 }
 
-inline int launch_attention(int bits, const AttnParams& p, int ctas, cudaStream_t s, bool pdl = false) {
+inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas,
+                            cudaStream_t s, bool pdl = false) {
     // TQ_ATTN_QSPLIT=0 selects the variant that feeds the query to the tensor cores as plain fp16 (no high/low split)
     static const bool qsplit = !(getenv("TQ_ATTN_QSPLIT") && atoi(getenv("TQ_ATTN_QSPLIT")) == 0);
-    if (bits == 4) return qsplit ? launch_attention_t<4, true>(p, ctas, s, pdl) : launch_attention_t<4, false>(p, ctas, s, pdl);
-    return qsplit ? launch_attention_t<2, true>(p, ctas, s, pdl) : launch_attention_t<2, false>(p, ctas, s, pdl);
+    if (bits == 4)
+        return qsplit ? launch_attention_t<4, true>(tmK, tmV, p, ctas, s, pdl) : launch_attention_t<4, false>(tmK, tmV, p, ctas, s, pdl);
+    return qsplit ? launch_attention_t<2, true>(tmK, tmV, p, ctas, s, pdl) : launch_attention_t<2, false>(tmK, tmV, p, ctas, s, pdl);
 }
 
 __global__ void transpose_rotation_kernel(__half* dst, const __half* src) {
@@ -209,6 +252,7 @@ __global__ void iota_rows_kernel(int* pos, long long* rows, int n, long long row
 struct CompatState {
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    std::map<std::tuple<const void*, long long, int>, CUtensorMap> maps;  // descriptors by (base, rows, row bytes)
 };
 
 inline CompatState& compat_state() {
@@ -237,6 +281,21 @@ inline int compat_workspace(size_t need, void** out, cudaStream_t s) {
         c.ws_bytes = need;
     }
     *out = c.ws;
+    return TQ_OK;
+}
+
+inline int cached_code_map(CUtensorMap* out, const void* base, long long rows, int kvp) {
+    CompatState& c = compat_state();
+    auto key = std::make_tuple(base, rows, kvp);
+    auto it = c.maps.find(key);
+    if (it == c.maps.end()) {
+        CUtensorMap m;
+        int r = make_code_map(&m, base, rows, kvp);
+        if (r != TQ_OK) return r;
+        if (c.maps.size() > 4096) c.maps.clear();
+        it = c.maps.emplace(key, m).first;
+    }
+    *out = it->second;
     return TQ_OK;
 }
 
@@ -270,6 +329,7 @@ struct tq_engine {
         void* v = nullptr;
         void* kn = nullptr;
         void* vn = nullptr;
+        CUtensorMap tmK{}, tmV{};  // packed modes: descriptors of the code arrays
     };
     std::vector<Layer> layers;
 
