@@ -143,6 +143,24 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
                         int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
                         size_t workspace_bytes, tq_stream_t s);
 
+/* No counterpart in the reference.  Decode attention over the packed cache for callers that cannot allocate device
+ * memory once they are running: processes whose memory pool already owns the whole GPU, serving loops that forbid
+ * cudaMalloc because it stalls the device, code that is already inside a CUDA-graph capture when it gets here.  Same
+ * result as launch_turbo_gqa_attention_batch (it takes the un-rotated queries q [G][q_dim]), but the kernel's scratch
+ * (rotated queries, tile table, tickets, split-K partials, transposed rotation) lives in a fixed 20 MiB device array
+ * inside the library image, present on every GPU that loads the library until the process exits.  The call makes no
+ * cudaMalloc / cudaFree and uses no allocator of any framework.
+ *   Limit: tq_workspace_bytes(G, num_heads) must not exceed 20 MiB -- that covers 64 sequences x 32 query heads or
+ *   256 x 16; larger requests return TQ_ERR_CAPACITY and launch nothing.
+ *   The first call on a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream
+ *   capture.  All calls share the one array and it keeps the previous call's contents (the call itself clears what
+ *   must start at zero): two calls that overlap on the GPU -- different streams, or graphs replayed concurrently --
+ *   race on it and must be serialised by the caller. */
+int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
+                               const void* k_norms, const void* v_norms, const void* rotation,
+                               const int* positions, long long total_rows, int max_seq_len, int G, int num_heads,
+                               int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, tq_stream_t s);
+
 /* kv_bits = 0 twins with the same slot addressing (replace launch_kv_cache_write_batch and
  * launch_gqa_attention_batch, engine/kernels.cu:1351-1357). */
 int tq_fp16_append_decode(void* ck, void* cv, const void* k_buf, const void* v_buf, const int* positions,

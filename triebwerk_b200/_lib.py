@@ -19,7 +19,7 @@ SYMBOLS = [
     "launch_turbo_gqa_attention", "launch_turbo_gqa_prefill_attention", "launch_kv_cache_write_batch",
     "launch_gqa_attention_batch", "launch_gqa_attention",
     "tq_rotation_generate", "tq_workspace_bytes", "tq_append_decode", "tq_decode_attention",
-    "tq_fp16_append_decode", "tq_fp16_decode_attention", "tq_workspace_status",
+    "tq_fp16_append_decode", "tq_fp16_decode_attention", "tq_workspace_status", "tq_decode_attention_static",
     "tq_engine_create", "tq_engine_destroy", "tq_engine_kv_bits", "tq_engine_arena_bytes", "tq_engine_set_arena",
     "tq_engine_alloc_batch", "tq_engine_reset", "tq_engine_sleep", "tq_engine_wake", "tq_engine_positions",
     "tq_engine_set_positions", "tq_engine_advance", "tq_engine_layer_ptrs", "tq_engine_row_base",
@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
     sig("tq_fp16_append_decode", i, [vp, vp, vp, vp, ip, ip, i, i, i, vp])
     sig("tq_fp16_decode_attention", i, [vp, vp, vp, vp, ip, i, ip, ll, i, i, i, i, i, i, i, vp, sz, vp])
     sig("tq_workspace_status", i, [vp, vp])
+    sig("tq_decode_attention_static", i, [vp, vp, vp, vp, vp, vp, vp, ip, ll, i, i, i, i, i, i, i, i, vp])
     sig("tq_engine_create", i, [C.POINTER(ModelShape), i, i, C.POINTER(vp)])
     sig("tq_engine_destroy", None, [vp])
     sig("tq_engine_kv_bits", i, [vp])

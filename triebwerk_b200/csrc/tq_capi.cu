@@ -188,6 +188,67 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
                           max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
 }
 
+// ---- allocation-free decode attention -----------------------------------------------------------------------------------
+// Some embedders may not allocate device memory at all once they are running: every byte of the GPU was handed to
+// their own pool at start-up (a raw cudaMalloc would fail or fight that pool), they sit inside a serving loop whose
+// latency budget rules out cudaMalloc (it synchronises the whole device), or they are already recording a CUDA graph
+// when they first reach this library.  For them the scratch that the attention kernel needs lives in the library
+// image itself: a fixed device array that every GPU loading this library carries until the process exits.
+constexpr size_t TQ_STATIC_SCRATCH_BYTES = (size_t)20 << 20;  // 20 MiB: 64 sequences x 32 query heads fit, see the header
+static __device__ __align__(256) unsigned char g_static_scratch[TQ_STATIC_SCRATCH_BYTES];
+
+// In host code the name g_static_scratch is only a stand-in for the device array, never a device address.  Its address
+// is looked up once per device, with that device current, and handed to the kernels like any other workspace pointer.
+static int static_scratch_ptr(void** out) {
+    static std::mutex mu;
+    static std::map<int, void*> by_device;
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = by_device.find(dev);
+    if (it == by_device.end()) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!ptr) return TQ_ERR_STATE;
+        it = by_device.emplace(dev, ptr).first;
+    }
+    *out = it->second;
+    return TQ_OK;
+}
+
+int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms,
+                               const void* v_norms, const void* rotation, const int* positions, long long total_rows,
+                               int max_seq_len, int G, int num_heads, int num_kv_heads, int head_dim, int q_dim,
+                               int kv_dim, int bits, tq_stream_t s) {
+    int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    if (r != TQ_OK) return r;
+    if (!out || !q || !ck_q || !cv_q || !k_norms || !v_norms || !rotation || !positions) return TQ_ERR_ARG;
+    const size_t need = carve_full(nullptr, G, num_heads).bytes;
+    if (need > TQ_STATIC_SCRATCH_BYTES) return TQ_ERR_CAPACITY;  // batch x heads too large for the built-in scratch
+    void* ws = nullptr;
+    r = static_scratch_ptr(&ws);  // first call on a device: symbol lookup (do it before capturing a graph)
+    if (r != TQ_OK) return r;
+    // The array keeps whatever the previous call left.  What has to start from zero: the status word (header) here,
+    // the per-sequence tickets in the rotate kernel below; everything else is written before it is read.
+    TQ_CUDA(cudaMemsetAsync(ws, 0, 256, cs(s)));
+    FullWorkspace fw = carve_full(ws, G, num_heads);
+    transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation);
+    r = cuda_status(cudaGetLastError());
+    if (r != TQ_OK) return r;
+    r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, positions, 0, nullptr, 0, 0,
+                    max_seq_len, G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
+    if (r != TQ_OK) return r;
+    const int kvp = kv_dim / (bits == 2 ? 4 : 2);
+    CUtensorMap tmK, tmV;  // encoded on the host stack every call: no cache, nothing allocated
+    r = make_code_map(&tmK, ck_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
+    r = make_code_map(&tmV, cv_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
+    return attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, -1, nullptr, total_rows,
+                          max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, ws, need, cs(s));
+}
+
 // ---- fp16 twin ---------------------------------------------------------------------------------------------------------
 int tq_fp16_append_decode(void* ck, void* cv, const void* k_buf, const void* v_buf, const int* positions,
                           const long long* row_base, int max_seq_len, int G, int kv_dim, tq_stream_t s) {
