@@ -37,6 +37,8 @@
 //     anybody: the ticket is a single atomicAdd.
 #pragma once
 
+#include <type_traits>
+
 #include "tq_common.cuh"
 
 namespace tq {
@@ -130,8 +132,8 @@ __device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from sha
     return __half2float(__ushort_as_half(h));
 }
 
-template <int BITS, bool QSPLIT>
-__global__ void __launch_bounds__(512, 1)
+template <int BITS, bool QSPLIT, int HKV>
+__global__ void __launch_bounds__(ATTN_GROUPS * 32 * HKV, 1)
 decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const AttnParams p) {
     using Geo = AttnGeom<BITS>;
@@ -140,18 +142,18 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int Hkv = p.Hkv;
+    constexpr int Hkv = HKV;  // compile time: row pitches, tile sizes and norm strides fold into immediates
     const int group = warp / Hkv;        // worker within the CTA
     const int head = warp - group * Hkv; // KV head of this warp
     const int gl = lane >> 2;            // mma "group id": token (K side), coordinate row (V side), head (S layout)
     const int t4 = lane & 3;             // mma "thread in group"
     const int grp = p.H / Hkv;           // query heads per KV head (<= 8)
-    const int gthreads = 32 * Hkv;       // threads of a worker
+    constexpr int gthreads = 32 * Hkv;   // threads of a worker
     const int gtid = tid - group * gthreads;
-    const uint32_t kvp = (uint32_t)Hkv * Geo::BPH;               // code bytes per token row (all heads)
-    const uint32_t code_tile = TILE_TOKENS * kvp;                // one K (or V) tile
-    const uint32_t norm_tile = TILE_TOKENS * (uint32_t)Hkv * 2u; // one norm tile
-    const uint32_t stage_bytes = 2u * code_tile + 2u * norm_tile;
+    constexpr uint32_t kvp = (uint32_t)Hkv * Geo::BPH;               // code bytes per token row (all heads)
+    constexpr uint32_t code_tile = TILE_TOKENS * kvp;                // one K (or V) tile
+    constexpr uint32_t norm_tile = TILE_TOKENS * (uint32_t)Hkv * 2u; // one norm tile
+    constexpr uint32_t stage_bytes = 2u * code_tile + 2u * norm_tile;
 
     // ---- shared memory map (absolute shared addresses) ----
     const uint32_t dyn_base = smem_u32(dyn_smem);
@@ -256,7 +258,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
     // One elected thread issues the four copies of a tile (K codes, V codes, K norms, V norms), clipped to the
     // end of the arrays; rows past a sequence's position only ever reach masked tokens.
-    const int nbox = (int)(kvp / 128u);  // 128-byte boxes per token row
+    constexpr int nbox = (int)(kvp / 128u);  // 128-byte boxes per token row
     auto issue_tile = [&](int row, int s) {
         int nrows = total_rows_i - row;
         if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
@@ -373,7 +375,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             if (!dead && loads_on) {
                 const uint32_t bar = bar0 + 8u * s, parity = (uint32_t)(consumed >> s_log) & 1u;
                 uint32_t ok = 0;
-                for (uint32_t it = 0; it < (1u << 20) && !ok; ++it) ok = mbar_try_wait(bar, parity);
+                for (uint32_t it = 0; it < (1u << 14) && !ok; ++it) ok = mbar_try_wait_hint(bar, parity, 20000u);
                 if (!ok) {
                     dead = true;
                     if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
@@ -381,12 +383,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 dead = __any_sync(0xffffffffu, dead);
                 token = ok ^ 1u;
             }
-            if (!dead && !(p.debug & 1)) {
+            // The tile body exists twice: for tiles in which every token is attended to (all but the last tile of a
+            // sequence) without any masking code, and for the last, partly filled tile with it.
+            auto tile_body = [&](auto full_tag) {
+                constexpr bool FULLT = decltype(full_tag)::value;
                 const uint32_t kt = stage_addr(s) + token;
                 const uint32_t vt = kt + code_tile;
                 const uint32_t kns = stage_addr(s) + token + 2u * code_tile + (uint32_t)head * 2u;
                 const uint32_t vns = kns + norm_tile;
-                const uint32_t nstride = (uint32_t)Hkv * 2u;
+                constexpr uint32_t nstride = (uint32_t)Hkv * 2u;
 
                 // ---------------- scores: 4 blocks of 8 tokens ----------------
                 float sv[8];
@@ -422,7 +427,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
 
                 // ---------------- online softmax (row = head gl; rows >= grp carry zeros and are never read) ----
-                if (!full) {  // rows past the position may hold anything (even NaN norms): force them out
+                if constexpr (!FULLT) {  // rows past the position may hold anything (even NaN norms): force them out
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
@@ -449,7 +454,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 float pv[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) pv[i] = ex2_approx(sv[i] - m_run);
-                if (!full) {
+                if constexpr (!FULLT) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
@@ -465,7 +470,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     const uint32_t rA = (uint32_t)(16 * gam) + tokA, rB = (uint32_t)(16 * gam) + tokB;
                     float v0 = ldsp_h2f(vns + rA * nstride), v1 = ldsp_h2f(vns + rB * nstride);
                     float v8 = ldsp_h2f(vns + (rA + 8u) * nstride), v9 = ldsp_h2f(vns + (rB + 8u) * nstride);
-                    if (!full) {  // 0 * NaN would poison the accumulators
+                    if constexpr (!FULLT) {  // 0 * NaN would poison the accumulators
                         if (t0 + (int)rA >= L) v0 = 0.0f;
                         if (t0 + (int)rB >= L) v1 = 0.0f;
                         if (t0 + (int)rA + 8 >= L) v8 = 0.0f;
@@ -519,6 +524,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                         }
                     }
                 }
+            };
+            if (!dead && !(p.debug & 1)) {
+                if (full) tile_body(std::true_type{});
+                else tile_body(std::false_type{});
             }
             // Everything this warp read from the stage has been consumed by the (ordered) mma instructions above.
             // The last warp of the worker to get here re-arms the stage with the tile S ahead; nobody waits.

@@ -174,6 +174,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep inside the instruction until the phase
+// completes or the time is up, instead of burning issue slots on polls.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok;
+}
 // Bounded wait: gives up after `limit` polls (each poll may itself block for a hardware-defined short
 // time).  Returns false on give-up; the caller records ST_TMA_WAIT_TIMEOUT and stops using the pipeline.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 20)) {

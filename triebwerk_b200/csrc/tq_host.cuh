@@ -185,20 +185,20 @@ inline int attention_ctas(int G, int max_seq_len) {
     return (int)(w < 1 ? 1 : w);
 }
 
-template <int BITS, bool QSPLIT>
+template <int BITS, bool QSPLIT, int HKV>
 inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas, cudaStream_t s,
                               bool pdl) {
     static std::map<int, bool> attr_set;  // per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)ATTN_DYN_SMEM));
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(ATTN_GROUPS * 32 * p.Hkv);
+    cfg.blockDim = dim3(ATTN_GROUPS * 32 * HKV);
     cfg.dynamicSmemBytes = ATTN_DYN_SMEM;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -206,16 +206,25 @@ inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT>, tmK, tmV, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT, HKV>, tmK, tmV, p));
 }
 
 inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas,
                             cudaStream_t s, bool pdl = false) {
     // TQ_ATTN_QSPLIT=0 selects the variant that feeds the query to the tensor cores as plain fp16 (no high/low split)
     static const bool qsplit = !(getenv("TQ_ATTN_QSPLIT") && atoi(getenv("TQ_ATTN_QSPLIT")) == 0);
-    if (bits == 4)
-        return qsplit ? launch_attention_t<4, true>(tmK, tmV, p, ctas, s, pdl) : launch_attention_t<4, false>(tmK, tmV, p, ctas, s, pdl);
-    return qsplit ? launch_attention_t<2, true>(tmK, tmV, p, ctas, s, pdl) : launch_attention_t<2, false>(tmK, tmV, p, ctas, s, pdl);
+    if (p.Hkv == 8) {
+        if (bits == 4)
+            return qsplit ? launch_attention_t<4, true, 8>(tmK, tmV, p, ctas, s, pdl)
+                          : launch_attention_t<4, false, 8>(tmK, tmV, p, ctas, s, pdl);
+        return qsplit ? launch_attention_t<2, true, 8>(tmK, tmV, p, ctas, s, pdl)
+                      : launch_attention_t<2, false, 8>(tmK, tmV, p, ctas, s, pdl);
+    }
+    if (p.Hkv == 4) {
+        if (bits == 4) return launch_attention_t<4, true, 4>(tmK, tmV, p, ctas, s, pdl);
+        return launch_attention_t<2, true, 4>(tmK, tmV, p, ctas, s, pdl);
+    }
+    return TQ_ERR_UNSUPPORTED;
 }
 
 __global__ void transpose_rotation_kernel(__half* dst, const __half* src) {
