@@ -258,7 +258,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
     // One elected thread issues the four copies of a tile (K codes, V codes, K norms, V norms), clipped to the
     // end of the arrays; rows past a sequence's position only ever reach masked tokens.
-    constexpr int nbox = (int)(kvp / 128u);  // 128-byte boxes per token row
     auto issue_tile = [&](int row, int s) {
         int nrows = total_rows_i - row;
         if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
@@ -268,10 +267,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const uint32_t dst = stage_addr(s);
         // a tensor-map box always delivers its full size (rows past the end of the array arrive as zeros)
         mbar_arrive_expect_tx(bar, 2u * code_tile + 2u * nb);
-        for (int b = 0; b < nbox; ++b) {
-            tma_load_2d(dst + (uint32_t)b * 4096u, &tmK, bar, b * 128, row);
-            tma_load_2d(dst + code_tile + (uint32_t)b * 4096u, &tmV, bar, b * 128, row);
-        }
+        tma_load_3d(dst, &tmK, bar, 0, row, 0);
+        tma_load_3d(dst + code_tile, &tmV, bar, 0, row, 0);
         if (nrows > 0) {
             bulk_load(dst + 2u * code_tile, p.kn + (size_t)row * Hkv, nb, bar);
             bulk_load(dst + 2u * code_tile + norm_tile, p.vn + (size_t)row * Hkv, nb, bar);

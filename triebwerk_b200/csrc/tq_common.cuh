@@ -205,4 +205,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// 3-D form of the same load; the coordinates are (x, y, z) from the innermost dimension outwards.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 }  // namespace tq

@@ -66,11 +66,14 @@ inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int k
     auto fn = encode_fn();
     if (!fn) return TQ_ERR_UNSUPPORTED;
     if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31) || kvp % 128 != 0) return TQ_ERR_ARG;
-    cuuint64_t dims[2] = {(cuuint64_t)kvp, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kvp};
-    cuuint32_t box[2] = {128u, (cuuint32_t)TILE_TOKENS};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+    // Three dimensions: 128 bytes of a row, the rows, and the 128-byte column blocks of a row.  One box covers a whole
+    // tile (32 rows x all column blocks) and lands in shared memory as [column block][row][128 B]: one copy
+    // instruction per tile and array, and the 128-byte swizzle still goes by the row number.
+    cuuint64_t dims[3] = {128u, (cuuint64_t)rows, (cuuint64_t)(kvp / 128)};
+    cuuint64_t strides[2] = {(cuuint64_t)kvp, 128u};
+    cuuint32_t box[3] = {128u, (cuuint32_t)TILE_TOKENS, (cuuint32_t)(kvp / 128)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
