@@ -585,7 +585,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 const uint32_t flag = (old == parts - 1) ? 1u : 0u;
                 if (flag) {
                     p.tickets[g] = 0;  // everybody has arrived: leave the ticket ready for the next launch
-                    __threadfence();
                 }
                 asm volatile("st.shared.u32 [%0], %1;" ::"r"(ctrl_s), "r"(flag) : "memory");
             }
@@ -595,29 +594,37 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         if (is_last) {
             const int H = p.H;
             for (int hb = 0; hb < H; hb += 16) {
-                // ---- phase A: heads hb .. hb+15, one warp per head in turn: combine the parts, normalise,
-                //      split into fp16 high + low, store as the A operand [16][MERGE_ROW]
-                for (int hh = head; hh < 16; hh += Hkv) {
-                    const int hq = hb + hh;
-                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (hq < H) {
-                        const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
-                        const size_t pstride = (size_t)H * PART_STRIDE;
-                        if (parts <= 8) {
-                            // common case: all loads go out together (one round trip), weights afterwards
-                            float4 v[8];
-                            float2 ml = make_float2(-1e30f, 0.0f);
-                            if (lane < parts) ml = __ldcg(reinterpret_cast<const float2*>(base + lane * pstride + HEAD_DIM));
+                // ---- phase A: heads hb .. hb+15, two heads per warp at a time with all their loads in flight
+                //      together: combine the parts, normalise, split into fp16 high + low, store as the A operand
+                //      [16][MERGE_ROW]
+                for (int hh0 = head; hh0 < 16; hh0 += 2 * Hkv) {
+                    float4 a[2];
+                    a[0] = a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const size_t pstride = (size_t)H * PART_STRIDE;
+                    if (parts <= 8) {
+                        // common case: one round trip for everything, weights afterwards
+                        float4 v[2][8];
+                        float2 ml[2];
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const int hq = hb + hh0 + r * Hkv;
+                            const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
+                            const bool on = hq < H && hh0 + r * Hkv < 16;
+                            ml[r] = make_float2(-1e30f, 0.0f);
+                            if (on && lane < parts) ml[r] = __ldcg(reinterpret_cast<const float2*>(base + lane * pstride + HEAD_DIM));
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
-                                v[j] = j < parts ? __ldcg(reinterpret_cast<const float4*>(base + j * pstride) + lane)
-                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-                            float M = ml.x;
+                                v[r][j] = (on && j < parts) ? __ldcg(reinterpret_cast<const float4*>(base + j * pstride) + lane)
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            float M = ml[r].x;
 #pragma unroll
                             for (int o = 4; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
                             M = __shfl_sync(0xffffffffu, M, 0);
-                            const float e = lane < parts ? ex2_approx(ml.x - M) : 0.0f;
-                            float Z = ml.y * e;
+                            const float e = lane < parts ? ex2_approx(ml[r].x - M) : 0.0f;
+                            float Z = ml[r].y * e;
 #pragma unroll
                             for (int o = 4; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
                             Z = __shfl_sync(0xffffffffu, Z, 0);
@@ -625,10 +632,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const float wj = __shfl_sync(0xffffffffu, sc, j);
-                                a.x = fmaf(wj, v[j].x, a.x); a.y = fmaf(wj, v[j].y, a.y);
-                                a.z = fmaf(wj, v[j].z, a.z); a.w = fmaf(wj, v[j].w, a.w);
+                                a[r].x = fmaf(wj, v[r][j].x, a[r].x); a[r].y = fmaf(wj, v[r][j].y, a[r].y);
+                                a[r].z = fmaf(wj, v[r][j].z, a[r].z); a[r].w = fmaf(wj, v[r][j].w, a[r].w);
                             }
-                        } else {
+                        }
+                    } else {
+                        for (int r = 0; r < 2; ++r) {
+                            const int hq = hb + hh0 + r * Hkv;
+                            if (hq >= H || hh0 + r * Hkv >= 16) continue;
+                            const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
                             float M = -1e30f;
                             for (int j = lane; j < parts; j += 32) M = fmaxf(M, __ldcg(base + j * pstride + HEAD_DIM));
 #pragma unroll
@@ -646,47 +658,63 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                                 for (int j = 0; j < jn; ++j) {
                                     const float wj = __shfl_sync(0xffffffffu, sc, j);
                                     const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (j0 + j) * pstride) + lane);
-                                    a.x = fmaf(wj, v.x, a.x); a.y = fmaf(wj, v.y, a.y);
-                                    a.z = fmaf(wj, v.z, a.z); a.w = fmaf(wj, v.w, a.w);
+                                    a[r].x = fmaf(wj, v.x, a[r].x); a[r].y = fmaf(wj, v.y, a[r].y);
+                                    a[r].z = fmaf(wj, v.z, a[r].z); a[r].w = fmaf(wj, v.w, a[r].w);
                                 }
                             }
                         }
                     }
-                    __half2 h01 = __floats2half2_rn(a.x, a.y), h23 = __floats2half2_rn(a.z, a.w);
-                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                    const uint32_t dst = merge_s + (uint32_t)(hh * MERGE_ROW + 4 * lane) * 2u;
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h01)),
-                                 "r"(*reinterpret_cast<uint32_t*>(&h23)) : "memory");
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + 16u * MERGE_ROW * 2u),
-                                 "r"(pack_half2(a.x - f01.x, a.y - f01.y)), "r"(pack_half2(a.z - f23.x, a.w - f23.y)) : "memory");
-                }
-                group_barrier(group, gthreads);
-                // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k]
-                for (int nb = head; nb < 16; nb += Hkv) {
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    const __half* rt = p.rotation_t + (size_t)(8 * nb + gl) * HEAD_DIM + 2 * t4;
-                    uint32_t bfrag[8][2];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        bfrag[j][0] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j));
-                        bfrag[j][1] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j + 8));
+                    for (int r = 0; r < 2; ++r) {
+                        const int hh = hh0 + r * Hkv;
+                        if (hh >= 16) continue;
+                        __half2 h01 = __floats2half2_rn(a[r].x, a[r].y), h23 = __floats2half2_rn(a[r].z, a[r].w);
+                        float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                        const uint32_t dst = merge_s + (uint32_t)(hh * MERGE_ROW + 4 * lane) * 2u;
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h01)),
+                                     "r"(*reinterpret_cast<uint32_t*>(&h23)) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + 16u * MERGE_ROW * 2u),
+                                     "r"(pack_half2(a[r].x - f01.x, a[r].y - f01.y)), "r"(pack_half2(a[r].z - f23.x, a[r].w - f23.y)) : "memory");
                     }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t r0 = merge_s + (uint32_t)(gl * MERGE_ROW + 16 * j + 2 * t4) * 2u;
-                        const uint32_t r8 = r0 + 8u * MERGE_ROW * 2u;
-                        const uint32_t lo_off = 16u * MERGE_ROW * 2u;
-                        mma16816(c, lds32(r0), lds32(r8), lds32(r0 + 16u), lds32(r8 + 16u), bfrag[j][0], bfrag[j][1]);
-                        mma16816(c, lds32(r0 + lo_off), lds32(r8 + lo_off), lds32(r0 + lo_off + 16u), lds32(r8 + lo_off + 16u),
-                                 bfrag[j][0], bfrag[j][1]);
-                    }
-                    const int d = 8 * nb + 2 * t4;
-                    if (hb + gl < H)
-                        *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl) * HEAD_DIM + d) = __floats2half2_rn(c[0], c[1]);
-                    if (hb + gl + 8 < H)
-                        *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl + 8) * HEAD_DIM + d) = __floats2half2_rn(c[2], c[3]);
                 }
-                group_barrier(group, gthreads);
+                // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k].
+                //      Two column blocks of 8 per warp and pass; their B fragments are fetched before the barrier so that
+                //      the round trip overlaps the other warps' phase A.
+                for (int nb0 = head; nb0 < 16; nb0 += 2 * Hkv) {
+                    uint32_t bfrag[2][8][2];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int nb = nb0 + i * Hkv;
+                        const __half* rt = p.rotation_t + (size_t)(8 * (nb < 16 ? nb : 0) + gl) * HEAD_DIM + 2 * t4;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            bfrag[i][j][0] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j));
+                            bfrag[i][j][1] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j + 8));
+                        }
+                    }
+                    if (nb0 == head) group_barrier(group, gthreads);  // phase A of every warp is in shared memory
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int nb = nb0 + i * Hkv;
+                        if (nb >= 16) continue;
+                        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t r0 = merge_s + (uint32_t)(gl * MERGE_ROW + 16 * j + 2 * t4) * 2u;
+                            const uint32_t r8 = r0 + 8u * MERGE_ROW * 2u;
+                            const uint32_t lo_off = 16u * MERGE_ROW * 2u;
+                            mma16816(c, lds32(r0), lds32(r8), lds32(r0 + 16u), lds32(r8 + 16u), bfrag[i][j][0], bfrag[i][j][1]);
+                            mma16816(c, lds32(r0 + lo_off), lds32(r8 + lo_off), lds32(r0 + lo_off + 16u), lds32(r8 + lo_off + 16u),
+                                     bfrag[i][j][0], bfrag[i][j][1]);
+                        }
+                        const int d = 8 * nb + 2 * t4;
+                        if (hb + gl < H)
+                            *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl) * HEAD_DIM + d) = __floats2half2_rn(c[0], c[1]);
+                        if (hb + gl + 8 < H)
+                            *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl + 8) * HEAD_DIM + d) = __floats2half2_rn(c[2], c[3]);
+                    }
+                }
+                group_barrier(group, gthreads);  // the A operand may be overwritten (next 16 heads, next segment)
             }
         }
         ++g;
