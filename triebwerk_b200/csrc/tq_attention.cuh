@@ -94,13 +94,6 @@ __device__ __forceinline__ void group_barrier(int group, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(nthreads) : "memory");
 }
 
-// Contiguous bulk copy global -> shared of this CTA, completion on an mbarrier.  Addresses 16-byte aligned,
-// size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }

@@ -94,7 +94,8 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
                        const void* q, const void* rotation, const int* positions, int pos_value,
                        const long long* row_base, int token_mode, long long token_row0, int max_seq_len, int n_src,
                        int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
-                       size_t workspace_bytes, bool build_tiles, cudaStream_t s, bool pdl = false) {
+                       size_t workspace_bytes, bool build_tiles, cudaStream_t s, bool pdl = false,
+                       const float* rot_prep = nullptr) {
     if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
     if (bits != 2 && bits != 4) return TQ_ERR_ARG;
     if (n_src <= 0 || num_kv_heads <= 0 || kv_dim != num_kv_heads * head_dim || !rotation) return TQ_ERR_ARG;
@@ -108,6 +109,7 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.ck = ck_q; p.kn = (__half*)k_norms; p.cv = cv_q; p.vn = (__half*)v_norms;
     p.k_buf = (const __half*)k_buf; p.v_buf = (const __half*)v_buf; p.q = (const __half*)q;
     p.rotation = (const __half*)rotation;
+    p.rot_prep = rot_prep;
     p.positions = positions; p.row_base = row_base;
     p.q_rot = fw.w.q_rot;
     p.tile_start = build_tiles ? fw.w.tile_start : nullptr;
@@ -120,8 +122,6 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.max_seq_len = max_seq_len; p.capacity_rows = max_seq_len;
     p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
     p.pos_value = pos_value;
-    static const bool stamps = getenv("TQ_APPEND_STAMPS") != nullptr;  // measurement: clock stamps in the header's spare words
-    p.stamps = stamps ? reinterpret_cast<long long*>(reinterpret_cast<char*>(workspace) + 64) : nullptr;
     return launch_append(p, s, pdl);
 }
 
@@ -468,6 +468,16 @@ static int engine_upload_rotation(tq_engine* e, cudaStream_t s) {
         for (int d = 0; d < HEAD_DIM; ++d) t[(size_t)d * HEAD_DIM + k] = e->h_rotation[(size_t)k * HEAD_DIM + d];
     TQ_CUDA(cudaMemcpyAsync(e->d_rotation, e->h_rotation.data(), bytes, cudaMemcpyHostToDevice, s));
     TQ_CUDA(cudaMemcpyAsync(e->d_rotation_t, t.data(), bytes, cudaMemcpyHostToDevice, s));
+    // R as fp32 in the append kernel's shared-memory order [k/4][d][k%4], so that the kernel stages it with one copy
+    if (!e->d_rotation_prep) TQ_CUDA(cudaMalloc(&e->d_rotation_prep, (size_t)HEAD_DIM * HEAD_DIM * sizeof(float)));
+    std::vector<float> prep((size_t)HEAD_DIM * HEAD_DIM);
+    for (int d = 0; d < HEAD_DIM; ++d)
+        for (int k = 0; k < HEAD_DIM; ++k) {
+            __half_raw raw;
+            raw.x = e->h_rotation[(size_t)d * HEAD_DIM + k];
+            prep[((size_t)(k / 4) * HEAD_DIM + d) * 4 + (k % 4)] = __half2float(__half(raw));
+        }
+    TQ_CUDA(cudaMemcpyAsync(e->d_rotation_prep, prep.data(), prep.size() * sizeof(float), cudaMemcpyHostToDevice, s));
     TQ_CUDA(cudaStreamSynchronize(s));  // t and h_rotation are pageable host memory
     return TQ_OK;
 }
@@ -490,6 +500,7 @@ void tq_engine_destroy(tq_engine* e) {
     engine_release_arena(e);
     if (e->d_rotation) cudaFree(e->d_rotation);
     if (e->d_rotation_t) cudaFree(e->d_rotation_t);
+    if (e->d_rotation_prep) cudaFree(e->d_rotation_prep);
     delete e;
 }
 
@@ -714,7 +725,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
-                        e->ws_bytes, true, cs(s), use_pdl());
+                        e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep);
     if (r != TQ_OK) return r;
     return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
                           e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl());
@@ -792,6 +803,7 @@ int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, co
     p.ck = (uint8_t*)L.k; p.kn = (__half*)L.kn; p.cv = (uint8_t*)L.v; p.vn = (__half*)L.vn;
     p.k_buf = (const __half*)k; p.v_buf = (const __half*)v; p.q = nullptr;
     p.rotation = (const __half*)e->d_rotation;
+    p.rot_prep = e->d_rotation_prep;
     p.positions = d_iota; p.row_base = nullptr; p.q_rot = nullptr;
     p.tile_start = nullptr; p.tickets = nullptr; p.total_tiles = nullptr;
     p.status = (int*)e->workspace;

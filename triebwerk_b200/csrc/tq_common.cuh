@@ -205,6 +205,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// Contiguous bulk copy global -> shared of this CTA, completion on an mbarrier.  Addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // 3-D form of the same load; the coordinates are (x, y, z) from the innermost dimension outwards.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
     asm volatile(

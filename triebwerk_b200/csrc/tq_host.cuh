@@ -154,7 +154,7 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
         TQ_CUDA(cudaFuncSetAttribute(append_rotate_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)APPEND_SMEM));
         attr_set[dev] = true;
     }
-    return launch_kernel(append_rotate_kernel<NV>, grid, dim3(128), APPEND_SMEM, s, pdl, p);
+    return launch_kernel(append_rotate_kernel<NV>, grid, dim3(APPEND_THREADS), APPEND_SMEM, s, pdl, p);
 }
 
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
@@ -163,18 +163,18 @@ inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false
     const bool tables = p.tile_start != nullptr && !p.token_mode;
     if (total <= 0 && !tables) return TQ_OK;
     if (total >= (1ll << 31)) return TQ_ERR_CAPACITY;
-    // As few vectors per CTA as still fit the whole launch into one wave (3 CTAs of 64 KB shared memory per SM):
-    // short dependent chains when the batch is small, amortised staging of R when it is large.
-    const long long slots = (long long)device_props().sm_count * 3 - 1;
-    int nvec = 2;
-    while (nvec < APPEND_MAX_NV && (total + nvec - 1) / nvec > slots) nvec *= 2;
-    long long groups = (total + nvec - 1) / nvec;
-    if (groups > slots) groups = slots;
-    if (groups < 1) groups = 1;
-    const dim3 grid((unsigned)(groups + (tables ? 1 : 0)));
+    // One CTA per SM at most.  As few vectors per group as still fit the whole launch into that one wave: short
+    // dependent chains when the batch is small, amortised staging of R when it is large (then the CTAs loop).
+    const long long slots = (long long)device_props().sm_count - 1;
+    int nvec = 1;
+    while (nvec < APPEND_MAX_NV && (total + nvec * APPEND_GROUPS - 1) / (nvec * APPEND_GROUPS) > slots) nvec *= 2;
+    long long blocks = (total + nvec * APPEND_GROUPS - 1) / (nvec * APPEND_GROUPS);
+    if (blocks > slots) blocks = slots;
+    if (blocks < 1) blocks = 1;
+    const dim3 grid((unsigned)(blocks + (tables ? 1 : 0)));
+    if (nvec == 1) return launch_append_t<1>(p, grid, s, pdl);
     if (nvec == 2) return launch_append_t<2>(p, grid, s, pdl);
-    if (nvec == 4) return launch_append_t<4>(p, grid, s, pdl);
-    return launch_append_t<8>(p, grid, s, pdl);
+    return launch_append_t<4>(p, grid, s, pdl);
 }
 
 // Number of attention CTAs: one per SM (each holds ATTN_GROUPS workers), fewer when the cache cannot hold that
@@ -358,6 +358,7 @@ struct tq_engine {
     std::vector<uint16_t> h_rotation;
     void* d_rotation = nullptr;
     void* d_rotation_t = nullptr;
+    float* d_rotation_prep = nullptr;  // fp32, in the append kernel's shared-memory order
 
     int q_dim() const { return shape.num_heads * shape.head_dim; }
     int kv_dim() const { return shape.num_kv_heads * shape.head_dim; }
