@@ -241,8 +241,9 @@ int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s);
 int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
                            tq_stream_t s);
 
-/* The attention half of tq_engine_decode_layer alone, on the queries the last tq_engine_decode_layer of
- * this engine rotated (packed modes only).  Used to time the attention kernel by itself. */
+/* The attention over the current positions alone, on whatever rotated queries the engine's workspace holds (those
+ * of the last two-launch tq_engine_decode_layer, zeros before; packed modes only).  Used to time the attention
+ * kernel by itself. */
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s);
 
 /* tq_engine_attend_layer for every layer in turn: out [layers][G][q_dim] on the device. */

@@ -53,17 +53,6 @@ struct AppendParams {
     int pos_value;               // used when positions == nullptr
 };
 
-__device__ __forceinline__ int quantize_code(float v, int bits) {
-    if (bits == 4) {
-        if (v != v) return 15;
-        int c = 0;
-#pragma unroll
-        for (int i = 0; i < 15; ++i) c += (v >= kBnd4[i]) ? 1 : 0;
-        return c;
-    }
-    return ((v >= kBnd2[0]) ? 1 : 0) + ((v >= kBnd2[1]) ? 1 : 0) + ((v >= kBnd2[2]) ? 1 : 0);
-}
-
 // One CTA = APPEND_GROUPS groups of 128 threads around one copy of R in shared memory; thread d of a group owns
 // output coordinate d and row d of R, and a group carries NV head vectors at a time.  When the launch also has to
 // build the attention kernel's tables, block 0 does only that and the head vectors start at block 1.

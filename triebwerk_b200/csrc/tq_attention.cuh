@@ -71,6 +71,16 @@ struct AttnParams {
     int pos_value;
     int max_seq_len;
     int G, H, Hkv, q_dim;
+    // fused form (one launch per layer and step: append the new token, rotate the queries, attend)
+    const __half* new_k;       // [G][kv_dim] this step's keys, values and queries
+    const __half* new_v;
+    const __half* new_q;       // [G][q_dim]
+    const __half* rotation;    // R row-major (B operand of the query rotation); rot_copies copies back to back
+    const __half* rot_prep16;  // R in the order [k/4][d][k%4] (fp16, 32 KB): rows of the exact fp32 chain, staged in shared memory; rot_copies copies
+    int rot_copies;            // every worker reads copy (worker % rot_copies): 300 workers fetching the same 32 KB at once queue up in L2
+    int kv_dim;
+    int capacity_rows;         // rows a sequence may use (position check)
+    int app_weight;            // cost of one append in tiles, for the balance of the work list
     int l2_ahead;              // tiles prefetched into L2 beyond the shared-memory ring
     int debug;                 // measurement switches (TQ_ATTN_DEBUG): bit 0 = skip the math, bit 1 = skip the loads
 };
@@ -88,7 +98,14 @@ struct RegionA {
     static constexpr uint32_t MERGE_OFF = 512;   // per group: hi + lo [16][MERGE_ROW] halves
     static constexpr uint32_t MERGE_GROUP_BYTES = 2 * 16 * MERGE_ROW * 2;  // 8704
     static constexpr uint32_t BLOCKS_OFF = MERGE_OFF + ATTN_GROUPS * MERGE_GROUP_BYTES;
+    // fused form only: tile table of the launch, then per group the append's codes, partial sums and destinations
+    static constexpr uint32_t FUSED_SCAN_OFF = BLOCKS_OFF;           // 32 ints of scan scratch
+    static constexpr uint32_t FUSED_TS_OFF = FUSED_SCAN_OFF + 128;   // tile_start[G + 1], G <= FUSED_MAX_G
+    static constexpr uint32_t FUSED_APP_OFF = FUSED_TS_OFF + 4096;
+    static constexpr uint32_t FUSED_APP_GROUP_BYTES = 16 * 128 + 16 * 4 * 4 + 128;  // codes, warp sums, 16 dest rows
+    static constexpr uint32_t FUSED_BLOCKS_OFF = FUSED_APP_OFF + ATTN_GROUPS * FUSED_APP_GROUP_BYTES;
 };
+constexpr int FUSED_MAX_G = 1023;
 
 __device__ __forceinline__ void group_barrier(int group, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(nthreads) : "memory");
@@ -119,13 +136,25 @@ __device__ __forceinline__ uint4 ldsp128(uint32_t addr) {
     asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
     return r;
 }
+// The same loads kept in program order relative to barriers and other volatile accesses (staging buffers that are
+// rewritten between uses).
+__device__ __forceinline__ uint2 ldsv64(uint32_t addr) {
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint4 ldsv128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
 __device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from shared memory as float
     unsigned short h;
     asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
     return __half2float(__ushort_as_half(h));
 }
 
-template <int BITS, bool QSPLIT, int HKV>
+template <int BITS, bool QSPLIT, int HKV, bool FUSED>
 __global__ void __launch_bounds__(ATTN_GROUPS * 32 * HKV, 1)
 decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const AttnParams p) {
@@ -151,7 +180,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     // ---- shared memory map (absolute shared addresses) ----
     const uint32_t dyn_base = smem_u32(dyn_smem);
     const uint32_t a_base = (dyn_base + 1023u) & ~1023u;
-    const uint32_t blocks_a = (a_base + RegionA::BLOCKS_OFF + 1023u) & ~1023u;
+    const uint32_t blocks_a = (a_base + (FUSED ? RegionA::FUSED_BLOCKS_OFF : RegionA::BLOCKS_OFF) + 1023u) & ~1023u;
     const uint32_t n_a = blocks_a < LUT_ABS ? (LUT_ABS - blocks_a) / stage_bytes : 0u;
     const uint32_t dyn_end = dyn_base + (uint32_t)ATTN_DYN_SMEM;
     const uint32_t n_b = dyn_end > REGION_B_ABS ? (dyn_end - REGION_B_ABS) / stage_bytes : 0u;
@@ -193,6 +222,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     }
     if (gtid == 0) {
+        if (FUSED) mbar_init(a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group, 1);
         for (int s = 0; s < ATTN_MAX_STAGES; ++s) {
             mbar_init(bar0 + 8u * s, 1);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
@@ -202,8 +232,46 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     }
     // Everything above touches only shared memory and may overlap the tail of the previous kernel in the stream.
     pdl_wait();
-    const long long N = p.tile_start[G];
+    // Tile table.  The fused form builds it here, in shared memory, from the positions (every CTA the same table);
+    // the plain form reads the one the append kernel left in the workspace.
+    const int* ts;
+    if constexpr (FUSED) {
+        int* ts_s = reinterpret_cast<int*>(dyn_smem + (a_base - dyn_base) + RegionA::FUSED_TS_OFF);
+        int* scan_s = reinterpret_cast<int*>(dyn_smem + (a_base - dyn_base) + RegionA::FUSED_SCAN_OFF);
+        int carry = 0;
+        for (int base = 0; base < G; base += (int)blockDim.x) {
+            const int gq = base + tid;
+            int n = 0;
+            if (gq < G) {
+                int pos = p.positions ? p.positions[gq] : p.pos_value;
+                if (pos < 0) pos = 0;
+                n = (pos + TILE_TOKENS) / TILE_TOKENS;
+            }
+            int incl = n;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += v;
+            }
+            if (lane == 31) scan_s[warp] = incl;
+            __syncthreads();
+            int before = 0, all = 0;
+            for (int w2 = 0; w2 < (int)(blockDim.x >> 5); ++w2) {
+                const int v = scan_s[w2];
+                before += (w2 < warp) ? v : 0;
+                all += v;
+            }
+            if (gq < G) ts_s[gq] = carry + before + incl - n;
+            carry += all;
+            __syncthreads();
+        }
+        if (tid == 0) ts_s[G] = carry;
+        ts = ts_s;
+    } else {
+        ts = p.tile_start;
+    }
     __syncthreads();
+    const long long N = ts[G];
 
     // ---- work slice of this worker ----
     // Only min(workers, N) workers take part, so that every participant owns at least one tile: the ticket
@@ -212,20 +280,43 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int W = w_all < N ? (int)w_all : (int)N;
     const int wid = blockIdx.x * ATTN_GROUPS + group;
     if (wid >= W) return;  // uniform for the worker; no CTA-wide barrier follows
-    const long long lo = (long long)wid * N / W;
-    const long long hi = (long long)(wid + 1) * N / W;
-
-    // first sequence of the slice: largest g with tile_start[g] <= lo
+    // The flat list is cut in UNITS: a tile is one unit, except the last tile of a sequence in the fused form, which
+    // counts 1 + A units because its owner also appends the sequence's new token (A = p.app_weight, the append's
+    // cost in tiles).  Sequence g starts at unit ts[g] + g*A; a tile belongs to the worker its first unit falls to.
+    const long long A = FUSED ? (long long)p.app_weight : 0;
+    const long long U = N + (long long)G * A;
+    long long lo, hi;
     int g;
-    if (p.worker_g) {
-        g = p.worker_g[wid];
+    if constexpr (FUSED) {
+        auto tiles_before = [&](long long x, int* gfirst) -> long long {  // tiles whose first unit is below unit x
+            if (x >= U) { *gfirst = G; return N; }
+            int a = 0, b = G;  // invariant: unit start of a <= x < unit start of b
+            while (b - a > 1) {
+                const int mid = (a + b) >> 1;
+                if ((long long)ts[mid] + mid * A <= x) a = mid; else b = mid;
+            }
+            const long long off = x - ((long long)ts[a] + a * A), n = ts[a + 1] - ts[a];
+            *gfirst = off >= n ? a + 1 : a;
+            return ts[a] + (off < n ? off : n);
+        };
+        int g_hi;
+        lo = tiles_before((long long)wid * U / W, &g);
+        hi = tiles_before((long long)(wid + 1) * U / W, &g_hi);
+        if (lo >= hi) return;  // the worker's units all lie inside an append's share: nothing to do
     } else {
-        int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
-        while (b - a > 1) {
-            int mid = (a + b) >> 1;
-            if ((long long)p.tile_start[mid] <= lo) a = mid; else b = mid;
+        lo = (long long)wid * N / W;
+        hi = (long long)(wid + 1) * N / W;
+        // first sequence of the slice: largest g with tile_start[g] <= lo
+        if (p.worker_g) {
+            g = p.worker_g[wid];
+        } else {
+            int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
+            while (b - a > 1) {
+                int mid = (a + b) >> 1;
+                if ((long long)ts[mid] <= lo) a = mid; else b = mid;
+            }
+            g = a;
         }
-        g = a;
     }
 
     // ---- load cursor over the flat tile list (warp-uniform, advanced in step by every warp of the worker) ----
@@ -233,14 +324,14 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int lo_i = (int)lo, hi_i = (int)hi;
     int cl_tile = lo_i;                         // next tile to load into shared memory
     int cl_g = g;
-    int cl_gend = p.tile_start[g + 1];
-    int cl_row = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - p.tile_start[g]) * TILE_TOKENS;
+    int cl_gend = ts[g + 1];
+    int cl_row = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - ts[g]) * TILE_TOKENS;
     auto cursor_advance = [&]() {
         ++cl_tile;
         cl_row += TILE_TOKENS;
         if (cl_tile == cl_gend && cl_tile < hi_i) {
             ++cl_g;
-            cl_gend = p.tile_start[cl_g + 1];
+            cl_gend = ts[cl_g + 1];
             cl_row = (int)(p.row_base ? p.row_base[cl_g] : (long long)cl_g * p.max_seq_len);
         }
     };
@@ -279,15 +370,164 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
         }
     };
-    // prologue: fill the ring (and prefetch a few tiles beyond each)
-    for (int s = 0; s < S; ++s) {
-        if (cl_tile < hi_i) {
-            if (gtid == 0 && loads_on) {
-                issue_tile(cl_row, s);
-                prefetch_ahead(cl_row, cl_tile, cl_gend);
+    auto fill_ring = [&]() {  // prologue: fill the ring (and prefetch a few tiles beyond each)
+        for (int s = 0; s < S; ++s) {
+            if (cl_tile < hi_i) {
+                if (gtid == 0 && loads_on) {
+                    issue_tile(cl_row, s);
+                    prefetch_ahead(cl_row, cl_tile, cl_gend);
+                }
+                cursor_advance();
             }
-            cursor_advance();
         }
+    };
+    if constexpr (FUSED) {
+        // The new token of a sequence is appended by the worker that owns the sequence's last tile (the only tile the
+        // row can be in), before that tile is fetched.  Such a worker first borrows its two (still empty) stages for
+        // R, which the exact fp32 chain reads row by row, and fills the ring afterwards.
+        int g_app0 = g;  // first sequence whose last tile starts at or after lo
+        while (g_app0 < G && ts[g_app0 + 1] - 1 < lo_i) ++g_app0;
+        const bool have_app = g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
+        if (have_app) {
+            const uint32_t abar = a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group;
+            const uint32_t r_lo = stage_addr(0), r_hi = stage_addr(1);  // R[.][k < 64] and R[.][k >= 64], 16 KB each
+            if (gtid == 0) {
+                mbar_arrive_expect_tx(abar, 32768u);
+                const __half* rsrc = p.rot_prep16 + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);
+                bulk_load(r_lo, rsrc, 16384u, abar);
+                bulk_load(r_hi, rsrc + 8192, 16384u, abar);
+            }
+            const uint32_t xs_a = merge_s;  // [16][128] fp32 staging of the normalised vectors (the merge area is idle)
+            const uint32_t app_a = a_base + RegionA::FUSED_APP_OFF + (uint32_t)group * RegionA::FUSED_APP_GROUP_BYTES;
+            const uint32_t codes_a = app_a, part_a = app_a + 2048u;
+            const int d = gtid & 127, sub = gtid >> 7;  // 8 vectors per 128 threads: K heads first, then V heads
+            const int wsub = (gtid >> 5) & 3;
+            bool r_ready = false;
+            for (int ga = g_app0; ga < G && ts[ga + 1] - 1 < hi_i; ++ga) {
+                const int pos = p.positions ? p.positions[ga] : p.pos_value;
+                const bool ok = pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows);
+                const long long row = (p.row_base ? p.row_base[ga] : (long long)ga * p.max_seq_len) + pos;
+                float val[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const int vi = sub * 8 + v;
+                    const __half* srcp = (vi < Hkv ? p.new_k : p.new_v) + (size_t)ga * p.kv_dim + (size_t)(vi % Hkv) * HEAD_DIM + d;
+                    val[v] = __half2float(*srcp);
+                }
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float sq = mul_ftz(val[v], val[v]);
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) sq = add_ftz(sq, __shfl_down_sync(0xffffffffu, sq, off));
+                    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_a + (uint32_t)((sub * 8 + v) * 4 + wsub) * 4u), "f"(sq) : "memory");
+                }
+                group_barrier(group, gthreads);
+                float tn[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float4 pp;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(pp.x), "=f"(pp.y), "=f"(pp.z), "=f"(pp.w)
+                                 : "r"(part_a + (uint32_t)(sub * 8 + v) * 16u) : "memory");
+                    const float ss = add_ftz(add_ftz(pp.x, pp.z), add_ftz(pp.y, pp.w));
+                    tn[v] = add_ftz(ss, 1e-12f);
+                    const float xh = mul_ftz(val[v], rsqrt_approx_ftz(tn[v]));
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + d) * 4u), "f"(xh) : "memory");
+                }
+                group_barrier(group, gthreads);
+                if (!r_ready) {
+                    if (!mbar_wait_bounded(abar, 0u, 1u << 22)) {
+                        dead = true;
+                        if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+                    }
+                    r_ready = true;
+                }
+                // k-ascending fused chain per output coordinate, eight vectors interleaved; a short rolled loop
+                float acc[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) acc[v] = 0.0f;
+#pragma unroll 4
+                for (int j = 0; j < HEAD_DIM / 4; ++j) {
+                    const uint2 rw = ldsv64((j < 16 ? r_lo : r_hi) + (uint32_t)(((j & 15) * HEAD_DIM + d) * 8));
+                    const float2 r01 = __half22float2(*reinterpret_cast<const __half2*>(&rw.x));
+                    const float2 r23 = __half22float2(*reinterpret_cast<const __half2*>(&rw.y));
+                    float4 x[8];
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const uint4 xw = ldsv128(xs_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + 4 * j) * 4u);
+                        x[v] = make_float4(__uint_as_float(xw.x), __uint_as_float(xw.y), __uint_as_float(xw.z), __uint_as_float(xw.w));
+                    }
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r01.x, x[v].x, acc[v]);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r01.y, x[v].y, acc[v]);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r23.x, x[v].z, acc[v]);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r23.y, x[v].w, acc[v]);
+                }
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(codes_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + d)),
+                                 "r"(quantize_code(acc[v], BITS)) : "memory");
+                // the norm of vector v, by thread v of its 128
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    if (d == v) {
+                        const int vi = sub * 8 + v;
+                        if (ok) {
+                            __half* cn = const_cast<__half*>(vi < Hkv ? p.kn : p.vn);
+                            cn[(size_t)row * Hkv + (vi % Hkv)] = __float2half_rn(sqrt_approx_ftz(tn[v]));
+                        } else if (vi == 0) {
+                            atomicMax(p.status, ST_BAD_POSITION);
+                        }
+                    }
+                }
+                group_barrier(group, gthreads);
+                // pack: one 32-bit word (8 four-bit or 16 two-bit codes) per thread
+                {
+                    constexpr int words_per_vec = (int)Geo::BPH / 4;
+                    if (ok && d < 8 * words_per_vec) {
+                        const int v = d / words_per_vec, wv = d - v * words_per_vec;
+                        const int vi = sub * 8 + v;
+                        uint32_t word = 0;
+                        if (BITS == 2) {
+                            uint4 c4;  // ordered after the barrier: a volatile load, unlike the tile loop's
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c4.x), "=r"(c4.y), "=r"(c4.z), "=r"(c4.w)
+                                         : "r"(codes_a + (uint32_t)(vi * HEAD_DIM + 16 * wv)) : "memory");
+                            const uint32_t cw[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const uint32_t x = cw[b];
+                                const uint32_t pk = (x & 3u) | ((x >> 6) & 0xcu) | ((x >> 12) & 0x30u) | ((x >> 18) & 0xc0u);
+                                word |= pk << (8 * b);
+                            }
+                        } else {
+                            uint2 c2;
+                            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(c2.x), "=r"(c2.y)
+                                         : "r"(codes_a + (uint32_t)(vi * HEAD_DIM + 8 * wv)) : "memory");
+                            const uint32_t cw[2] = {c2.x, c2.y};
+#pragma unroll
+                            for (int hb2 = 0; hb2 < 2; ++hb2) {
+                                const uint32_t x = cw[hb2];
+                                const uint32_t pk = (x & 0xfu) | ((x >> 4) & 0xf0u) | ((x >> 8) & 0xf00u) | ((x >> 12) & 0xf000u);
+                                word |= pk << (16 * hb2);
+                            }
+                        }
+                        uint8_t* cq = const_cast<uint8_t*>(vi < Hkv ? p.ck : p.cv);
+                        *reinterpret_cast<uint32_t*>(cq + (size_t)row * kvp + (size_t)(vi % Hkv) * Geo::BPH + 4 * wv) = word;
+                    }
+                }
+                // the row is read back by tensor-map copies (async proxy) of this worker
+                __threadfence();
+                fence_proxy_async_all();
+                group_barrier(group, gthreads);
+            }
+            // the stages go back to the ring: generic-proxy reads of R before, async-proxy writes of tiles after
+            if (gtid == 0) fence_proxy_async_all();
+        }
+        fill_ring();
+    } else {
+        fill_ring();
     }
 
     if (p.debug & 64) return;
@@ -316,8 +556,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     long long tile = lo;
     while (tile < hi) {
         // ================= one segment: tiles [tile, seg_end) of sequence g =================
-        const long long ts_g = p.tile_start[g];
-        const long long ts_g1 = p.tile_start[g + 1];
+        const long long ts_g = ts[g];
+        const long long ts_g1 = ts[g + 1];
         const long long seg_end = hi < ts_g1 ? hi : ts_g1;
         const int pos = p.positions ? p.positions[g] : p.pos_value;
         const int L = (pos < 0 ? 0 : pos) + 1;
@@ -326,7 +566,70 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         uint32_t qa[8][QSPLIT ? 4 : 2];
         {
             float qv[32];
-            if (gl < grp && !(p.debug & 8)) {
+            if constexpr (FUSED) {
+                // Rotate this sequence's queries here: rot[h][d] = sum_k q[h][k] * R[d][k] on the tensor cores, 16 heads
+                // at a time, every warp two (Hkv = 8) or four (Hkv = 4) blocks of 8 coordinates; the result goes through
+                // shared memory (the idle merge area) to the lanes that need it, scaled by log2(e) / sqrt(128).
+                const uint32_t qs_a = merge_s;  // [16][128] fp32
+#pragma unroll
+                for (int i = 0; i < 32; ++i) qv[i] = 0.0f;
+                for (int hb = 0; hb < p.H; hb += 16) {
+                    // 16 query heads (4 KB) into shared memory with one coalesced 16-byte load per thread
+                    for (int i = gtid; i < 256; i += gthreads) {
+                        const int r = i >> 4;
+                        uint4 u = make_uint4(0u, 0u, 0u, 0u);
+                        if (hb + r < p.H)
+                            u = __ldg(reinterpret_cast<const uint4*>(p.new_q + (size_t)g * p.q_dim + (size_t)(hb + r) * HEAD_DIM) + (i & 15));
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(qs_a + (uint32_t)i * 16u), "r"(u.x), "r"(u.y),
+                                     "r"(u.z), "r"(u.w) : "memory");
+                    }
+                    // B fragments straight from R (16 contiguous bytes per lane and load: whole sectors).  The contraction
+                    // index is permuted the same way on both sides: step (m, e) of lane t4 covers k = 32m + 8*t4 + 4e .. +3.
+                    uint4 bq[16 / Hkv][4];
+#pragma unroll
+                    for (int nbi = 0; nbi < 16 / Hkv; ++nbi) {
+                        const int nb = head + nbi * Hkv;
+                        const uint4* rr = reinterpret_cast<const uint4*>(p.rotation + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM) +
+                                                                         (size_t)(8 * nb + gl) * HEAD_DIM) + t4;
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) bq[nbi][m] = __ldg(rr + 4 * m);
+                    }
+                    group_barrier(group, gthreads);
+                    uint4 a_lo[4], a_hi[4];  // rows gl and gl + 8
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        a_lo[m] = ldsv128(qs_a + (uint32_t)(gl * HEAD_DIM + 32 * m + 8 * t4) * 2u);
+                        a_hi[m] = ldsv128(qs_a + (uint32_t)((gl + 8) * HEAD_DIM + 32 * m + 8 * t4) * 2u);
+                    }
+                    group_barrier(group, gthreads);  // the staging area turns into the fp32 result area
+#pragma unroll
+                    for (int nbi = 0; nbi < 16 / Hkv; ++nbi) {
+                        const int nb = head + nbi * Hkv;
+                        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            mma16816(c, a_lo[m].x, a_hi[m].x, a_lo[m].y, a_hi[m].y, bq[nbi][m].x, bq[nbi][m].y);
+                            mma16816(c, a_lo[m].z, a_hi[m].z, a_lo[m].w, a_hi[m].w, bq[nbi][m].z, bq[nbi][m].w);
+                        }
+                        const float sc = 0.12751743074602467f;
+                        const uint32_t o0 = qs_a + (uint32_t)(gl * HEAD_DIM + 8 * nb + 2 * t4) * 4u;
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(o0), "f"(c[0] * sc), "f"(c[1] * sc) : "memory");
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(o0 + 8u * HEAD_DIM * 4u), "f"(c[2] * sc), "f"(c[3] * sc) : "memory");
+                    }
+                    group_barrier(group, gthreads);
+                    const int myrow = head * grp + gl - hb;
+                    if (gl < grp && myrow >= 0 && myrow < 16 && !(p.debug & 8)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float4 f;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w)
+                                         : "r"(qs_a + (uint32_t)(myrow * HEAD_DIM + 32 * t4 + 4 * i) * 4u) : "memory");
+                            qv[4 * i] = f.x; qv[4 * i + 1] = f.y; qv[4 * i + 2] = f.z; qv[4 * i + 3] = f.w;
+                        }
+                    }
+                    group_barrier(group, gthreads);
+                }
+            } else if (gl < grp && !(p.debug & 8)) {
                 const float4* src =
                     reinterpret_cast<const float4*>(p.q_rot + ((size_t)g * p.H + (size_t)head * grp + gl) * HEAD_DIM + 32 * t4);
 #pragma unroll
@@ -566,8 +869,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
         if (p.debug & 4) { ++g; continue; }
         // number of workers that hold a part of sequence g
-        const int first_w = (int)(((ts_g + 1) * W - 1) / N);
-        const int last_w = (int)((ts_g1 * W - 1) / N);
+        // owners of the sequence's first and last tile (of the units those tiles start at)
+        const int first_w = (int)(((ts_g + g * A + 1) * W - 1) / U);
+        const int last_w = (int)(((ts_g1 + g * A) * W - 1) / U);
         const int parts = last_w - first_w + 1;
         group_barrier(group, gthreads);  // every warp's partial is written (happens-before the fence below)
         uint32_t is_last = 1u;

@@ -135,11 +135,22 @@ int tq_append_decode(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms,
                        workspace_bytes, true, cs(s));
 }
 
+// Inputs of the fused per-layer launch (append + query rotation + attention in one kernel).
+struct FusedInputs {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* rotation;
+    const void* rot_prep16;
+    int rot_copies;
+};
+
 static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* ck_q, const void* cv_q,
                           const void* k_norms, const void* v_norms,
                           const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
                           long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
-                          int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false) {
+                          int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false,
+                          const FusedInputs* fused = nullptr) {
     FullWorkspace fw = carve_full(workspace, G, num_heads);
     if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
     // bulk copies need 16-byte aligned sources: rows are 512/256 B (codes) and 2*Hkv B (norms, Hkv % 4 == 0 -> 8|16 B)
@@ -160,7 +171,16 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     p.debug = debug_mode;
     static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
     p.l2_ahead = l2_ahead > 0 ? l2_ahead : (1 << 28);  // 0 switches the prefetch off
-    return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl);
+    if (fused) {
+        p.new_k = (const __half*)fused->k; p.new_v = (const __half*)fused->v; p.new_q = (const __half*)fused->q;
+        p.rotation = (const __half*)fused->rotation; p.rot_prep16 = (const __half*)fused->rot_prep16;
+        p.rot_copies = fused->rot_copies;
+        // what the append of one token costs its worker, in 32-token tiles (measured; TQ_FUSED_WEIGHT overrides)
+        static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 5;
+        p.app_weight = app_weight < 0 ? 0 : app_weight;
+        p.kv_dim = num_kv_heads * HEAD_DIM; p.capacity_rows = max_seq_len;
+    }
+    return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl, fused != nullptr);
 }
 
 int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms, const void* v_norms,
@@ -459,6 +479,8 @@ int tq_engine_create(const tq_model_shape* shape, int max_seq_len, int kv_bits, 
 }
 
 // R and its transpose (for the merge's tensor-core product) to the device; both live outside the arena.
+constexpr int ROT_COPIES = 32;
+
 static int engine_upload_rotation(tq_engine* e, cudaStream_t s) {
     const size_t bytes = e->h_rotation.size() * 2;
     if (!e->d_rotation) TQ_CUDA(cudaMalloc(&e->d_rotation, bytes));
@@ -478,6 +500,18 @@ static int engine_upload_rotation(tq_engine* e, cudaStream_t s) {
             prep[((size_t)(k / 4) * HEAD_DIM + d) * 4 + (k % 4)] = __half2float(__half(raw));
         }
     TQ_CUDA(cudaMemcpyAsync(e->d_rotation_prep, prep.data(), prep.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+    // For the fused kernel: R and R in that order as fp16, ROT_COPIES copies of each back to back.  Every worker of the
+    // kernel reads all of R at the same moment; with one copy those reads queue up on the same L2 lines.
+    if (!e->d_rotation_rep) TQ_CUDA(cudaMalloc(&e->d_rotation_rep, bytes * ROT_COPIES));
+    if (!e->d_rotation_prep16) TQ_CUDA(cudaMalloc(&e->d_rotation_prep16, bytes * ROT_COPIES));
+    std::vector<uint16_t> prep16(e->h_rotation.size());
+    for (int d = 0; d < HEAD_DIM; ++d)
+        for (int k = 0; k < HEAD_DIM; ++k)
+            prep16[((size_t)(k / 4) * HEAD_DIM + d) * 4 + (k % 4)] = e->h_rotation[(size_t)d * HEAD_DIM + k];
+    for (int c = 0; c < ROT_COPIES; ++c) {
+        TQ_CUDA(cudaMemcpyAsync((char*)e->d_rotation_rep + bytes * c, e->h_rotation.data(), bytes, cudaMemcpyHostToDevice, s));
+        TQ_CUDA(cudaMemcpyAsync((char*)e->d_rotation_prep16 + bytes * c, prep16.data(), bytes, cudaMemcpyHostToDevice, s));
+    }
     TQ_CUDA(cudaStreamSynchronize(s));  // t and h_rotation are pageable host memory
     return TQ_OK;
 }
@@ -501,6 +535,8 @@ void tq_engine_destroy(tq_engine* e) {
     if (e->d_rotation) cudaFree(e->d_rotation);
     if (e->d_rotation_t) cudaFree(e->d_rotation_t);
     if (e->d_rotation_prep) cudaFree(e->d_rotation_prep);
+    if (e->d_rotation_prep16) cudaFree(e->d_rotation_prep16);
+    if (e->d_rotation_rep) cudaFree(e->d_rotation_rep);
     delete e;
 }
 
@@ -723,6 +759,14 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->d_row_base, e->total_rows, e->msl, e->G,
                                         H, Hkv, D, e->q_dim(), e->kv_dim(), e->workspace, e->ws_bytes, s);
     }
+    // One launch per layer when the batch fits the kernel's shared-memory tile table (TQ_FUSED=0: two launches).
+    static const bool fuse = !(getenv("TQ_FUSED") && atoi(getenv("TQ_FUSED")) == 0);
+    if (fuse && e->G <= FUSED_MAX_G && q && k && v) {
+        FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES};
+        return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
+                              e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s),
+                              use_pdl(), &in);
+    }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
                         e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep);
@@ -736,6 +780,11 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
     const tq_engine::Layer& L = e->layers[layer];
+    // the tile table of the current positions (a launch of the append kernel without vectors), then the attention
+    int r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, e->d_rotation, e->d_positions, 0,
+                        e->d_row_base, 0, 0, e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim,
+                        e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace, e->ws_bytes, true, cs(s), use_pdl());
+    if (r != TQ_OK) return r;
     return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
                           e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace,
                           e->ws_bytes, cs(s), use_pdl());

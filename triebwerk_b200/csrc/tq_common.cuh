@@ -157,6 +157,8 @@ __device__ __forceinline__ void mbar_inval(uint32_t bar) {
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// generic-proxy writes (any state space) before, async-proxy (bulk / tensor copy) reads after
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -203,6 +205,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst_smem), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+
+// Code of a rotated coordinate: the number of decision bounds it has reached (reference engine/kernels.cu:1540-1560).
+__device__ __forceinline__ int quantize_code(float v, int bits) {
+    if (bits == 4) {
+        if (v != v) return 15;
+        int c = 0;
+#pragma unroll
+        for (int i = 0; i < 15; ++i) c += (v >= kBnd4[i]) ? 1 : 0;
+        return c;
+    }
+    return ((v >= kBnd2[0]) ? 1 : 0) + ((v >= kBnd2[1]) ? 1 : 0) + ((v >= kBnd2[2]) ? 1 : 0);
 }
 
 // Contiguous bulk copy global -> shared of this CTA, completion on an mbarrier.  Addresses 16-byte aligned,

@@ -188,15 +188,15 @@ inline int attention_ctas(int G, int max_seq_len) {
     return (int)(w < 1 ? 1 : w);
 }
 
-template <int BITS, bool QSPLIT, int HKV>
+template <int BITS, bool QSPLIT, int HKV, bool FUSED>
 inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas, cudaStream_t s,
                               bool pdl) {
     static std::map<int, bool> attr_set;  // per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)ATTN_DYN_SMEM));
+        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT, HKV, FUSED>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_DYN_SMEM));
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
@@ -209,23 +209,33 @@ inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT, HKV>, tmK, tmV, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT, HKV, FUSED>, tmK, tmV, p));
 }
 
+// `fused`: the launch also appends the step's new token and rotates the queries (AttnParams::new_k ... are set).
 inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas,
-                            cudaStream_t s, bool pdl = false) {
+                            cudaStream_t s, bool pdl = false, bool fused = false) {
     // TQ_ATTN_QSPLIT=0 selects the variant that feeds the query to the tensor cores as plain fp16 (no high/low split)
     static const bool qsplit = !(getenv("TQ_ATTN_QSPLIT") && atoi(getenv("TQ_ATTN_QSPLIT")) == 0);
+    if (fused) {
+        if (p.Hkv == 8)
+            return bits == 4 ? launch_attention_t<4, true, 8, true>(tmK, tmV, p, ctas, s, pdl)
+                             : launch_attention_t<2, true, 8, true>(tmK, tmV, p, ctas, s, pdl);
+        if (p.Hkv == 4)
+            return bits == 4 ? launch_attention_t<4, true, 4, true>(tmK, tmV, p, ctas, s, pdl)
+                             : launch_attention_t<2, true, 4, true>(tmK, tmV, p, ctas, s, pdl);
+        return TQ_ERR_UNSUPPORTED;
+    }
     if (p.Hkv == 8) {
         if (bits == 4)
-            return qsplit ? launch_attention_t<4, true, 8>(tmK, tmV, p, ctas, s, pdl)
-                          : launch_attention_t<4, false, 8>(tmK, tmV, p, ctas, s, pdl);
-        return qsplit ? launch_attention_t<2, true, 8>(tmK, tmV, p, ctas, s, pdl)
-                      : launch_attention_t<2, false, 8>(tmK, tmV, p, ctas, s, pdl);
+            return qsplit ? launch_attention_t<4, true, 8, false>(tmK, tmV, p, ctas, s, pdl)
+                          : launch_attention_t<4, false, 8, false>(tmK, tmV, p, ctas, s, pdl);
+        return qsplit ? launch_attention_t<2, true, 8, false>(tmK, tmV, p, ctas, s, pdl)
+                      : launch_attention_t<2, false, 8, false>(tmK, tmV, p, ctas, s, pdl);
     }
     if (p.Hkv == 4) {
-        if (bits == 4) return launch_attention_t<4, true, 4>(tmK, tmV, p, ctas, s, pdl);
-        return launch_attention_t<2, true, 4>(tmK, tmV, p, ctas, s, pdl);
+        if (bits == 4) return launch_attention_t<4, true, 4, false>(tmK, tmV, p, ctas, s, pdl);
+        return launch_attention_t<2, true, 4, false>(tmK, tmV, p, ctas, s, pdl);
     }
     return TQ_ERR_UNSUPPORTED;
 }
@@ -359,6 +369,8 @@ struct tq_engine {
     void* d_rotation = nullptr;
     void* d_rotation_t = nullptr;
     float* d_rotation_prep = nullptr;  // fp32, in the append kernel's shared-memory order
+    void* d_rotation_prep16 = nullptr; // the same order in fp16, for the fused kernel (several copies)
+    void* d_rotation_rep = nullptr;    // R row-major, several copies, for the fused kernel's query rotation
 
     int q_dim() const { return shape.num_heads * shape.head_dim; }
     int kv_dim() const { return shape.num_kv_heads * shape.head_dim; }
