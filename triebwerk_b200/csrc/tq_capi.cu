@@ -176,7 +176,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         p.rotation = (const __half*)fused->rotation; p.rot_prep16 = (const __half*)fused->rot_prep16;
         p.rot_copies = fused->rot_copies;
         // what the append of one token costs its worker, in 32-token tiles (measured; TQ_FUSED_WEIGHT overrides)
-        static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 5;
+        static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 7;
         p.app_weight = app_weight < 0 ? 0 : app_weight;
         p.kv_dim = num_kv_heads * HEAD_DIM; p.capacity_rows = max_seq_len;
     }
