@@ -537,6 +537,16 @@ void tq_engine_destroy(tq_engine* e) {
     if (e->d_rotation_prep) cudaFree(e->d_rotation_prep);
     if (e->d_rotation_prep16) cudaFree(e->d_rotation_prep16);
     if (e->d_rotation_rep) cudaFree(e->d_rotation_rep);
+    if (e->st_in) {
+        cudaStreamDestroy(e->st_in);
+        cudaStreamDestroy(e->st_out);
+        cudaEventDestroy(e->ev_begin);
+        cudaEventDestroy(e->ev_done);
+        for (int c = 0; c < tq_engine::HOST_STEP_CHUNKS; ++c) {
+            cudaEventDestroy(e->ev_in[c]);
+            cudaEventDestroy(e->ev_out[c]);
+        }
+    }
     delete e;
 }
 
@@ -869,15 +879,49 @@ int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_h
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     const int NL = e->shape.num_layers;
     const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
-    TQ_CUDA(cudaMemcpyAsync(e->stage_q, q_host, qb * NL, cudaMemcpyHostToDevice, cs(s)));
-    TQ_CUDA(cudaMemcpyAsync(e->stage_k, k_host, kb * NL, cudaMemcpyHostToDevice, cs(s)));
-    TQ_CUDA(cudaMemcpyAsync(e->stage_v, v_host, kb * NL, cudaMemcpyHostToDevice, cs(s)));
-    for (int l = 0; l < NL; ++l) {
-        int r = tq_engine_decode_layer(e, l, (char*)e->stage_q + qb * l, (char*)e->stage_k + kb * l,
-                                       (char*)e->stage_v + kb * l, (char*)e->stage_out + qb * l, s);
-        if (r != TQ_OK) return r;
+    // The layers go in a few groups: the inputs of group c+1 are copied in (and the outputs of group c-1 copied out)
+    // on two copy streams while the kernels of group c run on the caller's stream.
+    constexpr int NC = tq_engine::HOST_STEP_CHUNKS;
+    if (!e->st_in) {
+        TQ_CUDA(cudaStreamCreateWithFlags(&e->st_in, cudaStreamNonBlocking));
+        TQ_CUDA(cudaStreamCreateWithFlags(&e->st_out, cudaStreamNonBlocking));
+        TQ_CUDA(cudaEventCreateWithFlags(&e->ev_begin, cudaEventDisableTiming));
+        TQ_CUDA(cudaEventCreateWithFlags(&e->ev_done, cudaEventDisableTiming));
+        for (int c = 0; c < NC; ++c) {
+            TQ_CUDA(cudaEventCreateWithFlags(&e->ev_in[c], cudaEventDisableTiming));
+            TQ_CUDA(cudaEventCreateWithFlags(&e->ev_out[c], cudaEventDisableTiming));
+        }
     }
-    TQ_CUDA(cudaMemcpyAsync(out_host, e->stage_out, qb * NL, cudaMemcpyDeviceToHost, cs(s)));
+    const int chunks = NL < NC ? NL : NC;
+    auto first_layer = [&](int c) { return (int)((long long)c * NL / chunks); };
+    TQ_CUDA(cudaEventRecord(e->ev_begin, cs(s)));  // the staging buffers are free once earlier work on s is done
+    TQ_CUDA(cudaStreamWaitEvent(e->st_in, e->ev_begin, 0));
+    for (int c = 0; c < chunks; ++c) {
+        const int l0 = first_layer(c), n = first_layer(c + 1) - l0;
+        TQ_CUDA(cudaMemcpyAsync((char*)e->stage_q + qb * l0, (const char*)q_host + qb * l0, qb * n, cudaMemcpyHostToDevice, e->st_in));
+        TQ_CUDA(cudaMemcpyAsync((char*)e->stage_k + kb * l0, (const char*)k_host + kb * l0, kb * n, cudaMemcpyHostToDevice, e->st_in));
+        TQ_CUDA(cudaMemcpyAsync((char*)e->stage_v + kb * l0, (const char*)v_host + kb * l0, kb * n, cudaMemcpyHostToDevice, e->st_in));
+        TQ_CUDA(cudaEventRecord(e->ev_in[c], e->st_in));
+    }
+    for (int c = 0; c < chunks; ++c) {
+        const int l0 = first_layer(c), l1 = first_layer(c + 1);
+        TQ_CUDA(cudaStreamWaitEvent(cs(s), e->ev_in[c], 0));
+        for (int l = l0; l < l1; ++l) {
+            int r = tq_engine_decode_layer(e, l, (char*)e->stage_q + qb * l, (char*)e->stage_k + kb * l,
+                                           (char*)e->stage_v + kb * l, (char*)e->stage_out + qb * l, s);
+            if (r != TQ_OK) {
+                cudaStreamSynchronize(e->st_in);
+                cudaStreamSynchronize(cs(s));
+                return r;
+            }
+        }
+        TQ_CUDA(cudaEventRecord(e->ev_out[c], cs(s)));
+        TQ_CUDA(cudaStreamWaitEvent(e->st_out, e->ev_out[c], 0));
+        TQ_CUDA(cudaMemcpyAsync((char*)out_host + qb * l0, (char*)e->stage_out + qb * l0, qb * (l1 - l0), cudaMemcpyDeviceToHost,
+                                e->st_out));
+    }
+    TQ_CUDA(cudaEventRecord(e->ev_done, e->st_out));
+    TQ_CUDA(cudaStreamWaitEvent(cs(s), e->ev_done, 0));
     TQ_CUDA(cudaStreamSynchronize(cs(s)));
     return TQ_OK;
 }

@@ -363,6 +363,11 @@ struct tq_engine {
     void* stage_k = nullptr;   // [layers][G][kv_dim]
     void* stage_v = nullptr;
     void* stage_out = nullptr; // [layers][G][q_dim]
+    // host-buffer steps: copy streams and events that let the copies of one group of layers overlap the kernels of another
+    static constexpr int HOST_STEP_CHUNKS = 7;
+    cudaStream_t st_in = nullptr, st_out = nullptr;
+    cudaEvent_t ev_begin = nullptr, ev_done = nullptr;
+    cudaEvent_t ev_in[HOST_STEP_CHUNKS] = {}, ev_out[HOST_STEP_CHUNKS] = {};
 
     // rotation: host copy kept across sleep, device copies (R and R transposed, 32 KB each) outside the arena
     std::vector<uint16_t> h_rotation;
