@@ -326,7 +326,8 @@ def run_ours(args, w, rank, world, local_rank):
         "pct_of_8TBs": 100.0 * value / world / 8000.0,
         "append_tokens_per_s": tokens_per_s,
         "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": int(NL * G * (q_dim + 2 * kv_dim) * 2), "d2h_bytes_per_step": int(NL * G * q_dim * 2)},
+                "h2d_bytes_per_step": int(world * NL * G * (q_dim + 2 * kv_dim) * 2),
+                "d2h_bytes_per_step": int(world * NL * G * q_dim * 2)},
         "gpu_launches": int(args.steps * NL * (1 if fused else 2)),
         "roofline": {"kernel": f"decode_attention_kernel<{bits}>" + (" (fused: append + query rotation + attention)" if fused else ""),
                      "bound": "hbm", "achieved": achieved, "peak": peak,
@@ -342,9 +343,12 @@ def run_ours(args, w, rank, world, local_rank):
     print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per attention launch from the committed ncu capture (profiles/), or
-# None while no capture of that workload exists.
-TRAFFIC = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed ncu capture
+# (profiles/; the per-layer shape of c1 was captured on the 4-layer workload c1l4), or None while no capture exists.
+TRAFFIC = {
+    # profiles/decode_attention_kernel_4bit_fused_c1_layer.md: 281.74 MB read + 5.28 MB written for one layer-step launch
+    "c1": 287024640, "c1l4": 287024640,
+}
 
 
 def main():
