@@ -333,7 +333,7 @@ def run_ours(args, w, rank, world, local_rank):
                      "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "us_per_launch": attn_ms * 1e3, "algorithmic_bytes_per_launch": kernel_bytes,
-                     "traffic": TRAFFIC.get(args.workload)},
+                     "traffic": TRAFFIC.get(args.workload if fused else args.workload + "/unfused")},
         "clocks": clocks,
     }
     if args.cpu_seconds > 0 and world == 1:
@@ -348,6 +348,8 @@ def run_ours(args, w, rank, world, local_rank):
 TRAFFIC = {
     # profiles/decode_attention_kernel_4bit_fused_c1_layer.md: 281.74 MB read + 5.28 MB written for one layer-step launch
     "c1": 287024640, "c1l4": 287024640,
+    # profiles/decode_attention_kernel_4bit_unfused_c1_layer.md (TQ_FUSED=0): 278.32 MB read + 4.51 MB written
+    "c1/unfused": 282830592, "c1l4/unfused": 282830592,
 }
 
 
