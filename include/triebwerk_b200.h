@@ -193,6 +193,12 @@ int tq_engine_create(const tq_model_shape* shape, int max_seq_len, int kv_bits, 
 void tq_engine_destroy(tq_engine* e);
 int tq_engine_kv_bits(const tq_engine* e);
 
+/* Packed modes: choose between ONE launch per layer and step (on = 1, the default: the attention kernel also appends
+ * the new token and rotates the queries) and the two-launch form (on = 0: append kernel, then attention kernel).
+ * Both store identical bytes.  Returns the previous setting, or a negative status.  The environment variable
+ * TQ_FUSED=0 makes the two-launch form the default of new engines.  No counterpart in the reference. */
+int tq_engine_set_fused(tq_engine* e, int on);
+
 /* Bytes of arena needed for G sequences.  capacities == NULL: dense slots of max_seq_len rows each (the
  * reference's layout, row(g) = g*max_seq_len).  Otherwise sequence g gets capacities[g] rows (rounded up
  * to 32) and row(g) is the running sum. */

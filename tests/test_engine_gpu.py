@@ -226,3 +226,79 @@ def test_full_size_layer_properties():
         ref, _ = tqo.attention_single(gu.host(q[g]), cq, vq, cn, vn, R, L - 1, L, H, Hkv, D, bits)
         w, r = hp.assert_attention_close(out[g][None], ref[None], H, D, f"full-size sequence {g}")
         print(f"full-size sequence {g}: max-abs {w:.2e}, rel {r:.2e}")
+
+
+@pytest.mark.parametrize("bits,H,Hkv", [(4, 16, 8), (2, 32, 8), (4, 16, 4)])
+def test_fused_and_two_launch_forms_store_the_same_bytes(bits, H, Hkv):
+    """One launch per layer-step (append + query rotation + attention in the attention kernel) against the
+    two-launch form on the same ragged batch: identical cache bytes and norms after every step, outputs equal up
+    to the order of the fp32 sums (the query rotation runs on the tensor cores in one form, as an fp32 chain in
+    the other).  Several steps, so that new tokens cross tile boundaries and land in freshly started tiles."""
+    D, NL = 128, 2
+    kv_dim, q_dim = Hkv * D, H * D
+    lengths = [130, 1, 31, 700, 33, 256, 95]
+    G = len(lengths)
+    steps = 4
+    caps = [n + steps + 1 for n in lengths]
+    rng = np.random.default_rng(7)
+    engines = []
+    for fused in (True, False):
+        eng = tq.Engine(1024, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+        eng.alloc_batch(G, 1024, caps)
+        assert eng.set_fused(fused) in (True, False)
+        engines.append(eng)
+    for layer in range(NL):
+        for g, n in enumerate(lengths):
+            k = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            v = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            for eng in engines:
+                eng.prefill_append(layer, g, k, v, 0)
+    for eng in engines:
+        eng.set_positions(lengths)
+    for step in range(steps):
+        q = torch.from_numpy(rng.standard_normal((NL, G, q_dim), dtype=np.float32).astype(np.float16)).cuda()
+        k = torch.from_numpy(rng.standard_normal((NL, G, kv_dim), dtype=np.float32).astype(np.float16)).cuda()
+        v = torch.from_numpy(rng.standard_normal((NL, G, kv_dim), dtype=np.float32).astype(np.float16)).cuda()
+        outs = []
+        for eng in engines:
+            out = torch.empty_like(q)
+            eng.decode_step(q, k, v, out)
+            outs.append(out.cpu().numpy())
+            assert eng.status() == 0
+        for layer in range(NL):
+            a, b = engines[0].layer_cache(layer), engines[1].layer_cache(layer)
+            for x, y, name in zip(a, b, ("k codes", "v codes", "k norms", "v norms")):
+                assert torch.equal(x.view(torch.uint8), y.view(torch.uint8)), f"step {step} layer {layer}: {name} differ"
+        hp.assert_attention_close(outs[0].reshape(NL * G, q_dim), outs[1].reshape(NL * G, q_dim), H, D,
+                                  f"bits={bits} step {step}: fused against two-launch")
+        for eng in engines:
+            eng.advance()
+
+
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("bits", [4, 2])
+def test_four_kv_heads_long_context_against_oracle(bits, fused):
+    """4 KV heads make the stages small enough for a ring of four, and a context long enough that every worker
+    streams several tiles walks that whole ring (stage addresses, parities, swizzle alignment of every stage)."""
+    H, Hkv, D = 16, 4, 128
+    kv_dim, q_dim = Hkv * D, H * D
+    n, msl = 12000, 12032
+    rng = np.random.default_rng(11)
+    R = tq.ops.rotation_matrix().numpy()
+    eng = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(1, msl)
+    eng.set_fused(fused)
+    k = rng.standard_normal((n + 1, kv_dim), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((n + 1, kv_dim), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((1, 1, q_dim), dtype=np.float32).astype(np.float16)
+    eng.prefill_append(0, 0, gu.dev(k[:-1]), gu.dev(v[:-1]), 0)
+    eng.set_positions([n])
+    out = torch.empty(1, 1, q_dim, dtype=torch.float16, device="cuda")
+    eng.decode_step(gu.dev(q), gu.dev(k[-1:].reshape(1, 1, kv_dim)), gu.dev(v[-1:].reshape(1, 1, kv_dim)), out)
+    assert eng.status() == 0
+    cq, cn = tqo.alloc_cache(1, n + 1, Hkv, D, bits)
+    vq, vn = tqo.alloc_cache(1, n + 1, Hkv, D, bits)
+    tqo.append_tokens(cq, cn, k, R, np.arange(n + 1, dtype=np.int32), n + 1, Hkv, D, bits)
+    tqo.append_tokens(vq, vn, v, R, np.arange(n + 1, dtype=np.int32), n + 1, Hkv, D, bits)
+    ref, _ = tqo.attention_single(q[0, 0], cq, vq, cn, vn, R, n, n + 1, H, Hkv, D, bits)
+    hp.assert_attention_close(out.cpu().numpy().reshape(1, q_dim), ref[None], H, D, f"bits={bits} fused={fused}")

@@ -20,7 +20,7 @@ SYMBOLS = [
     "launch_gqa_attention_batch", "launch_gqa_attention",
     "tq_rotation_generate", "tq_workspace_bytes", "tq_append_decode", "tq_decode_attention",
     "tq_fp16_append_decode", "tq_fp16_decode_attention", "tq_workspace_status", "tq_decode_attention_static",
-    "tq_engine_create", "tq_engine_destroy", "tq_engine_kv_bits", "tq_engine_arena_bytes", "tq_engine_set_arena",
+    "tq_engine_create", "tq_engine_destroy", "tq_engine_kv_bits", "tq_engine_set_fused", "tq_engine_arena_bytes", "tq_engine_set_arena",
     "tq_engine_alloc_batch", "tq_engine_reset", "tq_engine_sleep", "tq_engine_wake", "tq_engine_positions",
     "tq_engine_set_positions", "tq_engine_advance", "tq_engine_layer_ptrs", "tq_engine_row_base",
     "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append",
@@ -75,6 +75,7 @@ def lib() -> C.CDLL:
     sig("tq_engine_create", i, [C.POINTER(ModelShape), i, i, C.POINTER(vp)])
     sig("tq_engine_destroy", None, [vp])
     sig("tq_engine_kv_bits", i, [vp])
+    sig("tq_engine_set_fused", i, [vp, i])
     sig("tq_engine_arena_bytes", sz, [vp, i, i, C.POINTER(i)])
     sig("tq_engine_set_arena", i, [vp, vp, sz])
     sig("tq_engine_alloc_batch", i, [vp, i, i, C.POINTER(i)])

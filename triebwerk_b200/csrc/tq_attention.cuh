@@ -175,7 +175,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     constexpr uint32_t kvp = (uint32_t)Hkv * Geo::BPH;               // code bytes per token row (all heads)
     constexpr uint32_t code_tile = TILE_TOKENS * kvp;                // one K (or V) tile
     constexpr uint32_t norm_tile = TILE_TOKENS * (uint32_t)Hkv * 2u; // one norm tile
-    constexpr uint32_t stage_bytes = 2u * code_tile + 2u * norm_tile;
+    // a stage starts on a 1024-byte boundary: the 128-byte swizzle of the tensor-map copies goes by the shared address
+    constexpr uint32_t stage_bytes = (2u * code_tile + 2u * norm_tile + 1023u) & ~1023u;
 
     // ---- shared memory map (absolute shared addresses) ----
     const uint32_t dyn_base = smem_u32(dyn_smem);
@@ -187,7 +188,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int s_fit = (int)((n_a + n_b) / ATTN_GROUPS);
     const int S = s_fit >= 4 ? 4 : 2;       // a power of two: stage index and parity are masks and shifts
     const int s_log = s_fit >= 4 ? 2 : 1;
-    if (blocks_a >= LUT_ABS || s_fit < 2 || dyn_end < REGION_B_ABS) {
+    auto stage_addr = [&](int s) -> uint32_t {
+        const uint32_t blk = (uint32_t)(group * S + s);
+        return blk < n_a ? blocks_a + blk * stage_bytes : REGION_B_ABS + (blk - n_a) * stage_bytes;
+    };
+    bool layout_ok = !(blocks_a >= LUT_ABS || s_fit < 2 || dyn_end < REGION_B_ABS);
+    if (FUSED && layout_ok && stage_bytes < 16384u)  // the append borrows stages 0+1 and 2+3 as two 16 KB buffers
+        layout_ok = S >= 4 && 2u * stage_bytes >= 16384u && stage_addr(1) == stage_addr(0) + stage_bytes &&
+                    stage_addr(3) == stage_addr(2) + stage_bytes;
+    if (!layout_ok) {
         if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
         return;
     }
@@ -195,10 +204,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const uint32_t cnt0 = a_base + RegionA::CNT_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 4u);
     const uint32_t ctrl_s = a_base + RegionA::CTRL_OFF + (uint32_t)group * 16u;
     const uint32_t merge_s = a_base + RegionA::MERGE_OFF + (uint32_t)group * RegionA::MERGE_GROUP_BYTES;
-    auto stage_addr = [&](int s) -> uint32_t {
-        const uint32_t blk = (uint32_t)(group * S + s);
-        return blk < n_a ? blocks_a + blk * stage_bytes : REGION_B_ABS + (blk - n_a) * stage_bytes;
-    };
 
     pdl_launch_dependents();
     if (p.debug & 32) { pdl_wait(); return; }
@@ -390,7 +395,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const bool have_app = g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
         if (have_app) {
             const uint32_t abar = a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group;
-            const uint32_t r_lo = stage_addr(0), r_hi = stage_addr(1);  // R[.][k < 64] and R[.][k >= 64], 16 KB each
+            // R[.][k < 64] and R[.][k >= 64], 16 KB each: one stage each, or two adjacent ones when stages are smaller
+            const uint32_t r_lo = stage_addr(0), r_hi = stage_addr(stage_bytes >= 16384u ? 1 : 2);
             if (gtid == 0) {
                 mbar_arrive_expect_tx(abar, 32768u);
                 const __half* rsrc = p.rot_prep16 + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);

@@ -552,6 +552,13 @@ void tq_engine_destroy(tq_engine* e) {
 
 int tq_engine_kv_bits(const tq_engine* e) { return e ? e->kv_bits : TQ_ERR_ARG; }
 
+int tq_engine_set_fused(tq_engine* e, int on) {
+    if (!e) return TQ_ERR_ARG;
+    const int prev = e->fused ? 1 : 0;
+    e->fused = on != 0;
+    return prev;
+}
+
 // One walk of the arena; with base == nullptr it only measures.
 static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long rows, bool ragged, bool assign) {
     size_t off = 0;
@@ -769,9 +776,8 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->d_row_base, e->total_rows, e->msl, e->G,
                                         H, Hkv, D, e->q_dim(), e->kv_dim(), e->workspace, e->ws_bytes, s);
     }
-    // One launch per layer when the batch fits the kernel's shared-memory tile table (TQ_FUSED=0: two launches).
-    static const bool fuse = !(getenv("TQ_FUSED") && atoi(getenv("TQ_FUSED")) == 0);
-    if (fuse && e->G <= FUSED_MAX_G && q && k && v) {
+    // One launch per layer when the batch fits the kernel's shared-memory tile table (tq_engine_set_fused).
+    if (e->fused && e->G <= FUSED_MAX_G) {
         FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES};
         return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
                               e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s),

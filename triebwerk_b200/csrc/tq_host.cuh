@@ -337,6 +337,7 @@ struct tq_engine {
     size_t arena_cap = 0;
     bool arena_external = false;
     bool asleep = false;
+    bool fused = !(getenv("TQ_FUSED") && atoi(getenv("TQ_FUSED")) == 0);  // one launch per layer-step (packed modes)
 
     // current carving
     int G = 0;

@@ -44,6 +44,12 @@ class Engine:
     def kv_bits(self) -> int:
         return int(lib().tq_engine_kv_bits(self._h))
 
+    def set_fused(self, on: bool) -> bool:
+        """One launch per layer and step (default) or the two-launch form; returns the previous setting."""
+        r = int(lib().tq_engine_set_fused(self._h, int(bool(on))))
+        check(min(r, 0), "set_fused")
+        return bool(r)
+
     def reset(self, zero_cache: bool = True) -> None:
         check(lib().tq_engine_reset(self._h, int(zero_cache), self._stream()), "reset")
 
