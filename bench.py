@@ -45,6 +45,8 @@ WORKLOADS = {
                desc="Qwen3-8B shape decode step: 36 layers, 32 seq per GPU x ctx 8192, kv_bits=2"),
     "c1l4": dict(layers=4, H=16, Hkv=8, G=64, L=4096, bits=4, prompt=100,
                  desc="4 of the 28 layers of c1 (same per-layer shape; for profiler captures): 64 seq x ctx 4096, kv_bits=4"),
+    "c2": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=2048, append_only=True,
+               desc="prefill append only (a slice of config 2: 16 of 512 sequences x 2048 tokens, 4 of 28 layers, K and V, kv_bits=4)"),
     "small": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=100,
                   desc="reduced case for profiler captures: 4 layers, 16 seq x ctx 2048, kv_bits=4"),
 }
@@ -228,6 +230,64 @@ def build_engine(w, device_seed):
     return eng, gen, scales
 
 
+def run_append_only(args, w, rank, world, local_rank):
+    """Config 2's shape: whole prompts appended to the packed cache (token-mode append kernel), nothing attended.
+    One step = every sequence's 2048 tokens through the layers of the slice."""
+    import torch
+    import triebwerk_b200 as tq
+    from triebwerk_b200 import synth
+
+    torch.cuda.set_device(local_rank)
+    G, T, H, Hkv, bits, NL = w["G"], w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
+    kv_dim = Hkv * D
+    eng = tq.Engine(T, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, T)
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    kp, vp = synth.torch_kv(gen, T, kv_dim, scales)  # one prompt's K/V, reused for every sequence and layer
+
+    def step():
+        for layer in range(NL):
+            for g in range(G):
+                eng.prefill_append(layer, g, kp, vp, 0)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    steps = max(1, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    assert eng.status() == 0
+    vectors = NL * G * T * 2 * Hkv
+    vpb = 4 if bits == 2 else 2
+    bytes_step = vectors * (256 + D // vpb + 2)
+    peak, peak_kind = measured_peaks()
+    value = bytes_step / (ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 in, tcgen05 f16 hi/lo -> f32 (+ exact f32 chain near bounds), u8 codes", "data": "synthetic",
+        "config": {"workload": w["desc"], "kv_bits": bits, "l2": "every step rewrites %.0f MB of cache" % (vectors * (D // vpb + 2) / 1e6)},
+        "head_vectors_per_s": vectors / (ms * 1e-3),
+        "append_tokens_per_s_28_layers": vectors / (ms * 1e-3) / (28 * 2 * Hkv),
+        "fp32_tflops": vectors * 2 * D * D / (ms * 1e-3) / 1e12,
+        "gpu_launches": steps * NL * G,
+        "roofline": {"kernel": "prefill_append_tc_kernel (tcgen05)", "bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s",
+                     "frac": value / peak, "peak_kind": peak_kind, "traffic": None,
+                     "note": "one call per sequence and layer (2048 tokens = 256 tiles = one wave): launch and set-up bound"},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -375,7 +435,11 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, w, rank, world, local_rank)
+        if w.get("append_only"):
+            if rank == 0:
+                run_append_only(args, w, rank, world, local_rank)
+        else:
+            run_ours(args, w, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -176,3 +176,42 @@ def test_append_equals_reference_kernels_live(bits):
     print(f"tq{bits}: {nbad} of {mq.size} code bytes differ from the live reference kernels over {T * Hkv * D} coordinates")
     assert nbad == 0
     assert (mn.view(np.uint16) == rnh.view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("bits,Hkv,T", [(4, 8, 2048), (2, 8, 1000), (4, 4, 777), (2, 4, 300)])
+def test_tensor_core_prefill_append_equals_the_chain_kernel_and_the_oracle(bits, Hkv, T):
+    """Whole prompts take the tcgen05 kernel (rotation on the tensor cores, exact fp32 chain for coordinates near a
+    decision bound); single tokens take the chain kernel.  Same inputs through both, token by token for the chain
+    kernel: every stored byte must agree, including an all-zero vector (all of its coordinates sit ON the bound 0),
+    huge values, a NaN vector and the ragged last tile; a seeded subset is also checked against the oracle."""
+    import triebwerk_b200 as tq
+    H, D = 16, 128
+    kv_dim = Hkv * D
+    rng = np.random.default_rng(21)
+    k = rng.standard_normal((T, kv_dim), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((T, kv_dim), dtype=np.float32).astype(np.float16)
+    k[3, :D] = 0
+    k[5, D:2 * D] *= np.float16(300.0)
+    v[7, :D] = np.float16(np.nan)
+    v[9, :D] = np.float16(6e-8)  # subnormal inputs
+    msl = T + 32
+    eng_tc = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng_ch = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng_tc.alloc_batch(1, msl)
+    eng_ch.alloc_batch(1, msl)
+    kd, vd = gu.dev(k), gu.dev(v)
+    eng_tc.prefill_append(0, 0, kd, vd, 3)          # one call: T * Hkv >= 512 vectors -> tensor-core kernel
+    step = 32 // Hkv                                 # fewer than 512 vectors per call -> chain kernel
+    for t0 in range(0, T, step):
+        eng_ch.prefill_append(0, 0, kd[t0:t0 + step], vd[t0:t0 + step], 3 + t0)
+    assert eng_tc.status() == 0 and eng_ch.status() == 0
+    for a, b, name in zip(eng_tc.layer_cache(0), eng_ch.layer_cache(0), ("k codes", "v codes", "k norms", "v norms")):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), f"{name} differ between the two kernels"
+    R = tq.ops.rotation_matrix().numpy()
+    n = min(T, 64)
+    cq, cn = tqo.alloc_cache(1, n + 3, Hkv, D, bits)
+    tqo.append_tokens(cq, cn, k[:n], R, np.arange(3, n + 3, dtype=np.int32), n + 3, Hkv, D, bits)
+    got = eng_tc.layer_cache(0)[0].cpu().numpy().reshape(msl, -1)[3:n + 3]
+    ref = cq.reshape(n + 3, -1)[3:n + 3]
+    bad = int((got != ref).sum())
+    assert bad <= hp.ORACLE_ULP_SLACK, f"{bad} packed bytes differ from the oracle"

@@ -15,6 +15,7 @@
 
 #include "../../include/triebwerk_b200.h"
 #include "tq_append.cuh"
+#include "tq_prefill_tc.cuh"
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
 #include "tq_fp16.cuh"
@@ -157,7 +158,33 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
     return launch_kernel(append_rotate_kernel<NV>, grid, dim3(APPEND_THREADS), APPEND_SMEM, s, pdl, p);
 }
 
+// Whole prompts (token form, K and/or V, no queries) go to the tensor-core kernel; TQ_PREFILL_TC=0 keeps them on
+// the fp32-chain kernel.  Both store the same bytes.
+inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s) {
+    static std::map<int, bool> attr_set;  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(prefill_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_DYN_SMEM));
+        attr_set[dev] = true;
+    }
+    PrefillTcParams t{};
+    t.ck = p.ck; t.kn = p.kn; t.cv = p.cv; t.vn = p.vn;
+    t.k_buf = p.k_buf; t.v_buf = p.v_buf; t.rotation = p.rotation; t.positions = p.positions; t.status = p.status;
+    t.token_row0 = p.token_row0; t.capacity_rows = p.capacity_rows;
+    t.T = p.n_src; t.Hkv = p.Hkv; t.kv_dim = p.kv_dim; t.bits = p.bits;
+    const long long tiles = (((long long)p.n_src * p.Hkv + TC_TILE - 1) / TC_TILE) * ((p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0));
+    long long grid = 2ll * device_props().sm_count;
+    if (grid > tiles) grid = tiles;
+    prefill_append_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
+    return cuda_status(cudaGetLastError());
+}
+
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
+    static const bool prefill_tc = !(getenv("TQ_PREFILL_TC") && atoi(getenv("TQ_PREFILL_TC")) == 0);
+    if (prefill_tc && p.token_mode && !p.q && (p.k_buf || p.v_buf) && p.positions &&
+        (long long)p.n_src * p.Hkv >= 4 * TC_TILE && (long long)p.n_src * p.Hkv < (1ll << 31))
+        return launch_prefill_tc(p, s);
     const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
     const long long total = (long long)p.n_src * (nk + nv + nq);
     const bool tables = p.tile_start != nullptr && !p.token_mode;

@@ -1,0 +1,406 @@
+// Prefill append on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// Replaces turbo_kv_quantize_kernel (reference engine/kernels.cu:1482-1560) for whole prompts: T tokens x Hkv heads x
+// {K, V} head vectors are normalised, rotated by R, quantised and packed.  The rotation of many vectors is a GEMM
+// (vectors x 128) . R^T, so it runs as tcgen05.mma (M = 128 vectors, N = 128 coordinates, K = 128) with the
+// accumulators in tensor memory.  Stored bytes must still equal the reference's, whose rotation is a k-ascending fp32
+// FMA chain; the tensor-core sum has another order.  Therefore:
+//   * the normalised vector x (fp32, computed exactly as the reference does) is fed as TWO fp16 operands,
+//     hi = fp16(x) and lo = fp16((x - hi) * 4096), into two accumulators: x.R = hi.R + 2^-12 * lo.R represents x to
+//     2^-23 relative, as good as fp32 itself;
+//   * a coordinate whose value lies within TC_MARGIN of a decision bound is recomputed with the reference's exact
+//     chain (R read back from the shared-memory operand tile, x rebuilt from the input); everywhere else the
+//     two sums cannot fall on different sides of a bound.  TC_MARGIN (1.6e-5) is twice the textbook bound on the
+//     distance of a 128-term fp32 sum from the exact value when sum|r_k x_k| <= 1 (128 * 2^-24 = 7.6e-6; |x| = 1 and
+//     |R row| = 1): once for the chain, once for the tensor-core sum.  About 1 coordinate in 700 takes the exact path.
+// Sums of squares, rsqrt/sqrt and the norm use the reference's own order and instructions (see tq_append.cuh).
+//
+// One CTA = 128 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), two CTAs per SM:
+//   1. thread (vector, 32-coordinate chunk) loads 64 bytes, builds the reference's shuffle-tree sum of squares in
+//      registers, the four chunk sums meet by shuffles; hi/lo go to shared memory in the canonical K-major
+//      128-byte-swizzled operand layout (rows of 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7));
+//   2. one thread issues 16 tcgen05.mma (2 operands x 8 K-steps of 16) against the resident R tile and commits to
+//      an mbarrier; every wait is bounded;
+//   3. each thread reads ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per warp
+//      and instruction), quantises through a 512-bucket uniform grid (bucket -> code, or -> the one bound inside
+//      it), packs, and queues near-bound coordinates;
+//   4. queued coordinates get the exact chain and patch the packed tile; the tile leaves as coalesced 16-byte stores.
+#pragma once
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int TC_TILE = 128;       // head vectors per tile = MMA M
+constexpr int TC_THREADS = 128;
+constexpr float TC_MARGIN = 1.6e-5f;
+constexpr int TC_LIST_CAP = 256;   // queued near-bound coordinates per tile; the rest is handled by their owners
+
+struct TcSmem {
+    static constexpr uint32_t A_HI = 0;                  // 2 K-regions x [128 rows][128 B]
+    static constexpr uint32_t A_LO = 32768;
+    static constexpr uint32_t B_R = 65536;               // R: rows = output coordinate d, K-major
+    static constexpr uint32_t STAGE = 98304;             // packed codes of the tile, 64 B (4-bit) per vector
+    static constexpr uint32_t ROWS = STAGE + 8192;       // long long[128] destination row per vector (-1: none)
+    static constexpr uint32_t INV = ROWS + 1024;         // float[128] 1/norm per vector
+    static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
+    static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint2[512] bucket table: {code | 0x80 + bound index, bound}
+    static constexpr uint32_t CTRL = GRID + 4096;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
+    static constexpr uint32_t BYTES = CTRL + 16;
+};
+constexpr size_t TC_DYN_SMEM = TcSmem::BYTES + 1024;  // + alignment slack
+
+struct PrefillTcParams {
+    uint8_t* ck;
+    __half* kn;
+    uint8_t* cv;
+    __half* vn;
+    const __half* k_buf;       // [T][kv_dim], either may be null
+    const __half* v_buf;
+    const __half* rotation;    // [128][128] row-major
+    const int* positions;      // [T] device
+    int* status;
+    long long token_row0;
+    int capacity_rows;
+    int T, Hkv, kv_dim, bits;
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem]^T, fp16 operands, fp32 accumulate, issued by ONE thread
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread l of the warp receives lane (row) base+l
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart; `addr` is the shared address of the tile (1024-byte aligned) plus 32 bytes per K-step.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu)      // start address
+           | (1ull << 16)                          // leading byte offset (unused with a swizzle)
+           | ((uint64_t)(1024u >> 4) << 32)        // stride byte offset: next group of 8 rows
+           | (1ull << 46)                          // descriptor version of this architecture
+           | (2ull << 61);                         // layout: 128-byte swizzle
+}
+// fp16 x fp16 -> fp32, both operands K-major, M = 128, N = 128
+constexpr uint32_t TC_IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int k) {  // byte address of element (row, k)
+    const uint32_t region = (uint32_t)k >> 6, kk = (uint32_t)k & 63u;
+    return tile + region * 16384u + (uint32_t)row * 128u + ((((kk >> 3) ^ ((uint32_t)row & 7u))) << 4) + (kk & 7u) * 2u;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const PrefillTcParams p) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    const uint32_t base = (smem_u32(tc_smem) + 1023u) & ~1023u;
+    uint8_t* gbase = tc_smem + (base - smem_u32(tc_smem));
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bar = base + TcSmem::CTRL;
+    volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
+    long long* rows_s = reinterpret_cast<long long*>(gbase + TcSmem::ROWS);
+    float* inv_s = reinterpret_cast<float*>(gbase + TcSmem::INV);
+    uint32_t* list_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::LIST);
+    uint2* grid_s = reinterpret_cast<uint2*>(gbase + TcSmem::GRID);
+
+    const int bits = p.bits;
+    const int nb = bits == 4 ? 15 : 3;
+    const int bpv = bits == 4 ? 64 : 32;  // packed bytes per vector
+    const int kvp = p.Hkv * bpv;
+
+    // ---- once per CTA: tensor memory, barrier, R operand tile, bucket table ----
+    if (warp == 0) {
+        tmem_alloc(base + TcSmem::CTRL + 8u, 256u);  // two accumulators of 128 columns
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    for (int c = tid; c < 2048; c += TC_THREADS) {  // R as the B operand: row d, 16-byte chunk j
+        const int d = c >> 4, j = c & 15;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM) + j);
+        *reinterpret_cast<uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base)) = u;
+    }
+    for (int i = tid; i < 512; i += TC_THREADS) {
+        // bucket i = values that round to i - 256 when multiplied by 1024, i.e. [(i - 256.5) / 1024, (i - 255.5) / 1024]
+        // (the first and last bucket extend to infinity).  Entry {base, bound}: code = base + (value >= bound), where
+        // `bound` is the one decision bound within the margin of the bucket, or +inf (then base is the code itself).
+        const float lo = ((float)(i - 256) - 0.5f) * (1.0f / 1024.0f), hi = lo + (1.0f / 1024.0f);
+        int code = 0, amb = -1;
+        float ambv = __int_as_float(0x7f800000);
+        for (int b = 0; b < nb; ++b) {
+            const float bv = bits == 4 ? kBnd4[b] : kBnd2[b];
+            if (bv <= lo) ++code;
+            if (bv >= lo - 4.0f * TC_MARGIN && bv <= hi + 4.0f * TC_MARGIN) { amb = b; ambv = bv; }
+        }
+        grid_s[i] = make_uint2((uint32_t)(amb >= 0 ? amb : code), __float_as_uint(ambv));
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctrl[2];
+
+    const int vec_per_kind = p.T * p.Hkv;
+    const int tiles_per_kind = (vec_per_kind + TC_TILE - 1) / TC_TILE;
+    const int n_kinds = (p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0);
+    const int total_tiles = tiles_per_kind * n_kinds;
+    uint32_t phase = 0;
+    bool dead = false;
+
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
+        const int vec0 = (tile - (kind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
+        const __half* src_buf = kind == 0 ? p.k_buf : p.v_buf;
+        uint8_t* cq = kind == 0 ? p.ck : p.cv;
+        __half* cn = kind == 0 ? p.kn : p.vn;
+        if (tid == 0) ctrl[3] = 0;
+
+        // ---- 1. load, sum of squares in the reference's order, normalise, split, write the A operand ----
+        uint4 raw_all[4][4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {  // every load of the tile goes out before the arithmetic starts
+            const int vid = vec0 + pass * 32 + (tid >> 2);
+            const bool live = vid < vec_per_kind;
+            const int t = live ? vid / p.Hkv : 0, head = live ? vid - t * p.Hkv : 0;
+            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)t * p.kv_dim + (size_t)head * HEAD_DIM + 32 * (tid & 3));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int v = pass * 32 + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
+            const int vid = vec0 + v;
+            const bool live = vid < vec_per_kind;
+            const int t = live ? vid / p.Hkv : 0, head = live ? vid - t * p.Hkv : 0;
+            const uint4 (&raw)[4] = raw_all[pass];
+            float val[32], sq[32];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h2[e]);
+                    val[8 * i + 2 * e] = f.x;
+                    val[8 * i + 2 * e + 1] = f.y;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
+            // the warp-shuffle tree of the reference (offsets 16, 8, 4, 2, 1), element l taking lane l's place
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
+            const float part = sq[0];
+            const int l0 = lane & ~3;
+            const float p0 = __shfl_sync(0xffffffffu, part, l0), p1 = __shfl_sync(0xffffffffu, part, l0 + 1);
+            const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
+            const float tt = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
+            const float inv = rsqrt_approx_ftz(tt);
+            if (c == 0) {
+                long long row = -1;
+                if (live) {
+                    const int pos = p.positions[t];
+                    if (pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows)) {
+                        row = p.token_row0 + pos;
+                        cn[(size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
+                    } else {
+                        atomicMax(p.status, ST_BAD_POSITION);
+                    }
+                }
+                rows_s[v] = row;
+                inv_s[v] = inv;
+            }
+            uint32_t hi_w[16], lo_w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float x0 = mul_ftz(val[2 * i], inv), x1 = mul_ftz(val[2 * i + 1], inv);
+                const __half2 h = __floats2half2_rn(x0, x1);
+                const float2 hf = __half22float2(h);
+                hi_w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                lo_w[i] = pack_half2((x0 - hf.x) * 4096.0f, (x1 - hf.y) * 4096.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {  // 16-byte chunks: coordinates 32c + 8i .. + 7
+                const uint32_t a = tc_operand_addr(base + TcSmem::A_HI, v, 32 * c + 8 * i);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(hi_w[4 * i]), "r"(hi_w[4 * i + 1]),
+                             "r"(hi_w[4 * i + 2]), "r"(hi_w[4 * i + 3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a + (TcSmem::A_LO - TcSmem::A_HI)), "r"(lo_w[4 * i]),
+                             "r"(lo_w[4 * i + 1]), "r"(lo_w[4 * i + 2]), "r"(lo_w[4 * i + 3]) : "memory");
+            }
+        }
+        fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
+        __syncthreads();
+
+        // ---- 2. the rotation: two accumulators (hi and scaled lo), 8 K-steps each ----
+        if (tid == 0 && !dead) {
+            tc_fence_after();
+#pragma unroll
+            for (int op = 0; op < 2; ++op) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t koff = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+                    umma_f16(tmem + (uint32_t)op * 128u, umma_desc_sw128(base + (op ? TcSmem::A_LO : TcSmem::A_HI) + koff),
+                             umma_desc_sw128(base + TcSmem::B_R + koff), TC_IDESC, ks != 0);
+                }
+            }
+            umma_commit(bar);
+        }
+        if (!dead && !mbar_wait_bounded(bar, phase, 1u << 22)) {
+            dead = true;
+            atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+        }
+        dead = __syncthreads_or(dead ? 1 : 0) != 0;
+        phase ^= 1u;
+        tc_fence_after();
+
+        // ---- 3. accumulators -> codes; thread `tid` owns vector `tid` of the tile (TMEM lane tid) ----
+        const int nan_code = bits == 4 ? 15 : 0;  // what the reference's comparisons make of a NaN
+        uint32_t own_cc[4] = {0u, 0u, 0u, 0u};  // near-bound coordinates that did not fit the shared queue
+        if (!dead) {
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t hi_r[32], lo_r[32];
+                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc * 32u;
+                tmem_ld32(taddr, hi_r);
+                tmem_ld32(taddr + 128u, lo_r);
+                tmem_ld_wait();
+                uint32_t words[4] = {0u, 0u, 0u, 0u};
+                uint32_t near_mask = 0u;  // queued after the loop: no store may sit between the table look-ups
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float dval = fmaf(__uint_as_float(lo_r[i]), 1.0f / 4096.0f, __uint_as_float(hi_r[i]));
+                    // branch-free: round(value * 1024) by the 1.5 * 2^23 trick, clamped to the table (values beyond
+                    // the table are beyond every bound; huge values and infinities land on the right end as well)
+                    const float tt = fmaf(dval, 1024.0f, 12582912.0f);
+                    int idx = __float_as_int(tt) - 0x4B400000 + 256;
+                    idx = max(0, min(511, idx));
+                    const uint2 e = grid_s[idx];
+                    const float bv = __uint_as_float(e.y);
+                    int code = (int)e.x + (dval >= bv ? 1 : 0);
+                    code = (dval != dval) ? nan_code : code;
+                    near_mask |= (fabsf(dval - bv) < TC_MARGIN ? 1u : 0u) << i;
+                    if (bits == 4) words[i >> 3] |= (uint32_t)code << (4 * (i & 7));
+                    else words[i >> 4] |= (uint32_t)code << (2 * (i & 15));
+                }
+                while (near_mask) {
+                    const int i = __ffs(near_mask) - 1;
+                    near_mask &= near_mask - 1;
+                    const uint32_t slot = atomicAdd(const_cast<uint32_t*>(&ctrl[3]), 1u);
+                    if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)tid << 8) | (uint32_t)(32 * cc + i);
+                    else own_cc[cc] |= 1u << i;
+                }
+                uint8_t* st = gbase + TcSmem::STAGE + (size_t)tid * bpv;
+                if (bits == 4) *reinterpret_cast<uint4*>(st + 16 * cc) = make_uint4(words[0], words[1], words[2], words[3]);
+                else *reinterpret_cast<uint2*>(st + 8 * cc) = make_uint2(words[0], words[1]);
+            }
+        }
+        tc_fence_before();  // the tensor-memory reads are done before the next tile's mma overwrites the accumulators
+        __syncthreads();
+
+        // ---- 4. exact chain for the queued coordinates, patch the packed tile ----
+        auto exact_code = [&](int v, int d) -> int {
+            const int vid = vec0 + v;
+            const int t = vid / p.Hkv, head = vid - t * p.Hkv;
+            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)t * p.kv_dim + (size_t)head * HEAD_DIM);
+            const float inv = inv_s[v];
+            uint4 xall[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) xall[j] = __ldg(src + j);
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint4 xv = xall[j];
+                const uint4 rv = *reinterpret_cast<const uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base));
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                    acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
+                    acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+                }
+            }
+            return quantize_code(acc, bits);
+        };
+        auto patch = [&](int v, int d, int code) {
+            uint32_t* w = reinterpret_cast<uint32_t*>(gbase + TcSmem::STAGE + (size_t)v * bpv) + (bits == 4 ? d >> 3 : d >> 4);
+            const int sh = bits == 4 ? 4 * (d & 7) : 2 * (d & 15);
+            const uint32_t m = (bits == 4 ? 0xfu : 0x3u) << sh;
+            atomicAnd(w, ~m);
+            atomicOr(w, (uint32_t)code << sh);
+        };
+        if (!dead) {
+            const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
+            for (uint32_t i = tid; i < queued; i += TC_THREADS) {
+                const uint32_t item = list_s[i];
+                const int v = (int)(item >> 8), d = (int)(item & 255u);
+                if (vec0 + v < vec_per_kind) patch(v, d, exact_code(v, d));
+            }
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t m = own_cc[cc];
+                while (m) {
+                    const int i = __ffs(m) - 1;
+                    m &= m - 1;
+                    if (vec0 + tid < vec_per_kind) patch(tid, 32 * cc + i, exact_code(tid, 32 * cc + i));
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- 5. the packed tile leaves as 16-byte stores; the heads of a token are contiguous in the cache ----
+        if (!dead) {
+            const int chunks_per_vec = bpv / 16;
+            for (int c16 = tid; c16 < TC_TILE * chunks_per_vec; c16 += TC_THREADS) {
+                const int v = c16 / chunks_per_vec, part = c16 - v * chunks_per_vec;
+                const long long row = rows_s[v];
+                if (row >= 0) {
+                    const int head = (vec0 + v) % p.Hkv;
+                    const uint4 u = *reinterpret_cast<const uint4*>(gbase + TcSmem::STAGE + (size_t)v * bpv + 16 * part);
+                    *reinterpret_cast<uint4*>(cq + (size_t)row * kvp + (size_t)head * bpv + 16 * part) = u;
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256u);
+}
+
+}  // namespace tq
