@@ -47,6 +47,9 @@ WORKLOADS = {
                  desc="4 of the 28 layers of c1 (same per-layer shape; for profiler captures): 64 seq x ctx 4096, kv_bits=4"),
     "c2": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=2048, append_only=True,
                desc="prefill append only (a slice of config 2: 16 of 512 sequences x 2048 tokens, 4 of 28 layers, K and V, kv_bits=4)"),
+    "c4": dict(layers=36, H=32, Hkv=8, G=128, L=16384, bits=4, prompt=100, ragged=True,
+               desc="Qwen3-8B shape, ragged decode step: 36 layers, one GPU's share (LPT by tokens, 1 of 8) of 1024 sequences with "
+                    "context ~ U{128..16384}, kv_bits=4"),
     "small": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=100,
                   desc="reduced case for profiler captures: 4 layers, 16 seq x ctx 2048, kv_bits=4"),
 }
@@ -54,12 +57,22 @@ D = 128
 METRIC = "decode-attn HBM GB/s over 4-bit KV (% of ~8 TB/s); append tokens/s"
 
 
+def ragged_lengths(w, rank):
+    """Config 4's contexts: 1024 lengths ~ U{128..16384} from default_rng(0), split over 8 GPUs by longest-processing-
+    time on tokens; this rank's share."""
+    from triebwerk_b200.partition import lpt_partition
+    lengths = np.random.default_rng(0).integers(128, 16385, size=1024)
+    share = lpt_partition([int(x) for x in lengths], 8)[rank % 8]
+    return [int(lengths[i]) for i in share]
+
+
 def algorithmic_bytes(w, attention_only=False):
     """Bytes one step must move, per GPU: every cache byte of the context once (GQA sharing does not count
     twice), q in / out out, R once per layer; plus, for the append, the new K/V vectors in and codes+norm out."""
     vpb = 4 if w["bits"] == 2 else 2
     kvp = w["Hkv"] * D // vpb
-    per_layer_attn = w["G"] * w["L"] * (2 * kvp + 4 * w["Hkv"]) + 4 * w["G"] * w["H"] * D + 32768
+    tokens = sum(w["lengths"]) if "lengths" in w else w["G"] * w["L"]
+    per_layer_attn = tokens * (2 * kvp + 4 * w["Hkv"]) + 4 * w["G"] * w["H"] * D + 32768
     per_vec = 256 + D // vpb + 2
     per_layer_append = w["G"] * w["Hkv"] * 2 * per_vec
     if attention_only:
@@ -213,9 +226,23 @@ def build_engine(w, device_seed):
     G, L, H, Hkv, bits, NL = w["G"], w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
     kv_dim = Hkv * D
     eng = tq.Engine(L, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
-    eng.alloc_batch(G, L)
     gen = torch.Generator(device="cuda").manual_seed(device_seed)
     scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    if w.get("ragged"):
+        # per-sequence slots: the arena holds the sum of the contexts, not G x the longest one
+        lengths = w["lengths"]
+        eng.alloc_batch(G, L, lengths)
+        pool_k, pool_v = synth.torch_kv(gen, L, kv_dim, scales)  # one random pool, sliced per sequence and layer
+        for layer in range(NL):
+            for g, n in enumerate(lengths):
+                off = (37 * layer + 101 * g) % 64
+                if n > 1:
+                    eng.prefill_append(layer, g, pool_k[off:off + n - 1] if off + n - 1 <= L else pool_k[:n - 1],
+                                       pool_v[off:off + n - 1] if off + n - 1 <= L else pool_v[:n - 1], 0)
+        eng.set_positions([n - 1 for n in lengths])
+        torch.cuda.synchronize()
+        return eng, gen, scales
+    eng.alloc_batch(G, L)
     prompt = w["prompt"]
     # The cache is produced by the library's own append (prefill form), not filled with random bytes.
     for layer in range(NL):
@@ -295,6 +322,9 @@ def run_ours(args, w, rank, world, local_rank):
     from triebwerk_b200 import synth
 
     torch.cuda.set_device(local_rank)
+    if w.get("ragged"):
+        w = dict(w, lengths=ragged_lengths(w, rank))
+        w["G"] = len(w["lengths"])
     G, L, H, Hkv, bits, NL = w["G"], w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
     kv_dim, q_dim = Hkv * D, H * D
     eng, gen, scales = build_engine(w, 1234 + rank)
@@ -380,7 +410,7 @@ def run_ours(args, w, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 codes, f16 mma, f32 accumulate", "data": "synthetic",
-        "config": {"workload": w["desc"], "kv_bits": bits, "sequences_per_gpu": G, "context": L, "layers": NL,
+        "config": {"workload": w["desc"], "kv_bits": bits, "sequences_per_gpu": G, "context": L if "lengths" not in w else "ragged, %d tokens" % sum(w["lengths"]), "layers": NL,
                    "l2": "inputs larger than L2 (one layer's cache is %.0f MB, 126 MB L2)" % (attn_bytes / 1e6),
                    "parallelism": f"sequence-sharded x{world}" if world > 1 else "1 GPU"},
         "pct_of_8TBs": 100.0 * value / world / 8000.0,
