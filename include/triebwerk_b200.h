@@ -263,6 +263,13 @@ int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void
 int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos,
                              int T, tq_stream_t s);
 
+/* The same for n_seq consecutive sequences (first_seq, first_seq + 1, ...) in ONE launch: k, v are
+ * [n_seq][T][kv_dim], every sequence receives its T tokens at positions first_pos .. first_pos + T - 1.  The reference
+ * prefills one sequence and copies its cache to the others (engine/engine.cpp:2173-2214); this entry point is for
+ * batches of different prompts of equal (padded) length.  No counterpart in the reference. */
+int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v,
+                                   int first_pos, int T, tq_stream_t s);
+
 /* A whole decode step from HOST buffers: q_host [layers][G][q_dim], k_host/v_host [layers][G][kv_dim],
  * out_host [layers][G][q_dim], fp16, ideally pinned.  Copies the inputs in, runs every layer, copies the
  * outputs back and waits.  This is the end-to-end call bench.py times. */

@@ -215,3 +215,31 @@ def test_tensor_core_prefill_append_equals_the_chain_kernel_and_the_oracle(bits,
     ref = cq.reshape(n + 3, -1)[3:n + 3]
     bad = int((got != ref).sum())
     assert bad <= hp.ORACLE_ULP_SLACK, f"{bad} packed bytes differ from the oracle"
+
+
+@pytest.mark.parametrize("bits,ragged", [(4, False), (2, True)])
+def test_batched_prefill_append_equals_per_sequence_calls(bits, ragged):
+    """Several prompts in one launch (tensor-core kernel over [n_seq][T][kv_dim]) against one call per sequence: the same
+    bytes in every slot, dense and per-sequence (ragged) slots, at a non-zero first position, leaving the neighbouring
+    sequences untouched."""
+    import triebwerk_b200 as tq
+    H, Hkv, D, T, G = 16, 8, 128, 70, 5
+    kv_dim = Hkv * D
+    rng = np.random.default_rng(3)
+    k = gu.dev(rng.standard_normal((3, T, kv_dim), dtype=np.float32).astype(np.float16))
+    v = gu.dev(rng.standard_normal((3, T, kv_dim), dtype=np.float32).astype(np.float16))
+    caps = [200, 90, 100, 96, 300] if ragged else None
+    engines = []
+    for _ in range(2):
+        e = tq.Engine(320, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+        e.alloc_batch(G, 320, caps)
+        engines.append(e)
+    engines[0].prefill_append_batch(0, 1, k, v, 9)
+    for i in range(3):
+        engines[1].prefill_append(0, 1 + i, k[i], v[i], 9)
+    assert engines[0].status() == 0 and engines[1].status() == 0
+    for a, b, name in zip(engines[0].layer_cache(0), engines[1].layer_cache(0), ("k codes", "v codes", "k norms", "v norms")):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), f"{name} differ"
+    assert int(engines[0].layer_cache(0)[0].view(torch.uint8).ne(0).sum()) > 0
+    with pytest.raises(tq.TqError):
+        engines[0].prefill_append_batch(0, 3, k, v, 0)  # sequences 3, 4, 5: one too many

@@ -23,7 +23,7 @@ SYMBOLS = [
     "tq_engine_create", "tq_engine_destroy", "tq_engine_kv_bits", "tq_engine_set_fused", "tq_engine_arena_bytes", "tq_engine_set_arena",
     "tq_engine_alloc_batch", "tq_engine_reset", "tq_engine_sleep", "tq_engine_wake", "tq_engine_positions",
     "tq_engine_set_positions", "tq_engine_advance", "tq_engine_layer_ptrs", "tq_engine_row_base",
-    "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append",
+    "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append", "tq_engine_prefill_append_batch",
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
 ]
 
@@ -91,6 +91,7 @@ def lib() -> C.CDLL:
     sig("tq_engine_set_rotation", i, [vp, vp, vp])
     sig("tq_engine_decode_layer", i, [vp, i, vp, vp, vp, vp, vp])
     sig("tq_engine_prefill_append", i, [vp, i, i, vp, vp, i, i, vp])
+    sig("tq_engine_prefill_append_batch", i, [vp, i, i, i, vp, vp, i, i, vp])
     sig("tq_engine_decode_step_host", i, [vp, vp, vp, vp, vp, vp])
     sig("tq_engine_attend_layer", i, [vp, i, vp, vp])
     sig("tq_engine_decode_step", i, [vp, vp, vp, vp, vp, vp])

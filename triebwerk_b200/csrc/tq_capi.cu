@@ -1,6 +1,8 @@
 // extern "C" surface of libtriebwerk_b200.so (declared in include/triebwerk_b200.h).
 // The whole library is this one translation unit; kernels live in the .cuh files it includes.
 
+#include <algorithm>
+
 #include "tq_host.cuh"
 
 using namespace tq;
@@ -834,21 +836,29 @@ __global__ void iota_from_kernel(int* pos, int n, int first) {
     if (i < n) pos[i] = first + i;
 }
 
-int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos, int T,
-                             tq_stream_t s) {
-    if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0) return TQ_ERR_ARG;
+// Prompts of n_seq consecutive sequences (first_seq ..), all T tokens long and all at positions first_pos ..; inputs
+// [n_seq][T][kv_dim].  One launch.
+static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v, int first_pos,
+                               int T, tq_stream_t s) {
+    if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0 || n_seq <= 0) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
-    if (seq < 0 || seq >= e->G) return TQ_ERR_ARG;
-    const int cap = e->ragged ? e->capacities[seq] : e->msl;
+    if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;
+    int cap = e->msl;
+    if (e->ragged) {
+        cap = e->capacities[first_seq];
+        for (int i = 1; i < n_seq; ++i) cap = std::min(cap, e->capacities[first_seq + i]);
+    }
     if (first_pos + T > cap) return TQ_ERR_CAPACITY;
-    const long long row0 = e->ragged ? e->h_row_base[seq] : (long long)seq * e->msl;
     const tq_engine::Layer& L = e->layers[layer];
     if (e->kv_bits == 0) {
         const size_t row_bytes = (size_t)e->kv_dim() * 2;
-        TQ_CUDA(cudaMemcpyAsync((char*)L.k + (size_t)(row0 + first_pos) * row_bytes, k, (size_t)T * row_bytes,
-                                cudaMemcpyDeviceToDevice, cs(s)));
-        TQ_CUDA(cudaMemcpyAsync((char*)L.v + (size_t)(row0 + first_pos) * row_bytes, v, (size_t)T * row_bytes,
-                                cudaMemcpyDeviceToDevice, cs(s)));
+        for (int i = 0; i < n_seq; ++i) {
+            const long long row0 = e->ragged ? e->h_row_base[first_seq + i] : (long long)(first_seq + i) * e->msl;
+            TQ_CUDA(cudaMemcpyAsync((char*)L.k + (size_t)(row0 + first_pos) * row_bytes, (const char*)k + (size_t)i * T * row_bytes,
+                                    (size_t)T * row_bytes, cudaMemcpyDeviceToDevice, cs(s)));
+            TQ_CUDA(cudaMemcpyAsync((char*)L.v + (size_t)(row0 + first_pos) * row_bytes, (const char*)v + (size_t)i * T * row_bytes,
+                                    (size_t)T * row_bytes, cudaMemcpyDeviceToDevice, cs(s)));
+        }
         return TQ_OK;
     }
     // token form: positions are first_pos + t; pass them by value through a per-token iota kept in a scratch
@@ -863,6 +873,7 @@ int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, co
     iota_from_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(d_iota, T, first_pos);
     int r = cuda_status(cudaGetLastError());
     if (r != TQ_OK) return r;
+    const long long row0 = e->ragged ? e->h_row_base[first_seq] : (long long)first_seq * e->msl;
     // the append kernel only needs the header of the workspace here (status word)
     AppendParams p{};
     p.ck = (uint8_t*)L.k; p.kn = (__half*)L.kn; p.cv = (uint8_t*)L.v; p.vn = (__half*)L.vn;
@@ -876,7 +887,20 @@ int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, co
     p.max_seq_len = e->msl; p.capacity_rows = cap;
     p.n_src = T; p.H = e->shape.num_heads; p.Hkv = e->shape.num_kv_heads; p.q_dim = e->q_dim(); p.kv_dim = e->kv_dim();
     p.bits = e->kv_bits; p.pos_value = 0;
-    return launch_append(p, cs(s));
+    if (n_seq == 1) return launch_append(p, cs(s));
+    if ((long long)n_seq * T * p.Hkv >= (1ll << 31)) return TQ_ERR_CAPACITY;
+    // several sequences: the tensor-core kernel takes them in one launch (whatever their number of head vectors)
+    return launch_prefill_tc(p, cs(s), n_seq, e->msl, e->ragged ? e->d_row_base + first_seq : nullptr);
+}
+
+int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos, int T,
+                             tq_stream_t s) {
+    return engine_prefill_impl(e, layer, seq, 1, k, v, first_pos, T, s);
+}
+
+int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v,
+                                   int first_pos, int T, tq_stream_t s) {
+    return engine_prefill_impl(e, layer, first_seq, n_seq, k, v, first_pos, T, s);
 }
 
 int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_host, const void* v_host, void* out_host,

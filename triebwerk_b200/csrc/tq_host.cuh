@@ -160,7 +160,8 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
 
 // Whole prompts (token form, K and/or V, no queries) go to the tensor-core kernel; TQ_PREFILL_TC=0 keeps them on
 // the fp32-chain kernel.  Both store the same bytes.
-inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s) {
+inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 1, long long seq_stride_rows = 0,
+                             const long long* seq_row_base = nullptr) {
     static std::map<int, bool> attr_set;  // per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -172,8 +173,9 @@ inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s) {
     t.ck = p.ck; t.kn = p.kn; t.cv = p.cv; t.vn = p.vn;
     t.k_buf = p.k_buf; t.v_buf = p.v_buf; t.rotation = p.rotation; t.positions = p.positions; t.status = p.status;
     t.token_row0 = p.token_row0; t.capacity_rows = p.capacity_rows;
+    t.seq_stride_rows = seq_stride_rows; t.row_base = seq_row_base; t.n_seq = n_seq;
     t.T = p.n_src; t.Hkv = p.Hkv; t.kv_dim = p.kv_dim; t.bits = p.bits;
-    const long long tiles = (((long long)p.n_src * p.Hkv + TC_TILE - 1) / TC_TILE) * ((p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0));
+    const long long tiles = (((long long)n_seq * p.n_src * p.Hkv + TC_TILE - 1) / TC_TILE) * ((p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0));
     long long grid = 2ll * device_props().sm_count;
     if (grid > tiles) grid = tiles;
     prefill_append_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);

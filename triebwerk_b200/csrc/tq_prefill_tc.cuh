@@ -60,8 +60,11 @@ struct PrefillTcParams {
     const __half* rotation;    // [128][128] row-major
     const int* positions;      // [T] device
     int* status;
-    long long token_row0;
+    long long token_row0;      // first cache row of sequence 0 of the call
+    long long seq_stride_rows; // rows between consecutive sequences of the call (when row_base is null)
+    const long long* row_base; // optional: first cache row per sequence, indexed from the call's first sequence
     int capacity_rows;
+    int n_seq;                 // sequences in the call: inputs are [n_seq][T][kv_dim], all at the same positions
     int T, Hkv, kv_dim, bits;
 };
 
@@ -173,7 +176,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
     tc_fence_after();
     const uint32_t tmem = ctrl[2];
 
-    const int vec_per_kind = p.T * p.Hkv;
+    const int vec_per_seq = p.T * p.Hkv;
+    const int vec_per_kind = p.n_seq * vec_per_seq;
     const int tiles_per_kind = (vec_per_kind + TC_TILE - 1) / TC_TILE;
     const int n_kinds = (p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0);
     const int total_tiles = tiles_per_kind * n_kinds;
@@ -194,8 +198,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         for (int pass = 0; pass < 4; ++pass) {  // every load of the tile goes out before the arithmetic starts
             const int vid = vec0 + pass * 32 + (tid >> 2);
             const bool live = vid < vec_per_kind;
-            const int t = live ? vid / p.Hkv : 0, head = live ? vid - t * p.Hkv : 0;
-            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)t * p.kv_dim + (size_t)head * HEAD_DIM + 32 * (tid & 3));
+            const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;  // tok = sequence * T + t
+            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * (tid & 3));
 #pragma unroll
             for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
         }
@@ -204,7 +208,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             const int v = pass * 32 + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
             const int vid = vec0 + v;
             const bool live = vid < vec_per_kind;
-            const int t = live ? vid / p.Hkv : 0, head = live ? vid - t * p.Hkv : 0;
+            const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;
+            const int seq = tok / p.T, t = tok - seq * p.T;
             const uint4 (&raw)[4] = raw_all[pass];
             float val[32], sq[32];
 #pragma unroll
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 if (live) {
                     const int pos = p.positions[t];
                     if (pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows)) {
-                        row = p.token_row0 + pos;
+                        row = (p.row_base ? p.row_base[seq] : p.token_row0 + (long long)seq * p.seq_stride_rows) + pos;
                         cn[(size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
                     } else {
                         atomicMax(p.status, ST_BAD_POSITION);
@@ -334,8 +339,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         // ---- 4. exact chain for the queued coordinates, patch the packed tile ----
         auto exact_code = [&](int v, int d) -> int {
             const int vid = vec0 + v;
-            const int t = vid / p.Hkv, head = vid - t * p.Hkv;
-            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)t * p.kv_dim + (size_t)head * HEAD_DIM);
+            const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
+            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM);
             const float inv = inv_s[v];
             uint4 xall[16];
 #pragma unroll

@@ -140,6 +140,12 @@ class Engine:
         check(lib().tq_engine_prefill_append(self._h, layer, seq, k.data_ptr(), v.data_ptr(), first_pos, k.shape[0],
                                              self._stream()), "prefill_append")
 
+    def prefill_append_batch(self, layer: int, first_seq: int, k: torch.Tensor, v: torch.Tensor, first_pos: int = 0) -> None:
+        """Token-form append of k/v [n_seq, T, kv_dim] for the sequences first_seq .. first_seq + n_seq - 1 in one launch."""
+        assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous() and k.dim() == 3 and k.shape == v.shape
+        check(lib().tq_engine_prefill_append_batch(self._h, layer, first_seq, k.shape[0], k.data_ptr(), v.data_ptr(), first_pos,
+                                                   k.shape[1], self._stream()), "prefill_append_batch")
+
     def decode_step_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
                          out_host: torch.Tensor) -> torch.Tensor:
         """A whole decode step from host (ideally pinned) buffers [layers, G, dim]; returns out_host."""
