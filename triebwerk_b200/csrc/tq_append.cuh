@@ -51,6 +51,7 @@ struct AppendParams {
     int n_src;                   // G (batch mode) or T (token mode)
     int H, Hkv, q_dim, kv_dim, bits;
     int pos_value;               // used when positions == nullptr
+    int qg;                      // > 1: rotated queries are stored for the prefill form of the attention (groups of qg tokens)
 };
 
 // One CTA = APPEND_GROUPS groups of 128 threads around one copy of R in shared memory; thread d of a group owns
@@ -262,7 +263,15 @@ __global__ void __launch_bounds__(APPEND_THREADS) append_rotate_kernel(const App
         for (int v = 0; v < NV; ++v) {
             codes[grp][v][d] = (uint8_t)quantize_code(acc[v], p.bits);
             // log2(e) / sqrt(128): the attention kernel works with exp2 and folds the softmax scale here
-            if (kind[v] == 2) p.q_rot[((size_t)srcid[v] * p.H + head[v]) * HEAD_DIM + d] = acc[v] * 0.12751743074602467f;
+            if (kind[v] == 2) {
+                size_t qrow = (size_t)srcid[v] * p.H + head[v];
+                if (p.qg > 1) {  // row order (group of tokens, kv head, token in group, head of the kv head)
+                    const int grp = p.H / p.Hkv, kvh = head[v] / grp, hq = head[v] - kvh * grp;
+                    const int gq = srcid[v] / p.qg, qi = srcid[v] - gq * p.qg;
+                    qrow = ((size_t)gq * p.Hkv + kvh) * (size_t)(grp * p.qg) + (size_t)qi * grp + hq;
+                }
+                p.q_rot[qrow * HEAD_DIM + d] = acc[v] * 0.12751743074602467f;
+            }
         }
         // destination row and norm of vector v, by thread v of the group
 #pragma unroll

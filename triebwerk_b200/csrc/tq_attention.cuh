@@ -81,6 +81,10 @@ struct AttnParams {
     int kv_dim;
     int capacity_rows;         // rows a sequence may use (position check)
     int app_weight;            // cost of one append in tiles, for the balance of the work list
+    // prefill form: a "sequence" of the launch is a group of qg consecutive query tokens of ONE cache (row base 0); its
+    // H = qg * (real heads) rows are ordered (kv head, token in group, head of the kv head); token t attends to rows 0..t
+    int qg;                    // 0 or 1: plain decode
+    int qg_tokens;             // number of query tokens (the last group may be partial)
     int l2_ahead;              // tiles prefetched into L2 beyond the shared-memory ring
     int debug;                 // measurement switches (TQ_ATTN_DEBUG): bit 0 = skip the math, bit 1 = skip the loads
 };
@@ -567,6 +571,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const long long seg_end = hi < ts_g1 ? hi : ts_g1;
         const int pos = p.positions ? p.positions[g] : p.pos_value;
         const int L = (pos < 0 ? 0 : pos) + 1;
+        // causal limit of this lane's score row (row gl) and of the group's first token; equal to L outside the prefill form
+        const int qg = FUSED ? 0 : p.qg;  // the fused form is a decode step: no token groups
+        const int grp_real = qg > 1 ? grp / qg : grp;
+        const int Lrow = qg > 1 ? min(L, g * qg + gl / grp_real + 1) : L;
+        const int Lmin = qg > 1 ? min(L, g * qg + 1) : L;
 
         // query fragments: lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head  head*grp + gl
         uint32_t qa[8][QSPLIT ? 4 : 2];
@@ -668,7 +677,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
         for (; tile < seg_end; ++tile) {
             const int t0 = (int)(tile - ts_g) * TILE_TOKENS;
-            const bool full = t0 + TILE_TOKENS <= L;  // warp-uniform: no token of the tile is masked
+            const bool full = t0 + TILE_TOKENS <= Lmin;  // warp-uniform: no token of the tile is masked for any row
             const int s = consumed & (S - 1);
             uint32_t token = 0;  // 0 at run time; produced by the wait, so that the tile's loads cannot move above it
             if (!dead && loads_on) {
@@ -730,7 +739,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
-                        if (tok >= L) sv[i] = -1e30f;
+                        if (tok >= Lrow) sv[i] = -1e30f;
                     }
                 }
                 float tmax = fmaxf(fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])), fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7])));
@@ -757,7 +766,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
-                        if (tok >= L) pv[i] = 0.0f;
+                        if (tok >= Lrow) pv[i] = 0.0f;
                     }
                 }
                 l_run += ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
@@ -896,6 +905,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
         if (is_last) {
             const int H = p.H;
+            // where row vh of this sequence's output goes (null: nowhere)
+            auto out_row = [&](int vh) -> __half* {
+                if (vh >= H) return nullptr;
+                if (qg <= 1) return p.out + (size_t)g * p.q_dim + (size_t)vh * HEAD_DIM;
+                const int kvh = vh / grp, r = vh - kvh * grp, qi = r / grp_real, hq = r - qi * grp_real;
+                const int token = g * qg + qi;
+                if (token >= p.qg_tokens) return nullptr;
+                return p.out + (size_t)token * p.q_dim + (size_t)(kvh * grp_real + hq) * HEAD_DIM;
+            };
             for (int hb = 0; hb < H; hb += 16) {
                 // ---- phase A: heads hb .. hb+15, two heads per warp at a time with all their loads in flight
                 //      together: combine the parts, normalise, split into fp16 high + low, store as the A operand
@@ -1011,10 +1029,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                                      bfrag[i][j][0], bfrag[i][j][1]);
                         }
                         const int d = 8 * nb + 2 * t4;
-                        if (hb + gl < H)
-                            *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl) * HEAD_DIM + d) = __floats2half2_rn(c[0], c[1]);
-                        if (hb + gl + 8 < H)
-                            *reinterpret_cast<__half2*>(p.out + (size_t)g * p.q_dim + (size_t)(hb + gl + 8) * HEAD_DIM + d) = __floats2half2_rn(c[2], c[3]);
+                        if (__half* o = out_row(hb + gl))
+                            *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[0], c[1]);
+                        if (__half* o = out_row(hb + gl + 8))
+                            *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[2], c[3]);
                     }
                 }
                 group_barrier(group, gthreads);  // the A operand may be overwritten (next 16 heads, next segment)

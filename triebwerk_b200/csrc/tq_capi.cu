@@ -97,7 +97,7 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
                        const long long* row_base, int token_mode, long long token_row0, int max_seq_len, int n_src,
                        int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
                        size_t workspace_bytes, bool build_tiles, cudaStream_t s, bool pdl = false,
-                       const float* rot_prep = nullptr) {
+                       const float* rot_prep = nullptr, int qg = 0) {
     if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
     if (bits != 2 && bits != 4) return TQ_ERR_ARG;
     if (n_src <= 0 || num_kv_heads <= 0 || kv_dim != num_kv_heads * head_dim || !rotation) return TQ_ERR_ARG;
@@ -124,6 +124,7 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.max_seq_len = max_seq_len; p.capacity_rows = max_seq_len;
     p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
     p.pos_value = pos_value;
+    p.qg = qg;
     return launch_append(p, s, pdl);
 }
 
@@ -152,7 +153,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
                           const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
                           long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
                           int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false,
-                          const FusedInputs* fused = nullptr) {
+                          const FusedInputs* fused = nullptr, int qg = 0, int qg_tokens = 0) {
     FullWorkspace fw = carve_full(workspace, G, num_heads);
     if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
     // bulk copies need 16-byte aligned sources: rows are 512/256 B (codes) and 2*Hkv B (norms, Hkv % 4 == 0 -> 8|16 B)
@@ -169,6 +170,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     p.total_rows = total_rows;
     p.pos_value = pos_value; p.max_seq_len = max_seq_len;
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim;
+    p.qg = qg; p.qg_tokens = qg_tokens;
     static const int debug_mode = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
     p.debug = debug_mode;
     static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
@@ -389,27 +391,53 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
                                         int T, int msl, int num_heads, int num_kv_heads, int head_dim, int q_dim,
                                         int kv_dim, int bits, tq_stream_t s) {
     (void)as;
-    // Query tq attends to rows 0..tq of ONE sequence: run the decode kernel with T "sequences" that all start
-    // at row 0 and have positions 0..T-1.
+    // Query t attends to rows 0..t of ONE sequence.  The decode kernel serves up to 8 score rows per KV head at the
+    // price of one: groups of qg = 8 / (heads per KV head) consecutive query tokens become the "sequences" of the launch,
+    // their rows ordered (kv head, token in group, head), each row with its own causal limit.  Every cache tile is then
+    // fetched and dequantised once per group instead of once per token.
     bits = bits == 4 ? 4 : 2;
     int r = check_shape(T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r == TQ_OK && T > msl) r = TQ_ERR_CAPACITY;
     void* ws = nullptr;
     size_t need = 0;
+    int qg = 1, groups = T, vheads = num_heads;
     if (r == TQ_OK) {
-        need = carve_full(nullptr, T, num_heads).bytes;
+        const int grp = num_heads / num_kv_heads;
+        static const bool grouped = !(getenv("TQ_PREFILL_QG") && atoi(getenv("TQ_PREFILL_QG")) == 0);
+        qg = grouped ? 8 / grp : 1;
+        if (qg < 1) qg = 1;
+        groups = (T + qg - 1) / qg;
+        vheads = num_heads * qg;
+        need = std::max(carve_full(nullptr, groups, vheads).bytes, carve_full(nullptr, T, num_heads).bytes);
         r = compat_workspace(need, &ws, cs(s));
     }
     if (r == TQ_OK) {
-        FullWorkspace fw = carve_full(ws, T, num_heads);
-        iota_rows_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(fw.aux_pos, fw.aux_rows, T, 0);
-        r = cuda_status(cudaGetLastError());
+        FullWorkspace fw = carve_full(ws, groups, vheads);
+        // rotated queries of all T tokens (positions play no part in that), written in the grouped row order
+        r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, nullptr, 0, nullptr, 0, 0, msl, T,
+                        num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, false, cs(s), false, nullptr, qg);
+        // the tile table of the groups: group j ends at token min((j + 1) * qg, T) - 1; every group starts at row 0
+        if (r == TQ_OK) {
+            group_rows_kernel<<<(groups + 127) / 128, 128, 0, cs(s)>>>(fw.aux_pos, fw.aux_rows, groups, qg, T);
+            r = cuda_status(cudaGetLastError());
+        }
         if (r == TQ_OK)
-            r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, fw.aux_pos, 0, fw.aux_rows,
-                            0, 0, msl, T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
-        if (r == TQ_OK)
-            r = tq_decode_attention(out, ck_q, cv_q, k_norms, v_norms, rotation, fw.aux_pos, -1, fw.aux_rows, msl, msl, T,
-                                    num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, s);
+            r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, rotation, fw.aux_pos, 0, fw.aux_rows,
+                            0, 0, msl, groups, vheads, num_kv_heads, head_dim, vheads * head_dim, kv_dim, bits, ws, need, true,
+                            cs(s));
+        if (r == TQ_OK) {
+            CUtensorMap tmK, tmV;
+            const int kvp = num_kv_heads * (bits == 4 ? 64 : 32);
+            r = cached_code_map(&tmK, ck_q, msl, kvp);
+            if (r == TQ_OK) r = cached_code_map(&tmV, cv_q, msl, kvp);
+            if (r == TQ_OK) {
+                transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation);
+                r = cuda_status(cudaGetLastError());
+            }
+            if (r == TQ_OK)
+                r = attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, fw.aux_pos, -1, fw.aux_rows, msl, msl,
+                                   groups, vheads, num_kv_heads, q_dim, bits, ws, need, cs(s), false, nullptr, qg, T);
+        }
     }
     g_compat_status = r;
 }

@@ -299,6 +299,16 @@ __global__ void iota_rows_kernel(int* pos, long long* rows, int n, long long row
     }
 }
 
+// positions and row bases of the prefill form's token groups: group j ends at token min((j + 1) * qg, T) - 1, row base 0
+__global__ void group_rows_kernel(int* pos, long long* rows, int groups, int qg, int T) {
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < groups) {
+        const int last = (j + 1) * qg;
+        pos[j] = (last < T ? last : T) - 1;
+        rows[j] = 0;
+    }
+}
+
 // ---- per-device workspace of the compat launchers + descriptor cache ----------------------------------------------------------
 struct CompatState {
     void* ws = nullptr;
