@@ -62,7 +62,7 @@ __global__ void fp16_cache_write_kernel(__half* ck, __half* cv, const __half* k,
 template <int GRP>
 __global__ void __launch_bounds__(FP16_WARPS * 32)
 fp16_decode_attention_kernel(const Fp16AttnParams p) {
-    const int chunk = blockIdx.x, kvh = blockIdx.y, g = blockIdx.z;
+    const int kvh = blockIdx.x, chunk = blockIdx.y, g = blockIdx.z;
     const int pos = p.positions ? p.positions[g] : p.pos_value;
     const int L = (pos < 0 ? 0 : pos) + 1;
     const int c0 = chunk * FP16_CHUNK;

@@ -279,7 +279,7 @@ __global__ void transpose_rotation_kernel(__half* dst, const __half* src) {
 
 inline int launch_fp16_attention(const Fp16AttnParams& p, cudaStream_t s) {
     const int grp = p.H / p.Hkv;
-    dim3 grid(p.nchunk_max, p.Hkv, p.G);
+    dim3 grid(p.Hkv, p.nchunk_max, p.G);  // KV heads fastest: CTAs that run together read the same 2 KB rows (DRAM page locality)
     dim3 block(FP16_WARPS * 32);
     switch (grp) {
         case 1: fp16_decode_attention_kernel<1><<<grid, block, 0, s>>>(p); break;
