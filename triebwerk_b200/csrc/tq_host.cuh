@@ -184,8 +184,10 @@ inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 
 
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
     static const bool prefill_tc = !(getenv("TQ_PREFILL_TC") && atoi(getenv("TQ_PREFILL_TC")) == 0);
-    if (prefill_tc && p.token_mode && !p.q && (p.k_buf || p.v_buf) && p.positions &&
-        (long long)p.n_src * p.Hkv >= 4 * TC_TILE && (long long)p.n_src * p.Hkv < (1ll << 31))
+    // (the tensor-core kernel moves 16 bytes at a time: every array it touches has to be 16-byte aligned)
+    const uintptr_t align_or = (uintptr_t)p.k_buf | (uintptr_t)p.v_buf | (uintptr_t)p.ck | (uintptr_t)p.cv | (uintptr_t)p.rotation;
+    if (prefill_tc && p.token_mode && !p.q && (p.k_buf || p.v_buf) && p.positions && (align_or & 15u) == 0 &&
+        p.kv_dim == p.Hkv * HEAD_DIM && (long long)p.n_src * p.Hkv >= 4 * TC_TILE && (long long)p.n_src * p.Hkv < (1ll << 31))
         return launch_prefill_tc(p, s);
     const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
     const long long total = (long long)p.n_src * (nk + nv + nq);
