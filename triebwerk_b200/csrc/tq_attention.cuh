@@ -81,6 +81,9 @@ struct AttnParams {
     int kv_dim;
     int capacity_rows;         // rows a sequence may use (position check)
     int app_weight;            // cost of one append in tiles, for the balance of the work list
+    int early;                 // 1: positions and this layer's cache tiles may be read before the previous kernel in the
+                               // stream has finished (the caller knows it writes neither): table, slice and first copies
+                               // then run under that kernel's tail
     // prefill form: a "sequence" of the launch is a group of qg consecutive query tokens of ONE cache (row base 0); its
     // H = qg * (real heads) rows are ordered (kv head, token in group, head of the kv head); token t attends to rows 0..t
     int qg;                    // 0 or 1: plain decode
@@ -209,8 +212,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const uint32_t ctrl_s = a_base + RegionA::CTRL_OFF + (uint32_t)group * 16u;
     const uint32_t merge_s = a_base + RegionA::MERGE_OFF + (uint32_t)group * RegionA::MERGE_GROUP_BYTES;
 
-    pdl_launch_dependents();
-    if (p.debug & 32) { pdl_wait(); return; }
+    // The fused form lets its successor start only once it has itself seen its predecessor finish (see `early`).
+    if (!FUSED) pdl_launch_dependents();
+    if (p.debug & 32) { pdl_wait(); pdl_launch_dependents(); return; }
     const int G = p.G;
 
     // ---- byte -> centroid table, one column per lane ----
@@ -240,7 +244,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         fence_proxy_async_smem();
     }
     // Everything above touches only shared memory and may overlap the tail of the previous kernel in the stream.
-    pdl_wait();
+    const bool early = FUSED && p.early != 0;
+    if (!early) {
+        pdl_wait();
+        if (FUSED) pdl_launch_dependents();
+    }
     // Tile table.  The fused form builds it here, in shared memory, from the positions (every CTA the same table);
     // the plain form reads the one the append kernel left in the workspace.
     const int* ts;
@@ -397,6 +405,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         int g_app0 = g;  // first sequence whose last tile starts at or after lo
         while (g_app0 < G && ts[g_app0 + 1] - 1 < lo_i) ++g_app0;
         const bool have_app = g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
+        if (early) {
+            // none of this worker's first tiles can hold a row the step is about to write unless it appends itself
+            if (!have_app) fill_ring();
+            pdl_wait();
+            pdl_launch_dependents();
+        }
         if (have_app) {
             const uint32_t abar = a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group;
             // R[.][k < 64] and R[.][k >= 64], 16 KB each: one stage each, or two adjacent ones when stages are smaller
@@ -535,7 +549,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             // the stages go back to the ring: generic-proxy reads of R before, async-proxy writes of tiles after
             if (gtid == 0) fence_proxy_async_all();
         }
-        fill_ring();
+        if (have_app || !early) fill_ring();
     } else {
         fill_ring();
     }

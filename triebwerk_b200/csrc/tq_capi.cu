@@ -146,6 +146,7 @@ struct FusedInputs {
     const void* rotation;
     const void* rot_prep16;
     int rot_copies;
+    int early;
 };
 
 static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* ck_q, const void* cv_q,
@@ -179,6 +180,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         p.new_k = (const __half*)fused->k; p.new_v = (const __half*)fused->v; p.new_q = (const __half*)fused->q;
         p.rotation = (const __half*)fused->rotation; p.rot_prep16 = (const __half*)fused->rot_prep16;
         p.rot_copies = fused->rot_copies;
+        p.early = fused->early;
         // what the append of one token costs its worker, in 32-token tiles (measured; TQ_FUSED_WEIGHT overrides)
         static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 7;
         p.app_weight = app_weight < 0 ? 0 : app_weight;
@@ -583,6 +585,7 @@ void tq_engine_destroy(tq_engine* e) {
 int tq_engine_kv_bits(const tq_engine* e) { return e ? e->kv_bits : TQ_ERR_ARG; }
 
 int tq_engine_set_fused(tq_engine* e, int on) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e) return TQ_ERR_ARG;
     const int prev = e->fused ? 1 : 0;
     e->fused = on != 0;
@@ -638,6 +641,7 @@ size_t tq_engine_arena_bytes(const tq_engine* e, int G, int max_seq_len, const i
 }
 
 int tq_engine_set_arena(tq_engine* e, void* device_ptr, size_t bytes) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || !device_ptr || bytes == 0) return TQ_ERR_ARG;
     if (((uintptr_t)device_ptr & 255u) != 0) return TQ_ERR_ARG;
     engine_release_arena(e);  // frees only memory this library allocated
@@ -649,6 +653,7 @@ int tq_engine_set_arena(tq_engine* e, void* device_ptr, size_t bytes) {
 }
 
 int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capacities) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || G <= 0 || max_seq_len <= 0) return TQ_ERR_ARG;
     if (e->asleep) return TQ_ERR_STATE;
     int r = check_shape(G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim, e->q_dim(), e->kv_dim(),
@@ -709,6 +714,7 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
 }
 
 int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e) return TQ_ERR_ARG;
     if (!e->arena || e->G == 0) return TQ_OK;
     TQ_CUDA(cudaMemsetAsync(e->d_positions, 0, (size_t)e->G * sizeof(int), cs(s)));
@@ -726,6 +732,7 @@ int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s) {
 }
 
 int tq_engine_sleep(tq_engine* e) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e) return TQ_ERR_ARG;
     TQ_CUDA(cudaDeviceSynchronize());
     engine_release_arena(e);
@@ -734,6 +741,7 @@ int tq_engine_sleep(tq_engine* e) {
 }
 
 int tq_engine_wake(tq_engine* e) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e) return TQ_ERR_ARG;
     e->asleep = false;  // the arena comes back lazily with the next tq_engine_alloc_batch, as in the reference
     return TQ_OK;
@@ -748,6 +756,7 @@ int tq_engine_status(tq_engine* e, tq_stream_t s) {
 int* tq_engine_positions(tq_engine* e) { return e ? e->d_positions : nullptr; }
 
 int tq_engine_set_positions(tq_engine* e, const int* host_positions, int G, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || !host_positions) return TQ_ERR_ARG;
     if (!e->arena || G != e->G) return TQ_ERR_STATE;
     for (int g = 0; g < G; ++g) {
@@ -764,6 +773,7 @@ __global__ void advance_positions_kernel(int* pos, int n) {
 }
 
 int tq_engine_advance(tq_engine* e, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || !e->arena || e->G == 0) return TQ_ERR_STATE;
     advance_positions_kernel<<<(e->G + 127) / 128, 128, 0, cs(s)>>>(e->d_positions, e->G);
     return cuda_status(cudaGetLastError());
@@ -786,6 +796,7 @@ const long long* tq_engine_row_base(tq_engine* e) { return e ? e->d_row_base : n
 const void* tq_engine_rotation(tq_engine* e) { return e ? e->d_rotation : nullptr; }
 
 int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || !host_half) return TQ_ERR_ARG;
     memcpy(e->h_rotation.data(), host_half, e->h_rotation.size() * 2);
     return engine_upload_rotation(e, cs(s));
@@ -795,6 +806,8 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
                            tq_stream_t s) {
     if (!e || layer < 0 || layer >= e->shape.num_layers || !q || !k || !v || !out) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    const bool chained = e->chain_ok;  // whatever happens below, the chain of fused launches starts afresh unless it continues
+    e->chain_ok = false;
     const tq_engine::Layer& L = e->layers[layer];
     const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, D = e->shape.head_dim;
     if (e->kv_bits == 0) {
@@ -808,10 +821,15 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     }
     // One launch per layer when the batch fits the kernel's shared-memory tile table (tq_engine_set_fused).
     if (e->fused && e->G <= FUSED_MAX_G) {
-        FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES};
-        return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
-                              e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s),
-                              use_pdl(), &in);
+        static const bool early_on = !(getenv("TQ_FUSED_EARLY") && atoi(getenv("TQ_FUSED_EARLY")) == 0);
+        const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s)) ? 1 : 0;
+        FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES, early};
+        const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
+                                     e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
+                                     cs(s), use_pdl(), &in);
+        e->chain_ok = r == TQ_OK;
+        e->chain_stream = cs(s);
+        return r;
     }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
@@ -822,6 +840,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
 }
 
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || layer < 0 || layer >= e->shape.num_layers || !out) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
@@ -868,6 +887,7 @@ __global__ void iota_from_kernel(int* pos, int n, int first) {
 // [n_seq][T][kv_dim].  One launch.
 static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v, int first_pos,
                                int T, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0 || n_seq <= 0) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
     if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;

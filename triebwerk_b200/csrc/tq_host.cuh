@@ -378,6 +378,10 @@ struct tq_engine {
     size_t arena_cap = 0;
     bool arena_external = false;
     bool asleep = false;
+    // The last thing this engine put on `chain_stream` was a fused decode launch: positions and caches are as that
+    // launch saw them, so the next fused launch may read them before it has seen its predecessor finish.
+    bool chain_ok = false;
+    cudaStream_t chain_stream = nullptr;
     bool fused = !(getenv("TQ_FUSED") && atoi(getenv("TQ_FUSED")) == 0);  // one launch per layer-step (packed modes)
 
     // current carving
