@@ -822,7 +822,11 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     // One launch per layer when the batch fits the kernel's shared-memory tile table (tq_engine_set_fused).
     if (e->fused && e->G <= FUSED_MAX_G) {
         static const bool early_on = !(getenv("TQ_FUSED_EARLY") && atoi(getenv("TQ_FUSED_EARLY")) == 0);
-        const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s)) ? 1 : 0;
+        // (a launch that is being captured into a graph is replayed after whatever the caller puts in front of the
+        // graph: it never reads early)
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(cs(s), &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
+        const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s) && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
         FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES, early};
         const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
                                      e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
