@@ -452,8 +452,8 @@ def run_ours(args, w, rank, world, local_rank):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the committed ncu capture
 # (profiles/; the per-layer shape of c1 was captured on the 4-layer workload c1l4), or None while no capture exists.
 TRAFFIC = {
-    # profiles/decode_attention_kernel_4bit_fused_c1_layer.md: 281.74 MB read + 5.28 MB written for one layer-step launch
-    "c1": 287024640, "c1l4": 287024640,
+    # profiles/decode_attention_kernel_4bit_fused_c1_layer.md: 281.71 MB read + 5.99 MB written for one layer-step launch
+    "c1": 287702784, "c1l4": 287702784,
     # profiles/decode_attention_kernel_4bit_unfused_c1_layer.md (TQ_FUSED=0): 278.32 MB read + 4.51 MB written
     "c1/unfused": 282830592, "c1l4/unfused": 282830592,
 }
