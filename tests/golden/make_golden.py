@@ -6,7 +6,7 @@ its kernels themselves: oracle/Makefile compiles engine/kernels.cu unmodified (w
 launchers of that library (engine/kernels.cu:1963-2028, :737-752, :1351-1357) on seeded inputs and stores inputs and
 outputs.  Run on a GPU machine from the repository root:
 
-    python tests/golden/make_golden.py --out gpurun_out/golden
+    python tests/golden/make_golden.py --out new_golden
 
 then copy the .npz files into tests/golden/.  The CPU oracle and the CUDA library are both tested against
 these files.  Rotation bytes come from the oracle's restatement of the reference generator and are stored
@@ -54,7 +54,7 @@ def edge_vectors(kv_dim, rng):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/golden")
+    ap.add_argument("--out", default="new_golden")
     args = ap.parse_args()
     os.makedirs(args.out, exist_ok=True)
     ref = C.CDLL(REF_SO)
