@@ -76,7 +76,6 @@ struct AttnParams {
     const __half* new_v;
     const __half* new_q;       // [G][q_dim]
     const __half* rotation;    // R row-major (B operand of the query rotation); rot_copies copies back to back
-    const __half* rot_prep16;  // R in the order [k/4][d][k%4] (fp16, 32 KB): rows of the exact fp32 chain, staged in shared memory; rot_copies copies
     int rot_copies;            // every worker reads copy (worker % rot_copies): 300 workers fetching the same 32 KB at once queue up in L2
     int kv_dim;
     int capacity_rows;         // rows a sequence may use (position check)
@@ -109,7 +108,7 @@ struct RegionA {
     static constexpr uint32_t FUSED_SCAN_OFF = BLOCKS_OFF;           // 32 ints of scan scratch
     static constexpr uint32_t FUSED_TS_OFF = FUSED_SCAN_OFF + 128;   // tile_start[G + 1], G <= FUSED_MAX_G
     static constexpr uint32_t FUSED_APP_OFF = FUSED_TS_OFF + 4096;
-    static constexpr uint32_t FUSED_APP_GROUP_BYTES = 16 * 128 + 16 * 4 * 4 + 128;  // codes, warp sums, 16 dest rows
+    static constexpr uint32_t FUSED_APP_GROUP_BYTES = 16 * 128 + 16 * 4 * 4 + 128;  // codes [16][128], 1/norm [16], spare
     static constexpr uint32_t FUSED_BLOCKS_OFF = FUSED_APP_OFF + ATTN_GROUPS * FUSED_APP_GROUP_BYTES;
 };
 constexpr int FUSED_MAX_G = 1023;
@@ -200,9 +199,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         return blk < n_a ? blocks_a + blk * stage_bytes : REGION_B_ABS + (blk - n_a) * stage_bytes;
     };
     bool layout_ok = !(blocks_a >= LUT_ABS || s_fit < 2 || dyn_end < REGION_B_ABS);
-    if (FUSED && layout_ok && stage_bytes < 16384u)  // the append borrows stages 0+1 and 2+3 as two 16 KB buffers
-        layout_ok = S >= 4 && 2u * stage_bytes >= 16384u && stage_addr(1) == stage_addr(0) + stage_bytes &&
-                    stage_addr(3) == stage_addr(2) + stage_bytes;
     if (!layout_ok) {
         if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
         return;
@@ -235,7 +231,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     }
     if (gtid == 0) {
-        if (FUSED) mbar_init(a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group, 1);
         for (int s = 0; s < ATTN_MAX_STAGES; ++s) {
             mbar_init(bar0 + 8u * s, 1);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
@@ -400,119 +395,174 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     };
     if constexpr (FUSED) {
         // The new token of a sequence is appended by the worker that owns the sequence's last tile (the only tile the
-        // row can be in), before that tile is fetched.  Such a worker first borrows its two (still empty) stages for
-        // R, which the exact fp32 chain reads row by row, and fills the ring afterwards.
+        // row can be in), before that tile is fetched.  The rotation of the sequence's 2 * Hkv head vectors runs on the
+        // tensor cores (16 rows x 128 x 128, fp16 hi/lo operands as in the prefill kernel); a coordinate within
+        // APPEND_MARGIN of a decision bound is recomputed with the reference's exact fp32 chain, so that the stored
+        // bytes are the reference's.  The ring is filled first unless one of its tiles is the tile being written.
         int g_app0 = g;  // first sequence whose last tile starts at or after lo
         while (g_app0 < G && ts[g_app0 + 1] - 1 < lo_i) ++g_app0;
         const bool have_app = g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
+        const bool fill_before = !have_app || ts[g_app0 + 1] - 1 >= lo_i + S;
         if (early) {
-            // none of this worker's first tiles can hold a row the step is about to write unless it appends itself
-            if (!have_app) fill_ring();
+            // none of the tiles filled here can hold a row the step is about to write
+            if (fill_before) fill_ring();
             pdl_wait();
             pdl_launch_dependents();
+        } else if (fill_before) {
+            fill_ring();
         }
         if (have_app) {
-            const uint32_t abar = a_base + RegionA::BAR_OFF + 64u + 8u * (uint32_t)group;
-            // R[.][k < 64] and R[.][k >= 64], 16 KB each: one stage each, or two adjacent ones when stages are smaller
-            const uint32_t r_lo = stage_addr(0), r_hi = stage_addr(stage_bytes >= 16384u ? 1 : 2);
-            if (gtid == 0) {
-                mbar_arrive_expect_tx(abar, 32768u);
-                const __half* rsrc = p.rot_prep16 + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);
-                bulk_load(r_lo, rsrc, 16384u, abar);
-                bulk_load(r_hi, rsrc + 8192, 16384u, abar);
-            }
-            const uint32_t xs_a = merge_s;  // [16][128] fp32 staging of the normalised vectors (the merge area is idle)
+            constexpr float APPEND_MARGIN = 1.6e-5f;  // twice the worst-case rounding of a 128-term fp32 sum with sum|r x| <= 1
+            constexpr int NVEC = 2 * Hkv;              // head vectors of one token: K heads, then V heads
+            const uint32_t hi_a = merge_s, lo_a = merge_s + 16u * MERGE_ROW * 2u;  // A operands [16][MERGE_ROW] fp16 (idle merge area)
             const uint32_t app_a = a_base + RegionA::FUSED_APP_OFF + (uint32_t)group * RegionA::FUSED_APP_GROUP_BYTES;
-            const uint32_t codes_a = app_a, part_a = app_a + 2048u;
-            const int d = gtid & 127, sub = gtid >> 7;  // 8 vectors per 128 threads: K heads first, then V heads
-            const int wsub = (gtid >> 5) & 3;
-            bool r_ready = false;
+            const uint32_t codes_a = app_a, inv_a = app_a + 2048u;  // codes [16][128] u8, 1/norm [16] f32
+            const __half* rot_w = p.rotation + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);
             for (int ga = g_app0; ga < G && ts[ga + 1] - 1 < hi_i; ++ga) {
                 const int pos = p.positions ? p.positions[ga] : p.pos_value;
                 const bool ok = pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows);
                 const long long row = (p.row_base ? p.row_base[ga] : (long long)ga * p.max_seq_len) + pos;
-                float val[8];
+                // B fragments (R), 16 bytes per lane and load, contraction index permuted as in the query rotation
+                uint4 bq[16 / Hkv][4];
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    const int vi = sub * 8 + v;
-                    const __half* srcp = (vi < Hkv ? p.new_k : p.new_v) + (size_t)ga * p.kv_dim + (size_t)(vi % Hkv) * HEAD_DIM + d;
-                    val[v] = __half2float(*srcp);
+                for (int nbi = 0; nbi < 16 / Hkv; ++nbi) {
+                    const uint4* rr = reinterpret_cast<const uint4*>(rot_w + (size_t)(8 * (head + nbi * Hkv) + gl) * HEAD_DIM) + t4;
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) bq[nbi][m] = __ldg(rr + 4 * m);
                 }
+                // ---- thread (vector v, 32-coordinate chunk c): sum of squares in the reference's order, norm, hi/lo ----
+                if (gtid < NVEC * 4) {
+                    const int v = gtid >> 2, c = gtid & 3;
+                    const uint4* src = reinterpret_cast<const uint4*>((v < Hkv ? p.new_k : p.new_v) + (size_t)ga * p.kv_dim +
+                                                                      (size_t)(v % Hkv) * HEAD_DIM + 32 * c);
+                    uint4 raw[4];
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    float sq = mul_ftz(val[v], val[v]);
+                    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
+                    float val[32], sq[32];
 #pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) sq = add_ftz(sq, __shfl_down_sync(0xffffffffu, sq, off));
-                    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(part_a + (uint32_t)((sub * 8 + v) * 4 + wsub) * 4u), "f"(sq) : "memory");
-                }
-                group_barrier(group, gthreads);
-                float tn[8];
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    float4 pp;
-                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(pp.x), "=f"(pp.y), "=f"(pp.z), "=f"(pp.w)
-                                 : "r"(part_a + (uint32_t)(sub * 8 + v) * 16u) : "memory");
-                    const float ss = add_ftz(add_ftz(pp.x, pp.z), add_ftz(pp.y, pp.w));
-                    tn[v] = add_ftz(ss, 1e-12f);
-                    const float xh = mul_ftz(val[v], rsqrt_approx_ftz(tn[v]));
-                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + d) * 4u), "f"(xh) : "memory");
-                }
-                group_barrier(group, gthreads);
-                if (!r_ready) {
-                    if (!mbar_wait_bounded(abar, 0u, 1u << 22)) {
-                        dead = true;
-                        if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
-                    }
-                    r_ready = true;
-                }
-                // k-ascending fused chain per output coordinate, eight vectors interleaved; a short rolled loop
-                float acc[8];
-#pragma unroll
-                for (int v = 0; v < 8; ++v) acc[v] = 0.0f;
-#pragma unroll 4
-                for (int j = 0; j < HEAD_DIM / 4; ++j) {
-                    const uint2 rw = ldsv64((j < 16 ? r_lo : r_hi) + (uint32_t)(((j & 15) * HEAD_DIM + d) * 8));
-                    const float2 r01 = __half22float2(*reinterpret_cast<const __half2*>(&rw.x));
-                    const float2 r23 = __half22float2(*reinterpret_cast<const __half2*>(&rw.y));
-                    float4 x[8];
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const uint4 xw = ldsv128(xs_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + 4 * j) * 4u);
-                        x[v] = make_float4(__uint_as_float(xw.x), __uint_as_float(xw.y), __uint_as_float(xw.z), __uint_as_float(xw.w));
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(h2[e]);
+                            val[8 * i + 2 * e] = f.x;
+                            val[8 * i + 2 * e + 1] = f.y;
+                        }
                     }
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r01.x, x[v].x, acc[v]);
+                    for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
+                    // the warp-shuffle tree of the reference (offsets 16, 8, 4, 2, 1), element l taking lane l's place
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r01.y, x[v].y, acc[v]);
+                    for (int off = 16; off > 0; off >>= 1)
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r23.x, x[v].z, acc[v]);
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) acc[v] = fma_ftz(r23.y, x[v].w, acc[v]);
-                }
-#pragma unroll
-                for (int v = 0; v < 8; ++v)
-                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(codes_a + (uint32_t)((sub * 8 + v) * HEAD_DIM + d)),
-                                 "r"(quantize_code(acc[v], BITS)) : "memory");
-                // the norm of vector v, by thread v of its 128
-#pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    if (d == v) {
-                        const int vi = sub * 8 + v;
+                        for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
+                    const float part = sq[0];
+                    const int l0 = lane & ~3;
+                    const float p0 = __shfl_sync(0xffffffffu, part, l0), p1 = __shfl_sync(0xffffffffu, part, l0 + 1);
+                    const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
+                    const float tt = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
+                    const float inv = rsqrt_approx_ftz(tt);
+                    if (c == 0) {
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(inv_a + (uint32_t)v * 4u), "f"(inv) : "memory");
                         if (ok) {
-                            __half* cn = const_cast<__half*>(vi < Hkv ? p.kn : p.vn);
-                            cn[(size_t)row * Hkv + (vi % Hkv)] = __float2half_rn(sqrt_approx_ftz(tn[v]));
-                        } else if (vi == 0) {
+                            __half* cn = const_cast<__half*>(v < Hkv ? p.kn : p.vn);
+                            cn[(size_t)row * Hkv + (v % Hkv)] = __float2half_rn(sqrt_approx_ftz(tt));
+                        } else if (v == 0) {
                             atomicMax(p.status, ST_BAD_POSITION);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {  // 8 coordinates = 16 bytes at a time
+                        uint32_t hw[4], lw[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float x0 = mul_ftz(val[8 * i + 2 * e], inv), x1 = mul_ftz(val[8 * i + 2 * e + 1], inv);
+                            const __half2 h = __floats2half2_rn(x0, x1);
+                            const float2 hf = __half22float2(h);
+                            hw[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            lw[e] = pack_half2((x0 - hf.x) * 4096.0f, (x1 - hf.y) * 4096.0f);
+                        }
+                        const uint32_t o = (uint32_t)(v * MERGE_ROW + 32 * c + 8 * i) * 2u;
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(hi_a + o), "r"(hw[0]), "r"(hw[1]), "r"(hw[2]), "r"(hw[3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(lo_a + o), "r"(lw[0]), "r"(lw[1]), "r"(lw[2]), "r"(lw[3]) : "memory");
+                    }
+                } else if (NVEC < 16) {
+                    // fewer than 16 vectors: rows NVEC .. 15 of both operands are zero (16-byte pieces, 17 per row)
+                    for (int i = gtid - NVEC * 4; i < (16 - NVEC) * 17; i += gthreads - NVEC * 4) {
+                        const uint32_t o = (uint32_t)((NVEC + i / 17) * MERGE_ROW) * 2u + (uint32_t)(i % 17) * 16u;
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(hi_a + o), "r"(0u) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(lo_a + o), "r"(0u) : "memory");
+                    }
+                }
+                group_barrier(group, gthreads);
+                // ---- rotation on the tensor cores: two accumulators per column block (hi part, scaled lo part) ----
+                uint4 ah_lo[4], ah_hi[4], al_lo[4], al_hi[4];  // operand hi / lo, rows gl / gl + 8
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const uint32_t o0 = (uint32_t)(gl * MERGE_ROW + 32 * m + 8 * t4) * 2u, o8 = o0 + 8u * MERGE_ROW * 2u;
+                    ah_lo[m] = ldsv128(hi_a + o0);
+                    ah_hi[m] = ldsv128(hi_a + o8);
+                    al_lo[m] = ldsv128(lo_a + o0);
+                    al_hi[m] = ldsv128(lo_a + o8);
+                }
+                // the exact chain of the reference for coordinate d of vector v (R row from global, x rebuilt from the input)
+                auto exact_code = [&](int v, int d) -> int {
+                    const uint4* xs = reinterpret_cast<const uint4*>((v < Hkv ? p.new_k : p.new_v) + (size_t)ga * p.kv_dim +
+                                                                     (size_t)(v % Hkv) * HEAD_DIM);
+                    const uint4* rs = reinterpret_cast<const uint4*>(rot_w + (size_t)d * HEAD_DIM);
+                    float inv;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(inv) : "r"(inv_a + (uint32_t)v * 4u) : "memory");
+                    float acc = 0.0f;
+#pragma unroll 2
+                    for (int j = 0; j < 16; ++j) {
+                        const uint4 xv = __ldg(xs + j), rv = __ldg(rs + j);
+                        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                        const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                            acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
+                            acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+                        }
+                    }
+                    return quantize_code(acc, BITS);
+                };
+#pragma unroll
+                for (int nbi = 0; nbi < 16 / Hkv; ++nbi) {
+                    const int nb = head + nbi * Hkv;
+                    float ch[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        mma16816(ch, ah_lo[m].x, ah_hi[m].x, ah_lo[m].y, ah_hi[m].y, bq[nbi][m].x, bq[nbi][m].y);
+                        mma16816(ch, ah_lo[m].z, ah_hi[m].z, ah_lo[m].w, ah_hi[m].w, bq[nbi][m].z, bq[nbi][m].w);
+                        mma16816(cl, al_lo[m].x, al_hi[m].x, al_lo[m].y, al_hi[m].y, bq[nbi][m].x, bq[nbi][m].y);
+                        mma16816(cl, al_lo[m].z, al_hi[m].z, al_lo[m].w, al_hi[m].w, bq[nbi][m].z, bq[nbi][m].w);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {  // (row gl, col), (row gl, col + 1), (row gl + 8, col), (row gl + 8, col + 1)
+                        const int v = gl + 8 * (e >> 1), d = 8 * nb + 2 * t4 + (e & 1);
+                        const float dval = fmaf(cl[e], 1.0f / 4096.0f, ch[e]);
+                        int code = quantize_code(dval, BITS);
+                        float dist = 3.0e38f;  // distance to the nearest decision bound
+                        if (BITS == 4) {
+#pragma unroll
+                            for (int i = 0; i < 15; ++i) dist = fminf(dist, fabsf(dval - kBnd4[i]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 3; ++i) dist = fminf(dist, fabsf(dval - kBnd2[i]));
+                        }
+                        if (v < NVEC) {
+                            if (dist < APPEND_MARGIN) code = exact_code(v, d);
+                            asm volatile("st.shared.u8 [%0], %1;" ::"r"(codes_a + (uint32_t)(v * HEAD_DIM + d)), "r"(code) : "memory");
                         }
                     }
                 }
                 group_barrier(group, gthreads);
-                // pack: one 32-bit word (8 four-bit or 16 two-bit codes) per thread
+                // ---- pack: one 32-bit word (8 four-bit or 16 two-bit codes) per thread; NVEC vectors ----
                 {
                     constexpr int words_per_vec = (int)Geo::BPH / 4;
-                    if (ok && d < 8 * words_per_vec) {
-                        const int v = d / words_per_vec, wv = d - v * words_per_vec;
-                        const int vi = sub * 8 + v;
+                    for (int wi = gtid; ok && wi < NVEC * words_per_vec; wi += gthreads) {
+                        const int vi = wi / words_per_vec, wv = wi - vi * words_per_vec;
                         uint32_t word = 0;
                         if (BITS == 2) {
                             uint4 c4;  // ordered after the barrier: a volatile load, unlike the tile loop's
@@ -520,10 +570,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                                          : "r"(codes_a + (uint32_t)(vi * HEAD_DIM + 16 * wv)) : "memory");
                             const uint32_t cw[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                const uint32_t x = cw[b];
+                            for (int b2 = 0; b2 < 4; ++b2) {
+                                const uint32_t x = cw[b2];
                                 const uint32_t pk = (x & 3u) | ((x >> 6) & 0xcu) | ((x >> 12) & 0x30u) | ((x >> 18) & 0xc0u);
-                                word |= pk << (8 * b);
+                                word |= pk << (8 * b2);
                             }
                         } else {
                             uint2 c2;
@@ -546,10 +596,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 fence_proxy_async_all();
                 group_barrier(group, gthreads);
             }
-            // the stages go back to the ring: generic-proxy reads of R before, async-proxy writes of tiles after
             if (gtid == 0) fence_proxy_async_all();
         }
-        if (have_app || !early) fill_ring();
+        if (!fill_before) fill_ring();
     } else {
         fill_ring();
     }

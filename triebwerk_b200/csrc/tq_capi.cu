@@ -144,7 +144,6 @@ struct FusedInputs {
     const void* k;
     const void* v;
     const void* rotation;
-    const void* rot_prep16;
     int rot_copies;
     int early;
 };
@@ -178,7 +177,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     p.l2_ahead = l2_ahead > 0 ? l2_ahead : (1 << 28);  // 0 switches the prefetch off
     if (fused) {
         p.new_k = (const __half*)fused->k; p.new_v = (const __half*)fused->v; p.new_q = (const __half*)fused->q;
-        p.rotation = (const __half*)fused->rotation; p.rot_prep16 = (const __half*)fused->rot_prep16;
+        p.rotation = (const __half*)fused->rotation;
         p.rot_copies = fused->rot_copies;
         p.early = fused->early;
         // what the append of one token costs its worker, in 32-token tiles (measured; TQ_FUSED_WEIGHT overrides)
@@ -532,18 +531,11 @@ static int engine_upload_rotation(tq_engine* e, cudaStream_t s) {
             prep[((size_t)(k / 4) * HEAD_DIM + d) * 4 + (k % 4)] = __half2float(__half(raw));
         }
     TQ_CUDA(cudaMemcpyAsync(e->d_rotation_prep, prep.data(), prep.size() * sizeof(float), cudaMemcpyHostToDevice, s));
-    // For the fused kernel: R and R in that order as fp16, ROT_COPIES copies of each back to back.  Every worker of the
-    // kernel reads all of R at the same moment; with one copy those reads queue up on the same L2 lines.
+    // For the fused kernel: ROT_COPIES copies of R back to back.  Every worker of the kernel reads all of R at the same
+    // moment; with one copy those reads queue up on the same L2 lines.
     if (!e->d_rotation_rep) TQ_CUDA(cudaMalloc(&e->d_rotation_rep, bytes * ROT_COPIES));
-    if (!e->d_rotation_prep16) TQ_CUDA(cudaMalloc(&e->d_rotation_prep16, bytes * ROT_COPIES));
-    std::vector<uint16_t> prep16(e->h_rotation.size());
-    for (int d = 0; d < HEAD_DIM; ++d)
-        for (int k = 0; k < HEAD_DIM; ++k)
-            prep16[((size_t)(k / 4) * HEAD_DIM + d) * 4 + (k % 4)] = e->h_rotation[(size_t)d * HEAD_DIM + k];
-    for (int c = 0; c < ROT_COPIES; ++c) {
+    for (int c = 0; c < ROT_COPIES; ++c)
         TQ_CUDA(cudaMemcpyAsync((char*)e->d_rotation_rep + bytes * c, e->h_rotation.data(), bytes, cudaMemcpyHostToDevice, s));
-        TQ_CUDA(cudaMemcpyAsync((char*)e->d_rotation_prep16 + bytes * c, prep16.data(), bytes, cudaMemcpyHostToDevice, s));
-    }
     TQ_CUDA(cudaStreamSynchronize(s));  // t and h_rotation are pageable host memory
     return TQ_OK;
 }
@@ -567,7 +559,6 @@ void tq_engine_destroy(tq_engine* e) {
     if (e->d_rotation) cudaFree(e->d_rotation);
     if (e->d_rotation_t) cudaFree(e->d_rotation_t);
     if (e->d_rotation_prep) cudaFree(e->d_rotation_prep);
-    if (e->d_rotation_prep16) cudaFree(e->d_rotation_prep16);
     if (e->d_rotation_rep) cudaFree(e->d_rotation_rep);
     if (e->st_in) {
         cudaStreamDestroy(e->st_in);
@@ -827,7 +818,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(cs(s), &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
         const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s) && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
-        FusedInputs in{q, k, v, e->d_rotation_rep, e->d_rotation_prep16, ROT_COPIES, early};
+        FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early};
         const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
                                      e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
                                      cs(s), use_pdl(), &in);

@@ -420,7 +420,6 @@ struct tq_engine {
     void* d_rotation = nullptr;
     void* d_rotation_t = nullptr;
     float* d_rotation_prep = nullptr;  // fp32, in the append kernel's shared-memory order
-    void* d_rotation_prep16 = nullptr; // the same order in fp16, for the fused kernel (several copies)
     void* d_rotation_rep = nullptr;    // R row-major, several copies, for the fused kernel's query rotation
 
     int q_dim() const { return shape.num_heads * shape.head_dim; }
