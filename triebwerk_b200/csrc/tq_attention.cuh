@@ -292,14 +292,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int W = w_all < N ? (int)w_all : (int)N;
     const int wid = blockIdx.x * ATTN_GROUPS + group;
     if (wid >= W) return;  // uniform for the worker; no CTA-wide barrier follows
-    // The flat list is cut in UNITS: a tile is one unit, except the last tile of a sequence in the fused form, which
-    // counts 1 + A units because its owner also appends the sequence's new token (A = p.app_weight, the append's
-    // cost in tiles).  Sequence g starts at unit ts[g] + g*A; a tile belongs to the worker its first unit falls to.
-    const long long A = FUSED ? (long long)p.app_weight : 0;
+    // The flat list is cut in UNITS: a tile is one unit, except the last tile of a sequence, which counts 1 + A units
+    // for what a sequence costs beside its tiles (A = p.app_weight, in tiles): in the fused form its owner also appends
+    // the sequence's new token; in the prefill form sequences are short and their partials and merges weigh as much
+    // as their tiles.  Sequence g starts at unit ts[g] + g*A; a tile belongs to the worker its first unit falls to.
+    const long long A = (long long)p.app_weight;
     const long long U = N + (long long)G * A;
     long long lo, hi;
     int g;
-    if constexpr (FUSED) {
+    if (FUSED || A > 0) {
         auto tiles_before = [&](long long x, int* gfirst) -> long long {  // tiles whose first unit is below unit x
             if (x >= U) { *gfirst = G; return N; }
             int a = 0, b = G;  // invariant: unit start of a <= x < unit start of b

@@ -171,6 +171,10 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     p.pos_value = pos_value; p.max_seq_len = max_seq_len;
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim;
     p.qg = qg; p.qg_tokens = qg_tokens;
+    if (qg > 1) {  // groups of query tokens are short sequences: what each costs beside its tiles, in tiles (measured)
+        static const int seq_weight = getenv("TQ_PREFILL_SEQ_WEIGHT") ? atoi(getenv("TQ_PREFILL_SEQ_WEIGHT")) : 10;
+        p.app_weight = seq_weight < 0 ? 0 : seq_weight;
+    }
     static const int debug_mode = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
     p.debug = debug_mode;
     static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
