@@ -402,7 +402,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         // bytes are the reference's.  The ring is filled first unless one of its tiles is the tile being written.
         int g_app0 = g;  // first sequence whose last tile starts at or after lo
         while (g_app0 < G && ts[g_app0 + 1] - 1 < lo_i) ++g_app0;
-        const bool have_app = g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
+        // (without new keys and values the launch only builds its table, rotates the queries and attends)
+        const bool have_app = p.new_k != nullptr && g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
         const bool fill_before = !have_app || ts[g_app0 + 1] - 1 >= lo_i + S;
         if (early) {
             // none of the tiles filled here can hold a row the step is about to write

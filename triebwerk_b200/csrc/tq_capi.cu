@@ -186,7 +186,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         p.early = fused->early;
         // what the append of one token costs its worker, in 32-token tiles (measured; TQ_FUSED_WEIGHT overrides)
         static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 7;
-        p.app_weight = app_weight < 0 ? 0 : app_weight;
+        p.app_weight = (!fused->k || app_weight < 0) ? 0 : app_weight;  // nothing to weigh without an append
         p.kv_dim = num_kv_heads * HEAD_DIM; p.capacity_rows = max_seq_len;
     }
     return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl, fused != nullptr);
@@ -358,6 +358,29 @@ void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* c
     if (r == TQ_OK) {
         need = carve_full(nullptr, G, num_heads).bytes;
         r = compat_workspace(need, &ws, cs(s));
+    }
+    static const bool one_launch = !(getenv("TQ_FUSED") && atoi(getenv("TQ_FUSED")) == 0);
+    if (r == TQ_OK && one_launch && G <= FUSED_MAX_G && pos) {
+        // one launch: the attention kernel builds its tile table and rotates the queries itself (its fused form without
+        // an append); only the transpose of R for the merge precedes it
+        if (!q || !out || !ck_q || !cv_q || !k_norms || !v_norms || !rotation) r = TQ_ERR_ARG;
+        FullWorkspace fw = carve_full(ws, G, num_heads);
+        CUtensorMap tmK, tmV;
+        const int kvp = num_kv_heads * (bits == 4 ? 64 : 32);
+        if (r == TQ_OK) r = cached_code_map(&tmK, ck_q, (long long)G * msl, kvp);
+        if (r == TQ_OK) r = cached_code_map(&tmV, cv_q, (long long)G * msl, kvp);
+        if (r == TQ_OK) {
+            // (the shared workspace is carved per call: whatever an earlier call left where the tickets now live goes)
+            transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation, fw.w.tickets, G);
+            r = cuda_status(cudaGetLastError());
+        }
+        if (r == TQ_OK) {
+            FusedInputs in{q, nullptr, nullptr, rotation, 1, 0};
+            r = attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, pos, -1, nullptr, (long long)G * msl, msl, G,
+                               num_heads, num_kv_heads, q_dim, bits, ws, need, cs(s), false, &in);
+        }
+        g_compat_status = r;
+        return;
     }
     if (r == TQ_OK)
         r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, pos, 0, nullptr, 0, 0, msl, G,

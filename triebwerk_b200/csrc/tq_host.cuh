@@ -271,12 +271,14 @@ inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap&
     return TQ_ERR_UNSUPPORTED;
 }
 
-__global__ void transpose_rotation_kernel(__half* dst, const __half* src) {
+__global__ void transpose_rotation_kernel(__half* dst, const __half* src, int* tickets = nullptr, int n_tickets = 0) {
     // dst[d][k] = src[k][d]; one block per 32x32 tile would be overkill for 32 KB: a plain strided copy
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < HEAD_DIM * HEAD_DIM; i += gridDim.x * blockDim.x) {
         const int d = i >> 7, k = i & 127;
         dst[i] = src[k * HEAD_DIM + d];
     }
+    // optionally also clears the per-sequence tickets for a launch that is not preceded by the append kernel
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_tickets; i += gridDim.x * blockDim.x) tickets[i] = 0;
 }
 
 inline int launch_fp16_attention(const Fp16AttnParams& p, cudaStream_t s) {
