@@ -192,7 +192,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const uint32_t dyn_end = dyn_base + (uint32_t)ATTN_DYN_SMEM;
     const uint32_t n_b = dyn_end > REGION_B_ABS ? (dyn_end - REGION_B_ABS) / stage_bytes : 0u;
     const int s_fit = (int)((n_a + n_b) / ATTN_GROUPS);
-    const int S = s_fit >= 4 ? 4 : 2;       // a power of two: stage index and parity are masks and shifts
+    // 4-bit: a power of two (stage index and parity are masks and shifts).  2-bit stages are half the size and three of
+    // them fit where two 4-bit ones do: there the index and the parity are carried along instead.
+    const int S = s_fit >= 4 ? 4 : ((BITS == 2 && s_fit == 3) ? 3 : 2);
     const int s_log = s_fit >= 4 ? 2 : 1;
     auto stage_addr = [&](int s) -> uint32_t {
         const uint32_t blk = (uint32_t)(group * S + s);
@@ -349,6 +351,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     };
     int consumed = 0;
+    int s_idx = 0;          // 2-bit form: stage of the tile being consumed and the parity of its barrier
+    uint32_t s_par = 0;
     bool dead = false;  // a bounded wait gave up: keep the control flow, stop touching the pipeline
     const bool loads_on = !(p.debug & 2);
     const int total_rows_i = (int)p.total_rows;
@@ -743,10 +747,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         for (; tile < seg_end; ++tile) {
             const int t0 = (int)(tile - ts_g) * TILE_TOKENS;
             const bool full = t0 + TILE_TOKENS <= Lmin;  // warp-uniform: no token of the tile is masked for any row
-            const int s = consumed & (S - 1);
+            const int s = BITS == 2 ? s_idx : (consumed & (S - 1));
             uint32_t token = 0;  // 0 at run time; produced by the wait, so that the tile's loads cannot move above it
             if (!dead && loads_on) {
-                const uint32_t bar = bar0 + 8u * s, parity = (uint32_t)(consumed >> s_log) & 1u;
+                const uint32_t bar = bar0 + 8u * s, parity = BITS == 2 ? s_par : ((uint32_t)(consumed >> s_log) & 1u);
                 uint32_t ok = 0;
                 for (uint32_t it = 0; it < (1u << 14) && !ok; ++it) ok = mbar_try_wait_hint(bar, parity, 20000u);
                 if (!ok) {
@@ -905,6 +909,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             // Everything this warp read from the stage has been consumed by the (ordered) mma instructions above.
             // The last warp of the worker to get here re-arms the stage with the tile S ahead; nobody waits.
             ++consumed;
+            if (BITS == 2) {
+                if (++s_idx == S) {
+                    s_idx = 0;
+                    s_par ^= 1u;
+                }
+            }
             const int next_row = cl_row, next_tile = cl_tile, next_gend = cl_gend;
             const bool more = cl_tile < hi_i;
             if (more) cursor_advance();
@@ -1110,7 +1120,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     // before the CTA (and its shared memory) goes away.
     if (dead) {
         for (int n = consumed; n < consumed + S && lo + n < hi; ++n)
-            mbar_wait_bounded(bar0 + 8u * (n & (S - 1)), (uint32_t)(n >> s_log) & 1u, 1u << 16);
+            mbar_wait_bounded(bar0 + 8u * (uint32_t)(n % S), (uint32_t)(n / S) & 1u, 1u << 16);
     }
 }
 
