@@ -992,8 +992,15 @@ int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_h
             TQ_CUDA(cudaEventCreateWithFlags(&e->ev_out[c], cudaEventDisableTiming));
         }
     }
+    // The first and the last group are single layers: the first copy-in and the last copy-out are the only ones
+    // nothing can hide.
     const int chunks = NL < NC ? NL : NC;
-    auto first_layer = [&](int c) { return (int)((long long)c * NL / chunks); };
+    auto first_layer = [&](int c) {
+        if (chunks < 4) return (int)((long long)c * NL / chunks);
+        if (c <= 0) return 0;
+        if (c >= chunks) return NL;
+        return 1 + (int)((long long)(c - 1) * (NL - 2) / (chunks - 2));
+    };
     TQ_CUDA(cudaEventRecord(e->ev_begin, cs(s)));  // the staging buffers are free once earlier work on s is done
     TQ_CUDA(cudaStreamWaitEvent(e->st_in, e->ev_begin, 0));
     for (int c = 0; c < chunks; ++c) {

@@ -412,7 +412,7 @@ struct tq_engine {
     void* stage_v = nullptr;
     void* stage_out = nullptr; // [layers][G][q_dim]
     // host-buffer steps: copy streams and events that let the copies of one group of layers overlap the kernels of another
-    static constexpr int HOST_STEP_CHUNKS = 7;
+    static constexpr int HOST_STEP_CHUNKS = 9;
     cudaStream_t st_in = nullptr, st_out = nullptr;
     cudaEvent_t ev_begin = nullptr, ev_done = nullptr;
     cudaEvent_t ev_in[HOST_STEP_CHUNKS] = {}, ev_out[HOST_STEP_CHUNKS] = {};
