@@ -52,6 +52,10 @@ WORKLOADS = {
                     "context ~ U{128..16384}, kv_bits=4"),
     "c1f16": dict(layers=8, H=16, Hkv=8, G=64, L=4096, bits=0, prompt=100,
                   desc="kv_bits=0 twin of c1 (fp16 cache, 4096 B per token): 8 of 28 layers, 64 seq x ctx 4096"),
+    "c3l4": dict(layers=4, H=32, Hkv=8, G=32, L=8192, bits=2, prompt=100,
+                 desc="4 of the 36 layers of c3 (same per-layer shape; for profiler captures): 32 seq x ctx 8192, kv_bits=2"),
+    "c1f16l2": dict(layers=2, H=16, Hkv=8, G=64, L=4096, bits=0, prompt=100,
+                    desc="2 layers of c1f16 (same per-layer shape; for profiler captures): fp16 cache, 64 seq x ctx 4096"),
     "small": dict(layers=4, H=16, Hkv=8, G=16, L=2048, bits=4, prompt=100,
                   desc="reduced case for profiler captures: 4 layers, 16 seq x ctx 2048, kv_bits=4"),
 }
@@ -439,7 +443,7 @@ def run_ours(args, w, rank, world, local_rank):
                      "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "us_per_launch": attn_ms * 1e3, "algorithmic_bytes_per_launch": kernel_bytes,
-                     "traffic": TRAFFIC.get(args.workload if fused else args.workload + "/unfused")},
+                     "traffic": TRAFFIC.get(args.workload if (fused or bits == 0) else args.workload + "/unfused")},
         "clocks": clocks,
     }
     if args.cpu_seconds > 0 and world == 1:
@@ -456,6 +460,10 @@ TRAFFIC = {
     "c1": 287702784, "c1l4": 287702784,
     # profiles/decode_attention_kernel_4bit_unfused_c1_layer.md (TQ_FUSED=0): 278.32 MB read + 4.51 MB written
     "c1/unfused": 282830592, "c1l4/unfused": 282830592,
+    # profiles/decode_attention_kernel_2bit_fused_c3_layer.md: 1.453 TB/s x 104.9 us
+    "c3": 152340000, "c3l4": 152340000,
+    # profiles/fp16_decode_attention_kernel_c1f16_layer.md: 4.141 TB/s x 260.8 us
+    "c1f16": 1080060000, "c1f16l2": 1080060000,
 }
 
 
