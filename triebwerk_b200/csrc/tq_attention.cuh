@@ -226,8 +226,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     } else {
         for (int idx = tid; idx < 256 * 32; idx += blockDim.x) {
             int v = idx >> 5, l = idx & 31;
-            uint32_t lo2 = pack_half2(kCent2[v & 3], kCent2[(v >> 2) & 3]);
-            uint32_t hi2 = pack_half2(kCent2[(v >> 4) & 3], kCent2[(v >> 6) & 3]);
+            // (c0, c2), (c1, c3): the low and the high nibble each give one value to either word.  For K a byte is four
+            // coordinates of one token (the query fragments are packed in the same order); for V a byte is put together
+            // from the nibbles of two tokens, and either word is then one coordinate of that token pair.
+            uint32_t lo2 = pack_half2(kCent2[v & 3], kCent2[(v >> 4) & 3]);
+            uint32_t hi2 = pack_half2(kCent2[(v >> 2) & 3], kCent2[(v >> 6) & 3]);
             asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(LUT_ABS + (uint32_t)v * 256u + (uint32_t)l * 8u),
                          "r"(lo2), "r"(hi2) : "memory");
         }
@@ -727,14 +730,17 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                __half2 h01 = __floats2half2_rn(qv[4 * j], qv[4 * j + 1]);
-                __half2 h23 = __floats2half2_rn(qv[4 * j + 2], qv[4 * j + 3]);
+                // the 2-bit table returns the four values of a byte as (0, 2), (1, 3)
+                const float x0 = qv[4 * j], x1 = BITS == 2 ? qv[4 * j + 2] : qv[4 * j + 1];
+                const float x2 = BITS == 2 ? qv[4 * j + 1] : qv[4 * j + 2], x3 = qv[4 * j + 3];
+                __half2 h01 = __floats2half2_rn(x0, x1);
+                __half2 h23 = __floats2half2_rn(x2, x3);
                 qa[j][0] = *reinterpret_cast<uint32_t*>(&h01);
                 qa[j][QSPLIT ? 2 : 1] = *reinterpret_cast<uint32_t*>(&h23);
                 if (QSPLIT) {
                     float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                    qa[j][1] = pack_half2(qv[4 * j] - f01.x, qv[4 * j + 1] - f01.y);
-                    qa[j][3] = pack_half2(qv[4 * j + 2] - f23.x, qv[4 * j + 3] - f23.y);
+                    qa[j][1] = pack_half2(x0 - f01.x, x1 - f01.y);
+                    qa[j][3] = pack_half2(x2 - f23.x, x3 - f23.y);
                 }
             }
         }
@@ -887,17 +893,21 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                         const uint32_t xb = ldsp32(vg + vB_off);
                         const uint32_t xc = ldsp32(vg + vA_off + 1024u);
                         const uint32_t xd = ldsp32(vg + vB_off + 1024u);
+                        // As in the 4-bit form: byte b of `ev` = (low nibble of token A, low nibble of token B), `od` the high
+                        // nibbles; the table turns it into the (A, B) pairs of two coordinates, which are two rows of the operand.
+                        const uint32_t ev_ab = (xa & 0x0f0f0f0fu) | ((xb << 4) & 0xf0f0f0f0u);
+                        const uint32_t od_ab = ((xa >> 4) & 0x0f0f0f0fu) | (xb & 0xf0f0f0f0u);
+                        const uint32_t ev_cd = (xc & 0x0f0f0f0fu) | ((xd << 4) & 0xf0f0f0f0u);
+                        const uint32_t od_cd = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
 #pragma unroll
                         for (int bb = 0; bb < 4; ++bb) {
                             const uint32_t sel = 0x7604u | ((uint32_t)bb << 4);
-                            const uint2 la = ldsp64(prmt(xa, lutlane, sel));
-                            const uint2 lb = ldsp64(prmt(xb, lutlane, sel));
-                            const uint2 lc = ldsp64(prmt(xc, lutlane, sel));
-                            const uint2 ld = ldsp64(prmt(xd, lutlane, sel));
-                            mma16816(acc[2 * bb], prmt(la.x, lb.x, 0x5410u), prmt(la.x, lb.x, 0x7632u),
-                                     prmt(lc.x, ld.x, 0x5410u), prmt(lc.x, ld.x, 0x7632u), pb0, pb1);
-                            mma16816(acc[2 * bb + 1], prmt(la.y, lb.y, 0x5410u), prmt(la.y, lb.y, 0x7632u),
-                                     prmt(lc.y, ld.y, 0x5410u), prmt(lc.y, ld.y, 0x7632u), pb0, pb1);
+                            const uint2 eab = ldsp64(prmt(ev_ab, lutlane, sel));
+                            const uint2 ecd = ldsp64(prmt(ev_cd, lutlane, sel));
+                            const uint2 oab = ldsp64(prmt(od_ab, lutlane, sel));
+                            const uint2 ocd = ldsp64(prmt(od_cd, lutlane, sel));
+                            mma16816(acc[2 * bb], eab.x, eab.y, ecd.x, ecd.y, pb0, pb1);
+                            mma16816(acc[2 * bb + 1], oab.x, oab.y, ocd.x, ocd.y, pb0, pb1);
                         }
                     }
                 }
@@ -1033,29 +1043,45 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                             }
                         }
                     } else {
+                        // many parts: one round trip for all (max, sum) pairs, then the vectors 16 at a time
+#pragma unroll
                         for (int r = 0; r < 2; ++r) {
                             const int hq = hb + hh0 + r * Hkv;
                             if (hq >= H || hh0 + r * Hkv >= 16) continue;
                             const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
-                            float M = -1e30f;
-                            for (int j = lane; j < parts; j += 32) M = fmaxf(M, __ldcg(base + j * pstride + HEAD_DIM));
+                            float M = -1e30f, Z = 0.0f, m0 = -1e30f;  // m0: the max of part `lane` (parts 0 .. 31)
+                            for (int j0 = 0; j0 < parts; j0 += 32) {
+                                float2 t = make_float2(-1e30f, 0.0f);
+                                if (j0 + lane < parts) t = __ldcg(reinterpret_cast<const float2*>(base + (j0 + lane) * pstride + HEAD_DIM));
+                                if (j0 == 0) m0 = t.x;
+                                const float Mn = fmaxf(M, t.x);
+                                Z = Z * ex2_approx(M - Mn) + t.y * ex2_approx(t.x - Mn);
+                                M = Mn;
+                            }
+                            float Mw = M;
 #pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-                            float Z = 0.0f;
-                            for (int j = lane; j < parts; j += 32)
-                                Z += __ldcg(base + j * pstride + HEAD_DIM + 1) * ex2_approx(__ldcg(base + j * pstride + HEAD_DIM) - M);
+                            for (int o = 16; o > 0; o >>= 1) Mw = fmaxf(Mw, __shfl_xor_sync(0xffffffffu, Mw, o));
+                            Z *= ex2_approx(M - Mw);
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
                             const float inv = 1.0f / (Z + 1e-8f);
                             for (int j0 = 0; j0 < parts; j0 += 32) {
-                                const int jn = parts - j0 < 32 ? parts - j0 : 32;
-                                float sc = 0.0f;
-                                if (lane < jn) sc = ex2_approx(__ldcg(base + (j0 + lane) * pstride + HEAD_DIM) - M) * inv;
-                                for (int j = 0; j < jn; ++j) {
-                                    const float wj = __shfl_sync(0xffffffffu, sc, j);
-                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (j0 + j) * pstride) + lane);
-                                    a[r].x = fmaf(wj, v.x, a[r].x); a[r].y = fmaf(wj, v.y, a[r].y);
-                                    a[r].z = fmaf(wj, v.z, a[r].z); a[r].w = fmaf(wj, v.w, a[r].w);
+                                float mj = m0;
+                                if (j0 > 0) mj = j0 + lane < parts ? __ldcg(base + (j0 + lane) * pstride + HEAD_DIM) : -1e30f;
+                                const float sc = j0 + lane < parts ? ex2_approx(mj - Mw) * inv : 0.0f;
+#pragma unroll 1
+                                for (int j1 = j0; j1 < parts && j1 < j0 + 32; j1 += 16) {
+                                    float4 v[16];
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j)
+                                        v[j] = j1 + j < parts ? __ldcg(reinterpret_cast<const float4*>(base + (j1 + j) * pstride) + lane)
+                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j) {
+                                        const float wj = __shfl_sync(0xffffffffu, sc, (j1 - j0) + j);
+                                        a[r].x = fmaf(wj, v[j].x, a[r].x); a[r].y = fmaf(wj, v[j].y, a[r].y);
+                                        a[r].z = fmaf(wj, v[j].z, a[r].z); a[r].w = fmaf(wj, v[j].w, a[r].w);
+                                    }
                                 }
                             }
                         }
