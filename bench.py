@@ -462,8 +462,8 @@ TRAFFIC = {
     "c1/unfused": 282830592, "c1l4/unfused": 282830592,
     # profiles/decode_attention_kernel_2bit_fused_c3_layer.md: 1.453 TB/s x 104.9 us
     "c3": 152340000, "c3l4": 152340000,
-    # profiles/fp16_decode_attention_kernel_c1f16_layer.md: 4.141 TB/s x 260.8 us
-    "c1f16": 1080060000, "c1f16l2": 1080060000,
+    # profiles/fp16_decode_attention_kernel_c1f16_layer.md: 6.195 TB/s x 174.9 us
+    "c1f16": 1083480000, "c1f16l2": 1083480000,
 }
 
 

@@ -10,7 +10,8 @@
 //
 // A cache row of one head is 256 B, four times the packed 4-bit row, so the instruction budget per byte
 // is four times larger than on the quantised path and plain fp32 FMAs with 8-lane shuffle reductions
-// keep up with HBM: 8 lanes share a token (32 B = 16 coordinates each), a warp covers 4 tokens per step.
+// keep up with HBM: 8 lanes share a token (16 coordinates each), a warp covers 4 tokens per step, and the rows
+// reach the lanes through a per-warp ring of asynchronous 16-byte copies that runs three steps ahead.
 #pragma once
 
 #include "tq_common.cuh"
@@ -19,6 +20,7 @@ namespace tq {
 
 constexpr int FP16_CHUNK = 512;    // tokens per CTA
 constexpr int FP16_WARPS = 4;
+constexpr int FP16_STAGES = 4;   // ring slots per warp (2 KB each)
 constexpr int FP16_MAX_GRP = 8;
 
 struct Fp16AttnParams {
@@ -71,7 +73,8 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
     const int nparts = (L + FP16_CHUNK - 1) / FP16_CHUNK;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sub = lane & 7;   // which 16 coordinates of the row
+    const int sub = lane & 7;   // which 16 coordinates of the row: 8*sub .. 8*sub+7 and 64+8*sub .. 64+8*sub+7 (a copy
+                                // instruction of 8 lanes then covers 128 contiguous bytes)
     const int tg = lane >> 3;   // which of the 4 tokens of a step
     const long long row0 = p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len;
 
@@ -79,10 +82,10 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
     float qf[GRP][16];
 #pragma unroll
     for (int h = 0; h < GRP; ++h) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)g * p.q_dim + (size_t)(kvh * GRP + h) * HEAD_DIM + 16 * sub);
+        const __half* src = p.q + (size_t)g * p.q_dim + (size_t)(kvh * GRP + h) * HEAD_DIM + 8 * sub;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            uint4 u = __ldg(src + i);
+            uint4 u = __ldg(reinterpret_cast<const uint4*>(src + 64 * i));
             const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -103,16 +106,41 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
 
     // tokens of this warp: c0 + warp*4 + tg, stepping by 4*FP16_WARPS
     const int step = 4 * FP16_WARPS;
-    for (int tb = c0 + warp * 4; tb < c1; tb += step) {
-        const int tok = tb + tg;
+    // Rows travel through a per-warp ring in shared memory filled by 16-byte asynchronous copies, FP16_STAGES - 1 steps
+    // (2 KB each) ahead of the arithmetic.  Every lane reads back exactly the 64 bytes it asked for itself, so waiting
+    // for its own copy groups is all the synchronisation the ring needs.
+    __shared__ __align__(16) unsigned char sm_ring[FP16_WARPS * FP16_STAGES * 4 * 32 * 16];
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(sm_ring) + (uint32_t)warp * (FP16_STAGES * 4 * 32 * 16) + (uint32_t)lane * 16u;
+    const int t_first = c0 + warp * 4;
+    const int nsteps = t_first < c1 ? (c1 - t_first + step - 1) / step : 0;
+    auto issue = [&](int i) {
+        const int tok = t_first + i * step + tg;
+        if (i < nsteps && tok < c1) {
+            const size_t off = (size_t)(row0 + tok) * p.kv_dim + (size_t)kvh * HEAD_DIM + 8 * sub;
+            const uint32_t dst = ring + (uint32_t)(i % FP16_STAGES) * (4 * 32 * 16);
+            const __half* kp = p.ck + off;
+            const __half* vp = p.cv + off;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kp) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512u), "l"(kp + 64) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 1024u), "l"(vp) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 1536u), "l"(vp + 64) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per step, empty or not: the count stays uniform
+    };
+#pragma unroll
+    for (int i = 0; i < FP16_STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < nsteps; ++i) {
+        const int tok = t_first + i * step + tg;
         const bool valid = tok < c1;
+        issue(i + FP16_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(FP16_STAGES - 1) : "memory");
         uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
         if (valid) {
-            const size_t off = (size_t)(row0 + tok) * p.kv_dim + (size_t)kvh * HEAD_DIM + 16 * sub;
-            const uint4* kp = reinterpret_cast<const uint4*>(p.ck + off);
-            const uint4* vp = reinterpret_cast<const uint4*>(p.cv + off);
-            k0 = __ldcs(kp); k1 = __ldcs(kp + 1);
-            v0 = __ldcs(vp); v1 = __ldcs(vp + 1);
+            const uint32_t src = ring + (uint32_t)(i % FP16_STAGES) * (4 * 32 * 16);
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(k0.x), "=r"(k0.y), "=r"(k0.z), "=r"(k0.w) : "r"(src) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(k1.x), "=r"(k1.y), "=r"(k1.z), "=r"(k1.w) : "r"(src + 512u) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w) : "r"(src + 1024u) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w) : "r"(src + 1536u) : "memory");
         }
         float kf[16], vf[16];
         {
@@ -164,7 +192,11 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
     }
 
     // ---- combine the 4 token groups of the warp, then the warps ----
-    __shared__ float sm_acc[FP16_WARPS][GRP][HEAD_DIM];
+    // the ring is idle from here on (every copy group has been waited for): the per-warp results reuse its space
+    static_assert(sizeof(float) * FP16_WARPS * FP16_MAX_GRP * HEAD_DIM <= sizeof(sm_ring), "results must fit the ring");
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    float (*sm_acc)[GRP][HEAD_DIM] = reinterpret_cast<float (*)[GRP][HEAD_DIM]>(sm_ring);
     __shared__ float sm_m[FP16_WARPS][GRP], sm_l[FP16_WARPS][GRP];
     __shared__ int sm_last;
 #pragma unroll
@@ -181,7 +213,7 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
             float a = acc[h][c] * w;
             a += __shfl_xor_sync(0xffffffffu, a, 8);
             a += __shfl_xor_sync(0xffffffffu, a, 16);
-            if (tg == 0) sm_acc[warp][h][16 * sub + c] = a;
+            if (tg == 0) sm_acc[warp][h][(c < 8 ? 0 : 56) + 8 * sub + c] = a;
         }
         if (lane == 0) {
             sm_m[warp][h] = m;
