@@ -60,12 +60,15 @@ def test_rows_past_the_position_are_ignored(bits):
 
 
 @pytest.mark.parametrize("bits", [4, 2])
-def test_long_context_split_over_many_ctas(bits):
-    # 8 sequences x 4096 tokens: every sequence is cut across several CTAs and merged by the last one to arrive
+@pytest.mark.parametrize("copies", [1, 3])
+def test_long_context_split_over_many_ctas(bits, copies):
+    # 8 (24) sequences x 4096 tokens: every sequence is cut across ~37 (~12) workers and merged by the last one to
+    # arrive; the merge has one path for up to 8 parts, one for more, and reloads its weights every 32 parts
     rng = np.random.default_rng(30)
     R, _ = tqo.rotation()
-    G, H, Hkv, D, msl = 8, 16, 8, 128, 4096
-    lengths = [4096, 4096, 4095, 4065, 3000, 4096, 17, 4096]
+    H, Hkv, D, msl = 16, 8, 128, 4096
+    lengths = [4096, 4096, 4095, 4065, 3000, 4096, 17, 4096] * copies
+    G = len(lengths)
     ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R, _scales(Hkv * D))
     q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
     pos = np.array(lengths, np.int32) - 1
