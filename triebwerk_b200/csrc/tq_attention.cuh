@@ -778,35 +778,45 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
                 // ---------------- scores: 4 blocks of 8 tokens ----------------
                 float sv[8];
+                {
+                    // the four 8-token blocks advance together: four independent accumulator chains
+                    float c[4][4];
+                    uint32_t w[4][4];
 #pragma unroll
-                for (int blk = 0; blk < 4; ++blk) {
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (BITS == 4) {
-                        const uint4 kw = ldsp128(kt + (uint32_t)blk * 1024u + k_off);
-                        const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t word = w[j >> 1];
-                            const uint32_t b0 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7624u : 0x7604u));
-                            const uint32_t b1 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7634u : 0x7614u));
-                            if (QSPLIT) mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], b0, b1);
-                            else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, b0, b1);
-                        }
-                    } else {
-                        const uint2 kw = ldsp64(kt + (uint32_t)blk * 1024u + k_off);
-                        const uint32_t w[2] = {kw.x, kw.y};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t word = w[j >> 2];
-                            const uint2 bb = ldsp64(prmt(word, lutlane, 0x7604u | ((uint32_t)(j & 3) << 4)));
-                            if (QSPLIT) mma16816(c, qa[j][0], qa[j][1], qa[j][2], qa[j][3], bb.x, bb.y);
-                            else mma16816(c, qa[j][0], 0u, qa[j][1], 0u, bb.x, bb.y);
+                    for (int blk = 0; blk < 4; ++blk) {
+                        c[blk][0] = c[blk][1] = c[blk][2] = c[blk][3] = 0.0f;
+                        if (BITS == 4) {
+                            const uint4 kw = ldsp128(kt + (uint32_t)blk * 1024u + k_off);
+                            w[blk][0] = kw.x; w[blk][1] = kw.y; w[blk][2] = kw.z; w[blk][3] = kw.w;
+                        } else {
+                            const uint2 kw = ldsp64(kt + (uint32_t)blk * 1024u + k_off);
+                            w[blk][0] = kw.x; w[blk][1] = kw.y; w[blk][2] = w[blk][3] = 0u;
                         }
                     }
-                    const float k0 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokA) * nstride);
-                    const float k1 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokB) * nstride);
-                    sv[2 * blk] = (QSPLIT ? c[0] + c[2] : c[0]) * k0;
-                    sv[2 * blk + 1] = (QSPLIT ? c[1] + c[3] : c[1]) * k1;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                        for (int blk = 0; blk < 4; ++blk) {
+                            uint32_t b0, b1;
+                            if (BITS == 4) {
+                                const uint32_t word = w[blk][j >> 1];
+                                b0 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7624u : 0x7604u));
+                                b1 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7634u : 0x7614u));
+                            } else {
+                                const uint2 bb = ldsp64(prmt(w[blk][j >> 2], lutlane, 0x7604u | ((uint32_t)(j & 3) << 4)));
+                                b0 = bb.x; b1 = bb.y;
+                            }
+                            if (QSPLIT) mma16816(c[blk], qa[j][0], qa[j][1], qa[j][2], qa[j][3], b0, b1);
+                            else mma16816(c[blk], qa[j][0], 0u, qa[j][1], 0u, b0, b1);
+                        }
+                    }
+#pragma unroll
+                    for (int blk = 0; blk < 4; ++blk) {
+                        const float k0 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokA) * nstride);
+                        const float k1 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokB) * nstride);
+                        sv[2 * blk] = (QSPLIT ? c[blk][0] + c[blk][2] : c[blk][0]) * k0;
+                        sv[2 * blk + 1] = (QSPLIT ? c[blk][1] + c[blk][3] : c[blk][1]) * k1;
+                    }
                 }
 
                 // ---------------- online softmax (row = head gl; rows >= grp carry zeros and are never read) ----
