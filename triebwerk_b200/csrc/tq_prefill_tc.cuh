@@ -203,6 +203,19 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 #pragma unroll
             for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
         }
+        {   // the CTA's next tile (same kind or the other one) on its way into L2 while this one is worked on
+            const int ntile = tile + (int)gridDim.x;
+            if (ntile < total_tiles) {
+                const int nkind = (p.k_buf && ntile < tiles_per_kind) ? 0 : 1;
+                const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + tid;
+                if (nvid < vec_per_kind) {
+                    const int ntok = nvid / p.Hkv, nhead = nvid - ntok * p.Hkv;
+                    const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 64));
+                }
+            }
+        }
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
             const int v = pass * 32 + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
