@@ -15,15 +15,15 @@
 //     |R row| = 1): once for the chain, once for the tensor-core sum.  About 1 coordinate in 700 takes the exact path.
 // Sums of squares, rsqrt/sqrt and the norm use the reference's own order and instructions (see tq_append.cuh).
 //
-// One CTA = 128 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), two CTAs per SM:
+// One CTA = 256 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), two CTAs per SM:
 //   1. thread (vector, 32-coordinate chunk) loads 64 bytes, builds the reference's shuffle-tree sum of squares in
 //      registers, the four chunk sums meet by shuffles; hi/lo go to shared memory in the canonical K-major
 //      128-byte-swizzled operand layout (rows of 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7));
 //   2. one thread issues 16 tcgen05.mma (2 operands x 8 K-steps of 16) against the resident R tile and commits to
 //      an mbarrier; every wait is bounded;
-//   3. each thread reads ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per warp
-//      and instruction), quantises through a 512-bucket uniform grid (bucket -> code, or -> the one bound inside
-//      it), packs, and queues near-bound coordinates;
+//   3. each thread reads 64 of ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per
+//      warp and instruction; warps w and w + 4 share a lane quarter), quantises through a 512-bucket uniform grid
+//      (bucket -> code, or -> the one bound inside it), packs, and queues near-bound coordinates;
 //   4. queued coordinates get the exact chain and patch the packed tile; the tile leaves as coalesced 16-byte stores.
 #pragma once
 
@@ -32,7 +32,7 @@
 namespace tq {
 
 constexpr int TC_TILE = 128;       // head vectors per tile = MMA M
-constexpr int TC_THREADS = 128;
+constexpr int TC_THREADS = 256;
 constexpr float TC_MARGIN = 1.6e-5f;
 constexpr int TC_LIST_CAP = 256;   // queued near-bound coordinates per tile; the rest is handled by their owners
 
@@ -193,10 +193,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         if (tid == 0) ctrl[3] = 0;
 
         // ---- 1. load, sum of squares in the reference's order, normalise, split, write the A operand ----
-        uint4 raw_all[4][4];
+        constexpr int PASSES = 4 * TC_TILE / TC_THREADS, VPP = TC_THREADS / 4;  // passes per tile, vectors per pass
+        uint4 raw_all[PASSES][4];
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {  // every load of the tile goes out before the arithmetic starts
-            const int vid = vec0 + pass * 32 + (tid >> 2);
+        for (int pass = 0; pass < PASSES; ++pass) {  // every load of the tile goes out before the arithmetic starts
+            const int vid = vec0 + pass * VPP + (tid >> 2);
             const bool live = vid < vec_per_kind;
             const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;  // tok = sequence * T + t
             const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * (tid & 3));
@@ -207,18 +208,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             const int ntile = tile + (int)gridDim.x;
             if (ntile < total_tiles) {
                 const int nkind = (p.k_buf && ntile < tiles_per_kind) ? 0 : 1;
-                const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + tid;
-                if (nvid < vec_per_kind) {
+                const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + (tid >> 1);
+                if (nvid < vec_per_kind) {  // one 128-byte line per thread
                     const int ntok = nvid / p.Hkv, nhead = nvid - ntok * p.Hkv;
-                    const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM;
+                    const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM + 64 * (tid & 1);
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 64));
                 }
             }
         }
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-            const int v = pass * 32 + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
+        for (int pass = 0; pass < PASSES; ++pass) {
+            const int v = pass * VPP + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
             const int vid = vec0 + v;
             const bool live = vid < vec_per_kind;
             const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;
@@ -262,22 +262,21 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 rows_s[v] = row;
                 inv_s[v] = inv;
             }
-            uint32_t hi_w[16], lo_w[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float x0 = mul_ftz(val[2 * i], inv), x1 = mul_ftz(val[2 * i + 1], inv);
-                const __half2 h = __floats2half2_rn(x0, x1);
-                const float2 hf = __half22float2(h);
-                hi_w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                lo_w[i] = pack_half2((x0 - hf.x) * 4096.0f, (x1 - hf.y) * 4096.0f);
-            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // 16-byte chunks: coordinates 32c + 8i .. + 7
+                uint32_t hw[4], lw[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x0 = mul_ftz(val[8 * i + 2 * e], inv), x1 = mul_ftz(val[8 * i + 2 * e + 1], inv);
+                    const __half2 h = __floats2half2_rn(x0, x1);
+                    const float2 hf = __half22float2(h);
+                    hw[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    lw[e] = pack_half2((x0 - hf.x) * 4096.0f, (x1 - hf.y) * 4096.0f);
+                }
                 const uint32_t a = tc_operand_addr(base + TcSmem::A_HI, v, 32 * c + 8 * i);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(hi_w[4 * i]), "r"(hi_w[4 * i + 1]),
-                             "r"(hi_w[4 * i + 2]), "r"(hi_w[4 * i + 3]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a + (TcSmem::A_LO - TcSmem::A_HI)), "r"(lo_w[4 * i]),
-                             "r"(lo_w[4 * i + 1]), "r"(lo_w[4 * i + 2]), "r"(lo_w[4 * i + 3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(hw[0]), "r"(hw[1]), "r"(hw[2]), "r"(hw[3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a + (TcSmem::A_LO - TcSmem::A_HI)), "r"(lw[0]),
+                             "r"(lw[1]), "r"(lw[2]), "r"(lw[3]) : "memory");
             }
         }
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
@@ -305,14 +304,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         phase ^= 1u;
         tc_fence_after();
 
-        // ---- 3. accumulators -> codes; thread `tid` owns vector `tid` of the tile (TMEM lane tid) ----
+        // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
+        //         w + 4 share those vectors and take 64 of the 128 coordinates (two blocks of 32 columns) each ----
         const int nan_code = bits == 4 ? 15 : 0;  // what the reference's comparisons make of a NaN
-        uint32_t own_cc[4] = {0u, 0u, 0u, 0u};  // near-bound coordinates that did not fit the shared queue
+        const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
+        const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
+        uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
         if (!dead) {
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = cc0; cc < cc0 + 2; ++cc) {
                 uint32_t hi_r[32], lo_r[32];
-                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc * 32u;
+                const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cc * 32u;
                 tmem_ld32(taddr, hi_r);
                 tmem_ld32(taddr + 128u, lo_r);
                 tmem_ld_wait();
@@ -338,10 +340,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                     const int i = __ffs(near_mask) - 1;
                     near_mask &= near_mask - 1;
                     const uint32_t slot = atomicAdd(const_cast<uint32_t*>(&ctrl[3]), 1u);
-                    if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)tid << 8) | (uint32_t)(32 * cc + i);
-                    else own_cc[cc] |= 1u << i;
+                    if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)ev << 8) | (uint32_t)(32 * cc + i);
+                    else own_cc[cc - cc0] |= 1u << i;
                 }
-                uint8_t* st = gbase + TcSmem::STAGE + (size_t)tid * bpv;
+                uint8_t* st = gbase + TcSmem::STAGE + (size_t)ev * bpv;
                 if (bits == 4) *reinterpret_cast<uint4*>(st + 16 * cc) = make_uint4(words[0], words[1], words[2], words[3]);
                 else *reinterpret_cast<uint2*>(st + 8 * cc) = make_uint2(words[0], words[1]);
             }
@@ -388,13 +390,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 const int v = (int)(item >> 8), d = (int)(item & 255u);
                 if (vec0 + v < vec_per_kind) patch(v, d, exact_code(v, d));
             }
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t m = own_cc[cc];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                uint32_t m = own_cc[k];
                 while (m) {
                     const int i = __ffs(m) - 1;
                     m &= m - 1;
-                    if (vec0 + tid < vec_per_kind) patch(tid, 32 * cc + i, exact_code(tid, 32 * cc + i));
+                    if (vec0 + ev < vec_per_kind) patch(ev, 32 * (cc0 + k) + i, exact_code(ev, 32 * (cc0 + k) + i));
                 }
             }
         }
