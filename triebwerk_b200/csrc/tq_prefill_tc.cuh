@@ -384,11 +384,50 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             atomicOr(w, (uint32_t)code << sh);
         };
         if (!dead) {
+            // Queued coordinates: 8 lanes per item.  Lane s of the group prepares terms k = 16 s .. 16 s + 15 (R from the
+            // shared-memory operand tile, x from the input, x / norm as the reference forms it); the k-ascending chain
+            // then runs through the lanes in order, the running sum handed on by a shuffle.
             const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
-            for (uint32_t i = tid; i < queued; i += TC_THREADS) {
-                const uint32_t item = list_s[i];
+            const int sub = lane & 7;
+            for (uint32_t i0 = (uint32_t)warp * 4u; i0 < queued; i0 += (TC_THREADS / 32) * 4) {  // warp-uniform
+                const uint32_t i = i0 + (uint32_t)(lane >> 3);
+                const uint32_t item = i < queued ? list_s[i] : 0u;
                 const int v = (int)(item >> 8), d = (int)(item & 255u);
-                if (vec0 + v < vec_per_kind) patch(v, d, exact_code(v, d));
+                const bool live = i < queued && vec0 + v < vec_per_kind;
+                float xs[16], rr[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) xs[e] = rr[e] = 0.0f;
+                if (live) {
+                    const int vid = vec0 + v;
+                    const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
+                    const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM) + 2 * sub;
+                    const float inv = inv_s[v];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const uint4 xv = __ldg(src + j);
+                        const uint4 rv = *reinterpret_cast<const uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 16 * sub + 8 * j) - base));
+                        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                        const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                            xs[8 * j + 2 * e] = mul_ftz(xf.x, inv);
+                            xs[8 * j + 2 * e + 1] = mul_ftz(xf.y, inv);
+                            rr[8 * j + 2 * e] = rf.x;
+                            rr[8 * j + 2 * e + 1] = rf.y;
+                        }
+                    }
+                }
+                float acc = 0.0f;
+#pragma unroll
+                for (int st = 0; st < 8; ++st) {
+                    if (sub == st) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) acc = fma_ftz(rr[e], xs[e], acc);
+                    }
+                    acc = __shfl_sync(0xffffffffu, acc, (lane & ~7) + st);
+                }
+                if (live && sub == 0) patch(v, d, quantize_code(acc, bits));
             }
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
