@@ -460,8 +460,8 @@ TRAFFIC = {
     "c1": 287702784, "c1l4": 287702784,
     # profiles/decode_attention_kernel_4bit_unfused_c1_layer.md (TQ_FUSED=0): 278.32 MB read + 4.51 MB written
     "c1/unfused": 282830592, "c1l4/unfused": 282830592,
-    # profiles/decode_attention_kernel_2bit_fused_c3_layer.md: 1.453 TB/s x 104.9 us
-    "c3": 152340000, "c3l4": 152340000,
+    # profiles/decode_attention_kernel_2bit_fused_c3_layer.md: 1.576 TB/s x 95.2 us
+    "c3": 150060000, "c3l4": 150060000,
     # profiles/fp16_decode_attention_kernel_c1f16_layer.md: 6.195 TB/s x 174.9 us
     "c1f16": 1083480000, "c1f16l2": 1083480000,
 }
