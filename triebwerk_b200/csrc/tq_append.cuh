@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(APPEND_THREADS) append_rotate_kernel(const App
         for (int w = 0; w < 4; ++w) before += (w < wid) ? scan[w] : 0;
         const int N = scan[0] + scan[1] + scan[2] + scan[3];
         int run = before + incl - local;  // exclusive
-        const int W = p.n_workers < N ? p.n_workers : N;
+        const int W = attention_workers(p.n_workers, N, G);
         for (int i = 0; i < per; ++i) {
             int g = d * per + i;
             if (g < G) {

@@ -291,10 +291,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const long long N = ts[G];
 
     // ---- work slice of this worker ----
-    // Only min(workers, N) workers take part, so that every participant owns at least one tile: the ticket
-    // count of a sequence is then simply (last owner - first owner + 1).
+    // At most min(workers, N) workers take part, so that every participant owns at least one tile: the ticket
+    // count of a sequence is then simply (last owner - first owner + 1).  Fewer when the list is short.
     const long long w_all = (long long)gridDim.x * ATTN_GROUPS;
-    const int W = w_all < N ? (int)w_all : (int)N;
+    const int W = attention_workers(w_all, N, G, (p.debug >> 8) ? (p.debug >> 8) : 16);  // debug bits 8+: another factor (timing experiments)
     const int wid = blockIdx.x * ATTN_GROUPS + group;
     if (wid >= W) return;  // uniform for the worker; no CTA-wide barrier follows
     // The flat list is cut in UNITS: a tile is one unit, except the last tile of a sequence, which counts 1 + A units
@@ -325,7 +325,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         lo = (long long)wid * N / W;
         hi = (long long)(wid + 1) * N / W;
         // first sequence of the slice: largest g with tile_start[g] <= lo
-        if (p.worker_g) {
+        if (p.worker_g && !(p.debug >> 8)) {
             g = p.worker_g[wid];
         } else {
             int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
