@@ -426,6 +426,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             const uint32_t hi_a = merge_s, lo_a = merge_s + 16u * MERGE_ROW * 2u;  // A operands [16][MERGE_ROW] fp16 (idle merge area)
             const uint32_t app_a = a_base + RegionA::FUSED_APP_OFF + (uint32_t)group * RegionA::FUSED_APP_GROUP_BYTES;
             const uint32_t codes_a = app_a, inv_a = app_a + 2048u;  // codes [16][128] u8, 1/norm [16] f32
+            const uint32_t qcnt_a = app_a + 2112u, queue_a = app_a + 2128u;  // near-bound coordinates: count, [APPEND_QUEUE] items
+            constexpr uint32_t APPEND_QUEUE = 64;
             const __half* rot_w = p.rotation + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);
             for (int ga = g_app0; ga < G && ts[ga + 1] - 1 < hi_i; ++ga) {
                 const int pos = p.positions ? p.positions[ga] : p.pos_value;
@@ -439,6 +441,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
                     for (int m = 0; m < 4; ++m) bq[nbi][m] = __ldg(rr + 4 * m);
                 }
+                if (gtid == gthreads - 1) asm volatile("st.shared.u32 [%0], %1;" ::"r"(qcnt_a), "r"(0u) : "memory");
                 // ---- thread (vector v, 32-coordinate chunk c): sum of squares in the reference's order, norm, hi/lo ----
                 if (gtid < NVEC * 4) {
                     const int v = gtid >> 2, c = gtid & 3;
@@ -561,9 +564,67 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                             for (int i = 0; i < 3; ++i) dist = fminf(dist, fabsf(dval - kBnd2[i]));
                         }
                         if (v < NVEC) {
-                            if (dist < APPEND_MARGIN) code = exact_code(v, d);
+                            if (dist < APPEND_MARGIN) {  // rare (about 1 coordinate in 700): queued for the exact chain below
+                                const uint32_t slot = atom_add_shared(qcnt_a, 1u);
+                                if (slot < APPEND_QUEUE)
+                                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(queue_a + 4u * slot), "r"((uint32_t)(v << 8 | d)) : "memory");
+                                else
+                                    code = exact_code(v, d);
+                            }
                             asm volatile("st.shared.u8 [%0], %1;" ::"r"(codes_a + (uint32_t)(v * HEAD_DIM + d)), "r"(code) : "memory");
                         }
+                    }
+                }
+                group_barrier(group, gthreads);
+                // ---- the exact chain of the reference for the queued coordinates, 8 lanes per item: lane s of a group
+                //      prepares terms k = 16 s .. 16 s + 15 (one round trip for everything), then the k-ascending chain
+                //      runs through the lanes in order, the running sum handed on by a shuffle ----
+                {
+                    uint32_t queued;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(queued) : "r"(qcnt_a) : "memory");
+                    queued = queued < APPEND_QUEUE ? queued : APPEND_QUEUE;
+                    const int sub = lane & 7;
+                    for (uint32_t i0 = (uint32_t)head * 4u; i0 < queued; i0 += (uint32_t)Hkv * 4u) {  // warp-uniform
+                        const uint32_t i = i0 + (uint32_t)(lane >> 3);
+                        const bool live = i < queued;
+                        uint32_t item = 0u;
+                        if (live) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(item) : "r"(queue_a + 4u * i) : "memory");
+                        const int v = (int)(item >> 8), d = (int)(item & 255u);
+                        float xs[16], rr[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) xs[e] = rr[e] = 0.0f;
+                        if (live) {
+                            const uint4* xsrc = reinterpret_cast<const uint4*>((v < Hkv ? p.new_k : p.new_v) + (size_t)ga * p.kv_dim +
+                                                                               (size_t)(v % Hkv) * HEAD_DIM) + 2 * sub;
+                            const uint4* rsrc = reinterpret_cast<const uint4*>(rot_w + (size_t)d * HEAD_DIM) + 2 * sub;
+                            float inv;
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(inv) : "r"(inv_a + (uint32_t)v * 4u) : "memory");
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const uint4 xv = __ldg(xsrc + j), rv = __ldg(rsrc + j);
+                                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                                    xs[8 * j + 2 * e] = mul_ftz(xf.x, inv);
+                                    xs[8 * j + 2 * e + 1] = mul_ftz(xf.y, inv);
+                                    rr[8 * j + 2 * e] = rf.x;
+                                    rr[8 * j + 2 * e + 1] = rf.y;
+                                }
+                            }
+                        }
+                        float acc = 0.0f;
+#pragma unroll
+                        for (int st = 0; st < 8; ++st) {
+                            if (sub == st) {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) acc = fma_ftz(rr[e], xs[e], acc);
+                            }
+                            acc = __shfl_sync(0xffffffffu, acc, (lane & ~7) + st);
+                        }
+                        if (live && sub == 0)
+                            asm volatile("st.shared.u8 [%0], %1;" ::"r"(codes_a + (uint32_t)(v * HEAD_DIM + d)), "r"(quantize_code(acc, BITS)) : "memory");
                     }
                 }
                 group_barrier(group, gthreads);
