@@ -81,3 +81,27 @@ def test_fp16_against_reference_kernel_outputs():
     ops.launch_gqa_attention_batch(out, gu.dev(hp.h(g["q"])), dck, dcv, None, gu.dev(g["final_pos"]), msl, G, H, Hkv, D,
                                    H * D, Hkv * D)
     hp.assert_attention_close(gu.host(out), hp.h(g["out"]), H, D, "fp16 vs reference kernels")
+
+
+@pytest.mark.parametrize("H,Hkv", [(16, 4), (32, 4), (8, 8)])
+def test_fp16_attention_many_chunks_and_wide_groups(H, Hkv):
+    """Contexts of several 512-token chunks (ticketed merge), chunk tails of every length modulo the 16-token step of
+    a CTA, and 4 or 8 query heads per KV head."""
+    rng = np.random.default_rng(50 + H + Hkv)
+    D, msl = 128, 2100
+    lengths = [2100, 2049, 1537, 1025, 515, 514, 513, 17, 16, 15, 5, 4, 3]
+    G = len(lengths)
+    ck, cv = _fill(rng, G, lengths, msl, Hkv * D)
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    ref, _ = tqo.fp16_attention_batch(q, ck, cv, pos, msl, H, Hkv, D)
+    out = torch.zeros(G, H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_attention_batch(out, gu.dev(q), gu.dev(ck), gu.dev(cv), None, gu.dev(pos), msl, G, H, Hkv, D, H * D,
+                                   Hkv * D)
+    worst, rel = hp.assert_attention_close(gu.host(out), ref, H, D, f"fp16 H={H} Hkv={Hkv}")
+    print(f"fp16 H={H} Hkv={Hkv}: max-abs {worst:.2e}, rel {rel:.2e}")
+    # a second launch on the same workspace: tickets must have been left ready
+    out2 = torch.zeros_like(out)
+    ops.launch_gqa_attention_batch(out2, gu.dev(q), gu.dev(ck), gu.dev(cv), None, gu.dev(pos), msl, G, H, Hkv, D, H * D,
+                                   Hkv * D)
+    assert torch.equal(out, out2)
