@@ -297,8 +297,8 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
     if (!out || !q || !ck || !cv) return TQ_ERR_ARG;
     if (!positions && pos_value < 0) return TQ_ERR_ARG;
     if (!workspace) return TQ_ERR_WORKSPACE;
-    // fp16 layout of the workspace: [0,256) header, tickets int[G*Hkv], partials
-    const size_t tick_bytes = align_up((size_t)G * num_kv_heads * sizeof(int), 256);
+    // fp16 layout of the workspace: [0,256) header, tickets int[G*H] (one per sequence and virtual KV head, at most H), partials
+    const size_t tick_bytes = align_up((size_t)G * num_heads * sizeof(int), 256);
     const size_t need = 256 + tick_bytes + fp16_partials_bytes(G, num_heads, max_seq_len);
     if (need > workspace_bytes) return TQ_ERR_WORKSPACE;
     char* base = (char*)workspace;
@@ -309,12 +309,12 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
     p.pos_value = pos_value; p.max_seq_len = max_seq_len;
     p.nchunk_max = (max_seq_len + FP16_CHUNK - 1) / FP16_CHUNK;
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim;
-    TQ_CUDA(cudaMemsetAsync(p.tickets, 0, (size_t)G * num_kv_heads * sizeof(int), cs(s)));
+    TQ_CUDA(cudaMemsetAsync(p.tickets, 0, (size_t)G * num_heads * sizeof(int), cs(s)));
     return launch_fp16_attention(p, cs(s));
 }
 
 static size_t fp16_workspace_bytes(int G, int H, int Hkv, int max_seq_len) {
-    return 256 + align_up((size_t)G * Hkv * sizeof(int), 256) + fp16_partials_bytes(G, H, max_seq_len);
+    return 256 + align_up((size_t)G * H * sizeof(int), 256) + fp16_partials_bytes(G, H, max_seq_len);
 }
 
 // ===================================================================================================================

@@ -21,6 +21,7 @@ namespace tq {
 constexpr int FP16_CHUNK = 512;    // tokens per CTA
 constexpr int FP16_WARPS = 4;
 constexpr int FP16_STAGES = 4;   // ring slots per warp (2 KB each)
+constexpr int FP16_RING_BYTES = FP16_WARPS * FP16_STAGES * 4 * 32 * 16;
 constexpr int FP16_MAX_GRP = 8;
 
 struct Fp16AttnParams {
@@ -36,7 +37,8 @@ struct Fp16AttnParams {
     int pos_value;
     int max_seq_len;
     int nchunk_max;
-    int G, H, Hkv, q_dim, kv_dim;
+    int G, H, Hkv, q_dim, kv_dim;  // Hkv counts VIRTUAL KV heads: real heads << KV_SHIFT (2^KV_SHIFT CTAs share the
+                                   // rows of one real KV head, each serving GRP of its query heads)
 };
 
 __global__ void fp16_cache_write_kernel(__half* ck, __half* cv, const __half* k, const __half* v, const int* positions,
@@ -61,7 +63,7 @@ __global__ void fp16_cache_write_kernel(__half* ck, __half* cv, const __half* k,
     }
 }
 
-template <int GRP>
+template <int GRP, int KV_SHIFT>
 __global__ void __launch_bounds__(FP16_WARPS * 32)
 fp16_decode_attention_kernel(const Fp16AttnParams p) {
     const int kvh = blockIdx.x, chunk = blockIdx.y, g = blockIdx.z;
@@ -109,14 +111,14 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
     // Rows travel through a per-warp ring in shared memory filled by 16-byte asynchronous copies, FP16_STAGES - 1 steps
     // (2 KB each) ahead of the arithmetic.  Every lane reads back exactly the 64 bytes it asked for itself, so waiting
     // for its own copy groups is all the synchronisation the ring needs.
-    __shared__ __align__(16) unsigned char sm_ring[FP16_WARPS * FP16_STAGES * 4 * 32 * 16];
+    __shared__ __align__(16) unsigned char sm_ring[FP16_RING_BYTES];
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(sm_ring) + (uint32_t)warp * (FP16_STAGES * 4 * 32 * 16) + (uint32_t)lane * 16u;
     const int t_first = c0 + warp * 4;
     const int nsteps = t_first < c1 ? (c1 - t_first + step - 1) / step : 0;
     auto issue = [&](int i) {
         const int tok = t_first + i * step + tg;
         if (i < nsteps && tok < c1) {
-            const size_t off = (size_t)(row0 + tok) * p.kv_dim + (size_t)kvh * HEAD_DIM + 8 * sub;
+            const size_t off = (size_t)(row0 + tok) * p.kv_dim + (size_t)(kvh >> KV_SHIFT) * HEAD_DIM + 8 * sub;
             const uint32_t dst = ring + (uint32_t)(i % FP16_STAGES) * (4 * 32 * 16);
             const __half* kp = p.ck + off;
             const __half* vp = p.cv + off;
@@ -193,7 +195,7 @@ fp16_decode_attention_kernel(const Fp16AttnParams p) {
 
     // ---- combine the 4 token groups of the warp, then the warps ----
     // the ring is idle from here on (every copy group has been waited for): the per-warp results reuse its space
-    static_assert(sizeof(float) * FP16_WARPS * FP16_MAX_GRP * HEAD_DIM <= sizeof(sm_ring), "results must fit the ring");
+    static_assert(sizeof(float) * FP16_WARPS * GRP * HEAD_DIM <= FP16_RING_BYTES, "results must fit the ring");
     asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     float (*sm_acc)[GRP][HEAD_DIM] = reinterpret_cast<float (*)[GRP][HEAD_DIM]>(sm_ring);

@@ -281,15 +281,20 @@ __global__ void transpose_rotation_kernel(__half* dst, const __half* src, int* t
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_tickets; i += gridDim.x * blockDim.x) tickets[i] = 0;
 }
 
-inline int launch_fp16_attention(const Fp16AttnParams& p, cudaStream_t s) {
-    const int grp = p.H / p.Hkv;
+inline int launch_fp16_attention(const Fp16AttnParams& p_in, cudaStream_t s) {
+    // A CTA serves at most two query heads per pass over the rows (more cost it its occupancy: 47 % of the copy
+    // bandwidth with four, 23 % with eight).  With 4 or 8 query heads per KV head, 2 or 4 CTAs share the rows of a KV
+    // head as "virtual" KV heads; they are neighbours in the grid, so all but the first read the rows from L2.
+    const int grp = p_in.H / p_in.Hkv;
+    Fp16AttnParams p = p_in;
+    p.Hkv = p_in.Hkv << (grp == 4 ? 1 : (grp == 8 ? 2 : 0));
     dim3 grid(p.Hkv, p.nchunk_max, p.G);  // KV heads fastest: CTAs that run together read the same 2 KB rows (DRAM page locality)
     dim3 block(FP16_WARPS * 32);
     switch (grp) {
-        case 1: fp16_decode_attention_kernel<1><<<grid, block, 0, s>>>(p); break;
-        case 2: fp16_decode_attention_kernel<2><<<grid, block, 0, s>>>(p); break;
-        case 4: fp16_decode_attention_kernel<4><<<grid, block, 0, s>>>(p); break;
-        case 8: fp16_decode_attention_kernel<8><<<grid, block, 0, s>>>(p); break;
+        case 1: fp16_decode_attention_kernel<1, 0><<<grid, block, 0, s>>>(p); break;
+        case 2: fp16_decode_attention_kernel<2, 0><<<grid, block, 0, s>>>(p); break;
+        case 4: fp16_decode_attention_kernel<2, 1><<<grid, block, 0, s>>>(p); break;
+        case 8: fp16_decode_attention_kernel<2, 2><<<grid, block, 0, s>>>(p); break;
         default: return TQ_ERR_UNSUPPORTED;
     }
     return cuda_status(cudaGetLastError());
