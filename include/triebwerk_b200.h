@@ -255,8 +255,20 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s);
 /* tq_engine_attend_layer for every layer in turn: out [layers][G][q_dim] on the device. */
 int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s);
 
-/* Every layer of a decode step on DEVICE buffers: q/out [layers][G][q_dim], k/v [layers][G][kv_dim]. */
+/* Every layer of a decode step on DEVICE buffers: q/out [layers][G][q_dim], k/v [layers][G][kv_dim]; the layers'
+ * append + attention of forward_layer_batch (engine/engine.cpp:1979-2006) for callers that hold all layers' q/k/v
+ * at once.  Packed modes run it as three launches whatever the number of layers (one append of every layer's new
+ * token, one attention launch that streams the layers back to back, one merge); set TQ_WHOLE_STEP=0 in the
+ * environment to get one launch per layer instead. */
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
+
+/* Error reporting aid, packed modes: with enable != 0 the engine also keeps every attention result as fp32, i.e. before
+ * its final rounding to fp16 ([layers][G][num_heads][128], allocated outside the arena; call after
+ * tq_engine_alloc_batch, and again after the batch shape changes); enable == 0 frees the buffer.
+ * tq_engine_read_output_f32 copies n_layers layers of it to host memory and synchronises the stream.  No counterpart
+ * in the reference (its kernels round to fp16 in registers, engine/kernels.cu:1772-1775). */
+int tq_engine_output_f32(tq_engine* e, int enable);
+int tq_engine_read_output_f32(tq_engine* e, float* host_out, int first_layer, int n_layers, tq_stream_t s);
 
 /* Token-form append of T tokens of sequence `seq` (prefill, engine/engine.cpp:2121-2130): k/v
  * [T][kv_dim] fp16 on the device, written at positions first_pos .. first_pos+T-1. */

@@ -60,9 +60,10 @@ def test_config3_shape_two_bit_32_heads_8192_tokens(fused):
     v_new = torch.randn(NL, G, kv_dim, generator=gen, device="cuda").to(torch.float16)
     q = torch.randn(NL, G, q_dim, generator=gen, device="cuda").to(torch.float16)
     out = torch.empty_like(q)
+    eng.enable_output_f32()
     eng.decode_step(q, k_new, v_new, out)
     assert eng.status() == 0
-    out_f32 = eng.last_output_f32(NL) if hasattr(eng, "last_output_f32") else None
+    out_f32 = eng.last_output_f32(NL)
     out = gu.host(out)
     for (layer, g), (kh, vh) in keep.items():
         kk = np.concatenate([kh, gu.host(k_new[layer, g:g + 1])])
@@ -97,9 +98,11 @@ def test_config4_shape_ragged_slots_up_to_16384(bits):
     q = synth.q_batch(rng, G, q_dim)
     k_new = np.stack([s[0][-1] for s in seqs])
     v_new = np.stack([s[1][-1] for s in seqs])
+    if bits != 0:
+        eng.enable_output_f32()
     out = gu.host(eng.decode_layer(0, gu.dev(q), gu.dev(k_new), gu.dev(v_new)))
     assert eng.status() == 0
-    out_f32 = eng.last_output_f32(1)[0] if hasattr(eng, "last_output_f32") and bits != 0 else None
+    out_f32 = eng.last_output_f32(1)[0] if bits != 0 else None
     worst = worst32 = 0.0
     for g, (k, v) in enumerate(seqs):
         ref, ref32 = _oracle_single(q[g], k, v, R, H, Hkv, bits)

@@ -60,6 +60,7 @@ struct AttnParams {
     const float* q_rot;        // [G][H][128], pre-scaled by log2(e)/sqrt(128)
     const __half* rotation_t;  // R transposed: rotation_t[d][k] = R[k][d]
     __half* out;               // [G][q_dim]
+    float* out_f32;            // optional [G][H][128]: the same results before the rounding to fp16 (error reports), or null
     const int* positions;      // device [G] or null
     const long long* row_base;
     const int* tile_start;     // [G+1]
@@ -88,8 +89,29 @@ struct AttnParams {
     int qg;                    // 0 or 1: plain decode
     int qg_tokens;             // number of query tokens (the last group may be partial)
     int l2_ahead;              // tiles prefetched into L2 beyond the shared-memory ring
-    int debug;                 // measurement switches (TQ_ATTN_DEBUG): bit 0 = skip the math, bit 1 = skip the loads
+    // whole-step form (MODE 2): ONE launch streams the layers [layer0, layer0 + n_layers) back to back -- every worker
+    // walks its slice of the tile list once per layer, its ring of stages never drains in between -- rotates the
+    // queries itself and only PUBLISHES its split-K partials, per layer; merge_partials_kernel finishes the step.
+    // ck/cv/kn/vn are the arrays of layer0, the tensor maps have the layer as their outermost coordinate.
+    int layer0, n_layers;
+    long long norm_layer_stride;   // halves between consecutive layers' norm arrays
+    long long q_layer_stride;      // halves between consecutive layers' queries (and outputs)
+    long long part_layer_stride;   // floats between consecutive layers' partial areas
+    int* table_out;                // [G + 4]: the tile table, then {workers taking part, total tiles}, for the merge kernel
+#ifdef TQ_TIMING_SWITCHES
+    int debug;                 // timing-experiment builds only: bit 0 = skip the math, bit 1 = skip the loads, ... (results are then wrong)
+#endif
 };
+
+// Switches that leave parts of the kernel out, for timing experiments.  They exist only in builds made with
+// -DTQ_TIMING_SWITCHES; in the library they are the constant false and the compiler removes the branches.
+#ifdef TQ_TIMING_SWITCHES
+#define TQ_DBG(bit) ((p.debug & (bit)) != 0)
+#define TQ_DBG_FACTOR (p.debug >> 8)
+#else
+#define TQ_DBG(bit) false
+#define TQ_DBG_FACTOR 0
+#endif
 
 template <int BITS>
 struct AttnGeom {
@@ -154,17 +176,186 @@ __device__ __forceinline__ uint4 ldsv128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
     return r;
 }
+__device__ __forceinline__ float ldsv_h2f(uint32_t addr) {  // one fp16 from shared memory as float, kept in program order
+    unsigned short h;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+    return __half2float(__ushort_as_half(h));
+}
+// Transpose of an 8 x 8 matrix of 16-bit elements held by the warp, one 32-bit register per lane: lane (r, c) holds
+// the elements (row r, columns 2c and 2c + 1) before and after.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from shared memory as float
     unsigned short h;
     asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
     return __half2float(__ushort_as_half(h));
 }
 
-template <int BITS, bool QSPLIT, int HKV, bool FUSED>
+// Split-K merge of one sequence: combines the `parts` partials (acc[128], m, l) of every query head, normalises, and
+// multiplies by R^T on the tensor cores (normalised accumulators split into fp16 high + low parts as the A operand, R^T
+// as B).  Run by NW warps (`head` = warp index among them) that share the named barrier `bar_group` and the staging
+// area `merge_s` ([2][16][MERGE_ROW] halves of shared memory).  part0: the first part's rows, [H][PART_STRIDE]; parts
+// follow each other H * PART_STRIDE floats apart.  out_row(h) / out_row_f32(h): where head h's 128 outputs go, or null.
+template <int NW, typename OutRow, typename OutRowF32>
+__device__ __forceinline__ void merge_sequence(const float* part0, int parts, int H, uint32_t merge_s, const __half* rotation_t,
+                                               int head, int lane, int bar_group, int nthreads, OutRow out_row,
+                                               OutRowF32 out_row_f32) {
+    const int gl = lane >> 2, t4 = lane & 3;
+    for (int hb = 0; hb < H; hb += 16) {
+        // ---- phase A: heads hb .. hb+15, two heads per warp at a time with all their loads in flight
+        //      together: combine the parts, normalise, split into fp16 high + low, store as the A operand
+        //      [16][MERGE_ROW]
+        for (int hh0 = head; hh0 < 16; hh0 += 2 * NW) {
+            float4 a[2];
+            a[0] = a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const size_t pstride = (size_t)H * PART_STRIDE;
+            if (parts <= 8) {
+                // common case: one round trip for everything, weights afterwards
+                float4 v[2][8];
+                float2 ml[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int hq = hb + hh0 + r * NW;
+                    const float* base = part0 + (size_t)hq * PART_STRIDE;
+                    const bool on = hq < H && hh0 + r * NW < 16;
+                    ml[r] = make_float2(-1e30f, 0.0f);
+                    if (on && lane < parts) ml[r] = __ldcg(reinterpret_cast<const float2*>(base + lane * pstride + HEAD_DIM));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        v[r][j] = (on && j < parts) ? __ldcg(reinterpret_cast<const float4*>(base + j * pstride) + lane)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float M = ml[r].x;
+#pragma unroll
+                    for (int o = 4; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                    M = __shfl_sync(0xffffffffu, M, 0);
+                    const float e = lane < parts ? ex2_approx(ml[r].x - M) : 0.0f;
+                    float Z = ml[r].y * e;
+#pragma unroll
+                    for (int o = 4; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
+                    Z = __shfl_sync(0xffffffffu, Z, 0);
+                    const float sc = e / (Z + 1e-8f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float wj = __shfl_sync(0xffffffffu, sc, j);
+                        a[r].x = fmaf(wj, v[r][j].x, a[r].x); a[r].y = fmaf(wj, v[r][j].y, a[r].y);
+                        a[r].z = fmaf(wj, v[r][j].z, a[r].z); a[r].w = fmaf(wj, v[r][j].w, a[r].w);
+                    }
+                }
+            } else {
+                // many parts: one round trip for all (max, sum) pairs, then the vectors 16 at a time
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int hq = hb + hh0 + r * NW;
+                    if (hq >= H || hh0 + r * NW >= 16) continue;
+                    const float* base = part0 + (size_t)hq * PART_STRIDE;
+                    float M = -1e30f, Z = 0.0f, m0 = -1e30f;  // m0: the max of part `lane` (parts 0 .. 31)
+                    for (int j0 = 0; j0 < parts; j0 += 32) {
+                        float2 t = make_float2(-1e30f, 0.0f);
+                        if (j0 + lane < parts) t = __ldcg(reinterpret_cast<const float2*>(base + (j0 + lane) * pstride + HEAD_DIM));
+                        if (j0 == 0) m0 = t.x;
+                        const float Mn = fmaxf(M, t.x);
+                        Z = Z * ex2_approx(M - Mn) + t.y * ex2_approx(t.x - Mn);
+                        M = Mn;
+                    }
+                    float Mw = M;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) Mw = fmaxf(Mw, __shfl_xor_sync(0xffffffffu, Mw, o));
+                    Z *= ex2_approx(M - Mw);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
+                    const float inv = 1.0f / (Z + 1e-8f);
+                    for (int j0 = 0; j0 < parts; j0 += 32) {
+                        float mj = m0;
+                        if (j0 > 0) mj = j0 + lane < parts ? __ldcg(base + (j0 + lane) * pstride + HEAD_DIM) : -1e30f;
+                        const float sc = j0 + lane < parts ? ex2_approx(mj - Mw) * inv : 0.0f;
+#pragma unroll 1
+                        for (int j1 = j0; j1 < parts && j1 < j0 + 32; j1 += 16) {
+                            float4 v[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                v[j] = j1 + j < parts ? __ldcg(reinterpret_cast<const float4*>(base + (j1 + j) * pstride) + lane)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float wj = __shfl_sync(0xffffffffu, sc, (j1 - j0) + j);
+                                a[r].x = fmaf(wj, v[j].x, a[r].x); a[r].y = fmaf(wj, v[j].y, a[r].y);
+                                a[r].z = fmaf(wj, v[j].z, a[r].z); a[r].w = fmaf(wj, v[j].w, a[r].w);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int hh = hh0 + r * NW;
+                if (hh >= 16) continue;
+                __half2 h01 = __floats2half2_rn(a[r].x, a[r].y), h23 = __floats2half2_rn(a[r].z, a[r].w);
+                float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                const uint32_t dst = merge_s + (uint32_t)(hh * MERGE_ROW + 4 * lane) * 2u;
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h01)),
+                             "r"(*reinterpret_cast<uint32_t*>(&h23)) : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + 16u * MERGE_ROW * 2u),
+                             "r"(pack_half2(a[r].x - f01.x, a[r].y - f01.y)), "r"(pack_half2(a[r].z - f23.x, a[r].w - f23.y)) : "memory");
+            }
+        }
+        // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k].
+        //      Two column blocks of 8 per warp and pass; their B fragments are fetched before the barrier so that
+        //      the round trip overlaps the other warps' phase A.
+        for (int nb0 = head; nb0 < 16; nb0 += 2 * NW) {
+            uint32_t bfrag[2][8][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int nb = nb0 + i * NW;
+                const __half* rt = rotation_t + (size_t)(8 * (nb < 16 ? nb : 0) + gl) * HEAD_DIM + 2 * t4;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    bfrag[i][j][0] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j));
+                    bfrag[i][j][1] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j + 8));
+                }
+            }
+            if (nb0 == head) group_barrier(bar_group, nthreads);  // phase A of every warp is in shared memory
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int nb = nb0 + i * NW;
+                if (nb >= 16) continue;
+                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t r0 = merge_s + (uint32_t)(gl * MERGE_ROW + 16 * j + 2 * t4) * 2u;
+                    const uint32_t r8 = r0 + 8u * MERGE_ROW * 2u;
+                    const uint32_t lo_off = 16u * MERGE_ROW * 2u;
+                    mma16816(c, lds32(r0), lds32(r8), lds32(r0 + 16u), lds32(r8 + 16u), bfrag[i][j][0], bfrag[i][j][1]);
+                    mma16816(c, lds32(r0 + lo_off), lds32(r8 + lo_off), lds32(r0 + lo_off + 16u), lds32(r8 + lo_off + 16u),
+                             bfrag[i][j][0], bfrag[i][j][1]);
+                }
+                const int d = 8 * nb + 2 * t4;
+                if (__half* o = out_row(hb + gl))
+                    *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[0], c[1]);
+                if (__half* o = out_row(hb + gl + 8))
+                    *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[2], c[3]);
+                if (float* o = out_row_f32(hb + gl)) *reinterpret_cast<float2*>(o + d) = make_float2(c[0], c[1]);
+                if (float* o = out_row_f32(hb + gl + 8)) *reinterpret_cast<float2*>(o + d) = make_float2(c[2], c[3]);
+            }
+        }
+        group_barrier(bar_group, nthreads);  // the A operand may be overwritten (next 16 heads, next segment)
+    }
+}
+
+// MODE 0: queries pre-rotated and tile table built by append_rotate_kernel; 1: the kernel builds its table, rotates the
+// queries, optionally appends the step's token (one launch per layer and step); 2: whole-step form, see AttnParams.
+template <int BITS, int HKV, int MODE>
 __global__ void __launch_bounds__(ATTN_GROUPS * 32 * HKV, 1)
 decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const AttnParams p) {
     using Geo = AttnGeom<BITS>;
+    constexpr bool FUSED = MODE >= 1;
+    constexpr bool PERSIST = MODE == 2;
     extern __shared__ __align__(1024) uint8_t dyn_smem[];
 
     const int tid = threadIdx.x;
@@ -205,18 +396,20 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
         return;
     }
-    const uint32_t bar0 = a_base + RegionA::BAR_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 8u);
-    const uint32_t cnt0 = a_base + RegionA::CNT_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 4u);
+    // two barriers and two done-counters per stage: the K part (codes + norms) and the V part are filled, waited for
+    // and handed back separately, so that a stage's K half is on its way again while its V half is still being read
+    const uint32_t bar0 = a_base + RegionA::BAR_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 16u);
+    const uint32_t cnt0 = a_base + RegionA::CNT_OFF + (uint32_t)group * (ATTN_MAX_STAGES * 8u);
     const uint32_t ctrl_s = a_base + RegionA::CTRL_OFF + (uint32_t)group * 16u;
     const uint32_t merge_s = a_base + RegionA::MERGE_OFF + (uint32_t)group * RegionA::MERGE_GROUP_BYTES;
 
     // The fused form lets its successor start only once it has itself seen its predecessor finish (see `early`).
     if (!FUSED) pdl_launch_dependents();
-    if (p.debug & 32) { pdl_wait(); pdl_launch_dependents(); return; }
+    if (TQ_DBG(32)) { pdl_wait(); pdl_launch_dependents(); return; }
     const int G = p.G;
 
     // ---- byte -> centroid table, one column per lane ----
-    if (p.debug & 16) {
+    if (TQ_DBG(16)) {
     } else if (BITS == 4) {
         for (int idx = tid; idx < 256 * 32; idx += blockDim.x) {
             int v = idx >> 5, l = idx & 31;
@@ -236,7 +429,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     }
     if (gtid == 0) {
-        for (int s = 0; s < ATTN_MAX_STAGES; ++s) {
+        for (int s = 0; s < 2 * ATTN_MAX_STAGES; ++s) {
             mbar_init(bar0 + 8u * s, 1);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
         }
@@ -284,6 +477,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
         if (tid == 0) ts_s[G] = carry;
         ts = ts_s;
+        if constexpr (PERSIST) {
+            if (blockIdx.x == 0) {  // the merge kernel reads the table from global memory
+                __syncthreads();
+                for (int i = tid; i <= G; i += (int)blockDim.x) p.table_out[i] = ts_s[i];
+            }
+        }
     } else {
         ts = p.tile_start;
     }
@@ -294,8 +493,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     // At most min(workers, N) workers take part, so that every participant owns at least one tile: the ticket
     // count of a sequence is then simply (last owner - first owner + 1).  Fewer when the list is short.
     const long long w_all = (long long)gridDim.x * ATTN_GROUPS;
-    const int W = attention_workers(w_all, N, G, (p.debug >> 8) ? (p.debug >> 8) : 16);  // debug bits 8+: another factor (timing experiments)
+    const int W = attention_workers(w_all, N, G, TQ_DBG_FACTOR ? TQ_DBG_FACTOR : 16);
     const int wid = blockIdx.x * ATTN_GROUPS + group;
+    if (PERSIST && blockIdx.x == 0 && tid == 0) {
+        p.table_out[G + 1] = W;
+        p.table_out[G + 2] = (int)N;
+    }
     if (wid >= W) return;  // uniform for the worker; no CTA-wide barrier follows
     // The flat list is cut in UNITS: a tile is one unit, except the last tile of a sequence, which counts 1 + A units
     // for what a sequence costs beside its tiles (A = p.app_weight, in tiles): in the fused form its owner also appends
@@ -325,7 +528,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         lo = (long long)wid * N / W;
         hi = (long long)(wid + 1) * N / W;
         // first sequence of the slice: largest g with tile_start[g] <= lo
-        if (p.worker_g && !(p.debug >> 8)) {
+        if (p.worker_g && !TQ_DBG_FACTOR) {
             g = p.worker_g[wid];
         } else {
             int a = 0, b = G;  // invariant: tile_start[a] <= lo < tile_start[b]
@@ -343,40 +546,59 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     int cl_tile = lo_i;                         // next tile to load into shared memory
     int cl_g = g;
     int cl_gend = ts[g + 1];
-    int cl_row = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - ts[g]) * TILE_TOKENS;
+    const int row_lo = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - ts[g]) * TILE_TOKENS;
+    int cl_row = row_lo;
+    int cl_layer = 0;                           // whole-step form: layer (relative to layer0) the cursor is in
+    const int g_lo = g;
+    const int n_layers = PERSIST ? p.n_layers : 1;
     auto cursor_advance = [&]() {
         ++cl_tile;
         cl_row += TILE_TOKENS;
-        if (cl_tile == cl_gend && cl_tile < hi_i) {
+        if (PERSIST && cl_tile == hi_i) {  // the same slice again, one layer on
+            ++cl_layer;
+            cl_tile = lo_i;
+            cl_g = g_lo;
+            cl_gend = ts[g_lo + 1];
+            cl_row = row_lo;
+        } else if (cl_tile == cl_gend && cl_tile < hi_i) {
             ++cl_g;
             cl_gend = ts[cl_g + 1];
             cl_row = (int)(p.row_base ? p.row_base[cl_g] : (long long)cl_g * p.max_seq_len);
         }
     };
+    auto cursor_more = [&]() -> bool { return PERSIST ? cl_layer < n_layers : cl_tile < hi_i; };
     int consumed = 0;
     int s_idx = 0;          // 2-bit form: stage of the tile being consumed and the parity of its barrier
     uint32_t s_par = 0;
     bool dead = false;  // a bounded wait gave up: keep the control flow, stop touching the pipeline
-    const bool loads_on = !(p.debug & 2);
+    const bool loads_on = !TQ_DBG(2);
     const int total_rows_i = (int)p.total_rows;
 
-    // One elected thread issues the four copies of a tile (K codes, V codes, K norms, V norms), clipped to the
-    // end of the arrays; rows past a sequence's position only ever reach masked tokens.
-    auto issue_tile = [&](int row, int s) {
+    // One elected thread issues the two copies of a tile's K part (codes, norms) or V part, clipped to the end of the
+    // arrays; rows past a sequence's position only ever reach masked tokens.
+    auto issue_part = [&](int row, int s, int part, int layer) {
         int nrows = total_rows_i - row;
         if (nrows > TILE_TOKENS) nrows = TILE_TOKENS;
         if (nrows < 0) nrows = 0;
         const uint32_t nb = (uint32_t)nrows * (uint32_t)Hkv * 2u;
-        const uint32_t bar = bar0 + 8u * s;
+        const uint32_t bar = bar0 + 16u * s + 8u * part;
         const uint32_t dst = stage_addr(s);
         // a tensor-map box always delivers its full size (rows past the end of the array arrive as zeros)
-        mbar_arrive_expect_tx(bar, 2u * code_tile + 2u * nb);
-        tma_load_3d(dst, &tmK, bar, 0, row, 0);
-        tma_load_3d(dst + code_tile, &tmV, bar, 0, row, 0);
-        if (nrows > 0) {
-            bulk_load(dst + 2u * code_tile, p.kn + (size_t)row * Hkv, nb, bar);
-            bulk_load(dst + 2u * code_tile + norm_tile, p.vn + (size_t)row * Hkv, nb, bar);
+        mbar_arrive_expect_tx(bar, code_tile + nb);
+        const size_t noff = (size_t)row * Hkv + (PERSIST ? (size_t)layer * (size_t)p.norm_layer_stride : (size_t)0);
+        if (part == 0) {
+            if (PERSIST) tma_load_4d(dst, &tmK, bar, 0, row, 0, p.layer0 + layer);
+            else tma_load_3d(dst, &tmK, bar, 0, row, 0);
+            if (nrows > 0) bulk_load(dst + 2u * code_tile, p.kn + noff, nb, bar);
+        } else {
+            if (PERSIST) tma_load_4d(dst + code_tile, &tmV, bar, 0, row, 0, p.layer0 + layer);
+            else tma_load_3d(dst + code_tile, &tmV, bar, 0, row, 0);
+            if (nrows > 0) bulk_load(dst + 2u * code_tile + norm_tile, p.vn + noff, nb, bar);
         }
+    };
+    auto issue_tile = [&](int row, int s, int layer) {
+        issue_part(row, s, 0, layer);
+        issue_part(row, s, 1, layer);
     };
     // L2 prefetch of the tile ATTN_L2_AHEAD further on, when it belongs to the same sequence (rows are then contiguous)
     auto prefetch_ahead = [&](int row, int tile_idx, int gend) {
@@ -392,9 +614,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     };
     auto fill_ring = [&]() {  // prologue: fill the ring (and prefetch a few tiles beyond each)
         for (int s = 0; s < S; ++s) {
-            if (cl_tile < hi_i) {
+            if (cursor_more()) {
                 if (gtid == 0 && loads_on) {
-                    issue_tile(cl_row, s);
+                    issue_tile(cl_row, s, cl_layer);
                     prefetch_ahead(cl_row, cl_tile, cl_gend);
                 }
                 cursor_advance();
@@ -410,7 +632,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         int g_app0 = g;  // first sequence whose last tile starts at or after lo
         while (g_app0 < G && ts[g_app0 + 1] - 1 < lo_i) ++g_app0;
         // (without new keys and values the launch only builds its table, rotates the queries and attends)
-        const bool have_app = p.new_k != nullptr && g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
+        const bool have_app = !PERSIST && p.new_k != nullptr && g_app0 < G && ts[g_app0 + 1] - 1 < hi_i;
         const bool fill_before = !have_app || ts[g_app0 + 1] - 1 >= lo_i + S;
         if (early) {
             // none of the tiles filled here can hold a row the step is about to write
@@ -673,7 +895,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         fill_ring();
     }
 
-    if (p.debug & 64) return;
+    if (TQ_DBG(64)) return;
     const uint32_t lutlane = LUT_ABS | ((uint32_t)lane << (BITS == 4 ? 2 : 3));
     // ---- swizzled addressing.  A box holds [32 rows][128 B]; the 16-byte chunk c of row r sits at chunk c ^ (r & 7).
     // Tokens of an 8-token score block are taken in the order tau(n) = n ^ ((n & 1) << 2), which keeps both the
@@ -696,7 +918,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         vB_off = box_off + tokB * 128u + ((vch ^ tokB) << 4) + vsub;
     }
 
+    for (int layer = 0; layer < n_layers; ++layer) {  // (one pass unless this is the whole-step form)
     long long tile = lo;
+    g = g_lo;
     while (tile < hi) {
         // ================= one segment: tiles [tile, seg_end) of sequence g =================
         const long long ts_g = ts[g];
@@ -707,11 +931,14 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         // causal limit of this lane's score row (row gl) and of the group's first token; equal to L outside the prefill form
         const int qg = FUSED ? 0 : p.qg;  // the fused form is a decode step: no token groups
         const int grp_real = qg > 1 ? grp / qg : grp;
-        const int Lrow = qg > 1 ? min(L, g * qg + gl / grp_real + 1) : L;
+        // (this lane's score columns are the heads 2*t4 and 2*t4 + 1 of its KV head)
+        const int Lcol0 = qg > 1 ? min(L, g * qg + (2 * t4) / grp_real + 1) : L;
+        const int Lcol1 = qg > 1 ? min(L, g * qg + (2 * t4 + 1) / grp_real + 1) : L;
         const int Lmin = qg > 1 ? min(L, g * qg + 1) : L;
 
-        // query fragments: lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head  head*grp + gl
-        uint32_t qa[8][QSPLIT ? 4 : 2];
+        // query fragments (B operand of the score product): lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head
+        // head*grp + gl as fp16
+        uint32_t qb[8][2];
         {
             float qv[32];
             if constexpr (FUSED) {
@@ -727,7 +954,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                         const int r = i >> 4;
                         uint4 u = make_uint4(0u, 0u, 0u, 0u);
                         if (hb + r < p.H)
-                            u = __ldg(reinterpret_cast<const uint4*>(p.new_q + (size_t)g * p.q_dim + (size_t)(hb + r) * HEAD_DIM) + (i & 15));
+                            u = __ldg(reinterpret_cast<const uint4*>(p.new_q + (PERSIST ? (size_t)layer * (size_t)p.q_layer_stride : (size_t)0) +
+                                                                     (size_t)g * p.q_dim + (size_t)(hb + r) * HEAD_DIM) + (i & 15));
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(qs_a + (uint32_t)i * 16u), "r"(u.x), "r"(u.y),
                                      "r"(u.z), "r"(u.w) : "memory");
                     }
@@ -766,7 +994,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     }
                     group_barrier(group, gthreads);
                     const int myrow = head * grp + gl - hb;
-                    if (gl < grp && myrow >= 0 && myrow < 16 && !(p.debug & 8)) {
+                    if (gl < grp && myrow >= 0 && myrow < 16 && !TQ_DBG(8)) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             float4 f;
@@ -777,7 +1005,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     }
                     group_barrier(group, gthreads);
                 }
-            } else if (gl < grp && !(p.debug & 8)) {
+            } else if (gl < grp && !TQ_DBG(8)) {
                 const float4* src =
                     reinterpret_cast<const float4*>(p.q_rot + ((size_t)g * p.H + (size_t)head * grp + gl) * HEAD_DIM + 32 * t4);
 #pragma unroll
@@ -794,19 +1022,13 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 // the 2-bit table returns the four values of a byte as (0, 2), (1, 3)
                 const float x0 = qv[4 * j], x1 = BITS == 2 ? qv[4 * j + 2] : qv[4 * j + 1];
                 const float x2 = BITS == 2 ? qv[4 * j + 1] : qv[4 * j + 2], x3 = qv[4 * j + 3];
-                __half2 h01 = __floats2half2_rn(x0, x1);
-                __half2 h23 = __floats2half2_rn(x2, x3);
-                qa[j][0] = *reinterpret_cast<uint32_t*>(&h01);
-                qa[j][QSPLIT ? 2 : 1] = *reinterpret_cast<uint32_t*>(&h23);
-                if (QSPLIT) {
-                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                    qa[j][1] = pack_half2(x0 - f01.x, x1 - f01.y);
-                    qa[j][3] = pack_half2(x2 - f23.x, x3 - f23.y);
-                }
+                qb[j][0] = pack_half2(x0, x1);
+                qb[j][1] = pack_half2(x2, x3);
             }
         }
 
-        float m_run = -1e30f, l_run = 0.0f;
+        // running maximum and (per lane: over its own token rows) sum of the two score columns of this lane
+        float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.0f, 0.0f};
         float acc[8][4];
 #pragma unroll
         for (int b = 0; b < 8; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
@@ -815,37 +1037,62 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             const int t0 = (int)(tile - ts_g) * TILE_TOKENS;
             const bool full = t0 + TILE_TOKENS <= Lmin;  // warp-uniform: no token of the tile is masked for any row
             const int s = BITS == 2 ? s_idx : (consumed & (S - 1));
-            uint32_t token = 0;  // 0 at run time; produced by the wait, so that the tile's loads cannot move above it
-            if (!dead && loads_on) {
-                const uint32_t bar = bar0 + 8u * s, parity = BITS == 2 ? s_par : ((uint32_t)(consumed >> s_log) & 1u);
-                uint32_t ok = 0;
-                for (uint32_t it = 0; it < (1u << 14) && !ok; ++it) ok = mbar_try_wait_hint(bar, parity, 20000u);
-                if (!ok) {
-                    dead = true;
-                    if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+            const uint32_t parity = BITS == 2 ? s_par : ((uint32_t)(consumed >> s_log) & 1u);
+            // the tile that takes this stage's place (warp-uniform; every warp of the worker advances the cursor in step)
+            const int next_row = cl_row, next_tile = cl_tile, next_gend = cl_gend, next_layer = cl_layer;
+            const bool more = cursor_more();
+            if (more) cursor_advance();
+            // Wait for one part (0: K codes and norms, 1: V codes and norms) of the stage.  Returns 0 at run time, as a
+            // value PRODUCED by the wait: the part's loads take it into their address and so cannot move above the wait.
+            auto wait_part = [&](int part) -> uint32_t {
+                uint32_t token = 0;
+                if (!dead && loads_on) {
+                    const uint32_t bar = bar0 + 16u * s + 8u * part;
+                    uint32_t ok = 0;
+                    for (uint32_t it = 0; it < (1u << 14) && !ok; ++it) ok = mbar_try_wait_hint(bar, parity, 20000u);
+                    if (!ok) {
+                        dead = true;
+                        if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+                    }
+                    dead = __any_sync(0xffffffffu, dead);
+                    token = ok ^ 1u;
                 }
-                dead = __any_sync(0xffffffffu, dead);
-                token = ok ^ 1u;
-            }
+                return token;
+            };
+            // Hand a part back: everything this warp read from it has been consumed by (ordered) instructions above.  The
+            // last warp of the worker to get here re-arms the part with the same part of the tile S ahead; nobody waits.
+            auto release_part = [&](int part) {
+                __syncwarp();
+                if (lane == 0 && more && !dead && loads_on) {
+                    __threadfence_block();  // this warp's reads of the part are ordered before the hand-over below
+                    const uint32_t cnt = cnt0 + 8u * s + 4u * part;
+                    const uint32_t old = atom_add_shared(cnt, 1u);
+                    if (old == (uint32_t)Hkv - 1u) {
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt), "r"(0u) : "memory");
+                        fence_proxy_async_smem();
+                        issue_part(next_row, s, part, next_layer);
+                        if (part == 1) prefetch_ahead(next_row, next_tile, next_gend);
+                    }
+                }
+            };
             // The tile body exists twice: for tiles in which every token is attended to (all but the last tile of a
             // sequence) without any masking code, and for the last, partly filled tile with it.
             auto tile_body = [&](auto full_tag) {
                 constexpr bool FULLT = decltype(full_tag)::value;
-                const uint32_t kt = stage_addr(s) + token;
-                const uint32_t vt = kt + code_tile;
-                const uint32_t kns = stage_addr(s) + token + 2u * code_tile + (uint32_t)head * 2u;
-                const uint32_t vns = kns + norm_tile;
                 constexpr uint32_t nstride = (uint32_t)Hkv * 2u;
+                const uint32_t tokK = wait_part(0);
+                if (dead) return;
+                const uint32_t kt = stage_addr(s) + tokK;
+                const uint32_t kns = kt + 2u * code_tile + (uint32_t)head * 2u;
 
-                // ---------------- scores: 4 blocks of 8 tokens ----------------
-                float sv[8];
+                // ---------------- scores: S^T = K (16 token rows x 16 coordinates) * Q^T (16 coordinates x 8 heads), two
+                // blocks of 16 token rows.  Row r of block rb is token 16*rb + 8*(r >> 3) + tau(r & 7) of the tile; the
+                // eight 16-coordinate steps of a row block form one accumulator chain.
+                float c[2][4];
                 {
-                    // the four 8-token blocks advance together: four independent accumulator chains
-                    float c[4][4];
                     uint32_t w[4][4];
 #pragma unroll
                     for (int blk = 0; blk < 4; ++blk) {
-                        c[blk][0] = c[blk][1] = c[blk][2] = c[blk][3] = 0.0f;
                         if (BITS == 4) {
                             const uint4 kw = ldsp128(kt + (uint32_t)blk * 1024u + k_off);
                             w[blk][0] = kw.x; w[blk][1] = kw.y; w[blk][2] = kw.z; w[blk][3] = kw.w;
@@ -855,83 +1102,110 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                         }
                     }
 #pragma unroll
+                    for (int rb = 0; rb < 2; ++rb) c[rb][0] = c[rb][1] = c[rb][2] = c[rb][3] = 0.0f;
+#pragma unroll
                     for (int j = 0; j < 8; ++j) {
 #pragma unroll
-                        for (int blk = 0; blk < 4; ++blk) {
-                            uint32_t b0, b1;
+                        for (int rb = 0; rb < 2; ++rb) {
+                            uint32_t a0, a1, a2, a3;  // rows gl / gl + 8, coordinate pairs (4j, 4j+1) / (4j+2, 4j+3) of the lane's 32
                             if (BITS == 4) {
-                                const uint32_t word = w[blk][j >> 1];
-                                b0 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7624u : 0x7604u));
-                                b1 = ldsp32(prmt(word, lutlane, (j & 1) ? 0x7634u : 0x7614u));
+                                const uint32_t sel0 = (j & 1) ? 0x7624u : 0x7604u, sel1 = (j & 1) ? 0x7634u : 0x7614u;
+                                const uint32_t wlo = w[2 * rb][j >> 1], whi = w[2 * rb + 1][j >> 1];
+                                a0 = ldsp32(prmt(wlo, lutlane, sel0));
+                                a1 = ldsp32(prmt(whi, lutlane, sel0));
+                                a2 = ldsp32(prmt(wlo, lutlane, sel1));
+                                a3 = ldsp32(prmt(whi, lutlane, sel1));
                             } else {
-                                const uint2 bb = ldsp64(prmt(w[blk][j >> 2], lutlane, 0x7604u | ((uint32_t)(j & 3) << 4)));
-                                b0 = bb.x; b1 = bb.y;
+                                const uint32_t sel = 0x7604u | ((uint32_t)(j & 3) << 4);
+                                const uint2 lo2 = ldsp64(prmt(w[2 * rb][j >> 2], lutlane, sel));
+                                const uint2 hi2 = ldsp64(prmt(w[2 * rb + 1][j >> 2], lutlane, sel));
+                                a0 = lo2.x; a1 = hi2.x; a2 = lo2.y; a3 = hi2.y;
                             }
-                            if (QSPLIT) mma16816(c[blk], qa[j][0], qa[j][1], qa[j][2], qa[j][3], b0, b1);
-                            else mma16816(c[blk], qa[j][0], 0u, qa[j][1], 0u, b0, b1);
+                            mma16816(c[rb], a0, a1, a2, a3, qb[j][0], qb[j][1]);
                         }
                     }
-#pragma unroll
-                    for (int blk = 0; blk < 4; ++blk) {
-                        const float k0 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokA) * nstride);
-                        const float k1 = ldsp_h2f(kns + ((uint32_t)(8 * blk) + tokB) * nstride);
-                        sv[2 * blk] = (QSPLIT ? c[blk][0] + c[blk][2] : c[blk][0]) * k0;
-                        sv[2 * blk + 1] = (QSPLIT ? c[blk][1] + c[blk][3] : c[blk][1]) * k1;
-                    }
                 }
+                // K norms of this lane's four token rows (ordered loads: they precede the hand-over of the K part)
+                float kn4[4];
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) kn4[blk] = ldsv_h2f(kns + ((uint32_t)(8 * blk) + tauK) * nstride);
+                release_part(0);
 
-                // ---------------- online softmax (row = head gl; rows >= grp carry zeros and are never read) ----
+                // ---------------- online softmax: sv[blk][e] = score of token row (block blk, tau(gl)) and head 2*t4 + e.
+                // Columns of heads >= grp carry zeros and are never read.
+                float sv[4][2];
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {
+                    sv[blk][0] = c[blk >> 1][2 * (blk & 1)] * kn4[blk];
+                    sv[blk][1] = c[blk >> 1][2 * (blk & 1) + 1] * kn4[blk];
+                }
                 if constexpr (!FULLT) {  // rows past the position may hold anything (even NaN norms): force them out
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
-                        if (tok >= Lrow) sv[i] = -1e30f;
+                    for (int blk = 0; blk < 4; ++blk) {
+                        const int tok = t0 + 8 * blk + (int)tauK;
+                        if (tok >= Lcol0) sv[blk][0] = -1e30f;
+                        if (tok >= Lcol1) sv[blk][1] = -1e30f;
                     }
                 }
-                float tmax = fmaxf(fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])), fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7])));
-                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-                const float m_new = fmaxf(m_run, tmax);
-                if (__any_sync(0xffffffffu, m_new > m_run)) {
-                    const float corr = ex2_approx(m_run - m_new);  // 1 when unchanged, 0 at the first tile
-                    l_run *= corr;
-                    // accumulators of head (2*t4 + e) live in lanes with this t4; its corr lives in lanes gl' = 2*t4 + e
-                    const float c0 = __shfl_sync(0xffffffffu, corr, (2 * t4) * 4);
-                    const float c1 = __shfl_sync(0xffffffffu, corr, (2 * t4 + 1) * 4);
+                float mx0 = fmaxf(fmaxf(sv[0][0], sv[1][0]), fmaxf(sv[2][0], sv[3][0]));
+                float mx1 = fmaxf(fmaxf(sv[0][1], sv[1][1]), fmaxf(sv[2][1], sv[3][1]));
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+                }
+                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+                if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
+                    // 1 when unchanged, 0 at the first tile; the accumulators of heads 2*t4, 2*t4 + 1 live in this very lane
+                    const float c0 = ex2_approx(m_run[0] - mn0), c1 = ex2_approx(m_run[1] - mn1);
+                    l_run[0] *= c0;
+                    l_run[1] *= c1;
 #pragma unroll
                     for (int b = 0; b < 8; ++b) {
                         acc[b][0] *= c0; acc[b][2] *= c0;
                         acc[b][1] *= c1; acc[b][3] *= c1;
                     }
-                    m_run = m_new;
+                    m_run[0] = mn0;
+                    m_run[1] = mn1;
                 }
-                float pv[8];
+                float pv[4][2];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) pv[i] = ex2_approx(sv[i] - m_run);
+                for (int blk = 0; blk < 4; ++blk) {
+                    pv[blk][0] = ex2_approx(sv[blk][0] - m_run[0]);
+                    pv[blk][1] = ex2_approx(sv[blk][1] - m_run[1]);
+                }
                 if constexpr (!FULLT) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int tok = t0 + 8 * (i >> 1) + (int)((i & 1) ? tokB : tokA);
-                        if (tok >= Lrow) pv[i] = 0.0f;
+                    for (int blk = 0; blk < 4; ++blk) {
+                        const int tok = t0 + 8 * blk + (int)tauK;
+                        if (tok >= Lcol0) pv[blk][0] = 0.0f;
+                        if (tok >= Lcol1) pv[blk][1] = 0.0f;
                     }
                 }
-                l_run += ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
+                l_run[0] += (pv[0][0] + pv[1][0]) + (pv[2][0] + pv[3][0]);
+                l_run[1] += (pv[0][1] + pv[1][1]) + (pv[2][1] + pv[3][1]);
 
                 // ---------------- values: 2 blocks of 16 tokens ----------------
+                const uint32_t tokV = wait_part(1);
+                if (dead) return;
+                const uint32_t vt = stage_addr(s) + code_tile + tokV;
+                const uint32_t vns = stage_addr(s) + tokV + 2u * code_tile + norm_tile + (uint32_t)head * 2u;
+                // weights times V norms as fp16 pairs (heads 2*t4, 2*t4 + 1) of this lane's token rows, then transposed
+                // across the warp into the B operand of the value product: lane (gl, t4) receives head gl of the token
+                // rows tau(2*t4), tau(2*t4 + 1) of every 8-row block
+                uint32_t pb[4];
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {
+                    float vn = ldsp_h2f(vns + ((uint32_t)(8 * blk) + tauK) * nstride);
+                    if constexpr (!FULLT) {  // 0 * NaN would poison the accumulators
+                        if (t0 + 8 * blk + (int)tauK >= L) vn = 0.0f;
+                    }
+                    pb[blk] = movmatrix_trans(pack_half2(pv[blk][0] * vn, pv[blk][1] * vn));
+                }
 #pragma unroll
                 for (int gam = 0; gam < 2; ++gam) {
                     // token rows of this lane: A, B from score block 2*gam, C, D from block 2*gam+1
-                    const uint32_t rA = (uint32_t)(16 * gam) + tokA, rB = (uint32_t)(16 * gam) + tokB;
-                    float v0 = ldsp_h2f(vns + rA * nstride), v1 = ldsp_h2f(vns + rB * nstride);
-                    float v8 = ldsp_h2f(vns + (rA + 8u) * nstride), v9 = ldsp_h2f(vns + (rB + 8u) * nstride);
-                    if constexpr (!FULLT) {  // 0 * NaN would poison the accumulators
-                        if (t0 + (int)rA >= L) v0 = 0.0f;
-                        if (t0 + (int)rB >= L) v1 = 0.0f;
-                        if (t0 + (int)rA + 8 >= L) v8 = 0.0f;
-                        if (t0 + (int)rB + 8 >= L) v9 = 0.0f;
-                    }
-                    const uint32_t pb0 = pack_half2(pv[4 * gam] * v0, pv[4 * gam + 1] * v1);
-                    const uint32_t pb1 = pack_half2(pv[4 * gam + 2] * v8, pv[4 * gam + 3] * v9);
+                    const uint32_t pb0 = pb[2 * gam], pb1 = pb[2 * gam + 1];
                     if (BITS == 4) {
                         // lane reads bytes 8*gl .. 8*gl+7 (coordinates 16*gl .. 16*gl+15) of token rows A, B, C = A+8, D = B+8
                         const uint32_t vg = vt + (uint32_t)gam * 2048u;
@@ -983,12 +1257,16 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     }
                 }
             };
-            if (!dead && !(p.debug & 1)) {
+            if (!dead && !TQ_DBG(1)) {
                 if (full) tile_body(std::true_type{});
                 else tile_body(std::false_type{});
             }
-            // Everything this warp read from the stage has been consumed by the (ordered) mma instructions above.
-            // The last warp of the worker to get here re-arms the stage with the tile S ahead; nobody waits.
+            if (TQ_DBG(1)) {  // timing experiments: the copies without the arithmetic
+                wait_part(0);
+                release_part(0);
+                wait_part(1);
+            }
+            release_part(1);
             ++consumed;
             if (BITS == 2) {
                 if (++s_idx == S) {
@@ -996,38 +1274,34 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     s_par ^= 1u;
                 }
             }
-            const int next_row = cl_row, next_tile = cl_tile, next_gend = cl_gend;
-            const bool more = cl_tile < hi_i;
-            if (more) cursor_advance();
-            __syncwarp();
-            if (lane == 0 && more && !dead && loads_on) {
-                __threadfence_block();  // this warp's reads of the stage are ordered before the hand-over below
-                const uint32_t old = atom_add_shared(cnt0 + 4u * s, 1u);
-                if (old == (uint32_t)Hkv - 1u) {
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
-                    fence_proxy_async_smem();
-                    issue_tile(next_row, s);
-                    prefetch_ahead(next_row, next_tile, next_gend);
-                }
-            }
         }
 
         // ================= end of segment: publish the partial, maybe merge =================
         const int slot = wid + g;
-        if (!(p.debug & 8)) {
-            float lsum = l_run;
-            lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-            lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-            if (gl < grp && t4 == 0) {
-                float* dst = p.partials + ((size_t)slot * p.H + (size_t)head * grp + gl) * PART_STRIDE;
-                dst[HEAD_DIM] = m_run;
-                dst[HEAD_DIM + 1] = lsum;
+        float* const part_base = p.partials + (PERSIST ? (size_t)layer * (size_t)p.part_layer_stride : (size_t)0);
+        if (!TQ_DBG(8)) {
+            float lsum0 = l_run[0], lsum1 = l_run[1];  // per lane over its own token rows: sum over the eight row lanes
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                lsum0 += __shfl_xor_sync(0xffffffffu, lsum0, o);
+                lsum1 += __shfl_xor_sync(0xffffffffu, lsum1, o);
+            }
+            if (gl == 0) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int hq = 2 * t4 + e;
+                    if (hq < grp) {
+                        float* dst = part_base + ((size_t)slot * p.H + (size_t)head * grp + hq) * PART_STRIDE;
+                        dst[HEAD_DIM] = e ? m_run[1] : m_run[0];
+                        dst[HEAD_DIM + 1] = e ? lsum1 : lsum0;
+                    }
+                }
             }
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int hq = 2 * t4 + e;
                 if (hq < grp) {
-                    float* dst = p.partials + ((size_t)slot * p.H + (size_t)head * grp + hq) * PART_STRIDE + 16 * gl;
+                    float* dst = part_base + ((size_t)slot * p.H + (size_t)head * grp + hq) * PART_STRIDE + 16 * gl;
 #pragma unroll
                     for (int b2 = 0; b2 < 4; ++b2) {
                         float4 o;
@@ -1038,7 +1312,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 }
             }
         }
-        if (p.debug & 4) { ++g; continue; }
+        if (TQ_DBG(4)) { ++g; continue; }
+        if constexpr (PERSIST) {  // the partials of all layers are merged by merge_partials_kernel
+            ++g;
+            continue;
+        }
         // number of workers that hold a part of sequence g
         // owners of the sequence's first and last tile (of the units those tiles start at)
         const int first_w = (int)(((ts_g + g * A + 1) * W - 1) / U);
@@ -1070,155 +1348,66 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 if (token >= p.qg_tokens) return nullptr;
                 return p.out + (size_t)token * p.q_dim + (size_t)(kvh * grp_real + hq) * HEAD_DIM;
             };
-            for (int hb = 0; hb < H; hb += 16) {
-                // ---- phase A: heads hb .. hb+15, two heads per warp at a time with all their loads in flight
-                //      together: combine the parts, normalise, split into fp16 high + low, store as the A operand
-                //      [16][MERGE_ROW]
-                for (int hh0 = head; hh0 < 16; hh0 += 2 * Hkv) {
-                    float4 a[2];
-                    a[0] = a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    const size_t pstride = (size_t)H * PART_STRIDE;
-                    if (parts <= 8) {
-                        // common case: one round trip for everything, weights afterwards
-                        float4 v[2][8];
-                        float2 ml[2];
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            const int hq = hb + hh0 + r * Hkv;
-                            const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
-                            const bool on = hq < H && hh0 + r * Hkv < 16;
-                            ml[r] = make_float2(-1e30f, 0.0f);
-                            if (on && lane < parts) ml[r] = __ldcg(reinterpret_cast<const float2*>(base + lane * pstride + HEAD_DIM));
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                v[r][j] = (on && j < parts) ? __ldcg(reinterpret_cast<const float4*>(base + j * pstride) + lane)
-                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            float M = ml[r].x;
-#pragma unroll
-                            for (int o = 4; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-                            M = __shfl_sync(0xffffffffu, M, 0);
-                            const float e = lane < parts ? ex2_approx(ml[r].x - M) : 0.0f;
-                            float Z = ml[r].y * e;
-#pragma unroll
-                            for (int o = 4; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
-                            Z = __shfl_sync(0xffffffffu, Z, 0);
-                            const float sc = e / (Z + 1e-8f);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float wj = __shfl_sync(0xffffffffu, sc, j);
-                                a[r].x = fmaf(wj, v[r][j].x, a[r].x); a[r].y = fmaf(wj, v[r][j].y, a[r].y);
-                                a[r].z = fmaf(wj, v[r][j].z, a[r].z); a[r].w = fmaf(wj, v[r][j].w, a[r].w);
-                            }
-                        }
-                    } else {
-                        // many parts: one round trip for all (max, sum) pairs, then the vectors 16 at a time
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            const int hq = hb + hh0 + r * Hkv;
-                            if (hq >= H || hh0 + r * Hkv >= 16) continue;
-                            const float* base = p.partials + ((size_t)(first_w + g) * H + hq) * PART_STRIDE;
-                            float M = -1e30f, Z = 0.0f, m0 = -1e30f;  // m0: the max of part `lane` (parts 0 .. 31)
-                            for (int j0 = 0; j0 < parts; j0 += 32) {
-                                float2 t = make_float2(-1e30f, 0.0f);
-                                if (j0 + lane < parts) t = __ldcg(reinterpret_cast<const float2*>(base + (j0 + lane) * pstride + HEAD_DIM));
-                                if (j0 == 0) m0 = t.x;
-                                const float Mn = fmaxf(M, t.x);
-                                Z = Z * ex2_approx(M - Mn) + t.y * ex2_approx(t.x - Mn);
-                                M = Mn;
-                            }
-                            float Mw = M;
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) Mw = fmaxf(Mw, __shfl_xor_sync(0xffffffffu, Mw, o));
-                            Z *= ex2_approx(M - Mw);
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
-                            const float inv = 1.0f / (Z + 1e-8f);
-                            for (int j0 = 0; j0 < parts; j0 += 32) {
-                                float mj = m0;
-                                if (j0 > 0) mj = j0 + lane < parts ? __ldcg(base + (j0 + lane) * pstride + HEAD_DIM) : -1e30f;
-                                const float sc = j0 + lane < parts ? ex2_approx(mj - Mw) * inv : 0.0f;
-#pragma unroll 1
-                                for (int j1 = j0; j1 < parts && j1 < j0 + 32; j1 += 16) {
-                                    float4 v[16];
-#pragma unroll
-                                    for (int j = 0; j < 16; ++j)
-                                        v[j] = j1 + j < parts ? __ldcg(reinterpret_cast<const float4*>(base + (j1 + j) * pstride) + lane)
-                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                                    for (int j = 0; j < 16; ++j) {
-                                        const float wj = __shfl_sync(0xffffffffu, sc, (j1 - j0) + j);
-                                        a[r].x = fmaf(wj, v[j].x, a[r].x); a[r].y = fmaf(wj, v[j].y, a[r].y);
-                                        a[r].z = fmaf(wj, v[j].z, a[r].z); a[r].w = fmaf(wj, v[j].w, a[r].w);
-                                    }
-                                }
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        const int hh = hh0 + r * Hkv;
-                        if (hh >= 16) continue;
-                        __half2 h01 = __floats2half2_rn(a[r].x, a[r].y), h23 = __floats2half2_rn(a[r].z, a[r].w);
-                        float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-                        const uint32_t dst = merge_s + (uint32_t)(hh * MERGE_ROW + 4 * lane) * 2u;
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h01)),
-                                     "r"(*reinterpret_cast<uint32_t*>(&h23)) : "memory");
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + 16u * MERGE_ROW * 2u),
-                                     "r"(pack_half2(a[r].x - f01.x, a[r].y - f01.y)), "r"(pack_half2(a[r].z - f23.x, a[r].w - f23.y)) : "memory");
-                    }
-                }
-                // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k].
-                //      Two column blocks of 8 per warp and pass; their B fragments are fetched before the barrier so that
-                //      the round trip overlaps the other warps' phase A.
-                for (int nb0 = head; nb0 < 16; nb0 += 2 * Hkv) {
-                    uint32_t bfrag[2][8][2];
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int nb = nb0 + i * Hkv;
-                        const __half* rt = p.rotation_t + (size_t)(8 * (nb < 16 ? nb : 0) + gl) * HEAD_DIM + 2 * t4;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            bfrag[i][j][0] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j));
-                            bfrag[i][j][1] = __ldg(reinterpret_cast<const unsigned int*>(rt + 16 * j + 8));
-                        }
-                    }
-                    if (nb0 == head) group_barrier(group, gthreads);  // phase A of every warp is in shared memory
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int nb = nb0 + i * Hkv;
-                        if (nb >= 16) continue;
-                        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t r0 = merge_s + (uint32_t)(gl * MERGE_ROW + 16 * j + 2 * t4) * 2u;
-                            const uint32_t r8 = r0 + 8u * MERGE_ROW * 2u;
-                            const uint32_t lo_off = 16u * MERGE_ROW * 2u;
-                            mma16816(c, lds32(r0), lds32(r8), lds32(r0 + 16u), lds32(r8 + 16u), bfrag[i][j][0], bfrag[i][j][1]);
-                            mma16816(c, lds32(r0 + lo_off), lds32(r8 + lo_off), lds32(r0 + lo_off + 16u), lds32(r8 + lo_off + 16u),
-                                     bfrag[i][j][0], bfrag[i][j][1]);
-                        }
-                        const int d = 8 * nb + 2 * t4;
-                        if (__half* o = out_row(hb + gl))
-                            *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[0], c[1]);
-                        if (__half* o = out_row(hb + gl + 8))
-                            *reinterpret_cast<__half2*>(o + d) = __floats2half2_rn(c[2], c[3]);
-                    }
-                }
-                group_barrier(group, gthreads);  // the A operand may be overwritten (next 16 heads, next segment)
-            }
+            // optional copy of the results before their rounding to fp16 (decode form only)
+            auto out_row_f32 = [&](int vh) -> float* {
+                if (!p.out_f32 || vh >= H || qg > 1) return nullptr;
+                return p.out_f32 + ((size_t)g * H + (size_t)vh) * HEAD_DIM;
+            };
+            merge_sequence<Hkv>(p.partials + (size_t)(first_w + g) * H * PART_STRIDE, parts, H, merge_s, p.rotation_t, head, lane,
+                                group, gthreads, out_row, out_row_f32);
         }
         ++g;
+    }
     }
 
     // A warp that gave up on a wait may still have copies in flight: give them a bounded chance to land
     // before the CTA (and its shared memory) goes away.
     if (dead) {
-        for (int n = consumed; n < consumed + S && lo + n < hi; ++n)
-            mbar_wait_bounded(bar0 + 8u * (uint32_t)(n % S), (uint32_t)(n / S) & 1u, 1u << 16);
+        for (int n = consumed; n < consumed + S && n < (int)(hi - lo) * n_layers; ++n) {
+            mbar_wait_bounded(bar0 + 16u * (uint32_t)(n % S), (uint32_t)(n / S) & 1u, 1u << 16);
+            mbar_wait_bounded(bar0 + 16u * (uint32_t)(n % S) + 8u, (uint32_t)(n / S) & 1u, 1u << 16);
+        }
     }
+}
+
+// ---- whole-step form: merge of the published partials --------------------------------------------------------------
+struct MergeParams {
+    const float* partials;       // [layers][workers + G][H][PART_STRIDE]
+    const int* table;            // tile table [G + 1], then {workers that took part, total tiles}
+    const __half* rotation_t;
+    __half* out;                 // [layers][G][q_dim]
+    float* out_f32;              // optional [layers][G][H][128]
+    long long part_layer_stride; // floats
+    long long q_layer_stride;    // halves
+    int G, H, q_dim;
+};
+constexpr int MERGE_WARPS = 8;
+
+// One CTA per (sequence, layer): the merge that decode_attention_kernel's last-arriving worker does in the one-launch
+// forms, here as a launch of its own after the whole-step kernel, spread over the whole GPU.
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_partials_kernel(const MergeParams p) {
+    __shared__ __align__(16) uint8_t merge_buf[RegionA::MERGE_GROUP_BYTES];
+    pdl_wait();  // the partials and the table come from the previous kernel in the stream
+    const int g = blockIdx.x, layer = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long ts_g = p.table[g], ts_g1 = p.table[g + 1];
+    const long long W = p.table[p.G + 1], N = p.table[p.G + 2];
+    if (N <= 0 || W <= 0) return;
+    // owners of the sequence's first and last tile: worker w holds the tiles [w * N / W, (w + 1) * N / W)
+    const int first_w = (int)(((ts_g + 1) * W - 1) / N);
+    const int last_w = (int)((ts_g1 * W - 1) / N);
+    const int parts = last_w - first_w + 1;
+    const int H = p.H;
+    auto out_row = [&](int vh) -> __half* {
+        if (vh >= H) return nullptr;
+        return p.out + (size_t)layer * (size_t)p.q_layer_stride + (size_t)g * p.q_dim + (size_t)vh * HEAD_DIM;
+    };
+    auto out_row_f32 = [&](int vh) -> float* {
+        if (!p.out_f32 || vh >= H) return nullptr;
+        return p.out_f32 + (((size_t)layer * p.G + (size_t)g) * H + (size_t)vh) * HEAD_DIM;
+    };
+    merge_sequence<MERGE_WARPS>(p.partials + (size_t)layer * (size_t)p.part_layer_stride + (size_t)(first_w + g) * H * PART_STRIDE,
+                                parts, H, smem_u32(merge_buf), p.rotation_t, warp, lane, 0, MERGE_WARPS * 32, out_row, out_row_f32);
 }
 
 }  // namespace tq

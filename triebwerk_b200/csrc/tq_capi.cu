@@ -153,7 +153,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
                           const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
                           long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
                           int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false,
-                          const FusedInputs* fused = nullptr, int qg = 0, int qg_tokens = 0) {
+                          const FusedInputs* fused = nullptr, int qg = 0, int qg_tokens = 0, float* out_f32 = nullptr) {
     FullWorkspace fw = carve_full(workspace, G, num_heads);
     if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
     // bulk copies need 16-byte aligned sources: rows are 512/256 B (codes) and 2*Hkv B (norms, Hkv % 4 == 0 -> 8|16 B)
@@ -163,7 +163,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     AttnParams p{};
     p.ck = (const uint8_t*)ck_q; p.cv = (const uint8_t*)cv_q;
     p.kn = (const __half*)k_norms; p.vn = (const __half*)v_norms;
-    p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)rotation_t; p.out = (__half*)out;
+    p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)rotation_t; p.out = (__half*)out; p.out_f32 = out_f32;
     p.positions = positions; p.row_base = row_base;
     p.tile_start = fw.w.tile_start; p.worker_g = fw.w.worker_g; p.tickets = fw.w.tickets; p.partials = fw.w.partials;
     p.status = fw.w.status;
@@ -175,8 +175,10 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         static const int seq_weight = getenv("TQ_PREFILL_SEQ_WEIGHT") ? atoi(getenv("TQ_PREFILL_SEQ_WEIGHT")) : 10;
         p.app_weight = seq_weight < 0 ? 0 : seq_weight;
     }
+#ifdef TQ_TIMING_SWITCHES
     static const int debug_mode = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
     p.debug = debug_mode;
+#endif
     static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
     p.l2_ahead = l2_ahead > 0 ? l2_ahead : (1 << 28);  // 0 switches the prefetch off
     if (fused) {
@@ -189,7 +191,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         p.app_weight = (!fused->k || app_weight < 0) ? 0 : app_weight;  // nothing to weigh without an append
         p.kv_dim = num_kv_heads * HEAD_DIM; p.capacity_rows = max_seq_len;
     }
-    return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl, fused != nullptr);
+    return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl, fused != nullptr ? 1 : 0);
 }
 
 int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms, const void* v_norms,
@@ -575,7 +577,10 @@ static void engine_release_arena(tq_engine* e) {
     e->G = 0;
     e->total_rows = 0;
     e->d_positions = nullptr;
+    e->d_capacities = nullptr;
     e->d_row_base = nullptr;
+    e->step_partials = nullptr;
+    e->step_table = nullptr;
     e->workspace = nullptr;
     for (auto& l : e->layers) l = tq_engine::Layer();
 }
@@ -587,6 +592,7 @@ void tq_engine_destroy(tq_engine* e) {
     if (e->d_rotation_t) cudaFree(e->d_rotation_t);
     if (e->d_rotation_prep) cudaFree(e->d_rotation_prep);
     if (e->d_rotation_rep) cudaFree(e->d_rotation_rep);
+    if (e->out_f32) cudaFree(e->out_f32);
     if (e->st_in) {
         cudaStreamDestroy(e->st_in);
         cudaStreamDestroy(e->st_out);
@@ -632,7 +638,12 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
         }
     }
     size_t opos = bump(off, (size_t)G * sizeof(int));
+    size_t ocap = bump(off, (size_t)G * sizeof(int));
     size_t orb = bump(off, (size_t)G * sizeof(long long));
+    // whole-step form (packed modes): per-layer split-K partials and the tile table handed to the merge kernel
+    const size_t part_stride = e->kv_bits ? (size_t)(attention_ctas(G, msl) * ATTN_GROUPS + G) * e->shape.num_heads * PART_STRIDE : 0;
+    size_t osp = bump(off, part_stride * e->shape.num_layers * sizeof(float));
+    size_t ost = bump(off, (size_t)(G + 4) * sizeof(int));
     size_t ws_bytes = e->kv_bits ? carve_full(nullptr, G, e->shape.num_heads).bytes
                                  : fp16_workspace_bytes(G, e->shape.num_heads, e->shape.num_kv_heads, msl);
     size_t ows = bump(off, ws_bytes);
@@ -641,7 +652,11 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
     size_t oq = bump(off, qb), okk = bump(off, kb), ovv = bump(off, kb), oo = bump(off, qb);
     if (assign) {
         e->d_positions = (int*)(base + opos);
+        e->d_capacities = ragged ? (int*)(base + ocap) : nullptr;
         e->d_row_base = ragged ? (long long*)(base + orb) : nullptr;
+        e->step_partials = e->kv_bits ? (float*)(base + osp) : nullptr;
+        e->step_part_stride = part_stride;
+        e->step_table = (int*)(base + ost);
         e->workspace = base + ows;
         e->ws_bytes = ws_bytes;
         e->stage_q = base + oq;
@@ -705,6 +720,10 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
         e->arena = (char*)p;
         e->arena_cap = need;
     }
+    if (e->out_f32 && G != e->G) {  // sized for the previous batch
+        cudaFree(e->out_f32);
+        e->out_f32 = nullptr;
+    }
     e->G = G;
     e->msl = msl;
     e->ragged = ragged;
@@ -714,7 +733,10 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
     engine_carve(e, e->arena, G, msl, rows, ragged, true);
     TQ_CUDA(cudaMemset(e->d_positions, 0, (size_t)G * sizeof(int)));
     TQ_CUDA(cudaMemset(e->workspace, 0, e->ws_bytes));
-    if (ragged) TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
+    if (ragged) {
+        TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
+        TQ_CUDA(cudaMemcpy(e->d_capacities, caps.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice));
+    }
     if (!e->d_rotation) {
         int ur = engine_upload_rotation(e, nullptr);
         if (ur != TQ_OK) return ur;
@@ -727,6 +749,14 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
             r = make_code_map(&L.tmV, L.v, rows, kvp);
             if (r != TQ_OK) return r;
         }
+        // every layer is carved alike, so consecutive layers' arrays lie a constant distance apart
+        const int NL = e->shape.num_layers;
+        e->code_layer_stride = NL > 1 ? (size_t)((char*)e->layers[1].k - (char*)e->layers[0].k) : (size_t)rows * kvp;
+        e->norm_layer_stride = NL > 1 ? (size_t)((char*)e->layers[1].kn - (char*)e->layers[0].kn) : (size_t)rows * e->shape.num_kv_heads * 2;
+        r = make_code_map_layers(&e->tmK4, e->layers[0].k, rows, kvp, NL, e->code_layer_stride);
+        if (r != TQ_OK) return r;
+        r = make_code_map_layers(&e->tmV4, e->layers[0].v, rows, kvp, NL, e->code_layer_stride);
+        if (r != TQ_OK) return r;
     }
     return TQ_OK;
 }
@@ -820,6 +850,33 @@ int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s) {
     return engine_upload_rotation(e, cs(s));
 }
 
+int tq_engine_output_f32(tq_engine* e, int enable) {
+    if (!e) return TQ_ERR_ARG;
+    if (!enable) {
+        if (e->out_f32) cudaFree(e->out_f32);
+        e->out_f32 = nullptr;
+        return TQ_OK;
+    }
+    if (e->kv_bits == 0 || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (e->out_f32) cudaFree(e->out_f32);
+    e->out_f32 = nullptr;
+    const size_t bytes = (size_t)e->shape.num_layers * e->G * e->shape.num_heads * HEAD_DIM * sizeof(float);
+    if (cudaMalloc(&e->out_f32, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return TQ_ERR_NOMEM;
+    }
+    return cuda_status(cudaMemset(e->out_f32, 0, bytes));
+}
+
+int tq_engine_read_output_f32(tq_engine* e, float* host_out, int first_layer, int n_layers, tq_stream_t s) {
+    if (!e || !host_out || first_layer < 0 || n_layers <= 0 || first_layer + n_layers > e->shape.num_layers) return TQ_ERR_ARG;
+    if (!e->out_f32) return TQ_ERR_STATE;
+    const size_t per_layer = (size_t)e->G * e->shape.num_heads * HEAD_DIM;
+    TQ_CUDA(cudaMemcpyAsync(host_out, e->out_f32 + per_layer * first_layer, per_layer * n_layers * sizeof(float),
+                            cudaMemcpyDeviceToHost, cs(s)));
+    return cuda_status(cudaStreamSynchronize(cs(s)));
+}
+
 int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
                            tq_stream_t s) {
     if (!e || layer < 0 || layer >= e->shape.num_layers || !q || !k || !v || !out) return TQ_ERR_ARG;
@@ -828,6 +885,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     e->chain_ok = false;
     const tq_engine::Layer& L = e->layers[layer];
     const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, D = e->shape.head_dim;
+    float* const f32 = e->out_f32 ? e->out_f32 + (size_t)layer * e->G * H * HEAD_DIM : nullptr;
     if (e->kv_bits == 0) {
         fp16_cache_write_kernel<<<e->G, 128, 0, cs(s)>>>((__half*)L.k, (__half*)L.v, (const __half*)k, (const __half*)v,
                                                          e->d_positions, e->d_row_base, e->msl, e->msl, e->G,
@@ -848,7 +906,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early};
         const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
                                      e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
-                                     cs(s), use_pdl(), &in);
+                                     cs(s), use_pdl(), &in, 0, 0, f32);
         e->chain_ok = r == TQ_OK;
         e->chain_stream = cs(s);
         return r;
@@ -858,7 +916,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
                         e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep);
     if (r != TQ_OK) return r;
     return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
-                          e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl());
+                          e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl(), nullptr, 0, 0, f32);
 }
 
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
@@ -888,9 +946,64 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s) {
     return TQ_OK;
 }
 
+// Whole-step form of the layers [l0, l0 + n): three launches whatever n is.
+//   1. the new token of every sequence goes into every layer's cache at once (tensor-core append, decode-step form);
+//   2. ONE attention launch streams the n layers back to back and publishes its split-K partials per layer;
+//   3. the merge kernel (one CTA per sequence and layer) combines them and applies the inverse rotation.
+// q, k, v, out point at layer l0's [G][dim] blocks of [layers][G][dim] buffers.
+static bool engine_whole_step_ok(const tq_engine* e, const void* q, const void* k, const void* v, const void* out) {
+    return e->kv_bits != 0 && e->fused && e->whole_step && e->G <= FUSED_MAX_G && e->step_partials &&
+           ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) == 0);
+}
+
+static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, void* out, cudaStream_t s) {
+    e->chain_ok = false;
+    const tq_engine::Layer& L = e->layers[l0];
+    const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, G = e->G;
+    PrefillTcParams t{};
+    t.ck = (uint8_t*)L.k; t.kn = (__half*)L.kn; t.cv = (uint8_t*)L.v; t.vn = (__half*)L.vn;
+    t.k_buf = (const __half*)k; t.v_buf = (const __half*)v; t.rotation = (const __half*)e->d_rotation;
+    t.positions = e->d_positions; t.status = (int*)e->workspace;
+    t.token_row0 = 0; t.seq_stride_rows = e->msl; t.row_base = e->d_row_base;
+    t.capacity_rows = e->msl; t.seq_capacity = e->d_capacities;
+    t.n_seq = n * G; t.T = 1; t.Hkv = Hkv; t.kv_dim = e->kv_dim(); t.bits = e->kv_bits;
+    t.step_G = G; t.code_layer_stride = (long long)e->code_layer_stride; t.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
+    int r = launch_prefill_tc_params(t, s);
+    if (r != TQ_OK) return r;
+
+    FullWorkspace fw = carve_full(e->workspace, G, H);
+    AttnParams p{};
+    p.ck = (const uint8_t*)L.k; p.cv = (const uint8_t*)L.v; p.kn = (const __half*)L.kn; p.vn = (const __half*)L.vn;
+    p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)e->d_rotation_t; p.out = (__half*)out;
+    p.positions = e->d_positions; p.row_base = e->d_row_base;
+    p.tile_start = fw.w.tile_start; p.worker_g = fw.w.worker_g; p.tickets = fw.w.tickets;
+    p.partials = e->step_partials + (size_t)l0 * e->step_part_stride;
+    p.status = fw.w.status;
+    p.total_rows = e->total_rows; p.pos_value = -1; p.max_seq_len = e->msl;
+    p.G = G; p.H = H; p.Hkv = Hkv; p.q_dim = e->q_dim();
+    p.new_q = (const __half*)q; p.rotation = (const __half*)e->d_rotation_rep; p.rot_copies = ROT_COPIES;
+    p.kv_dim = e->kv_dim(); p.capacity_rows = e->msl;
+    p.l2_ahead = 1 << 28;
+    p.layer0 = l0; p.n_layers = n;
+    p.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
+    p.q_layer_stride = (long long)G * e->q_dim();
+    p.part_layer_stride = (long long)e->step_part_stride;
+    p.table_out = e->step_table;
+    r = launch_attention(e->kv_bits, e->tmK4, e->tmV4, p, attention_ctas(G, e->msl), s, use_pdl(), 2);
+    if (r != TQ_OK) return r;
+
+    MergeParams m{};
+    m.partials = p.partials; m.table = e->step_table; m.rotation_t = (const __half*)e->d_rotation_t;
+    m.out = (__half*)out; m.out_f32 = e->out_f32 ? e->out_f32 + (size_t)l0 * G * H * HEAD_DIM : nullptr;
+    m.part_layer_stride = p.part_layer_stride; m.q_layer_stride = p.q_layer_stride;
+    m.G = G; m.H = H; m.q_dim = e->q_dim();
+    return launch_kernel(merge_partials_kernel, dim3(G, n), dim3(MERGE_WARPS * 32), 0, s, use_pdl(), m);
+}
+
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {
     if (!e || !q || !k || !v || !out) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (engine_whole_step_ok(e, q, k, v, out)) return engine_step_layers(e, 0, e->shape.num_layers, q, k, v, out, cs(s));
     const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
     for (int l = 0; l < e->shape.num_layers; ++l) {
         int r = tq_engine_decode_layer(e, l, (const char*)q + qb * l, (const char*)k + kb * l, (const char*)v + kb * l,
@@ -1013,9 +1126,17 @@ int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_h
     for (int c = 0; c < chunks; ++c) {
         const int l0 = first_layer(c), l1 = first_layer(c + 1);
         TQ_CUDA(cudaStreamWaitEvent(cs(s), e->ev_in[c], 0));
+        const bool whole = engine_whole_step_ok(e, e->stage_q, e->stage_k, e->stage_v, e->stage_out) && ((qb | kb) & 15u) == 0;
         for (int l = l0; l < l1; ++l) {
-            int r = tq_engine_decode_layer(e, l, (char*)e->stage_q + qb * l, (char*)e->stage_k + kb * l,
+            int r;
+            if (whole) {  // the chunk's layers in one whole-step pass
+                r = engine_step_layers(e, l0, l1 - l0, (char*)e->stage_q + qb * l0, (char*)e->stage_k + kb * l0,
+                                       (char*)e->stage_v + kb * l0, (char*)e->stage_out + qb * l0, cs(s));
+                l = l1;
+            } else {
+                r = tq_engine_decode_layer(e, l, (char*)e->stage_q + qb * l, (char*)e->stage_k + kb * l,
                                            (char*)e->stage_v + kb * l, (char*)e->stage_out + qb * l, s);
+            }
             if (r != TQ_OK) {
                 cudaStreamSynchronize(e->st_in);
                 cudaStreamSynchronize(cs(s));

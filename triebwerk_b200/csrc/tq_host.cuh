@@ -80,6 +80,23 @@ inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int k
     return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
 }
 
+// All layers' code arrays (layer_stride bytes apart) as ONE map with the layer as the fourth coordinate; same boxes.
+inline int make_code_map_layers(CUtensorMap* m, const void* base, long long rows, int kvp, int layers, size_t layer_stride) {
+    auto fn = encode_fn();
+    if (!fn) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31) || kvp % 128 != 0 || layers <= 0 ||
+        (layer_stride & 15u) != 0 || layer_stride < (size_t)rows * kvp)
+        return TQ_ERR_ARG;
+    cuuint64_t dims[4] = {128u, (cuuint64_t)rows, (cuuint64_t)(kvp / 128), (cuuint64_t)layers};
+    cuuint64_t strides[3] = {(cuuint64_t)kvp, 128u, (cuuint64_t)layer_stride};
+    cuuint32_t box[4] = {128u, (cuuint32_t)TILE_TOKENS, (cuuint32_t)(kvp / 128), 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
+}
+
 // ---- workspace ------------------------------------------------------------------------------------------------------
 // The carve of tq_common.cuh plus two helper arrays used by the prefill form (positions 0..T-1 and a
 // constant row base) and the fp16 twin's ticket/partial area, which aliases the packed path's partials.
@@ -182,6 +199,26 @@ inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 
     return cuda_status(cudaGetLastError());
 }
 
+inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s) {
+    static std::mutex mu;
+    static std::map<int, bool> attr_set;  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev]) {
+            TQ_CUDA(cudaFuncSetAttribute(prefill_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_DYN_SMEM));
+            attr_set[dev] = true;
+        }
+    }
+    const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
+    long long grid = 2ll * device_props().sm_count;
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) return TQ_OK;
+    prefill_append_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
+    return cuda_status(cudaGetLastError());
+}
+
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
     static const bool prefill_tc = !(getenv("TQ_PREFILL_TC") && atoi(getenv("TQ_PREFILL_TC")) == 0);
     // (the tensor-core kernel moves 16 bytes at a time: every array it touches has to be 16-byte aligned)
@@ -219,14 +256,14 @@ inline int attention_ctas(int G, int max_seq_len) {
     return (int)(w < 1 ? 1 : w);
 }
 
-template <int BITS, bool QSPLIT, int HKV, bool FUSED>
+template <int BITS, int HKV, int MODE>
 inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas, cudaStream_t s,
                               bool pdl) {
     static std::map<int, bool> attr_set;  // per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, QSPLIT, HKV, FUSED>,
+        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, HKV, MODE>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_DYN_SMEM));
         attr_set[dev] = true;
     }
@@ -240,35 +277,24 @@ inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, QSPLIT, HKV, FUSED>, tmK, tmV, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, decode_attention_kernel<BITS, HKV, MODE>, tmK, tmV, p));
 }
 
-// `fused`: the launch also appends the step's new token and rotates the queries (AttnParams::new_k ... are set).
+// mode 0: after append_rotate_kernel (rotated queries and tile table in the workspace); 1: one launch per layer and step
+// (table, query rotation, optional append and merge in the kernel); 2: whole-step form over AttnParams::n_layers layers.
 inline int launch_attention(int bits, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas,
-                            cudaStream_t s, bool pdl = false, bool fused = false) {
-    // TQ_ATTN_QSPLIT=0 selects the variant that feeds the query to the tensor cores as plain fp16 (no high/low split)
-    static const bool qsplit = !(getenv("TQ_ATTN_QSPLIT") && atoi(getenv("TQ_ATTN_QSPLIT")) == 0);
-    if (fused) {
-        if (p.Hkv == 8)
-            return bits == 4 ? launch_attention_t<4, true, 8, true>(tmK, tmV, p, ctas, s, pdl)
-                             : launch_attention_t<2, true, 8, true>(tmK, tmV, p, ctas, s, pdl);
-        if (p.Hkv == 4)
-            return bits == 4 ? launch_attention_t<4, true, 4, true>(tmK, tmV, p, ctas, s, pdl)
-                             : launch_attention_t<2, true, 4, true>(tmK, tmV, p, ctas, s, pdl);
-        return TQ_ERR_UNSUPPORTED;
-    }
-    if (p.Hkv == 8) {
-        if (bits == 4)
-            return qsplit ? launch_attention_t<4, true, 8, false>(tmK, tmV, p, ctas, s, pdl)
-                          : launch_attention_t<4, false, 8, false>(tmK, tmV, p, ctas, s, pdl);
-        return qsplit ? launch_attention_t<2, true, 8, false>(tmK, tmV, p, ctas, s, pdl)
-                      : launch_attention_t<2, false, 8, false>(tmK, tmV, p, ctas, s, pdl);
-    }
-    if (p.Hkv == 4) {
-        if (bits == 4) return launch_attention_t<4, true, 4, false>(tmK, tmV, p, ctas, s, pdl);
-        return launch_attention_t<2, true, 4, false>(tmK, tmV, p, ctas, s, pdl);
-    }
-    return TQ_ERR_UNSUPPORTED;
+                            cudaStream_t s, bool pdl = false, int mode = 0) {
+    if (p.Hkv != 8 && p.Hkv != 4) return TQ_ERR_UNSUPPORTED;
+#define TQ_ATTN_DISPATCH(MODE)                                                                                  \
+    if (p.Hkv == 8)                                                                                             \
+        return bits == 4 ? launch_attention_t<4, 8, MODE>(tmK, tmV, p, ctas, s, pdl)                            \
+                         : launch_attention_t<2, 8, MODE>(tmK, tmV, p, ctas, s, pdl);                           \
+    return bits == 4 ? launch_attention_t<4, 4, MODE>(tmK, tmV, p, ctas, s, pdl)                                \
+                     : launch_attention_t<2, 4, MODE>(tmK, tmV, p, ctas, s, pdl);
+    if (mode == 2) { TQ_ATTN_DISPATCH(2) }
+    if (mode == 1) { TQ_ATTN_DISPATCH(1) }
+    TQ_ATTN_DISPATCH(0)
+#undef TQ_ATTN_DISPATCH
 }
 
 __global__ void transpose_rotation_kernel(__half* dst, const __half* src, int* tickets = nullptr, int n_tickets = 0) {
@@ -408,7 +434,18 @@ struct tq_engine {
     };
     std::vector<Layer> layers;
 
+    // whole-step form: all layers' code arrays as one tensor map each, per-layer split-K partials, the tile table
+    CUtensorMap tmK4{}, tmV4{};
+    size_t code_layer_stride = 0;      // bytes between consecutive layers' K (and V) code arrays
+    size_t norm_layer_stride = 0;      // bytes between consecutive layers' norm arrays
+    float* step_partials = nullptr;    // [layers][workers + G][H][PART_STRIDE]
+    size_t step_part_stride = 0;       // floats per layer
+    int* step_table = nullptr;         // [G + 4]
+    bool whole_step = !(getenv("TQ_WHOLE_STEP") && atoi(getenv("TQ_WHOLE_STEP")) == 0);
+    float* out_f32 = nullptr;          // optional [layers][G][H][128]: results before the fp16 rounding (outside the arena)
+
     int* d_positions = nullptr;
+    int* d_capacities = nullptr;       // ragged mode: rows each sequence may use
     long long* d_row_base = nullptr;
     void* workspace = nullptr;
     size_t ws_bytes = 0;

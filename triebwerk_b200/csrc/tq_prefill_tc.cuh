@@ -46,7 +46,8 @@ struct TcSmem {
     static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
     static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint2[512] bucket table: {code | 0x80 + bound index, bound}
     static constexpr uint32_t CTRL = GRID + 4096;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
-    static constexpr uint32_t BYTES = CTRL + 16;
+    static constexpr uint32_t LAYERS = CTRL + 16;        // int[128] layer of each vector (decode-step form)
+    static constexpr uint32_t BYTES = LAYERS + 512;
 };
 constexpr size_t TC_DYN_SMEM = TcSmem::BYTES + 1024;  // + alignment slack
 
@@ -66,6 +67,14 @@ struct PrefillTcParams {
     int capacity_rows;
     int n_seq;                 // sequences in the call: inputs are [n_seq][T][kv_dim], all at the same positions
     int T, Hkv, kv_dim, bits;
+    // Decode-step form (step_G > 0): the call appends ONE new token of each of step_G sequences in n_seq / step_G layers
+    // at once.  "Sequence" s of the call is then (layer s / step_G, sequence s % step_G): T = 1, inputs [layers][step_G]
+    // [kv_dim], position positions[s % step_G], row base of sequence s % step_G, and the arrays of layer l lie
+    // code_layer_stride bytes (norm_layer_stride halves) behind those of the call's first layer.
+    int step_G;
+    long long code_layer_stride;
+    long long norm_layer_stride;
+    const int* seq_capacity;   // optional, decode-step form: rows each sequence may use (else capacity_rows for all)
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
@@ -134,6 +143,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
     volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
     long long* rows_s = reinterpret_cast<long long*>(gbase + TcSmem::ROWS);
     float* inv_s = reinterpret_cast<float*>(gbase + TcSmem::INV);
+    int* layer_s = reinterpret_cast<int*>(gbase + TcSmem::LAYERS);
     uint32_t* list_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::LIST);
     uint2* grid_s = reinterpret_cast<uint2*>(gbase + TcSmem::GRID);
 
@@ -250,16 +260,24 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             const float inv = rsqrt_approx_ftz(tt);
             if (c == 0) {
                 long long row = -1;
+                int layer = 0;
                 if (live) {
-                    const int pos = p.positions[t];
-                    if (pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows)) {
-                        row = (p.row_base ? p.row_base[seq] : p.token_row0 + (long long)seq * p.seq_stride_rows) + pos;
-                        cn[(size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
+                    int sq = seq, cap = p.capacity_rows;
+                    if (p.step_G > 0) {
+                        layer = seq / p.step_G;
+                        sq = seq - layer * p.step_G;
+                        if (p.seq_capacity) cap = p.seq_capacity[sq];
+                    }
+                    const int pos = p.step_G > 0 ? p.positions[sq] : p.positions[t];
+                    if (pos >= 0 && (cap <= 0 || pos < cap)) {
+                        row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
+                        cn[(size_t)layer * (size_t)p.norm_layer_stride + (size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
                     } else {
                         atomicMax(p.status, ST_BAD_POSITION);
                     }
                 }
                 rows_s[v] = row;
+                layer_s[v] = layer;
                 inv_s[v] = inv;
             }
 #pragma unroll
@@ -450,7 +468,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 if (row >= 0) {
                     const int head = (vec0 + v) % p.Hkv;
                     const uint4 u = *reinterpret_cast<const uint4*>(gbase + TcSmem::STAGE + (size_t)v * bpv + 16 * part);
-                    *reinterpret_cast<uint4*>(cq + (size_t)row * kvp + (size_t)head * bpv + 16 * part) = u;
+                    *reinterpret_cast<uint4*>(cq + (size_t)layer_s[v] * (size_t)p.code_layer_stride + (size_t)row * kvp +
+                                              (size_t)head * bpv + 16 * part) = u;
                 }
             }
         }

@@ -134,6 +134,18 @@ class Engine:
                                           self._stream()), "decode_step")
         return out
 
+    def enable_output_f32(self, on: bool = True) -> None:
+        """Also keep the attention results as fp32, before their rounding to fp16 (error reports; packed modes)."""
+        check(lib().tq_engine_output_f32(self._h, int(bool(on))), "output_f32")
+
+    def last_output_f32(self, n_layers: int = 1, first_layer: int = 0):
+        """numpy [n_layers, G, num_heads, head_dim] fp32 results of the last step (after enable_output_f32)."""
+        import numpy as np
+        s = self.shape
+        out = np.empty((n_layers, self.G, s.num_heads, s.head_dim), np.float32)
+        check(lib().tq_engine_read_output_f32(self._h, out.ctypes.data, first_layer, n_layers, self._stream()), "read_output_f32")
+        return out
+
     def prefill_append(self, layer: int, seq: int, k: torch.Tensor, v: torch.Tensor, first_pos: int = 0) -> None:
         """Token-form append of k/v [T, kv_dim] for one sequence (reference engine/engine.cpp:2121-2130)."""
         assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous()
