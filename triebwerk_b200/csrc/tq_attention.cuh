@@ -98,6 +98,8 @@ struct AttnParams {
     long long q_layer_stride;      // halves between consecutive layers' queries (and outputs)
     long long part_layer_stride;   // floats between consecutive layers' partial areas
     int* table_out;                // [G + 4]: the tile table, then {workers taking part, total tiles}, for the merge kernel
+    const __half* q_rot16;         // whole-step form: pre-rotated, pre-scaled fp16 queries of layer0, [layers][G][H][128]
+                                   // (rotate_queries_kernel); a sequence's block reaches shared memory by one bulk copy
 #ifdef TQ_TIMING_SWITCHES
     int debug;                 // timing-experiment builds only: bit 0 = skip the math, bit 1 = skip the loads, ... (results are then wrong)
 #endif
@@ -433,6 +435,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             mbar_init(bar0 + 8u * s, 1);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(cnt0 + 4u * s), "r"(0u) : "memory");
         }
+        if (PERSIST) mbar_init(a_base + 320u + 8u * (uint32_t)group, 1);
         fence_mbar_init();
         fence_proxy_async_smem();
     }
@@ -567,6 +570,16 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         }
     };
     auto cursor_more = [&]() -> bool { return PERSIST ? cl_layer < n_layers : cl_tile < hi_i; };
+    // whole-step form: the rotated queries of a segment's sequence arrive by a bulk copy into the (otherwise idle) merge
+    // area of the worker, completion on a barrier of their own; the copy for the next segment goes out as soon as every
+    // warp has taken its fragments of the current one
+    const uint32_t qbar = a_base + 320u + 8u * (uint32_t)group;
+    const uint32_t q_block_bytes = (uint32_t)p.H * HEAD_DIM * 2u;
+    uint32_t q_par = 0;
+    auto issue_queries = [&](int layer, int gq) {
+        mbar_arrive_expect_tx(qbar, q_block_bytes);
+        bulk_load(merge_s, p.q_rot16 + ((size_t)layer * p.G + (size_t)gq) * (size_t)p.H * HEAD_DIM, q_block_bytes, qbar);
+    };
     int consumed = 0;
     int s_idx = 0;          // 2-bit form: stage of the tile being consumed and the parity of its barrier
     uint32_t s_par = 0;
@@ -623,6 +636,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
         }
     };
+    if (PERSIST && gtid == 0 && loads_on) issue_queries(0, g);
     if constexpr (FUSED) {
         // The new token of a sequence is appended by the worker that owns the sequence's last tile (the only tile the
         // row can be in), before that tile is fetched.  The rotation of the sequence's 2 * Hkv head vectors runs on the
@@ -939,7 +953,41 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         // query fragments (B operand of the score product): lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head
         // head*grp + gl as fp16
         uint32_t qb[8][2];
-        {
+        if constexpr (PERSIST) {
+            uint32_t ok = (dead || !loads_on) ? 1u : 0u;
+            for (uint32_t it = 0; it < (1u << 14) && !ok; ++it) ok = mbar_try_wait_hint(qbar, q_par, 20000u);
+            if (!ok) {
+                dead = true;
+                if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            q_par ^= 1u;
+            // lane (gl, t4): the 32 coordinates 32*t4 .. of head head*grp + gl, 64 bytes
+            uint4 qw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                qw[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (gl < grp && !dead) qw[i] = ldsv128(merge_s + (uint32_t)((head * grp + gl) * HEAD_DIM + 32 * t4 + 8 * i) * 2u);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t w4[4] = {qw[i].x, qw[i].y, qw[i].z, qw[i].w};
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    // step j = 2*i + h2 takes the coordinates 4j .. 4j+3: (4j, 4j+1), (4j+2, 4j+3) -- the 2-bit table
+                    // returns the four values of a byte as (0, 2), (1, 3)
+                    const uint32_t a = w4[2 * h2], b = w4[2 * h2 + 1];
+                    qb[2 * i + h2][0] = BITS == 2 ? prmt(a, b, 0x5410u) : a;
+                    qb[2 * i + h2][1] = BITS == 2 ? prmt(a, b, 0x7632u) : b;
+                }
+            }
+            group_barrier(group, gthreads);  // every warp holds its fragments: the area may take the next block
+            if (gtid == 0 && !dead && loads_on) {
+                fence_proxy_async_smem();
+                if (seg_end < hi) issue_queries(layer, g + 1);
+                else if (layer + 1 < n_layers) issue_queries(layer + 1, g_lo);
+            }
+        } else {
             float qv[32];
             if constexpr (FUSED) {
                 // Rotate this sequence's queries here: rot[h][d] = sum_k q[h][k] * R[d][k] on the tensor cores, 16 heads

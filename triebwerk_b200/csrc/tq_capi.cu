@@ -581,6 +581,7 @@ static void engine_release_arena(tq_engine* e) {
     e->d_row_base = nullptr;
     e->step_partials = nullptr;
     e->step_table = nullptr;
+    e->step_qrot = nullptr;
     e->workspace = nullptr;
     for (auto& l : e->layers) l = tq_engine::Layer();
 }
@@ -644,6 +645,7 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
     const size_t part_stride = e->kv_bits ? (size_t)(attention_ctas(G, msl) * ATTN_GROUPS + G) * e->shape.num_heads * PART_STRIDE : 0;
     size_t osp = bump(off, part_stride * e->shape.num_layers * sizeof(float));
     size_t ost = bump(off, (size_t)(G + 4) * sizeof(int));
+    size_t osq = bump(off, e->kv_bits ? (size_t)e->shape.num_layers * G * e->shape.num_heads * HEAD_DIM * 2 : 0);
     size_t ws_bytes = e->kv_bits ? carve_full(nullptr, G, e->shape.num_heads).bytes
                                  : fp16_workspace_bytes(G, e->shape.num_heads, e->shape.num_kv_heads, msl);
     size_t ows = bump(off, ws_bytes);
@@ -657,6 +659,7 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
         e->step_partials = e->kv_bits ? (float*)(base + osp) : nullptr;
         e->step_part_stride = part_stride;
         e->step_table = (int*)(base + ost);
+        e->step_qrot = base + osq;
         e->workspace = base + ows;
         e->ws_bytes = ws_bytes;
         e->stage_q = base + oq;
@@ -970,6 +973,18 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     t.step_G = G; t.code_layer_stride = (long long)e->code_layer_stride; t.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
     int r = launch_prefill_tc_params(t, s);
     if (r != TQ_OK) return r;
+    {   // all query heads of the n layers, rotated and scaled, as fp16
+        QRotParams qr{};
+        qr.q = (const __half*)q; qr.rotation = (const __half*)e->d_rotation;
+        qr.q_rot = (__half*)e->step_qrot + (size_t)l0 * G * H * HEAD_DIM;
+        qr.n_vec = (long long)n * G * H; qr.H = H; qr.q_dim = e->q_dim();
+        long long blocks = (qr.n_vec + 15) / 16;
+        const long long cap = 4ll * device_props().sm_count;
+        if (blocks > cap) blocks = cap;
+        rotate_queries_kernel<<<(unsigned)blocks, QROT_WARPS * 32, 0, s>>>(qr);
+        r = cuda_status(cudaGetLastError());
+        if (r != TQ_OK) return r;
+    }
 
     FullWorkspace fw = carve_full(e->workspace, G, H);
     AttnParams p{};
@@ -983,12 +998,17 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     p.G = G; p.H = H; p.Hkv = Hkv; p.q_dim = e->q_dim();
     p.new_q = (const __half*)q; p.rotation = (const __half*)e->d_rotation_rep; p.rot_copies = ROT_COPIES;
     p.kv_dim = e->kv_dim(); p.capacity_rows = e->msl;
-    p.l2_ahead = 1 << 28;
+    static const int l2_ahead = getenv("TQ_ATTN_L2_AHEAD") ? atoi(getenv("TQ_ATTN_L2_AHEAD")) : ATTN_L2_AHEAD;
+    p.l2_ahead = l2_ahead > 0 ? l2_ahead : (1 << 28);  // 0 switches the prefetch off
     p.layer0 = l0; p.n_layers = n;
     p.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
     p.q_layer_stride = (long long)G * e->q_dim();
     p.part_layer_stride = (long long)e->step_part_stride;
     p.table_out = e->step_table;
+    p.q_rot16 = (const __half*)e->step_qrot + (size_t)l0 * G * H * HEAD_DIM;
+#ifdef TQ_TIMING_SWITCHES
+    p.debug = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
+#endif
     r = launch_attention(e->kv_bits, e->tmK4, e->tmV4, p, attention_ctas(G, e->msl), s, use_pdl(), 2);
     if (r != TQ_OK) return r;
 

@@ -19,6 +19,7 @@
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
 #include "tq_fp16.cuh"
+#include "tq_qrot.cuh"
 
 namespace tq {
 
@@ -441,6 +442,7 @@ struct tq_engine {
     float* step_partials = nullptr;    // [layers][workers + G][H][PART_STRIDE]
     size_t step_part_stride = 0;       // floats per layer
     int* step_table = nullptr;         // [G + 4]
+    void* step_qrot = nullptr;         // [layers][G][H][128] fp16: pre-rotated, pre-scaled queries
     bool whole_step = !(getenv("TQ_WHOLE_STEP") && atoi(getenv("TQ_WHOLE_STEP")) == 0);
     float* out_f32 = nullptr;          // optional [layers][G][H][128]: results before the fp16 rounding (outside the arena)
 
