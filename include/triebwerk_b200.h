@@ -262,6 +262,11 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s);
  * environment to get one launch per layer instead. */
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
 
+/* The same for the layers first_layer .. first_layer + n_layers - 1 only; q, k, v, out point at the block of
+ * first_layer ([n_layers][G][dim]).  Lets a caller exchange or copy out one group of layers while the next is computed. */
+int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v,
+                            void* out, tq_stream_t s);
+
 /* Error reporting aid, packed modes: with enable != 0 the engine also keeps every attention result as fp32, i.e. before
  * its final rounding to fp16 ([layers][G][num_heads][128], allocated outside the arena; call after
  * tq_engine_alloc_batch, and again after the batch shape changes); enable == 0 frees the buffer.

@@ -74,3 +74,40 @@ def test_two_ranks_reproduce_single_process_result():
     assert abs(loads[0] - loads[1]) <= max(pb["lengths"])
     assert (out0.view(np.uint16) == ref.view(np.uint16)).all()
     assert (out1.view(np.uint16) == ref.view(np.uint16)).all()
+
+
+def _worker_groups(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from triebwerk_b200.sharded import LayerGroupGatherer, layer_groups, shard_plan
+        lengths = [9, 3, 40, 17, 5, 60, 33]
+        plan = shard_plan(lengths, world)
+        n_layers, width = 5, 6
+        groups = layer_groups(n_layers, 3)
+        assert groups[0][0] == 0 and groups[-1] == (n_layers - 1, n_layers)
+        assert all(a[1] == b[0] for a, b in zip(groups, groups[1:]))
+        # value of (layer, sequence, column) is unique, so misplaced rows show
+        full = torch.arange(n_layers * len(lengths) * width, dtype=torch.float32).view(n_layers, len(lengths), width)
+        local = full[:, plan[rank]].contiguous()
+        gat = LayerGroupGatherer(plan, groups)
+        for step in range(2):  # buffers are reused from step to step
+            for gi, (l0, l1) in enumerate(groups):
+                gat.gather(gi, local[l0:l1] + step)
+            gat.finish()
+            ret[(rank, step)] = gat.result().numpy().copy()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layer_group_gather_two_ranks():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker_groups, args=(world, port, ret), nprocs=world, join=True)
+    ref = np.arange(5 * 7 * 6, dtype=np.float32).reshape(5, 7, 6)
+    for rank in range(world):
+        for step in range(2):
+            assert (ret[(rank, step)] == ref + step).all()

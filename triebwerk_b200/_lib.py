@@ -25,7 +25,7 @@ SYMBOLS = [
     "tq_engine_set_positions", "tq_engine_advance", "tq_engine_layer_ptrs", "tq_engine_row_base",
     "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append", "tq_engine_prefill_append_batch",
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
-    "tq_engine_output_f32", "tq_engine_read_output_f32",
+    "tq_engine_output_f32", "tq_engine_read_output_f32", "tq_engine_decode_layers",
 ]
 
 
@@ -98,6 +98,7 @@ def lib() -> C.CDLL:
     sig("tq_engine_decode_step", i, [vp, vp, vp, vp, vp, vp])
     sig("tq_engine_status", i, [vp, vp])
     sig("tq_engine_attend_step", i, [vp, vp, vp])
+    sig("tq_engine_decode_layers", i, [vp, i, i, vp, vp, vp, vp, vp])
     sig("tq_engine_output_f32", i, [vp, i])
     sig("tq_engine_read_output_f32", i, [vp, vp, i, i, vp])
     _lib = L

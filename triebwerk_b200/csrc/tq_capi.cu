@@ -1020,17 +1020,24 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     return launch_kernel(merge_partials_kernel, dim3(G, n), dim3(MERGE_WARPS * 32), 0, s, use_pdl(), m);
 }
 
-int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {
-    if (!e || !q || !k || !v || !out) return TQ_ERR_ARG;
+int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v, void* out,
+                            tq_stream_t s) {
+    if (!e || !q || !k || !v || !out || first_layer < 0 || n_layers <= 0 || first_layer + n_layers > e->shape.num_layers)
+        return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
-    if (engine_whole_step_ok(e, q, k, v, out)) return engine_step_layers(e, 0, e->shape.num_layers, q, k, v, out, cs(s));
+    if (engine_whole_step_ok(e, q, k, v, out)) return engine_step_layers(e, first_layer, n_layers, q, k, v, out, cs(s));
     const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
-    for (int l = 0; l < e->shape.num_layers; ++l) {
-        int r = tq_engine_decode_layer(e, l, (const char*)q + qb * l, (const char*)k + kb * l, (const char*)v + kb * l,
-                                       (char*)out + qb * l, s);
+    for (int i = 0; i < n_layers; ++i) {
+        int r = tq_engine_decode_layer(e, first_layer + i, (const char*)q + qb * i, (const char*)k + kb * i, (const char*)v + kb * i,
+                                       (char*)out + qb * i, s);
         if (r != TQ_OK) return r;
     }
     return TQ_OK;
+}
+
+int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {
+    if (!e) return TQ_ERR_ARG;
+    return tq_engine_decode_layers(e, 0, e->shape.num_layers, q, k, v, out, s);
 }
 
 __global__ void iota_from_kernel(int* pos, int n, int first) {

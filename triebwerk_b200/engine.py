@@ -134,6 +134,16 @@ class Engine:
                                           self._stream()), "decode_step")
         return out
 
+    def decode_layers(self, first_layer: int, n_layers: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                      out: torch.Tensor) -> torch.Tensor:
+        """The layers first_layer .. first_layer + n_layers - 1 of a decode step; q/k/v/out are the whole-step buffers
+        [layers, G, dim] (the call addresses the blocks of its layers itself)."""
+        for t in (q, k, v, out):
+            assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16 and t.shape[0] == self.shape.num_layers
+        check(lib().tq_engine_decode_layers(self._h, first_layer, n_layers, q[first_layer].data_ptr(), k[first_layer].data_ptr(),
+                                            v[first_layer].data_ptr(), out[first_layer].data_ptr(), self._stream()), "decode_layers")
+        return out
+
     def enable_output_f32(self, on: bool = True) -> None:
         """Also keep the attention results as fp32, before their rounding to fp16 (error reports; packed modes)."""
         check(lib().tq_engine_output_f32(self._h, int(bool(on))), "output_f32")
