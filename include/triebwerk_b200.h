@@ -144,22 +144,26 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
                         size_t workspace_bytes, tq_stream_t s);
 
 /* No counterpart in the reference.  Decode attention over the packed cache for callers that cannot allocate device
- * memory once they are running: processes whose memory pool already owns the whole GPU, serving loops that forbid
- * cudaMalloc because it stalls the device, code that is already inside a CUDA-graph capture when it gets here.  Same
- * result as launch_turbo_gqa_attention_batch (it takes the un-rotated queries q [G][q_dim]), but the kernel's scratch
- * (rotated queries, tile table, tickets, split-K partials, transposed rotation) lives in a fixed 20 MiB device array
- * inside the library image, present on every GPU that loads the library until the process exits.  The call makes no
- * cudaMalloc / cudaFree and uses no allocator of any framework.
+ * memory once they are running: processes whose memory pool already owns the whole GPU (a raw cudaMalloc would fail or
+ * fight that pool) and serving loops that forbid cudaMalloc because it synchronises the device.  Same result as
+ * launch_turbo_gqa_attention_batch (it takes the un-rotated queries q [G][q_dim]), but the kernel's scratch (rotated
+ * queries, tile table, tickets, split-K partials, transposed rotation) lives in a fixed 20 MiB device array inside the
+ * library image, present on every GPU that loads the library until the process exits.  The call makes no cudaMalloc /
+ * cudaFree and uses no allocator of any framework.
  *   Limit: tq_workspace_bytes(G, num_heads) must not exceed 20 MiB -- that covers 64 sequences x 32 query heads or
- *   256 x 16; larger requests return TQ_ERR_CAPACITY and launch nothing.
+ *   256 x 16; larger requests return TQ_ERR_CAPACITY and launch nothing.  Arguments are checked before anything is
+ *   enqueued: a refused call leaves the stream untouched.
  *   The first call on a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream
  *   capture.  All calls share the one array and it keeps the previous call's contents (the call itself clears what
- *   must start at zero): two calls that overlap on the GPU -- different streams, or graphs replayed concurrently --
- *   race on it and must be serialised by the caller. */
+ *   must start at zero): two calls that overlap on the GPU -- different streams, or work replayed concurrently --
+ *   race on it and must be serialised by the caller.
+ *   Device-side trouble (a bounded wait that gave up = 1, a shared-memory layout refused = 2) is collected in a status
+ *   word inside the array; tq_static_status reads and clears it (0 = fine) and synchronises the stream. */
 int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
                                const void* k_norms, const void* v_norms, const void* rotation,
                                const int* positions, long long total_rows, int max_seq_len, int G, int num_heads,
                                int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, tq_stream_t s);
+int tq_static_status(tq_stream_t s);
 
 /* kv_bits = 0 twins with the same slot addressing (replace launch_kv_cache_write_batch and
  * launch_gqa_attention_batch, engine/kernels.cu:1351-1357). */
@@ -173,6 +177,13 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
 /* Reads (and clears) the device status word kept in `workspace`: 0, or a code saying which bounded wait
  * gave up.  Synchronises the stream. */
 int tq_workspace_status(void* workspace, tq_stream_t s);
+
+/* Self-test of the bounded waits (no counterpart in the reference, whose kernels have no asynchronous copies): runs a
+ * one-warp kernel that arms a copy barrier for bytes nobody sends and waits for them with at most `limit` polls
+ * (1 .. 2^20).  The wait gives up, the kernel records status 1 in the int at `status_word` (device memory, zero
+ * before the call) and exits normally; the call returns that word (1 expected) after clearing it.  Nothing traps or
+ * spins without bound. */
+int tq_selftest_bounded_wait(void* status_word, unsigned limit, tq_stream_t s);
 
 /* ---- KV arena / engine state ----------------------------------------------------------------------------------------
  * The part of InferenceEngine that owns the cache: constructor arguments (engine/engine.cpp:300-317),
@@ -222,6 +233,25 @@ int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s);
  * reference (engine/engine.cpp:922-1022).  An external arena is detached by sleep and must be set again. */
 int tq_engine_sleep(tq_engine* e);
 int tq_engine_wake(tq_engine* e);
+
+/* Cache persistence (the reference's sleep()/wake(), engine/engine.cpp:922-1022, drop the KV cache and the caller
+ * has to prefill again; these calls keep it).
+ * A sequence's written rows travel as a self-describing blob in the ON-CACHE byte layout: 8 int32 of header ("TQKV",
+ * version, kv_bits, layers, kv heads, head_dim, tokens, 0), then per layer K codes [tokens][kvp], V codes, K norms
+ * [tokens][kv heads] fp16, V norms (kv_bits = 0: K rows [tokens][kv_dim] fp16, V rows).  A blob can go to disk, to
+ * another engine of the same shape or to another slot and back; nothing is re-quantised.
+ *   tq_engine_sequence_blob_bytes: size of a blob of n_tokens rows.
+ *   tq_engine_export_sequence: rows 0 .. n_tokens-1 of sequence `seq` into host memory; synchronises the stream.
+ *   tq_engine_import_sequence: the blob's rows into slot `seq` (TQ_ERR_UNSUPPORTED for a blob of another shape or
+ *     cache mode, TQ_ERR_CAPACITY if it does not fit the slot); the slot's position becomes the blob's token count,
+ *     i.e. the next token is appended right behind the imported rows.
+ *   tq_engine_sleep_keep: like tq_engine_sleep, but every sequence's rows 0 .. position-1 and the positions are kept in
+ *     host memory; tq_engine_wake (library-owned arena) or the next tq_engine_alloc_batch of the same batch shape
+ *     (caller-owned arena: after tq_engine_set_arena) puts them back, and decoding continues without a new prefill. */
+size_t tq_engine_sequence_blob_bytes(const tq_engine* e, int n_tokens);
+int tq_engine_export_sequence(tq_engine* e, int seq, int n_tokens, void* host_blob, size_t blob_bytes, tq_stream_t s);
+int tq_engine_import_sequence(tq_engine* e, int seq, const void* host_blob, size_t blob_bytes, tq_stream_t s);
+int tq_engine_sleep_keep(tq_engine* e);
 
 /* Reads and clears the engine's device status word (0 = fine; 1 = a bounded wait on a TMA barrier gave up;
  * 2 = shared-memory layout refused; 3 = a position outside its slot).  Synchronises the stream. */

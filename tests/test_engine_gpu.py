@@ -302,3 +302,112 @@ def test_four_kv_heads_long_context_against_oracle(bits, fused):
     tqo.append_tokens(vq, vn, v, R, np.arange(n + 1, dtype=np.int32), n + 1, Hkv, D, bits)
     ref, _ = tqo.attention_single(q[0, 0], cq, vq, cn, vn, R, n, n + 1, H, Hkv, D, bits)
     hp.assert_attention_close(out.cpu().numpy().reshape(1, q_dim), ref[None], H, D, f"bits={bits} fused={fused}")
+
+
+@pytest.mark.parametrize("bits,form", [(4, "whole-step"), (4, "one-launch"), (2, "two-launch"), (0, "fp16")])
+def test_position_past_its_own_slot_is_refused(bits, form, monkeypatch):
+    """Ragged slots of 32 and 64 rows: sequence 0 is advanced to position 32, one row past ITS slot (which would be row
+    0 of sequence 1's slot).  The append must skip it, raise status 3 and leave sequence 1's rows as they were."""
+    H, Hkv, D, NL = 16, 8, 128, 2
+    kv_dim, q_dim = Hkv * D, H * D
+    rng = np.random.default_rng(21)
+    eng = tq.Engine(64, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(2, 64, [32, 64])
+    eng.set_fused(form != "two-launch")
+    for layer in range(NL):
+        for g, n in enumerate((32, 40)):
+            k = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            v = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            eng.prefill_append(layer, g, k, v, 0)
+    eng.set_positions([31, 40])
+    eng.advance()  # sequence 0 -> 32 = its capacity, sequence 1 -> 41
+    assert eng.positions().tolist() == [32, 41]
+    before = [[t.clone() for t in eng.layer_cache(layer) if t is not None] for layer in range(NL)]
+    q = gu.dev(rng.standard_normal((NL, 2, q_dim), dtype=np.float32).astype(np.float16))
+    k = gu.dev(rng.standard_normal((NL, 2, kv_dim), dtype=np.float32).astype(np.float16))
+    v = gu.dev(rng.standard_normal((NL, 2, kv_dim), dtype=np.float32).astype(np.float16))
+    out = torch.empty_like(q)
+    if form == "one-launch":
+        for layer in range(NL):
+            eng.decode_layer(layer, q[layer], k[layer], v[layer], out[layer])
+    else:
+        eng.decode_step(q, k, v, out)
+    assert eng.status() == 3
+    for layer in range(NL):
+        after = [t for t in eng.layer_cache(layer) if t is not None]
+        for a, b in zip(before[layer], after):
+            # rows 32 .. 72 are sequence 1's written rows (its slot starts at row 32); row 32 + 41 is its new token
+            assert torch.equal(a[32:32 + 41].view(torch.uint8), b[32:32 + 41].view(torch.uint8)), "a neighbour's rows changed"
+            assert not torch.equal(a[32 + 41].view(torch.uint8), b[32 + 41].view(torch.uint8)), "sequence 1's own token is missing"
+
+
+def test_bounded_wait_gives_up_with_status_1():
+    """A copy barrier armed for bytes that never arrive: the bounded wait runs out, the kernel reports status 1
+    (a wait on a copy barrier gave up) and exits normally; the context stays usable."""
+    word = torch.zeros(64, dtype=torch.int32, device="cuda")
+    st = tq.lib().tq_selftest_bounded_wait(word.data_ptr(), 2000, torch.cuda.current_stream().cuda_stream)
+    assert st == 1
+    assert int(word[0].item()) == 0  # read and cleared
+    x = torch.arange(8, device="cuda").sum().item()  # the context still works
+    assert x == 28
+
+
+@pytest.mark.parametrize("bits", [4, 0])
+def test_sleep_keep_wake_and_sequence_blobs(bits):
+    """Cache persistence: sleep_keep() + wake() bring back every sequence's rows and positions, and a decode step
+    afterwards gives the bytes and outputs of an engine that never slept; a sequence exported as a blob and imported
+    into another engine's slot continues there."""
+    H, Hkv, D, NL = 16, 8, 128, 2
+    kv_dim, q_dim = Hkv * D, H * D
+    lengths = [70, 5, 33]
+    caps = [96, 32, 64]
+    rng = np.random.default_rng(31)
+    engines = [tq.Engine(128, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D) for _ in range(2)]
+    for eng in engines:
+        eng.alloc_batch(3, 128, caps)
+    for layer in range(NL):
+        for g, n in enumerate(lengths):
+            k = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            v = gu.dev(rng.standard_normal((n, kv_dim), dtype=np.float32).astype(np.float16))
+            for eng in engines:
+                eng.prefill_append(layer, g, k, v, 0)
+    for eng in engines:
+        eng.set_positions(lengths)
+    a, b = engines
+    blob1 = a.export_sequence(1, lengths[1])
+    a.sleep_keep()
+    with pytest.raises(tq.TqError):
+        a.decode_layer(0, torch.zeros(3, q_dim, dtype=torch.float16, device="cuda"), torch.zeros(3, kv_dim, dtype=torch.float16, device="cuda"),
+                       torch.zeros(3, kv_dim, dtype=torch.float16, device="cuda"))
+    a.wake()
+    a.G = 3
+    assert a.positions().tolist() == lengths
+    q = gu.dev(rng.standard_normal((NL, 3, q_dim), dtype=np.float32).astype(np.float16))
+    k = gu.dev(rng.standard_normal((NL, 3, kv_dim), dtype=np.float32).astype(np.float16))
+    v = gu.dev(rng.standard_normal((NL, 3, kv_dim), dtype=np.float32).astype(np.float16))
+    outs = []
+    for eng in engines:
+        out = torch.empty_like(q)
+        eng.decode_step(q, k, v, out)
+        assert eng.status() == 0
+        outs.append(out)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16)), "outputs differ after sleep_keep + wake"
+    for layer in range(NL):
+        for x, y in zip(a.layer_cache(layer), b.layer_cache(layer)):
+            if x is None:
+                continue
+            base = 0
+            for g, n in enumerate(lengths):  # rows 0 .. n of every slot (n = the token the step appended)
+                assert torch.equal(x[base:base + n + 1].view(torch.uint8), y[base:base + n + 1].view(torch.uint8))
+                base += caps[g]
+    # a blob moves a sequence into another slot of another engine: sequence 1 of `a` (before the step) into slot 2 of a new one
+    c = tq.Engine(128, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    c.alloc_batch(3, 128)
+    c.import_sequence(2, blob1)
+    assert c.positions().tolist()[2] == lengths[1]
+    assert c.export_sequence(2, lengths[1]) == blob1
+    other = tq.Engine(128, 2 if bits != 2 else 4, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    other.alloc_batch(1, 128)
+    with pytest.raises(tq.TqError) as e:
+        other.import_sequence(0, blob1)
+    assert e.value.status == -4

@@ -46,6 +46,8 @@ def test_static_scratch_variant_matches_regular_entry_point(bits):
         print(f"tq{bits} call {n}: max-abs {worst:.2e}, rel {rel:.2e}, {100 * same:.2f}% of outputs bit-identical")
         ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, pos.astype(np.int32), msl, H, Hkv, D, bits)
         hp.assert_attention_close(got, ref, H, D, f"static scratch vs oracle, call {n}, tq{bits}")
+    # no kernel of the two calls gave up on a wait or refused its shared-memory layout
+    assert L.tq_static_status(torch.cuda.current_stream().cuda_stream) == 0
 
 
 def test_static_scratch_variant_refuses_oversized_requests():

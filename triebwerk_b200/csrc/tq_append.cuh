@@ -48,9 +48,10 @@ struct AppendParams {
     int token_mode;              // 0: one token per sequence (row = row(g)+positions[g]); 1: row = row0+positions[t]
     int max_seq_len;
     int capacity_rows;           // rows a sequence may use (position check); <=0 disables the check
+    const int* seq_capacity;     // batch mode, optional [G]: rows sequence g may use (ragged slots), instead of capacity_rows
     int n_src;                   // G (batch mode) or T (token mode)
     int H, Hkv, q_dim, kv_dim, bits;
-    int pos_value;               // used when positions == nullptr
+    int pos_value;               // used when positions == nullptr (token mode: token t goes to position pos_value + t)
     int qg;                      // > 1: rotated queries are stored for the prefill form of the attention (groups of qg tokens)
 };
 
@@ -203,12 +204,15 @@ __global__ void __launch_bounds__(APPEND_THREADS) append_rotate_kernel(const App
 #pragma unroll
         for (int v = 0; v < NV; ++v) val[v] = kind[v] >= 0 ? __half2float(*src[v]) : 0.0f;
         // thread v of the group also fetches where vector v goes (position and first row of its sequence)
-        int my_pos = p.pos_value;
+        int my_pos = p.pos_value;  // (token mode without a position array: consecutive positions from pos_value, set below)
+        int my_cap = p.capacity_rows;
         long long my_row0 = 0;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
             if (d == v && (kind[v] == 0 || kind[v] == 1)) {
                 if (p.positions) my_pos = p.positions[srcid[v]];
+                else if (p.token_mode) my_pos = p.pos_value + srcid[v];
+                if (p.seq_capacity && !p.token_mode) my_cap = p.seq_capacity[srcid[v]];
                 my_row0 = p.token_mode ? p.token_row0
                                        : (p.row_base ? p.row_base[srcid[v]] : (long long)srcid[v] * p.max_seq_len);
             }
@@ -278,7 +282,7 @@ __global__ void __launch_bounds__(APPEND_THREADS) append_rotate_kernel(const App
         for (int v = 0; v < NV; ++v) {
             if (d == v) {
                 const bool kv = kind[v] == 0 || kind[v] == 1;
-                const bool ok = my_pos >= 0 && (p.capacity_rows <= 0 || my_pos < p.capacity_rows);
+                const bool ok = my_pos >= 0 && (my_cap <= 0 || my_pos < my_cap);
                 long long row = -1;
                 if (kv && ok) {
                     row = my_row0 + my_pos;

@@ -80,6 +80,7 @@ struct AttnParams {
     int rot_copies;            // every worker reads copy (worker % rot_copies): 300 workers fetching the same 32 KB at once queue up in L2
     int kv_dim;
     int capacity_rows;         // rows a sequence may use (position check)
+    const int* seq_capacity;   // optional [G]: rows sequence g may use (ragged slots), instead of capacity_rows
     int app_weight;            // cost of one append in tiles, for the balance of the work list
     int early;                 // 1: positions and this layer's cache tiles may be read before the previous kernel in the
                                // stream has finished (the caller knows it writes neither): table, slice and first copies
@@ -667,7 +668,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             const __half* rot_w = p.rotation + (size_t)(wid % p.rot_copies) * (HEAD_DIM * HEAD_DIM);
             for (int ga = g_app0; ga < G && ts[ga + 1] - 1 < hi_i; ++ga) {
                 const int pos = p.positions ? p.positions[ga] : p.pos_value;
-                const bool ok = pos >= 0 && (p.capacity_rows <= 0 || pos < p.capacity_rows);
+                const int cap = p.seq_capacity ? p.seq_capacity[ga] : p.capacity_rows;
+                const bool ok = pos >= 0 && (cap <= 0 || pos < cap);
                 const long long row = (p.row_base ? p.row_base[ga] : (long long)ga * p.max_seq_len) + pos;
                 // B fragments (R), 16 bytes per lane and load, contraction index permuted as in the query rotation
                 uint4 bq[16 / Hkv][4];

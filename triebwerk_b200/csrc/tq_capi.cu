@@ -91,13 +91,41 @@ int tq_workspace_status(void* workspace, tq_stream_t s) {
     return st;
 }
 
+// ---- self-test of the bounded waits ---------------------------------------------------------------------------------------
+// Every wait on a copy barrier in this library is bounded: after `limit` polls the waiter records
+// ST_TMA_WAIT_TIMEOUT in the status word, stops using the pipeline and lets its kernel finish.  This one-warp kernel
+// exercises exactly that give-up path without any fault: it arms a barrier for 16 bytes that nobody ever sends, waits
+// with a small limit, and reports what mbar_wait_bounded returned.
+__global__ void bounded_wait_probe_kernel(int* status, unsigned limit) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(b, 16u);
+    }
+    __syncthreads();
+    const bool arrived = mbar_wait_bounded(b, 0u, limit);
+    if (!arrived && threadIdx.x == 0) atomicMax(status, ST_TMA_WAIT_TIMEOUT);
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_inval(b);
+}
+
+int tq_selftest_bounded_wait(void* status_word, unsigned limit, tq_stream_t s) {
+    if (!status_word || limit == 0 || limit > (1u << 20)) return TQ_ERR_ARG;
+    bounded_wait_probe_kernel<<<1, 32, 0, cs(s)>>>((int*)status_word, limit);
+    int r = cuda_status(cudaGetLastError());
+    if (r != TQ_OK) return r;
+    return tq_workspace_status(status_word, s);
+}
+
 // ---- packed path ---------------------------------------------------------------------------------------------------------
 static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf, const void* v_buf,
                        const void* q, const void* rotation, const int* positions, int pos_value,
                        const long long* row_base, int token_mode, long long token_row0, int max_seq_len, int n_src,
                        int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, int bits, void* workspace,
                        size_t workspace_bytes, bool build_tiles, cudaStream_t s, bool pdl = false,
-                       const float* rot_prep = nullptr, int qg = 0) {
+                       const float* rot_prep = nullptr, int qg = 0, const int* seq_capacity = nullptr) {
     if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
     if (bits != 2 && bits != 4) return TQ_ERR_ARG;
     if (n_src <= 0 || num_kv_heads <= 0 || kv_dim != num_kv_heads * head_dim || !rotation) return TQ_ERR_ARG;
@@ -125,6 +153,7 @@ static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norm
     p.n_src = n_src; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim; p.bits = bits;
     p.pos_value = pos_value;
     p.qg = qg;
+    p.seq_capacity = seq_capacity;
     return launch_append(p, s, pdl);
 }
 
@@ -146,6 +175,7 @@ struct FusedInputs {
     const void* rotation;
     int rot_copies;
     int early;
+    const int* seq_capacity;  // ragged slots: per-sequence row limits (device), or null
 };
 
 static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& tmV, const void* ck_q, const void* cv_q,
@@ -190,6 +220,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
         static const int app_weight = getenv("TQ_FUSED_WEIGHT") ? atoi(getenv("TQ_FUSED_WEIGHT")) : 7;
         p.app_weight = (!fused->k || app_weight < 0) ? 0 : app_weight;  // nothing to weigh without an append
         p.kv_dim = num_kv_heads * HEAD_DIM; p.capacity_rows = max_seq_len;
+        p.seq_capacity = fused->seq_capacity;
     }
     return launch_attention(bits, tmK, tmV, p, attention_ctas(G, max_seq_len), s, pdl, fused != nullptr ? 1 : 0);
 }
@@ -211,10 +242,13 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
     if (r != TQ_OK) return r;
     const int kvp = kv_dim / (bits == 2 ? 4 : 2);
     CUtensorMap tmK, tmV;
-    r = cached_code_map(&tmK, ck_q, total_rows, kvp);
-    if (r != TQ_OK) return r;
-    r = cached_code_map(&tmV, cv_q, total_rows, kvp);
-    if (r != TQ_OK) return r;
+    {
+        std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // the descriptor cache is per-device compat state
+        r = cached_code_map(&tmK, ck_q, total_rows, kvp);
+        if (r != TQ_OK) return r;
+        r = cached_code_map(&tmV, cv_q, total_rows, kvp);
+        if (r != TQ_OK) return r;
+    }
     return attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, pos_value, row_base, total_rows,
                           max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
 }
@@ -255,14 +289,23 @@ int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, co
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r != TQ_OK) return r;
     if (!out || !q || !ck_q || !cv_q || !k_norms || !v_norms || !rotation || !positions) return TQ_ERR_ARG;
+    // everything that can refuse the call is checked before the first kernel is enqueued
+    if ((((uintptr_t)ck_q | (uintptr_t)cv_q | (uintptr_t)k_norms | (uintptr_t)v_norms) & 15u) != 0) return TQ_ERR_ARG;
+    if (num_kv_heads % 8 != 0 && ((max_seq_len & 1) || (total_rows & 1))) return TQ_ERR_UNSUPPORTED;
     const size_t need = carve_full(nullptr, G, num_heads).bytes;
     if (need > TQ_STATIC_SCRATCH_BYTES) return TQ_ERR_CAPACITY;  // batch x heads too large for the built-in scratch
+    const int kvp = kv_dim / (bits == 2 ? 4 : 2);
+    CUtensorMap tmK, tmV;  // encoded on the host stack every call: no cache, nothing allocated
+    r = make_code_map(&tmK, ck_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
+    r = make_code_map(&tmV, cv_q, total_rows, kvp);
+    if (r != TQ_OK) return r;
     void* ws = nullptr;
     r = static_scratch_ptr(&ws);  // first call on a device: symbol lookup (do it before capturing a graph)
     if (r != TQ_OK) return r;
-    // The array keeps whatever the previous call left.  What has to start from zero: the status word (header) here,
-    // the per-sequence tickets in the rotate kernel below; everything else is written before it is read.
-    TQ_CUDA(cudaMemsetAsync(ws, 0, 256, cs(s)));
+    // The array keeps whatever the previous call left.  What has to start from zero: the per-sequence tickets, cleared by
+    // the rotate kernel below; everything else is written before it is read.  The status word at the start of the array
+    // is NOT cleared here: it collects (atomicMax) until tq_static_status reads and clears it.
     FullWorkspace fw = carve_full(ws, G, num_heads);
     transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(fw.rot_t, (const __half*)rotation);
     r = cuda_status(cudaGetLastError());
@@ -270,14 +313,15 @@ int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, co
     r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, q, rotation, positions, 0, nullptr, 0, 0,
                     max_seq_len, G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, ws, need, true, cs(s));
     if (r != TQ_OK) return r;
-    const int kvp = kv_dim / (bits == 2 ? 4 : 2);
-    CUtensorMap tmK, tmV;  // encoded on the host stack every call: no cache, nothing allocated
-    r = make_code_map(&tmK, ck_q, total_rows, kvp);
-    if (r != TQ_OK) return r;
-    r = make_code_map(&tmV, cv_q, total_rows, kvp);
-    if (r != TQ_OK) return r;
     return attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, -1, nullptr, total_rows,
                           max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, ws, need, cs(s));
+}
+
+int tq_static_status(tq_stream_t s) {
+    void* ws = nullptr;
+    int r = static_scratch_ptr(&ws);
+    if (r != TQ_OK) return r;
+    return tq_workspace_status(ws, s);  // reads the word, clears it if it was set; synchronises the stream
 }
 
 // ---- fp16 twin ---------------------------------------------------------------------------------------------------------
@@ -325,6 +369,7 @@ static size_t fp16_workspace_bytes(int G, int H, int Hkv, int max_seq_len) {
 void launch_turbo_kv_quantize(uint8_t* cache_q, void* cache_norms, const void* kv_buf, const void* rotation,
                               const int* positions, int max_seq_len, int num_tokens, int num_kv_heads, int head_dim,
                               int kv_dim, int bits, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     void* ws = nullptr;
     const size_t need = carve_full(nullptr, num_tokens > 0 ? num_tokens : 1, 1).bytes;
     int r = compat_workspace(need, &ws, cs(s));
@@ -338,6 +383,7 @@ void launch_turbo_kv_quantize(uint8_t* cache_q, void* cache_norms, const void* k
 void launch_turbo_kv_quantize_batch(uint8_t* cache_q, void* cache_norms, const void* kv_buf, const void* rotation,
                                     const int* positions, int max_seq_len, int G, int num_kv_heads, int head_dim,
                                     int kv_dim, int bits, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     void* ws = nullptr;
     const size_t need = carve_full(nullptr, G > 0 ? G : 1, 1).bytes;
     int r = compat_workspace(need, &ws, cs(s));
@@ -352,6 +398,7 @@ void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* c
                                       const void* k_norms, const void* v_norms, const void* rotation, float* as,
                                       const int* pos, int msl, int G, int num_heads, int num_kv_heads, int head_dim,
                                       int q_dim, int kv_dim, int bits, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     (void)as;
     bits = bits == 4 ? 4 : 2;  // the reference treats anything that is not 4 as 2-bit
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
@@ -377,7 +424,7 @@ void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* c
             r = cuda_status(cudaGetLastError());
         }
         if (r == TQ_OK) {
-            FusedInputs in{q, nullptr, nullptr, rotation, 1, 0};
+            FusedInputs in{q, nullptr, nullptr, rotation, 1, 0, nullptr};
             r = attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, pos, -1, nullptr, (long long)G * msl, msl, G,
                                num_heads, num_kv_heads, q_dim, bits, ws, need, cs(s), false, &in);
         }
@@ -396,6 +443,7 @@ void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* c
 void launch_turbo_gqa_attention(const void* q, const uint8_t* ck_q, const uint8_t* cv_q, const void* k_norms,
                                 const void* v_norms, const void* rotation, void* output, float* as, int pos, int msl,
                                 int num_heads, int num_kv_heads, int head_dim, int bits, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     (void)as;
     bits = bits == 4 ? 4 : 2;
     const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
@@ -420,6 +468,7 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
                                         const void* k_norms, const void* v_norms, const void* rotation, float* as,
                                         int T, int msl, int num_heads, int num_kv_heads, int head_dim, int q_dim,
                                         int kv_dim, int bits, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     (void)as;
     // Query t attends to rows 0..t of ONE sequence.  The decode kernel serves up to 8 score rows per KV head at the
     // price of one: groups of qg = 8 / (heads per KV head) consecutive query tokens become the "sequences" of the launch,
@@ -480,6 +529,7 @@ void launch_kv_cache_write_batch(void* ck, void* cv, const void* k, const void* 
 void launch_gqa_attention_batch(void* out, const void* q, const void* ck, const void* cv, float* as, const int* pos,
                                 int msl, int G, int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim,
                                 tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     (void)as;
     void* ws = nullptr;
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
@@ -496,6 +546,7 @@ void launch_gqa_attention_batch(void* out, const void* q, const void* ck, const 
 
 void launch_gqa_attention(const void* q, const void* k_cache, const void* v_cache, void* output, float* attn_scratch,
                           int pos, int max_seq_len, int num_heads, int num_kv_heads, int head_dim, tq_stream_t stream) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
     (void)attn_scratch;
     const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
     void* ws = nullptr;
@@ -617,6 +668,12 @@ int tq_engine_set_fused(tq_engine* e, int on) {
     return prev;
 }
 
+// An engine belongs to the device that was current when it was created; every call that launches work checks it.
+static bool engine_on_its_device(const tq_engine* e) {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess && dev == e->device;
+}
+
 // One walk of the arena; with base == nullptr it only measures.
 static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long rows, bool ragged, bool assign) {
     size_t off = 0;
@@ -688,10 +745,13 @@ int tq_engine_set_arena(tq_engine* e, void* device_ptr, size_t bytes) {
     return TQ_OK;
 }
 
+static int engine_restore_kept(tq_engine* e);
+
 int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capacities) {
     if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || G <= 0 || max_seq_len <= 0) return TQ_ERR_ARG;
     if (e->asleep) return TQ_ERR_STATE;
+    if (!engine_on_its_device(e)) return TQ_ERR_STATE;
     int r = check_shape(G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim, e->q_dim(), e->kv_dim(),
                         e->kv_bits, e->kv_bits != 0);
     if (r != TQ_OK) return r;
@@ -761,7 +821,7 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
         r = make_code_map_layers(&e->tmV4, e->layers[0].v, rows, kvp, NL, e->code_layer_stride);
         if (r != TQ_OK) return r;
     }
-    return TQ_OK;
+    return e->kept.valid ? engine_restore_kept(e) : TQ_OK;
 }
 
 int tq_engine_reset(tq_engine* e, int zero_cache, tq_stream_t s) {
@@ -787,6 +847,7 @@ int tq_engine_sleep(tq_engine* e) {
     if (!e) return TQ_ERR_ARG;
     TQ_CUDA(cudaDeviceSynchronize());
     engine_release_arena(e);
+    e->kept = tq_engine::Kept();
     e->asleep = true;
     return TQ_OK;
 }
@@ -795,7 +856,130 @@ int tq_engine_wake(tq_engine* e) {
     if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e) return TQ_ERR_ARG;
     e->asleep = false;  // the arena comes back lazily with the next tq_engine_alloc_batch, as in the reference
+    if (e->kept.valid && !e->arena) {
+        // sequences were kept (tq_engine_sleep_keep) and no caller-owned arena is pending: re-create the batch now
+        const tq_engine::Kept& k = e->kept;
+        std::vector<int> caps = k.capacities;
+        return tq_engine_alloc_batch(e, k.G, k.max_seq_len, k.ragged ? caps.data() : nullptr);
+    }
     return TQ_OK;
+}
+
+// ---- cache persistence: a sequence's rows as a self-describing blob -----------------------------------------------------------
+// Blob = header (8 x int32: magic, version, kv_bits, layers, kv heads, head_dim, tokens, 0), then per layer the rows
+// 0 .. tokens-1 of the four arrays in the on-cache byte layout: K codes [tokens][kvp], V codes, K norms [tokens][Hkv]
+// fp16, V norms (packed modes) or K rows [tokens][kv_dim] fp16, V rows (kv_bits = 0).  The same bytes the attention
+// kernels read, so a blob can go to disk, to another engine or to another slot and back without re-quantising anything.
+constexpr int TQ_BLOB_MAGIC = 0x564b5154;  // "TQKV"
+constexpr int TQ_BLOB_VERSION = 1;
+constexpr size_t TQ_BLOB_HEADER = 8 * sizeof(int);
+
+size_t tq_engine_sequence_blob_bytes(const tq_engine* e, int n_tokens) {
+    if (!e || n_tokens < 0) return 0;
+    const size_t per_token = 2 * e->code_row_bytes() + (e->kv_bits ? 2 * (size_t)e->shape.num_kv_heads * 2 : 0);
+    return TQ_BLOB_HEADER + (size_t)e->shape.num_layers * per_token * (size_t)n_tokens;
+}
+
+static long long engine_seq_row0(const tq_engine* e, int seq) {
+    return e->ragged ? e->h_row_base[seq] : (long long)seq * e->msl;
+}
+
+int tq_engine_export_sequence(tq_engine* e, int seq, int n_tokens, void* host_blob, size_t blob_bytes, tq_stream_t s) {
+    if (!e || !host_blob || seq < 0 || n_tokens < 0) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || seq >= e->G || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (n_tokens > (e->ragged ? e->capacities[seq] : e->msl)) return TQ_ERR_CAPACITY;
+    if (blob_bytes < tq_engine_sequence_blob_bytes(e, n_tokens)) return TQ_ERR_CAPACITY;
+    int* hdr = (int*)host_blob;
+    hdr[0] = TQ_BLOB_MAGIC; hdr[1] = TQ_BLOB_VERSION; hdr[2] = e->kv_bits; hdr[3] = e->shape.num_layers;
+    hdr[4] = e->shape.num_kv_heads; hdr[5] = e->shape.head_dim; hdr[6] = n_tokens; hdr[7] = 0;
+    char* dst = (char*)host_blob + TQ_BLOB_HEADER;
+    const size_t crow = e->code_row_bytes(), nrow = (size_t)e->shape.num_kv_heads * 2;
+    const long long row0 = engine_seq_row0(e, seq);
+    for (const auto& L : e->layers) {
+        const void* arrays[4] = {L.k, L.v, L.kn, L.vn};
+        const size_t pitch[4] = {crow, crow, nrow, nrow};
+        for (int a = 0; a < (e->kv_bits ? 4 : 2); ++a) {
+            const size_t bytes = pitch[a] * (size_t)n_tokens;
+            if (bytes) TQ_CUDA(cudaMemcpyAsync(dst, (const char*)arrays[a] + (size_t)row0 * pitch[a], bytes, cudaMemcpyDeviceToHost, cs(s)));
+            dst += bytes;
+        }
+    }
+    return cuda_status(cudaStreamSynchronize(cs(s)));
+}
+
+int tq_engine_import_sequence(tq_engine* e, int seq, const void* host_blob, size_t blob_bytes, tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
+    if (!e || !host_blob || seq < 0 || blob_bytes < TQ_BLOB_HEADER) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || seq >= e->G || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    const int* hdr = (const int*)host_blob;
+    if (hdr[0] != TQ_BLOB_MAGIC || hdr[1] != TQ_BLOB_VERSION) return TQ_ERR_ARG;
+    if (hdr[2] != e->kv_bits || hdr[3] != e->shape.num_layers || hdr[4] != e->shape.num_kv_heads || hdr[5] != e->shape.head_dim)
+        return TQ_ERR_UNSUPPORTED;  // written by an engine of another shape or cache mode
+    const int n_tokens = hdr[6];
+    if (n_tokens < 0 || n_tokens > (e->ragged ? e->capacities[seq] : e->msl)) return TQ_ERR_CAPACITY;
+    if (blob_bytes < tq_engine_sequence_blob_bytes(e, n_tokens)) return TQ_ERR_ARG;
+    const char* src = (const char*)host_blob + TQ_BLOB_HEADER;
+    const size_t crow = e->code_row_bytes(), nrow = (size_t)e->shape.num_kv_heads * 2;
+    const long long row0 = engine_seq_row0(e, seq);
+    for (const auto& L : e->layers) {
+        void* arrays[4] = {L.k, L.v, L.kn, L.vn};
+        const size_t pitch[4] = {crow, crow, nrow, nrow};
+        for (int a = 0; a < (e->kv_bits ? 4 : 2); ++a) {
+            const size_t bytes = pitch[a] * (size_t)n_tokens;
+            if (bytes) TQ_CUDA(cudaMemcpyAsync((char*)arrays[a] + (size_t)row0 * pitch[a], src, bytes, cudaMemcpyHostToDevice, cs(s)));
+            src += bytes;
+        }
+    }
+    // the sequence continues where the blob ends: its next token goes to position n_tokens
+    TQ_CUDA(cudaMemcpyAsync(e->d_positions + seq, &hdr[6], sizeof(int), cudaMemcpyHostToDevice, cs(s)));
+    return cuda_status(cudaStreamSynchronize(cs(s)));
+}
+
+// sleep() that keeps the sequences: their written rows (0 .. position-1) go to host memory, the arena is released as
+// tq_engine_sleep does; tq_engine_wake (internal arena) or the next tq_engine_alloc_batch of the same batch shape
+// (external arena: after tq_engine_set_arena) brings rows and positions back.  Decoding then continues without
+// re-running the prompts.
+int tq_engine_sleep_keep(tq_engine* e) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
+    if (!e) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    TQ_CUDA(cudaDeviceSynchronize());
+    tq_engine::Kept k;
+    k.G = e->G; k.ragged = e->ragged; k.capacities = e->capacities;
+    k.positions.resize(e->G);
+    TQ_CUDA(cudaMemcpy(k.positions.data(), e->d_positions, (size_t)e->G * sizeof(int), cudaMemcpyDeviceToHost));
+    k.blobs.resize(e->G);
+    for (int g = 0; g < e->G; ++g) {
+        const int cap = e->ragged ? e->capacities[g] : e->msl;
+        const int n = std::max(0, std::min(k.positions[g], cap));
+        k.blobs[g].resize(tq_engine_sequence_blob_bytes(e, n));
+        int r = tq_engine_export_sequence(e, g, n, k.blobs[g].data(), k.blobs[g].size(), nullptr);
+        if (r != TQ_OK) return r;
+    }
+    k.max_seq_len = e->msl;  // (ragged: the largest capacity; the carving comes out the same)
+    k.valid = true;
+    engine_release_arena(e);
+    e->kept = std::move(k);
+    e->asleep = true;
+    return TQ_OK;
+}
+
+// Called at the end of tq_engine_alloc_batch: a batch of the shape that went to sleep gets its sequences back.
+static int engine_restore_kept(tq_engine* e) {
+    tq_engine::Kept k = std::move(e->kept);
+    e->kept = tq_engine::Kept();
+    if (!k.valid || k.G != e->G || k.ragged != e->ragged) return TQ_OK;  // another batch: the kept sequences are dropped
+    for (int g = 0; g < e->G; ++g) {
+        const int cap = e->ragged ? e->capacities[g] : e->msl;
+        const int n = ((const int*)k.blobs[g].data())[6];
+        if (n > cap) return TQ_OK;  // does not fit the new slots: dropped
+    }
+    for (int g = 0; g < e->G; ++g) {
+        int r = tq_engine_import_sequence(e, g, k.blobs[g].data(), k.blobs[g].size(), nullptr);
+        if (r != TQ_OK) return r;
+    }
+    // positions as they were (import sets position = tokens, which is the same unless a position was out of range)
+    return cuda_status(cudaMemcpy(e->d_positions, k.positions.data(), (size_t)e->G * sizeof(int), cudaMemcpyHostToDevice));
 }
 
 int tq_engine_status(tq_engine* e, tq_stream_t s) {
@@ -883,7 +1067,7 @@ int tq_engine_read_output_f32(tq_engine* e, float* host_out, int first_layer, in
 int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k, const void* v, void* out,
                            tq_stream_t s) {
     if (!e || layer < 0 || layer >= e->shape.num_layers || !q || !k || !v || !out) return TQ_ERR_ARG;
-    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
     const bool chained = e->chain_ok;  // whatever happens below, the chain of fused launches starts afresh unless it continues
     e->chain_ok = false;
     const tq_engine::Layer& L = e->layers[layer];
@@ -892,7 +1076,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     if (e->kv_bits == 0) {
         fp16_cache_write_kernel<<<e->G, 128, 0, cs(s)>>>((__half*)L.k, (__half*)L.v, (const __half*)k, (const __half*)v,
                                                          e->d_positions, e->d_row_base, e->msl, e->msl, e->G,
-                                                         e->kv_dim(), (int*)e->workspace);
+                                                         e->kv_dim(), (int*)e->workspace, e->d_capacities);
         int r = cuda_status(cudaGetLastError());
         if (r != TQ_OK) return r;
         return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->d_row_base, e->total_rows, e->msl, e->G,
@@ -906,7 +1090,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(cs(s), &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
         const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s) && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
-        FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early};
+        FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early, e->d_capacities};
         const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
                                      e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
                                      cs(s), use_pdl(), &in, 0, 0, f32);
@@ -916,7 +1100,7 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
                         e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
-                        e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep);
+                        e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep, 0, e->d_capacities);
     if (r != TQ_OK) return r;
     return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
                           e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl(), nullptr, 0, 0, f32);
@@ -1024,7 +1208,7 @@ int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const v
                             tq_stream_t s) {
     if (!e || !q || !k || !v || !out || first_layer < 0 || n_layers <= 0 || first_layer + n_layers > e->shape.num_layers)
         return TQ_ERR_ARG;
-    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
     if (engine_whole_step_ok(e, q, k, v, out)) return engine_step_layers(e, first_layer, n_layers, q, k, v, out, cs(s));
     const size_t qb = (size_t)e->G * e->q_dim() * 2, kb = (size_t)e->G * e->kv_dim() * 2;
     for (int i = 0; i < n_layers; ++i) {
@@ -1040,18 +1224,13 @@ int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void
     return tq_engine_decode_layers(e, 0, e->shape.num_layers, q, k, v, out, s);
 }
 
-__global__ void iota_from_kernel(int* pos, int n, int first) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) pos[i] = first + i;
-}
-
 // Prompts of n_seq consecutive sequences (first_seq ..), all T tokens long and all at positions first_pos ..; inputs
 // [n_seq][T][kv_dim].  One launch.
 static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v, int first_pos,
                                int T, tq_stream_t s) {
     if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0 || n_seq <= 0) return TQ_ERR_ARG;
-    if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
     if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;
     int cap = e->msl;
     if (e->ragged) {
@@ -1071,18 +1250,7 @@ static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq
         }
         return TQ_OK;
     }
-    // token form: positions are first_pos + t; pass them by value through a per-token iota kept in a scratch
-    // allocation sized on demand (outside the arena so that prompt length is not bounded by the batch size).
-    static thread_local int* d_iota = nullptr;
-    static thread_local int iota_cap = 0;
-    if (iota_cap < T) {
-        if (d_iota) cudaFree(d_iota);
-        TQ_CUDA(cudaMalloc(&d_iota, (size_t)T * sizeof(int)));
-        iota_cap = T;
-    }
-    iota_from_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(d_iota, T, first_pos);
-    int r = cuda_status(cudaGetLastError());
-    if (r != TQ_OK) return r;
+    // token form: token t goes to position first_pos + t (by value: no position array)
     const long long row0 = e->ragged ? e->h_row_base[first_seq] : (long long)first_seq * e->msl;
     // the append kernel only needs the header of the workspace here (status word)
     AppendParams p{};
@@ -1090,13 +1258,13 @@ static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq
     p.k_buf = (const __half*)k; p.v_buf = (const __half*)v; p.q = nullptr;
     p.rotation = (const __half*)e->d_rotation;
     p.rot_prep = e->d_rotation_prep;
-    p.positions = d_iota; p.row_base = nullptr; p.q_rot = nullptr;
+    p.positions = nullptr; p.row_base = nullptr; p.q_rot = nullptr;
     p.tile_start = nullptr; p.tickets = nullptr; p.total_tiles = nullptr;
     p.status = (int*)e->workspace;
     p.token_row0 = row0; p.token_mode = 1;
     p.max_seq_len = e->msl; p.capacity_rows = cap;
     p.n_src = T; p.H = e->shape.num_heads; p.Hkv = e->shape.num_kv_heads; p.q_dim = e->q_dim(); p.kv_dim = e->kv_dim();
-    p.bits = e->kv_bits; p.pos_value = 0;
+    p.bits = e->kv_bits; p.pos_value = first_pos;
     if (n_seq == 1) return launch_append(p, cs(s));
     if ((long long)n_seq * T * p.Hkv >= (1ll << 31)) return TQ_ERR_CAPACITY;
     // several sequences: the tensor-core kernel takes them in one launch (whatever their number of head vectors)

@@ -43,10 +43,11 @@ struct Fp16AttnParams {
 
 __global__ void fp16_cache_write_kernel(__half* ck, __half* cv, const __half* k, const __half* v, const int* positions,
                                         const long long* row_base, int max_seq_len, int capacity_rows, int G,
-                                        int kv_dim, int* status) {
+                                        int kv_dim, int* status, const int* seq_capacity = nullptr) {
     const int g = blockIdx.x;
     if (g >= G) return;
     const int pos = positions[g];
+    if (seq_capacity) capacity_rows = seq_capacity[g];  // ragged slots: every sequence has its own limit
     if (pos < 0 || (capacity_rows > 0 && pos >= capacity_rows)) {
         if (threadIdx.x == 0 && status) atomicMax(status, ST_BAD_POSITION);
         return;

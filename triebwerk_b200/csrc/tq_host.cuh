@@ -3,6 +3,7 @@
 // reference keeps inside InferenceEngine (engine/engine.cpp:292-409, 893-1022, 1338-1620).
 #pragma once
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -164,15 +165,25 @@ inline int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cuda
 
 constexpr size_t APPEND_SMEM = (size_t)HEAD_DIM * HEAD_DIM * sizeof(float);  // R as fp32
 
+// Opt-in to large dynamic shared memory, once per (device, kernel); safe to call from several host threads.
+inline int ensure_dynamic_smem(const void* func, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, bool> done;
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    bool& d = done[std::make_pair(dev, func)];
+    if (!d) {
+        TQ_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        d = true;
+    }
+    return TQ_OK;
+}
+
 template <int NV>
 inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, bool pdl) {
-    static std::map<int, bool> attr_set;  // per device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(append_rotate_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)APPEND_SMEM));
-        attr_set[dev] = true;
-    }
+    int r = ensure_dynamic_smem((const void*)append_rotate_kernel<NV>, APPEND_SMEM);
+    if (r != TQ_OK) return r;
     return launch_kernel(append_rotate_kernel<NV>, grid, dim3(APPEND_THREADS), APPEND_SMEM, s, pdl, p);
 }
 
@@ -180,16 +191,11 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
 // the fp32-chain kernel.  Both store the same bytes.
 inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 1, long long seq_stride_rows = 0,
                              const long long* seq_row_base = nullptr) {
-    static std::map<int, bool> attr_set;  // per device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(prefill_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_DYN_SMEM));
-        attr_set[dev] = true;
-    }
+    int ar = ensure_dynamic_smem((const void*)prefill_append_tc_kernel, TC_DYN_SMEM);
+    if (ar != TQ_OK) return ar;
     PrefillTcParams t{};
     t.ck = p.ck; t.kn = p.kn; t.cv = p.cv; t.vn = p.vn;
-    t.k_buf = p.k_buf; t.v_buf = p.v_buf; t.rotation = p.rotation; t.positions = p.positions; t.status = p.status;
+    t.k_buf = p.k_buf; t.v_buf = p.v_buf; t.rotation = p.rotation; t.positions = p.positions; t.pos_value = p.pos_value; t.status = p.status;
     t.token_row0 = p.token_row0; t.capacity_rows = p.capacity_rows;
     t.seq_stride_rows = seq_stride_rows; t.row_base = seq_row_base; t.n_seq = n_seq;
     t.T = p.n_src; t.Hkv = p.Hkv; t.kv_dim = p.kv_dim; t.bits = p.bits;
@@ -201,17 +207,8 @@ inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 
 }
 
 inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s) {
-    static std::mutex mu;
-    static std::map<int, bool> attr_set;  // per device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set[dev]) {
-            TQ_CUDA(cudaFuncSetAttribute(prefill_append_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_DYN_SMEM));
-            attr_set[dev] = true;
-        }
-    }
+    int ar = ensure_dynamic_smem((const void*)prefill_append_tc_kernel, TC_DYN_SMEM);
+    if (ar != TQ_OK) return ar;
     const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
     long long grid = 2ll * device_props().sm_count;
     if (grid > tiles) grid = tiles;
@@ -224,7 +221,7 @@ inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false
     static const bool prefill_tc = !(getenv("TQ_PREFILL_TC") && atoi(getenv("TQ_PREFILL_TC")) == 0);
     // (the tensor-core kernel moves 16 bytes at a time: every array it touches has to be 16-byte aligned)
     const uintptr_t align_or = (uintptr_t)p.k_buf | (uintptr_t)p.v_buf | (uintptr_t)p.ck | (uintptr_t)p.cv | (uintptr_t)p.rotation;
-    if (prefill_tc && p.token_mode && !p.q && (p.k_buf || p.v_buf) && p.positions && (align_or & 15u) == 0 &&
+    if (prefill_tc && p.token_mode && !p.q && (p.k_buf || p.v_buf) && (align_or & 15u) == 0 &&
         p.kv_dim == p.Hkv * HEAD_DIM && (long long)p.n_src * p.Hkv >= 4 * TC_TILE && (long long)p.n_src * p.Hkv < (1ll << 31))
         return launch_prefill_tc(p, s);
     const int nk = p.k_buf ? p.Hkv : 0, nv = p.v_buf ? p.Hkv : 0, nq = p.q ? p.H : 0;
@@ -260,14 +257,8 @@ inline int attention_ctas(int G, int max_seq_len) {
 template <int BITS, int HKV, int MODE>
 inline int launch_attention_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int ctas, cudaStream_t s,
                               bool pdl) {
-    static std::map<int, bool> attr_set;  // per device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_set[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_attention_kernel<BITS, HKV, MODE>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_DYN_SMEM));
-        attr_set[dev] = true;
-    }
+    int ar = ensure_dynamic_smem((const void*)decode_attention_kernel<BITS, HKV, MODE>, ATTN_DYN_SMEM);
+    if (ar != TQ_OK) return ar;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(ATTN_GROUPS * 32 * HKV);
@@ -346,41 +337,56 @@ __global__ void group_rows_kernel(int* pos, long long* rows, int groups, int qg,
 }
 
 // ---- per-device workspace of the compat launchers + descriptor cache ----------------------------------------------------------
+// The reference's launchers get every buffer from their caller; the kernels here need scratch of their own (rotated
+// queries, tile table, split-K partials), which the reference-compatible launchers keep per device.  All of this state
+// is guarded by ONE mutex that a launcher holds from its first look at the state until its kernels are enqueued: the
+// compat launchers serialise per process (their host part is a few microseconds).
 struct CompatState {
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    std::vector<void*> retired;  // outgrown workspaces: kernels already enqueued may still use them, so they stay allocated
     std::map<std::tuple<const void*, long long, int>, CUtensorMap> maps;  // descriptors by (base, rows, row bytes)
 };
 
+inline std::recursive_mutex& compat_mutex() {
+    static std::recursive_mutex mu;
+    return mu;
+}
+
+// Call with compat_mutex() held.
 inline CompatState& compat_state() {
-    static std::mutex mu;
     static std::map<int, CompatState> st;
-    std::lock_guard<std::mutex> lock(mu);
     int dev = 0;
     cudaGetDevice(&dev);
     return st[dev];
 }
 
+// Call with compat_mutex() held.  The workspace only ever grows, and by at least a factor of two (first allocation:
+// 64 MiB or the request), so a serving loop reaches its final size after a few calls; growth allocates a new buffer
+// and retires the old one without waiting for the device.
 inline int compat_workspace(size_t need, void** out, cudaStream_t s) {
     CompatState& c = compat_state();
     if (c.ws_bytes < need) {
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         cudaStreamIsCapturing(s, &cs);
         if (cs != cudaStreamCaptureStatusNone) return TQ_ERR_WORKSPACE;  // cannot allocate while capturing
-        if (c.ws) {
-            cudaDeviceSynchronize();
-            cudaFree(c.ws);
-            c.ws = nullptr;
-            c.ws_bytes = 0;
+        size_t bytes = std::max(need, std::max(c.ws_bytes * 2, (size_t)64 << 20));
+        void* fresh = nullptr;
+        if (cudaMalloc(&fresh, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            bytes = need;
+            TQ_CUDA(cudaMalloc(&fresh, bytes));
         }
-        TQ_CUDA(cudaMalloc(&c.ws, need));
-        TQ_CUDA(cudaMemset(c.ws, 0, need));
-        c.ws_bytes = need;
+        TQ_CUDA(cudaMemsetAsync(fresh, 0, bytes, s));
+        if (c.ws) c.retired.push_back(c.ws);
+        c.ws = fresh;
+        c.ws_bytes = bytes;
     }
     *out = c.ws;
     return TQ_OK;
 }
 
+// Call with compat_mutex() held.
 inline int cached_code_map(CUtensorMap* out, const void* base, long long rows, int kvp) {
     CompatState& c = compat_state();
     auto key = std::make_tuple(base, rows, kvp);
@@ -467,6 +473,15 @@ struct tq_engine {
     void* d_rotation_t = nullptr;
     float* d_rotation_prep = nullptr;  // fp32, in the append kernel's shared-memory order
     void* d_rotation_rep = nullptr;    // R row-major, several copies, for the fused kernel's query rotation
+
+    // sleep that keeps the sequences: every sequence's written rows as a blob in host memory (see tq_engine_export_sequence)
+    struct Kept {
+        bool valid = false;
+        int G = 0, max_seq_len = 0;
+        bool ragged = false;
+        std::vector<int> capacities, positions;
+        std::vector<std::vector<unsigned char>> blobs;
+    } kept;
 
     int q_dim() const { return shape.num_heads * shape.head_dim; }
     int kv_dim() const { return shape.num_kv_heads * shape.head_dim; }

@@ -59,7 +59,8 @@ struct PrefillTcParams {
     const __half* k_buf;       // [T][kv_dim], either may be null
     const __half* v_buf;
     const __half* rotation;    // [128][128] row-major
-    const int* positions;      // [T] device
+    const int* positions;      // [T] device, or null: token t goes to position pos_value + t
+    int pos_value;
     int* status;
     long long token_row0;      // first cache row of sequence 0 of the call
     long long seq_stride_rows; // rows between consecutive sequences of the call (when row_base is null)
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                         sq = seq - layer * p.step_G;
                         if (p.seq_capacity) cap = p.seq_capacity[sq];
                     }
-                    const int pos = p.step_G > 0 ? p.positions[sq] : p.positions[t];
+                    const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
                     if (pos >= 0 && (cap <= 0 || pos < cap)) {
                         row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
                         cn[(size_t)layer * (size_t)p.norm_layer_stride + (size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));

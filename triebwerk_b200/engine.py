@@ -66,6 +66,24 @@ class Engine:
     def wake(self) -> None:
         check(lib().tq_engine_wake(self._h), "wake")
 
+    def sleep_keep(self) -> None:
+        """sleep() that keeps every sequence's written rows and the positions in host memory; wake() (library-owned
+        arena) or the next alloc_batch of the same shape (caller-owned arena) brings them back."""
+        check(lib().tq_engine_sleep_keep(self._h), "sleep_keep")
+        self._arena_ref = None
+
+    def export_sequence(self, seq: int, n_tokens: int) -> bytes:
+        """Rows 0 .. n_tokens-1 of sequence `seq`, all layers, as a self-describing blob in the on-cache byte layout."""
+        n = int(lib().tq_engine_sequence_blob_bytes(self._h, n_tokens))
+        buf = (C.c_ubyte * n)()
+        check(lib().tq_engine_export_sequence(self._h, seq, n_tokens, buf, n, self._stream()), "export_sequence")
+        return bytes(buf)
+
+    def import_sequence(self, seq: int, blob: bytes) -> None:
+        """A blob from export_sequence into slot `seq`; the slot's position becomes the blob's token count."""
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        check(lib().tq_engine_import_sequence(self._h, seq, buf, len(blob), self._stream()), "import_sequence")
+
     def model_config(self) -> dict:
         s = self.shape
         return dict(num_layers=s.num_layers, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim)
