@@ -317,6 +317,17 @@ int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, co
 int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v,
                                    int first_pos, int T, tq_stream_t s);
 
+/* A prompt of T tokens shared by the n_seq sequences first_seq .. (rollouts of one prompt; the reference prefills
+ * sequence 0 and copies its cache to the other sequences, engine/engine.cpp:2173-2214, 2296).  The first
+ * P = 32 * floor(T / 32) tokens are quantised and stored once, in the slot of first_seq; the other sequences read
+ * those tiles from there and their own slots begin at token P (so they may be given smaller capacities); the last
+ * T - P tokens go into every sequence's own rows.  k, v: [T][kv_dim] fp16 on the device.  Call once per layer with the
+ * same T, before anything else is appended to these sequences; packed modes only.  Decode steps, positions and
+ * tq_engine_export_sequence work as for unshared sequences; tq_engine_import_sequence into a sharing slot makes it an
+ * ordinary slot again. */
+int tq_engine_prefill_shared(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v, int T,
+                             tq_stream_t s);
+
 /* A whole decode step from HOST buffers: q_host [layers][G][q_dim], k_host/v_host [layers][G][kv_dim],
  * out_host [layers][G][q_dim], fp16, ideally pinned.  Copies the inputs in, runs every layer, copies the
  * outputs back and waits.  This is the end-to-end call bench.py times. */

@@ -411,3 +411,69 @@ def test_sleep_keep_wake_and_sequence_blobs(bits):
     with pytest.raises(tq.TqError) as e:
         other.import_sequence(0, blob1)
     assert e.value.status == -4
+
+
+@pytest.mark.parametrize("bits,form", [(4, "whole-step"), (4, "one-launch"), (2, "two-launch")])
+def test_shared_prefix_equals_replicated_prompt(bits, form):
+    """Four rollouts of one 100-token prompt (twice: eight sequences): with prefill_shared the prompt's whole tiles are
+    stored once and read by all four; against an engine that holds the prompt four times, the sequences' own rows are
+    byte-equal after every step and the outputs agree to the order of the split-K sums."""
+    H, Hkv, D, NL = 16, 8, 128, 2
+    kv_dim, q_dim = Hkv * D, H * D
+    prompt, steps, G = 100, 40, 8
+    P = prompt // 32 * 32
+    rng = np.random.default_rng(41)
+    shared = tq.Engine(256, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    plain = tq.Engine(256, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    # followers only need rows for their own tokens: the prompt's remainder and the decoded ones
+    caps = [prompt + steps + 1 if g % 4 == 0 else prompt - P + steps + 1 for g in range(G)]
+    shared.alloc_batch(G, 256, caps)
+    plain.alloc_batch(G, 256)
+    assert shared.arena_bytes(G, 256, caps) < plain.arena_bytes(G, 256, [prompt + steps + 1] * G)
+    for eng in (shared, plain):
+        eng.set_fused(form != "two-launch")
+    for layer in range(NL):
+        for g0 in (0, 4):
+            k = gu.dev(rng.standard_normal((prompt, kv_dim), dtype=np.float32).astype(np.float16))
+            v = gu.dev(rng.standard_normal((prompt, kv_dim), dtype=np.float32).astype(np.float16))
+            shared.prefill_shared(layer, g0, 4, k, v)
+            for g in range(g0, g0 + 4):
+                plain.prefill_append(layer, g, k, v, 0)
+    for eng in (shared, plain):
+        eng.set_positions([prompt] * G)
+    with pytest.raises(tq.TqError):
+        shared.prefill_append(0, 1, gu.dev(np.zeros((4, kv_dim), np.float16)), gu.dev(np.zeros((4, kv_dim), np.float16)), 0)
+    worst = 0.0
+    for step in range(steps):
+        q = gu.dev(rng.standard_normal((NL, G, q_dim), dtype=np.float32).astype(np.float16))
+        k = gu.dev(rng.standard_normal((NL, G, kv_dim), dtype=np.float32).astype(np.float16))
+        v = gu.dev(rng.standard_normal((NL, G, kv_dim), dtype=np.float32).astype(np.float16))
+        outs = []
+        for eng in (shared, plain):
+            out = torch.empty_like(q)
+            if form == "one-launch":
+                for layer in range(NL):
+                    eng.decode_layer(layer, q[layer], k[layer], v[layer], out[layer])
+            else:
+                eng.decode_step(q, k, v, out)
+            assert eng.status() == 0
+            eng.advance()
+            outs.append(out.float())
+        worst = max(worst, float((outs[0] - outs[1]).abs().max()))
+    assert worst <= 5e-4, f"shared-prefix outputs differ from the replicated batch by {worst:.2e}"
+    # own rows: sequence g of the shared engine holds tokens P.. (followers) or 0.. (owners) in its slot
+    n_own = prompt + steps
+    for layer in range(NL):
+        base = 0
+        for g in range(G):
+            first = 0 if g % 4 == 0 else P
+            for x, y in zip(shared.layer_cache(layer), plain.layer_cache(layer)):
+                a = x[base:base + n_own - first]
+                b = y[g * 256 + first:g * 256 + n_own]
+                assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), f"layer {layer} sequence {g}: own rows differ"
+            base += (caps[g] + 31) // 32 * 32
+    # a follower exported as a blob carries its whole context, prefix included
+    blob_s = shared.export_sequence(5, n_own)
+    blob_p = plain.export_sequence(5, n_own)
+    assert blob_s == blob_p
+    print(f"shared prefix ({form}, {bits}-bit): largest output difference {worst:.2e}")

@@ -26,7 +26,7 @@ SYMBOLS = [
     "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append", "tq_engine_prefill_append_batch",
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
     "tq_engine_output_f32", "tq_engine_read_output_f32", "tq_engine_decode_layers", "tq_static_status", "tq_selftest_bounded_wait",
-    "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep",
+    "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep", "tq_engine_prefill_shared",
 ]
 
 
@@ -100,6 +100,7 @@ def lib() -> C.CDLL:
     sig("tq_engine_status", i, [vp, vp])
     sig("tq_engine_attend_step", i, [vp, vp, vp])
     sig("tq_static_status", i, [vp])
+    sig("tq_engine_prefill_shared", i, [vp, i, i, i, vp, vp, i, vp])
     sig("tq_engine_sequence_blob_bytes", sz, [vp, i])
     sig("tq_engine_export_sequence", i, [vp, i, i, vp, sz, vp])
     sig("tq_engine_import_sequence", i, [vp, i, vp, sz, vp])

@@ -63,6 +63,11 @@ struct AttnParams {
     float* out_f32;            // optional [G][H][128]: the same results before the rounding to fp16 (error reports), or null
     const int* positions;      // device [G] or null
     const long long* row_base;
+    // Shared prefixes (optional, both null otherwise): the first prefix_tiles[g] tiles of sequence g are read from the rows
+    // prefix_base[g] + 32 * tile (another sequence's slot, which holds the common prompt once); every later tile j from
+    // row_base[g] + 32 * j as usual -- row_base[g] then already has the prefix length subtracted.
+    const long long* prefix_base;
+    const int* prefix_tiles;
     const int* tile_start;     // [G+1]
     const int* worker_g;       // first sequence of each worker's slice, or null (then it is searched for)
     int* tickets;              // [G]
@@ -550,7 +555,13 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     int cl_tile = lo_i;                         // next tile to load into shared memory
     int cl_g = g;
     int cl_gend = ts[g + 1];
-    const int row_lo = (int)(p.row_base ? p.row_base[g] : (long long)g * p.max_seq_len) + (lo_i - ts[g]) * TILE_TOKENS;
+    // first cache row of tile j of sequence gq (j counted from the sequence's first tile)
+    auto tile_row = [&](int gq, int j) -> int {
+        if (p.prefix_tiles && j < p.prefix_tiles[gq]) return (int)p.prefix_base[gq] + j * TILE_TOKENS;
+        return (int)(p.row_base ? p.row_base[gq] : (long long)gq * p.max_seq_len) + j * TILE_TOKENS;
+    };
+    const int row_lo = tile_row(g, lo_i - ts[g]);
+    int cl_switch = p.prefix_tiles ? ts[g] + p.prefix_tiles[g] : -1;  // flat index of the current sequence's first private tile
     int cl_row = row_lo;
     int cl_layer = 0;                           // whole-step form: layer (relative to layer0) the cursor is in
     const int g_lo = g;
@@ -564,10 +575,14 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             cl_g = g_lo;
             cl_gend = ts[g_lo + 1];
             cl_row = row_lo;
+            if (p.prefix_tiles) cl_switch = ts[g_lo] + p.prefix_tiles[g_lo];
         } else if (cl_tile == cl_gend && cl_tile < hi_i) {
             ++cl_g;
             cl_gend = ts[cl_g + 1];
-            cl_row = (int)(p.row_base ? p.row_base[cl_g] : (long long)cl_g * p.max_seq_len);
+            cl_row = tile_row(cl_g, 0);
+            if (p.prefix_tiles) cl_switch = cl_tile + p.prefix_tiles[cl_g];
+        } else if (cl_tile == cl_switch) {  // from the shared prefix into the sequence's own rows
+            cl_row = tile_row(cl_g, cl_tile - ts[cl_g]);
         }
     };
     auto cursor_more = [&]() -> bool { return PERSIST ? cl_layer < n_layers : cl_tile < hi_i; };

@@ -183,7 +183,8 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
                           const void* rotation_t, const int* positions, int pos_value, const long long* row_base,
                           long long total_rows, int max_seq_len, int G, int num_heads, int num_kv_heads, int q_dim,
                           int bits, void* workspace, size_t workspace_bytes, cudaStream_t s, bool pdl = false,
-                          const FusedInputs* fused = nullptr, int qg = 0, int qg_tokens = 0, float* out_f32 = nullptr) {
+                          const FusedInputs* fused = nullptr, int qg = 0, int qg_tokens = 0, float* out_f32 = nullptr,
+                          const long long* prefix_base = nullptr, const int* prefix_tiles = nullptr) {
     FullWorkspace fw = carve_full(workspace, G, num_heads);
     if (fw.bytes > workspace_bytes) return TQ_ERR_WORKSPACE;
     // bulk copies need 16-byte aligned sources: rows are 512/256 B (codes) and 2*Hkv B (norms, Hkv % 4 == 0 -> 8|16 B)
@@ -195,6 +196,7 @@ static int attention_impl(void* out, const CUtensorMap& tmK, const CUtensorMap& 
     p.kn = (const __half*)k_norms; p.vn = (const __half*)v_norms;
     p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)rotation_t; p.out = (__half*)out; p.out_f32 = out_f32;
     p.positions = positions; p.row_base = row_base;
+    p.prefix_base = prefix_base; p.prefix_tiles = prefix_tiles;
     p.tile_start = fw.w.tile_start; p.worker_g = fw.w.worker_g; p.tickets = fw.w.tickets; p.partials = fw.w.partials;
     p.status = fw.w.status;
     p.total_rows = total_rows;
@@ -630,6 +632,9 @@ static void engine_release_arena(tq_engine* e) {
     e->d_positions = nullptr;
     e->d_capacities = nullptr;
     e->d_row_base = nullptr;
+    e->d_prefix_base = nullptr;
+    e->d_prefix_tiles = nullptr;
+    e->shared_active = false;
     e->step_partials = nullptr;
     e->step_table = nullptr;
     e->step_qrot = nullptr;
@@ -698,6 +703,8 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
     size_t opos = bump(off, (size_t)G * sizeof(int));
     size_t ocap = bump(off, (size_t)G * sizeof(int));
     size_t orb = bump(off, (size_t)G * sizeof(long long));
+    size_t opb = bump(off, (size_t)G * sizeof(long long));
+    size_t opt = bump(off, (size_t)G * sizeof(int));
     // whole-step form (packed modes): per-layer split-K partials and the tile table handed to the merge kernel
     const size_t part_stride = e->kv_bits ? (size_t)(attention_ctas(G, msl) * ATTN_GROUPS + G) * e->shape.num_heads * PART_STRIDE : 0;
     size_t osp = bump(off, part_stride * e->shape.num_layers * sizeof(float));
@@ -711,8 +718,10 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
     size_t oq = bump(off, qb), okk = bump(off, kb), ovv = bump(off, kb), oo = bump(off, qb);
     if (assign) {
         e->d_positions = (int*)(base + opos);
-        e->d_capacities = ragged ? (int*)(base + ocap) : nullptr;
-        e->d_row_base = ragged ? (long long*)(base + orb) : nullptr;
+        e->d_capacities = (int*)(base + ocap);
+        e->d_row_base = (long long*)(base + orb);
+        e->d_prefix_base = (long long*)(base + opb);
+        e->d_prefix_tiles = (int*)(base + opt);
         e->step_partials = e->kv_bits ? (float*)(base + osp) : nullptr;
         e->step_part_stride = part_stride;
         e->step_table = (int*)(base + ost);
@@ -763,8 +772,7 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
     long long rows = plan_rows(G, max_seq_len, capacities, &caps, &bases);
     if (rows >= (1ll << 31)) return TQ_ERR_CAPACITY;
     int msl = max_seq_len;
-    if (ragged)
-        for (int c : caps) msl = c > msl ? c : msl;
+    for (int c : caps) msl = c > msl ? c : msl;
     size_t need = engine_carve(e, nullptr, G, msl, rows, ragged, false);
     if (need > e->arena_cap) {
         if (e->arena_external) return TQ_ERR_CAPACITY;  // never free or replace caller-owned memory
@@ -796,10 +804,13 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
     engine_carve(e, e->arena, G, msl, rows, ragged, true);
     TQ_CUDA(cudaMemset(e->d_positions, 0, (size_t)G * sizeof(int)));
     TQ_CUDA(cudaMemset(e->workspace, 0, e->ws_bytes));
-    if (ragged) {
-        TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
-        TQ_CUDA(cudaMemcpy(e->d_capacities, caps.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice));
-    }
+    e->prefix_tokens.assign(G, 0);
+    e->prefix_owner.assign(G, -1);
+    e->shared_active = false;
+    TQ_CUDA(cudaMemcpy(e->d_row_base, bases.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice));
+    TQ_CUDA(cudaMemcpy(e->d_capacities, caps.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice));
+    TQ_CUDA(cudaMemset(e->d_prefix_base, 0, (size_t)G * sizeof(long long)));
+    TQ_CUDA(cudaMemset(e->d_prefix_tiles, 0, (size_t)G * sizeof(int)));
     if (!e->d_rotation) {
         int ur = engine_upload_rotation(e, nullptr);
         if (ur != TQ_OK) return ur;
@@ -880,28 +891,28 @@ size_t tq_engine_sequence_blob_bytes(const tq_engine* e, int n_tokens) {
     return TQ_BLOB_HEADER + (size_t)e->shape.num_layers * per_token * (size_t)n_tokens;
 }
 
-static long long engine_seq_row0(const tq_engine* e, int seq) {
-    return e->ragged ? e->h_row_base[seq] : (long long)seq * e->msl;
-}
 
 int tq_engine_export_sequence(tq_engine* e, int seq, int n_tokens, void* host_blob, size_t blob_bytes, tq_stream_t s) {
     if (!e || !host_blob || seq < 0 || n_tokens < 0) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || seq >= e->G || !engine_on_its_device(e)) return TQ_ERR_STATE;
-    if (n_tokens > (e->ragged ? e->capacities[seq] : e->msl)) return TQ_ERR_CAPACITY;
+    if (n_tokens > e->cap_eff(seq)) return TQ_ERR_CAPACITY;
     if (blob_bytes < tq_engine_sequence_blob_bytes(e, n_tokens)) return TQ_ERR_CAPACITY;
     int* hdr = (int*)host_blob;
     hdr[0] = TQ_BLOB_MAGIC; hdr[1] = TQ_BLOB_VERSION; hdr[2] = e->kv_bits; hdr[3] = e->shape.num_layers;
     hdr[4] = e->shape.num_kv_heads; hdr[5] = e->shape.head_dim; hdr[6] = n_tokens; hdr[7] = 0;
     char* dst = (char*)host_blob + TQ_BLOB_HEADER;
     const size_t crow = e->code_row_bytes(), nrow = (size_t)e->shape.num_kv_heads * 2;
-    const long long row0 = engine_seq_row0(e, seq);
+    // tokens below the shared prefix length come from the owner's slot, the rest from the sequence's own
+    const int shared = std::min(n_tokens, e->prefix_tokens[seq]);
+    const long long row_shared = shared ? e->h_row_base[e->prefix_owner[seq]] : 0, row_own = e->h_row_base[seq];
     for (const auto& L : e->layers) {
         const void* arrays[4] = {L.k, L.v, L.kn, L.vn};
         const size_t pitch[4] = {crow, crow, nrow, nrow};
         for (int a = 0; a < (e->kv_bits ? 4 : 2); ++a) {
-            const size_t bytes = pitch[a] * (size_t)n_tokens;
-            if (bytes) TQ_CUDA(cudaMemcpyAsync(dst, (const char*)arrays[a] + (size_t)row0 * pitch[a], bytes, cudaMemcpyDeviceToHost, cs(s)));
-            dst += bytes;
+            const size_t b0 = pitch[a] * (size_t)shared, b1 = pitch[a] * (size_t)(n_tokens - shared);
+            if (b0) TQ_CUDA(cudaMemcpyAsync(dst, (const char*)arrays[a] + (size_t)row_shared * pitch[a], b0, cudaMemcpyDeviceToHost, cs(s)));
+            if (b1) TQ_CUDA(cudaMemcpyAsync(dst + b0, (const char*)arrays[a] + (size_t)row_own * pitch[a], b1, cudaMemcpyDeviceToHost, cs(s)));
+            dst += b0 + b1;
         }
     }
     return cuda_status(cudaStreamSynchronize(cs(s)));
@@ -916,11 +927,23 @@ int tq_engine_import_sequence(tq_engine* e, int seq, const void* host_blob, size
     if (hdr[2] != e->kv_bits || hdr[3] != e->shape.num_layers || hdr[4] != e->shape.num_kv_heads || hdr[5] != e->shape.head_dim)
         return TQ_ERR_UNSUPPORTED;  // written by an engine of another shape or cache mode
     const int n_tokens = hdr[6];
-    if (n_tokens < 0 || n_tokens > (e->ragged ? e->capacities[seq] : e->msl)) return TQ_ERR_CAPACITY;
+    if (n_tokens < 0 || n_tokens > e->capacities[seq]) return TQ_ERR_CAPACITY;
     if (blob_bytes < tq_engine_sequence_blob_bytes(e, n_tokens)) return TQ_ERR_ARG;
+    for (int g = 0; g < e->G; ++g)
+        if (e->prefix_tokens[g] > 0 && e->prefix_owner[g] == seq) return TQ_ERR_STATE;  // other sequences read this slot's prompt
+    if (e->prefix_tokens[seq] > 0) {  // the imported rows are the slot's own from token 0 on: it stops sharing
+        e->prefix_tokens[seq] = 0;
+        e->prefix_owner[seq] = -1;
+        const long long rb0 = e->h_row_base[seq];
+        const int cap0 = e->capacities[seq], zero = 0;
+        TQ_CUDA(cudaMemcpyAsync(e->d_row_base + seq, &rb0, sizeof(rb0), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync(e->d_capacities + seq, &cap0, sizeof(cap0), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync(e->d_prefix_tiles + seq, &zero, sizeof(zero), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaStreamSynchronize(cs(s)));  // the sources are locals of this frame
+    }
     const char* src = (const char*)host_blob + TQ_BLOB_HEADER;
     const size_t crow = e->code_row_bytes(), nrow = (size_t)e->shape.num_kv_heads * 2;
-    const long long row0 = engine_seq_row0(e, seq);
+    const long long row0 = e->h_row_base[seq];
     for (const auto& L : e->layers) {
         void* arrays[4] = {L.k, L.v, L.kn, L.vn};
         const size_t pitch[4] = {crow, crow, nrow, nrow};
@@ -950,8 +973,7 @@ int tq_engine_sleep_keep(tq_engine* e) {
     TQ_CUDA(cudaMemcpy(k.positions.data(), e->d_positions, (size_t)e->G * sizeof(int), cudaMemcpyDeviceToHost));
     k.blobs.resize(e->G);
     for (int g = 0; g < e->G; ++g) {
-        const int cap = e->ragged ? e->capacities[g] : e->msl;
-        const int n = std::max(0, std::min(k.positions[g], cap));
+        const int n = std::max(0, std::min(k.positions[g], e->cap_eff(g)));
         k.blobs[g].resize(tq_engine_sequence_blob_bytes(e, n));
         int r = tq_engine_export_sequence(e, g, n, k.blobs[g].data(), k.blobs[g].size(), nullptr);
         if (r != TQ_OK) return r;
@@ -970,9 +992,8 @@ static int engine_restore_kept(tq_engine* e) {
     e->kept = tq_engine::Kept();
     if (!k.valid || k.G != e->G || k.ragged != e->ragged) return TQ_OK;  // another batch: the kept sequences are dropped
     for (int g = 0; g < e->G; ++g) {
-        const int cap = e->ragged ? e->capacities[g] : e->msl;
         const int n = ((const int*)k.blobs[g].data())[6];
-        if (n > cap) return TQ_OK;  // does not fit the new slots: dropped
+        if (n > e->capacities[g]) return TQ_OK;  // does not fit the new slots (a shared prefix comes back as own rows): dropped
     }
     for (int g = 0; g < e->G; ++g) {
         int r = tq_engine_import_sequence(e, g, k.blobs[g].data(), k.blobs[g].size(), nullptr);
@@ -995,8 +1016,7 @@ int tq_engine_set_positions(tq_engine* e, const int* host_positions, int G, tq_s
     if (!e || !host_positions) return TQ_ERR_ARG;
     if (!e->arena || G != e->G) return TQ_ERR_STATE;
     for (int g = 0; g < G; ++g) {
-        int cap = e->ragged ? e->capacities[g] : e->msl;
-        if (host_positions[g] < 0 || host_positions[g] >= cap) return TQ_ERR_CAPACITY;
+        if (host_positions[g] < 0 || host_positions[g] >= e->cap_eff(g)) return TQ_ERR_CAPACITY;
     }
     TQ_CUDA(cudaMemcpyAsync(e->d_positions, host_positions, (size_t)G * sizeof(int), cudaMemcpyHostToDevice, cs(s)));
     return TQ_OK;
@@ -1027,7 +1047,7 @@ int tq_engine_layer_ptrs(tq_engine* e, int layer, void** k_codes, void** v_codes
     return TQ_OK;
 }
 
-const long long* tq_engine_row_base(tq_engine* e) { return e ? e->d_row_base : nullptr; }
+const long long* tq_engine_row_base(tq_engine* e) { return e ? e->rb() : nullptr; }
 const void* tq_engine_rotation(tq_engine* e) { return e ? e->d_rotation : nullptr; }
 
 int tq_engine_set_rotation(tq_engine* e, const void* host_half, tq_stream_t s) {
@@ -1075,11 +1095,11 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
     float* const f32 = e->out_f32 ? e->out_f32 + (size_t)layer * e->G * H * HEAD_DIM : nullptr;
     if (e->kv_bits == 0) {
         fp16_cache_write_kernel<<<e->G, 128, 0, cs(s)>>>((__half*)L.k, (__half*)L.v, (const __half*)k, (const __half*)v,
-                                                         e->d_positions, e->d_row_base, e->msl, e->msl, e->G,
-                                                         e->kv_dim(), (int*)e->workspace, e->d_capacities);
+                                                         e->d_positions, e->rb(), e->msl, e->msl, e->G,
+                                                         e->kv_dim(), (int*)e->workspace, e->caps());
         int r = cuda_status(cudaGetLastError());
         if (r != TQ_OK) return r;
-        return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->d_row_base, e->total_rows, e->msl, e->G,
+        return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->rb(), e->total_rows, e->msl, e->G,
                                         H, Hkv, D, e->q_dim(), e->kv_dim(), e->workspace, e->ws_bytes, s);
     }
     // One launch per layer when the batch fits the kernel's shared-memory tile table (tq_engine_set_fused).
@@ -1090,20 +1110,22 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(cs(s), &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
         const int early = (early_on && use_pdl() && chained && e->chain_stream == cs(s) && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
-        FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early, e->d_capacities};
-        const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base,
+        FusedInputs in{q, k, v, e->d_rotation_rep, ROT_COPIES, early, e->caps()};
+        const int r = attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->rb(),
                                      e->total_rows, e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes,
-                                     cs(s), use_pdl(), &in, 0, 0, f32);
+                                     cs(s), use_pdl(), &in, 0, 0, f32, e->shared_active ? e->d_prefix_base : nullptr,
+                                     e->shared_active ? e->d_prefix_tiles : nullptr);
         e->chain_ok = r == TQ_OK;
         e->chain_stream = cs(s);
         return r;
     }
     int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, q, e->d_rotation, e->d_positions, 0,
-                        e->d_row_base, 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
-                        e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep, 0, e->d_capacities);
+                        e->rb(), 0, 0, e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace,
+                        e->ws_bytes, true, cs(s), use_pdl(), e->d_rotation_prep, 0, e->caps());
     if (r != TQ_OK) return r;
-    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
-                          e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl(), nullptr, 0, 0, f32);
+    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->rb(), e->total_rows,
+                          e->msl, e->G, H, Hkv, e->q_dim(), e->kv_bits, e->workspace, e->ws_bytes, cs(s), use_pdl(), nullptr, 0, 0, f32,
+                          e->shared_active ? e->d_prefix_base : nullptr, e->shared_active ? e->d_prefix_tiles : nullptr);
 }
 
 int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
@@ -1114,12 +1136,13 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
     const tq_engine::Layer& L = e->layers[layer];
     // the tile table of the current positions (a launch of the append kernel without vectors), then the attention
     int r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, e->d_rotation, e->d_positions, 0,
-                        e->d_row_base, 0, 0, e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim,
+                        e->rb(), 0, 0, e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->shape.head_dim,
                         e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace, e->ws_bytes, true, cs(s), use_pdl());
     if (r != TQ_OK) return r;
-    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->d_row_base, e->total_rows,
+    return attention_impl(out, L.tmK, L.tmV, L.k, L.v, L.kn, L.vn, e->d_rotation_t, e->d_positions, -1, e->rb(), e->total_rows,
                           e->msl, e->G, e->shape.num_heads, e->shape.num_kv_heads, e->q_dim(), e->kv_bits, e->workspace,
-                          e->ws_bytes, cs(s), use_pdl());
+                          e->ws_bytes, cs(s), use_pdl(), nullptr, 0, 0, nullptr, e->shared_active ? e->d_prefix_base : nullptr,
+                          e->shared_active ? e->d_prefix_tiles : nullptr);
 }
 
 int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s) {
@@ -1151,8 +1174,8 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     t.ck = (uint8_t*)L.k; t.kn = (__half*)L.kn; t.cv = (uint8_t*)L.v; t.vn = (__half*)L.vn;
     t.k_buf = (const __half*)k; t.v_buf = (const __half*)v; t.rotation = (const __half*)e->d_rotation;
     t.positions = e->d_positions; t.status = (int*)e->workspace;
-    t.token_row0 = 0; t.seq_stride_rows = e->msl; t.row_base = e->d_row_base;
-    t.capacity_rows = e->msl; t.seq_capacity = e->d_capacities;
+    t.token_row0 = 0; t.seq_stride_rows = e->msl; t.row_base = e->rb();
+    t.capacity_rows = e->msl; t.seq_capacity = e->caps();
     t.n_seq = n * G; t.T = 1; t.Hkv = Hkv; t.kv_dim = e->kv_dim(); t.bits = e->kv_bits;
     t.step_G = G; t.code_layer_stride = (long long)e->code_layer_stride; t.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
     int r = launch_prefill_tc_params(t, s);
@@ -1174,7 +1197,8 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     AttnParams p{};
     p.ck = (const uint8_t*)L.k; p.cv = (const uint8_t*)L.v; p.kn = (const __half*)L.kn; p.vn = (const __half*)L.vn;
     p.q_rot = fw.w.q_rot; p.rotation_t = (const __half*)e->d_rotation_t; p.out = (__half*)out;
-    p.positions = e->d_positions; p.row_base = e->d_row_base;
+    p.positions = e->d_positions; p.row_base = e->rb();
+    if (e->shared_active) { p.prefix_base = e->d_prefix_base; p.prefix_tiles = e->d_prefix_tiles; }
     p.tile_start = fw.w.tile_start; p.worker_g = fw.w.worker_g; p.tickets = fw.w.tickets;
     p.partials = e->step_partials + (size_t)l0 * e->step_part_stride;
     p.status = fw.w.status;
@@ -1232,17 +1256,18 @@ static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq
     if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || first_pos < 0 || n_seq <= 0) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
     if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;
-    int cap = e->msl;
-    if (e->ragged) {
-        cap = e->capacities[first_seq];
-        for (int i = 1; i < n_seq; ++i) cap = std::min(cap, e->capacities[first_seq + i]);
+    int cap = e->cap_eff(first_seq);
+    for (int i = 0; i < n_seq; ++i) {
+        cap = std::min(cap, e->cap_eff(first_seq + i));
+        // rows below a shared prefix belong to another sequence's slot: they are written through that sequence only
+        if (first_pos < e->prefix_tokens[first_seq + i]) return TQ_ERR_STATE;
     }
     if (first_pos + T > cap) return TQ_ERR_CAPACITY;
     const tq_engine::Layer& L = e->layers[layer];
     if (e->kv_bits == 0) {
         const size_t row_bytes = (size_t)e->kv_dim() * 2;
         for (int i = 0; i < n_seq; ++i) {
-            const long long row0 = e->ragged ? e->h_row_base[first_seq + i] : (long long)(first_seq + i) * e->msl;
+            const long long row0 = e->row0_eff(first_seq + i);
             TQ_CUDA(cudaMemcpyAsync((char*)L.k + (size_t)(row0 + first_pos) * row_bytes, (const char*)k + (size_t)i * T * row_bytes,
                                     (size_t)T * row_bytes, cudaMemcpyDeviceToDevice, cs(s)));
             TQ_CUDA(cudaMemcpyAsync((char*)L.v + (size_t)(row0 + first_pos) * row_bytes, (const char*)v + (size_t)i * T * row_bytes,
@@ -1251,7 +1276,7 @@ static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq
         return TQ_OK;
     }
     // token form: token t goes to position first_pos + t (by value: no position array)
-    const long long row0 = e->ragged ? e->h_row_base[first_seq] : (long long)first_seq * e->msl;
+    const long long row0 = e->row0_eff(first_seq);
     // the append kernel only needs the header of the workspace here (status word)
     AppendParams p{};
     p.ck = (uint8_t*)L.k; p.kn = (__half*)L.kn; p.cv = (uint8_t*)L.v; p.vn = (__half*)L.vn;
@@ -1268,7 +1293,59 @@ static int engine_prefill_impl(tq_engine* e, int layer, int first_seq, int n_seq
     if (n_seq == 1) return launch_append(p, cs(s));
     if ((long long)n_seq * T * p.Hkv >= (1ll << 31)) return TQ_ERR_CAPACITY;
     // several sequences: the tensor-core kernel takes them in one launch (whatever their number of head vectors)
-    return launch_prefill_tc(p, cs(s), n_seq, e->msl, e->ragged ? e->d_row_base + first_seq : nullptr);
+    return launch_prefill_tc(p, cs(s), n_seq, e->msl, e->rb() ? e->rb() + first_seq : nullptr);
+}
+
+// A prompt of T tokens shared by the sequences first_seq .. first_seq + n_seq - 1 (rollouts of one prompt: the
+// reference prefills sequence 0 and copies its cache to the others, engine/engine.cpp:2173-2214).  Here the first
+// P = 32 * floor(T / 32) tokens are quantised and stored ONCE, in the slot of first_seq; the other sequences read those
+// tiles from there (AttnParams::prefix_base) and their own slots start at token P.  The remaining T - P tokens (less
+// than a tile) go into every sequence's own rows.  Call it once per layer, with the same T, before anything else is
+// appended to these sequences.
+int tq_engine_prefill_shared(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v, int T,
+                             tq_stream_t s) {
+    if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
+    if (!e || layer < 0 || layer >= e->shape.num_layers || !k || !v || T <= 0 || n_seq <= 0) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;
+    if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;  // the fp16 twin's kernel reads every sequence from its own slot
+    const int P = T / TILE_TOKENS * TILE_TOKENS;
+    if (e->prefix_tokens[first_seq] != 0 || T > e->capacities[first_seq]) return e->prefix_tokens[first_seq] ? TQ_ERR_STATE : TQ_ERR_CAPACITY;
+    bool changed = false;
+    for (int i = 1; i < n_seq; ++i) {
+        const int g = first_seq + i;
+        if (e->prefix_tokens[g] == P && (P == 0 || e->prefix_owner[g] == first_seq)) continue;  // set by an earlier layer's call
+        if (e->prefix_tokens[g] != 0) return TQ_ERR_STATE;
+        if (T - P > e->capacities[g]) return TQ_ERR_CAPACITY;
+        if (P > 0) {
+            e->prefix_tokens[g] = P;
+            e->prefix_owner[g] = first_seq;
+            changed = true;
+        }
+    }
+    if (changed) {
+        e->shared_active = true;
+        std::vector<long long> rb(e->G), pb(e->G);
+        std::vector<int> cp(e->G), pt(e->G);
+        for (int g = 0; g < e->G; ++g) {
+            rb[g] = e->row0_eff(g);
+            cp[g] = e->cap_eff(g);
+            pb[g] = e->prefix_tokens[g] ? e->h_row_base[e->prefix_owner[g]] : 0;
+            pt[g] = e->prefix_tokens[g] / TILE_TOKENS;
+        }
+        TQ_CUDA(cudaMemcpyAsync(e->d_row_base, rb.data(), rb.size() * sizeof(long long), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync(e->d_capacities, cp.data(), cp.size() * sizeof(int), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync(e->d_prefix_base, pb.data(), pb.size() * sizeof(long long), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaMemcpyAsync(e->d_prefix_tiles, pt.data(), pt.size() * sizeof(int), cudaMemcpyHostToDevice, cs(s)));
+        TQ_CUDA(cudaStreamSynchronize(cs(s)));  // the sources are locals of this frame
+    }
+    // the whole prompt into the owner's slot (its rows P .. T-1 are its own remainder), the remainder into the others'
+    int r = engine_prefill_impl(e, layer, first_seq, 1, k, v, 0, T, s);
+    const size_t row_bytes = (size_t)e->kv_dim() * 2;
+    for (int i = 1; i < n_seq && r == TQ_OK && T > P; ++i)
+        r = engine_prefill_impl(e, layer, first_seq + i, 1, (const char*)k + (size_t)P * row_bytes, (const char*)v + (size_t)P * row_bytes,
+                                P, T - P, s);
+    return r;
 }
 
 int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos, int T,

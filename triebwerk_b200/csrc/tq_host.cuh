@@ -429,8 +429,19 @@ struct tq_engine {
     int msl = 0;          // dense slot size, or the largest capacity in ragged mode
     bool ragged = false;
     long long total_rows = 0;
-    std::vector<int> capacities;       // ragged mode, rounded up
-    std::vector<long long> h_row_base; // ragged mode
+    std::vector<int> capacities;       // rows of every slot (ragged: rounded up to 32; dense: the slot size)
+    std::vector<long long> h_row_base; // first row of every slot
+    // Shared prefixes: sequence g reads its first prefix_tokens[g] tokens (a multiple of 32) from the slot of
+    // prefix_owner[g]; its own slot then starts at token prefix_tokens[g].  0 / -1: nothing shared.
+    std::vector<int> prefix_tokens, prefix_owner;
+    bool shared_active = false;
+    long long* d_prefix_base = nullptr;  // [G] first row of the shared tiles
+    int* d_prefix_tiles = nullptr;       // [G] number of shared tiles
+    // the slot table the kernels see (null in the dense layout without shared prefixes: row = g * max_seq_len + pos)
+    const long long* rb() const { return (ragged || shared_active) ? d_row_base : nullptr; }
+    const int* caps() const { return (ragged || shared_active) ? d_capacities : nullptr; }
+    long long row0_eff(int g) const { return h_row_base[g] - prefix_tokens[g]; }   // row of token 0 if the slot started there
+    int cap_eff(int g) const { return capacities[g] + prefix_tokens[g]; }          // positions the sequence may reach
 
     struct Layer {
         void* k = nullptr;
@@ -453,8 +464,8 @@ struct tq_engine {
     float* out_f32 = nullptr;          // optional [layers][G][H][128]: results before the fp16 rounding (outside the arena)
 
     int* d_positions = nullptr;
-    int* d_capacities = nullptr;       // ragged mode: rows each sequence may use
-    long long* d_row_base = nullptr;
+    int* d_capacities = nullptr;       // [G] positions each sequence may reach (slot rows + shared prefix tokens)
+    long long* d_row_base = nullptr;   // [G] first row of every slot, minus the sequence's shared prefix tokens
     void* workspace = nullptr;
     size_t ws_bytes = 0;
     void* stage_q = nullptr;   // [layers][G][q_dim]
@@ -508,7 +519,13 @@ inline size_t bump(size_t& off, size_t bytes) {
 inline long long plan_rows(int G, int max_seq_len, const int* capacities, std::vector<int>* caps_out,
                            std::vector<long long>* base_out) {
     long long rows = 0;
-    if (capacities == nullptr) return (long long)G * max_seq_len;
+    if (capacities == nullptr) {
+        for (int g = 0; g < G; ++g) {
+            if (caps_out) caps_out->push_back(max_seq_len);
+            if (base_out) base_out->push_back((long long)g * max_seq_len);
+        }
+        return (long long)G * max_seq_len;
+    }
     for (int g = 0; g < G; ++g) {
         int c = capacities[g] < 1 ? 1 : capacities[g];
         c = (c + TILE_TOKENS - 1) / TILE_TOKENS * TILE_TOKENS;

@@ -180,6 +180,13 @@ class Engine:
         check(lib().tq_engine_prefill_append(self._h, layer, seq, k.data_ptr(), v.data_ptr(), first_pos, k.shape[0],
                                              self._stream()), "prefill_append")
 
+    def prefill_shared(self, layer: int, first_seq: int, n_seq: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        """One prompt k/v [T, kv_dim] for the sequences first_seq .. first_seq + n_seq - 1: its whole tiles are stored once
+        (in the slot of first_seq) and read by all of them; see tq_engine_prefill_shared."""
+        assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous() and k.shape == v.shape
+        check(lib().tq_engine_prefill_shared(self._h, layer, first_seq, n_seq, k.data_ptr(), v.data_ptr(), k.shape[0],
+                                             self._stream()), "prefill_shared")
+
     def prefill_append_batch(self, layer: int, first_seq: int, k: torch.Tensor, v: torch.Tensor, first_pos: int = 0) -> None:
         """Token-form append of k/v [n_seq, T, kv_dim] for the sequences first_seq .. first_seq + n_seq - 1 in one launch."""
         assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous() and k.dim() == 3 and k.shape == v.shape
