@@ -104,6 +104,10 @@ void launch_gqa_attention_batch(void* out, const void* q, const void* ck, const 
 void launch_gqa_attention(const void* q, const void* k_cache, const void* v_cache, void* output,
                           float* attn_scratch, int pos, int max_seq_len, int num_heads, int num_kv_heads,
                           int head_dim, tq_stream_t stream);
+/* engine/kernels.cu:1071-1158, 1359-1362: causal prefill attention over the fp16 cache of ONE sequence; query token t
+ * ([T][q_dim]) attends to rows 0 .. t.  `as` (the reference's [T][heads][T] score scratch) is accepted and ignored. */
+void launch_gqa_prefill_attention(void* out, const void* q, const void* ck, const void* cv, float* as, int T, int msl,
+                                  int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, tq_stream_t s);
 
 /* Status of the most recent compat launcher call on this host thread (TQ_OK or an error above). */
 int tq_last_compat_status(void);

@@ -194,13 +194,86 @@ def test_attention_equals_reference_kernels_live():
     print(f"vs live reference kernels: max-abs {worst:.2e}, rel {rel:.2e}")
 
 
-def test_unsupported_shapes_are_refused():
+def test_three_kv_heads_are_served_and_bad_shapes_refused():
+    """3 KV heads is outside the streaming kernel's layouts: the launcher serves it through the generic kernel, as the
+    reference would.  What no kernel can serve (heads not divisible, head_dim other than 128) is still refused."""
     import triebwerk_b200 as tq
+    from triebwerk_b200 import ops
     R, _ = tqo.rotation()
     rng = np.random.default_rng(80)
-    H, Hkv, D, msl, bits = 6, 3, 128, 32, 4  # 3 KV heads: outside what the kernel is built for
+    H, Hkv, D, msl, bits = 6, 3, 128, 32, 4
     ck, kn, cv, vn = hp.build_cache_oracle(rng, 1, [4], msl, Hkv, D, bits, R)
     q = rng.standard_normal((1, H * D), dtype=np.float32).astype(np.float16)
-    with pytest.raises(tq.TqError) as e:
-        gu.gpu_attention_batch(q, ck, cv, kn, vn, R, [3], msl, H, Hkv, D, bits)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, [3], msl, H, Hkv, D, bits)
+    ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, np.array([3], np.int32), msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got, ref, H, D, "3 KV heads")
+    with pytest.raises(tq.TqError) as e:  # 7 query heads over 3 KV heads
+        gu.gpu_attention_batch(np.zeros((1, 7 * D), np.float16), ck, cv, kn, vn, R, [3], msl, 7, Hkv, D, bits)
+    assert e.value.status == -1
+    with pytest.raises(tq.TqError) as e:  # the native entry point on pre-rotated queries: streaming layouts only
+        ws = ops.new_workspace(1, H)
+        out = torch.zeros(1, H * D, dtype=torch.float16, device="cuda")
+        ops.decode_attention(out, gu.dev(ck), gu.dev(cv), gu.dev(kn), gu.dev(vn), gu.dev(R), gu.dev(np.array([3], np.int32)), msl,
+                             H, Hkv, bits, ws)
     assert e.value.status == -4
+
+
+@pytest.mark.parametrize("bits,H,Hkv", [(4, 40, 8), (2, 8, 2), (4, 64, 8), (4, 6, 2), (0, 12, 4), (0, 40, 8)])
+def test_head_layouts_outside_the_streaming_kernel(bits, H, Hkv):
+    """The reference kernels take any number of heads (grid (G, num_heads)); so do the launchers here: layouts the
+    streaming kernels are not built for (more than 32 query heads, 2 KV heads, 3 or 5 query heads per KV head ...) go
+    through the generic kernel.  Batched, single-sequence and prefill forms against the oracle."""
+    import triebwerk_b200 as tq
+    from triebwerk_b200 import ops
+    rng = np.random.default_rng(300 + bits + H)
+    R, _ = tqo.rotation()
+    D, msl = 128, 320
+    lengths = [1, 33, 300, 129]
+    G = len(lengths)
+    q = rng.standard_normal((G, H * D), dtype=np.float32).astype(np.float16)
+    pos = np.array(lengths, np.int32) - 1
+    if bits == 0:
+        ck = rng.standard_normal((G * msl, Hkv * D), dtype=np.float32).astype(np.float16)
+        cv = rng.standard_normal((G * msl, Hkv * D), dtype=np.float32).astype(np.float16)
+        ref, _ = tqo.fp16_attention_batch(q, ck, cv, pos, msl, H, Hkv, D)
+        out = torch.zeros(G, H * D, dtype=torch.float16, device="cuda")
+        ops.launch_gqa_attention_batch(out, gu.dev(q), gu.dev(ck), gu.dev(cv), None, gu.dev(pos), msl, G, H, Hkv, D, H * D, Hkv * D)
+        hp.assert_attention_close(gu.host(out), ref, H, D, f"generic fp16 H={H} Hkv={Hkv}")
+        return
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, G, lengths, msl, Hkv, D, bits, R)
+    ref, _ = tqo.attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    got = gu.gpu_attention_batch(q, ck, cv, kn, vn, R, pos, msl, H, Hkv, D, bits)
+    w, r = hp.assert_attention_close(got, ref, H, D, f"generic batched tq{bits} H={H} Hkv={Hkv}")
+    print(f"generic kernel tq{bits} H={H} Hkv={Hkv}: max-abs {w:.2e}, rel {r:.2e}")
+    g = 2
+    sl = slice(g * msl, (g + 1) * msl)
+    got1 = gu.gpu_attention_single(q[g], ck[sl], cv[sl], kn[sl], vn[sl], R, pos[g], msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got1[None], ref[g][None], H, D, "generic single-sequence")
+    T = 40
+    qt = rng.standard_normal((T, H * D), dtype=np.float32).astype(np.float16)
+    refp, _ = tqo.prefill_attention(qt, ck[sl], cv[sl], kn[sl], vn[sl], R, msl, H, Hkv, D, bits)
+    gotp = gu.gpu_prefill_attention(qt, ck[sl], cv[sl], kn[sl], vn[sl], R, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(gotp, refp, H, D, "generic prefill")
+    # the engine serves the layout too: append (chain kernel) + generic attention, bytes as the oracle's
+    eng = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, msl)
+    ks = [rng.standard_normal((n, Hkv * D), dtype=np.float32).astype(np.float16) for n in lengths]
+    vs = [rng.standard_normal((n, Hkv * D), dtype=np.float32).astype(np.float16) for n in lengths]
+    for gi, n in enumerate(lengths):
+        if n > 1:
+            eng.prefill_append(0, gi, gu.dev(ks[gi][:-1]), gu.dev(vs[gi][:-1]), 0)
+    eng.set_positions([n - 1 for n in lengths])
+    oute = gu.host(eng.decode_layer(0, gu.dev(q), gu.dev(np.stack([k[-1] for k in ks])), gu.dev(np.stack([v[-1] for v in vs]))))
+    assert eng.status() == 0
+    # (against the oracle run on the engine's OWN cache bytes: a coordinate that sits on a quantiser bound may
+    # legitimately fall to the other side than in the oracle's append, see tests/test_append_gpu.py)
+    gk, gv, gkn, gvn = (gu.host(t) for t in eng.layer_cache(0))
+    n_diff = 0
+    for gi, n in enumerate(lengths):
+        sl = slice(gi * msl, gi * msl + n)
+        r1, _ = tqo.attention_single(q[gi], gk[sl], gv[sl], gkn[sl], gvn[sl], R, n - 1, n, H, Hkv, D, bits)
+        hp.assert_attention_close(oute[gi][None], r1[None], H, D, f"generic engine seq {gi}")
+        cq, cn = tqo.alloc_cache(1, n, Hkv, D, bits)
+        tqo.append_tokens(cq, cn, ks[gi], R, np.arange(n, dtype=np.int32), n, Hkv, D, bits)
+        n_diff += int((hp.unpack_codes(cq, bits) != hp.unpack_codes(gk[sl], bits)).sum())
+    assert n_diff <= 4, f"{n_diff} K coordinates differ from the oracle's append"

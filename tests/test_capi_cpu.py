@@ -116,3 +116,46 @@ def test_calls_before_alloc_report_state_errors():
     assert L.tq_engine_set_arena(h, None, 0) == -1
     assert L.tq_engine_set_arena(h, 0x1001, 4096) == -1  # arena must be 256-byte aligned
     L.tq_engine_destroy(h)
+
+
+def test_reference_engine_links_against_this_library_for_the_path():
+    """The reference's engine.cpp, compiled to an object where it lies (headers only, nothing is run), leaves a set of
+    launch_* symbols undefined.  Every one of them that belongs to this path must be exported by libtriebwerk_b200.so,
+    and the header's prototype must have the parameter list of the reference's own declaration (half* <-> void*,
+    cudaStream_t <-> tq_stream_t).  Symbol tables and declaration text only."""
+    import re
+    import subprocess
+    import tempfile
+    ref = os.path.join(os.path.dirname(ROOT), "reference", "engine", "engine.cpp")
+    if not os.path.exists(ref):
+        pytest.skip("the reference tree is not present on this machine")
+    with tempfile.TemporaryDirectory() as tmp:
+        obj = os.path.join(tmp, "engine_ref.o")
+        r = subprocess.run(["g++", "-std=c++17", "-c", "-I/usr/local/cuda/include", "-I" + os.path.dirname(ref), ref, "-o", obj],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            pytest.skip("the reference engine.cpp does not compile here: " + r.stderr[-200:])
+        undefined = {ln.split()[-1] for ln in subprocess.check_output(["nm", "-u", obj], text=True).splitlines() if " launch_" in ln}
+    path = {s for s in undefined if "turbo" in s} | (undefined & {
+        "launch_gqa_attention", "launch_gqa_attention_batch", "launch_gqa_prefill_attention", "launch_kv_cache_write_batch"})
+    assert len(path) == 9, sorted(path)
+    import triebwerk_b200
+    exported = {ln.split()[-1] for ln in subprocess.check_output(["nm", "-D", "--defined-only", triebwerk_b200._lib.LIB_PATH], text=True).splitlines()}
+    assert path <= exported, f"not exported: {sorted(path - exported)}"
+
+    def params(text, name):
+        m = re.search(r"void\s+" + name + r"\s*\(([^;{]*?)\)\s*[;{]", text, re.S)
+        assert m, name
+        out = []
+        for prm in m.group(1).split(","):
+            prm = re.sub(r"=.*", "", prm).strip()
+            ptr = "*" in prm
+            base = "int" if re.search(r"\bint\b", prm) and not ptr else ("float*" if "float" in prm else ("int*" if re.search(r"\bint\b", prm) else
+                   ("stream" if "tream" in prm and not ptr else ("ptr" if ptr else prm.split()[0]))))
+            out.append(base)
+        return out
+
+    ref_text = open(ref).read()
+    hdr_text = open(os.path.join(ROOT, "include", "triebwerk_b200.h")).read()
+    for name in sorted(path):
+        assert params(ref_text, name) == params(hdr_text, name), name

@@ -105,3 +105,34 @@ def test_fp16_attention_many_chunks_and_wide_groups(H, Hkv):
     ops.launch_gqa_attention_batch(out2, gu.dev(q), gu.dev(ck), gu.dev(cv), None, gu.dev(pos), msl, G, H, Hkv, D, H * D,
                                    Hkv * D)
     assert torch.equal(out, out2)
+
+
+def test_fp16_prefill_attention_against_oracle_and_reference_kernel():
+    """launch_gqa_prefill_attention (kv_bits = 0): query token t attends to rows 0 .. t of one sequence.  Against the
+    oracle's single-sequence attention per token, and against the reference's own kernel run live when its build is
+    there."""
+    import ctypes as C
+    import os
+    rng = np.random.default_rng(77)
+    H, Hkv, D, T, msl = 16, 8, 128, 70, 96
+    k = rng.standard_normal((msl, Hkv * D), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((msl, Hkv * D), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((T, H * D), dtype=np.float32).astype(np.float16)
+    dk, dv, dq = gu.dev(k), gu.dev(v), gu.dev(q)
+    out = torch.zeros(T, H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_prefill_attention(out, dq, dk, dv, None, T, msl, H, Hkv, D, H * D, Hkv * D)
+    got = gu.host(out)
+    ref = np.stack([tqo.fp16_attention_single(q[t], k, v, t, msl, H, Hkv, D)[0] for t in range(T)])
+    worst, rel = hp.assert_attention_close(got, ref, H, D, "fp16 prefill attention vs oracle")
+    print(f"fp16 prefill attention: max-abs {worst:.2e}, rel {rel:.2e} against the oracle")
+    if os.path.exists(gu.REF_SO):
+        refl = C.CDLL(gu.REF_SO)
+        scratch = torch.zeros(T * H * T, dtype=torch.float32, device="cuda")
+        out_ref = torch.zeros_like(out)
+        vp, i = C.c_void_p, C.c_int
+        refl.launch_gqa_prefill_attention.restype = None
+        refl.launch_gqa_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
+        refl.launch_gqa_prefill_attention(out_ref.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), T,
+                                          msl, H, Hkv, D, H * D, Hkv * D, torch.cuda.current_stream().cuda_stream)
+        w2, _ = hp.assert_attention_close(got, gu.host(out_ref), H, D, "fp16 prefill attention vs the reference kernel")
+        print(f"fp16 prefill attention: max-abs {w2:.2e} against the reference's own kernel")

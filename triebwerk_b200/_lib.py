@@ -17,7 +17,7 @@ SYMBOLS = [
     "tq_status_string", "tq_version", "tq_last_compat_status",
     "launch_turbo_kv_quantize", "launch_turbo_kv_quantize_batch", "launch_turbo_gqa_attention_batch",
     "launch_turbo_gqa_attention", "launch_turbo_gqa_prefill_attention", "launch_kv_cache_write_batch",
-    "launch_gqa_attention_batch", "launch_gqa_attention",
+    "launch_gqa_attention_batch", "launch_gqa_attention", "launch_gqa_prefill_attention",
     "tq_rotation_generate", "tq_workspace_bytes", "tq_append_decode", "tq_decode_attention",
     "tq_fp16_append_decode", "tq_fp16_decode_attention", "tq_workspace_status", "tq_decode_attention_static",
     "tq_engine_create", "tq_engine_destroy", "tq_engine_kv_bits", "tq_engine_set_fused", "tq_engine_arena_bytes", "tq_engine_set_arena",
@@ -66,6 +66,7 @@ def lib() -> C.CDLL:
     sig("launch_kv_cache_write_batch", None, [vp, vp, vp, vp, ip, i, i, i, vp])
     sig("launch_gqa_attention_batch", None, [vp, vp, vp, vp, vp, ip, i, i, i, i, i, i, i, vp])
     sig("launch_gqa_attention", None, [vp, vp, vp, vp, vp, i, i, i, i, i, vp])
+    sig("launch_gqa_prefill_attention", None, [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, vp])
     sig("tq_rotation_generate", i, [C.c_uint32, vp])
     sig("tq_workspace_bytes", sz, [i, i])
     sig("tq_append_decode", i, [vp, vp, vp, vp, vp, vp, vp, vp, ip, ip, i, i, i, i, i, i, i, i, vp, sz, vp])

@@ -233,6 +233,9 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
                         int q_dim, int kv_dim, int bits, void* workspace, size_t workspace_bytes, tq_stream_t s) {
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r != TQ_OK) return r;
+    // (this entry point reads queries that tq_append_decode rotated for the streaming kernel: its head layouts only;
+    // the launch_* symbols and the engine serve every layout)
+    if (!fast_shape(num_heads, num_kv_heads, true)) return TQ_ERR_UNSUPPORTED;
     if (!out || !ck_q || !cv_q || !k_norms || !v_norms || !rotation) return TQ_ERR_ARG;
     if (!positions && pos_value < 0) return TQ_ERR_ARG;
     if (!workspace) return TQ_ERR_WORKSPACE;
@@ -253,6 +256,28 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
     }
     return attention_impl(out, tmK, tmV, ck_q, cv_q, k_norms, v_norms, fw.rot_t, positions, pos_value, row_base, total_rows,
                           max_seq_len, G, num_heads, num_kv_heads, q_dim, bits, workspace, workspace_bytes, cs(s));
+}
+
+__global__ void causal_rows_kernel(int* pos, long long* rows, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        pos[i] = i;   // query token i attends to rows 0 .. i
+        rows[i] = 0;  // of the one sequence whose cache starts at row 0
+    }
+}
+
+// Any head layout: one CTA per (sequence, query head), see tq_generic.cuh.
+static int generic_packed_attention(void* out, const void* q, const void* ck_q, const void* cv_q, const void* k_norms,
+                                    const void* v_norms, const void* rotation, const int* positions, int pos_value,
+                                    const long long* row_base, int max_seq_len, int G, int H, int Hkv, int q_dim, int bits,
+                                    cudaStream_t s) {
+    if (!out || !q || !ck_q || !cv_q || !k_norms || !v_norms || !rotation) return TQ_ERR_ARG;
+    GenericAttnParams p{};
+    p.ck = (const uint8_t*)ck_q; p.cv = (const uint8_t*)cv_q; p.kn = (const __half*)k_norms; p.vn = (const __half*)v_norms;
+    p.q = (const __half*)q; p.rotation = (const __half*)rotation; p.out = (__half*)out;
+    p.positions = positions; p.row_base = row_base; p.pos_value = pos_value; p.max_seq_len = max_seq_len;
+    p.G = G; p.H = H; p.Hkv = Hkv; p.q_dim = q_dim; p.bits = bits;
+    return launch_generic_attention(p, false, s);
 }
 
 // ---- allocation-free decode attention -----------------------------------------------------------------------------------
@@ -290,6 +315,7 @@ int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, co
                                int kv_dim, int bits, tq_stream_t s) {
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r != TQ_OK) return r;
+    if (!fast_shape(num_heads, num_kv_heads, true)) return TQ_ERR_UNSUPPORTED;
     if (!out || !q || !ck_q || !cv_q || !k_norms || !v_norms || !rotation || !positions) return TQ_ERR_ARG;
     // everything that can refuse the call is checked before the first kernel is enqueued
     if ((((uintptr_t)ck_q | (uintptr_t)cv_q | (uintptr_t)k_norms | (uintptr_t)v_norms) & 15u) != 0) return TQ_ERR_ARG;
@@ -344,6 +370,13 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
     if (r != TQ_OK) return r;
     if (!out || !q || !ck || !cv) return TQ_ERR_ARG;
     if (!positions && pos_value < 0) return TQ_ERR_ARG;
+    if (!fast_shape(num_heads, num_kv_heads, false)) {  // 3, 5, 6, 7 or more than 8 query heads per KV head
+        GenericAttnParams gp{};
+        gp.ck = (const uint8_t*)ck; gp.cv = (const uint8_t*)cv; gp.q = (const __half*)q; gp.out = (__half*)out;
+        gp.positions = positions; gp.row_base = row_base; gp.pos_value = pos_value; gp.max_seq_len = max_seq_len;
+        gp.G = G; gp.H = num_heads; gp.Hkv = num_kv_heads; gp.q_dim = q_dim; gp.bits = 0;
+        return launch_generic_attention(gp, true, cs(s));
+    }
     if (!workspace) return TQ_ERR_WORKSPACE;
     // fp16 layout of the workspace: [0,256) header, tickets int[G*H] (one per sequence and virtual KV head, at most H), partials
     const size_t tick_bytes = align_up((size_t)G * num_heads * sizeof(int), 256);
@@ -404,6 +437,12 @@ void launch_turbo_gqa_attention_batch(void* out, const void* q, const uint8_t* c
     (void)as;
     bits = bits == 4 ? 4 : 2;  // the reference treats anything that is not 4 as 2-bit
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
+    if (r == TQ_OK && !fast_shape(num_heads, num_kv_heads, true)) {
+        g_compat_status = pos ? generic_packed_attention(out, q, ck_q, cv_q, k_norms, v_norms, rotation, pos, -1, nullptr, msl, G,
+                                                         num_heads, num_kv_heads, q_dim, bits, cs(s))
+                              : TQ_ERR_ARG;
+        return;
+    }
     void* ws = nullptr;
     size_t need = 0;
     if (r == TQ_OK) {
@@ -451,6 +490,11 @@ void launch_turbo_gqa_attention(const void* q, const uint8_t* ck_q, const uint8_
     const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
     int r = check_shape(1, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r == TQ_OK && (pos < 0 || pos >= msl)) r = TQ_ERR_CAPACITY;
+    if (r == TQ_OK && !fast_shape(num_heads, num_kv_heads, true)) {
+        g_compat_status = generic_packed_attention(output, q, ck_q, cv_q, k_norms, v_norms, rotation, nullptr, pos, nullptr, msl, 1,
+                                                   num_heads, num_kv_heads, q_dim, bits, cs(s));
+        return;
+    }
     void* ws = nullptr;
     size_t need = 0;
     if (r == TQ_OK) {
@@ -479,6 +523,23 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
     bits = bits == 4 ? 4 : 2;
     int r = check_shape(T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, bits, true);
     if (r == TQ_OK && T > msl) r = TQ_ERR_CAPACITY;
+    if (r == TQ_OK && !fast_shape(num_heads, num_kv_heads, true)) {
+        // every query token as a "sequence" of its own: position t, row base 0
+        void* gws = nullptr;
+        const size_t gneed = align_up((size_t)T * sizeof(int), 256) + align_up((size_t)T * sizeof(long long), 256);
+        r = compat_workspace(gneed, &gws, cs(s));
+        if (r == TQ_OK) {
+            int* gpos = (int*)gws;
+            long long* grows = (long long*)((char*)gws + align_up((size_t)T * sizeof(int), 256));
+            causal_rows_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(gpos, grows, T);
+            r = cuda_status(cudaGetLastError());
+            if (r == TQ_OK)
+                r = generic_packed_attention(out, q, ck_q, cv_q, k_norms, v_norms, rotation, gpos, -1, grows, msl, T, num_heads,
+                                             num_kv_heads, q_dim, bits, cs(s));
+        }
+        g_compat_status = r;
+        return;
+    }
     void* ws = nullptr;
     size_t need = 0;
     int qg = 1, groups = T, vheads = num_heads;
@@ -562,6 +623,34 @@ void launch_gqa_attention(const void* q, const void* k_cache, const void* v_cach
     if (r == TQ_OK)
         r = tq_fp16_decode_attention(output, q, k_cache, v_cache, nullptr, pos, nullptr, max_seq_len, max_seq_len, 1,
                                      num_heads, num_kv_heads, head_dim, q_dim, kv_dim, ws, need, stream);
+    g_compat_status = r;
+}
+
+// Causal prefill attention over an fp16 cache (kv_bits = 0), replaces launch_gqa_prefill_attention
+// (engine/kernels.cu:1071-1158, 1359-1362): query token t of ONE sequence attends to cache rows 0 .. t.  Served by the
+// fp16 decode kernel with every query token as a "sequence" of its own (position t, row base 0): no O(T^2) score scratch.
+void launch_gqa_prefill_attention(void* out, const void* q, const void* ck, const void* cv, float* as, int T, int msl,
+                                  int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, tq_stream_t s) {
+    std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // per-device compat state, see tq_host.cuh
+    (void)as;
+    int r = check_shape(T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
+    if (r == TQ_OK && T > msl) r = TQ_ERR_CAPACITY;
+    void* ws = nullptr;
+    size_t attn_bytes = 0, need = 0;
+    if (r == TQ_OK) {
+        attn_bytes = align_up(fp16_workspace_bytes(T, num_heads, num_kv_heads, msl), 256);
+        need = attn_bytes + align_up((size_t)T * sizeof(int), 256) + align_up((size_t)T * sizeof(long long), 256);
+        r = compat_workspace(need, &ws, cs(s));
+    }
+    if (r == TQ_OK) {
+        int* pos = (int*)((char*)ws + attn_bytes);
+        long long* rows = (long long*)((char*)pos + align_up((size_t)T * sizeof(int), 256));
+        causal_rows_kernel<<<(T + 127) / 128, 128, 0, cs(s)>>>(pos, rows, T);
+        r = cuda_status(cudaGetLastError());
+        if (r == TQ_OK)
+            r = tq_fp16_decode_attention(out, q, ck, cv, pos, -1, rows, msl, msl, T, num_heads, num_kv_heads, head_dim, q_dim,
+                                         kv_dim, ws, attn_bytes, s);
+    }
     g_compat_status = r;
 }
 
@@ -815,7 +904,8 @@ int tq_engine_alloc_batch(tq_engine* e, int G, int max_seq_len, const int* capac
         int ur = engine_upload_rotation(e, nullptr);
         if (ur != TQ_OK) return ur;
     }
-    if (e->kv_bits != 0) {
+    if (e->kv_bits != 0 && fast_shape(e->shape.num_heads, e->shape.num_kv_heads, true)) {
+        // (other head layouts take the generic kernel, which reads the cache with plain loads: no descriptors)
         const int kvp = e->kv_dim() / e->vpb();
         for (auto& L : e->layers) {
             r = make_code_map(&L.tmK, L.k, rows, kvp);
@@ -1102,6 +1192,16 @@ int tq_engine_decode_layer(tq_engine* e, int layer, const void* q, const void* k
         return tq_fp16_decode_attention(out, q, L.k, L.v, e->d_positions, -1, e->rb(), e->total_rows, e->msl, e->G,
                                         H, Hkv, D, e->q_dim(), e->kv_dim(), e->workspace, e->ws_bytes, s);
     }
+    if (!fast_shape(H, Hkv, true)) {
+        // a head layout outside the streaming kernel's: append with the chain kernel, attend with the generic one
+        if (e->shared_active) return TQ_ERR_UNSUPPORTED;
+        int r = append_impl((uint8_t*)L.k, L.kn, (uint8_t*)L.v, L.vn, k, v, nullptr, e->d_rotation, e->d_positions, 0, e->rb(), 0, 0,
+                            e->msl, e->G, H, Hkv, D, e->q_dim(), e->kv_dim(), e->kv_bits, e->workspace, e->ws_bytes, false, cs(s),
+                            false, e->d_rotation_prep, 0, e->caps());
+        if (r != TQ_OK) return r;
+        return generic_packed_attention(out, q, L.k, L.v, L.kn, L.vn, e->d_rotation, e->d_positions, -1, e->rb(), e->msl, e->G, H,
+                                        Hkv, e->q_dim(), e->kv_bits, cs(s));
+    }
     // One launch per layer when the batch fits the kernel's shared-memory tile table (tq_engine_set_fused).
     if (e->fused && e->G <= FUSED_MAX_G) {
         static const bool early_on = !(getenv("TQ_FUSED_EARLY") && atoi(getenv("TQ_FUSED_EARLY")) == 0);
@@ -1132,7 +1232,7 @@ int tq_engine_attend_layer(tq_engine* e, int layer, void* out, tq_stream_t s) {
     if (e) e->chain_ok = false;  // not a fused decode launch: the next one reads nothing early
     if (!e || layer < 0 || layer >= e->shape.num_layers || !out) return TQ_ERR_ARG;
     if (e->asleep || !e->arena || e->G == 0) return TQ_ERR_STATE;
-    if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;
+    if (e->kv_bits == 0 || !fast_shape(e->shape.num_heads, e->shape.num_kv_heads, true)) return TQ_ERR_UNSUPPORTED;
     const tq_engine::Layer& L = e->layers[layer];
     // the tile table of the current positions (a launch of the append kernel without vectors), then the attention
     int r = append_impl(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, e->d_rotation, e->d_positions, 0,
@@ -1163,6 +1263,7 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s) {
 // q, k, v, out point at layer l0's [G][dim] blocks of [layers][G][dim] buffers.
 static bool engine_whole_step_ok(const tq_engine* e, const void* q, const void* k, const void* v, const void* out) {
     return e->kv_bits != 0 && e->fused && e->whole_step && e->G <= FUSED_MAX_G && e->step_partials &&
+           fast_shape(e->shape.num_heads, e->shape.num_kv_heads, true) &&
            ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) == 0);
 }
 
@@ -1309,6 +1410,7 @@ int tq_engine_prefill_shared(tq_engine* e, int layer, int first_seq, int n_seq, 
     if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
     if (first_seq < 0 || first_seq + n_seq > e->G) return TQ_ERR_ARG;
     if (e->kv_bits == 0) return TQ_ERR_UNSUPPORTED;  // the fp16 twin's kernel reads every sequence from its own slot
+    if (!fast_shape(e->shape.num_heads, e->shape.num_kv_heads, true)) return TQ_ERR_UNSUPPORTED;
     const int P = T / TILE_TOKENS * TILE_TOKENS;
     if (e->prefix_tokens[first_seq] != 0 || T > e->capacities[first_seq]) return e->prefix_tokens[first_seq] ? TQ_ERR_STATE : TQ_ERR_CAPACITY;
     bool changed = false;

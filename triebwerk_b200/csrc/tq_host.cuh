@@ -21,6 +21,7 @@
 #include "tq_common.cuh"
 #include "tq_fp16.cuh"
 #include "tq_qrot.cuh"
+#include "tq_generic.cuh"
 
 namespace tq {
 
@@ -131,18 +132,29 @@ inline size_t fp16_partials_bytes(int G, int H, int max_seq_len) {
 }
 
 // ---- shape checks -------------------------------------------------------------------------------------------------------
+// What the entry points accept: any head layout the reference accepts (head_dim 128, num_heads a multiple of num_kv_heads).
 inline int check_shape(int G, int H, int Hkv, int head_dim, int q_dim, int kv_dim, int bits, bool packed) {
     if (head_dim != HEAD_DIM) return TQ_ERR_UNSUPPORTED;
     if (G <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0) return TQ_ERR_ARG;
     if (kv_dim != Hkv * head_dim || q_dim < H * head_dim) return TQ_ERR_ARG;
-    if (packed) {
-        if (bits != 2 && bits != 4) return TQ_ERR_ARG;
-        if (Hkv % 4 != 0 || Hkv > 8 || H / Hkv > 8 || H > ATTN_MAX_HEADS) return TQ_ERR_UNSUPPORTED;
-    } else {
-        int grp = H / Hkv;
-        if (grp != 1 && grp != 2 && grp != 4 && grp != 8) return TQ_ERR_UNSUPPORTED;
-    }
+    if (packed && bits != 2 && bits != 4) return TQ_ERR_ARG;
     return TQ_OK;
+}
+
+// What the streaming kernels serve; every other layout takes generic_decode_attention_kernel (one CTA per sequence
+// and query head, every cache byte read once per query head, as the reference does).
+inline bool fast_shape(int H, int Hkv, bool packed) {
+    if (packed) return Hkv % 4 == 0 && Hkv <= 8 && H / Hkv <= 8 && H <= ATTN_MAX_HEADS;
+    const int grp = H / Hkv;
+    return grp == 1 || grp == 2 || grp == 4 || grp == 8;
+}
+
+inline int launch_generic_attention(const GenericAttnParams& p, bool fp16, cudaStream_t s) {
+    if (p.G <= 0 || p.H <= 0 || p.G > 2147483647 / 1 || p.H > 65535) return TQ_ERR_ARG;
+    dim3 grid((unsigned)p.G, (unsigned)p.H);
+    if (fp16) generic_decode_attention_kernel<true><<<grid, GENERIC_WARPS * 32, 0, s>>>(p);
+    else generic_decode_attention_kernel<false><<<grid, GENERIC_WARPS * 32, 0, s>>>(p);
+    return cuda_status(cudaGetLastError());
 }
 
 // ---- launches -------------------------------------------------------------------------------------------------------------

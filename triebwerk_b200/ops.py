@@ -87,6 +87,13 @@ def launch_gqa_attention(q, k_cache, v_cache, output, attn_scratch, pos, max_seq
 
 
 # ---- native entry points ---------------------------------------------------------------------------------------------
+def launch_gqa_prefill_attention(out, q, ck, cv, attn_scratch, T, msl, num_heads, num_kv_heads, head_dim, q_dim, kv_dim):
+    """Causal prefill attention over an fp16 cache (reference engine/kernels.cu:1359-1362)."""
+    lib().launch_gqa_prefill_attention(_ptr(out), _ptr(q), _ptr(ck), _ptr(cv), _ptr(attn_scratch), T, msl, num_heads,
+                                       num_kv_heads, head_dim, q_dim, kv_dim, _stream())
+    _raise_compat("launch_gqa_prefill_attention")
+
+
 def rotation_matrix(seed: int = 42) -> torch.Tensor:
     """The engine's 128x128 fp16 rotation (reference engine/engine.cpp:364-392) as a CPU tensor."""
     out = torch.empty(128, 128, dtype=torch.float16)
