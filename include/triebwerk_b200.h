@@ -296,6 +296,32 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s);
  * environment to get one launch per layer instead. */
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
 
+/* The step's producer and consumer folded into it.  In the reference the projections' outputs pass through two more
+ * kernels before the cache write -- per-head RMS norm with weights (launch_qk_norm_batch) and rotary embedding
+ * (launch_rope_batch), engine/engine.cpp:1972-1977, kernels engine/kernels.cu:880-962 -- and the attention result
+ * through R^T before o_proj (engine/engine.cpp:2015).  tq_engine_decode_step_produce takes the RAW projections q_raw
+ * [layers][G][q_dim] and k_raw [layers][G][kv_dim]: norm and rotary embedding run inside the query rotation and inside
+ * the append, with the reference's arithmetic and its roundings to fp16, so cache bytes and results are those of the
+ * separate kernels followed by tq_engine_decode_step.  With rotated_output != 0 the results stay in rotated space
+ * (out = normalised weighted V sums, no R^T): the consumer multiplies by weights that carry R^T, built once by
+ * tq_fold_rotation_into_projection (w [rows][num_heads * 128] fp16, row-major: w_out[:, head block] =
+ * w_in[:, head block] * R^T).  Packed modes with the streaming kernels' head layouts; rope_dim 64 or 128; all arrays
+ * on the device, 16-byte aligned.  No counterpart in the reference (it runs the separate kernels). */
+typedef struct tq_step_producer {
+    const void* q_norm_weight; /* fp16 [layers][128] */
+    const void* k_norm_weight; /* fp16 [layers][128] */
+    const void* rope_cos;      /* fp16 [positions][rope_dim / 2] */
+    const void* rope_sin;
+    int rope_dim;
+    float eps;
+    int biased;                /* weights stored minus one (the reference's `biased` flag) */
+    int rotated_output;
+} tq_step_producer;
+int tq_engine_decode_step_produce(tq_engine* e, const void* q_raw, const void* k_raw, const void* v, void* out,
+                                  const tq_step_producer* prod, tq_stream_t s);
+int tq_fold_rotation_into_projection(void* w_out, const void* w_in, const void* rotation, long long rows, int num_heads,
+                                     tq_stream_t s);
+
 /* The same for the layers first_layer .. first_layer + n_layers - 1 only; q, k, v, out point at the block of
  * first_layer ([n_layers][G][dim]).  Lets a caller exchange or copy out one group of layers while the next is computed. */
 int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v,

@@ -469,6 +469,55 @@ void tqo_prefill_attention(uint16_t* out, float* out_f32, const uint16_t* q, con
 }
 
 // kv_bits = 0 cache write, engine/kernels.cu:964-977.
+// The producer of the step's q and k (engine/engine.cpp:1972-1977): per-head RMS norm with a weight vector
+// (qk_norm_batch_kernel, engine/kernels.cu:880-923) and rotary embedding (rope_batch_kernel, :926-962), both in place
+// on fp16 [G][dim] buffers, each rounding its results to fp16.  Arithmetic as the reference's build evaluates it:
+// one head per 128-thread block, sum of squares by the block tree above, `s / head_dim + eps` (the division by 128
+// is exact), rsqrtf (IEEE here, rsqrt.approx there: results may differ in the last fp16 bit), (x * rms) * w;
+// rotary pairs (d, d + rope_dim/2) with x0*c - x1*s evaluated as fma(x0, c, -(x1*s)) and x0*s + x1*c as
+// fma(x0, s, x1*c) (how the reference's -fmad=true build contracts the two expressions).
+static void qk_norm_one(uint16_t* data, const uint16_t* w, int head_dim, float eps, int biased) {
+    float sq[128], v[128];
+    for (int d = 0; d < 128; ++d) {
+        v[d] = d < head_dim ? h2f(data[d]) : 0.0f;
+        sq[d] = v[d] * v[d];
+    }
+    const float ss = block_sum128(sq);
+    const float rms = (float)(1.0 / std::sqrt((double)(ss / (float)head_dim + eps)));
+    for (int d = 0; d < head_dim; ++d) {
+        float wv = h2f(w[d]);
+        if (biased) wv += 1.0f;
+        data[d] = f2h((v[d] * rms) * wv);
+    }
+}
+static void rope_one(uint16_t* x, const uint16_t* cos_row, const uint16_t* sin_row, int half_rope) {
+    for (int d = 0; d < half_rope; ++d) {
+        const float c = h2f(cos_row[d]), sv = h2f(sin_row[d]);
+        const float x0 = h2f(x[d]), x1 = h2f(x[d + half_rope]);
+        x[d] = f2h(std::fmaf(x0, c, -(x1 * sv)));
+        x[d + half_rope] = f2h(std::fmaf(x0, sv, x1 * c));
+    }
+}
+void tqo_qk_norm_rope_batch(uint16_t* q, uint16_t* k, const uint16_t* q_w, const uint16_t* k_w, const uint16_t* cos_table,
+                            const uint16_t* sin_table, const int* positions, int G, int num_heads, int num_kv_heads,
+                            int head_dim, int q_dim, int kv_dim, int rope_dim, float eps, int biased) {
+    const int half_rope = rope_dim / 2;
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < G; ++g) {
+        const int pos = positions[g];
+        for (int h = 0; h < num_heads; ++h) {
+            uint16_t* x = q + (size_t)g * q_dim + (size_t)h * head_dim;
+            qk_norm_one(x, q_w, head_dim, eps, biased);
+            rope_one(x, cos_table + (size_t)pos * half_rope, sin_table + (size_t)pos * half_rope, half_rope);
+        }
+        for (int h = 0; h < num_kv_heads; ++h) {
+            uint16_t* x = k + (size_t)g * kv_dim + (size_t)h * head_dim;
+            qk_norm_one(x, k_w, head_dim, eps, biased);
+            rope_one(x, cos_table + (size_t)pos * half_rope, sin_table + (size_t)pos * half_rope, half_rope);
+        }
+    }
+}
+
 void tqo_fp16_write_batch(uint16_t* cache_k, uint16_t* cache_v, const uint16_t* k, const uint16_t* v,
                           const int* positions, int max_seq_len, int G, int kv_dim) {
     for (int g = 0; g < G; ++g) {

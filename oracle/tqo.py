@@ -202,3 +202,17 @@ def fnv1a64(data: bytes) -> str:
         h ^= b
         h = (h * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
     return f"{h:016x}"
+
+
+def qk_norm_rope_batch(q, k, q_w, k_w, cos_table, sin_table, positions, num_heads, num_kv_heads, head_dim, rope_dim,
+                       eps=1e-6, biased=False):
+    """Per-head RMS norm and rotary embedding of the step's q [G, q_dim] and k [G, kv_dim] (fp16), as the reference's
+    qk_norm_batch_kernel + rope_batch_kernel (engine/kernels.cu:880-962).  Returns new arrays."""
+    q, k = _h(q).copy(), _h(k).copy()
+    G, q_dim = q.shape
+    kv_dim = k.shape[1]
+    positions = np.ascontiguousarray(positions, np.int32)
+    lib().tqo_qk_norm_rope_batch(_p(q), _p(k), _p(_h(q_w)), _p(_h(k_w)), _p(_h(cos_table)), _p(_h(sin_table)), _p(positions),
+                                 C.c_int(G), C.c_int(num_heads), C.c_int(num_kv_heads), C.c_int(head_dim), C.c_int(q_dim),
+                                 C.c_int(kv_dim), C.c_int(rope_dim), C.c_float(eps), C.c_int(int(biased)))
+    return q, k

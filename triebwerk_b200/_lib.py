@@ -26,8 +26,13 @@ SYMBOLS = [
     "tq_engine_rotation", "tq_engine_set_rotation", "tq_engine_decode_layer", "tq_engine_prefill_append", "tq_engine_prefill_append_batch",
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
     "tq_engine_output_f32", "tq_engine_read_output_f32", "tq_engine_decode_layers", "tq_static_status", "tq_selftest_bounded_wait",
-    "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep", "tq_engine_prefill_shared",
+    "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep", "tq_engine_prefill_shared", "tq_engine_decode_step_produce", "tq_fold_rotation_into_projection",
 ]
+
+
+class StepProducer(C.Structure):
+    _fields_ = [("q_norm_weight", C.c_void_p), ("k_norm_weight", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+                ("rope_dim", C.c_int), ("eps", C.c_float), ("biased", C.c_int), ("rotated_output", C.c_int)]
 
 
 class ModelShape(C.Structure):
@@ -101,6 +106,8 @@ def lib() -> C.CDLL:
     sig("tq_engine_status", i, [vp, vp])
     sig("tq_engine_attend_step", i, [vp, vp, vp])
     sig("tq_static_status", i, [vp])
+    sig("tq_engine_decode_step_produce", i, [vp, vp, vp, vp, vp, C.POINTER(StepProducer), vp])
+    sig("tq_fold_rotation_into_projection", i, [vp, vp, vp, ll, i, vp])
     sig("tq_engine_prefill_shared", i, [vp, i, i, i, vp, vp, i, vp])
     sig("tq_engine_sequence_blob_bytes", sz, [vp, i])
     sig("tq_engine_export_sequence", i, [vp, i, i, vp, sz, vp])

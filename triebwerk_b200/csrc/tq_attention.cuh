@@ -210,7 +210,7 @@ __device__ __forceinline__ float ldsp_h2f(uint32_t addr) {  // one fp16 from sha
 template <int NW, typename OutRow, typename OutRowF32>
 __device__ __forceinline__ void merge_sequence(const float* part0, int parts, int H, uint32_t merge_s, const __half* rotation_t,
                                                int head, int lane, int bar_group, int nthreads, OutRow out_row,
-                                               OutRowF32 out_row_f32) {
+                                               OutRowF32 out_row_f32, bool rotated_out = false) {
     const int gl = lane >> 2, t4 = lane & 3;
     for (int hb = 0; hb < H; hb += 16) {
         // ---- phase A: heads hb .. hb+15, two heads per warp at a time with all their loads in flight
@@ -299,6 +299,20 @@ __device__ __forceinline__ void merge_sequence(const float* part0, int parts, in
                     }
                 }
             }
+            if (rotated_out) {
+                // the consumer's weights carry R^T (tq_fold_rotation_into_projection): the normalised sums leave as they are
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int hh = hh0 + r * NW;
+                    if (hh >= 16) continue;
+                    if (__half* o = out_row(hb + hh)) {
+                        const __half2 h01 = __floats2half2_rn(a[r].x, a[r].y), h23 = __floats2half2_rn(a[r].z, a[r].w);
+                        *reinterpret_cast<uint2*>(o + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                    }
+                    if (float* o = out_row_f32(hb + hh)) *reinterpret_cast<float4*>(o + 4 * lane) = a[r];
+                }
+                continue;
+            }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const int hh = hh0 + r * NW;
@@ -312,6 +326,7 @@ __device__ __forceinline__ void merge_sequence(const float* part0, int parts, in
                              "r"(pack_half2(a[r].x - f01.x, a[r].y - f01.y)), "r"(pack_half2(a[r].z - f23.x, a[r].w - f23.y)) : "memory");
             }
         }
+        if (rotated_out) continue;
         // ---- phase B: out[h][d] = sum_k a[h][k] * R[k][d]  ==  A(16 x 128) * B with B[k][n=d] = rotation_t[d][k].
         //      Two column blocks of 8 per warp and pass; their B fragments are fetched before the barrier so that
         //      the round trip overlaps the other warps' phase A.
@@ -1445,6 +1460,7 @@ struct MergeParams {
     long long part_layer_stride; // floats
     long long q_layer_stride;    // halves
     int G, H, q_dim;
+    int rotated_out;             // 1: leave the results in rotated space (the consumer's weights carry R^T)
 };
 constexpr int MERGE_WARPS = 8;
 
@@ -1472,7 +1488,8 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_partials_kernel(const 
         return p.out_f32 + (((size_t)layer * p.G + (size_t)g) * H + (size_t)vh) * HEAD_DIM;
     };
     merge_sequence<MERGE_WARPS>(p.partials + (size_t)layer * (size_t)p.part_layer_stride + (size_t)(first_w + g) * H * PART_STRIDE,
-                                parts, H, smem_u32(merge_buf), p.rotation_t, warp, lane, 0, MERGE_WARPS * 32, out_row, out_row_f32);
+                                parts, H, smem_u32(merge_buf), p.rotation_t, warp, lane, 0, MERGE_WARPS * 32, out_row, out_row_f32,
+                                p.rotated_out != 0);
 }
 
 }  // namespace tq

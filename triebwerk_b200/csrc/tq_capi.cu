@@ -727,6 +727,7 @@ static void engine_release_arena(tq_engine* e) {
     e->step_partials = nullptr;
     e->step_table = nullptr;
     e->step_qrot = nullptr;
+    e->step_kpost = nullptr;
     e->workspace = nullptr;
     for (auto& l : e->layers) l = tq_engine::Layer();
 }
@@ -799,6 +800,7 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
     size_t osp = bump(off, part_stride * e->shape.num_layers * sizeof(float));
     size_t ost = bump(off, (size_t)(G + 4) * sizeof(int));
     size_t osq = bump(off, e->kv_bits ? (size_t)e->shape.num_layers * G * e->shape.num_heads * HEAD_DIM * 2 : 0);
+    size_t okp = bump(off, e->kv_bits ? (size_t)e->shape.num_layers * G * e->kv_dim() * 2 : 0);
     size_t ws_bytes = e->kv_bits ? carve_full(nullptr, G, e->shape.num_heads).bytes
                                  : fp16_workspace_bytes(G, e->shape.num_heads, e->shape.num_kv_heads, msl);
     size_t ows = bump(off, ws_bytes);
@@ -815,6 +817,7 @@ static size_t engine_carve(tq_engine* e, char* base, int G, int msl, long long r
         e->step_part_stride = part_stride;
         e->step_table = (int*)(base + ost);
         e->step_qrot = base + osq;
+        e->step_kpost = base + okp;
         e->workspace = base + ows;
         e->ws_bytes = ws_bytes;
         e->stage_q = base + oq;
@@ -1267,7 +1270,8 @@ static bool engine_whole_step_ok(const tq_engine* e, const void* q, const void* 
            ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) == 0);
 }
 
-static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, void* out, cudaStream_t s) {
+static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, void* out, cudaStream_t s,
+                              const tq_step_producer* prod = nullptr) {
     e->chain_ok = false;
     const tq_engine::Layer& L = e->layers[l0];
     const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, G = e->G;
@@ -1279,9 +1283,15 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     t.capacity_rows = e->msl; t.seq_capacity = e->caps();
     t.n_seq = n * G; t.T = 1; t.Hkv = Hkv; t.kv_dim = e->kv_dim(); t.bits = e->kv_bits;
     t.step_G = G; t.code_layer_stride = (long long)e->code_layer_stride; t.norm_layer_stride = (long long)(e->norm_layer_stride / 2);
-    int r = launch_prefill_tc_params(t, s);
+    if (prod) {  // QK-norm and rotary embedding of the raw K projection on the way into the append
+        t.norm_w = (const __half*)prod->k_norm_weight + (size_t)l0 * HEAD_DIM;
+        t.rope_cos = (const __half*)prod->rope_cos; t.rope_sin = (const __half*)prod->rope_sin;
+        t.rope_dim = prod->rope_dim; t.eps = prod->eps; t.biased = prod->biased;
+        t.k_post = (__half*)e->step_kpost + (size_t)l0 * G * e->kv_dim();
+    }
+    int r = launch_prefill_tc_params(t, s, prod != nullptr);
     if (r != TQ_OK) return r;
-    {   // all query heads of the n layers, rotated and scaled, as fp16
+    {   // all query heads of the n layers, rotated and scaled, as fp16 (producer form: normed and rope'd first)
         QRotParams qr{};
         qr.q = (const __half*)q; qr.rotation = (const __half*)e->d_rotation;
         qr.q_rot = (__half*)e->step_qrot + (size_t)l0 * G * H * HEAD_DIM;
@@ -1289,7 +1299,14 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
         long long blocks = (qr.n_vec + 15) / 16;
         const long long cap = 4ll * device_props().sm_count;
         if (blocks > cap) blocks = cap;
-        rotate_queries_kernel<<<(unsigned)blocks, QROT_WARPS * 32, 0, s>>>(qr);
+        if (prod) {
+            qr.norm_w = (const __half*)prod->q_norm_weight + (size_t)l0 * HEAD_DIM;
+            qr.rope_cos = (const __half*)prod->rope_cos; qr.rope_sin = (const __half*)prod->rope_sin;
+            qr.positions = e->d_positions; qr.G = G; qr.rope_dim = prod->rope_dim; qr.eps = prod->eps; qr.biased = prod->biased;
+            rotate_queries_kernel<true><<<(unsigned)blocks, QROT_WARPS * 32, 0, s>>>(qr);
+        } else {
+            rotate_queries_kernel<false><<<(unsigned)blocks, QROT_WARPS * 32, 0, s>>>(qr);
+        }
         r = cuda_status(cudaGetLastError());
         if (r != TQ_OK) return r;
     }
@@ -1326,6 +1343,7 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     m.out = (__half*)out; m.out_f32 = e->out_f32 ? e->out_f32 + (size_t)l0 * G * H * HEAD_DIM : nullptr;
     m.part_layer_stride = p.part_layer_stride; m.q_layer_stride = p.q_layer_stride;
     m.G = G; m.H = H; m.q_dim = e->q_dim();
+    m.rotated_out = (prod && prod->rotated_output) ? 1 : 0;
     return launch_kernel(merge_partials_kernel, dim3(G, n), dim3(MERGE_WARPS * 32), 0, s, use_pdl(), m);
 }
 
@@ -1347,6 +1365,44 @@ int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const v
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s) {
     if (!e) return TQ_ERR_ARG;
     return tq_engine_decode_layers(e, 0, e->shape.num_layers, q, k, v, out, s);
+}
+
+// The decode step with its producer and consumer folded in: q_raw / k_raw are the projections' raw outputs; per-head RMS
+// norm and rotary embedding (the reference's launch_qk_norm_batch + launch_rope_batch, engine/engine.cpp:1972-1977) are
+// applied inside the query rotation and inside the append; with rotated_output the inverse rotation is left to the
+// consumer's weights (tq_fold_rotation_into_projection).
+int tq_engine_decode_step_produce(tq_engine* e, const void* q_raw, const void* k_raw, const void* v, void* out,
+                                  const tq_step_producer* prod, tq_stream_t s) {
+    if (!e || !q_raw || !k_raw || !v || !out || !prod) return TQ_ERR_ARG;
+    if (!prod->q_norm_weight || !prod->k_norm_weight || !prod->rope_cos || !prod->rope_sin) return TQ_ERR_ARG;
+    if (prod->rope_dim != 64 && prod->rope_dim != 128) return TQ_ERR_UNSUPPORTED;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (!engine_whole_step_ok(e, q_raw, k_raw, v, out)) return TQ_ERR_UNSUPPORTED;  // packed modes, streaming head layouts
+    if ((((uintptr_t)prod->q_norm_weight | (uintptr_t)prod->k_norm_weight | (uintptr_t)prod->rope_cos | (uintptr_t)prod->rope_sin) & 15u) != 0)
+        return TQ_ERR_ARG;
+    return engine_step_layers(e, 0, e->shape.num_layers, q_raw, k_raw, v, out, cs(s), prod);
+}
+
+__global__ void fold_rotation_kernel(__half* w_out, const __half* w_in, const __half* rotation, long long rows, int num_heads) {
+    // w_out[r][h*128 + k] = sum_d w_in[r][h*128 + d] * R[k][d]   (W' = W * blockdiag(R^T): then W' * acc = W * (R^T acc))
+    __shared__ float row_s[HEAD_DIM];
+    const long long r = blockIdx.x;
+    const int h = blockIdx.y, k = threadIdx.x;
+    const size_t base = ((size_t)r * num_heads + h) * HEAD_DIM;
+    row_s[k] = __half2float(w_in[base + k]);
+    __syncthreads();
+    float acc = 0.0f;
+    const __half* rr = rotation + (size_t)k * HEAD_DIM;
+    for (int d = 0; d < HEAD_DIM; ++d) acc = fmaf(row_s[d], __half2float(rr[d]), acc);
+    w_out[base + k] = __float2half_rn(acc);
+}
+
+int tq_fold_rotation_into_projection(void* w_out, const void* w_in, const void* rotation, long long rows, int num_heads,
+                                     tq_stream_t s) {
+    if (!w_out || !w_in || !rotation || rows <= 0 || num_heads <= 0 || rows > 2147483647ll || num_heads > 65535) return TQ_ERR_ARG;
+    fold_rotation_kernel<<<dim3((unsigned)rows, (unsigned)num_heads), HEAD_DIM, 0, cs(s)>>>((__half*)w_out, (const __half*)w_in,
+                                                                                         (const __half*)rotation, rows, num_heads);
+    return cuda_status(cudaGetLastError());
 }
 
 // Prompts of n_seq consecutive sequences (first_seq ..), all T tokens long and all at positions first_pos ..; inputs

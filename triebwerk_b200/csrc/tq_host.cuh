@@ -201,32 +201,29 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
 
 // Whole prompts (token form, K and/or V, no queries) go to the tensor-core kernel; TQ_PREFILL_TC=0 keeps them on
 // the fp32-chain kernel.  Both store the same bytes.
+// producer: the form that applies QK-norm and rotary embedding to the K vectors on the way in (PrefillTcParams)
+inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bool producer = false) {
+    int ar = producer ? ensure_dynamic_smem((const void*)prefill_append_tc_kernel<true>, TC_DYN_SMEM)
+                      : ensure_dynamic_smem((const void*)prefill_append_tc_kernel<false>, TC_DYN_SMEM);
+    if (ar != TQ_OK) return ar;
+    const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
+    long long grid = 2ll * device_props().sm_count;
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) return TQ_OK;
+    if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
+    else prefill_append_tc_kernel<false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
+    return cuda_status(cudaGetLastError());
+}
+
 inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 1, long long seq_stride_rows = 0,
                              const long long* seq_row_base = nullptr) {
-    int ar = ensure_dynamic_smem((const void*)prefill_append_tc_kernel, TC_DYN_SMEM);
-    if (ar != TQ_OK) return ar;
     PrefillTcParams t{};
     t.ck = p.ck; t.kn = p.kn; t.cv = p.cv; t.vn = p.vn;
     t.k_buf = p.k_buf; t.v_buf = p.v_buf; t.rotation = p.rotation; t.positions = p.positions; t.pos_value = p.pos_value; t.status = p.status;
     t.token_row0 = p.token_row0; t.capacity_rows = p.capacity_rows;
     t.seq_stride_rows = seq_stride_rows; t.row_base = seq_row_base; t.n_seq = n_seq;
     t.T = p.n_src; t.Hkv = p.Hkv; t.kv_dim = p.kv_dim; t.bits = p.bits;
-    const long long tiles = (((long long)n_seq * p.n_src * p.Hkv + TC_TILE - 1) / TC_TILE) * ((p.k_buf ? 1 : 0) + (p.v_buf ? 1 : 0));
-    long long grid = 2ll * device_props().sm_count;
-    if (grid > tiles) grid = tiles;
-    prefill_append_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
-    return cuda_status(cudaGetLastError());
-}
-
-inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s) {
-    int ar = ensure_dynamic_smem((const void*)prefill_append_tc_kernel, TC_DYN_SMEM);
-    if (ar != TQ_OK) return ar;
-    const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
-    long long grid = 2ll * device_props().sm_count;
-    if (grid > tiles) grid = tiles;
-    if (grid < 1) return TQ_OK;
-    prefill_append_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
-    return cuda_status(cudaGetLastError());
+    return launch_prefill_tc_params(t, s);
 }
 
 inline int launch_append(const AppendParams& p, cudaStream_t s, bool pdl = false) {
@@ -472,6 +469,7 @@ struct tq_engine {
     size_t step_part_stride = 0;       // floats per layer
     int* step_table = nullptr;         // [G + 4]
     void* step_qrot = nullptr;         // [layers][G][H][128] fp16: pre-rotated, pre-scaled queries
+    void* step_kpost = nullptr;        // [layers][G][kv_dim] fp16: K after QK-norm and rotary embedding (producer form)
     bool whole_step = !(getenv("TQ_WHOLE_STEP") && atoi(getenv("TQ_WHOLE_STEP")) == 0);
     float* out_f32 = nullptr;          // optional [layers][G][H][128]: results before the fp16 rounding (outside the arena)
 

@@ -76,6 +76,19 @@ struct PrefillTcParams {
     long long code_layer_stride;
     long long norm_layer_stride;
     const int* seq_capacity;   // optional, decode-step form: rows each sequence may use (else capacity_rows for all)
+    // Producer form (PRODUCER = true): k_buf holds the K projection's raw output; the per-head RMS norm with weights and
+    // the rotary embedding of the reference's qk_norm_batch_kernel + rope_batch_kernel (engine/kernels.cu:880-962) are
+    // applied while the vectors are loaded -- the reference's arithmetic, including its two roundings to fp16 -- so the
+    // K vectors that get quantised are bit for bit the ones the reference would have stored in its k buffer.  V vectors
+    // are taken as they are.
+    const __half* norm_w;      // [layers][128] RMS-norm weights of the K heads (layer of the call's first layer first)
+    const __half* rope_cos;    // [positions][rope_dim / 2]
+    const __half* rope_sin;
+    int rope_dim;              // 64 or 128
+    float eps;
+    int biased;
+    __half* k_post;            // [vectors][128] like k_buf: receives the produced K vectors (what the reference's k buffer
+                               // holds after its two kernels); the exact chains of near-bound coordinates re-read them
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
@@ -135,6 +148,7 @@ __device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int 
     return tile + region * 16384u + (uint32_t)row * 128u + ((((kk >> 3) ^ ((uint32_t)row & 7u))) << 4) + (kk & 7u) * 2u;
 }
 
+template <bool PRODUCER>
 __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const PrefillTcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     const uint32_t base = (smem_u32(tc_smem) + 1023u) & ~1023u;
@@ -246,6 +260,87 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                     val[8 * i + 2 * e + 1] = f.y;
                 }
             }
+            const int l0 = lane & ~3;
+            if constexpr (PRODUCER) {
+                if (kind == 0) {  // K vectors only; every thread of the warp walks the shuffles
+                    // RMS norm: sum of squares by the reference's block tree, x * rms * w rounded to fp16
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                        for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
+                    const float q0 = __shfl_sync(0xffffffffu, sq[0], l0), q1 = __shfl_sync(0xffffffffu, sq[0], l0 + 1);
+                    const float q2 = __shfl_sync(0xffffffffu, sq[0], l0 + 2), q3 = __shfl_sync(0xffffffffu, sq[0], l0 + 3);
+                    const float rms = rsqrt_approx_ftz(fma_ftz(add_ftz(add_ftz(q0, q2), add_ftz(q1, q3)), 1.0f / HEAD_DIM, p.eps));
+                    int layer = 0, sq_i = seq, ppos;
+                    if (p.step_G > 0) {
+                        layer = seq / p.step_G;
+                        sq_i = seq - layer * p.step_G;
+                        ppos = live ? p.positions[sq_i] : 0;
+                    } else {
+                        ppos = live ? (p.positions ? p.positions[t] : p.pos_value + t) : 0;
+                    }
+                    if (ppos < 0) ppos = 0;
+                    const uint4* wsrc = reinterpret_cast<const uint4*>(p.norm_w + (size_t)layer * HEAD_DIM + 32 * c);
+                    uint32_t nh[16];  // the normalised chunk as fp16 pairs
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 wu = __ldg(wsrc + i);
+                        const __half2* w2 = reinterpret_cast<const __half2*>(&wu);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float2 wf = __half22float2(w2[e]);
+                            if (p.biased) { wf.x = add_ftz(wf.x, 1.0f); wf.y = add_ftz(wf.y, 1.0f); }
+                            const __half2 h = __floats2half2_rn(mul_ftz(mul_ftz(val[8 * i + 2 * e], rms), wf.x),
+                                                                mul_ftz(mul_ftz(val[8 * i + 2 * e + 1], rms), wf.y));
+                            nh[4 * i + e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                    // rotary pairs (d, d + rope_dim / 2): this thread's chunk c with the chunk of thread c ^ (rope_dim / 64)
+                    const int hr32 = p.rope_dim >> 6, half_rope = p.rope_dim >> 1;
+                    const bool roped = c < 2 * hr32, low = c < hr32;
+                    const int cd = 32 * (low ? c : c - hr32);  // first rotary index of the pair's low chunk
+                    const uint4* csrc = reinterpret_cast<const uint4*>(p.rope_cos + (size_t)ppos * half_rope + (roped ? cd : 0));
+                    const uint4* ssrc = reinterpret_cast<const uint4*>(p.rope_sin + (size_t)ppos * half_rope + (roped ? cd : 0));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 cu = __ldg(csrc + i), su = __ldg(ssrc + i);
+                        const __half2* c2 = reinterpret_cast<const __half2*>(&cu);
+                        const __half2* s2 = reinterpret_cast<const __half2*>(&su);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t mine = nh[4 * i + e];
+                            const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, hr32);  // (lanes of one vector differ in c only)
+                            const float2 xo = __half22float2(*reinterpret_cast<const __half2*>(&mine));
+                            const float2 xp = __half22float2(*reinterpret_cast<const __half2*>(&other));
+                            const float2 cf = __half22float2(c2[e]), sf = __half22float2(s2[e]);
+                            float2 r = xo;
+                            if (roped) {
+                                if (low) {  // x0 = mine, x1 = partner: x0 * c - x1 * s
+                                    r.x = __half2float(__float2half_rn(fma_ftz(xo.x, cf.x, -mul_ftz(xp.x, sf.x))));
+                                    r.y = __half2float(__float2half_rn(fma_ftz(xo.y, cf.y, -mul_ftz(xp.y, sf.y))));
+                                } else {    // x0 = partner, x1 = mine: x0 * s + x1 * c
+                                    r.x = __half2float(__float2half_rn(fma_ftz(xp.x, sf.x, mul_ftz(xo.x, cf.x))));
+                                    r.y = __half2float(__float2half_rn(fma_ftz(xp.y, sf.y, mul_ftz(xo.y, cf.y))));
+                                }
+                            }
+                            val[8 * i + 2 * e] = r.x;
+                            val[8 * i + 2 * e + 1] = r.y;
+                        }
+                    }
+                    if (live) {
+                        uint4* dstp = reinterpret_cast<uint4*>(p.k_post + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * c);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            __half2 o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(val[8 * i + 2 * e], val[8 * i + 2 * e + 1]);
+                            dstp[i] = *reinterpret_cast<const uint4*>(o);
+                        }
+                    }
+                }
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
             // the warp-shuffle tree of the reference (offsets 16, 8, 4, 2, 1), element l taking lane l's place
@@ -254,7 +349,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 #pragma unroll
                 for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
             const float part = sq[0];
-            const int l0 = lane & ~3;
             const float p0 = __shfl_sync(0xffffffffu, part, l0), p1 = __shfl_sync(0xffffffffu, part, l0 + 1);
             const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
             const float tt = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
@@ -374,11 +468,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         auto exact_code = [&](int v, int d) -> int {
             const int vid = vec0 + v;
             const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
-            const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM);
+            const bool produced = PRODUCER && kind == 0;
+            const uint4* src = reinterpret_cast<const uint4*>((produced ? p.k_post : src_buf) + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM);
             const float inv = inv_s[v];
             uint4 xall[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) xall[j] = __ldg(src + j);
+            for (int j = 0; j < 16; ++j) xall[j] = produced ? src[j] : __ldg(src + j);
             float acc = 0.0f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -419,11 +514,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 if (live) {
                     const int vid = vec0 + v;
                     const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
-                    const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM) + 2 * sub;
+                    const bool produced = PRODUCER && kind == 0;
+                    const uint4* src = reinterpret_cast<const uint4*>((produced ? p.k_post : src_buf) + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM) + 2 * sub;
                     const float inv = inv_s[v];
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        const uint4 xv = __ldg(src + j);
+                        const uint4 xv = produced ? src[j] : __ldg(src + j);
                         const uint4 rv = *reinterpret_cast<const uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 16 * sub + 8 * j) - base));
                         const __half2* xh = reinterpret_cast<const __half2*>(&xv);
                         const __half2* rh = reinterpret_cast<const __half2*>(&rv);

@@ -16,7 +16,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from ._lib import ModelShape, check, lib
+from ._lib import ModelShape, StepProducer, check, lib
 
 QWEN3_0_6B = dict(num_layers=28, num_heads=16, num_kv_heads=8, head_dim=128)
 QWEN3_8B = dict(num_layers=36, num_heads=32, num_kv_heads=8, head_dim=128)
@@ -150,6 +150,18 @@ class Engine:
             assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16
         check(lib().tq_engine_decode_step(self._h, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                           self._stream()), "decode_step")
+        return out
+
+    def decode_step_produce(self, q_raw, k_raw, v, out, q_norm_weight, k_norm_weight, rope_cos, rope_sin, rope_dim=128,
+                            eps=1e-6, biased=False, rotated_output=False):
+        """decode_step on the projections' RAW outputs: per-head RMS norm (weights [layers, 128]) and rotary embedding
+        (tables [positions, rope_dim / 2]) are applied inside the step; rotated_output leaves R^T to the consumer."""
+        for t in (q_raw, k_raw, v, out, q_norm_weight, k_norm_weight, rope_cos, rope_sin):
+            assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16
+        prod = StepProducer(q_norm_weight.data_ptr(), k_norm_weight.data_ptr(), rope_cos.data_ptr(), rope_sin.data_ptr(),
+                            int(rope_dim), float(eps), int(bool(biased)), int(bool(rotated_output)))
+        check(lib().tq_engine_decode_step_produce(self._h, q_raw.data_ptr(), k_raw.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                                  C.byref(prod), self._stream()), "decode_step_produce")
         return out
 
     def decode_layers(self, first_layer: int, n_layers: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
