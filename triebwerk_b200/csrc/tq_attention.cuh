@@ -108,6 +108,7 @@ struct AttnParams {
                                    // (rotate_queries_kernel); a sequence's block reaches shared memory by one bulk copy
 #ifdef TQ_TIMING_SWITCHES
     int debug;                 // timing-experiment builds only: bit 0 = skip the math, bit 1 = skip the loads, ... (results are then wrong)
+    unsigned long long* stamps;  // timing-experiment builds only: [8] summed clock deltas of the tile loop's sections
 #endif
 };
 
@@ -116,9 +117,11 @@ struct AttnParams {
 #ifdef TQ_TIMING_SWITCHES
 #define TQ_DBG(bit) ((p.debug & (bit)) != 0)
 #define TQ_DBG_FACTOR (p.debug >> 8)
+#define TQ_STAMP(i) do { const long long _t = clock64(); stamp_acc[i] += _t - stamp_last; stamp_last = _t; } while (0)
 #else
 #define TQ_DBG(bit) false
 #define TQ_DBG_FACTOR 0
+#define TQ_STAMP(i) do { } while (0)
 #endif
 
 template <int BITS>
@@ -964,6 +967,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         vB_off = box_off + tokB * 128u + ((vch ^ tokB) << 4) + vsub;
     }
 
+#ifdef TQ_TIMING_SWITCHES
+    long long stamp_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    long long stamp_last = clock64();
+#endif
     for (int layer = 0; layer < n_layers; ++layer) {  // (one pass unless this is the whole-step form)
     long long tile = lo;
     g = g_lo;
@@ -982,6 +989,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         const int Lcol1 = qg > 1 ? min(L, g * qg + (2 * t4 + 1) / grp_real + 1) : L;
         const int Lmin = qg > 1 ? min(L, g * qg + 1) : L;
 
+        TQ_STAMP(8);   // loop tail + publishing of the previous segment + this segment's table / position reads
         // query fragments (B operand of the score product): lane (gl, t4) holds coordinates 32*t4 .. 32*t4+31 of head
         // head*grp + gl as fp16
         uint32_t qb[8][2];
@@ -994,6 +1002,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
             dead = __any_sync(0xffffffffu, dead);
             q_par ^= 1u;
+            TQ_STAMP(9);   // wait for the query block
             // lane (gl, t4): the 32 coordinates 32*t4 .. of head head*grp + gl, 64 bytes
             uint4 qw[4];
 #pragma unroll
@@ -1013,7 +1022,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                     qb[2 * i + h2][1] = BITS == 2 ? prmt(a, b, 0x7632u) : b;
                 }
             }
+            TQ_STAMP(10);  // fragments
             group_barrier(group, gthreads);  // every warp holds its fragments: the area may take the next block
+            TQ_STAMP(11);  // barrier of the worker's warps
             if (gtid == 0 && !dead && loads_on) {
                 fence_proxy_async_smem();
                 if (seg_end < hi) issue_queries(layer, g + 1);
@@ -1160,7 +1171,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             auto tile_body = [&](auto full_tag) {
                 constexpr bool FULLT = decltype(full_tag)::value;
                 constexpr uint32_t nstride = (uint32_t)Hkv * 2u;
+                TQ_STAMP(0);
                 const uint32_t tokK = wait_part(0);
+                TQ_STAMP(1);
                 if (dead) return;
                 const uint32_t kt = stage_addr(s) + tokK;
                 const uint32_t kns = kt + 2u * code_tile + (uint32_t)head * 2u;
@@ -1210,6 +1223,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 #pragma unroll
                 for (int blk = 0; blk < 4; ++blk) kn4[blk] = ldsv_h2f(kns + ((uint32_t)(8 * blk) + tauK) * nstride);
                 release_part(0);
+                TQ_STAMP(2);
 
                 // ---------------- online softmax: sv[blk][e] = score of token row (block blk, tau(gl)) and head 2*t4 + e.
                 // Columns of heads >= grp carry zeros and are never read.
@@ -1266,7 +1280,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 l_run[1] += (pv[0][1] + pv[1][1]) + (pv[2][1] + pv[3][1]);
 
                 // ---------------- values: 2 blocks of 16 tokens ----------------
+                TQ_STAMP(3);
                 const uint32_t tokV = wait_part(1);
+                TQ_STAMP(4);
                 if (dead) return;
                 const uint32_t vt = stage_addr(s) + code_tile + tokV;
                 const uint32_t vns = stage_addr(s) + tokV + 2u * code_tile + norm_tile + (uint32_t)head * 2u;
@@ -1341,6 +1357,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
                 if (full) tile_body(std::true_type{});
                 else tile_body(std::false_type{});
             }
+            TQ_STAMP(5);
             if (TQ_DBG(1)) {  // timing experiments: the copies without the arithmetic
                 wait_part(0);
                 release_part(0);
@@ -1356,6 +1373,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             }
         }
 
+        TQ_STAMP(12);  // (zero-length marker: everything up to here went to the tile stamps)
         // ================= end of segment: publish the partial, maybe merge =================
         const int slot = wid + g;
         float* const part_base = p.partials + (PERSIST ? (size_t)layer * (size_t)p.part_layer_stride : (size_t)0);
@@ -1440,6 +1458,13 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     }
     }
 
+#ifdef TQ_TIMING_SWITCHES
+    if (p.stamps && lane == 0) {
+        TQ_STAMP(6);
+        for (int i = 0; i < 15; ++i) atomicAdd(p.stamps + i, (unsigned long long)stamp_acc[i]);
+        atomicAdd(p.stamps + 15, 1ull);
+    }
+#endif
     // A warp that gave up on a wait may still have copies in flight: give them a bounded chance to land
     // before the CTA (and its shared memory) goes away.
     if (dead) {

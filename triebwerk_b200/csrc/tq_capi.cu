@@ -1334,6 +1334,13 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     p.q_rot16 = (const __half*)e->step_qrot + (size_t)l0 * G * H * HEAD_DIM;
 #ifdef TQ_TIMING_SWITCHES
     p.debug = getenv("TQ_ATTN_DEBUG") ? atoi(getenv("TQ_ATTN_DEBUG")) : 0;
+    static unsigned long long* d_stamps = nullptr;
+    static int stamp_calls = 0;
+    if (getenv("TQ_ATTN_STAMPS")) {
+        if (!d_stamps) cudaMalloc(&d_stamps, 128);
+        cudaMemsetAsync(d_stamps, 0, 128, s);
+        p.stamps = d_stamps;
+    }
 #endif
     r = launch_attention(e->kv_bits, e->tmK4, e->tmV4, p, attention_ctas(G, e->msl), s, use_pdl(), 2);
     if (r != TQ_OK) return r;
@@ -1344,6 +1351,17 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     m.part_layer_stride = p.part_layer_stride; m.q_layer_stride = p.q_layer_stride;
     m.G = G; m.H = H; m.q_dim = e->q_dim();
     m.rotated_out = (prod && prod->rotated_output) ? 1 : 0;
+#ifdef TQ_TIMING_SWITCHES
+    if (p.stamps && ++stamp_calls == 30) {
+        unsigned long long h[16];
+        cudaStreamSynchronize(s);
+        cudaMemcpy(h, p.stamps, 128, cudaMemcpyDeviceToHost);
+        const double w = (double)h[15];
+        fprintf(stderr, "stamps per warp (cycles, %d layers): loop-head %.0f | K wait %.0f | K phase %.0f | softmax %.0f | V wait %.0f | V phase %.0f | exit %.0f | "
+                        "seg: tail+publish+reads %.0f | q wait %.0f | fragments %.0f | barrier %.0f | after-loop %.0f | warps %.0f\n",
+                n, h[0] / w, h[1] / w, h[2] / w, h[3] / w, h[4] / w, h[5] / w, h[6] / w, h[8] / w, h[9] / w, h[10] / w, h[11] / w, h[12] / w, w);
+    }
+#endif
     return launch_kernel(merge_partials_kernel, dim3(G, n), dim3(MERGE_WARPS * 32), 0, s, use_pdl(), m);
 }
 
@@ -1537,7 +1555,12 @@ int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_h
     }
     // The first and the last group are single layers: the first copy-in and the last copy-out are the only ones
     // nothing can hide.
-    const int chunks = NL < NC ? NL : NC;
+    // (in the whole-step form every group costs four launches and a pipeline fill, so few groups: TQ_HOST_STEP_GROUPS)
+    static const int want = getenv("TQ_HOST_STEP_GROUPS") ? atoi(getenv("TQ_HOST_STEP_GROUPS")) : 0;
+    const bool whole_form = engine_whole_step_ok(e, e->stage_q, e->stage_k, e->stage_v, e->stage_out);
+    int nc = want > 0 ? want : (whole_form ? 5 : NC);
+    if (nc > NC) nc = NC;
+    const int chunks = NL < nc ? NL : nc;
     auto first_layer = [&](int c) {
         if (chunks < 4) return (int)((long long)c * NL / chunks);
         if (c <= 0) return 0;
