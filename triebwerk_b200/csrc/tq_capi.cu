@@ -365,7 +365,6 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
                              int pos_value, const long long* row_base, long long total_rows, int max_seq_len, int G,
                              int num_heads, int num_kv_heads, int head_dim, int q_dim, int kv_dim, void* workspace,
                              size_t workspace_bytes, tq_stream_t s) {
-    (void)total_rows;
     int r = check_shape(G, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
     if (r != TQ_OK) return r;
     if (!out || !q || !ck || !cv) return TQ_ERR_ARG;
@@ -391,6 +390,21 @@ int tq_fp16_decode_attention(void* out, const void* q, const void* ck, const voi
     p.nchunk_max = (max_seq_len + FP16_CHUNK - 1) / FP16_CHUNK;
     p.G = G; p.H = num_heads; p.Hkv = num_kv_heads; p.q_dim = q_dim; p.kv_dim = kv_dim;
     TQ_CUDA(cudaMemsetAsync(p.tickets, 0, (size_t)G * num_heads * sizeof(int), cs(s)));
+    // The tensor-core form by default (with four or eight query heads per KV head the fp32-FMA form is bound by its FMAs).
+    // TQ_FP16_TC=0 keeps everything on the FMA form, TQ_FP16_TC=1 only one and two heads per KV head.
+    static const int tc_mode = getenv("TQ_FP16_TC") ? atoi(getenv("TQ_FP16_TC")) : 2;
+    const int grp = num_heads / num_kv_heads;
+    if (tc_mode != 0 && (grp >= 4 || tc_mode == 2) && total_rows > 0 && (((uintptr_t)ck | (uintptr_t)cv | (uintptr_t)q) & 15u) == 0 &&
+        (kv_dim * 2) % 256 == 0) {
+        CUtensorMap tmK, tmV;
+        int r2;
+        {
+            std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());  // the descriptor cache is per-device compat state
+            r2 = cached_fp16_map(&tmK, ck, total_rows, kv_dim);
+            if (r2 == TQ_OK) r2 = cached_fp16_map(&tmV, cv, total_rows, kv_dim);
+        }
+        if (r2 == TQ_OK) return launch_fp16_tc_attention(tmK, tmV, p, cs(s));
+    }
     return launch_fp16_attention(p, cs(s));
 }
 
@@ -1558,7 +1572,7 @@ int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_h
     // (in the whole-step form every group costs four launches and a pipeline fill, so few groups: TQ_HOST_STEP_GROUPS)
     static const int want = getenv("TQ_HOST_STEP_GROUPS") ? atoi(getenv("TQ_HOST_STEP_GROUPS")) : 0;
     const bool whole_form = engine_whole_step_ok(e, e->stage_q, e->stage_k, e->stage_v, e->stage_out);
-    int nc = want > 0 ? want : (whole_form ? 5 : NC);
+    int nc = want > 0 ? want : (whole_form ? 4 : NC);
     if (nc > NC) nc = NC;
     const int chunks = NL < nc ? NL : nc;
     auto first_layer = [&](int c) {

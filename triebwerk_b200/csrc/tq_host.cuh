@@ -20,6 +20,7 @@
 #include "tq_attention.cuh"
 #include "tq_common.cuh"
 #include "tq_fp16.cuh"
+#include "tq_fp16_tc.cuh"
 #include "tq_qrot.cuh"
 #include "tq_generic.cuh"
 
@@ -76,6 +77,23 @@ inline int make_code_map(CUtensorMap* m, const void* base, long long rows, int k
     cuuint64_t dims[3] = {128u, (cuuint64_t)rows, (cuuint64_t)(kvp / 128)};
     cuuint64_t strides[2] = {(cuuint64_t)kvp, 128u};
     cuuint32_t box[3] = {128u, (cuuint32_t)TILE_TOKENS, (cuuint32_t)(kvp / 128)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
+}
+
+// fp16 K or V array [rows][kv_dim] viewed as bytes for fp16_tc_decode_attention_kernel: box = one head's 256 bytes
+// (two 128-byte blocks) x 16 rows, 128-byte swizzle.
+inline int make_fp16_rows_map(CUtensorMap* m, const void* base, long long rows, int kv_dim) {
+    auto fn = encode_fn();
+    if (!fn) return TQ_ERR_UNSUPPORTED;
+    const long long row_bytes = (long long)kv_dim * 2;
+    if (((uintptr_t)base & 15u) != 0 || rows <= 0 || rows >= (1ll << 31) || row_bytes % 256 != 0) return TQ_ERR_ARG;
+    cuuint64_t dims[3] = {128u, (cuuint64_t)rows, (cuuint64_t)(row_bytes / 128)};
+    cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 128u};
+    cuuint32_t box[3] = {128u, (cuuint32_t)FP16TC_BLOCK, 2u};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -308,6 +326,25 @@ __global__ void transpose_rotation_kernel(__half* dst, const __half* src, int* t
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_tickets; i += gridDim.x * blockDim.x) tickets[i] = 0;
 }
 
+// Tensor-core form of the twin (tq_fp16_tc.cuh): every query head of a KV head from one pass, whatever their number.
+template <int GRP>
+inline int launch_fp16_tc_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const Fp16AttnParams& p, cudaStream_t s) {
+    int ar = ensure_dynamic_smem((const void*)fp16_tc_decode_attention_kernel<GRP>, FP16TC_SMEM);
+    if (ar != TQ_OK) return ar;
+    dim3 grid(p.Hkv, p.nchunk_max, p.G);
+    fp16_tc_decode_attention_kernel<GRP><<<grid, FP16TC_WARPS * 32, FP16TC_SMEM, s>>>(tmK, tmV, p);
+    return cuda_status(cudaGetLastError());
+}
+inline int launch_fp16_tc_attention(const CUtensorMap& tmK, const CUtensorMap& tmV, const Fp16AttnParams& p, cudaStream_t s) {
+    switch (p.H / p.Hkv) {
+        case 1: return launch_fp16_tc_t<1>(tmK, tmV, p, s);
+        case 2: return launch_fp16_tc_t<2>(tmK, tmV, p, s);
+        case 4: return launch_fp16_tc_t<4>(tmK, tmV, p, s);
+        case 8: return launch_fp16_tc_t<8>(tmK, tmV, p, s);
+        default: return TQ_ERR_UNSUPPORTED;
+    }
+}
+
 inline int launch_fp16_attention(const Fp16AttnParams& p_in, cudaStream_t s) {
     // A CTA serves at most two query heads per pass over the rows (more cost it its occupancy: 47 % of the copy
     // bandwidth with four, 23 % with eight).  With 4 or 8 query heads per KV head, 2 or 4 CTAs share the rows of a KV
@@ -392,6 +429,22 @@ inline int compat_workspace(size_t need, void** out, cudaStream_t s) {
         c.ws_bytes = bytes;
     }
     *out = c.ws;
+    return TQ_OK;
+}
+
+// Call with compat_mutex() held.  The fp16 twin's descriptors share the cache (key: minus the row bytes).
+inline int cached_fp16_map(CUtensorMap* out, const void* base, long long rows, int kv_dim) {
+    CompatState& c = compat_state();
+    auto key = std::make_tuple(base, rows, -2 * kv_dim);
+    auto it = c.maps.find(key);
+    if (it == c.maps.end()) {
+        CUtensorMap m;
+        int r = make_fp16_rows_map(&m, base, rows, kv_dim);
+        if (r != TQ_OK) return r;
+        if (c.maps.size() > 4096) c.maps.clear();
+        it = c.maps.emplace(key, m).first;
+    }
+    *out = it->second;
     return TQ_OK;
 }
 
