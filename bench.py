@@ -629,7 +629,8 @@ def sharded_groups(n_layers, world):
 # dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel PER LAYER from the ncu captures summarised under
 # profiles/ (a capture covers a launch over 4 layers of the same per-layer shape), or absent while no capture exists.
 TRAFFIC_PER_LAYER = {
-    "c1": 283645536, "c1l4": 283645536,   # 4-layer launch: 1.1194 GB read + 15.2 MB written
+    "c1": 281445338, "c1l4": 281445338,   # 4-layer launch: 1111.2 MB read + 14.6 MB written
+    "c3l4": 148555328, "c3": 148555328,   # 4-layer launch of 32 sequences x 8192, 2-bit: 573.9 MB read + 20.4 MB written
 }
 
 

@@ -1,0 +1,307 @@
+// Causal prefill attention over the cache of ONE sequence with the query tokens in the M dimension, sm_100a.
+//
+// Replaces turbo_gqa_prefill_attention_kernel (reference engine/kernels.cu:1874-1960, packed cache) and
+// gqa_prefill_attention_kernel (engine/kernels.cu:1071-1158, fp16 cache): query token t attends to cache rows 0 .. t.
+// The reference runs one CTA per (head, query token), reads every cache row once per query token and keeps a
+// [T][heads][T] score array in global memory.  Here one CTA owns 128 score rows = (128 / GRP) consecutive query tokens x
+// the GRP query heads of ONE KV head and walks the cache in tiles of 64 rows:
+//   * a tile's codes are dequantised ONCE per CTA into an fp16 tile in shared memory (byte -> centroid pair through a
+//     table with a private column per lane; the fp16 cache is copied as it is), 128-byte-chunk swizzled;
+//   * S = Q . K^T on the tensor cores (mma.sync m16n8k16): each warp holds 16 query rows as A fragments for the whole
+//     launch, the B fragments come from the K tile by ldmatrix; the K norm multiplies the score column, the causal limit
+//     masks it, the softmax runs online in registers (base 2, the scale folded into the queries);
+//   * O += P . V with P taken from the score accumulators as the A operand (times the V norm) and the V tile through
+//     ldmatrix.trans; O stays in registers (16 rows x 128 coordinates per warp);
+//   * the next tile is fetched into registers before the arithmetic of the current one and dequantised into the other
+//     half of the double buffer after it: one barrier per tile.
+// Packed form: queries arrive pre-rotated and pre-scaled (rotate_queries_kernel), the unnormalised sums leave as split-K
+// partials with one part per (token, head) and merge_partials_kernel normalises and multiplies by R^T.  fp16 form: raw
+// queries, the result is normalised and stored here.  No O(T^2) scratch either way.
+#pragma once
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int PFA_THREADS = 256;   // 8 warps x 16 score rows
+constexpr int PFA_ROWS = 128;      // score rows per CTA
+constexpr int PFA_KT = 64;         // cache rows per tile
+
+struct PfaSmem {
+    static constexpr uint32_t K = 0;             // [2][64 rows][256 B]
+    static constexpr uint32_t V = 32768;         // [2][64 rows][256 B]
+    static constexpr uint32_t NORMS = 65536;     // [2 buffers][K, V][64] halves
+    static constexpr uint32_t LUT = 66048;       // 4-bit: [256][32 lanes] half2; 2-bit: [16][32 lanes] half2
+    static constexpr uint32_t BYTES = LUT + 32768;
+};
+
+struct PrefillAttnParams {
+    const __half* q;          // packed: rotated, scaled queries [T][H][128]; fp16: raw queries [T][q_dim]
+    long long q_tok_stride;   // halves between the queries of consecutive tokens
+    const uint8_t* ck;        // packed codes [rows][kvp], or fp16 rows [rows][Hkv * 128]
+    const uint8_t* cv;
+    const __half* kn;         // [rows][Hkv] (packed forms)
+    const __half* vn;
+    float* partials;          // packed forms: token t, head h -> partials[(2 t * H + h) * PART_STRIDE]: acc[128], m, l
+    __half* out;              // fp16 form: [T][q_dim]
+    int q_dim;
+    int T;                    // query tokens = cache rows in use
+    int rows;                 // cache rows that exist (loads are clamped to them)
+    int H, Hkv, grp_shift;    // GRP = 1 << grp_shift query heads per KV head
+    float score_scale;        // 1 when the queries carry log2(e) / sqrt(128) already
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const PrefillAttnParams p) {
+    extern __shared__ __align__(1024) uint8_t pfa_smem[];
+    const uint32_t sb = smem_u32(pfa_smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gl = lane >> 2, t4 = lane & 3;
+    const int gs = p.grp_shift, GRP = 1 << gs, QT = PFA_ROWS >> gs;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // the blocks with the longest prefixes start first
+    const int kvh = blockIdx.y;
+    const int q0 = qb * QT;
+    const int q_last = min(q0 + QT, p.T) - 1;
+    const int n_tiles = q_last / PFA_KT + 1;
+    constexpr int ROW_BYTES = BITS == 4 ? 64 : BITS == 2 ? 32 : 256;  // bytes of one head in a cache row
+    const size_t row_stride = (size_t)p.Hkv * ROW_BYTES;
+
+    // ---- byte (4-bit) or nibble (2-bit) -> two fp16 centroids, one column per lane: no bank conflicts ----
+    if (BITS == 4) {
+        for (int i = tid; i < 256 * 32; i += PFA_THREADS) {
+            const int e = i >> 5;
+            reinterpret_cast<uint32_t*>(pfa_smem + PfaSmem::LUT)[i] = pack_half2(kCent4[e & 15], kCent4[e >> 4]);
+        }
+    } else if (BITS == 2) {
+        for (int i = tid; i < 16 * 32; i += PFA_THREADS) {
+            const int e = i >> 5;
+            reinterpret_cast<uint32_t*>(pfa_smem + PfaSmem::LUT)[i] = pack_half2(kCent2[e & 3], kCent2[e >> 2]);
+        }
+    }
+    const uint32_t lut = sb + PfaSmem::LUT + 4u * (uint32_t)lane;
+
+    // ---- this warp's 16 query rows as A fragments: rows gl and gl + 8, 8 steps of 16 coordinates ----
+    uint32_t qa[8][4];
+    {
+        const int r_lo = 16 * warp + gl, r_hi = r_lo + 8;
+        const int tok_lo = q0 + (r_lo >> gs), tok_hi = q0 + (r_hi >> gs);
+        const __half* ql = p.q + (size_t)tok_lo * p.q_tok_stride + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
+        const __half* qh = p.q + (size_t)tok_hi * p.q_tok_stride + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = tok_lo < p.T ? __ldg(reinterpret_cast<const uint32_t*>(ql + 16 * ks)) : 0u;
+            qa[ks][1] = tok_hi < p.T ? __ldg(reinterpret_cast<const uint32_t*>(qh + 16 * ks)) : 0u;
+            qa[ks][2] = tok_lo < p.T ? __ldg(reinterpret_cast<const uint32_t*>(ql + 16 * ks + 8)) : 0u;
+            qa[ks][3] = tok_hi < p.T ? __ldg(reinterpret_cast<const uint32_t*>(qh + 16 * ks + 8)) : 0u;
+        }
+    }
+    const int tq_lo = q0 + ((16 * warp + gl) >> gs), tq_hi = q0 + ((16 * warp + gl + 8) >> gs);
+
+    // ---- tile fetch and dequantisation: thread (row tr of the tile, c) owns the 16-byte chunks c, c + 4, c + 8, c + 12
+    //      of the row's 256 fp16 bytes; the two rows of a quarter warp lie 4 apart, so their swizzled chunks never share
+    //      a bank group ----
+    const int tr = 8 * warp + ((lane >> 2) & 1) * 4 + (lane >> 3), c = lane & 3;
+    using Raw = typename std::conditional<BITS == 0, uint4, typename std::conditional<BITS == 4, uint32_t, unsigned short>::type>::type;
+    Raw rawk[4], rawv[4];
+    __half nrm_next = __float2half(1.0f);
+    auto fetch = [&](int j) {
+        int row = j * PFA_KT + tr;
+        row = min(row, p.rows - 1);
+        const uint8_t* kp = p.ck + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
+        const uint8_t* vp = p.cv + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // chunk c + 4 i: 16 fp16 bytes = 8 coordinates = 4 (4-bit) / 2 (2-bit) code bytes
+            const int ch = c + 4 * i;
+            rawk[i] = __ldg(reinterpret_cast<const Raw*>(kp + ch * (int)sizeof(Raw)));
+            rawv[i] = __ldg(reinterpret_cast<const Raw*>(vp + ch * (int)sizeof(Raw)));
+        }
+        if (BITS != 0 && tid < 2 * PFA_KT) {
+            const int r = min(j * PFA_KT + (tid & (PFA_KT - 1)), p.rows - 1);
+            nrm_next = (tid < PFA_KT ? p.kn : p.vn)[(size_t)r * p.Hkv + kvh];
+        }
+    };
+    auto dequant = [&](Raw w) -> uint4 {
+        if constexpr (BITS == 0) {
+            return w;
+        } else if constexpr (BITS == 4) {
+            uint4 o;
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((w & 0xffu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((w >> 8) & 0xffu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((w >> 16) & 0xffu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((w >> 24) << 7)));
+            return o;
+        } else {
+            const uint32_t u = w;
+            uint4 o;
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((u & 0xfu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((u >> 4) & 0xfu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((u >> 8) & 0xfu) << 7)));
+            asm("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((u >> 12) << 7)));
+            return o;
+        }
+    };
+    auto stage = [&](int b) {  // the fetched tile into buffer b
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t off = (uint32_t)b * 16384u + (uint32_t)tr * 256u + (uint32_t)(((c + 4 * i) ^ (tr & 7)) << 4);
+            const uint4 kq = dequant(rawk[i]), vq = dequant(rawv[i]);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::K + off), "r"(kq.x), "r"(kq.y), "r"(kq.z), "r"(kq.w) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::V + off), "r"(vq.x), "r"(vq.y), "r"(vq.z), "r"(vq.w) : "memory");
+        }
+        if (BITS != 0 && tid < 2 * PFA_KT)
+            reinterpret_cast<__half*>(pfa_smem + PfaSmem::NORMS)[b * 2 * PFA_KT + tid] = nrm_next;
+    };
+
+    float o[16][4];
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+    float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.0f, l_hi = 0.0f;
+
+    __syncthreads();  // the table is complete
+    fetch(0);
+    stage(0);
+    if (n_tiles > 1) fetch(1);
+    __syncthreads();
+
+    // ldmatrix lane roles: matrix mi = lane / 8, row lane % 8 of it
+    const int mi = lane >> 3, mrow = lane & 7;
+    const int k_tok = (mi >> 1) * 8 + mrow, k_chunk = mi & 1;   // K: matrices (tokens 0-7 | 8-15) x (chunk 0 | 1)
+    const int v_tok = (mi & 1) * 8 + mrow, v_chunk = mi >> 1;   // V: matrices (tokens 0-7 | 8-15) x (chunk 0 | 1), transposed
+
+    for (int j = 0; j < n_tiles; ++j) {
+        const int b = j & 1;
+        const uint32_t kt = sb + PfaSmem::K + (uint32_t)b * 16384u, vt = sb + PfaSmem::V + (uint32_t)b * 16384u;
+        // ---- S = Q . K^T: 8 blocks of 8 cache rows ----
+        float s[8][4];
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const int tok = 16 * np + k_tok, ch = 2 * ks + k_chunk;
+                uint32_t r[4];
+                ldmatrix_x4(r, kt + (uint32_t)tok * 256u + (uint32_t)((ch ^ (tok & 7)) << 4));
+                mma16816(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r[0], r[1]);
+                mma16816(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r[2], r[3]);
+            }
+        }
+        // ---- norms, causal limit, online softmax (columns 8 nb + 2 t4, + 1 of the tile; rows gl and gl + 8) ----
+        const bool diagonal = j * PFA_KT + PFA_KT - 1 > q0;
+        const uint32_t nk = sb + PfaSmem::NORMS + (uint32_t)b * 4u * PFA_KT + 4u * (uint32_t)t4;
+        float mx_lo = -1e30f, mx_hi = -1e30f;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+            float2 kn2 = make_float2(p.score_scale, p.score_scale);
+            if (BITS != 0) {
+                uint32_t w;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(nk + 16u * nb));
+                kn2 = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                kn2.x *= p.score_scale;
+                kn2.y *= p.score_scale;
+            }
+            s[nb][0] *= kn2.x; s[nb][1] *= kn2.y; s[nb][2] *= kn2.x; s[nb][3] *= kn2.y;
+            if (diagonal) {
+                const int tk = j * PFA_KT + 8 * nb + 2 * t4;
+                if (tk > tq_lo) s[nb][0] = -1e30f;
+                if (tk + 1 > tq_lo) s[nb][1] = -1e30f;
+                if (tk > tq_hi) s[nb][2] = -1e30f;
+                if (tk + 1 > tq_hi) s[nb][3] = -1e30f;
+            }
+            mx_lo = fmaxf(mx_lo, fmaxf(s[nb][0], s[nb][1]));
+            mx_hi = fmaxf(mx_hi, fmaxf(s[nb][2], s[nb][3]));
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float cr_lo = ex2_approx(m_lo - mn_lo), cr_hi = ex2_approx(m_hi - mn_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        l_lo *= cr_lo;
+        l_hi *= cr_hi;
+#pragma unroll
+        for (int nb = 0; nb < 16; ++nb) {
+            o[nb][0] *= cr_lo; o[nb][1] *= cr_lo; o[nb][2] *= cr_hi; o[nb][3] *= cr_hi;
+        }
+        uint32_t pa[4][4];  // P (times the V norm) as A fragments: step kk covers the tile's rows 16 kk .. 16 kk + 15
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+            // a masked column weighs exactly 0 (its score is -1e30; a row that has seen no live column yet has m = -1e30,
+            // but every row's first tile holds cache row 0, which is live)
+            const float p0 = s[nb][0] <= -1e30f ? 0.0f : ex2_approx(s[nb][0] - m_lo);
+            const float p1 = s[nb][1] <= -1e30f ? 0.0f : ex2_approx(s[nb][1] - m_lo);
+            const float p2 = s[nb][2] <= -1e30f ? 0.0f : ex2_approx(s[nb][2] - m_hi);
+            const float p3 = s[nb][3] <= -1e30f ? 0.0f : ex2_approx(s[nb][3] - m_hi);
+            l_lo += p0 + p1;
+            l_hi += p2 + p3;
+            float2 vn2 = make_float2(1.0f, 1.0f);
+            if (BITS != 0) {
+                uint32_t w;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(nk + 2u * PFA_KT + 16u * nb));
+                vn2 = __half22float2(*reinterpret_cast<const __half2*>(&w));
+            }
+            // (rows past the prompt can hold anything, a norm that is not a number included: select, do not multiply)
+            pa[nb >> 1][(nb & 1) * 2] = pack_half2(p0 == 0.0f ? 0.0f : p0 * vn2.x, p1 == 0.0f ? 0.0f : p1 * vn2.y);
+            pa[nb >> 1][(nb & 1) * 2 + 1] = pack_half2(p2 == 0.0f ? 0.0f : p2 * vn2.x, p3 == 0.0f ? 0.0f : p3 * vn2.y);
+        }
+        // ---- O += P . V: 4 steps of 16 cache rows x 16 blocks of 8 coordinates ----
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                const int tok = 16 * kk + v_tok, ch = 2 * np + v_chunk;
+                uint32_t r[4];
+                ldmatrix_x4_trans(r, vt + (uint32_t)tok * 256u + (uint32_t)((ch ^ (tok & 7)) << 4));
+                mma16816(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], r[0], r[1]);
+                mma16816(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], r[2], r[3]);
+            }
+        }
+        // ---- the next tile into the other buffer (all warps left it before the previous barrier), the one after it
+        //      on its way into registers ----
+        if (j + 1 < n_tiles) {
+            stage(b ^ 1);
+            if (j + 2 < n_tiles) fetch(j + 2);
+        }
+        __syncthreads();
+    }
+
+    // ---- row sums over the four lanes of a row; results out ----
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = 16 * warp + gl + 8 * half;
+        const int tok = q0 + (r >> gs), head = kvh * GRP + (r & (GRP - 1));
+        if (tok >= p.T) continue;
+        const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
+        if (BITS == 0) {
+            const float inv = 1.0f / (l + 1e-8f);
+            __half* dst = p.out + (size_t)tok * p.q_dim + (size_t)head * HEAD_DIM + 2 * t4;
+#pragma unroll
+            for (int nb = 0; nb < 16; ++nb)
+                *reinterpret_cast<__half2*>(dst + 8 * nb) = __floats2half2_rn(o[nb][2 * half] * inv, o[nb][2 * half + 1] * inv);
+        } else {
+            float* dst = p.partials + ((size_t)2 * tok * p.H + head) * PART_STRIDE;
+#pragma unroll
+            for (int nb = 0; nb < 16; ++nb)
+                *reinterpret_cast<float2*>(dst + 8 * nb + 2 * t4) = make_float2(o[nb][2 * half], o[nb][2 * half + 1]);
+            if (t4 == 0) *reinterpret_cast<float2*>(dst + HEAD_DIM) = make_float2(m, l);
+        }
+    }
+}
+
+// Tile table of a launch in which every "sequence" (query token) has exactly one part: table[g] = g, workers = tiles = T.
+__global__ void one_part_table_kernel(int* table, int T) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= T) table[i] = i;
+    if (i == 0) {
+        table[T + 1] = T;
+        table[T + 2] = T;
+    }
+}
+
+}  // namespace tq
