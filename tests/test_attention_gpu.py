@@ -277,3 +277,29 @@ def test_head_layouts_outside_the_streaming_kernel(bits, H, Hkv):
         tqo.append_tokens(cq, cn, ks[gi], R, np.arange(n, dtype=np.int32), n, Hkv, D, bits)
         n_diff += int((hp.unpack_codes(cq, bits) != hp.unpack_codes(gk[sl], bits)).sum())
     assert n_diff <= 4, f"{n_diff} K coordinates differ from the oracle's append"
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("H,Hkv", [(16, 8), (32, 8), (8, 8), (32, 4)])
+def test_prefill_attention_with_query_tiles_at_ragged_sizes(bits, H, Hkv):
+    """launch_turbo_gqa_prefill_attention through the kernel that holds the query tokens in the M dimension: T and the
+    slot size are no multiples of the 64-row cache tile or of the query block, and the cache rows past the prompt hold
+    garbage (codes 0xff, norms that are not numbers) which no result may depend on.  Against the oracle
+    (engine/kernels.cu:1874-1960 restated)."""
+    rng = np.random.default_rng(300 + bits + H)
+    R, _ = tqo.rotation()
+    D, T, msl = 128, 333, 350
+    ck, kn, cv, vn = hp.build_cache_oracle(rng, 1, [T], msl, Hkv, D, bits, R)
+    ck[T:] = 0xFF
+    cv[T:] = 0xFF
+    kn.view(np.uint16)[T:] = 0x7E00
+    vn.view(np.uint16)[T:] = 0x7E00
+    q = rng.standard_normal((T, H * D), dtype=np.float32).astype(np.float16)
+    ref, _ = tqo.prefill_attention(q, ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    got = gu.gpu_prefill_attention(q, ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    assert np.isfinite(got.astype(np.float32)).all()
+    w, r = hp.assert_attention_close(got, ref, H, D, f"prefill attention tq{bits} H={H} Hkv={Hkv}")
+    print(f"prefill attention tq{bits} H={H} Hkv={Hkv} T={T}: max-abs {w:.2e}, rel {r:.2e}")
+    # a short prompt: fewer query tokens than one block, one cache tile
+    got_s = gu.gpu_prefill_attention(q[:5], ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    hp.assert_attention_close(got_s, ref[:5], H, D, "prefill attention, 5 tokens")

@@ -136,3 +136,23 @@ def test_fp16_prefill_attention_against_oracle_and_reference_kernel():
                                           msl, H, Hkv, D, H * D, Hkv * D, torch.cuda.current_stream().cuda_stream)
         w2, _ = hp.assert_attention_close(got, gu.host(out_ref), H, D, "fp16 prefill attention vs the reference kernel")
         print(f"fp16 prefill attention: max-abs {w2:.2e} against the reference's own kernel")
+
+
+@pytest.mark.parametrize("H,Hkv,T,msl", [(16, 8, 333, 350), (32, 8, 200, 200), (8, 8, 130, 192), (32, 4, 97, 100)])
+def test_fp16_prefill_attention_with_query_tiles(H, Hkv, T, msl):
+    """launch_gqa_prefill_attention through the kernel with the query tokens in the M dimension, at sizes that are no
+    multiples of its tiles; rows past the prompt hold values that are not numbers."""
+    rng = np.random.default_rng(500 + H + T)
+    D = 128
+    k = rng.standard_normal((msl, Hkv * D), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((msl, Hkv * D), dtype=np.float32).astype(np.float16)
+    k.view(np.uint16)[T:] = 0x7E00
+    v.view(np.uint16)[T:] = 0x7E00
+    q = rng.standard_normal((T, H * D), dtype=np.float32).astype(np.float16)
+    out = torch.zeros(T, H * D, dtype=torch.float16, device="cuda")
+    ops.launch_gqa_prefill_attention(out, gu.dev(q), gu.dev(k), gu.dev(v), None, T, msl, H, Hkv, D, H * D, Hkv * D)
+    got = gu.host(out)
+    assert np.isfinite(got.astype(np.float32)).all()
+    ref = np.stack([tqo.fp16_attention_single(q[t], k, v, t, msl, H, Hkv, D)[0] for t in range(T)])
+    worst, rel = hp.assert_attention_close(got, ref, H, D, f"fp16 prefill attention H={H} Hkv={Hkv} T={T}")
+    print(f"fp16 prefill attention H={H} Hkv={Hkv} T={T}: max-abs {worst:.2e}, rel {rel:.2e}")

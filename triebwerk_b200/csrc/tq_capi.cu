@@ -554,6 +554,63 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
         g_compat_status = r;
         return;
     }
+    static const bool dedicated = !(getenv("TQ_PREFILL_ATTN") && atoi(getenv("TQ_PREFILL_ATTN")) == 0);
+    if (r == TQ_OK && dedicated && prefill_attn_shape(num_heads, num_kv_heads)) {
+        // the kernel with the query tokens in the M dimension: rotate the queries, attend, merge (normalise and R^T)
+        const size_t qrot_b = align_up((size_t)T * num_heads * HEAD_DIM * sizeof(__half), 256);
+        const size_t part_b = align_up((size_t)T * num_heads * PART_STRIDE * sizeof(float), 256);
+        const size_t table_b = align_up((size_t)(T + 3) * sizeof(int), 256);
+        const size_t rot_b = (size_t)HEAD_DIM * HEAD_DIM * sizeof(__half);
+        void* pws = nullptr;
+        r = compat_workspace(qrot_b + part_b + table_b + rot_b, &pws, cs(s));
+        if (r == TQ_OK) {
+            __half* qrot = (__half*)pws;
+            float* parts = (float*)((char*)pws + qrot_b);
+            int* table = (int*)((char*)pws + qrot_b + part_b);
+            __half* rot_t = (__half*)((char*)pws + qrot_b + part_b + table_b);
+            QRotParams qp{};
+            qp.q = (const __half*)q;
+            qp.rotation = (const __half*)rotation;
+            qp.q_rot = qrot;
+            qp.n_vec = (long long)T * num_heads;
+            qp.H = num_heads;
+            qp.q_dim = q_dim;
+            const long long qgroups = (qp.n_vec + 15) / 16;
+            rotate_queries_kernel<false><<<(unsigned)std::min<long long>(qgroups, 4ll * device_props().sm_count), QROT_WARPS * 32, 0, cs(s)>>>(qp);
+            one_part_table_kernel<<<(T + 1 + 255) / 256, 256, 0, cs(s)>>>(table, T);
+            transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(rot_t, (const __half*)rotation);
+            r = cuda_status(cudaGetLastError());
+            PrefillAttnParams ap{};
+            ap.q = qrot;
+            ap.q_tok_stride = (long long)num_heads * HEAD_DIM;
+            ap.ck = ck_q;
+            ap.cv = cv_q;
+            ap.kn = (const __half*)k_norms;
+            ap.vn = (const __half*)v_norms;
+            ap.partials = parts;
+            ap.q_dim = q_dim;
+            ap.T = T;
+            ap.rows = msl;
+            ap.H = num_heads;
+            ap.Hkv = num_kv_heads;
+            ap.score_scale = 1.0f;
+            if (r == TQ_OK) r = launch_prefill_attention(bits, ap, cs(s));
+            if (r == TQ_OK) {
+                MergeParams mp{};
+                mp.partials = parts;
+                mp.table = table;
+                mp.rotation_t = rot_t;
+                mp.out = (__half*)out;
+                mp.G = T;
+                mp.H = num_heads;
+                mp.q_dim = q_dim;
+                merge_partials_kernel<<<dim3((unsigned)T, 1), MERGE_WARPS * 32, 0, cs(s)>>>(mp);
+                r = cuda_status(cudaGetLastError());
+            }
+        }
+        g_compat_status = r;
+        return;
+    }
     void* ws = nullptr;
     size_t need = 0;
     int qg = 1, groups = T, vheads = num_heads;
@@ -649,6 +706,23 @@ void launch_gqa_prefill_attention(void* out, const void* q, const void* ck, cons
     (void)as;
     int r = check_shape(T, num_heads, num_kv_heads, head_dim, q_dim, kv_dim, 0, false);
     if (r == TQ_OK && T > msl) r = TQ_ERR_CAPACITY;
+    static const bool dedicated = !(getenv("TQ_PREFILL_ATTN") && atoi(getenv("TQ_PREFILL_ATTN")) == 0);
+    if (r == TQ_OK && dedicated && prefill_attn_shape(num_heads, num_kv_heads) && kv_dim == num_kv_heads * HEAD_DIM) {
+        PrefillAttnParams ap{};
+        ap.q = (const __half*)q;
+        ap.q_tok_stride = q_dim;
+        ap.ck = (const uint8_t*)ck;
+        ap.cv = (const uint8_t*)cv;
+        ap.out = (__half*)out;
+        ap.q_dim = q_dim;
+        ap.T = T;
+        ap.rows = msl;
+        ap.H = num_heads;
+        ap.Hkv = num_kv_heads;
+        ap.score_scale = 0.12751743074602467f;  // log2(e) / sqrt(128)
+        g_compat_status = launch_prefill_attention(0, ap, cs(s));
+        return;
+    }
     void* ws = nullptr;
     size_t attn_bytes = 0, need = 0;
     if (r == TQ_OK) {

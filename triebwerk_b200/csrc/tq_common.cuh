@@ -146,6 +146,18 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 }
 
 // D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
+// Four 8x8 fp16 matrices from shared memory as mma fragments: lane l supplies the address of row l % 8 of matrix l / 8;
+// the plain form hands lane l the elements (row l / 4, columns 2 (l % 4), + 1) of each matrix, the transposed form the
+// elements (rows 2 (l % 4), + 1, column l / 4).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
     asm volatile(

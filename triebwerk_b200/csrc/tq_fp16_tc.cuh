@@ -28,15 +28,6 @@ constexpr uint32_t FP16TC_ARRAY_BYTES = FP16TC_BLOCK * 256u;    // one array's r
 constexpr uint32_t FP16TC_STAGE_BYTES = 2u * FP16TC_ARRAY_BYTES;
 constexpr size_t FP16TC_SMEM = (size_t)FP16TC_WARPS * FP16TC_STAGES * FP16TC_STAGE_BYTES + 1024 + 256;  // + alignment + barriers
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-
 // GRP = query heads per KV head (1, 2, 4 or 8).  tmK / tmV: the fp16 arrays viewed as bytes, dimensions (128 B, rows,
 // 128-byte blocks of a row), box (128 B, 16 rows, 2 blocks = one head's 256 B).
 template <int GRP>

@@ -23,6 +23,7 @@
 #include "tq_fp16_tc.cuh"
 #include "tq_qrot.cuh"
 #include "tq_generic.cuh"
+#include "tq_prefill_attn.cuh"
 
 namespace tq {
 
@@ -343,6 +344,37 @@ inline int launch_fp16_tc_attention(const CUtensorMap& tmK, const CUtensorMap& t
         case 8: return launch_fp16_tc_t<8>(tmK, tmV, p, s);
         default: return TQ_ERR_UNSUPPORTED;
     }
+}
+
+// Causal prefill attention with the query tokens in the M dimension (tq_prefill_attn.cuh); bits 0 = fp16 cache.
+inline bool prefill_attn_shape(int H, int Hkv) {
+    const int grp = Hkv > 0 ? H / Hkv : 0;
+    return Hkv > 0 && Hkv <= 65535 && H == grp * Hkv && (grp == 1 || grp == 2 || grp == 4 || grp == 8 || grp == 16);
+}
+inline int launch_prefill_attention(int bits, PrefillAttnParams p, cudaStream_t s) {
+    const int grp = p.H / p.Hkv;
+    p.grp_shift = 0;
+    while ((1 << p.grp_shift) < grp) ++p.grp_shift;
+    const int qt = PFA_ROWS >> p.grp_shift;
+    dim3 grid((unsigned)((p.T + qt - 1) / qt), (unsigned)p.Hkv);
+    if (p.T <= 0) return TQ_OK;
+    int ar;
+    switch (bits) {
+        case 4:
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_kernel<4>, PfaSmem::BYTES)) != TQ_OK) return ar;
+            prefill_attention_kernel<4><<<grid, PFA_THREADS, PfaSmem::BYTES, s>>>(p);
+            break;
+        case 2:
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_kernel<2>, PfaSmem::BYTES)) != TQ_OK) return ar;
+            prefill_attention_kernel<2><<<grid, PFA_THREADS, PfaSmem::BYTES, s>>>(p);
+            break;
+        case 0:
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_kernel<0>, PfaSmem::BYTES)) != TQ_OK) return ar;
+            prefill_attention_kernel<0><<<grid, PFA_THREADS, PfaSmem::BYTES, s>>>(p);
+            break;
+        default: return TQ_ERR_UNSUPPORTED;
+    }
+    return cuda_status(cudaGetLastError());
 }
 
 inline int launch_fp16_attention(const Fp16AttnParams& p_in, cudaStream_t s) {

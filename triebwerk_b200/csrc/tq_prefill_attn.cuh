@@ -42,7 +42,7 @@ struct PrefillAttnParams {
     const uint8_t* cv;
     const __half* kn;         // [rows][Hkv] (packed forms)
     const __half* vn;
-    float* partials;          // packed forms: token t, head h -> partials[(2 t * H + h) * PART_STRIDE]: acc[128], m, l
+    float* partials;          // packed forms: token t, head h -> partials[(t * H + h) * PART_STRIDE]: acc[128], m, l
     __half* out;              // fp16 form: [T][q_dim]
     int q_dim;
     int T;                    // query tokens = cache rows in use
@@ -125,26 +125,30 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
             return w;
         } else if constexpr (BITS == 4) {
             uint4 o;
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((w & 0xffu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((w >> 8) & 0xffu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((w >> 16) & 0xffu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((w >> 24) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((w & 0xffu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((w >> 8) & 0xffu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((w >> 16) & 0xffu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((w >> 24) << 7)));
             return o;
         } else {
             const uint32_t u = w;
             uint4 o;
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((u & 0xfu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((u >> 4) & 0xfu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((u >> 8) & 0xfu) << 7)));
-            asm("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((u >> 12) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.x) : "r"(lut + ((u & 0xfu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.y) : "r"(lut + (((u >> 4) & 0xfu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.z) : "r"(lut + (((u >> 8) & 0xfu) << 7)));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o.w) : "r"(lut + ((u >> 12) << 7)));
             return o;
         }
     };
-    auto stage = [&](int b) {  // the fetched tile into buffer b
+    auto stage = [&](int b, int j) {  // the fetched tile j into buffer b
+        // fp16 rows past the prompt may hold anything (a masked weight of 0 times a value that is not a number would
+        // still poison the sums): they enter as zeros.  Packed rows dequantise to finite centroids whatever they hold.
+        const bool blank = BITS == 0 && j * PFA_KT + tr >= p.T;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t off = (uint32_t)b * 16384u + (uint32_t)tr * 256u + (uint32_t)(((c + 4 * i) ^ (tr & 7)) << 4);
-            const uint4 kq = dequant(rawk[i]), vq = dequant(rawv[i]);
+            uint4 kq = dequant(rawk[i]), vq = dequant(rawv[i]);
+            if (blank) kq = vq = make_uint4(0u, 0u, 0u, 0u);
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::K + off), "r"(kq.x), "r"(kq.y), "r"(kq.z), "r"(kq.w) : "memory");
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::V + off), "r"(vq.x), "r"(vq.y), "r"(vq.z), "r"(vq.w) : "memory");
         }
@@ -159,7 +163,7 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
 
     __syncthreads();  // the table is complete
     fetch(0);
-    stage(0);
+    stage(0, 0);
     if (n_tiles > 1) fetch(1);
     __syncthreads();
 
@@ -261,7 +265,7 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
         // ---- the next tile into the other buffer (all warps left it before the previous barrier), the one after it
         //      on its way into registers ----
         if (j + 1 < n_tiles) {
-            stage(b ^ 1);
+            stage(b ^ 1, j + 1);
             if (j + 2 < n_tiles) fetch(j + 2);
         }
         __syncthreads();
@@ -285,7 +289,7 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
             for (int nb = 0; nb < 16; ++nb)
                 *reinterpret_cast<__half2*>(dst + 8 * nb) = __floats2half2_rn(o[nb][2 * half] * inv, o[nb][2 * half + 1] * inv);
         } else {
-            float* dst = p.partials + ((size_t)2 * tok * p.H + head) * PART_STRIDE;
+            float* dst = p.partials + ((size_t)tok * p.H + head) * PART_STRIDE;
 #pragma unroll
             for (int nb = 0; nb < 16; ++nb)
                 *reinterpret_cast<float2*>(dst + 8 * nb + 2 * t4) = make_float2(o[nb][2 * half], o[nb][2 * half + 1]);
@@ -294,13 +298,14 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     }
 }
 
-// Tile table of a launch in which every "sequence" (query token) has exactly one part: table[g] = g, workers = tiles = T.
+// Tile table that makes merge_partials_kernel treat query token g as a sequence with ONE part stored at slot g:
+// table[g] = g, one worker, more tiles than tokens (every token's first and last tile then belong to worker 0).
 __global__ void one_part_table_kernel(int* table, int T) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i <= T) table[i] = i;
     if (i == 0) {
-        table[T + 1] = T;
-        table[T + 2] = T;
+        table[T + 1] = 1;
+        table[T + 2] = T + 1;
     }
 }
 
