@@ -40,14 +40,15 @@ struct TcSmem {
     static constexpr uint32_t A_HI = 0;                  // 2 K-regions x [128 rows][128 B]
     static constexpr uint32_t A_LO = 32768;
     static constexpr uint32_t B_R = 65536;               // R: rows = output coordinate d, K-major
-    static constexpr uint32_t STAGE = 98304;             // packed codes of the tile, 64 B (4-bit) per vector
-    static constexpr uint32_t ROWS = STAGE + 8192;       // long long[128] destination row per vector (-1: none)
-    static constexpr uint32_t INV = ROWS + 1024;         // float[128] 1/norm per vector
+    static constexpr uint32_t STAGE = A_HI;              // packed codes of the tile, 64 B (4-bit) per vector: written after
+                                                         // the MMAs have consumed the operand tile it overlays
+    static constexpr uint32_t DST = 98304;               // long long[128] byte offset of each vector's codes in the cache (-1: none)
+    static constexpr uint32_t INV = DST + 1024;          // float[128] 1/norm per vector
     static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
-    static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint2[512] bucket table: {code | 0x80 + bound index, bound}
-    static constexpr uint32_t CTRL = GRID + 4096;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
-    static constexpr uint32_t LAYERS = CTRL + 16;        // int[128] layer of each vector (decode-step form)
-    static constexpr uint32_t BYTES = LAYERS + 512;
+    static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint32[2048] bucket table, see the kernel
+    static constexpr uint32_t CTRL = GRID + 8192;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
+    static constexpr uint32_t ABN = CTRL + 16;           // uint8[128]: the vector holds an infinity or a NaN
+    static constexpr uint32_t BYTES = ABN + 128;
 };
 constexpr size_t TC_DYN_SMEM = TcSmem::BYTES + 1024;  // + alignment slack
 
@@ -156,11 +157,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t bar = base + TcSmem::CTRL;
     volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
-    long long* rows_s = reinterpret_cast<long long*>(gbase + TcSmem::ROWS);
+    long long* dst_s = reinterpret_cast<long long*>(gbase + TcSmem::DST);
     float* inv_s = reinterpret_cast<float*>(gbase + TcSmem::INV);
-    int* layer_s = reinterpret_cast<int*>(gbase + TcSmem::LAYERS);
+    uint8_t* abn_s = gbase + TcSmem::ABN;
     uint32_t* list_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::LIST);
-    uint2* grid_s = reinterpret_cast<uint2*>(gbase + TcSmem::GRID);
+    uint32_t* grid_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::GRID);
 
     const int bits = p.bits;
     const int nb = bits == 4 ? 15 : 3;
@@ -181,19 +182,24 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM) + j);
         *reinterpret_cast<uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base)) = u;
     }
-    for (int i = tid; i < 512; i += TC_THREADS) {
-        // bucket i = values that round to i - 256 when multiplied by 1024, i.e. [(i - 256.5) / 1024, (i - 255.5) / 1024]
-        // (the first and last bucket extend to infinity).  Entry {base, bound}: code = base + (value >= bound), where
-        // `bound` is the one decision bound within the margin of the bucket, or +inf (then base is the code itself).
-        const float lo = ((float)(i - 256) - 0.5f) * (1.0f / 1024.0f), hi = lo + (1.0f / 1024.0f);
+    for (int i = tid; i < 2048; i += TC_THREADS) {
+        // Bucket table over the rotated coordinate x.  The epilogue forms k = rne(2048 x) in the low mantissa bits of
+        // fma(x, 512, 1.5 * 2^21) and takes bucket k >> 2 (modulo 2048): bucket n holds x in [(4 n - 0.5) / 2048,
+        // (4 n + 3.5) / 2048], |x| < 2.  An entry is ONE float: the decision bound that lies inside the bucket (widened by
+        // four margins) with its five lowest mantissa bits replaced by the code a value at or above the bound gets --
+        // the code is then entry_code - (x < bound) -- or, when no bound is near the bucket, 0x7f000000 (1.7e38: every x
+        // is below it) carrying the bucket's code + 1.  The replaced bits move the bound by less than 5e-7; the near-bound
+        // test uses a margin wider by that much, and only coordinates outside it keep the code found here.
+        const int n = i < 1024 ? i : i - 2048;
+        const float lo = ((float)(4 * n) - 0.5f) * (1.0f / 2048.0f), hi = lo + (1.0f / 512.0f);
         int code = 0, amb = -1;
-        float ambv = __int_as_float(0x7f800000);
+        float ambv = 0.0f;
         for (int b = 0; b < nb; ++b) {
             const float bv = bits == 4 ? kBnd4[b] : kBnd2[b];
             if (bv <= lo) ++code;
             if (bv >= lo - 4.0f * TC_MARGIN && bv <= hi + 4.0f * TC_MARGIN) { amb = b; ambv = bv; }
         }
-        grid_s[i] = make_uint2((uint32_t)(amb >= 0 ? amb : code), __float_as_uint(ambv));
+        grid_s[i] = amb >= 0 ? ((__float_as_uint(ambv) & ~31u) | (uint32_t)(amb + 1)) : (0x7f000000u | (uint32_t)(code + 1));
     }
     fence_proxy_async_smem();
     tc_fence_before();
@@ -208,6 +214,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
     const int total_tiles = tiles_per_kind * n_kinds;
     uint32_t phase = 0;
     bool dead = false;
+    // Vector -> (token, head) and token -> (sequence, position) without a division per vector: one division per tile for
+    // its first vector, then a multiplication by a reciprocal (exact for the small offsets inside a tile) and, for
+    // prompts longer than a tile, one conditional step into the next sequence.
+    const bool fast_head = p.Hkv <= 256;
+    const uint32_t hkv_magic = ((1u << 20) + (uint32_t)p.Hkv - 1u) / (uint32_t)p.Hkv;
+    const bool fast_tok = p.T > TC_TILE + 1;
+    const int cpv_shift = bits == 4 ? 2 : 1;  // 16-byte chunks per packed vector, as a shift
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
@@ -216,6 +229,29 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         uint8_t* cq = kind == 0 ? p.ck : p.cv;
         __half* cn = kind == 0 ? p.kn : p.vn;
         if (tid == 0) ctrl[3] = 0;
+        const int tok0 = vec0 / p.Hkv, head0 = vec0 - tok0 * p.Hkv;
+        const int seq0 = tok0 / p.T, t0 = tok0 - seq0 * p.T;
+        auto split_vec = [&](int v, int& tok, int& head) {  // vector vec0 + v of the tile
+            if (fast_head) {
+                const uint32_t x = (uint32_t)(head0 + v), dq = (x * hkv_magic) >> 20;
+                tok = tok0 + (int)dq;
+                head = (int)(x - dq * (uint32_t)p.Hkv);
+            } else {
+                tok = (vec0 + v) / p.Hkv;
+                head = (vec0 + v) - tok * p.Hkv;
+            }
+        };
+        auto split_tok = [&](int tok, int& seq, int& t) {
+            if (fast_tok) {
+                const int tt = t0 + (tok - tok0);
+                const bool wrap = tt >= p.T;
+                seq = seq0 + (wrap ? 1 : 0);
+                t = tt - (wrap ? p.T : 0);
+            } else {
+                seq = tok / p.T;
+                t = tok - seq * p.T;
+            }
+        };
 
         // ---- 1. load, sum of squares in the reference's order, normalise, split, write the A operand ----
         constexpr int PASSES = 4 * TC_TILE / TC_THREADS, VPP = TC_THREADS / 4;  // passes per tile, vectors per pass
@@ -224,7 +260,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         for (int pass = 0; pass < PASSES; ++pass) {  // every load of the tile goes out before the arithmetic starts
             const int vid = vec0 + pass * VPP + (tid >> 2);
             const bool live = vid < vec_per_kind;
-            const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;  // tok = sequence * T + t
+            int tok = 0, head = 0;  // tok = sequence * T + t
+            if (live) split_vec(pass * VPP + (tid >> 2), tok, head);
             const uint4* src = reinterpret_cast<const uint4*>(src_buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * (tid & 3));
 #pragma unroll
             for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
@@ -235,7 +272,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 const int nkind = (p.k_buf && ntile < tiles_per_kind) ? 0 : 1;
                 const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + (tid >> 1);
                 if (nvid < vec_per_kind) {  // one 128-byte line per thread
-                    const int ntok = nvid / p.Hkv, nhead = nvid - ntok * p.Hkv;
+                    const int ntok = nvid / p.Hkv, nhead = nvid - ntok * p.Hkv;  // (one division per thread and tile)
                     const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM + 64 * (tid & 1);
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
                 }
@@ -246,8 +283,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             const int v = pass * VPP + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
             const int vid = vec0 + v;
             const bool live = vid < vec_per_kind;
-            const int tok = live ? vid / p.Hkv : 0, head = live ? vid - tok * p.Hkv : 0;
-            const int seq = tok / p.T, t = tok - seq * p.T;
+            int tok = 0, head = 0, seq = 0, t = 0;
+            if (live) {
+                split_vec(v, tok, head);
+                split_tok(tok, seq, t);
+            }
             const uint4 (&raw)[4] = raw_all[pass];
             float val[32], sq[32];
 #pragma unroll
@@ -356,6 +396,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             if (c == 0) {
                 long long row = -1;
                 int layer = 0;
+                abn_s[v] = tt < 3.0e38f ? 0 : 1;  // an infinity or a NaN among the inputs: every coordinate is a NaN
                 if (live) {
                     int sq = seq, cap = p.capacity_rows;
                     if (p.step_G > 0) {
@@ -371,8 +412,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                         atomicMax(p.status, ST_BAD_POSITION);
                     }
                 }
-                rows_s[v] = row;
-                layer_s[v] = layer;
+                dst_s[v] = row < 0 ? -1ll : (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
                 inv_s[v] = inv;
             }
 #pragma unroll
@@ -419,11 +459,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 
         // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
         //         w + 4 share those vectors and take 64 of the 128 coordinates (two blocks of 32 columns) each ----
-        const int nan_code = bits == 4 ? 15 : 0;  // what the reference's comparisons make of a NaN
         const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
         const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
         uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
         if (!dead) {
+            const bool abn = abn_s[ev] != 0;
 #pragma unroll 1
             for (int cc = cc0; cc < cc0 + 2; ++cc) {
                 uint32_t hi_r[32], lo_r[32];
@@ -433,21 +473,30 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 tmem_ld_wait();
                 uint32_t words[4] = {0u, 0u, 0u, 0u};
                 uint32_t near_mask = 0u;  // queued after the loop: no store may sit between the table look-ups
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                // coordinates in descending order: codes and near-bound flags are shifted in from the right
+                auto one = [&](int i, uint32_t& word, int width) {
                     const float dval = fmaf(__uint_as_float(lo_r[i]), 1.0f / 4096.0f, __uint_as_float(hi_r[i]));
-                    // branch-free: round(value * 1024) by the 1.5 * 2^23 trick, clamped to the table (values beyond
-                    // the table are beyond every bound; huge values and infinities land on the right end as well)
-                    const float tt = fmaf(dval, 1024.0f, 12582912.0f);
-                    int idx = __float_as_int(tt) - 0x4B400000 + 256;
-                    idx = max(0, min(511, idx));
-                    const uint2 e = grid_s[idx];
-                    const float bv = __uint_as_float(e.y);
-                    int code = (int)e.x + (dval >= bv ? 1 : 0);
-                    code = (dval != dval) ? nan_code : code;
-                    near_mask |= (fabsf(dval - bv) < TC_MARGIN ? 1u : 0u) << i;
-                    if (bits == 4) words[i >> 3] |= (uint32_t)code << (4 * (i & 7));
-                    else words[i >> 4] |= (uint32_t)code << (2 * (i & 15));
+                    const uint32_t kb = __float_as_uint(fmaf(dval, 512.0f, 3145728.0f));  // k = rne(2048 x) in the low bits
+                    const uint32_t e = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(grid_s) + (kb & 0x1ffcu));
+                    const float d = dval - __uint_as_float(e);
+                    const uint32_t code = (e & 31u) - (__float_as_uint(d) >> 31);
+                    word = (word << width) + code;
+                    near_mask = (near_mask << 1) + (fabsf(d) < TC_MARGIN + 1.0e-6f ? 1u : 0u);
+                };
+                if (bits == 4) {
+#pragma unroll
+                    for (int j = 3; j >= 0; --j)
+#pragma unroll
+                        for (int k = 7; k >= 0; --k) one(8 * j + k, words[j], 4);
+                } else {
+#pragma unroll
+                    for (int j = 1; j >= 0; --j)
+#pragma unroll
+                        for (int k = 15; k >= 0; --k) one(16 * j + k, words[j], 2);
+                }
+                if (abn) {  // what the reference's comparisons make of a NaN: the top code at 4 bits, code 0 at 2 bits
+                    words[0] = words[1] = words[2] = words[3] = bits == 4 ? 0xffffffffu : 0u;
+                    near_mask = 0u;
                 }
                 while (near_mask) {
                     const int i = __ffs(near_mask) - 1;
@@ -558,15 +607,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 
         // ---- 5. the packed tile leaves as 16-byte stores; the heads of a token are contiguous in the cache ----
         if (!dead) {
-            const int chunks_per_vec = bpv / 16;
-            for (int c16 = tid; c16 < TC_TILE * chunks_per_vec; c16 += TC_THREADS) {
-                const int v = c16 / chunks_per_vec, part = c16 - v * chunks_per_vec;
-                const long long row = rows_s[v];
-                if (row >= 0) {
-                    const int head = (vec0 + v) % p.Hkv;
+            for (int c16 = tid; c16 < (TC_TILE << cpv_shift); c16 += TC_THREADS) {
+                const int v = c16 >> cpv_shift, part = c16 & ((1 << cpv_shift) - 1);
+                const long long dst = dst_s[v];
+                if (dst >= 0) {
                     const uint4 u = *reinterpret_cast<const uint4*>(gbase + TcSmem::STAGE + (size_t)v * bpv + 16 * part);
-                    *reinterpret_cast<uint4*>(cq + (size_t)layer_s[v] * (size_t)p.code_layer_stride + (size_t)row * kvp +
-                                              (size_t)head * bpv + 16 * part) = u;
+                    *reinterpret_cast<uint4*>(cq + dst + 16 * part) = u;
                 }
             }
         }
