@@ -19,8 +19,9 @@ the same step looped for two seconds with the clocks sampled; `configs` = the ot
 measured in the same run (config 3 sharded over the N GPUs, config 4 at kv_bits 4 and 0).
 
 With N > 1 (torchrun) every rank owns its own 64 sequences (sequences are independent: weak scaling, no
-data-path collective) and the per-sequence outputs are all-gathered over NCCL inside the timed region, one group of
-layers at a time on a side stream (triebwerk_b200.sharded.LayerGroupGatherer); after the timed region a small ragged
+data-path collective) and the per-sequence outputs are gathered inside the timed region, one group of layers at a
+time on a side stream: by copy-engine copies into every peer's buffer (triebwerk_b200.sharded.PeerCopyGatherer), or over
+NCCL (LayerGroupGatherer; TQ_BENCH_GATHER=nccl); after the timed region a small ragged
 batch is run both unsharded and sharded + gathered on every rank and compared (`gather_check`).
 `--impl reference` times the CPU port with all host threads on rank 0 only.
 """
@@ -386,6 +387,18 @@ def decode_inputs(w, gen, scales):
     return q_dev, k_dev, v_dev, torch.empty_like(q_dev)
 
 
+def make_gatherer(plan, groups, row_shape):
+    """The exchange of the per-sequence outputs: copy-engine copies into the peers' buffers (TQ_BENCH_GATHER=peer, the
+    default) or NCCL all-gathers (=nccl, and whenever the peer buffers cannot be set up).  Returns (gatherer, kind)."""
+    from triebwerk_b200 import sharded
+    if os.environ.get("TQ_BENCH_GATHER", "peer") == "peer":
+        try:
+            return sharded.PeerCopyGatherer(plan, groups, row_shape), "peer_copy"
+        except RuntimeError as e:   # raised on every rank together (the set-up is collective)
+            sys.stderr.write(f"peer-copy exchange unavailable, using NCCL: {e}\n")
+    return sharded.LayerGroupGatherer(plan, groups), "nccl"
+
+
 def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
     """Builds the workload's cache on this rank and times its decode step.  full: also the host-buffer (e2e) path, the
     two-second sustained loop and the clocks; otherwise only the device-timed step (the extra configurations)."""
@@ -404,13 +417,13 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
     q_dev, k_dev, v_dev, out_dev = decode_inputs(w, gen, scales)
 
     # N > 1: the per-sequence outputs of all ranks are gathered (NCCL) one group of layers at a time on a side stream
-    # while the next group is computed; the groups are set by TQ_BENCH_GATHER_GROUPS (default 2: all layers but the
+    # while the next group is computed; the groups are set by TQ_BENCH_GATHER_GROUPS (default 3: two groups of layers, then the
     # last, then the last one, whose exchange is the only one left exposed)
-    gat, groups = None, [(0, NL)]
+    gat, groups, gat_kind = None, [(0, NL)], None
     if world > 1:
-        n_groups = int(os.environ.get("TQ_BENCH_GATHER_GROUPS", "2"))
+        n_groups = int(os.environ.get("TQ_BENCH_GATHER_GROUPS", "3"))
         groups = sharded.layer_groups(NL, n_groups)
-        gat = sharded.LayerGroupGatherer(sharded.contiguous_partition(world * G, world), groups)
+        gat, gat_kind = make_gatherer(sharded.contiguous_partition(world * G, world), groups, (q_dim,))
 
     def barrier():
         if world > 1:
@@ -483,6 +496,10 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
         res["sustained"] = sustained
     status = eng.status()
     assert status == 0, f"device status word is {status}: a kernel gave up on a bounded wait or saw a bad position"
+    res["gather"] = gat_kind
+    if gat_kind == "peer_copy":
+        assert gat.status() == 0, "a wait for the peers' copies ran out of time"
+        gat.close()
     del eng, q_dev, k_dev, v_dev, out_dev
     torch.cuda.empty_cache()
     return res
@@ -490,7 +507,7 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
 
 def gather_check(rank, world):
     """A small ragged batch run twice on every rank: all sequences on this GPU, and only this rank's shard
-    (sharded.shard_plan) with the outputs gathered over NCCL (sharded.LayerGroupGatherer).  Returns the largest
+    (sharded.shard_plan) with the outputs gathered (make_gatherer).  Returns the largest
     difference between the two results and whether the shard's cache bytes equal the unsharded run's."""
     import torch
     import torch.distributed as dist
@@ -536,19 +553,22 @@ def gather_check(rank, world):
     mine = plan[rank]
     out_loc, rows_loc = run(mine)
     groups = sharded.layer_groups(NL, 2)
-    gat = sharded.LayerGroupGatherer(plan, groups)
+    gat, kind = make_gatherer(plan, groups, (q_dim,))
     for gi, (l0, l1) in enumerate(groups):
-        gat.gather(gi, out_loc[l0:l1])
+        gat.gather(gi, out_loc[l0:l1].contiguous())
     gat.finish()
     torch.cuda.synchronize()
     got = gat.result()
+    if kind == "peer_copy":
+        assert gat.status() == 0, "a wait for the peers' copies ran out of time"
+        gat.close()
     diff = float((got.float() - out_all.float()).abs().max())
     same = all(torch.equal(a, b) for layer in range(NL) for j, i in enumerate(mine)
                for a, b in zip(rows_loc[layer][j], rows_all[layer][i]))
     t = torch.tensor([diff, 0.0 if same else 1.0], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return {"max_abs": float(t[0].item()), "cache_bytes_equal": bool(t[1].item() == 0.0), "sequences": n_seq,
-            "layers": NL, "shards": [len(p) for p in plan]}
+            "layers": NL, "shards": [len(p) for p in plan], "exchange": kind}
 
 
 def run_ours(args, w, rank, world, local_rank):
@@ -614,6 +634,11 @@ def run_ours(args, w, rank, world, local_rank):
         "clocks": res["clocks"],
         "sustained": res["sustained"],
     }
+    if world > 1:
+        line["exchange"] = {"kind": res.get("gather"), "layer_groups": len(sharded_groups(NL, world)),
+                            "ms_per_step_without_exchange": res["ms_compute"],
+                            "bytes_per_rank_and_step": int(NL * G * q_dim * 2),
+                            "note": "peer_copy: copy-engine copies into every peer's buffer + flag words; nccl: all_gather_into_tensor"}
     if extras:
         line["configs"] = extras
     if check is not None:
@@ -629,7 +654,7 @@ def run_ours(args, w, rank, world, local_rank):
 
 def sharded_groups(n_layers, world):
     from triebwerk_b200 import sharded
-    return [(0, n_layers)] if world == 1 else sharded.layer_groups(n_layers, int(os.environ.get("TQ_BENCH_GATHER_GROUPS", "2")))
+    return [(0, n_layers)] if world == 1 else sharded.layer_groups(n_layers, int(os.environ.get("TQ_BENCH_GATHER_GROUPS", "3")))
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel PER LAYER from the ncu captures summarised under

@@ -366,6 +366,29 @@ int tq_engine_prefill_shared(tq_engine* e, int layer, int first_seq, int n_seq, 
 int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_host, const void* v_host,
                                void* out_host, tq_stream_t s);
 
+/* ===================================================================================================================
+ * Peer exchange for sequence-sharded ranks (one process per GPU).  No counterpart in the reference, which runs on one
+ * GPU.  Every rank owns one buffer (made here with cudaMalloc so that a CUDA IPC handle names it); its peers open the
+ * handle, copy their attention outputs into their slice with plain device-to-device copies (copy engines over NVLink:
+ * no SM is taken from the attention kernel) and then write a step number into the owner's flag words; the owner waits,
+ * with a time limit, for all of them.  Layout of a buffer is the caller's; the first TQ_PEER_MAX 8-byte words are the
+ * flags by convention of triebwerk_b200.sharded.PeerCopyGatherer.
+ * =================================================================================================================== */
+#define TQ_PEER_MAX 32
+/* cudaMalloc + zero fill + IPC handle (64 bytes, to be sent to the peers by any host channel). */
+int tq_peer_buffer_create(size_t bytes, void** dptr, void* handle64);
+/* Map a peer's buffer into this process (peer access is enabled on first use); close it again. */
+int tq_peer_buffer_open(const void* handle64, void** dptr);
+int tq_peer_buffer_close(void* dptr);
+int tq_peer_buffer_destroy(void* dptr);
+/* One asynchronous device-to-device copy on `s` (dst may be a peer's buffer). */
+int tq_peer_copy(void* dst, const void* src, size_t bytes, tq_stream_t s);
+/* After everything enqueued on `s` so far: flag_arrays[i][slot] = value for the n peers (release, system scope). */
+int tq_peer_signal(void* const* flag_arrays, int n, int slot, unsigned long long value, tq_stream_t s);
+/* Enqueue a wait on `s` until flags[0 .. n) have all reached `value`; after limit_ms (1 .. 10000) the kernel gives up,
+ * raises status 4 in the int at status_word (device memory, may be null) and returns: the context stays usable. */
+int tq_peer_wait(const void* flags, int n, unsigned long long value, void* status_word, unsigned limit_ms, tq_stream_t s);
+
 #ifdef __cplusplus
 }
 #endif

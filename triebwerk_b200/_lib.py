@@ -27,6 +27,7 @@ SYMBOLS = [
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
     "tq_engine_output_f32", "tq_engine_read_output_f32", "tq_engine_decode_layers", "tq_static_status", "tq_selftest_bounded_wait",
     "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep", "tq_engine_prefill_shared", "tq_engine_decode_step_produce", "tq_fold_rotation_into_projection",
+    "tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy", "tq_peer_copy", "tq_peer_signal", "tq_peer_wait",
 ]
 
 
@@ -108,6 +109,13 @@ def lib() -> C.CDLL:
     sig("tq_static_status", i, [vp])
     sig("tq_engine_decode_step_produce", i, [vp, vp, vp, vp, vp, C.POINTER(StepProducer), vp])
     sig("tq_fold_rotation_into_projection", i, [vp, vp, vp, ll, i, vp])
+    sig("tq_peer_buffer_create", i, [sz, C.POINTER(vp), vp])
+    sig("tq_peer_buffer_open", i, [vp, C.POINTER(vp)])
+    sig("tq_peer_buffer_close", i, [vp])
+    sig("tq_peer_buffer_destroy", i, [vp])
+    sig("tq_peer_copy", i, [vp, vp, sz, vp])
+    sig("tq_peer_signal", i, [C.POINTER(vp), i, i, C.c_ulonglong, vp])
+    sig("tq_peer_wait", i, [vp, i, C.c_ulonglong, vp, C.c_uint, vp])
     sig("tq_engine_prefill_shared", i, [vp, i, i, i, vp, vp, i, vp])
     sig("tq_engine_sequence_blob_bytes", sz, [vp, i])
     sig("tq_engine_export_sequence", i, [vp, i, i, vp, sz, vp])

@@ -119,6 +119,109 @@ int tq_selftest_bounded_wait(void* status_word, unsigned limit, tq_stream_t s) {
     return tq_workspace_status(status_word, s);
 }
 
+// ---- peer exchange: outputs of sequence-sharded ranks land in every rank's buffer through the copy engines ----------------
+// One buffer per rank, made with cudaMalloc here so that its CUDA IPC handle names the whole allocation.  Peers open
+// the handle, copy their rows in with plain device-to-device copies (copy engines over NVLink: no SM is taken from the
+// attention kernel, which holds all of them) and announce completion by writing a step number into the owner's flag
+// words.  Nothing here reads a peer's memory from a kernel; the only kernel-side peer access is the 8-byte flag store.
+struct PeerFlagPtrs {
+    unsigned long long* p[TQ_PEER_MAX];
+};
+
+__global__ void peer_signal_kernel(PeerFlagPtrs flags, int n, int slot, unsigned long long value) {
+    const int i = threadIdx.x;
+    if (i < n && flags.p[i]) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flags.p[i] + slot), "l"(value) : "memory");
+    }
+}
+
+__global__ void peer_wait_kernel(const unsigned long long* flags, int n, unsigned long long value, int* status,
+                                 unsigned long long limit_ns) {
+    const int i = threadIdx.x;
+    if (i >= n) return;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + i) : "memory");
+        if (v >= value) return;
+        __nanosleep(200);
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > limit_ns) {  // give up: the host reads the status word, the context stays usable
+            if (status) atomicMax(status, ST_PEER_WAIT_TIMEOUT);
+            return;
+        }
+    }
+}
+
+int tq_peer_buffer_create(size_t bytes, void** dptr, void* handle64) {
+    if (!dptr || !handle64 || bytes == 0) return TQ_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return TQ_ERR_NOMEM;
+    }
+    TQ_CUDA(cudaMemset(p, 0, bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return (int)e;
+    }
+    memcpy(handle64, &h, 64);
+    *dptr = p;
+    return TQ_OK;
+}
+
+int tq_peer_buffer_open(const void* handle64, void** dptr) {
+    if (!handle64 || !dptr) return TQ_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return (int)e;
+    }
+    return TQ_OK;
+}
+
+int tq_peer_buffer_close(void* dptr) {
+    if (!dptr) return TQ_OK;
+    TQ_CUDA(cudaIpcCloseMemHandle(dptr));
+    return TQ_OK;
+}
+
+int tq_peer_buffer_destroy(void* dptr) {
+    if (!dptr) return TQ_OK;
+    TQ_CUDA(cudaFree(dptr));
+    return TQ_OK;
+}
+
+int tq_peer_copy(void* dst, const void* src, size_t bytes, tq_stream_t s) {
+    if (!dst || !src) return TQ_ERR_ARG;
+    if (bytes == 0) return TQ_OK;
+    TQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, cs(s)));
+    return TQ_OK;
+}
+
+int tq_peer_signal(void* const* flag_arrays, int n, int slot, unsigned long long value, tq_stream_t s) {
+    if (!flag_arrays || n <= 0 || n > TQ_PEER_MAX || slot < 0 || slot >= TQ_PEER_MAX) return TQ_ERR_ARG;
+    PeerFlagPtrs f{};
+    for (int i = 0; i < n; ++i) f.p[i] = (unsigned long long*)flag_arrays[i];
+    peer_signal_kernel<<<1, TQ_PEER_MAX, 0, cs(s)>>>(f, n, slot, value);
+    return cuda_status(cudaGetLastError());
+}
+
+int tq_peer_wait(const void* flags, int n, unsigned long long value, void* status_word, unsigned limit_ms, tq_stream_t s) {
+    if (!flags || n <= 0 || n > TQ_PEER_MAX || limit_ms == 0 || limit_ms > 10000) return TQ_ERR_ARG;
+    peer_wait_kernel<<<1, TQ_PEER_MAX, 0, cs(s)>>>((const unsigned long long*)flags, n, value, (int*)status_word,
+                                                  (unsigned long long)limit_ms * 1000000ull);
+    return cuda_status(cudaGetLastError());
+}
+
 // ---- packed path ---------------------------------------------------------------------------------------------------------
 static int append_impl(uint8_t* ck_q, void* k_norms, uint8_t* cv_q, void* v_norms, const void* k_buf, const void* v_buf,
                        const void* q, const void* rotation, const int* positions, int pos_value,

@@ -27,7 +27,8 @@ enum : int {
     ST_OK = 0,
     ST_TMA_WAIT_TIMEOUT = 1,   // a bounded wait on a TMA mbarrier ran out
     ST_SMEM_LAYOUT = 2,        // dynamic shared memory does not start where the kernel needs it
-    ST_BAD_POSITION = 3        // a position outside [0, capacity)
+    ST_BAD_POSITION = 3,       // a position outside [0, capacity)
+    ST_PEER_WAIT_TIMEOUT = 4   // a peer's completion flag did not arrive within the time limit
 };
 
 // ---- workspace layout ---------------------------------------------------------------------------------------
