@@ -60,6 +60,11 @@ WORKLOADS = {
     "c2full": dict(layers=28, H=16, Hkv=8, G=512, L=2048, bits=4, prompt=2048, append_only=True, batch=32,
                    desc="config 2 in full, prefill append: 512 sequences x 2048 tokens x 28 layers (K and V, kv_bits=4), streamed through "
                         "in batches of 32 prompts, one launch per batch and layer; 31 GB of cache written"),
+    "c2attn": dict(layers=4, H=16, Hkv=8, G=1, L=2048, bits=4, prompt=2048, prefill_attention=True,
+                   desc="causal prefill attention over the packed cache of one 2048-token prompt of config 2 (16/8 heads, kv_bits=4), "
+                        "4 of the 28 layers, one launcher call per layer"),
+    "c2attn8k": dict(layers=4, H=16, Hkv=8, G=1, L=8192, bits=4, prompt=8192, prefill_attention=True,
+                     desc="causal prefill attention over the packed cache of one 8192-token prompt (16/8 heads, kv_bits=4), 4 layers"),
     "c4": dict(layers=36, H=32, Hkv=8, G=128, L=16384, bits=4, prompt=100, ragged=True,
                desc="Qwen3-8B shape, ragged decode step: 36 layers, one GPU's share (LPT by tokens, 1 of 8) of 1024 sequences with "
                     "context ~ U{128..16384}, kv_bits=4"),
@@ -368,6 +373,73 @@ def run_append_only(args, w, rank, world, local_rank):
                      "frac": value / peak, "peak_kind": peak_kind, "traffic": None,
                      "note": ("one launch per sequence and layer (2048 tokens = 256 tiles = one wave): launch and set-up bound"
                               if per_sequence else "one launch per layer for all prompts; instruction-issue bound, not HBM bound")},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def run_prefill_attention(args, w, rank, world, local_rank):
+    """Prefill attention of whole prompts through the reference's launcher symbol (launch_turbo_gqa_prefill_attention):
+    one step = every layer's causal attention of the prompt over its own packed cache."""
+    import torch
+    import triebwerk_b200 as tq
+    from triebwerk_b200 import ops, synth
+
+    torch.cuda.set_device(local_rank)
+    T, H, Hkv, bits, NL = w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
+    kv_dim, q_dim = Hkv * D, H * D
+    eng = tq.Engine(T, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(1, T)
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    for layer in range(NL):
+        kp, vp = synth.torch_kv(gen, T, kv_dim, scales)
+        eng.prefill_append(layer, 0, kp, vp, 0)
+    caches = [eng.layer_cache(layer) for layer in range(NL)]
+    R = ops.rotation_matrix().cuda()
+    q = torch.randn(NL, T, q_dim, generator=gen, device="cuda").to(torch.float16)
+    out = torch.empty_like(q)
+
+    def step():
+        for layer in range(NL):
+            ck, cv, kn, vn = caches[layer]
+            ops.launch_turbo_gqa_prefill_attention(out[layer], q[layer], ck, cv, kn, vn, R, None, T, T, H, Hkv, D, q_dim, kv_dim, bits)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    steps = max(1, min(args.steps, 20))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    flops = NL * 2.0 * 2.0 * D * H * T * (T + 1) / 2.0          # QK^T and PV over the causal half
+    vpb = 4 if bits == 2 else 2
+    bytes_step = NL * (T * (2 * Hkv * D // vpb + 4 * Hkv) + 4 * T * q_dim)
+    tf_peak = None
+    try:
+        tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf_peak = 1590.0
+    tfs = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": bytes_step / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 codes -> f16 tiles, f16 mma.sync, f32 accumulate", "data": "synthetic",
+        "config": {"workload": w["desc"], "kv_bits": bits, "l2": "each step reads every layer's cache and queries again (one prompt fits L2: compute bound)"},
+        "us_per_layer": ms * 1e3 / NL, "causal_tflops": tfs,
+        "gpu_launches": steps * NL * 5,   # query rotation, table, transposed rotation, attention, merge
+        "roofline": {"kernel": f"prefill_attention_kernel<{bits}> (mma.sync; + query rotation and merge launches)", "bound": "tensor",
+                     "achieved": tfs, "peak": tf_peak, "unit": "TFLOP/s", "frac": tfs / tf_peak,
+                     "peak_kind": "measured cuBLAS bf16 (tcgen05); this kernel issues mma.sync", "traffic": None},
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -688,9 +760,9 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        if w.get("append_only"):
+        if w.get("append_only") or w.get("prefill_attention"):
             if rank == 0:
-                run_append_only(args, w, rank, world, local_rank)
+                (run_append_only if w.get("append_only") else run_prefill_attention)(args, w, rank, world, local_rank)
         else:
             run_ours(args, w, rank, world, local_rank)
     finally:
