@@ -554,6 +554,17 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
     res = {"w": w, "ms_step": ms_step, "clocks": clocks, "bytes_step": algorithmic_bytes(w)}
     # the step without the exchange (for the kernel's own launch duration at N > 1)
     res["ms_compute"] = ms_step if world == 1 else timed(step_compute, steps)
+    # the attention launch alone: CUDA events recorded by the library on the launching stream directly before and after it
+    # (whole-step form of the packed modes), averaged over steps that follow the timed ones at once
+    res["ms_attn_launch"] = None
+    if full and bits != 0 and os.environ.get("TQ_WHOLE_STEP", "1") != "0" and os.environ.get("TQ_FUSED", "1") != "0":
+        eng.time_attention(True)
+        samples = []
+        for _ in range(max(10, min(steps, 50))):
+            step_compute()
+            samples.append(eng.last_attention_ms())
+        eng.time_attention(False)
+        res["ms_attn_launch"] = sum(samples) / len(samples)
 
     if full:
         q_host, k_host, v_host = (t.cpu().pin_memory() for t in (q_dev, k_dev, v_dev))
@@ -676,12 +687,17 @@ def run_ours(args, w, rank, world, local_rank):
     peak, peak_kind = measured_peaks()
     fused = os.environ.get("TQ_FUSED", "1") != "0" and bits != 0
     whole = fused and os.environ.get("TQ_WHOLE_STEP", "1") != "0"
-    # The dominant kernel.  Whole-step form (default, packed modes): ONE attention launch streams all layers; the step
-    # holds three small launches beside it (append of every layer's token, query rotation, split-K merge: 4 % of the
-    # step in the profiler's launch list), so the attention kernel's time PER LAYER is bounded above by the device time
-    # of the step / layers, which is what is reported (at N > 1: of the step without the exchange).
+    # The dominant kernel.  Whole-step form (default, packed modes): ONE attention launch streams all layers; its
+    # duration is measured with CUDA events recorded directly around it (tq_engine_time_attention).  Other forms: the
+    # step holds small launches beside the attention, so the kernel's time per layer is bounded above by the device
+    # time of the step / layers, which is then what is reported (at N > 1: of the step without the exchange).
     kernel_bytes = bytes_step // NL
     attn_ms = res["ms_compute"] / NL
+    timed_by = "step time / layers (upper bound: the step's other launches are included)"
+    if res.get("ms_attn_launch"):
+        kernel_bytes = algorithmic_bytes(w, attention_only=True)
+        attn_ms = res["ms_attn_launch"] / NL
+        timed_by = "CUDA events on the launching stream directly around the attention launch, mean over the steps after the timed ones"
     achieved = kernel_bytes / (attn_ms * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -698,7 +714,7 @@ def run_ours(args, w, rank, world, local_rank):
         "roofline": {"kernel": "fp16_cache_write_kernel + fp16_decode_attention_kernel" if bits == 0 else
                      f"decode_attention_kernel<{bits}>" + (" (whole-step form: one launch streams all layers; per layer)" if whole else
                                                            " (one launch per layer: append + query rotation + attention)" if fused else ""),
-                     "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "bound": "hbm", "achieved": achieved, "peak": peak, "timed_by": timed_by,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "us_per_launch": attn_ms * 1e3 * (NL if whole else 1), "us_per_layer": attn_ms * 1e3,
                      "algorithmic_bytes_per_launch": kernel_bytes * (NL if whole else 1), "algorithmic_bytes_per_layer": kernel_bytes,

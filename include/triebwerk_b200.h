@@ -337,6 +337,13 @@ int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const v
 int tq_engine_output_f32(tq_engine* e, int enable);
 int tq_engine_read_output_f32(tq_engine* e, float* host_out, int first_layer, int n_layers, tq_stream_t s);
 
+/* Measurement aid: with enable != 0 the whole-step calls (tq_engine_decode_step / _decode_layers) record a CUDA event on
+ * their stream directly before and after the attention launch (which is then launched without the programmatic overlap
+ * with its predecessor); tq_engine_last_attention_ms waits for the second event of the most recent call and returns the
+ * time between the two: the launch duration of decode_attention_kernel alone.  No counterpart in the reference. */
+int tq_engine_time_attention(tq_engine* e, int enable);
+int tq_engine_last_attention_ms(tq_engine* e, float* ms);
+
 /* Token-form append of T tokens of sequence `seq` (prefill, engine/engine.cpp:2121-2130): k/v
  * [T][kv_dim] fp16 on the device, written at positions first_pos .. first_pos+T-1. */
 int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, const void* v, int first_pos,

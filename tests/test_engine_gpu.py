@@ -477,3 +477,39 @@ def test_shared_prefix_equals_replicated_prompt(bits, form):
     blob_p = plain.export_sequence(5, n_own)
     assert blob_s == blob_p
     print(f"shared prefix ({form}, {bits}-bit): largest output difference {worst:.2e}")
+
+
+def test_attention_launch_timing_leaves_results_unchanged():
+    """tq_engine_time_attention records events around the attention launch of the whole-step call: the reported time is
+    positive and below the wall time of the step, the results are the same bits as without it, and switching it off
+    makes the query an error."""
+    import time
+    H, Hkv, D, G, bits, msl, NL = 16, 8, 128, 8, 4, 512, 3
+    kv_dim, q_dim = Hkv * D, H * D
+    eng = tq.Engine(msl, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(G, msl)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    for layer in range(NL):
+        for g in range(G):
+            k, v = synth.torch_kv(gen, 300 + 7 * g, kv_dim, scales)
+            eng.prefill_append(layer, g, k, v, 0)
+    eng.set_positions([300 + 7 * g for g in range(G)])
+    q = torch.randn(NL, G, q_dim, generator=gen, device="cuda").to(torch.float16)
+    k = torch.randn(NL, G, kv_dim, generator=gen, device="cuda").to(torch.float16)
+    v = torch.randn(NL, G, kv_dim, generator=gen, device="cuda").to(torch.float16)
+    out_a, out_b = torch.empty_like(q), torch.empty_like(q)
+    eng.decode_step(q, k, v, out_a)
+    torch.cuda.synchronize()
+    eng.time_attention(True)
+    t0 = time.perf_counter()
+    eng.decode_step(q, k, v, out_b)   # the same token at the same positions again
+    ms = eng.last_attention_ms()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    assert 0.0 < ms < wall_ms
+    assert torch.equal(out_a, out_b)
+    eng.time_attention(False)
+    with pytest.raises(Exception):
+        eng.last_attention_ms()
+    assert eng.status() == 0

@@ -924,6 +924,11 @@ static void engine_release_arena(tq_engine* e) {
 }
 
 void tq_engine_destroy(tq_engine* e) {
+    if (e && e->ev_attn[0]) {
+        cudaEventDestroy(e->ev_attn[0]);
+        cudaEventDestroy(e->ev_attn[1]);
+        e->ev_attn[0] = e->ev_attn[1] = nullptr;
+    }
     if (!e) return;
     engine_release_arena(e);
     if (e->d_rotation) cudaFree(e->d_rotation);
@@ -1533,7 +1538,9 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
         p.stamps = d_stamps;
     }
 #endif
-    r = launch_attention(e->kv_bits, e->tmK4, e->tmV4, p, attention_ctas(G, e->msl), s, use_pdl(), 2);
+    if (e->ev_attn[0]) cudaEventRecord(e->ev_attn[0], s);
+    r = launch_attention(e->kv_bits, e->tmK4, e->tmV4, p, attention_ctas(G, e->msl), s, use_pdl() && !e->ev_attn[0], 2);
+    if (e->ev_attn[0]) cudaEventRecord(e->ev_attn[1], s);
     if (r != TQ_OK) return r;
 
     MergeParams m{};
@@ -1554,6 +1561,28 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
     }
 #endif
     return launch_kernel(merge_partials_kernel, dim3(G, n), dim3(MERGE_WARPS * 32), 0, s, use_pdl(), m);
+}
+
+int tq_engine_time_attention(tq_engine* e, int enable) {
+    if (!e) return TQ_ERR_ARG;
+    if (!engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (enable && !e->ev_attn[0]) {
+        TQ_CUDA(cudaEventCreate(&e->ev_attn[0]));
+        TQ_CUDA(cudaEventCreate(&e->ev_attn[1]));
+    } else if (!enable && e->ev_attn[0]) {
+        cudaEventDestroy(e->ev_attn[0]);
+        cudaEventDestroy(e->ev_attn[1]);
+        e->ev_attn[0] = e->ev_attn[1] = nullptr;
+    }
+    return TQ_OK;
+}
+
+int tq_engine_last_attention_ms(tq_engine* e, float* ms) {
+    if (!e || !ms) return TQ_ERR_ARG;
+    if (!e->ev_attn[0]) return TQ_ERR_STATE;
+    TQ_CUDA(cudaEventSynchronize(e->ev_attn[1]));
+    TQ_CUDA(cudaEventElapsedTime(ms, e->ev_attn[0], e->ev_attn[1]));
+    return TQ_OK;
 }
 
 int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v, void* out,

@@ -557,6 +557,7 @@ struct tq_engine {
     void* step_kpost = nullptr;        // [layers][G][kv_dim] fp16: K after QK-norm and rotary embedding (producer form)
     bool whole_step = !(getenv("TQ_WHOLE_STEP") && atoi(getenv("TQ_WHOLE_STEP")) == 0);
     float* out_f32 = nullptr;          // optional [layers][G][H][128]: results before the fp16 rounding (outside the arena)
+    cudaEvent_t ev_attn[2] = {nullptr, nullptr};  // optional: recorded around the attention launch of the whole-step form
 
     int* d_positions = nullptr;
     int* d_capacities = nullptr;       // [G] positions each sequence may reach (slot rows + shared prefix tokens)

@@ -174,6 +174,17 @@ class Engine:
                                             v[first_layer].data_ptr(), out[first_layer].data_ptr(), self._stream()), "decode_layers")
         return out
 
+    def time_attention(self, on: bool = True) -> None:
+        """Record CUDA events around the attention launch of the whole-step calls (measurement aid)."""
+        check(lib().tq_engine_time_attention(self._h, int(bool(on))), "time_attention")
+
+    def last_attention_ms(self) -> float:
+        """Duration of the attention launch of the most recent whole-step call (after time_attention())."""
+        import ctypes as C
+        ms = C.c_float()
+        check(lib().tq_engine_last_attention_ms(self._h, C.byref(ms)), "last_attention_ms")
+        return float(ms.value)
+
     def enable_output_f32(self, on: bool = True) -> None:
         """Also keep the attention results as fp32, before their rounding to fp16 (error reports; packed modes)."""
         check(lib().tq_engine_output_f32(self._h, int(bool(on))), "output_f32")
