@@ -159,8 +159,8 @@ int tq_decode_attention(void* out, const uint8_t* ck_q, const uint8_t* cv_q, con
  *   Limit: tq_workspace_bytes(G, num_heads) must not exceed 20 MiB -- that covers 64 sequences x 32 query heads or
  *   256 x 16; larger requests return TQ_ERR_CAPACITY and launch nothing.  Arguments are checked before anything is
  *   enqueued: a refused call leaves the stream untouched.
- *   The first call on a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream
- *   capture.  All calls share the one array and it keeps the previous call's contents (the call itself clears what
+ *   The first call on a device looks the array's address up (cudaGetSymbolAddress), once.  All calls share the one
+ *   array and it keeps the previous call's contents (the call itself clears what
  *   must start at zero): two calls that overlap on the GPU -- different streams, or work replayed concurrently --
  *   race on it and must be serialised by the caller.
  *   Device-side trouble (a bounded wait that gave up = 1, a shared-memory layout refused = 2) is collected in a status

@@ -385,9 +385,8 @@ static int generic_packed_attention(void* out, const void* q, const void* ck_q, 
 
 // ---- allocation-free decode attention -----------------------------------------------------------------------------------
 // Some embedders may not allocate device memory at all once they are running: every byte of the GPU was handed to
-// their own pool at start-up (a raw cudaMalloc would fail or fight that pool), they sit inside a serving loop whose
-// latency budget rules out cudaMalloc (it synchronises the whole device), or they are already recording a CUDA graph
-// when they first reach this library.  For them the scratch that the attention kernel needs lives in the library
+// their own pool at start-up (a raw cudaMalloc would fail or fight that pool), or they sit inside a serving loop whose
+// latency limits rule out cudaMalloc (it synchronises the whole device).  For them the scratch that the attention kernel needs lives in the library
 // image itself: a fixed device array that every GPU loading this library carries until the process exits.
 constexpr size_t TQ_STATIC_SCRATCH_BYTES = (size_t)20 << 20;  // 20 MiB: 64 sequences x 32 query heads fit, see the header
 static __device__ __align__(256) unsigned char g_static_scratch[TQ_STATIC_SCRATCH_BYTES];
@@ -432,7 +431,7 @@ int tq_decode_attention_static(void* out, const void* q, const uint8_t* ck_q, co
     r = make_code_map(&tmV, cv_q, total_rows, kvp);
     if (r != TQ_OK) return r;
     void* ws = nullptr;
-    r = static_scratch_ptr(&ws);  // first call on a device: symbol lookup (do it before capturing a graph)
+    r = static_scratch_ptr(&ws);  // first call on a device: one symbol lookup
     if (r != TQ_OK) return r;
     // The array keeps whatever the previous call left.  What has to start from zero: the per-sequence tickets, cleared by
     // the rotate kernel below; everything else is written before it is read.  The status word at the start of the array
