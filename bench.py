@@ -566,6 +566,23 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
         eng.time_attention(False)
         res["ms_attn_launch"] = sum(samples) / len(samples)
 
+    res["variants"] = None
+    if full and world == 1 and bits != 0 and res["ms_attn_launch"]:
+        # the step that takes the projections' raw outputs (per-head RMS norm and rotary embedding inside it), and the
+        # same with the inverse rotation left to the consumer's weights
+        nw_q = (1.0 + 0.1 * torch.randn(NL, D, generator=gen, device="cuda")).to(torch.float16)
+        nw_k = (1.0 + 0.1 * torch.randn(NL, D, generator=gen, device="cuda")).to(torch.float16)
+        ang = torch.arange(L, device="cuda", dtype=torch.float32)[:, None] * (1e6 ** (-torch.arange(D // 2, device="cuda", dtype=torch.float32) / (D // 2)))[None]
+        rc, rs = ang.cos().to(torch.float16).contiguous(), ang.sin().to(torch.float16).contiguous()
+        var = {}
+        for name, rot_out in (("produce", False), ("produce_rotated_output", True)):
+            fn = lambda: eng.decode_step_produce(q_dev, k_dev, v_dev, out_dev, nw_q, nw_k, rc, rs, D, 1e-6, False, rot_out)
+            for _ in range(3):
+                fn()
+            var[name] = {"ms_per_step": timed(fn, max(10, min(steps, 50)))}
+        var["note"] = ("tq_engine_decode_step_produce on the same workload: QK-norm and rotary embedding of the reference's "
+                       "launch_qk_norm_batch + launch_rope_batch happen inside the step's own four launches")
+        res["variants"] = var
     if full:
         q_host, k_host, v_host = (t.cpu().pin_memory() for t in (q_dev, k_dev, v_dev))
         out_host = torch.empty(NL, G, q_dim, dtype=torch.float16).pin_memory()
@@ -722,6 +739,8 @@ def run_ours(args, w, rank, world, local_rank):
         "clocks": res["clocks"],
         "sustained": res["sustained"],
     }
+    if res.get("variants"):
+        line["step_variants"] = res["variants"]
     if world > 1:
         line["exchange"] = {"kind": res.get("gather"), "layer_groups": len(sharded_groups(NL, world)),
                             "ms_per_step_without_exchange": res["ms_compute"],
