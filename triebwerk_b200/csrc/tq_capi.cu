@@ -658,18 +658,13 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
     }
     static const bool dedicated = !(getenv("TQ_PREFILL_ATTN") && atoi(getenv("TQ_PREFILL_ATTN")) == 0);
     if (r == TQ_OK && dedicated && prefill_attn_shape(num_heads, num_kv_heads)) {
-        // the kernel with the query tokens in the M dimension: rotate the queries, attend, merge (normalise and R^T)
+        // the kernel with the query tokens in the M dimension: rotate the queries, then attend (the kernel normalises and
+        // applies R^T itself)
         const size_t qrot_b = align_up((size_t)T * num_heads * HEAD_DIM * sizeof(__half), 256);
-        const size_t part_b = align_up((size_t)T * num_heads * PART_STRIDE * sizeof(float), 256);
-        const size_t table_b = align_up((size_t)(T + 3) * sizeof(int), 256);
-        const size_t rot_b = (size_t)HEAD_DIM * HEAD_DIM * sizeof(__half);
         void* pws = nullptr;
-        r = compat_workspace(qrot_b + part_b + table_b + rot_b, &pws, cs(s));
+        r = compat_workspace(qrot_b, &pws, cs(s));
         if (r == TQ_OK) {
             __half* qrot = (__half*)pws;
-            float* parts = (float*)((char*)pws + qrot_b);
-            int* table = (int*)((char*)pws + qrot_b + part_b);
-            __half* rot_t = (__half*)((char*)pws + qrot_b + part_b + table_b);
             QRotParams qp{};
             qp.q = (const __half*)q;
             qp.rotation = (const __half*)rotation;
@@ -679,8 +674,6 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
             qp.q_dim = q_dim;
             const long long qgroups = (qp.n_vec + 15) / 16;
             rotate_queries_kernel<false><<<(unsigned)std::min<long long>(qgroups, 4ll * device_props().sm_count), QROT_WARPS * 32, 0, cs(s)>>>(qp);
-            one_part_table_kernel<<<(T + 1 + 255) / 256, 256, 0, cs(s)>>>(table, T);
-            transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>(rot_t, (const __half*)rotation);
             r = cuda_status(cudaGetLastError());
             PrefillAttnParams ap{};
             ap.q = qrot;
@@ -689,7 +682,8 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
             ap.cv = cv_q;
             ap.kn = (const __half*)k_norms;
             ap.vn = (const __half*)v_norms;
-            ap.partials = parts;
+            ap.rotation = (const __half*)rotation;
+            ap.out = (__half*)out;
             ap.q_dim = q_dim;
             ap.T = T;
             ap.rows = msl;
@@ -697,18 +691,6 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
             ap.Hkv = num_kv_heads;
             ap.score_scale = 1.0f;
             if (r == TQ_OK) r = launch_prefill_attention(bits, ap, cs(s));
-            if (r == TQ_OK) {
-                MergeParams mp{};
-                mp.partials = parts;
-                mp.table = table;
-                mp.rotation_t = rot_t;
-                mp.out = (__half*)out;
-                mp.G = T;
-                mp.H = num_heads;
-                mp.q_dim = q_dim;
-                merge_partials_kernel<<<dim3((unsigned)T, 1), MERGE_WARPS * 32, 0, cs(s)>>>(mp);
-                r = cuda_status(cudaGetLastError());
-            }
         }
         g_compat_status = r;
         return;

@@ -14,9 +14,9 @@
 //     ldmatrix.trans; O stays in registers (16 rows x 128 coordinates per warp);
 //   * the next tile is fetched into registers before the arithmetic of the current one and dequantised into the other
 //     half of the double buffer after it: one barrier per tile.
-// Packed form: queries arrive pre-rotated and pre-scaled (rotate_queries_kernel), the unnormalised sums leave as split-K
-// partials with one part per (token, head) and merge_partials_kernel normalises and multiplies by R^T.  fp16 form: raw
-// queries, the result is normalised and stored here.  No O(T^2) scratch either way.
+// Packed form: queries arrive pre-rotated and pre-scaled (rotate_queries_kernel); at the end each warp normalises its 16
+// rows and multiplies them by R^T with one more tensor-core product (fp16 high + low parts against R in the idle tile
+// buffers).  fp16 form: raw queries, the result is normalised and stored.  No O(T^2) scratch either way.
 #pragma once
 
 #include "tq_common.cuh"
@@ -42,8 +42,8 @@ struct PrefillAttnParams {
     const uint8_t* cv;
     const __half* kn;         // [rows][Hkv] (packed forms)
     const __half* vn;
-    float* partials;          // packed forms: token t, head h -> partials[(t * H + h) * PART_STRIDE]: acc[128], m, l
-    __half* out;              // fp16 form: [T][q_dim]
+    const __half* rotation;   // packed forms: R row-major [128][128] (the way back out of the rotated space)
+    __half* out;              // [T][q_dim]
     int q_dim;
     int T;                    // query tokens = cache rows in use
     int rows;                 // cache rows that exist (loads are clamped to them)
@@ -271,41 +271,72 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
         __syncthreads();
     }
 
-    // ---- row sums over the four lanes of a row; results out ----
+    // ---- row sums over the four lanes of a row ----
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float inv_lo = 1.0f / (l_lo + 1e-8f), inv_hi = 1.0f / (l_hi + 1e-8f);
+    const int r_lo = 16 * warp + gl, r_hi = r_lo + 8;
+    const int otok_lo = q0 + (r_lo >> gs), otok_hi = q0 + (r_hi >> gs);
+    __half* dst_lo = p.out + (size_t)otok_lo * p.q_dim + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
+    __half* dst_hi = p.out + (size_t)otok_hi * p.q_dim + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
+    if (BITS == 0) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = 16 * warp + gl + 8 * half;
-        const int tok = q0 + (r >> gs), head = kvh * GRP + (r & (GRP - 1));
-        if (tok >= p.T) continue;
-        const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
-        if (BITS == 0) {
-            const float inv = 1.0f / (l + 1e-8f);
-            __half* dst = p.out + (size_t)tok * p.q_dim + (size_t)head * HEAD_DIM + 2 * t4;
+        for (int nb = 0; nb < 16; ++nb) {
+            if (otok_lo < p.T) *reinterpret_cast<__half2*>(dst_lo + 8 * nb) = __floats2half2_rn(o[nb][0] * inv_lo, o[nb][1] * inv_lo);
+            if (otok_hi < p.T) *reinterpret_cast<__half2*>(dst_hi + 8 * nb) = __floats2half2_rn(o[nb][2] * inv_hi, o[nb][3] * inv_hi);
+        }
+        return;
+    }
+    // ---- packed forms: back out of the rotated space, out[d] = sum_k R[k][d] * acc[k] (reference engine/kernels.cu:1957),
+    //      as one more tensor-core product per warp: the normalised sums, split into fp16 high and low parts, are the A
+    //      operand exactly as the weights were in P . V, and R [k][d] (copied into the idle tile buffers, same swizzle)
+    //      plays V's part through ldmatrix.trans ----
+    uint32_t ah[8][4], al[8][4];  // step ks: coordinates k = 16 ks .. 16 ks + 15 of the rows gl and gl + 8
 #pragma unroll
-            for (int nb = 0; nb < 16; ++nb)
-                *reinterpret_cast<__half2*>(dst + 8 * nb) = __floats2half2_rn(o[nb][2 * half] * inv, o[nb][2 * half + 1] * inv);
-        } else {
-            float* dst = p.partials + ((size_t)tok * p.H + head) * PART_STRIDE;
+    for (int ks = 0; ks < 8; ++ks) {
 #pragma unroll
-            for (int nb = 0; nb < 16; ++nb)
-                *reinterpret_cast<float2*>(dst + 8 * nb + 2 * t4) = make_float2(o[nb][2 * half], o[nb][2 * half + 1]);
-            if (t4 == 0) *reinterpret_cast<float2*>(dst + HEAD_DIM) = make_float2(m, l);
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const float x0 = o[2 * ks + h2][0] * inv_lo, x1 = o[2 * ks + h2][1] * inv_lo;
+            const float y0 = o[2 * ks + h2][2] * inv_hi, y1 = o[2 * ks + h2][3] * inv_hi;
+            const __half2 hx = __floats2half2_rn(x0, x1), hy = __floats2half2_rn(y0, y1);
+            const float2 fx = __half22float2(hx), fy = __half22float2(hy);
+            ah[ks][2 * h2] = *reinterpret_cast<const uint32_t*>(&hx);
+            ah[ks][2 * h2 + 1] = *reinterpret_cast<const uint32_t*>(&hy);
+            al[ks][2 * h2] = pack_half2(x0 - fx.x, x1 - fx.y);
+            al[ks][2 * h2 + 1] = pack_half2(y0 - fy.x, y1 - fy.y);
         }
     }
-}
-
-// Tile table that makes merge_partials_kernel treat query token g as a sequence with ONE part stored at slot g:
-// table[g] = g, one worker, more tiles than tokens (every token's first and last tile then belong to worker 0).
-__global__ void one_part_table_kernel(int* table, int T) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i <= T) table[i] = i;
-    if (i == 0) {
-        table[T + 1] = 1;
-        table[T + 2] = T + 1;
+    // (every warp left the tile buffers at the loop's last barrier) R: 128 rows of 256 bytes over the K buffers
+    for (int i = tid; i < 128 * 16; i += PFA_THREADS) {
+        const int row = i >> 4, ch = i & 15;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)row * HEAD_DIM) + ch);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::K + (uint32_t)row * 256u + (uint32_t)((ch ^ (row & 7)) << 4)),
+                     "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int np = 0; np < 8; ++np) {
+        float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const int row = 16 * ks + v_tok, ch = 2 * np + v_chunk;
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, sb + PfaSmem::K + (uint32_t)row * 256u + (uint32_t)((ch ^ (row & 7)) << 4));
+            mma16816(c0, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], r[0], r[1]);
+            mma16816(c0, al[ks][0], al[ks][1], al[ks][2], al[ks][3], r[0], r[1]);
+            mma16816(c1, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], r[2], r[3]);
+            mma16816(c1, al[ks][0], al[ks][1], al[ks][2], al[ks][3], r[2], r[3]);
+        }
+        if (otok_lo < p.T) {
+            *reinterpret_cast<__half2*>(dst_lo + 16 * np) = __floats2half2_rn(c0[0], c0[1]);
+            *reinterpret_cast<__half2*>(dst_lo + 16 * np + 8) = __floats2half2_rn(c1[0], c1[1]);
+        }
+        if (otok_hi < p.T) {
+            *reinterpret_cast<__half2*>(dst_hi + 16 * np) = __floats2half2_rn(c0[2], c0[3]);
+            *reinterpret_cast<__half2*>(dst_hi + 16 * np + 8) = __floats2half2_rn(c1[2], c1[3]);
+        }
     }
 }
 
