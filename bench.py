@@ -436,8 +436,8 @@ def run_prefill_attention(args, w, rank, world, local_rank):
         "dtype": "u8 codes -> f16 tiles, f16 mma.sync, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["desc"], "kv_bits": bits, "l2": "each step reads every layer's cache and queries again (one prompt fits L2: compute bound)"},
         "us_per_layer": ms * 1e3 / NL, "causal_tflops": tfs,
-        "gpu_launches": steps * NL * 2,   # query rotation, attention
-        "roofline": {"kernel": f"prefill_attention_kernel<{bits}> (mma.sync; + the query rotation launch)", "bound": "tensor",
+        "gpu_launches": steps * NL,   # one launch per layer
+        "roofline": {"kernel": f"prefill_attention_kernel<{bits}> (mma.sync)", "bound": "tensor",
                      "achieved": tfs, "peak": tf_peak, "unit": "TFLOP/s", "frac": tfs / tf_peak,
                      "peak_kind": "measured cuBLAS bf16 (tcgen05); this kernel issues mma.sync", "traffic": None},
         "clocks": clocks,

@@ -87,7 +87,8 @@ void launch_turbo_gqa_attention(const void* q, const uint8_t* ck_q, const uint8_
 /* engine/kernels.cu:2015-2028 (kernel :1874-1960).  Causal prefill attention over a single-sequence
  * packed cache: query row tq of q [T][q_dim] attends to positions 0..tq.  Served by a kernel that holds 128 / (heads
  * per KV head) query tokens in the M dimension of the tensor-core products and dequantises every 64-row cache tile once
- * per block; `as` (the reference's [T][heads][T] score scratch) is accepted and ignored. */
+ * per block, in one launch and without any workspace (the query rotation and the way back through R^T are tensor-core
+ * products inside it); `as` (the reference's [T][heads][T] score scratch) is accepted and ignored. */
 void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t* ck_q, const uint8_t* cv_q,
                                         const void* k_norms, const void* v_norms, const void* rotation,
                                         float* as, int T, int msl, int num_heads, int num_kv_heads,

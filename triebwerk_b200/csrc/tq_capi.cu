@@ -658,40 +658,24 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
     }
     static const bool dedicated = !(getenv("TQ_PREFILL_ATTN") && atoi(getenv("TQ_PREFILL_ATTN")) == 0);
     if (r == TQ_OK && dedicated && prefill_attn_shape(num_heads, num_kv_heads)) {
-        // the kernel with the query tokens in the M dimension: rotate the queries, then attend (the kernel normalises and
-        // applies R^T itself)
-        const size_t qrot_b = align_up((size_t)T * num_heads * HEAD_DIM * sizeof(__half), 256);
-        void* pws = nullptr;
-        r = compat_workspace(qrot_b, &pws, cs(s));
-        if (r == TQ_OK) {
-            __half* qrot = (__half*)pws;
-            QRotParams qp{};
-            qp.q = (const __half*)q;
-            qp.rotation = (const __half*)rotation;
-            qp.q_rot = qrot;
-            qp.n_vec = (long long)T * num_heads;
-            qp.H = num_heads;
-            qp.q_dim = q_dim;
-            const long long qgroups = (qp.n_vec + 15) / 16;
-            rotate_queries_kernel<false><<<(unsigned)std::min<long long>(qgroups, 4ll * device_props().sm_count), QROT_WARPS * 32, 0, cs(s)>>>(qp);
-            r = cuda_status(cudaGetLastError());
-            PrefillAttnParams ap{};
-            ap.q = qrot;
-            ap.q_tok_stride = (long long)num_heads * HEAD_DIM;
-            ap.ck = ck_q;
-            ap.cv = cv_q;
-            ap.kn = (const __half*)k_norms;
-            ap.vn = (const __half*)v_norms;
-            ap.rotation = (const __half*)rotation;
-            ap.out = (__half*)out;
-            ap.q_dim = q_dim;
-            ap.T = T;
-            ap.rows = msl;
-            ap.H = num_heads;
-            ap.Hkv = num_kv_heads;
-            ap.score_scale = 1.0f;
-            if (r == TQ_OK) r = launch_prefill_attention(bits, ap, cs(s));
-        }
+        // the kernel with the query tokens in the M dimension: one launch (it rotates its queries, attends, normalises and
+        // applies R^T)
+        PrefillAttnParams ap{};
+        ap.q = (const __half*)q;
+        ap.q_tok_stride = q_dim;
+        ap.ck = ck_q;
+        ap.cv = cv_q;
+        ap.kn = (const __half*)k_norms;
+        ap.vn = (const __half*)v_norms;
+        ap.rotation = (const __half*)rotation;
+        ap.out = (__half*)out;
+        ap.q_dim = q_dim;
+        ap.T = T;
+        ap.rows = msl;
+        ap.H = num_heads;
+        ap.Hkv = num_kv_heads;
+        ap.score_scale = 1.0f;
+        r = launch_prefill_attention(bits, ap, cs(s));
         g_compat_status = r;
         return;
     }

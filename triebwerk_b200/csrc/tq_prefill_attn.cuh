@@ -14,9 +14,10 @@
 //     ldmatrix.trans; O stays in registers (16 rows x 128 coordinates per warp);
 //   * the next tile is fetched into registers before the arithmetic of the current one and dequantised into the other
 //     half of the double buffer after it: one barrier per tile.
-// Packed form: queries arrive pre-rotated and pre-scaled (rotate_queries_kernel); at the end each warp normalises its 16
-// rows and multiplies them by R^T with one more tensor-core product (fp16 high + low parts against R in the idle tile
-// buffers).  fp16 form: raw queries, the result is normalised and stored.  No O(T^2) scratch either way.
+// Packed form: each warp first rotates its 16 query rows (one tensor-core product against R in the still idle tile
+// buffers, scaled by log2(e) / sqrt(128)), and at the end normalises its 16 result rows and multiplies them by R^T with
+// one more product (fp16 high + low parts against R copied into the buffers again).  fp16 form: the result is
+// normalised and stored.  One launch, no O(T^2) scratch, no workspace.
 #pragma once
 
 #include "tq_common.cuh"
@@ -36,7 +37,7 @@ struct PfaSmem {
 };
 
 struct PrefillAttnParams {
-    const __half* q;          // packed: rotated, scaled queries [T][H][128]; fp16: raw queries [T][q_dim]
+    const __half* q;          // queries [T][q_dim] as the model makes them
     long long q_tok_stride;   // halves between the queries of consecutive tokens
     const uint8_t* ck;        // packed codes [rows][kvp], or fp16 rows [rows][Hkv * 128]
     const uint8_t* cv;
@@ -48,7 +49,7 @@ struct PrefillAttnParams {
     int T;                    // query tokens = cache rows in use
     int rows;                 // cache rows that exist (loads are clamped to them)
     int H, Hkv, grp_shift;    // GRP = 1 << grp_shift query heads per KV head
-    float score_scale;        // 1 when the queries carry log2(e) / sqrt(128) already
+    float score_scale;        // fp16 form: log2(e) / sqrt(128); packed forms: 1 (the rotated queries carry it)
 };
 
 template <int BITS>
@@ -161,7 +162,42 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
     float m_lo = -1e30f, m_hi = -1e30f, l_lo = 0.0f, l_hi = 0.0f;
 
-    __syncthreads();  // the table is complete
+    if (BITS != 0) {
+        // ---- packed forms: the queries arrive as the model makes them; q_rot[d] = sum_k R[d][k] q[k] (reference
+        //      engine/kernels.cu:1896-1903) is one tensor-core product per warp against R [d][k] in the (still idle) tile
+        //      buffers, read like a K tile; the results, times log2(e) / sqrt(128), are the A fragments of the score product ----
+        for (int i = tid; i < 128 * 16; i += PFA_THREADS) {
+            const int row = i >> 4, ch = i & 15;
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)row * HEAD_DIM) + ch);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sb + PfaSmem::K + (uint32_t)row * 256u + (uint32_t)((ch ^ (row & 7)) << 4)),
+                         "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+        }
+        __syncthreads();
+        const int mi0 = lane >> 3, mr0 = lane & 7;
+        uint32_t qr[8][4];
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {  // output coordinates 16 np .. 16 np + 15
+            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const int row = 16 * np + (mi0 >> 1) * 8 + mr0, ch = 2 * ks + (mi0 & 1);
+                uint32_t r[4];
+                ldmatrix_x4(r, sb + PfaSmem::K + (uint32_t)row * 256u + (uint32_t)((ch ^ (row & 7)) << 4));
+                mma16816(c0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r[0], r[1]);
+                mma16816(c1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r[2], r[3]);
+            }
+            const float sc = 0.12751743074602467f;  // log2(e) / sqrt(128)
+            qr[np][0] = pack_half2(c0[0] * sc, c0[1] * sc);   // row gl, coordinates 16 np + 2 t4, + 1
+            qr[np][1] = pack_half2(c0[2] * sc, c0[3] * sc);   // row gl + 8
+            qr[np][2] = pack_half2(c1[0] * sc, c1[1] * sc);   // row gl, coordinates 16 np + 8 + 2 t4, + 1
+            qr[np][3] = pack_half2(c1[2] * sc, c1[3] * sc);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = qr[ks][0]; qa[ks][1] = qr[ks][1]; qa[ks][2] = qr[ks][2]; qa[ks][3] = qr[ks][3];
+        }
+    }
+    __syncthreads();  // the table is complete; R has been read by every warp
     fetch(0);
     stage(0, 0);
     if (n_tiles > 1) fetch(1);
