@@ -357,6 +357,13 @@ int tq_engine_prefill_append(tq_engine* e, int layer, int seq, const void* k, co
 int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* k, const void* v,
                                    int first_pos, int T, tq_stream_t s);
 
+/* One layer of a prompt's prefill (engine/engine.cpp:2110-2146: the cache write of all T tokens, then the causal
+ * self-attention): k/v [T][kv_dim] of sequence `seq` go to positions 0 .. T-1 of its slot, and query token t of
+ * q [T][q_stride] attends to rows 0 .. t; out [T][q_stride] (the reference passes one stride, Q_PROJ_DIM, for both).
+ * Packed modes and kv_bits = 0; sequences behind a shared prefix are refused (TQ_ERR_STATE). */
+int tq_engine_prefill_layer(tq_engine* e, int layer, int seq, const void* q, const void* k, const void* v, void* out, int T,
+                            int q_stride, tq_stream_t s);
+
 /* A prompt of T tokens shared by the n_seq sequences first_seq .. (rollouts of one prompt; the reference prefills
  * sequence 0 and copies its cache to the other sequences, engine/engine.cpp:2173-2214, 2296).  The first
  * P = 32 * floor(T / 32) tokens are quantised and stored once, in the slot of first_seq; the other sequences read

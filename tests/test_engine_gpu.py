@@ -513,3 +513,42 @@ def test_attention_launch_timing_leaves_results_unchanged():
     with pytest.raises(Exception):
         eng.last_attention_ms()
     assert eng.status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 2, 0])
+def test_prefill_layer_of_a_prompt_against_oracle(bits):
+    """tq_engine_prefill_layer: the cache write of a prompt and its causal self-attention (reference
+    engine/engine.cpp:2110-2146) for the second sequence of a ragged batch, with the query and output stride of a gated
+    model (twice the query width, the gate columns untouched)."""
+    H, Hkv, D, NL = 16, 8, 128, 2
+    kv_dim, q_dim = Hkv * D, H * D
+    caps = [64, 224, 96]
+    T = 200
+    rng = np.random.default_rng(800 + bits)
+    R, _ = tqo.rotation()
+    eng = tq.Engine(256, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+    eng.alloc_batch(3, 256, caps)
+    k = rng.standard_normal((T, kv_dim), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((T, kv_dim), dtype=np.float32).astype(np.float16)
+    q2 = rng.standard_normal((T, 2 * q_dim), dtype=np.float32).astype(np.float16)
+    out = torch.full((T, 2 * q_dim), 7.0, dtype=torch.float16, device="cuda")
+    eng.prefill_layer(1, 1, gu.dev(q2), gu.dev(k), gu.dev(v), out)
+    got = gu.host(out)
+    assert (got[:, q_dim:] == np.float16(7.0)).all(), "columns past the query heads were written"
+    msl = caps[1]
+    if bits == 0:
+        ref = np.stack([tqo.fp16_attention_single(q2[t, :q_dim], np.pad(k, ((0, msl - T), (0, 0))), np.pad(v, ((0, msl - T), (0, 0))),
+                                                  t, msl, H, Hkv, D)[0] for t in range(T)])
+    else:
+        ck, kn = tqo.alloc_cache(1, msl, Hkv, D, bits)
+        cv, vn = tqo.alloc_cache(1, msl, Hkv, D, bits)
+        pos = np.arange(T, dtype=np.int32)
+        tqo.append_tokens(ck, kn, k, R, pos, msl, Hkv, D, bits)
+        tqo.append_tokens(cv, vn, v, R, pos, msl, Hkv, D, bits)
+        ref, _ = tqo.prefill_attention(np.ascontiguousarray(q2[:, :q_dim]), ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+    w, r = hp.assert_attention_close(got[:, :q_dim], ref, H, D, f"prefill layer kv_bits={bits}")
+    print(f"prefill layer kv_bits={bits}: max-abs {w:.2e}, rel {r:.2e}")
+    # the neighbours' slots are untouched, and a prompt longer than the slot is refused before anything runs
+    assert eng.status() == 0
+    with pytest.raises(Exception):
+        eng.prefill_layer(0, 0, gu.dev(q2), gu.dev(k), gu.dev(v), out)   # T = 200 > 64 rows

@@ -197,6 +197,17 @@ class Engine:
         check(lib().tq_engine_read_output_f32(self._h, out.ctypes.data, first_layer, n_layers, self._stream()), "read_output_f32")
         return out
 
+    def prefill_layer(self, layer: int, seq: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor = None):
+        """One layer of a prompt's prefill (reference engine/engine.cpp:2110-2146): k/v [T, kv_dim] into positions 0..T-1 of
+        the sequence's slot, then causal attention of q [T, q_stride] over them; returns out [T, q_stride]."""
+        for t in (q, k, v):
+            assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16
+        if out is None:
+            out = torch.empty_like(q)
+        check(lib().tq_engine_prefill_layer(self._h, layer, seq, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            k.shape[0], q.shape[1], self._stream()), "prefill_layer")
+        return out
+
     def prefill_append(self, layer: int, seq: int, k: torch.Tensor, v: torch.Tensor, first_pos: int = 0) -> None:
         """Token-form append of k/v [T, kv_dim] for one sequence (reference engine/engine.cpp:2121-2130)."""
         assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous()
