@@ -63,6 +63,9 @@ WORKLOADS = {
     "c2attn": dict(layers=4, H=16, Hkv=8, G=1, L=2048, bits=4, prompt=2048, prefill_attention=True,
                    desc="causal prefill attention over the packed cache of one 2048-token prompt of config 2 (16/8 heads, kv_bits=4), "
                         "4 of the 28 layers, one launcher call per layer"),
+    "c2prefill": dict(layers=4, H=16, Hkv=8, G=32, L=2048, bits=4, prompt=2048, prefill_attention=True, batch=32,
+                      desc="prefill of config 2's prompts through the engine handle: 32 of the 512 prompts x 2048 tokens, 4 of the 28 layers; "
+                           "per layer one cache-write launch (tcgen05) and one causal-attention launch for all 32 prompts, kv_bits=4"),
     "c2attn8k": dict(layers=4, H=16, Hkv=8, G=1, L=8192, bits=4, prompt=8192, prefill_attention=True,
                      desc="causal prefill attention over the packed cache of one 8192-token prompt (16/8 heads, kv_bits=4), 4 layers"),
     "c4": dict(layers=36, H=32, Hkv=8, G=128, L=16384, bits=4, prompt=100, ragged=True,
@@ -387,23 +390,34 @@ def run_prefill_attention(args, w, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     T, H, Hkv, bits, NL = w["L"], w["H"], w["Hkv"], w["bits"], w["layers"]
+    B = w.get("batch", 0)   # > 0: that many prompts per launch through the engine handle (cache write + attention)
     kv_dim, q_dim = Hkv * D, H * D
     eng = tq.Engine(T, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
-    eng.alloc_batch(1, T)
+    eng.alloc_batch(max(1, B), T)
     gen = torch.Generator(device="cuda").manual_seed(4321)
     scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
-    for layer in range(NL):
-        kp, vp = synth.torch_kv(gen, T, kv_dim, scales)
-        eng.prefill_append(layer, 0, kp, vp, 0)
-    caches = [eng.layer_cache(layer) for layer in range(NL)]
-    R = ops.rotation_matrix().cuda()
-    q = torch.randn(NL, T, q_dim, generator=gen, device="cuda").to(torch.float16)
-    out = torch.empty_like(q)
+    if B:
+        kp, vp = synth.torch_kv(gen, B * T, kv_dim, scales)
+        kp, vp = kp.view(B, T, kv_dim), vp.view(B, T, kv_dim)
+        qb = torch.randn(B, T, q_dim, generator=gen, device="cuda").to(torch.float16)
+        outb = torch.empty_like(qb)
 
-    def step():
+        def step():
+            for layer in range(NL):
+                eng.prefill_layer_batch(layer, 0, qb, kp, vp, outb)
+    else:
         for layer in range(NL):
-            ck, cv, kn, vn = caches[layer]
-            ops.launch_turbo_gqa_prefill_attention(out[layer], q[layer], ck, cv, kn, vn, R, None, T, T, H, Hkv, D, q_dim, kv_dim, bits)
+            kp, vp = synth.torch_kv(gen, T, kv_dim, scales)
+            eng.prefill_append(layer, 0, kp, vp, 0)
+        caches = [eng.layer_cache(layer) for layer in range(NL)]
+        R = ops.rotation_matrix().cuda()
+        q = torch.randn(NL, T, q_dim, generator=gen, device="cuda").to(torch.float16)
+        out = torch.empty_like(q)
+
+        def step():
+            for layer in range(NL):
+                ck, cv, kn, vn = caches[layer]
+                ops.launch_turbo_gqa_prefill_attention(out[layer], q[layer], ck, cv, kn, vn, R, None, T, T, H, Hkv, D, q_dim, kv_dim, bits)
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -421,9 +435,10 @@ def run_prefill_attention(args, w, rank, world, local_rank):
     torch.cuda.profiler.stop()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / steps
-    flops = NL * 2.0 * 2.0 * D * H * T * (T + 1) / 2.0          # QK^T and PV over the causal half
+    NP = max(1, B)
+    flops = NP * NL * 2.0 * 2.0 * D * H * T * (T + 1) / 2.0          # QK^T and PV over the causal half
     vpb = 4 if bits == 2 else 2
-    bytes_step = NL * (T * (2 * Hkv * D // vpb + 4 * Hkv) + 4 * T * q_dim)
+    bytes_step = NP * NL * (T * (2 * Hkv * D // vpb + 4 * Hkv) + 4 * T * q_dim + (4 * T * kv_dim if B else 0))
     tf_peak = None
     try:
         tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
@@ -435,8 +450,8 @@ def run_prefill_attention(args, w, rank, world, local_rank):
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 codes -> f16 tiles, f16 mma.sync, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["desc"], "kv_bits": bits, "l2": "each step reads every layer's cache and queries again (one prompt fits L2: compute bound)"},
-        "us_per_layer": ms * 1e3 / NL, "causal_tflops": tfs,
-        "gpu_launches": steps * NL,   # one launch per layer
+        "us_per_layer": ms * 1e3 / NL, "us_per_prompt_and_layer": ms * 1e3 / NL / NP, "causal_tflops": tfs,
+        "gpu_launches": steps * NL * (2 if B else 1),   # (cache write +) attention, one launch each per layer
         "roofline": {"kernel": f"prefill_attention_kernel<{bits}> (mma.sync)", "bound": "tensor",
                      "achieved": tfs, "peak": tf_peak, "unit": "TFLOP/s", "frac": tfs / tf_peak,
                      "peak_kind": "measured cuBLAS bf16 (tcgen05); this kernel issues mma.sync", "traffic": None},

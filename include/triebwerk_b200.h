@@ -363,6 +363,10 @@ int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n
  * Packed modes and kv_bits = 0; sequences behind a shared prefix are refused (TQ_ERR_STATE). */
 int tq_engine_prefill_layer(tq_engine* e, int layer, int seq, const void* q, const void* k, const void* v, void* out, int T,
                             int q_stride, tq_stream_t s);
+/* The same for the n_seq prompts of T tokens of the sequences first_seq .. : q and out [n_seq][T][q_stride], k/v
+ * [n_seq][T][kv_dim]; one append launch and one attention launch for all of them. */
+int tq_engine_prefill_layer_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* q, const void* k, const void* v,
+                                  void* out, int T, int q_stride, tq_stream_t s);
 
 /* A prompt of T tokens shared by the n_seq sequences first_seq .. (rollouts of one prompt; the reference prefills
  * sequence 0 and copies its cache to the other sequences, engine/engine.cpp:2173-2214, 2296).  The first

@@ -552,3 +552,36 @@ def test_prefill_layer_of_a_prompt_against_oracle(bits):
     assert eng.status() == 0
     with pytest.raises(Exception):
         eng.prefill_layer(0, 0, gu.dev(q2), gu.dev(k), gu.dev(v), out)   # T = 200 > 64 rows
+
+
+@pytest.mark.parametrize("bits", [4, 0])
+def test_prefill_layer_batch_equals_prompt_by_prompt(bits):
+    """Several prompts in one launch give the bits that the same prompts give one at a time, in dense and in ragged
+    slots, and the first of them agrees with the oracle."""
+    H, Hkv, D, NL, T, n = 16, 8, 128, 1, 130, 3
+    kv_dim, q_dim = Hkv * D, H * D
+    rng = np.random.default_rng(900 + bits)
+    k = rng.standard_normal((n, T, kv_dim), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((n, T, kv_dim), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((n, T, q_dim), dtype=np.float32).astype(np.float16)
+    for caps in (None, [160, 256, 192, 64]):
+        eng = tq.Engine(256, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+        eng.alloc_batch(4, 256, caps)
+        together = gu.host(eng.prefill_layer_batch(0, 0, gu.dev(q), gu.dev(k), gu.dev(v)))
+        caches_a = [t.clone() for t in eng.layer_cache(0) if t is not None]
+        eng.reset()
+        single = np.stack([gu.host(eng.prefill_layer(0, i, gu.dev(q[i]), gu.dev(k[i]), gu.dev(v[i]))) for i in range(n)])
+        assert (together.view(np.uint16) == single.view(np.uint16)).all()
+        for a, b in zip(caches_a, [t for t in eng.layer_cache(0) if t is not None]):
+            assert torch.equal(a, b)
+        assert eng.status() == 0
+    if bits == 4:
+        R, _ = tqo.rotation()
+        msl = 160
+        ck, kn = tqo.alloc_cache(1, msl, Hkv, D, bits)
+        cv, vn = tqo.alloc_cache(1, msl, Hkv, D, bits)
+        pos = np.arange(T, dtype=np.int32)
+        tqo.append_tokens(ck, kn, k[0], R, pos, msl, Hkv, D, bits)
+        tqo.append_tokens(cv, vn, v[0], R, pos, msl, Hkv, D, bits)
+        ref, _ = tqo.prefill_attention(q[0], ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
+        hp.assert_attention_close(together[0], ref, H, D, "first prompt of the batch")

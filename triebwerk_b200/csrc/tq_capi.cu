@@ -1719,30 +1719,41 @@ int tq_engine_prefill_append_batch(tq_engine* e, int layer, int first_seq, int n
     return engine_prefill_impl(e, layer, first_seq, n_seq, k, v, first_pos, T, s);
 }
 
-// One layer of a prompt's prefill (reference engine/engine.cpp:2110-2146: cache write of all T tokens, then causal
-// self-attention): the T tokens of sequence `seq` go to positions 0 .. T-1 of its slot and query token t attends to
-// rows 0 .. t.  q [T][q_stride] and out [T][q_stride] share the stride (the reference passes Q_PROJ_DIM for both).
-int tq_engine_prefill_layer(tq_engine* e, int layer, int seq, const void* q, const void* k, const void* v, void* out, int T,
-                            int q_stride, tq_stream_t s) {
+// One layer of the prefill of n_seq prompts of T tokens each (reference engine/engine.cpp:2110-2146 for one prompt: cache
+// write of all T tokens, then causal self-attention): the tokens of sequence first_seq + i go to positions 0 .. T-1 of its
+// slot and its query token t attends to rows 0 .. t.  q [n_seq][T][q_stride] and out [n_seq][T][q_stride] share the stride
+// (the reference passes Q_PROJ_DIM for both).  All prompts' blocks are one launch, the longest causal prefixes first.
+int tq_engine_prefill_layer_batch(tq_engine* e, int layer, int first_seq, int n_seq, const void* q, const void* k, const void* v,
+                                  void* out, int T, int q_stride, tq_stream_t s) {
     if (!e || !q || !out) return TQ_ERR_ARG;
-    int r = engine_prefill_impl(e, layer, seq, 1, k, v, 0, T, s);
+    int r = engine_prefill_impl(e, layer, first_seq, n_seq, k, v, 0, T, s);
     if (r != TQ_OK) return r;
     const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads;
     if (q_stride < H * HEAD_DIM || (q_stride & 7) != 0) return TQ_ERR_ARG;
-    if (e->prefix_tokens[seq] > 0) return TQ_ERR_STATE;   // a slot that begins behind a shared prefix holds no rows 0 .. P-1
+    int cap = e->cap_eff(first_seq);
+    for (int i = 0; i < n_seq; ++i) {
+        // a slot that begins behind a shared prefix holds no rows 0 .. P-1
+        if (e->prefix_tokens[first_seq + i] > 0) return TQ_ERR_STATE;
+        cap = std::min(cap, e->cap_eff(first_seq + i));
+    }
     const tq_engine::Layer& L = e->layers[layer];
-    const long long row0 = e->row0_eff(seq);
-    const int cap = e->cap_eff(seq);
-    if (!prefill_attn_shape(H, Hkv)) {   // layouts outside the tiled kernel: the compat launchers' generic path
+    const size_t row_bytes = e->code_row_bytes();
+    if (!prefill_attn_shape(H, Hkv)) {   // layouts outside the tiled kernel: the compat launchers' generic path, prompt by prompt
         std::lock_guard<std::recursive_mutex> compat_lock(compat_mutex());
-        if (e->kv_bits == 0)
-            launch_gqa_prefill_attention(out, q, (const char*)L.k + (size_t)row0 * e->kv_dim() * 2, (const char*)L.v + (size_t)row0 * e->kv_dim() * 2,
-                                         nullptr, T, cap, H, Hkv, HEAD_DIM, q_stride, e->kv_dim(), s);
-        else
-            launch_turbo_gqa_prefill_attention(out, q, (const uint8_t*)L.k + (size_t)row0 * e->code_row_bytes(), (const uint8_t*)L.v + (size_t)row0 * e->code_row_bytes(),
-                                               (const __half*)L.kn + (size_t)row0 * Hkv, (const __half*)L.vn + (size_t)row0 * Hkv, e->d_rotation,
-                                               nullptr, T, cap, H, Hkv, HEAD_DIM, q_stride, e->kv_dim(), e->kv_bits, s);
-        return tq_last_compat_status();
+        for (int i = 0; i < n_seq && r == TQ_OK; ++i) {
+            const long long row0 = e->row0_eff(first_seq + i);
+            const char* qi = (const char*)q + (size_t)i * T * q_stride * 2;
+            char* oi = (char*)out + (size_t)i * T * q_stride * 2;
+            if (e->kv_bits == 0)
+                launch_gqa_prefill_attention(oi, qi, (const char*)L.k + (size_t)row0 * row_bytes, (const char*)L.v + (size_t)row0 * row_bytes,
+                                             nullptr, T, cap, H, Hkv, HEAD_DIM, q_stride, e->kv_dim(), s);
+            else
+                launch_turbo_gqa_prefill_attention(oi, qi, (const uint8_t*)L.k + (size_t)row0 * row_bytes, (const uint8_t*)L.v + (size_t)row0 * row_bytes,
+                                                   (const __half*)L.kn + (size_t)row0 * Hkv, (const __half*)L.vn + (size_t)row0 * Hkv,
+                                                   e->d_rotation, nullptr, T, cap, H, Hkv, HEAD_DIM, q_stride, e->kv_dim(), e->kv_bits, s);
+            r = tq_last_compat_status();
+        }
+        return r;
     }
     PrefillAttnParams ap{};
     ap.q = (const __half*)q;
@@ -1753,20 +1764,26 @@ int tq_engine_prefill_layer(tq_engine* e, int layer, int seq, const void* q, con
     ap.rows = cap;
     ap.H = H;
     ap.Hkv = Hkv;
+    ap.n_seq = n_seq;
+    ap.seq_rows = e->msl;
+    ap.row_base = e->rb() ? e->rb() + first_seq : nullptr;
+    const long long row0 = ap.row_base ? 0 : e->row0_eff(first_seq);   // dense slots: first_seq * max_seq_len
+    ap.ck = (const uint8_t*)L.k + (size_t)row0 * row_bytes;
+    ap.cv = (const uint8_t*)L.v + (size_t)row0 * row_bytes;
     if (e->kv_bits == 0) {
-        const size_t row_bytes = (size_t)e->kv_dim() * 2;
-        ap.ck = (const uint8_t*)L.k + (size_t)row0 * row_bytes;
-        ap.cv = (const uint8_t*)L.v + (size_t)row0 * row_bytes;
         ap.score_scale = 0.12751743074602467f;
     } else {
-        ap.ck = (const uint8_t*)L.k + (size_t)row0 * e->code_row_bytes();
-        ap.cv = (const uint8_t*)L.v + (size_t)row0 * e->code_row_bytes();
         ap.kn = (const __half*)L.kn + (size_t)row0 * Hkv;
         ap.vn = (const __half*)L.vn + (size_t)row0 * Hkv;
         ap.rotation = (const __half*)e->d_rotation;
         ap.score_scale = 1.0f;
     }
     return launch_prefill_attention(e->kv_bits, ap, cs(s));
+}
+
+int tq_engine_prefill_layer(tq_engine* e, int layer, int seq, const void* q, const void* k, const void* v, void* out, int T,
+                            int q_stride, tq_stream_t s) {
+    return tq_engine_prefill_layer_batch(e, layer, seq, 1, q, k, v, out, T, q_stride, s);
 }
 
 int tq_engine_decode_step_host(tq_engine* e, const void* q_host, const void* k_host, const void* v_host, void* out_host,

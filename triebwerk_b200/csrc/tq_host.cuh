@@ -356,7 +356,9 @@ inline int launch_prefill_attention(int bits, PrefillAttnParams p, cudaStream_t 
     p.grp_shift = 0;
     while ((1 << p.grp_shift) < grp) ++p.grp_shift;
     const int qt = PFA_ROWS >> p.grp_shift;
-    dim3 grid((unsigned)((p.T + qt - 1) / qt), (unsigned)p.Hkv);
+    if (p.n_seq <= 0) p.n_seq = 1;
+    if ((long long)p.Hkv * p.n_seq > 2147483647ll || (p.T + qt - 1) / qt > 65535) return TQ_ERR_CAPACITY;
+    dim3 grid((unsigned)(p.Hkv * p.n_seq), (unsigned)((p.T + qt - 1) / qt));
     if (p.T <= 0) return TQ_OK;
     int ar;
     switch (bits) {

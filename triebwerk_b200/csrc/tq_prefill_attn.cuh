@@ -49,6 +49,11 @@ struct PrefillAttnParams {
     int T;                    // query tokens = cache rows in use
     int rows;                 // cache rows that exist (loads are clamped to them)
     int H, Hkv, grp_shift;    // GRP = 1 << grp_shift query heads per KV head
+    // Several prompts of the same length in one launch (grid.x = Hkv * n_seq): prompt i reads its queries and writes its
+    // results T * q_tok_stride halves behind prompt i - 1's, and its cache rows start at row_base[i] (or i * seq_rows).
+    int n_seq;
+    long long seq_rows;
+    const long long* row_base;
     float score_scale;        // fp16 form: log2(e) / sqrt(128); packed forms: 1 (the rotated queries carry it)
 };
 
@@ -59,13 +64,21 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gl = lane >> 2, t4 = lane & 3;
     const int gs = p.grp_shift, GRP = 1 << gs, QT = PFA_ROWS >> gs;
-    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // the blocks with the longest prefixes start first
-    const int kvh = blockIdx.y;
+    const int qb = (int)gridDim.y - 1 - (int)blockIdx.y;  // the blocks with the longest prefixes start first, of all heads
+    const int seq = (int)blockIdx.x / p.Hkv;               // and prompts
+    const int kvh = (int)blockIdx.x - seq * p.Hkv;
     const int q0 = qb * QT;
     const int q_last = min(q0 + QT, p.T) - 1;
     const int n_tiles = q_last / PFA_KT + 1;
     constexpr int ROW_BYTES = BITS == 4 ? 64 : BITS == 2 ? 32 : 256;  // bytes of one head in a cache row
     const size_t row_stride = (size_t)p.Hkv * ROW_BYTES;
+    const long long seq_row0 = p.row_base ? p.row_base[seq] : (long long)seq * p.seq_rows;
+    const __half* const q_seq = p.q + (size_t)seq * (size_t)p.T * (size_t)p.q_tok_stride;
+    __half* const out_seq = p.out + (size_t)seq * (size_t)p.T * (size_t)p.q_dim;
+    const uint8_t* const ck_seq = p.ck + (size_t)seq_row0 * row_stride;
+    const uint8_t* const cv_seq = p.cv + (size_t)seq_row0 * row_stride;
+    const __half* const kn_seq = BITS != 0 ? p.kn + (size_t)seq_row0 * p.Hkv : nullptr;
+    const __half* const vn_seq = BITS != 0 ? p.vn + (size_t)seq_row0 * p.Hkv : nullptr;
 
     // ---- byte (4-bit) or nibble (2-bit) -> two fp16 centroids, one column per lane: no bank conflicts ----
     if (BITS == 4) {
@@ -86,8 +99,8 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     {
         const int r_lo = 16 * warp + gl, r_hi = r_lo + 8;
         const int tok_lo = q0 + (r_lo >> gs), tok_hi = q0 + (r_hi >> gs);
-        const __half* ql = p.q + (size_t)tok_lo * p.q_tok_stride + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
-        const __half* qh = p.q + (size_t)tok_hi * p.q_tok_stride + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
+        const __half* ql = q_seq + (size_t)tok_lo * p.q_tok_stride + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
+        const __half* qh = q_seq + (size_t)tok_hi * p.q_tok_stride + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             qa[ks][0] = tok_lo < p.T ? __ldg(reinterpret_cast<const uint32_t*>(ql + 16 * ks)) : 0u;
@@ -108,8 +121,8 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     auto fetch = [&](int j) {
         int row = j * PFA_KT + tr;
         row = min(row, p.rows - 1);
-        const uint8_t* kp = p.ck + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
-        const uint8_t* vp = p.cv + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
+        const uint8_t* kp = ck_seq + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
+        const uint8_t* vp = cv_seq + (size_t)row * row_stride + (size_t)kvh * ROW_BYTES;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {  // chunk c + 4 i: 16 fp16 bytes = 8 coordinates = 4 (4-bit) / 2 (2-bit) code bytes
             const int ch = c + 4 * i;
@@ -118,7 +131,7 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
         }
         if (BITS != 0 && tid < 2 * PFA_KT) {
             const int r = min(j * PFA_KT + (tid & (PFA_KT - 1)), p.rows - 1);
-            nrm_next = (tid < PFA_KT ? p.kn : p.vn)[(size_t)r * p.Hkv + kvh];
+            nrm_next = (tid < PFA_KT ? kn_seq : vn_seq)[(size_t)r * p.Hkv + kvh];
         }
     };
     auto dequant = [&](Raw w) -> uint4 {
@@ -315,8 +328,8 @@ __global__ void __launch_bounds__(PFA_THREADS, 1) prefill_attention_kernel(const
     const float inv_lo = 1.0f / (l_lo + 1e-8f), inv_hi = 1.0f / (l_hi + 1e-8f);
     const int r_lo = 16 * warp + gl, r_hi = r_lo + 8;
     const int otok_lo = q0 + (r_lo >> gs), otok_hi = q0 + (r_hi >> gs);
-    __half* dst_lo = p.out + (size_t)otok_lo * p.q_dim + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
-    __half* dst_hi = p.out + (size_t)otok_hi * p.q_dim + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
+    __half* dst_lo = out_seq + (size_t)otok_lo * p.q_dim + (size_t)(kvh * GRP + (r_lo & (GRP - 1))) * HEAD_DIM + 2 * t4;
+    __half* dst_hi = out_seq + (size_t)otok_hi * p.q_dim + (size_t)(kvh * GRP + (r_hi & (GRP - 1))) * HEAD_DIM + 2 * t4;
     if (BITS == 0) {
 #pragma unroll
         for (int nb = 0; nb < 16; ++nb) {

@@ -208,6 +208,16 @@ class Engine:
                                             k.shape[0], q.shape[1], self._stream()), "prefill_layer")
         return out
 
+    def prefill_layer_batch(self, layer: int, first_seq: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor = None):
+        """prefill_layer for the prompts of several sequences at once: q [n, T, q_stride], k/v [n, T, kv_dim]."""
+        for t in (q, k, v):
+            assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16 and t.dim() == 3
+        if out is None:
+            out = torch.empty_like(q)
+        check(lib().tq_engine_prefill_layer_batch(self._h, layer, first_seq, k.shape[0], q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                  out.data_ptr(), k.shape[1], q.shape[2], self._stream()), "prefill_layer_batch")
+        return out
+
     def prefill_append(self, layer: int, seq: int, k: torch.Tensor, v: torch.Tensor, first_pos: int = 0) -> None:
         """Token-form append of k/v [T, kv_dim] for one sequence (reference engine/engine.cpp:2121-2130)."""
         assert k.is_cuda and v.is_cuda and k.is_contiguous() and v.is_contiguous()
