@@ -1776,8 +1776,10 @@ int tq_engine_prefill_layer_batch(tq_engine* e, int layer, int first_seq, int n_
         ap.kn = (const __half*)L.kn + (size_t)row0 * Hkv;
         ap.vn = (const __half*)L.vn + (size_t)row0 * Hkv;
         ap.rotation = (const __half*)e->d_rotation;
+        ap.rotation_t = (const __half*)e->d_rotation_t;
         ap.score_scale = 1.0f;
     }
+    ap.status = (int*)e->workspace;
     return launch_prefill_attention(e->kv_bits, ap, cs(s));
 }
 

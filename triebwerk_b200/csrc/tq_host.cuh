@@ -24,6 +24,7 @@
 #include "tq_qrot.cuh"
 #include "tq_generic.cuh"
 #include "tq_prefill_attn.cuh"
+#include "tq_prefill_attn_tc.cuh"
 
 namespace tq {
 
@@ -361,6 +362,18 @@ inline int launch_prefill_attention(int bits, PrefillAttnParams p, cudaStream_t 
     dim3 grid((unsigned)(p.Hkv * p.n_seq), (unsigned)((p.T + qt - 1) / qt));
     if (p.T <= 0) return TQ_OK;
     int ar;
+    // tcgen05 form (TQ_PREFILL_ATTN_TC=1): 4-bit cache (needs R^T) and fp16 cache
+    static const bool tc = getenv("TQ_PREFILL_ATTN_TC") && atoi(getenv("TQ_PREFILL_ATTN_TC")) != 0;
+    if (tc && ((bits == 4 && p.rotation_t) || bits == 0)) {
+        if (bits == 4) {
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_tc_kernel<4>, PTC_DYN_SMEM)) != TQ_OK) return ar;
+            prefill_attention_tc_kernel<4><<<grid, PTC_THREADS, PTC_DYN_SMEM, s>>>(p);
+        } else {
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_tc_kernel<0>, PTC_DYN_SMEM)) != TQ_OK) return ar;
+            prefill_attention_tc_kernel<0><<<grid, PTC_THREADS, PTC_DYN_SMEM, s>>>(p);
+        }
+        return cuda_status(cudaGetLastError());
+    }
     switch (bits) {
         case 4:
             if ((ar = ensure_dynamic_smem((const void*)prefill_attention_kernel<4>, PfaSmem::BYTES)) != TQ_OK) return ar;

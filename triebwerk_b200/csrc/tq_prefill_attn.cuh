@@ -44,6 +44,8 @@ struct PrefillAttnParams {
     const __half* kn;         // [rows][Hkv] (packed forms)
     const __half* vn;
     const __half* rotation;   // packed forms: R row-major [128][128] (the way back out of the rotated space)
+    const __half* rotation_t; // tcgen05 form, packed: R^T row-major [128][128] (null: the mma.sync form is used)
+    int* status;              // optional device status word (a bounded wait that gave up raises it)
     __half* out;              // [T][q_dim]
     int q_dim;
     int T;                    // query tokens = cache rows in use
