@@ -5,12 +5,14 @@
 // from shared memory by the tensor core itself and the accumulators in tensor memory, so no warp spends its
 // shared-memory bandwidth on ldmatrix:
 //   * one CTA = 128 score rows (128 / GRP query tokens x the GRP query heads of one KV head) = the M dimension, 256 threads;
-//   * warps 0-3 ("row threads": thread r owns score row r = TMEM lane r) do the softmax and keep the output row in
-//     registers; warps 4-7 dequantise the cache tiles: K as [64 tokens][128 coordinates] (the B operand of S = Q . K^T) and
-//     V TRANSPOSED as [128 coordinates][64 tokens] (the B operand of O += P . V), both fp16 in the canonical K-major
-//     128-byte-swizzled layout, double buffered and handed over through mbarriers;
+//   * warps 0-3 ("row threads": thread r owns score row r = TMEM lane r) do the softmax; warps 4-7 dequantise the cache
+//     tiles: K as [64 tokens][128 coordinates] (the B operand of S = Q . K^T) and V TRANSPOSED as [128 coordinates][64
+//     tokens] (the B operand of O += P . V; transposed 8 x 8 blocks at a time with ldmatrix.trans + stmatrix), both fp16
+//     in the canonical K-major 128-byte-swizzled layout, double buffered and handed over through mbarriers;
 //   * per 64-row tile: S (128 x 64, fp32) -> tensor memory -> registers; K norm, causal limit, online softmax; P (times the
-//     V norm, fp16) -> shared memory as an A operand; P . V -> tensor memory -> added to the output row in registers;
+//     V norm, fp16) -> shared memory as an A operand; O += P . V accumulates in tensor memory, and a warp rescales its 32
+//     output rows in place (tcgen05.ld / .st) only in tiles where one of their maxima grew; the score product of tile
+//     j + 1 is issued together with the value product of tile j;
 //   * packed forms: the query rotation (Q . R^T) at the start and the way back (O . R, with O split into fp16 high and low
 //     parts) at the end are tcgen05 products as well.
 // Every wait on a barrier is bounded; a wait that runs out raises the status word and the kernel runs to its end.
@@ -24,13 +26,16 @@ namespace tq {
 constexpr int PTC_THREADS = 256;
 constexpr int PTC_KT = 64;  // cache rows per tile
 
+constexpr int PTC_STAGES = 3;  // K / V tile buffers
+
 struct PtcSmem {
     static constexpr uint32_t Q = 0;            // A operand [2 regions][128 rows][128 B]; at the end: high parts of the results
-    static constexpr uint32_t K = 32768;        // 2 buffers x [2 regions][64 rows][128 B]; at the start: R; at the end: low parts
-    static constexpr uint32_t V = 65536;        // 2 buffers x [128 coordinate rows][128 B = 64 tokens]; at the end: R^T
-    static constexpr uint32_t P = 98304;        // A operand [128 rows][128 B = 64 tokens]
-    static constexpr uint32_t NORM = 114688;    // [2 buffers][K, V][64] halves
-    static constexpr uint32_t CTRL = NORM + 512;  // mbarriers: mma, ready[2], free[2]; tensor-memory base
+    static constexpr uint32_t K = 32768;        // PTC_STAGES x [2 regions][64 rows][128 B]; at the start: R; at the end: low parts
+    static constexpr uint32_t V = K + PTC_STAGES * 16384;   // PTC_STAGES x [128 coordinate rows][128 B = 64 tokens]; at the end: R^T
+    static constexpr uint32_t P = V + PTC_STAGES * 16384;   // A operand [128 rows][128 B = 64 tokens]
+    static constexpr uint32_t VRM = P + 16384;  // V tile as it lies in the cache, [64 tokens][256 B], chunk c of row r at c ^ (r & 7)
+    static constexpr uint32_t NORM = VRM + 16384;  // [PTC_STAGES][K, V][64] halves
+    static constexpr uint32_t CTRL = NORM + 1024;  // mbarriers: score product, value product, ready[], free[]; tensor-memory base
     static constexpr uint32_t LUT = CTRL + 128;   // 4-bit: [256][32 lanes] half2
     static constexpr uint32_t BYTES = LUT + 32768;
 };
@@ -38,6 +43,23 @@ constexpr size_t PTC_DYN_SMEM = PtcSmem::BYTES + 1024;  // + alignment slack
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns, registers -> tensor memory (the counterpart of tmem_ld32)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, const uint32_t (&r)[4]) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+                 : "memory");
 }
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -77,9 +99,10 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const __half* const kn_seq = BITS != 0 ? p.kn + (size_t)seq_row0 * p.Hkv + kvh : nullptr;
     const __half* const vn_seq = BITS != 0 ? p.vn + (size_t)seq_row0 * p.Hkv + kvh : nullptr;
 
-    const uint32_t bar_mma = sb + PtcSmem::CTRL;
-    const uint32_t bar_ready0 = sb + PtcSmem::CTRL + 8u, bar_free0 = sb + PtcSmem::CTRL + 24u;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gb + PtcSmem::CTRL + 64);
+    const uint32_t bar_mma = sb + PtcSmem::CTRL;         // score products (and the two rotations)
+    const uint32_t bar_pv = sb + PtcSmem::CTRL + 8u;     // value products
+    const uint32_t bar_ready0 = sb + PtcSmem::CTRL + 16u, bar_free0 = sb + PtcSmem::CTRL + 48u;  // one each per stage
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gb + PtcSmem::CTRL + 96);
     bool dead = false;
     auto give_up = [&]() {
         dead = true;
@@ -88,15 +111,16 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
 
     // ---- once: tensor memory, barriers, table, this block's queries, R ----
     if (warp == 0) {
-        tmem_alloc(sb + PtcSmem::CTRL + 64u, 512u);  // [0, 128): rotation products; [128, 192): S; [256, 384): P . V of a tile
+        tmem_alloc(sb + PtcSmem::CTRL + 96u, 512u);  // [0, 128): rotation products; [128, 192): S; [256, 384): the output rows
         tmem_relinquish();
     }
     if (tid == 0) {
         mbar_init(bar_mma, 1);
-        mbar_init(bar_ready0, 128);
-        mbar_init(bar_ready0 + 8u, 128);
-        mbar_init(bar_free0, 128);
-        mbar_init(bar_free0 + 8u, 128);
+        mbar_init(bar_pv, 1);
+        for (int i = 0; i < PTC_STAGES; ++i) {
+            mbar_init(bar_ready0 + 8u * i, 128);
+            mbar_init(bar_free0 + 8u * i, 128);
+        }
         fence_mbar_init();
     }
     if (BITS == 4) {
@@ -131,7 +155,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     uint32_t mph = 0;  // phase of bar_mma (row threads)
 
     auto wait_mma = [&]() {
-        if (!dead && !mbar_wait_bounded(bar_mma, mph, 1u << 22)) give_up();
+        if (!dead && !mbar_wait_bounded(bar_mma, mph, 1u << 17)) give_up();
         mph ^= 1u;
         tc_fence_after();
     };
@@ -171,103 +195,128 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         tc_fence_after();
     }
 
-    float o[128];
     float m_run = -1e30f, l_run = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.0f;
+    constexpr uint32_t O_COL = 256u;  // tensor-memory columns of the output rows
 
     if (!is_row) {
-        // ================= producers: tile j into buffer j & 1 =================
-        const int pt = tid - 128;
-        const int ktr = pt & 63, kc = pt >> 6;  // K: token row of the tile, half of its 128 coordinates
-        const int vcp = pt & 63, vth = pt >> 6;  // V: coordinate pair (2 vcp, 2 vcp + 1), half of the tile's 64 tokens
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            if (j >= 2 && !dead && !mbar_wait_bounded(bar_free0 + 8u * b, (uint32_t)(((j >> 1) - 1) & 1), 1u << 22)) give_up();
-            const int row0 = j * PTC_KT;
-            uint8_t* kt = gb + PtcSmem::K + (uint32_t)b * 16384u;
-            uint8_t* vt = gb + PtcSmem::V + (uint32_t)b * 16384u;
-            {   // K tile: row ktr, chunks 8 kc .. 8 kc + 7
-                const int row = min(row0 + ktr, p.rows - 1);
-                const bool blank = BITS == 0 && row0 + ktr >= p.T;  // fp16 rows past the prompt may hold anything
-                if (BITS == 4) {
-                    const uint4* src = reinterpret_cast<const uint4*>(ck_seq + (size_t)row * row_stride + 32 * kc);
-                    const uint4 w0 = __ldg(src), w1 = __ldg(src + 1);
-                    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        // ================= producers: tile j into stage j % PTC_STAGES =================
+        const int pt = tid - 128, pw = pt >> 5;
+        const int ktr = pt & 63, kc = pt >> 6;  // token row of the tile, half of its 128 coordinates
+        constexpr int NRAW = BITS == 4 ? 2 : 8;  // 16-byte loads per thread and array
+        uint4 kraw[NRAW], vraw[NRAW];
+        __half nraw = __float2half(1.0f);
+        auto fetch = [&](int j) {  // the raw words of tile j into registers
+            const int row = min(j * PTC_KT + ktr, p.rows - 1);
+            const uint4* ksrc = reinterpret_cast<const uint4*>(ck_seq + (size_t)row * row_stride + (BITS == 4 ? 32 : 128) * kc);
+            const uint4* vsrc = reinterpret_cast<const uint4*>(cv_seq + (size_t)row * row_stride + (BITS == 4 ? 32 : 128) * kc);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        uint4 u;
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.x) : "r"(lut + ((w[i] & 0xffu) << 7)));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.y) : "r"(lut + (((w[i] >> 8) & 0xffu) << 7)));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.z) : "r"(lut + (((w[i] >> 16) & 0xffu) << 7)));
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.w) : "r"(lut + ((w[i] >> 24) << 7)));
-                        *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
-                    }
-                } else {
-                    const uint4* src = reinterpret_cast<const uint4*>(ck_seq + (size_t)row * row_stride + 128 * kc);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint4 u = blank ? make_uint4(0u, 0u, 0u, 0u) : __ldg(src + i);
-                        *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
-                    }
-                }
-            }
-            {   // V tile, transposed: coordinates 2 vcp and 2 vcp + 1 of the tokens 32 vth .. 32 vth + 31
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint32_t x[8];  // (coordinate 2 vcp, coordinate 2 vcp + 1) of 8 consecutive tokens
-#pragma unroll
-                    for (int u8 = 0; u8 < 8; ++u8) {
-                        const int t = 32 * vth + 8 * g + u8;
-                        const int row = min(row0 + t, p.rows - 1);
-                        if (BITS == 4) {
-                            const uint32_t code = __ldg(cv_seq + (size_t)row * row_stride + vcp);
-                            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x[u8]) : "r"(lut + (code << 7)));
-                        } else {
-                            x[u8] = row0 + t >= p.T ? 0u : __ldg(reinterpret_cast<const uint32_t*>(cv_seq + (size_t)row * row_stride) + vcp);
-                        }
-                    }
-                    uint4 lo, hi;  // row 2 vcp: the low halves; row 2 vcp + 1: the high halves
-                    lo.x = prmt(x[0], x[1], 0x5410u); lo.y = prmt(x[2], x[3], 0x5410u);
-                    lo.z = prmt(x[4], x[5], 0x5410u); lo.w = prmt(x[6], x[7], 0x5410u);
-                    hi.x = prmt(x[0], x[1], 0x7632u); hi.y = prmt(x[2], x[3], 0x7632u);
-                    hi.z = prmt(x[4], x[5], 0x7632u); hi.w = prmt(x[6], x[7], 0x7632u);
-                    const int ch = 4 * vth + g;  // 8 tokens = one 16-byte chunk of the 64-token row
-                    *reinterpret_cast<uint4*>(vt + ptc_chunk(0u, 2 * vcp, ch)) = lo;
-                    *reinterpret_cast<uint4*>(vt + ptc_chunk(0u, 2 * vcp + 1, ch)) = hi;
-                }
+            for (int i = 0; i < NRAW; ++i) {
+                kraw[i] = __ldg(ksrc + i);
+                vraw[i] = __ldg(vsrc + i);
             }
             if (BITS != 0) {
-                const int row = min(row0 + (pt & 63), p.rows - 1);
-                reinterpret_cast<__half*>(gb + PtcSmem::NORM)[b * 128 + pt] = (pt < 64 ? kn_seq : vn_seq)[(size_t)row * p.Hkv];
+                const int nrow = min(j * PTC_KT + (pt & 63), p.rows - 1);
+                nraw = (pt < 64 ? kn_seq : vn_seq)[(size_t)nrow * p.Hkv];
+            }
+        };
+        fetch(0);
+        int b = 0, use = 0;  // stage of tile j and how often the stage has been used before
+        for (int j = 0; j < n_tiles; ++j) {
+            if (use > 0 && !dead && !mbar_wait_bounded(bar_free0 + 8u * b, (uint32_t)((use - 1) & 1), 1u << 17)) give_up();
+            const int row0 = j * PTC_KT;
+            uint8_t* kt = gb + PtcSmem::K + (uint32_t)b * 16384u;
+            const uint32_t vt = sb + PtcSmem::V + (uint32_t)b * 16384u;
+            const bool blank = BITS == 0 && row0 + ktr >= p.T;  // fp16 rows past the prompt may hold anything
+            // K tile (the B operand as it is) and V tile (row-major for now): row ktr, chunks 8 kc .. 8 kc + 7
+            if (BITS == 4) {
+                const uint32_t kw[8] = {kraw[0].x, kraw[0].y, kraw[0].z, kraw[0].w, kraw[NRAW > 1 ? 1 : 0].x, kraw[NRAW > 1 ? 1 : 0].y,
+                                        kraw[NRAW > 1 ? 1 : 0].z, kraw[NRAW > 1 ? 1 : 0].w};
+                const uint32_t vw[8] = {vraw[0].x, vraw[0].y, vraw[0].z, vraw[0].w, vraw[NRAW > 1 ? 1 : 0].x, vraw[NRAW > 1 ? 1 : 0].y,
+                                        vraw[NRAW > 1 ? 1 : 0].z, vraw[NRAW > 1 ? 1 : 0].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    uint4 u, w;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.x) : "r"(lut + ((kw[i] & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.y) : "r"(lut + (((kw[i] >> 8) & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.z) : "r"(lut + (((kw[i] >> 16) & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.w) : "r"(lut + ((kw[i] >> 24) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.x) : "r"(lut + ((vw[i] & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.y) : "r"(lut + (((vw[i] >> 8) & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.z) : "r"(lut + (((vw[i] >> 16) & 0xffu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.w) : "r"(lut + ((vw[i] >> 24) << 7)));
+                    *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::VRM + (uint32_t)ktr * 256u + (uint32_t)(((8 * kc + i) ^ (ktr & 7)) << 4)) = w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 u = blank ? make_uint4(0u, 0u, 0u, 0u) : kraw[i < NRAW ? i : 0];
+                    const uint4 w = blank ? make_uint4(0u, 0u, 0u, 0u) : vraw[i < NRAW ? i : 0];
+                    *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::VRM + (uint32_t)ktr * 256u + (uint32_t)(((8 * kc + i) ^ (ktr & 7)) << 4)) = w;
+                }
+            }
+            if (BITS != 0) reinterpret_cast<__half*>(gb + PtcSmem::NORM)[b * 128 + pt] = nraw;
+            if (j + 1 < n_tiles) fetch(j + 1);  // on its way during the transposition and the wait for the next stage
+            named_barrier(1, 128);  // the row-major V tile is complete
+            // V transposed into the B operand [128 coordinate rows][64 tokens]: 8 x 8 blocks through ldmatrix.trans /
+            // stmatrix, four at a time; this warp takes the coordinate blocks 4 pw .. 4 pw + 3
+            {
+                const int mi = lane >> 3, mr = lane & 7;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {  // token block `it` (8 tokens), coordinate blocks 4 pw + mi
+                    const int tok = 8 * it + mr, cb = 4 * pw + mi;
+                    uint32_t r[4];
+                    ldmatrix_x4_trans(r, sb + PtcSmem::VRM + (uint32_t)tok * 256u + (uint32_t)((cb ^ (tok & 7)) << 4));
+                    // matrix mi now holds (row = coordinate 8 cb + l / 4, columns = tokens 8 it + 2 (l % 4), + 1)
+                    const int crow = 8 * cb + mr;
+                    stmatrix_x4(vt + ptc_chunk(0u, crow, it), r);
+                }
             }
             fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
             mbar_arrive(bar_ready0 + 8u * b);
+            named_barrier(1, 128);  // nobody overwrites the row-major tile while a neighbour still transposes it
+            if (++b == PTC_STAGES) {
+                b = 0;
+                ++use;
+            }
         }
     } else {
         // ================= row threads =================
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            if (!dead && !mbar_wait_bounded(bar_ready0 + 8u * b, (uint32_t)((j >> 1) & 1), 1u << 22)) give_up();
+        uint32_t pph = 0;  // phase of bar_pv
+        auto wait_pv = [&]() {
+            if (!dead && !mbar_wait_bounded(bar_pv, pph, 1u << 17)) give_up();
+            pph ^= 1u;
             tc_fence_after();
-            if (tid == 0 && !dead) {  // S = Q . K^T: 128 x 64, 8 steps of 16 coordinates
+        };
+        auto issue_scores = [&](int b, int use) {  // S = Q . K^T of the tile in stage b: 128 x 64, 8 steps of 16 coordinates (one thread)
+            if (!dead && !mbar_wait_bounded(bar_ready0 + 8u * b, (uint32_t)(use & 1), 1u << 17)) give_up();
+            tc_fence_after();
+            if (dead) return;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t ka = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-                    const uint32_t kb = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-                    umma_f16(tmem + 128u, umma_desc_sw128(sb + PtcSmem::Q + ka),
-                             umma_desc_sw128(sb + PtcSmem::K + (uint32_t)b * 16384u + kb), PTC_IDESC_N64, ks != 0);
-                }
-                umma_commit(bar_mma);
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t ka = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+                const uint32_t kb = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
+                umma_f16(tmem + 128u, umma_desc_sw128(sb + PtcSmem::Q + ka), umma_desc_sw128(sb + PtcSmem::K + (uint32_t)b * 16384u + kb),
+                         PTC_IDESC_N64, ks != 0);
+            }
+            umma_commit(bar_mma);
+        };
+        if (tid == 0) issue_scores(0, 0);
+        int b = 0, use = 0, bprev = 0;  // stage of tile j, how often it has been used before, stage of tile j - 1
+        for (int j = 0; j < n_tiles; ++j) {
+            if (tid != 0) {  // (thread 0 waited for the tile when it issued the product) the norms of the tile are read below
+                if (!dead && !mbar_wait_bounded(bar_ready0 + 8u * b, (uint32_t)(use & 1), 1u << 17)) give_up();
             }
             wait_mma();
             uint32_t sr[64];
             tmem_ld32(my_lanes + 128u, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
             tmem_ld32(my_lanes + 160u, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
             tmem_ld_wait();
-            // ---- K norm, causal limit, online softmax; P (times the V norm) as fp16 into the A operand tile ----
+            // ---- K norm, causal limit, online softmax ----
             const bool diagonal = j * PTC_KT + PTC_KT - 1 > q0;
             const uint4* nrm = reinterpret_cast<const uint4*>(gb + PtcSmem::NORM + (uint32_t)b * 256u);
+            const int bnext = b + 1 == PTC_STAGES ? 0 : b + 1, unext = b + 1 == PTC_STAGES ? use + 1 : use;
             float mx = -1e30f;
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
@@ -285,15 +334,36 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const int c = 8 * c8 + e;
-                    float s = __uint_as_float(sr[c]) * (BITS != 0 ? kn8[e] : p.score_scale);
-                    if (diagonal && j * PTC_KT + c > my_tok) s = -1e30f;
-                    sr[c] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
+                    float sv = __uint_as_float(sr[c]) * (BITS != 0 ? kn8[e] : p.score_scale);
+                    if (diagonal && j * PTC_KT + c > my_tok) sv = -1e30f;
+                    sr[c] = __float_as_uint(sv);
+                    mx = fmaxf(mx, sv);
                 }
             }
             const float mn = fmaxf(m_run, mx);
             const float corr = ex2_approx(m_run - mn);
+            const bool grew = mn > m_run;
             m_run = mn;
+            // the value product of the previous tile has read the P tile and updated the output rows
+            if (j > 0) {
+                wait_pv();
+                tc_fence_before();
+                mbar_arrive(bar_free0 + 8u * bprev);  // its stage may take a later tile
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grew)) {  // a row's maximum grew: this warp's output rows are rescaled in place
+#pragma unroll 1
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        uint32_t r[32];
+                        tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                        tmem_st32(my_lanes + O_COL + 32u * c4, r);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // ---- P (times the V norm) as fp16 into the A operand tile ----
             float lsum = 0.0f;
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
@@ -311,8 +381,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 float pv[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float s = __uint_as_float(sr[8 * c8 + e]);
-                    const float pe = s <= -1e30f ? 0.0f : ex2_approx(s - mn);
+                    const float sv = __uint_as_float(sr[8 * c8 + e]);
+                    const float pe = sv <= -1e30f ? 0.0f : ex2_approx(sv - mn);
                     lsum += pe;
                     // (rows past the prompt can hold anything, a norm that is not a number included: select, do not multiply)
                     pv[e] = pe == 0.0f ? 0.0f : (BITS != 0 ? pe * vn8[e] : pe);
@@ -325,42 +395,46 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             l_run = l_run * corr + lsum;
             fence_proxy_async_smem();
             tc_fence_before();
-            named_barrier(2, 128);  // every row's P is written; every row has taken its S out of tensor memory
-            if (tid == 0 && !dead) {  // O_tile = P . V: 128 x 128, 4 steps of 16 tokens
+            named_barrier(2, 128);  // every row's P is written, its S taken out of tensor memory, its output row rescaled
+            if (tid == 0) {
                 tc_fence_after();
+                if (!dead) {  // O += P . V: 128 x 128, 4 steps of 16 tokens
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    umma_f16(tmem + 256u, umma_desc_sw128(sb + PtcSmem::P + 32u * ks),
-                             umma_desc_sw128(sb + PtcSmem::V + (uint32_t)b * 16384u + 32u * ks), PTC_IDESC_N128, ks != 0);
-                umma_commit(bar_mma);
+                    for (int ks = 0; ks < 4; ++ks)
+                        umma_f16(tmem + O_COL, umma_desc_sw128(sb + PtcSmem::P + 32u * ks),
+                                 umma_desc_sw128(sb + PtcSmem::V + (uint32_t)b * 16384u + 32u * ks), PTC_IDESC_N128, (j | ks) != 0);
+                    umma_commit(bar_pv);
+                }
+                if (j + 1 < n_tiles) issue_scores(bnext, unext);  // the next tile's scores run while this tile's values are multiplied
             }
-#pragma unroll
-            for (int i = 0; i < 128; ++i) o[i] *= corr;  // (while the product runs)
-            wait_mma();
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-                uint32_t r[32];
-                tmem_ld32(my_lanes + 256u + 32u * c4, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[32 * c4 + i] += __uint_as_float(r[i]);
-            }
-            tc_fence_before();
-            mbar_arrive(bar_free0 + 8u * b);  // the products that read buffer b (and the P tile) have completed
+            bprev = b;
+            b = bnext;
+            use = unext;
         }
+        wait_pv();  // the last value product
     }
 
     // ================= results =================
     const float inv = 1.0f / (l_run + 1e-8f);
     __half* const dst = out_seq + (size_t)my_tok * p.q_dim + (size_t)my_head * HEAD_DIM;
     if (BITS == 0) {
-        if (is_row && my_tok < p.T) {
+        if (is_row) {
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                uint32_t r[32];
+                tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                tmem_ld_wait();
+                if (my_tok < p.T) {
 #pragma unroll
-            for (int ch = 0; ch < 16; ++ch) {
-                uint4 u;
-                u.x = pack_half2(o[8 * ch] * inv, o[8 * ch + 1] * inv); u.y = pack_half2(o[8 * ch + 2] * inv, o[8 * ch + 3] * inv);
-                u.z = pack_half2(o[8 * ch + 4] * inv, o[8 * ch + 5] * inv); u.w = pack_half2(o[8 * ch + 6] * inv, o[8 * ch + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + 8 * ch) = u;
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 u;
+                        u.x = pack_half2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+                        u.y = pack_half2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+                        u.z = pack_half2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+                        u.w = pack_half2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + 32 * c4 + 8 * i) = u;
+                    }
+                }
             }
         }
     } else {
@@ -368,21 +442,27 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         // parts, times R^T [d][k] (the B operand's rows are the output coordinates)
         __syncthreads();  // every product of the tile loop has completed (each row thread waited for the last one)
         if (is_row) {
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                uint32_t r[32];
+                tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                tmem_ld_wait();
 #pragma unroll
-            for (int ch = 0; ch < 16; ++ch) {
-                uint4 uh, ul;
-                uint32_t* ph = &uh.x;
-                uint32_t* pl = &ul.x;
+                for (int i = 0; i < 4; ++i) {
+                    uint4 uh, ul;
+                    uint32_t* ph = &uh.x;
+                    uint32_t* pl = &ul.x;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float x0 = o[8 * ch + 2 * e] * inv, x1 = o[8 * ch + 2 * e + 1] * inv;
-                    const __half2 h = __floats2half2_rn(x0, x1);
-                    const float2 f = __half22float2(h);
-                    ph[e] = *reinterpret_cast<const uint32_t*>(&h);
-                    pl[e] = pack_half2(x0 - f.x, x1 - f.y);
+                    for (int e = 0; e < 4; ++e) {
+                        const float x0 = __uint_as_float(r[8 * i + 2 * e]) * inv, x1 = __uint_as_float(r[8 * i + 2 * e + 1]) * inv;
+                        const __half2 h = __floats2half2_rn(x0, x1);
+                        const float2 f = __half22float2(h);
+                        ph[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        pl[e] = pack_half2(x0 - f.x, x1 - f.y);
+                    }
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, tid, 4 * c4 + i)) = uh;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, tid, 4 * c4 + i)) = ul;
                 }
-                *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, tid, ch)) = uh;
-                *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, tid, ch)) = ul;
             }
         }
         for (int i = tid; i < 128 * 16; i += PTC_THREADS) {
