@@ -4,15 +4,18 @@
 // query token t of a prompt attends to cache rows 0 .. t.  Here the products run as tcgen05.mma with the operands read
 // from shared memory by the tensor core itself and the accumulators in tensor memory, so no warp spends its
 // shared-memory bandwidth on ldmatrix:
-//   * one CTA = 128 score rows (128 / GRP query tokens x the GRP query heads of one KV head) = the M dimension, 256 threads;
-//   * warps 0-3 ("row threads": thread r owns score row r = TMEM lane r) do the softmax; warps 4-7 dequantise the cache
+//   * one CTA = 128 score rows (128 / GRP query tokens x the GRP query heads of one KV head) = the M dimension, 13 warps;
+//   * warps 0-7 do the softmax, two threads per score row (row = TMEM lane; warps w and w + 4 reach the same lanes and take
+//     one half of a tile's 64 columns each, their row maxima meet through shared memory); warp 12 issues every product
+//     (one thread); warps 8-11 dequantise the cache
 //     tiles: K as [64 tokens][128 coordinates] (the B operand of S = Q . K^T) and V TRANSPOSED as [128 coordinates][64
 //     tokens] (the B operand of O += P . V; transposed 8 x 8 blocks at a time with ldmatrix.trans + stmatrix), both fp16
 //     in the canonical K-major 128-byte-swizzled layout, double buffered and handed over through mbarriers;
 //   * per 64-row tile: S (128 x 64, fp32) -> tensor memory -> registers; K norm, causal limit, online softmax; P (times the
 //     V norm, fp16) -> shared memory as an A operand; O += P . V accumulates in tensor memory, and a warp rescales its 32
-//     output rows in place (tcgen05.ld / .st) only in tiles where one of their maxima grew; the score product of tile
-//     j + 1 is issued together with the value product of tile j;
+//     output rows in place (tcgen05.ld / .st) only in tiles where one of their maxima grew; S is double buffered in
+//     tensor memory and the score product of tile j + 2 follows the value product of tile j on the tensor pipe, so the
+//     scores of the next tile are waiting when the softmax threads finish a tile;
 //   * packed forms: the query rotation (Q . R^T) at the start and the way back (O . R, with O split into fp16 high and low
 //     parts) at the end are tcgen05 products as well.
 // Every wait on a barrier is bounded; a wait that runs out raises the status word and the kernel runs to its end.
@@ -23,7 +26,7 @@
 
 namespace tq {
 
-constexpr int PTC_THREADS = 256;
+constexpr int PTC_THREADS = 416;  // 8 softmax warps, 4 producer warps, 1 warp that issues the products
 constexpr int PTC_KT = 64;  // cache rows per tile
 
 constexpr int PTC_STAGES = 3;  // K / V tile buffers
@@ -35,8 +38,9 @@ struct PtcSmem {
     static constexpr uint32_t P = V + PTC_STAGES * 16384;   // A operand [128 rows][128 B = 64 tokens]
     static constexpr uint32_t VRM = P + 16384;  // V tile as it lies in the cache, [64 tokens][256 B], chunk c of row r at c ^ (r & 7)
     static constexpr uint32_t NORM = VRM + 16384;  // [PTC_STAGES][K, V][64] halves
-    static constexpr uint32_t CTRL = NORM + 1024;  // mbarriers: score product, value product, ready[], free[]; tensor-memory base
-    static constexpr uint32_t LUT = CTRL + 128;   // 4-bit: [256][32 lanes] half2
+    static constexpr uint32_t CTRL = NORM + 1024;  // mbarriers and the tensor-memory base
+    static constexpr uint32_t XCH = CTRL + 128;   // float[2][256]: exchange between the two threads of a score row (by tile parity)
+    static constexpr uint32_t LUT = XCH + 2048;   // 4-bit: [256][32 lanes] half2
     static constexpr uint32_t BYTES = LUT + 32768;
 };
 constexpr size_t PTC_DYN_SMEM = PtcSmem::BYTES + 1024;  // + alignment slack
@@ -81,7 +85,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const uint32_t sb = (smem_u32(ptc_smem) + 1023u) & ~1023u;
     uint8_t* gb = ptc_smem + (sb - smem_u32(ptc_smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool is_row = tid < 128;
+    // roles: warps 0-7 softmax (thread = score row 32 (warp & 3) + lane, column half warp >> 2), 8-11 producers, 12 issues the products
+    const bool is_soft = warp < 8, is_prod = warp >= 8 && warp < 12, is_mma = warp == 12;
     const int gs = p.grp_shift, GRP = 1 << gs, QT = PFA_ROWS >> gs;
     const int qb = (int)gridDim.y - 1 - (int)blockIdx.y;  // the longest causal prefixes of all heads and prompts first
     const int seq = (int)blockIdx.x / p.Hkv;
@@ -99,27 +104,39 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const __half* const kn_seq = BITS != 0 ? p.kn + (size_t)seq_row0 * p.Hkv + kvh : nullptr;
     const __half* const vn_seq = BITS != 0 ? p.vn + (size_t)seq_row0 * p.Hkv + kvh : nullptr;
 
-    const uint32_t bar_mma = sb + PtcSmem::CTRL;         // score products (and the two rotations)
-    const uint32_t bar_pv = sb + PtcSmem::CTRL + 8u;     // value products
-    const uint32_t bar_ready0 = sb + PtcSmem::CTRL + 16u, bar_free0 = sb + PtcSmem::CTRL + 48u;  // one each per stage
+    // mbarriers
+    const uint32_t bar_rot = sb + PtcSmem::CTRL;            // the two rotation products (count 1, tcgen05.commit)
+    const uint32_t bar_pv = sb + PtcSmem::CTRL + 8u;        // value product of a tile done (count 1, commit)
+    const uint32_t bar_sfull0 = sb + PtcSmem::CTRL + 16u;   // [2] score product into S buffer i done (count 1, commit)
+    const uint32_t bar_pfull = sb + PtcSmem::CTRL + 32u;    // P of a tile written by all 256 softmax threads
+    const uint32_t bar_ready0 = sb + PtcSmem::CTRL + 40u;   // [PTC_STAGES] tile staged by the 128 producers
+    const uint32_t bar_free0 = sb + PtcSmem::CTRL + 64u;    // [PTC_STAGES] the products that read the stage are done (commit)
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gb + PtcSmem::CTRL + 96);
+    float* xch = reinterpret_cast<float*>(gb + PtcSmem::XCH);  // [256] row maxima / sums exchanged between the two halves of a row
     bool dead = false;
     auto give_up = [&]() {
         dead = true;
         if (p.status) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
     };
+    auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+        if (!dead && !mbar_wait_bounded(bar, parity, 1u << 17)) give_up();
+    };
 
     // ---- once: tensor memory, barriers, table, this block's queries, R ----
     if (warp == 0) {
-        tmem_alloc(sb + PtcSmem::CTRL + 96u, 512u);  // [0, 128): rotation products; [128, 192): S; [256, 384): the output rows
+        // columns [0, 128): rotation products; [128, 192) and [192, 256): S of even / odd tiles; [256, 384): the output rows
+        tmem_alloc(sb + PtcSmem::CTRL + 96u, 512u);
         tmem_relinquish();
     }
     if (tid == 0) {
-        mbar_init(bar_mma, 1);
+        mbar_init(bar_rot, 1);
         mbar_init(bar_pv, 1);
+        mbar_init(bar_sfull0, 1);
+        mbar_init(bar_sfull0 + 8u, 1);
+        mbar_init(bar_pfull, 256);
         for (int i = 0; i < PTC_STAGES; ++i) {
             mbar_init(bar_ready0 + 8u * i, 128);
-            mbar_init(bar_free0 + 8u * i, 128);
+            mbar_init(bar_free0 + 8u * i, 1);
         }
         fence_mbar_init();
     }
@@ -130,16 +147,19 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         }
     }
     const uint32_t lut = sb + PtcSmem::LUT + 4u * (uint32_t)lane;
-    const int my_tok = q0 + (tid >> gs), my_head = kvh * GRP + (tid & (GRP - 1));  // row threads: the score row's query
-    if (is_row) {
+    // softmax threads: score row, column half, the row's query
+    const int srow = (warp & 3) * 32 + lane, half = (warp >> 2) & 1;
+    const int my_tok = q0 + (srow >> gs), my_head = kvh * GRP + (srow & (GRP - 1));
+    if (is_soft) {  // the query row: this thread's half of its 16 chunks
         const uint4* src = reinterpret_cast<const uint4*>(q_seq + (size_t)my_tok * p.q_tok_stride + (size_t)my_head * HEAD_DIM);
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
+        for (int c = 0; c < 8; ++c) {
+            const int ch = 8 * half + c;
             const uint4 u = my_tok < p.T ? __ldg(src + ch) : make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, tid, ch)) = u;
+            *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, ch)) = u;
         }
     }
-    if (BITS != 0) {  // R [d][k] as a B operand (rows = output coordinate d) over the K buffers
+    if (BITS != 0) {  // R [d][k] as a B operand (rows = output coordinate d) over the K stages
         for (int i = tid; i < 128 * 16; i += PTC_THREADS) {
             const int row = i >> 4, ch = i & 15;
             *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, row, ch)) =
@@ -152,30 +172,25 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t my_lanes = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's quarter of the tensor-memory lanes
-    uint32_t mph = 0;  // phase of bar_mma (row threads)
-
-    auto wait_mma = [&]() {
-        if (!dead && !mbar_wait_bounded(bar_mma, mph, 1u << 17)) give_up();
-        mph ^= 1u;
-        tc_fence_after();
-    };
+    constexpr uint32_t O_COL = 256u;
 
     if (BITS != 0) {
         // ---- q_rot = Q . R^T (reference engine/kernels.cu:1896-1903), scaled by log2(e) / sqrt(128), back into the Q tile ----
-        if (tid == 0) {
+        if (is_mma && lane == 0) {
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 const uint32_t koff = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
                 umma_f16(tmem, umma_desc_sw128(sb + PtcSmem::Q + koff), umma_desc_sw128(sb + PtcSmem::K + koff), PTC_IDESC_N128, ks != 0);
             }
-            umma_commit(bar_mma);
+            umma_commit(bar_rot);
         }
-        if (is_row) {
-            wait_mma();
+        if (is_soft) {
+            wait_bar(bar_rot, 0u);
+            tc_fence_after();
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c2 = 0; c2 < 2; ++c2) {  // this thread's 64 coordinates
                 uint32_t r[32];
-                tmem_ld32(my_lanes + 32u * c4, r);
+                tmem_ld32(my_lanes + 64u * half + 32u * c2, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -185,22 +200,21 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     u.y = pack_half2(__uint_as_float(r[8 * i + 2]) * sc, __uint_as_float(r[8 * i + 3]) * sc);
                     u.z = pack_half2(__uint_as_float(r[8 * i + 4]) * sc, __uint_as_float(r[8 * i + 5]) * sc);
                     u.w = pack_half2(__uint_as_float(r[8 * i + 6]) * sc, __uint_as_float(r[8 * i + 7]) * sc);
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, tid, 4 * c4 + i)) = u;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = u;
                 }
             }
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        __syncthreads();  // the rotated queries are in place and R has been consumed: the K buffers may take tiles
+        __syncthreads();  // the rotated queries are in place and R has been consumed: the K stages may take tiles
         tc_fence_after();
     }
 
     float m_run = -1e30f, l_run = 0.0f;
-    constexpr uint32_t O_COL = 256u;  // tensor-memory columns of the output rows
 
-    if (!is_row) {
+    if (is_prod) {
         // ================= producers: tile j into stage j % PTC_STAGES =================
-        const int pt = tid - 128, pw = pt >> 5;
+        const int pt = tid - 256, pw = pt >> 5;
         const int ktr = pt & 63, kc = pt >> 6;  // token row of the tile, half of its 128 coordinates
         constexpr int NRAW = BITS == 4 ? 2 : 8;  // 16-byte loads per thread and array
         uint4 kraw[NRAW], vraw[NRAW];
@@ -222,7 +236,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         fetch(0);
         int b = 0, use = 0;  // stage of tile j and how often the stage has been used before
         for (int j = 0; j < n_tiles; ++j) {
-            if (use > 0 && !dead && !mbar_wait_bounded(bar_free0 + 8u * b, (uint32_t)((use - 1) & 1), 1u << 17)) give_up();
+            if (use > 0) wait_bar(bar_free0 + 8u * b, (uint32_t)((use - 1) & 1));
             const int row0 = j * PTC_KT;
             uint8_t* kt = gb + PtcSmem::K + (uint32_t)b * 16384u;
             const uint32_t vt = sb + PtcSmem::V + (uint32_t)b * 16384u;
@@ -281,48 +295,62 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 ++use;
             }
         }
-    } else {
-        // ================= row threads =================
-        uint32_t pph = 0;  // phase of bar_pv
-        auto wait_pv = [&]() {
-            if (!dead && !mbar_wait_bounded(bar_pv, pph, 1u << 17)) give_up();
-            pph ^= 1u;
-            tc_fence_after();
-        };
-        auto issue_scores = [&](int b, int use) {  // S = Q . K^T of the tile in stage b: 128 x 64, 8 steps of 16 coordinates (one thread)
-            if (!dead && !mbar_wait_bounded(bar_ready0 + 8u * b, (uint32_t)(use & 1), 1u << 17)) give_up();
-            tc_fence_after();
-            if (dead) return;
+    } else if (is_mma) {
+        // ================= one thread issues every product =================
+        // order on the tensor pipe: S(0), S(1), P.V(0), S(2), P.V(1), S(3), ...: the scores of tile j + 1 are ready when
+        // the softmax threads finish tile j
+        if (lane == 0) {
+            auto issue_scores = [&](int j) {  // S(j) = Q . K^T(j): 128 x 64, 8 steps of 16 coordinates, into S buffer j & 1
+                const int st = j % PTC_STAGES, use = j / PTC_STAGES;
+                wait_bar(bar_ready0 + 8u * st, (uint32_t)(use & 1));
+                tc_fence_after();
+                if (dead) return;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint32_t ka = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-                const uint32_t kb = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
-                umma_f16(tmem + 128u, umma_desc_sw128(sb + PtcSmem::Q + ka), umma_desc_sw128(sb + PtcSmem::K + (uint32_t)b * 16384u + kb),
-                         PTC_IDESC_N64, ks != 0);
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t ka = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+                    const uint32_t kb = (uint32_t)(ks >> 2) * 8192u + (uint32_t)(ks & 3) * 32u;
+                    umma_f16(tmem + 128u + 64u * (uint32_t)(j & 1), umma_desc_sw128(sb + PtcSmem::Q + ka),
+                             umma_desc_sw128(sb + PtcSmem::K + (uint32_t)st * 16384u + kb), PTC_IDESC_N64, ks != 0);
+                }
+                umma_commit(bar_sfull0 + 8u * (uint32_t)(j & 1));
+            };
+            issue_scores(0);
+            if (n_tiles > 1) issue_scores(1);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % PTC_STAGES;
+                wait_bar(bar_pfull, (uint32_t)(j & 1));  // P(j) is written (and S(j) taken out of tensor memory) by every row
+                tc_fence_after();
+                if (!dead) {  // O += P . V: 128 x 128, 4 steps of 16 tokens
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        umma_f16(tmem + O_COL, umma_desc_sw128(sb + PtcSmem::P + 32u * ks),
+                                 umma_desc_sw128(sb + PtcSmem::V + (uint32_t)st * 16384u + 32u * ks), PTC_IDESC_N128, (j | ks) != 0);
+                    umma_commit(bar_pv);
+                    umma_commit(bar_free0 + 8u * st);  // the stage has been read by S(j) and P.V(j)
+                }
+                if (j + 2 < n_tiles) issue_scores(j + 2);
             }
-            umma_commit(bar_mma);
-        };
-        if (tid == 0) issue_scores(0, 0);
-        int b = 0, use = 0, bprev = 0;  // stage of tile j, how often it has been used before, stage of tile j - 1
+        }
+    } else {
+        // ================= softmax threads: row srow, columns 32 half .. 32 half + 31 of every tile =================
+        const int pair_bar = 2 + (warp & 3);  // named barrier of the two warps that share 32 rows
         for (int j = 0; j < n_tiles; ++j) {
-            if (tid != 0) {  // (thread 0 waited for the tile when it issued the product) the norms of the tile are read below
-                if (!dead && !mbar_wait_bounded(bar_ready0 + 8u * b, (uint32_t)(use & 1), 1u << 17)) give_up();
-            }
-            wait_mma();
-            uint32_t sr[64];
-            tmem_ld32(my_lanes + 128u, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-            tmem_ld32(my_lanes + 160u, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+            const int st = j % PTC_STAGES, use = j / PTC_STAGES;
+            wait_bar(bar_ready0 + 8u * st, (uint32_t)(use & 1));  // (for the tile's norms; the products wait for it themselves)
+            wait_bar(bar_sfull0 + 8u * (uint32_t)(j & 1), (uint32_t)((j >> 1) & 1));
+            tc_fence_after();
+            uint32_t sr[32];
+            tmem_ld32(my_lanes + 128u + 64u * (uint32_t)(j & 1) + 32u * (uint32_t)half, sr);
             tmem_ld_wait();
-            // ---- K norm, causal limit, online softmax ----
+            // ---- K norm, causal limit, row maximum over both halves ----
             const bool diagonal = j * PTC_KT + PTC_KT - 1 > q0;
-            const uint4* nrm = reinterpret_cast<const uint4*>(gb + PtcSmem::NORM + (uint32_t)b * 256u);
-            const int bnext = b + 1 == PTC_STAGES ? 0 : b + 1, unext = b + 1 == PTC_STAGES ? use + 1 : use;
+            const uint4* nrm = reinterpret_cast<const uint4*>(gb + PtcSmem::NORM + (uint32_t)st * 256u);
             float mx = -1e30f;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
+            for (int c8 = 0; c8 < 4; ++c8) {
                 float kn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[c8];  // (every thread reads the same words: a broadcast)
+                    const uint4 u = nrm[4 * half + c8];  // (every thread of the warp reads the same words: a broadcast)
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -335,30 +363,31 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 for (int e = 0; e < 8; ++e) {
                     const int c = 8 * c8 + e;
                     float sv = __uint_as_float(sr[c]) * (BITS != 0 ? kn8[e] : p.score_scale);
-                    if (diagonal && j * PTC_KT + c > my_tok) sv = -1e30f;
+                    if (diagonal && j * PTC_KT + 32 * half + c > my_tok) sv = -1e30f;
                     sr[c] = __float_as_uint(sv);
                     mx = fmaxf(mx, sv);
                 }
             }
+            xch[(j & 1) * 256 + tid] = mx;
+            named_barrier(pair_bar, 64);
+            mx = fmaxf(mx, xch[(j & 1) * 256 + (tid ^ 128)]);
             const float mn = fmaxf(m_run, mx);
             const float corr = ex2_approx(m_run - mn);
             const bool grew = mn > m_run;
             m_run = mn;
             // the value product of the previous tile has read the P tile and updated the output rows
             if (j > 0) {
-                wait_pv();
-                tc_fence_before();
-                mbar_arrive(bar_free0 + 8u * bprev);  // its stage may take a later tile
+                wait_bar(bar_pv, (uint32_t)((j - 1) & 1));
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grew)) {  // a row's maximum grew: this warp's output rows are rescaled in place
+                if (__any_sync(0xffffffffu, grew)) {  // a row's maximum grew: this warp's half of the output rows is rescaled in place
 #pragma unroll 1
-                    for (int c4 = 0; c4 < 4; ++c4) {
+                    for (int c2 = 0; c2 < 2; ++c2) {
                         uint32_t r[32];
-                        tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                        tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        tmem_st32(my_lanes + O_COL + 32u * c4, r);
+                        tmem_st32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
                     }
                     tmem_st_wait();
                 }
@@ -366,10 +395,10 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             // ---- P (times the V norm) as fp16 into the A operand tile ----
             float lsum = 0.0f;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
+            for (int c8 = 0; c8 < 4; ++c8) {
                 float vn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[8 + c8];
+                    const uint4 u = nrm[8 + 4 * half + c8];
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -390,39 +419,31 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 uint4 u;
                 u.x = pack_half2(pv[0], pv[1]); u.y = pack_half2(pv[2], pv[3]);
                 u.z = pack_half2(pv[4], pv[5]); u.w = pack_half2(pv[6], pv[7]);
-                *reinterpret_cast<uint4*>(gb + PtcSmem::P + ptc_chunk(0u, tid, c8)) = u;
+                *reinterpret_cast<uint4*>(gb + PtcSmem::P + ptc_chunk(0u, srow, 4 * half + c8)) = u;
             }
             l_run = l_run * corr + lsum;
             fence_proxy_async_smem();
             tc_fence_before();
-            named_barrier(2, 128);  // every row's P is written, its S taken out of tensor memory, its output row rescaled
-            if (tid == 0) {
-                tc_fence_after();
-                if (!dead) {  // O += P . V: 128 x 128, 4 steps of 16 tokens
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        umma_f16(tmem + O_COL, umma_desc_sw128(sb + PtcSmem::P + 32u * ks),
-                                 umma_desc_sw128(sb + PtcSmem::V + (uint32_t)b * 16384u + 32u * ks), PTC_IDESC_N128, (j | ks) != 0);
-                    umma_commit(bar_pv);
-                }
-                if (j + 1 < n_tiles) issue_scores(bnext, unext);  // the next tile's scores run while this tile's values are multiplied
-            }
-            bprev = b;
-            b = bnext;
-            use = unext;
+            mbar_arrive(bar_pfull);
         }
-        wait_pv();  // the last value product
+        wait_bar(bar_pv, (uint32_t)((n_tiles - 1) & 1));  // the last value product
+        tc_fence_after();
+        // the row's sum over both column halves
+        named_barrier(pair_bar, 64);  // (the partner has read the last maxima)
+        xch[tid] = l_run;
+        named_barrier(pair_bar, 64);
+        l_run += xch[tid ^ 128];
     }
 
     // ================= results =================
     const float inv = 1.0f / (l_run + 1e-8f);
-    __half* const dst = out_seq + (size_t)my_tok * p.q_dim + (size_t)my_head * HEAD_DIM;
+    __half* const dst = out_seq + (size_t)my_tok * p.q_dim + (size_t)my_head * HEAD_DIM + 64 * half;
     if (BITS == 0) {
-        if (is_row) {
+        if (is_soft) {
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c2 = 0; c2 < 2; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
                 tmem_ld_wait();
                 if (my_tok < p.T) {
 #pragma unroll
@@ -432,7 +453,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                         u.y = pack_half2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
                         u.z = pack_half2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
                         u.w = pack_half2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + 32 * c4 + 8 * i) = u;
+                        *reinterpret_cast<uint4*>(dst + 32 * c2 + 8 * i) = u;
                     }
                 }
             }
@@ -440,12 +461,12 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     } else {
         // out[d] = sum_k R[k][d] * acc[k] (reference engine/kernels.cu:1957): the normalised rows, split into fp16 high and low
         // parts, times R^T [d][k] (the B operand's rows are the output coordinates)
-        __syncthreads();  // every product of the tile loop has completed (each row thread waited for the last one)
-        if (is_row) {
+        __syncthreads();  // every product of the tile loop has completed (the softmax threads waited for the last one)
+        if (is_soft) {
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c2 = 0; c2 < 2; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + O_COL + 32u * c4, r);
+                tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -460,8 +481,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                         ph[e] = *reinterpret_cast<const uint32_t*>(&h);
                         pl[e] = pack_half2(x0 - f.x, x1 - f.y);
                     }
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, tid, 4 * c4 + i)) = uh;
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, tid, 4 * c4 + i)) = ul;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = uh;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = ul;
                 }
             }
         }
@@ -474,7 +495,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
-        if (tid == 0 && !dead) {
+        if (is_mma && lane == 0 && !dead) {
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
 #pragma unroll
@@ -484,14 +505,15 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                              PTC_IDESC_N128, (part | ks) != 0);
                 }
             }
-            umma_commit(bar_mma);
+            umma_commit(bar_rot);
         }
-        if (is_row) {
-            wait_mma();
+        if (is_soft) {
+            wait_bar(bar_rot, 1u);
+            tc_fence_after();
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c2 = 0; c2 < 2; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + 32u * c4, r);
+                tmem_ld32(my_lanes + 64u * (uint32_t)half + 32u * c2, r);
                 tmem_ld_wait();
                 if (my_tok < p.T) {
 #pragma unroll
@@ -501,7 +523,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                         u.y = pack_half2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
                         u.z = pack_half2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
                         u.w = pack_half2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-                        *reinterpret_cast<uint4*>(dst + 32 * c4 + 8 * i) = u;
+                        *reinterpret_cast<uint4*>(dst + 32 * c2 + 8 * i) = u;
                     }
                 }
             }
