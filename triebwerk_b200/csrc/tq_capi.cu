@@ -668,6 +668,20 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
         ap.kn = (const __half*)k_norms;
         ap.vn = (const __half*)v_norms;
         ap.rotation = (const __half*)rotation;
+        if (bits == 4) {  // the tcgen05 form wants R^T as well: 32 KB of the launchers' workspace, written by a small launch
+            void* pws = nullptr;
+            r = compat_workspace((size_t)HEAD_DIM * HEAD_DIM * sizeof(__half) + 256, &pws, cs(s));
+            if (r == TQ_OK) {
+                ap.status = (int*)pws;
+                ap.rotation_t = (const __half*)((char*)pws + 256);
+                transpose_rotation_kernel<<<16, 256, 0, cs(s)>>>((__half*)((char*)pws + 256), (const __half*)rotation);
+                r = cuda_status(cudaGetLastError());
+            }
+            if (r != TQ_OK) {
+                g_compat_status = r;
+                return;
+            }
+        }
         ap.out = (__half*)out;
         ap.q_dim = q_dim;
         ap.T = T;

@@ -30,6 +30,7 @@ constexpr int PTC_THREADS = 416;  // 8 softmax warps, 4 producer warps, 1 warp t
 constexpr int PTC_KT = 64;  // cache rows per tile
 
 constexpr int PTC_STAGES = 3;  // K / V tile buffers
+constexpr float PTC_SLACK = 4.0f;  // see the softmax: how far a row maximum may run ahead of the exponentials' reference point
 
 struct PtcSmem {
     static constexpr uint32_t Q = 0;            // A operand [2 regions][128 rows][128 B]; at the end: high parts of the results
@@ -371,9 +372,12 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             xch[(j & 1) * 256 + tid] = mx;
             named_barrier(pair_bar, 64);
             mx = fmaxf(mx, xch[(j & 1) * 256 + (tid ^ 128)]);
-            const float mn = fmaxf(m_run, mx);
+            // The reference point of the exponentials follows the row maximum only when that has grown by more than
+            // PTC_SLACK (in powers of two) since the point was set: weights then stay below 2^PTC_SLACK, and the output rows
+            // in tensor memory need rescaling in the first tiles only.  The result does not depend on the point.
+            const bool grew = mx > m_run + PTC_SLACK;
+            const float mn = grew ? mx : m_run;
             const float corr = ex2_approx(m_run - mn);
-            const bool grew = mn > m_run;
             m_run = mn;
             // the value product of the previous tile has read the P tile and updated the output rows
             if (j > 0) {
@@ -408,13 +412,22 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     }
                 }
                 float pv[8];
+                if (diagonal) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float sv = __uint_as_float(sr[8 * c8 + e]);
-                    const float pe = sv <= -1e30f ? 0.0f : ex2_approx(sv - mn);
-                    lsum += pe;
-                    // (rows past the prompt can hold anything, a norm that is not a number included: select, do not multiply)
-                    pv[e] = pe == 0.0f ? 0.0f : (BITS != 0 ? pe * vn8[e] : pe);
+                    for (int e = 0; e < 8; ++e) {
+                        const float sv = __uint_as_float(sr[8 * c8 + e]);
+                        const float pe = sv <= -1e30f ? 0.0f : ex2_approx(sv - mn);
+                        lsum += pe;
+                        // (rows past the prompt can hold anything, a norm that is not a number included: select, do not multiply)
+                        pv[e] = pe == 0.0f ? 0.0f : (BITS != 0 ? pe * vn8[e] : pe);
+                    }
+                } else {  // every row of the tile lies before every query of the block: nothing is masked
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float pe = ex2_approx(__uint_as_float(sr[8 * c8 + e]) - mn);
+                        lsum += pe;
+                        pv[e] = BITS != 0 ? pe * vn8[e] : pe;
+                    }
                 }
                 uint4 u;
                 u.x = pack_half2(pv[0], pv[1]); u.y = pack_half2(pv[2], pv[3]);
