@@ -668,7 +668,7 @@ void launch_turbo_gqa_prefill_attention(void* out, const void* q, const uint8_t*
         ap.kn = (const __half*)k_norms;
         ap.vn = (const __half*)v_norms;
         ap.rotation = (const __half*)rotation;
-        if (bits == 4) {  // the tcgen05 form wants R^T as well: 32 KB of the launchers' workspace, written by a small launch
+        {  // the tcgen05 form wants R^T as well: 32 KB of the launchers' workspace, written by a small launch
             void* pws = nullptr;
             r = compat_workspace((size_t)HEAD_DIM * HEAD_DIM * sizeof(__half) + 256, &pws, cs(s));
             if (r == TQ_OK) {

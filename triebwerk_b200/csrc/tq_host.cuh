@@ -362,12 +362,15 @@ inline int launch_prefill_attention(int bits, PrefillAttnParams p, cudaStream_t 
     dim3 grid((unsigned)(p.Hkv * p.n_seq), (unsigned)((p.T + qt - 1) / qt));
     if (p.T <= 0) return TQ_OK;
     int ar;
-    // tcgen05 form (default; TQ_PREFILL_ATTN_TC=0 selects the mma.sync form): 4-bit cache (needs R^T) and fp16 cache
+    // tcgen05 form (default; TQ_PREFILL_ATTN_TC=0 selects the mma.sync form); the packed modes need R^T as well
     static const bool tc = !(getenv("TQ_PREFILL_ATTN_TC") && atoi(getenv("TQ_PREFILL_ATTN_TC")) == 0);
-    if (tc && ((bits == 4 && p.rotation_t) || bits == 0)) {
+    if (tc && ((bits != 0 && p.rotation_t) || bits == 0)) {
         if (bits == 4) {
             if ((ar = ensure_dynamic_smem((const void*)prefill_attention_tc_kernel<4>, PTC_DYN_SMEM)) != TQ_OK) return ar;
             prefill_attention_tc_kernel<4><<<grid, PTC_THREADS, PTC_DYN_SMEM, s>>>(p);
+        } else if (bits == 2) {
+            if ((ar = ensure_dynamic_smem((const void*)prefill_attention_tc_kernel<2>, PTC_DYN_SMEM)) != TQ_OK) return ar;
+            prefill_attention_tc_kernel<2><<<grid, PTC_THREADS, PTC_DYN_SMEM, s>>>(p);
         } else {
             if ((ar = ensure_dynamic_smem((const void*)prefill_attention_tc_kernel<0>, PTC_DYN_SMEM)) != TQ_OK) return ar;
             prefill_attention_tc_kernel<0><<<grid, PTC_THREADS, PTC_DYN_SMEM, s>>>(p);

@@ -81,7 +81,7 @@ __device__ __forceinline__ uint32_t ptc_chunk(uint32_t region_bytes, int row, in
 
 template <int BITS>
 __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(const PrefillAttnParams p) {
-    static_assert(BITS == 4 || BITS == 0, "forms built on tcgen05: the 4-bit cache and the fp16 cache");
+    static_assert(BITS == 4 || BITS == 2 || BITS == 0, "kv_bits");
     extern __shared__ __align__(1024) uint8_t ptc_smem[];
     const uint32_t sb = (smem_u32(ptc_smem) + 1023u) & ~1023u;
     uint8_t* gb = ptc_smem + (sb - smem_u32(ptc_smem));
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const int q0 = qb * QT;
     const int q_last = min(q0 + QT, p.T) - 1;
     const int n_tiles = q_last / PTC_KT + 1;
-    constexpr int ROW_BYTES = BITS == 4 ? 64 : 256;  // bytes of one head in a cache row
+    constexpr int ROW_BYTES = BITS == 4 ? 64 : BITS == 2 ? 32 : 256;  // bytes of one head in a cache row
     const size_t row_stride = (size_t)p.Hkv * ROW_BYTES;
     const long long seq_row0 = p.row_base ? p.row_base[seq] : (long long)seq * p.seq_rows;
     const __half* const q_seq = p.q + (size_t)seq * (size_t)p.T * (size_t)p.q_tok_stride;
@@ -141,10 +141,15 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         }
         fence_mbar_init();
     }
-    if (BITS == 4) {
+    if (BITS == 4) {  // byte -> the two centroids of its nibbles, one column per lane
         for (int i = tid; i < 256 * 32; i += PTC_THREADS) {
             const int e = i >> 5;
             reinterpret_cast<uint32_t*>(gb + PtcSmem::LUT)[i] = pack_half2(kCent4[e & 15], kCent4[e >> 4]);
+        }
+    } else if (BITS == 2) {  // nibble -> the two centroids of its 2-bit codes
+        for (int i = tid; i < 16 * 32; i += PTC_THREADS) {
+            const int e = i >> 5;
+            reinterpret_cast<uint32_t*>(gb + PtcSmem::LUT)[i] = pack_half2(kCent2[e & 3], kCent2[e >> 2]);
         }
     }
     const uint32_t lut = sb + PtcSmem::LUT + 4u * (uint32_t)lane;
@@ -217,13 +222,14 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         // ================= producers: tile j into stage j % PTC_STAGES =================
         const int pt = tid - 256, pw = pt >> 5;
         const int ktr = pt & 63, kc = pt >> 6;  // token row of the tile, half of its 128 coordinates
-        constexpr int NRAW = BITS == 4 ? 2 : 8;  // 16-byte loads per thread and array
+        constexpr int NRAW = BITS == 4 ? 2 : BITS == 2 ? 1 : 8;  // 16-byte loads per thread and array (64 coordinates)
+        constexpr int HALF_ROW = BITS == 4 ? 32 : BITS == 2 ? 16 : 128;  // their bytes
         uint4 kraw[NRAW], vraw[NRAW];
         __half nraw = __float2half(1.0f);
         auto fetch = [&](int j) {  // the raw words of tile j into registers
             const int row = min(j * PTC_KT + ktr, p.rows - 1);
-            const uint4* ksrc = reinterpret_cast<const uint4*>(ck_seq + (size_t)row * row_stride + (BITS == 4 ? 32 : 128) * kc);
-            const uint4* vsrc = reinterpret_cast<const uint4*>(cv_seq + (size_t)row * row_stride + (BITS == 4 ? 32 : 128) * kc);
+            const uint4* ksrc = reinterpret_cast<const uint4*>(ck_seq + (size_t)row * row_stride + HALF_ROW * kc);
+            const uint4* vsrc = reinterpret_cast<const uint4*>(cv_seq + (size_t)row * row_stride + HALF_ROW * kc);
 #pragma unroll
             for (int i = 0; i < NRAW; ++i) {
                 kraw[i] = __ldg(ksrc + i);
@@ -259,6 +265,24 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.y) : "r"(lut + (((vw[i] >> 8) & 0xffu) << 7)));
                     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.z) : "r"(lut + (((vw[i] >> 16) & 0xffu) << 7)));
                     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.w) : "r"(lut + ((vw[i] >> 24) << 7)));
+                    *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::VRM + (uint32_t)ktr * 256u + (uint32_t)(((8 * kc + i) ^ (ktr & 7)) << 4)) = w;
+                }
+            } else if (BITS == 2) {
+                const uint32_t kw[4] = {kraw[0].x, kraw[0].y, kraw[0].z, kraw[0].w};
+                const uint32_t vw[4] = {vraw[0].x, vraw[0].y, vraw[0].z, vraw[0].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {  // chunk i: 8 coordinates = 2 bytes = 4 nibbles
+                    const uint32_t k16 = (kw[i >> 1] >> (16 * (i & 1))) & 0xffffu, v16 = (vw[i >> 1] >> (16 * (i & 1))) & 0xffffu;
+                    uint4 u, w;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.x) : "r"(lut + ((k16 & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.y) : "r"(lut + (((k16 >> 4) & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.z) : "r"(lut + (((k16 >> 8) & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.w) : "r"(lut + ((k16 >> 12) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.x) : "r"(lut + ((v16 & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.y) : "r"(lut + (((v16 >> 4) & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.z) : "r"(lut + (((v16 >> 8) & 0xfu) << 7)));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w.w) : "r"(lut + ((v16 >> 12) << 7)));
                     *reinterpret_cast<uint4*>(kt + ptc_chunk(8192u, ktr, 8 * kc + i)) = u;
                     *reinterpret_cast<uint4*>(gb + PtcSmem::VRM + (uint32_t)ktr * 256u + (uint32_t)(((8 * kc + i) ^ (ktr & 7)) << 4)) = w;
                 }
