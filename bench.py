@@ -523,8 +523,12 @@ def measure_decode(args, w, rank, world, local_rank, steps, warmup, full=True):
     def step_device():
         if gat is None:
             return step_compute()
+        split = eng.step_prepare(q_dev, k_dev, v_dev)   # every layer's append and query rotation first, once
         for gi, (l0, l1) in enumerate(groups):
-            eng.decode_layers(l0, l1 - l0, q_dev, k_dev, v_dev, out_dev)
+            if split:
+                eng.step_attend_layers(l0, l1 - l0, out_dev)
+            else:
+                eng.decode_layers(l0, l1 - l0, q_dev, k_dev, v_dev, out_dev)
             gat.gather(gi, out_dev[l0:l1])
         gat.finish()
 
@@ -742,7 +746,7 @@ def run_ours(args, w, rank, world, local_rank):
                 "h2d_bytes_per_step": int(world * NL * G * (q_dim + 2 * kv_dim) * 2),
                 "d2h_bytes_per_step": int(world * NL * G * q_dim * 2)},
         # kernels of this library launched inside the timed region (none of anybody else's but NCCL's at N > 1)
-        "gpu_launches": int(steps * (4 * (len(sharded_groups(NL, world))) if whole else NL * (1 if fused else 2))),
+        "gpu_launches": int(steps * ((4 if world == 1 else 2 + 2 * len(sharded_groups(NL, world))) if whole else NL * (1 if fused else 2))),
         "roofline": {"kernel": "fp16_cache_write_kernel + fp16_decode_attention_kernel" if bits == 0 else
                      f"decode_attention_kernel<{bits}>" + (" (whole-step form: one launch streams all layers; per layer)" if whole else
                                                            " (one launch per layer: append + query rotation + attention)" if fused else ""),

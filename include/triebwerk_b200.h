@@ -330,6 +330,15 @@ int tq_fold_rotation_into_projection(void* w_out, const void* w_in, const void* 
 int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v,
                             void* out, tq_stream_t s);
 
+/* tq_engine_decode_step in two phases, for callers that hand the results on group of layers by group of layers (an
+ * exchange between GPUs, a copy to the host) while the rest is still being computed: tq_engine_step_prepare appends
+ * the new token of every layer and rotates all queries (two launches); tq_engine_step_attend_layers then runs the
+ * attention and the merge of the layers first_layer .. (two launches per call); out_first is the [G][q_dim] block of
+ * first_layer inside a [layers][G][q_dim] buffer.  Packed modes with the whole-step form (otherwise
+ * TQ_ERR_UNSUPPORTED: use tq_engine_decode_layers). */
+int tq_engine_step_prepare(tq_engine* e, const void* q, const void* k, const void* v, tq_stream_t s);
+int tq_engine_step_attend_layers(tq_engine* e, int first_layer, int n_layers, void* out_first, tq_stream_t s);
+
 /* Error reporting aid, packed modes: with enable != 0 the engine also keeps every attention result as fp32, i.e. before
  * its final rounding to fp16 ([layers][G][num_heads][128], allocated outside the arena; call after
  * tq_engine_alloc_batch, and again after the batch shape changes); enable == 0 frees the buffer.

@@ -585,3 +585,39 @@ def test_prefill_layer_batch_equals_prompt_by_prompt(bits):
         tqo.append_tokens(cv, vn, v[0], R, pos, msl, Hkv, D, bits)
         ref, _ = tqo.prefill_attention(q[0], ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
         hp.assert_attention_close(together[0], ref, H, D, "first prompt of the batch")
+
+
+def test_step_in_two_phases_equals_the_whole_step():
+    """tq_engine_step_prepare + tq_engine_step_attend_layers over groups of layers give the bits (outputs and cache) of
+    tq_engine_decode_step."""
+    H, Hkv, D, G, bits, msl, NL = 16, 8, 128, 6, 4, 384, 5
+    kv_dim, q_dim = Hkv * D, H * D
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    scales = torch.from_numpy(synth.channel_scales(kv_dim)).cuda()
+    prompts = [[synth.torch_kv(gen, 200 + 9 * g, kv_dim, scales) for g in range(G)] for _ in range(NL)]
+    q = torch.randn(NL, G, q_dim, generator=gen, device="cuda").to(torch.float16)
+    k = torch.randn(NL, G, kv_dim, generator=gen, device="cuda").to(torch.float16)
+    v = torch.randn(NL, G, kv_dim, generator=gen, device="cuda").to(torch.float16)
+    outs, caches = [], []
+    for split in (False, True):
+        eng = tq.Engine(msl, bits, num_layers=NL, num_heads=H, num_kv_heads=Hkv, head_dim=D)
+        eng.alloc_batch(G, msl)
+        for layer in range(NL):
+            for g in range(G):
+                eng.prefill_append(layer, g, prompts[layer][g][0], prompts[layer][g][1], 0)
+        eng.set_positions([200 + 9 * g for g in range(G)])
+        out = torch.zeros_like(q)
+        if split:
+            assert eng.step_prepare(q, k, v)
+            for l0, n in ((0, 2), (2, 2), (4, 1)):
+                eng.step_attend_layers(l0, n, out)
+        else:
+            eng.decode_step(q, k, v, out)
+        torch.cuda.synchronize()
+        assert eng.status() == 0
+        outs.append(out)
+        caches.append([[t.clone() for t in eng.layer_cache(layer)] for layer in range(NL)])
+    assert torch.equal(outs[0], outs[1])
+    for la, lb in zip(*caches):
+        for a, b in zip(la, lb):
+            assert torch.equal(a, b)

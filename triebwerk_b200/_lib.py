@@ -27,7 +27,7 @@ SYMBOLS = [
     "tq_engine_decode_step_host", "tq_engine_attend_layer", "tq_engine_decode_step", "tq_engine_status", "tq_engine_attend_step",
     "tq_engine_output_f32", "tq_engine_read_output_f32", "tq_engine_decode_layers", "tq_static_status", "tq_selftest_bounded_wait",
     "tq_engine_sequence_blob_bytes", "tq_engine_export_sequence", "tq_engine_import_sequence", "tq_engine_sleep_keep", "tq_engine_prefill_shared", "tq_engine_decode_step_produce", "tq_fold_rotation_into_projection",
-    "tq_engine_time_attention", "tq_engine_last_attention_ms", "tq_engine_prefill_layer", "tq_engine_prefill_layer_batch",
+    "tq_engine_time_attention", "tq_engine_last_attention_ms", "tq_engine_prefill_layer", "tq_engine_prefill_layer_batch", "tq_engine_step_prepare", "tq_engine_step_attend_layers",
     "tq_peer_buffer_create", "tq_peer_buffer_open", "tq_peer_buffer_close", "tq_peer_buffer_destroy", "tq_peer_copy", "tq_peer_signal", "tq_peer_wait",
 ]
 
@@ -127,6 +127,8 @@ def lib() -> C.CDLL:
     sig("tq_engine_output_f32", i, [vp, i])
     sig("tq_engine_prefill_layer", i, [vp, i, i, vp, vp, vp, vp, i, i, vp])
     sig("tq_engine_prefill_layer_batch", i, [vp, i, i, i, vp, vp, vp, vp, i, i, vp])
+    sig("tq_engine_step_prepare", i, [vp, vp, vp, vp, vp])
+    sig("tq_engine_step_attend_layers", i, [vp, i, i, vp, vp])
     sig("tq_engine_time_attention", i, [vp, i])
     sig("tq_engine_last_attention_ms", i, [vp, C.POINTER(C.c_float)])
     sig("tq_engine_read_output_f32", i, [vp, vp, i, i, vp])

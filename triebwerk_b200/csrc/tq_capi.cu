@@ -1445,8 +1445,11 @@ static bool engine_whole_step_ok(const tq_engine* e, const void* q, const void* 
            ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) == 0);
 }
 
-static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, void* out, cudaStream_t s,
-                              const tq_step_producer* prod = nullptr) {
+static int engine_step_attend(tq_engine* e, int l0, int n, const void* q, void* out, cudaStream_t s, const tq_step_producer* prod);
+
+// launches 1 and 1b of the whole-step form for the layers [l0, l0 + n): the append and the query rotation
+static int engine_step_prepare(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, cudaStream_t s,
+                               const tq_step_producer* prod) {
     e->chain_ok = false;
     const tq_engine::Layer& L = e->layers[l0];
     const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, G = e->G;
@@ -1485,7 +1488,22 @@ static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const 
         r = cuda_status(cudaGetLastError());
         if (r != TQ_OK) return r;
     }
+    return TQ_OK;
+}
 
+static int engine_step_layers(tq_engine* e, int l0, int n, const void* q, const void* k, const void* v, void* out, cudaStream_t s,
+                              const tq_step_producer* prod = nullptr) {
+    int r = engine_step_prepare(e, l0, n, q, k, v, s, prod);
+    if (r != TQ_OK) return r;
+    return engine_step_attend(e, l0, n, q, out, s, prod);
+}
+
+// launches 2 and 3 for the layers [l0, l0 + n): the attention over the rotated queries engine_step_prepare left, and the merge
+static int engine_step_attend(tq_engine* e, int l0, int n, const void* q, void* out, cudaStream_t s, const tq_step_producer* prod) {
+    e->chain_ok = false;
+    const tq_engine::Layer& L = e->layers[l0];
+    const int H = e->shape.num_heads, Hkv = e->shape.num_kv_heads, G = e->G;
+    int r = TQ_OK;
     FullWorkspace fw = carve_full(e->workspace, G, H);
     AttnParams p{};
     p.ck = (const uint8_t*)L.k; p.cv = (const uint8_t*)L.v; p.kn = (const __half*)L.kn; p.vn = (const __half*)L.vn;
@@ -1562,6 +1580,20 @@ int tq_engine_last_attention_ms(tq_engine* e, float* ms) {
     TQ_CUDA(cudaEventSynchronize(e->ev_attn[1]));
     TQ_CUDA(cudaEventElapsedTime(ms, e->ev_attn[0], e->ev_attn[1]));
     return TQ_OK;
+}
+
+int tq_engine_step_prepare(tq_engine* e, const void* q, const void* k, const void* v, tq_stream_t s) {
+    if (!e || !q || !k || !v) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (!engine_whole_step_ok(e, q, k, v, q)) return TQ_ERR_UNSUPPORTED;
+    return engine_step_prepare(e, 0, e->shape.num_layers, q, k, v, cs(s), nullptr);
+}
+
+int tq_engine_step_attend_layers(tq_engine* e, int first_layer, int n_layers, void* out_first, tq_stream_t s) {
+    if (!e || !out_first || first_layer < 0 || n_layers <= 0 || first_layer + n_layers > e->shape.num_layers) return TQ_ERR_ARG;
+    if (e->asleep || !e->arena || e->G == 0 || !engine_on_its_device(e)) return TQ_ERR_STATE;
+    if (!engine_whole_step_ok(e, out_first, out_first, out_first, out_first)) return TQ_ERR_UNSUPPORTED;
+    return engine_step_attend(e, first_layer, n_layers, nullptr, out_first, cs(s), nullptr);
 }
 
 int tq_engine_decode_layers(tq_engine* e, int first_layer, int n_layers, const void* q, const void* k, const void* v, void* out,

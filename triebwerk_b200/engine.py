@@ -174,6 +174,24 @@ class Engine:
                                             v[first_layer].data_ptr(), out[first_layer].data_ptr(), self._stream()), "decode_layers")
         return out
 
+    def step_prepare(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+        """First phase of decode_step: every layer's append and query rotation.  False when the engine cannot split the
+        step (fp16 cache, one launch per layer): use decode_layers then."""
+        for t in (q, k, v):
+            assert t.is_cuda and t.is_contiguous() and t.dtype == torch.float16 and t.shape[0] == self.shape.num_layers
+        r = lib().tq_engine_step_prepare(self._h, q.data_ptr(), k.data_ptr(), v.data_ptr(), self._stream())
+        if r == -4:  # TQ_ERR_UNSUPPORTED
+            return False
+        check(r, "step_prepare")
+        return True
+
+    def step_attend_layers(self, first_layer: int, n_layers: int, out: torch.Tensor) -> torch.Tensor:
+        """Second phase: attention and merge of a group of layers; out is the whole-step buffer [layers, G, q_dim]."""
+        assert out.is_cuda and out.is_contiguous() and out.dtype == torch.float16 and out.shape[0] == self.shape.num_layers
+        check(lib().tq_engine_step_attend_layers(self._h, first_layer, n_layers, out[first_layer].data_ptr(), self._stream()),
+              "step_attend_layers")
+        return out
+
     def time_attention(self, on: bool = True) -> None:
         """Record CUDA events around the attention launch of the whole-step calls (measurement aid)."""
         check(lib().tq_engine_time_attention(self._h, int(bool(on))), "time_attention")
