@@ -4,10 +4,10 @@
 // query token t of a prompt attends to cache rows 0 .. t.  Here the products run as tcgen05.mma with the operands read
 // from shared memory by the tensor core itself and the accumulators in tensor memory, so no warp spends its
 // shared-memory bandwidth on ldmatrix:
-//   * one CTA = 128 score rows (128 / GRP query tokens x the GRP query heads of one KV head) = the M dimension, 13 warps;
-//   * warps 0-7 do the softmax, two threads per score row (row = TMEM lane; warps w and w + 4 reach the same lanes and take
-//     one half of a tile's 64 columns each, their row maxima meet through shared memory); warp 12 issues every product
-//     (one thread); warps 8-11 dequantise the cache
+//   * one CTA = 128 score rows (128 / GRP query tokens x the GRP query heads of one KV head) = the M dimension, 21 warps;
+//   * warps 0-15 do the softmax, four threads per score row (row = TMEM lane; warps w, w + 4, w + 8, w + 12 reach the same
+//     lanes and take a quarter of a tile's 64 columns each, their row maxima meet through shared memory); warp 20 issues
+//     every product (one thread); warps 16-19 dequantise the cache
 //     tiles: K as [64 tokens][128 coordinates] (the B operand of S = Q . K^T) and V TRANSPOSED as [128 coordinates][64
 //     tokens] (the B operand of O += P . V; transposed 8 x 8 blocks at a time with ldmatrix.trans + stmatrix), both fp16
 //     in the canonical K-major 128-byte-swizzled layout, double buffered and handed over through mbarriers;
@@ -26,7 +26,11 @@
 
 namespace tq {
 
-constexpr int PTC_THREADS = 416;  // 8 softmax warps, 4 producer warps, 1 warp that issues the products
+constexpr int PTC_SPR = 4;                          // softmax threads per score row
+constexpr int PTC_CPT = 64 / PTC_SPR;               // score columns of a tile per softmax thread
+constexpr int PTC_OPT = 128 / PTC_SPR;              // output coordinates per softmax thread
+constexpr int PTC_SOFT = 128 * PTC_SPR;             // softmax threads
+constexpr int PTC_THREADS = PTC_SOFT + 128 + 32;    // + 4 producer warps + 1 warp that issues the products
 constexpr int PTC_KT = 64;  // cache rows per tile
 
 constexpr int PTC_STAGES = 3;  // K / V tile buffers
@@ -40,8 +44,8 @@ struct PtcSmem {
     static constexpr uint32_t VRM = P + 16384;  // V tile as it lies in the cache, [64 tokens][256 B], chunk c of row r at c ^ (r & 7)
     static constexpr uint32_t NORM = VRM + 16384;  // [PTC_STAGES][K, V][64] halves
     static constexpr uint32_t CTRL = NORM + 1024;  // mbarriers and the tensor-memory base
-    static constexpr uint32_t XCH = CTRL + 128;   // float[2][256]: exchange between the two threads of a score row (by tile parity)
-    static constexpr uint32_t LUT = XCH + 2048;   // 4-bit: [256][32 lanes] half2
+    static constexpr uint32_t XCH = CTRL + 128;   // float[2][PTC_SOFT]: exchange between the threads of a score row (by tile parity)
+    static constexpr uint32_t LUT = XCH + 8 * PTC_SOFT;   // 4-bit: [256][32 lanes] half2
     static constexpr uint32_t BYTES = LUT + 32768;
 };
 constexpr size_t PTC_DYN_SMEM = PtcSmem::BYTES + 1024;  // + alignment slack
@@ -59,6 +63,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
         "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
         "r"(r[31])
+        : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -86,8 +99,10 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const uint32_t sb = (smem_u32(ptc_smem) + 1023u) & ~1023u;
     uint8_t* gb = ptc_smem + (sb - smem_u32(ptc_smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // roles: warps 0-7 softmax (thread = score row 32 (warp & 3) + lane, column half warp >> 2), 8-11 producers, 12 issues the products
-    const bool is_soft = warp < 8, is_prod = warp >= 8 && warp < 12, is_mma = warp == 12;
+    // roles: the first 4 PTC_SPR warps softmax (thread = score row 32 (warp & 3) + lane, column part warp >> 2), then 4 producer
+    // warps, then the warp that issues the products
+    constexpr int SW = 4 * PTC_SPR;
+    const bool is_soft = warp < SW, is_prod = warp >= SW && warp < SW + 4, is_mma = warp == SW + 4;
     const int gs = p.grp_shift, GRP = 1 << gs, QT = PFA_ROWS >> gs;
     const int qb = (int)gridDim.y - 1 - (int)blockIdx.y;  // the longest causal prefixes of all heads and prompts first
     const int seq = (int)blockIdx.x / p.Hkv;
@@ -109,7 +124,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
     const uint32_t bar_rot = sb + PtcSmem::CTRL;            // the two rotation products (count 1, tcgen05.commit)
     const uint32_t bar_pv = sb + PtcSmem::CTRL + 8u;        // value product of a tile done (count 1, commit)
     const uint32_t bar_sfull0 = sb + PtcSmem::CTRL + 16u;   // [2] score product into S buffer i done (count 1, commit)
-    const uint32_t bar_pfull = sb + PtcSmem::CTRL + 32u;    // P of a tile written by all 256 softmax threads
+    const uint32_t bar_pfull = sb + PtcSmem::CTRL + 32u;    // P of a tile written by all softmax threads
     const uint32_t bar_ready0 = sb + PtcSmem::CTRL + 40u;   // [PTC_STAGES] tile staged by the 128 producers
     const uint32_t bar_free0 = sb + PtcSmem::CTRL + 64u;    // [PTC_STAGES] the products that read the stage are done (commit)
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gb + PtcSmem::CTRL + 96);
@@ -134,7 +149,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         mbar_init(bar_pv, 1);
         mbar_init(bar_sfull0, 1);
         mbar_init(bar_sfull0 + 8u, 1);
-        mbar_init(bar_pfull, 256);
+        mbar_init(bar_pfull, PTC_SOFT);
         for (int i = 0; i < PTC_STAGES; ++i) {
             mbar_init(bar_ready0 + 8u * i, 128);
             mbar_init(bar_free0 + 8u * i, 1);
@@ -153,14 +168,14 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         }
     }
     const uint32_t lut = sb + PtcSmem::LUT + 4u * (uint32_t)lane;
-    // softmax threads: score row, column half, the row's query
-    const int srow = (warp & 3) * 32 + lane, half = (warp >> 2) & 1;
+    // softmax threads: score row, column part, the row's query
+    const int srow = (warp & 3) * 32 + lane, part = is_soft ? (warp >> 2) : 0;
     const int my_tok = q0 + (srow >> gs), my_head = kvh * GRP + (srow & (GRP - 1));
-    if (is_soft) {  // the query row: this thread's half of its 16 chunks
+    if (is_soft) {  // the query row: this thread's share of its 16 chunks
         const uint4* src = reinterpret_cast<const uint4*>(q_seq + (size_t)my_tok * p.q_tok_stride + (size_t)my_head * HEAD_DIM);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int ch = 8 * half + c;
+        for (int c = 0; c < 16 / PTC_SPR; ++c) {
+            const int ch = (16 / PTC_SPR) * part + c;
             const uint4 u = my_tok < p.T ? __ldg(src + ch) : make_uint4(0u, 0u, 0u, 0u);
             *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, ch)) = u;
         }
@@ -194,9 +209,9 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             wait_bar(bar_rot, 0u);
             tc_fence_after();
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {  // this thread's 64 coordinates
+            for (int c2 = 0; c2 < PTC_OPT / 32; ++c2) {  // this thread's coordinates
                 uint32_t r[32];
-                tmem_ld32(my_lanes + 64u * half + 32u * c2, r);
+                tmem_ld32(my_lanes + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -206,7 +221,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     u.y = pack_half2(__uint_as_float(r[8 * i + 2]) * sc, __uint_as_float(r[8 * i + 3]) * sc);
                     u.z = pack_half2(__uint_as_float(r[8 * i + 4]) * sc, __uint_as_float(r[8 * i + 5]) * sc);
                     u.w = pack_half2(__uint_as_float(r[8 * i + 6]) * sc, __uint_as_float(r[8 * i + 7]) * sc);
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = u;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, (PTC_OPT / 8) * part + 4 * c2 + i)) = u;
                 }
             }
         }
@@ -220,7 +235,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
 
     if (is_prod) {
         // ================= producers: tile j into stage j % PTC_STAGES =================
-        const int pt = tid - 256, pw = pt >> 5;
+        const int pt = tid - PTC_SOFT, pw = pt >> 5;
         const int ktr = pt & 63, kc = pt >> 6;  // token row of the tile, half of its 128 coordinates
         constexpr int NRAW = BITS == 4 ? 2 : BITS == 2 ? 1 : 8;  // 16-byte loads per thread and array (64 coordinates)
         constexpr int HALF_ROW = BITS == 4 ? 32 : BITS == 2 ? 16 : 128;  // their bytes
@@ -357,25 +372,27 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             }
         }
     } else {
-        // ================= softmax threads: row srow, columns 32 half .. 32 half + 31 of every tile =================
-        const int pair_bar = 2 + (warp & 3);  // named barrier of the two warps that share 32 rows
+        // ================= softmax threads: row srow, columns PTC_CPT part .. + PTC_CPT - 1 of every tile =================
+        const int pair_bar = 2 + (warp & 3);  // named barrier of the PTC_SPR warps that share 32 rows
+        constexpr int ROW_THREADS = 32 * PTC_SPR;
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j % PTC_STAGES, use = j / PTC_STAGES;
             wait_bar(bar_ready0 + 8u * st, (uint32_t)(use & 1));  // (for the tile's norms; the products wait for it themselves)
             wait_bar(bar_sfull0 + 8u * (uint32_t)(j & 1), (uint32_t)((j >> 1) & 1));
             tc_fence_after();
-            uint32_t sr[32];
-            tmem_ld32(my_lanes + 128u + 64u * (uint32_t)(j & 1) + 32u * (uint32_t)half, sr);
+            uint32_t sr[PTC_CPT];
+            if constexpr (PTC_CPT == 32) tmem_ld32(my_lanes + 128u + 64u * (uint32_t)(j & 1) + (uint32_t)(PTC_CPT * part), reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+            else tmem_ld16(my_lanes + 128u + 64u * (uint32_t)(j & 1) + (uint32_t)(PTC_CPT * part), reinterpret_cast<uint32_t(&)[16]>(sr[0]));
             tmem_ld_wait();
             // ---- K norm, causal limit, row maximum over both halves ----
             const bool diagonal = j * PTC_KT + PTC_KT - 1 > q0;
             const uint4* nrm = reinterpret_cast<const uint4*>(gb + PtcSmem::NORM + (uint32_t)st * 256u);
             float mx = -1e30f;
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
+            for (int c8 = 0; c8 < PTC_CPT / 8; ++c8) {
                 float kn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[4 * half + c8];  // (every thread of the warp reads the same words: a broadcast)
+                    const uint4 u = nrm[(PTC_CPT / 8) * part + c8];  // (every thread of the warp reads the same words: a broadcast)
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -388,14 +405,15 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 for (int e = 0; e < 8; ++e) {
                     const int c = 8 * c8 + e;
                     float sv = __uint_as_float(sr[c]) * (BITS != 0 ? kn8[e] : p.score_scale);
-                    if (diagonal && j * PTC_KT + 32 * half + c > my_tok) sv = -1e30f;
+                    if (diagonal && j * PTC_KT + PTC_CPT * part + c > my_tok) sv = -1e30f;
                     sr[c] = __float_as_uint(sv);
                     mx = fmaxf(mx, sv);
                 }
             }
-            xch[(j & 1) * 256 + tid] = mx;
-            named_barrier(pair_bar, 64);
-            mx = fmaxf(mx, xch[(j & 1) * 256 + (tid ^ 128)]);
+            xch[(j & 1) * PTC_SOFT + tid] = mx;
+            named_barrier(pair_bar, ROW_THREADS);
+#pragma unroll
+            for (int k = 1; k < PTC_SPR; ++k) mx = fmaxf(mx, xch[(j & 1) * PTC_SOFT + ((tid + 128 * k) & (PTC_SOFT - 1))]);
             // The reference point of the exponentials follows the row maximum only when that has grown by more than
             // PTC_SLACK (in powers of two) since the point was set: weights then stay below 2^PTC_SLACK, and the output rows
             // in tensor memory need rescaling in the first tiles only.  The result does not depend on the point.
@@ -409,13 +427,13 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, grew)) {  // a row's maximum grew: this warp's half of the output rows is rescaled in place
 #pragma unroll 1
-                    for (int c2 = 0; c2 < 2; ++c2) {
+                    for (int c2 = 0; c2 < PTC_OPT / 32; ++c2) {
                         uint32_t r[32];
-                        tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
+                        tmem_ld32(my_lanes + O_COL + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        tmem_st32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
+                        tmem_st32(my_lanes + O_COL + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                     }
                     tmem_st_wait();
                 }
@@ -423,10 +441,10 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             // ---- P (times the V norm) as fp16 into the A operand tile ----
             float lsum = 0.0f;
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
+            for (int c8 = 0; c8 < PTC_CPT / 8; ++c8) {
                 float vn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[8 + 4 * half + c8];
+                    const uint4 u = nrm[8 + (PTC_CPT / 8) * part + c8];
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -456,7 +474,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 uint4 u;
                 u.x = pack_half2(pv[0], pv[1]); u.y = pack_half2(pv[2], pv[3]);
                 u.z = pack_half2(pv[4], pv[5]); u.w = pack_half2(pv[6], pv[7]);
-                *reinterpret_cast<uint4*>(gb + PtcSmem::P + ptc_chunk(0u, srow, 4 * half + c8)) = u;
+                *reinterpret_cast<uint4*>(gb + PtcSmem::P + ptc_chunk(0u, srow, (PTC_CPT / 8) * part + c8)) = u;
             }
             l_run = l_run * corr + lsum;
             fence_proxy_async_smem();
@@ -466,21 +484,22 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         wait_bar(bar_pv, (uint32_t)((n_tiles - 1) & 1));  // the last value product
         tc_fence_after();
         // the row's sum over both column halves
-        named_barrier(pair_bar, 64);  // (the partner has read the last maxima)
+        named_barrier(pair_bar, ROW_THREADS);  // (the partners have read the last maxima)
         xch[tid] = l_run;
-        named_barrier(pair_bar, 64);
-        l_run += xch[tid ^ 128];
+        named_barrier(pair_bar, ROW_THREADS);
+#pragma unroll
+        for (int k = 1; k < PTC_SPR; ++k) l_run += xch[(tid + 128 * k) & (PTC_SOFT - 1)];
     }
 
     // ================= results =================
     const float inv = 1.0f / (l_run + 1e-8f);
-    __half* const dst = out_seq + (size_t)my_tok * p.q_dim + (size_t)my_head * HEAD_DIM + 64 * half;
+    __half* const dst = out_seq + (size_t)my_tok * p.q_dim + (size_t)my_head * HEAD_DIM + PTC_OPT * part;
     if (BITS == 0) {
         if (is_soft) {
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {
+            for (int c2 = 0; c2 < PTC_OPT / 32; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
+                tmem_ld32(my_lanes + O_COL + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                 tmem_ld_wait();
                 if (my_tok < p.T) {
 #pragma unroll
@@ -501,9 +520,9 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         __syncthreads();  // every product of the tile loop has completed (the softmax threads waited for the last one)
         if (is_soft) {
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {
+            for (int c2 = 0; c2 < PTC_OPT / 32; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + O_COL + 64u * (uint32_t)half + 32u * c2, r);
+                tmem_ld32(my_lanes + O_COL + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -518,8 +537,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                         ph[e] = *reinterpret_cast<const uint32_t*>(&h);
                         pl[e] = pack_half2(x0 - f.x, x1 - f.y);
                     }
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = uh;
-                    *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, srow, 8 * half + 4 * c2 + i)) = ul;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::Q + ptc_chunk(16384u, srow, (PTC_OPT / 8) * part + 4 * c2 + i)) = uh;
+                    *reinterpret_cast<uint4*>(gb + PtcSmem::K + ptc_chunk(16384u, srow, (PTC_OPT / 8) * part + 4 * c2 + i)) = ul;
                 }
             }
         }
@@ -548,9 +567,9 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             wait_bar(bar_rot, 1u);
             tc_fence_after();
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {
+            for (int c2 = 0; c2 < PTC_OPT / 32; ++c2) {
                 uint32_t r[32];
-                tmem_ld32(my_lanes + 64u * (uint32_t)half + 32u * c2, r);
+                tmem_ld32(my_lanes + (uint32_t)(PTC_OPT * part) + 32u * c2, r);
                 tmem_ld_wait();
                 if (my_tok < p.T) {
 #pragma unroll
