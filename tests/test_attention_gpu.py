@@ -303,3 +303,20 @@ def test_prefill_attention_with_query_tiles_at_ragged_sizes(bits, H, Hkv):
     # a short prompt: fewer query tokens than one block, one cache tile
     got_s = gu.gpu_prefill_attention(q[:5], ck, cv, kn, vn, R, msl, H, Hkv, D, bits)
     hp.assert_attention_close(got_s, ref[:5], H, D, "prefill attention, 5 tokens")
+
+
+def test_prefill_attention_mma_sync_form_in_a_child_process():
+    """The tcgen05 form of the prefill attention is the default; the mma.sync form is selected by TQ_PREFILL_ATTN_TC=0, which
+    the library reads once per process: the parity tests of the prefill attention run again in a child with it set."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("TQ_PREFILL_ATTN_TC") == "0":
+        pytest.skip("already the child")
+    env = dict(os.environ, TQ_PREFILL_ATTN_TC="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_attention_gpu.py", "tests/test_fp16_gpu.py", "tests/test_engine_gpu.py",
+                        "-q", "-x", "-m", "gpu", "-k", "prefill and not child", "-p", "no:cacheprovider"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
