@@ -294,8 +294,8 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s);
 
 /* Every layer of a decode step on DEVICE buffers: q/out [layers][G][q_dim], k/v [layers][G][kv_dim]; the layers'
  * append + attention of forward_layer_batch (engine/engine.cpp:1979-2006) for callers that hold all layers' q/k/v
- * at once.  Packed modes run it as three launches whatever the number of layers (one append of every layer's new
- * token, one attention launch that streams the layers back to back, one merge); set TQ_WHOLE_STEP=0 in the
+ * at once.  Packed modes run it as four launches whatever the number of layers (one append of every layer's new
+ * token, one rotation of all queries, one attention launch that streams the layers back to back, one merge); set TQ_WHOLE_STEP=0 in the
  * environment to get one launch per layer instead. */
 int tq_engine_decode_step(tq_engine* e, const void* q, const void* k, const void* v, void* out, tq_stream_t s);
 

@@ -1434,8 +1434,9 @@ int tq_engine_attend_step(tq_engine* e, void* out, tq_stream_t s) {
     return TQ_OK;
 }
 
-// Whole-step form of the layers [l0, l0 + n): three launches whatever n is.
+// Whole-step form of the layers [l0, l0 + n): four launches whatever n is.
 //   1. the new token of every sequence goes into every layer's cache at once (tensor-core append, decode-step form);
+//   1b. all query heads of the n layers are rotated and scaled (tensor cores), stored as fp16;
 //   2. ONE attention launch streams the n layers back to back and publishes its split-K partials per layer;
 //   3. the merge kernel (one CTA per sequence and layer) combines them and applies the inverse rotation.
 // q, k, v, out point at layer l0's [G][dim] blocks of [layers][G][dim] buffers.
