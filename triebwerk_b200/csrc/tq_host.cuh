@@ -227,7 +227,7 @@ inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bo
                       : ensure_dynamic_smem((const void*)prefill_append_tc_kernel<false>, TC_DYN_SMEM);
     if (ar != TQ_OK) return ar;
     const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
-    long long grid = 2ll * device_props().sm_count;
+    long long grid = (long long)TC_CTAS_PER_SM * device_props().sm_count;
     if (grid > tiles) grid = tiles;
     if (grid < 1) return TQ_OK;
     if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);

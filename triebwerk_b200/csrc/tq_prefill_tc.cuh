@@ -5,25 +5,29 @@
 // (vectors x 128) . R^T, so it runs as tcgen05.mma (M = 128 vectors, N = 128 coordinates, K = 128) with the
 // accumulators in tensor memory.  Stored bytes must still equal the reference's, whose rotation is a k-ascending fp32
 // FMA chain; the tensor-core sum has another order.  Therefore:
-//   * the normalised vector x (fp32, computed exactly as the reference does) is fed as TWO fp16 operands,
-//     hi = fp16(x) and lo = fp16((x - hi) * 4096), into two accumulators: x.R = hi.R + 2^-12 * lo.R represents x to
-//     2^-23 relative, as good as fp32 itself;
+//   * the tensor cores rotate the vector AS IT ARRIVES: inputs and R are fp16, so every product r_k * v_k is exact in
+//     fp32 and the accumulator holds sum r_k v_k to fp32 summation error; the epilogue multiplies by 1/norm.  The
+//     reference scales first (x_k = v_k / norm, one fp32 rounding each) and sums then; the two differ by the two
+//     summation errors plus 2^-24 relative for the scaling -- no split of x into a high and a low operand is needed,
+//     and the operand tile is a plain copy of the input;
 //   * a coordinate whose value lies within TC_MARGIN of a decision bound is recomputed with the reference's exact
 //     chain (R read back from the shared-memory operand tile, x rebuilt from the input); everywhere else the
 //     two sums cannot fall on different sides of a bound.  TC_MARGIN (1.6e-5) is twice the textbook bound on the
 //     distance of a 128-term fp32 sum from the exact value when sum|r_k x_k| <= 1 (128 * 2^-24 = 7.6e-6; |x| = 1 and
-//     |R row| = 1): once for the chain, once for the tensor-core sum.  About 1 coordinate in 700 takes the exact path.
+//     |R row| = 1): once for the chain, once for the tensor-core sum, with 8e-7 left for the scaling roundings
+//     (1.2e-7 for |x.R| < 2 and 6e-8 for the x_k).  About 1 coordinate in 700 takes the exact path.
 // Sums of squares, rsqrt/sqrt and the norm use the reference's own order and instructions (see tq_append.cuh).
 //
-// One CTA = 256 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), two CTAs per SM:
+// One CTA = 256 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), three CTAs per SM
+// (76 KB of shared memory, 128 columns of tensor memory and at most 80 registers per thread each):
 //   1. thread (vector, 32-coordinate chunk) loads 64 bytes, builds the reference's shuffle-tree sum of squares in
-//      registers, the four chunk sums meet by shuffles; hi/lo go to shared memory in the canonical K-major
-//      128-byte-swizzled operand layout (rows of 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7));
-//   2. one thread issues 16 tcgen05.mma (2 operands x 8 K-steps of 16) against the resident R tile and commits to
-//      an mbarrier; every wait is bounded;
+//      registers, the four chunk sums meet by shuffles; the 64 bytes go to shared memory as they are, in the canonical
+//      K-major 128-byte-swizzled operand layout (rows of 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7));
+//   2. one thread issues 8 tcgen05.mma (K-steps of 16) against the resident R tile and commits to an mbarrier; every
+//      wait is bounded;
 //   3. each thread reads 64 of ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per
-//      warp and instruction; warps w and w + 4 share a lane quarter), quantises through a 512-bucket uniform grid
-//      (bucket -> code, or -> the one bound inside it), packs, and queues near-bound coordinates;
+//      warp and instruction; warps w and w + 4 share a lane quarter), scales by 1/norm, quantises through a 2048-bucket
+//      uniform grid (bucket -> code, or -> the one bound inside it), packs, and queues near-bound coordinates;
 //   4. queued coordinates get the exact chain and patch the packed tile; the tile leaves as coalesced 16-byte stores.
 #pragma once
 
@@ -34,23 +38,23 @@ namespace tq {
 constexpr int TC_TILE = 128;       // head vectors per tile = MMA M
 constexpr int TC_THREADS = 256;
 constexpr float TC_MARGIN = 1.6e-5f;
-constexpr int TC_LIST_CAP = 256;   // queued near-bound coordinates per tile; the rest is handled by their owners
+constexpr int TC_LIST_CAP = 96;    // queued near-bound coordinates per tile; the rest is handled by their owners
 
 struct TcSmem {
-    static constexpr uint32_t A_HI = 0;                  // 2 K-regions x [128 rows][128 B]
-    static constexpr uint32_t A_LO = 32768;
-    static constexpr uint32_t B_R = 65536;               // R: rows = output coordinate d, K-major
-    static constexpr uint32_t STAGE = A_HI;              // packed codes of the tile, 64 B (4-bit) per vector: written after
+    static constexpr uint32_t A_X = 0;                   // the vectors: 2 K-regions x [128 rows][128 B]
+    static constexpr uint32_t B_R = 32768;               // R: rows = output coordinate d, K-major
+    static constexpr uint32_t STAGE = A_X;               // packed codes of the tile, 64 B (4-bit) per vector: written after
                                                          // the MMAs have consumed the operand tile it overlays
-    static constexpr uint32_t DST = 98304;               // long long[128] byte offset of each vector's codes in the cache (-1: none)
-    static constexpr uint32_t INV = DST + 1024;          // float[128] 1/norm per vector
+    static constexpr uint32_t DST = 65536;               // long long[128] byte offset of each vector's codes in the cache (-1: none)
+    static constexpr uint32_t INV = DST + 1024;          // float[128] 1/norm per vector; -1: the vector holds an infinity or a NaN
     static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
     static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint32[2048] bucket table, see the kernel
     static constexpr uint32_t CTRL = GRID + 8192;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
-    static constexpr uint32_t ABN = CTRL + 16;           // uint8[128]: the vector holds an infinity or a NaN
-    static constexpr uint32_t BYTES = ABN + 128;
+    static constexpr uint32_t BYTES = CTRL + 16;
 };
 constexpr size_t TC_DYN_SMEM = TcSmem::BYTES + 1024;  // + alignment slack
+constexpr int TC_CTAS_PER_SM = 3;
+static_assert(TC_CTAS_PER_SM * (TC_DYN_SMEM + 1024) <= 228 * 1024, "three CTAs of the tensor-core append must fit one SM");
 
 struct PrefillTcParams {
     uint8_t* ck;
@@ -150,7 +154,7 @@ __device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int 
 }
 
 template <bool PRODUCER>
-__global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const PrefillTcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_kernel(const PrefillTcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     const uint32_t base = (smem_u32(tc_smem) + 1023u) & ~1023u;
     uint8_t* gbase = tc_smem + (base - smem_u32(tc_smem));
@@ -159,7 +163,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
     volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
     long long* dst_s = reinterpret_cast<long long*>(gbase + TcSmem::DST);
     float* inv_s = reinterpret_cast<float*>(gbase + TcSmem::INV);
-    uint8_t* abn_s = gbase + TcSmem::ABN;
     uint32_t* list_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::LIST);
     uint32_t* grid_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::GRID);
 
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 
     // ---- once per CTA: tensor memory, barrier, R operand tile, bucket table ----
     if (warp == 0) {
-        tmem_alloc(base + TcSmem::CTRL + 8u, 256u);  // two accumulators of 128 columns
+        tmem_alloc(base + TcSmem::CTRL + 8u, 128u);  // one accumulator of 128 columns (three CTAs share the SM's 512)
         tmem_relinquish();
     }
     if (tid == 0) {
@@ -253,7 +256,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             }
         };
 
-        // ---- 1. load, sum of squares in the reference's order, normalise, split, write the A operand ----
+        // ---- 1. load, sum of squares in the reference's order, write the A operand ----
         constexpr int PASSES = 4 * TC_TILE / TC_THREADS, VPP = TC_THREADS / 4;  // passes per tile, vectors per pass
         uint4 raw_all[PASSES][4];
 #pragma unroll
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                 split_vec(v, tok, head);
                 split_tok(tok, seq, t);
             }
-            const uint4 (&raw)[4] = raw_all[pass];
+            uint4 (&raw)[4] = raw_all[pass];  // becomes the operand: the input as it is, or the produced K vector
             float val[32], sq[32];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -379,6 +382,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                             dstp[i] = *reinterpret_cast<const uint4*>(o);
                         }
                     }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {  // (the values are fp16 numbers already: the conversion is exact)
+                        __half2 o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(val[8 * i + 2 * e], val[8 * i + 2 * e + 1]);
+                        raw[i] = *reinterpret_cast<const uint4*>(o);
+                    }
                 }
             }
 #pragma unroll
@@ -396,7 +406,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
             if (c == 0) {
                 long long row = -1;
                 int layer = 0;
-                abn_s[v] = tt < 3.0e38f ? 0 : 1;  // an infinity or a NaN among the inputs: every coordinate is a NaN
+                const bool abnormal = !(tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
                 if (live) {
                     int sq = seq, cap = p.capacity_rows;
                     if (p.step_G > 0) {
@@ -413,39 +423,24 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
                     }
                 }
                 dst_s[v] = row < 0 ? -1ll : (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
-                inv_s[v] = inv;
+                inv_s[v] = abnormal ? -1.0f : inv;
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // 16-byte chunks: coordinates 32c + 8i .. + 7
-                uint32_t hw[4], lw[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float x0 = mul_ftz(val[8 * i + 2 * e], inv), x1 = mul_ftz(val[8 * i + 2 * e + 1], inv);
-                    const __half2 h = __floats2half2_rn(x0, x1);
-                    const float2 hf = __half22float2(h);
-                    hw[e] = *reinterpret_cast<const uint32_t*>(&h);
-                    lw[e] = pack_half2((x0 - hf.x) * 4096.0f, (x1 - hf.y) * 4096.0f);
-                }
-                const uint32_t a = tc_operand_addr(base + TcSmem::A_HI, v, 32 * c + 8 * i);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(hw[0]), "r"(hw[1]), "r"(hw[2]), "r"(hw[3]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a + (TcSmem::A_LO - TcSmem::A_HI)), "r"(lw[0]),
-                             "r"(lw[1]), "r"(lw[2]), "r"(lw[3]) : "memory");
+                const uint32_t a = tc_operand_addr(base + TcSmem::A_X, v, 32 * c + 8 * i);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(raw[i].x), "r"(raw[i].y), "r"(raw[i].z), "r"(raw[i].w) : "memory");
             }
         }
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
         __syncthreads();
 
-        // ---- 2. the rotation: two accumulators (hi and scaled lo), 8 K-steps each ----
+        // ---- 2. the rotation: 8 K-steps into one accumulator ----
         if (tid == 0 && !dead) {
             tc_fence_after();
 #pragma unroll
-            for (int op = 0; op < 2; ++op) {
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t koff = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-                    umma_f16(tmem + (uint32_t)op * 128u, umma_desc_sw128(base + (op ? TcSmem::A_LO : TcSmem::A_HI) + koff),
-                             umma_desc_sw128(base + TcSmem::B_R + koff), TC_IDESC, ks != 0);
-                }
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t koff = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+                umma_f16(tmem, umma_desc_sw128(base + TcSmem::A_X + koff), umma_desc_sw128(base + TcSmem::B_R + koff), TC_IDESC, ks != 0);
             }
             umma_commit(bar);
         }
@@ -463,25 +458,26 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
         const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
         uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
         if (!dead) {
-            const bool abn = abn_s[ev] != 0;
+            const float inv = inv_s[ev];
+            const bool abn = inv < 0.0f;
 #pragma unroll 1
             for (int cc = cc0; cc < cc0 + 2; ++cc) {
-                uint32_t hi_r[32], lo_r[32];
+                uint32_t acc_r[32];
                 const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cc * 32u;
-                tmem_ld32(taddr, hi_r);
-                tmem_ld32(taddr + 128u, lo_r);
+                tmem_ld32(taddr, acc_r);
                 tmem_ld_wait();
                 uint32_t words[4] = {0u, 0u, 0u, 0u};
                 uint32_t near_mask = 0u;  // queued after the loop: no store may sit between the table look-ups
                 // coordinates in descending order: codes and near-bound flags are shifted in from the right
                 auto one = [&](int i, uint32_t& word, int width) {
-                    const float dval = fmaf(__uint_as_float(lo_r[i]), 1.0f / 4096.0f, __uint_as_float(hi_r[i]));
+                    const float dval = __uint_as_float(acc_r[i]) * inv;
                     const uint32_t kb = __float_as_uint(fmaf(dval, 512.0f, 3145728.0f));  // k = rne(2048 x) in the low bits
                     const uint32_t e = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(grid_s) + (kb & 0x1ffcu));
                     const float d = dval - __uint_as_float(e);
                     const uint32_t code = (e & 31u) - (__float_as_uint(d) >> 31);
                     word = (word << width) + code;
-                    near_mask = (near_mask << 1) + (fabsf(d) < TC_MARGIN + 1.0e-6f ? 1u : 0u);
+                    // (the sign bit of |d| - margin, shifted in from the right)
+                    near_mask = __funnelshift_l(__float_as_uint(fabsf(d) - (TC_MARGIN + 1.0e-6f)), near_mask, 1);
                 };
                 if (bits == 4) {
 #pragma unroll
@@ -621,7 +617,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_append_tc_kernel(const 
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256u);
+    if (warp == 0) tmem_dealloc(tmem, 128u);
 }
 
 }  // namespace tq
