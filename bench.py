@@ -366,7 +366,7 @@ def run_append_only(args, w, rank, world, local_rank):
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": 1 if big else max(3, args.warmup),
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 in, tcgen05 f16 hi/lo -> f32 (+ exact f32 chain near bounds), u8 codes", "data": "synthetic",
+        "dtype": "f16 in, tcgen05 f16 x f16 -> f32 (+ exact f32 chain near bounds), u8 codes", "data": "synthetic",
         "config": {"workload": w["desc"], "kv_bits": bits, "l2": "every step rewrites %.0f MB of cache" % (vectors * (D // vpb + 2) / 1e6)},
         "head_vectors_per_s": vectors / (ms * 1e-3),
         "append_tokens_per_s_28_layers": vectors / (ms * 1e-3) / (28 * 2 * Hkv),

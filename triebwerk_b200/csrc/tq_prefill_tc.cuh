@@ -40,19 +40,23 @@ constexpr int TC_THREADS = 256;
 constexpr float TC_MARGIN = 1.6e-5f;
 constexpr int TC_LIST_CAP = 96;    // queued near-bound coordinates per tile; the rest is handled by their owners
 
+// Shared memory by ABSOLUTE shared address (the kernel checks that its dynamic shared memory covers the range): the
+// bucket table sits on a 4096-byte boundary so that its look-up address is (bits & 0xffc) plus a constant.
 struct TcSmem {
-    static constexpr uint32_t A_X = 0;                   // the vectors: 2 K-regions x [128 rows][128 B]
-    static constexpr uint32_t B_R = 32768;               // R: rows = output coordinate d, K-major
+    static constexpr uint32_t DST = 0x0800;              // long long[128] byte offset of each vector's codes in the cache (-1: none)
+    static constexpr uint32_t INV = DST + 1024;          // float[128]: sum of squares, then 1/norm per vector; -1: the vector
+                                                         // holds an infinity or a NaN
+    static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
+    static constexpr uint32_t CTRL = LIST + 4 * TC_LIST_CAP;  // mbarrier (8 B), tmem base (4 B), list count (4 B)
+    static constexpr uint32_t GRID = 0x1000;             // uint32[1024] bucket table, see the kernel
+    static constexpr uint32_t A_X = 0x2000;              // the vectors: 2 K-regions x [128 rows][128 B]
+    static constexpr uint32_t B_R = 0xA000;              // R: rows = output coordinate d, K-major
     static constexpr uint32_t STAGE = A_X;               // packed codes of the tile, 64 B (4-bit) per vector: written after
                                                          // the MMAs have consumed the operand tile it overlays
-    static constexpr uint32_t DST = 65536;               // long long[128] byte offset of each vector's codes in the cache (-1: none)
-    static constexpr uint32_t INV = DST + 1024;          // float[128] 1/norm per vector; -1: the vector holds an infinity or a NaN
-    static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
-    static constexpr uint32_t GRID = LIST + 4 * TC_LIST_CAP;  // uint32[2048] bucket table, see the kernel
-    static constexpr uint32_t CTRL = GRID + 8192;        // mbarrier (8 B), tmem base (4 B), list count (4 B)
-    static constexpr uint32_t BYTES = CTRL + 16;
+    static constexpr uint32_t END = 0x12000;
 };
-constexpr size_t TC_DYN_SMEM = TcSmem::BYTES + 1024;  // + alignment slack
+static_assert(TcSmem::CTRL + 16 <= TcSmem::GRID, "control words run into the bucket table");
+constexpr size_t TC_DYN_SMEM = TcSmem::END;  // enough wherever the dynamic shared memory starts at or below TcSmem::DST
 constexpr int TC_CTAS_PER_SM = 3;
 static_assert(TC_CTAS_PER_SM * (TC_DYN_SMEM + 1024) <= 228 * 1024, "three CTAs of the tensor-core append must fit one SM");
 
@@ -136,6 +140,65 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Two fp32 operations per instruction (the packed fp32 forms of this architecture), each half rounded exactly like
+// the scalar instruction of the same name.
+__device__ __forceinline__ float2 mul2_ftz(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2_ftz(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fma2_ftz(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {  // (no flush to zero)
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+// Sum of the squares of 32 fp16 values given as 16 float pairs, in the order of the reference's shuffle tree over 32
+// lanes (offsets 16, 8, 4, 2, 1 with element l in lane l's place).  The square of an fp16 value is exact in fp32, so
+// the first level's a*a + b*b is one fused multiply-add on top of one multiplication: same bits as two products and a sum.
+__device__ __forceinline__ float sumsq_tree32(const float2 (&v)[16]) {
+    float2 s[8];
+#pragma unroll
+    for (int l = 0; l < 8; ++l) s[l] = fma2_ftz(v[l + 8], v[l + 8], mul2_ftz(v[l], v[l]));
+#pragma unroll
+    for (int l = 0; l < 4; ++l) s[l] = add2_ftz(s[l], s[l + 4]);
+    s[0] = add2_ftz(s[0], s[2]);
+    s[1] = add2_ftz(s[1], s[3]);
+    s[0] = add2_ftz(s[0], s[1]);
+    return add_ftz(s[0].x, s[0].y);
+}
+// One entry of the bucket table (see the kernel), addressed by the low mantissa bits of the grid value.
+__device__ __forceinline__ uint32_t bucket_entry(uint32_t grid_bits) {
+    uint32_t e;
+    asm("ld.shared.u32 %0, [%1 + %2];" : "=r"(e) : "r"(grid_bits & 0xffcu), "n"(TcSmem::GRID));
+    return e;
+}
+__device__ __forceinline__ uint32_t mad_hi_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // Shared-memory matrix descriptor of a K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of
 // 8 rows 1024 bytes apart; `addr` is the shared address of the tile (1024-byte aligned) plus 32 bytes per K-step.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
@@ -156,9 +219,14 @@ __device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int 
 template <bool PRODUCER>
 __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_kernel(const PrefillTcParams p) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
-    const uint32_t base = (smem_u32(tc_smem) + 1023u) & ~1023u;
-    uint8_t* gbase = tc_smem + (base - smem_u32(tc_smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t dyn_base = smem_u32(tc_smem);
+    if (dyn_base > TcSmem::DST || dyn_base + (uint32_t)TC_DYN_SMEM < TcSmem::END) {  // (uniform over the CTA)
+        if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
+        return;
+    }
+    constexpr uint32_t base = 0u;                 // TcSmem holds absolute shared addresses
+    uint8_t* gbase = tc_smem - dyn_base;          // generic address of shared address 0
     const uint32_t bar = base + TcSmem::CTRL;
     volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
     long long* dst_s = reinterpret_cast<long long*>(gbase + TcSmem::DST);
@@ -185,16 +253,17 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM) + j);
         *reinterpret_cast<uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base)) = u;
     }
-    for (int i = tid; i < 2048; i += TC_THREADS) {
-        // Bucket table over the rotated coordinate x.  The epilogue forms k = rne(2048 x) in the low mantissa bits of
-        // fma(x, 512, 1.5 * 2^21) and takes bucket k >> 2 (modulo 2048): bucket n holds x in [(4 n - 0.5) / 2048,
-        // (4 n + 3.5) / 2048], |x| < 2.  An entry is ONE float: the decision bound that lies inside the bucket (widened by
-        // four margins) with its five lowest mantissa bits replaced by the code a value at or above the bound gets --
-        // the code is then entry_code - (x < bound) -- or, when no bound is near the bucket, 0x7f000000 (1.7e38: every x
-        // is below it) carrying the bucket's code + 1.  The replaced bits move the bound by less than 5e-7; the near-bound
-        // test uses a margin wider by that much, and only coordinates outside it keep the code found here.
-        const int n = i < 1024 ? i : i - 2048;
-        const float lo = ((float)(4 * n) - 0.5f) * (1.0f / 2048.0f), hi = lo + (1.0f / 512.0f);
+    for (int i = tid; i < 1024; i += TC_THREADS) {
+        // Bucket table over the rotated coordinate x.  The epilogue forms k = rne(1024 x) in the low mantissa bits of
+        // fma(x, 256, 1.5 * 2^21) and takes bucket k >> 2 (modulo 1024): bucket n holds x in [(4 n - 0.5) / 1024,
+        // (4 n + 3.5) / 1024], |x| < 2; no two bounds are closer than five buckets.  An entry is ONE float: the decision
+        // bound that lies inside the bucket (widened by four margins) with its four lowest mantissa bits replaced by the
+        // code a value BELOW the bound gets -- the code is then entry_code + (x > bound) -- or, when no bound is near the
+        // bucket, 0x7f000000 (1.7e38: every x is below it) carrying the bucket's code.  The replaced bits move the bound
+        // by less than 3e-7; the near-bound test uses a margin wider by more than that, and only coordinates outside it
+        // keep the code found here.
+        const int n = i < 512 ? i : i - 1024;
+        const float lo = ((float)(4 * n) - 0.5f) * (1.0f / 1024.0f), hi = lo + (1.0f / 256.0f);
         int code = 0, amb = -1;
         float ambv = 0.0f;
         for (int b = 0; b < nb; ++b) {
@@ -202,7 +271,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             if (bv <= lo) ++code;
             if (bv >= lo - 4.0f * TC_MARGIN && bv <= hi + 4.0f * TC_MARGIN) { amb = b; ambv = bv; }
         }
-        grid_s[i] = amb >= 0 ? ((__float_as_uint(ambv) & ~31u) | (uint32_t)(amb + 1)) : (0x7f000000u | (uint32_t)(code + 1));
+        grid_s[i] = amb >= 0 ? ((__float_as_uint(ambv) & ~15u) | (uint32_t)amb) : (0x7f000000u | (uint32_t)code);
     }
     fence_proxy_async_smem();
     tc_fence_before();
@@ -287,34 +356,25 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             const int vid = vec0 + v;
             const bool live = vid < vec_per_kind;
             int tok = 0, head = 0, seq = 0, t = 0;
-            if (live) {
+            if (PRODUCER && live) {  // (where the vector goes is worked out once per vector, below)
                 split_vec(v, tok, head);
                 split_tok(tok, seq, t);
             }
             uint4 (&raw)[4] = raw_all[pass];  // becomes the operand: the input as it is, or the produced K vector
-            float val[32], sq[32];
+            float2 v2[16];                    // the chunk's 32 values as pairs (2j, 2j + 1)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __half22float2(h2[e]);
-                    val[8 * i + 2 * e] = f.x;
-                    val[8 * i + 2 * e + 1] = f.y;
-                }
+                for (int e = 0; e < 4; ++e) v2[4 * i + e] = __half22float2(h2[e]);
             }
             const int l0 = lane & ~3;
             if constexpr (PRODUCER) {
                 if (kind == 0) {  // K vectors only; every thread of the warp walks the shuffles
                     // RMS norm: sum of squares by the reference's block tree, x * rms * w rounded to fp16
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                        for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
-                    const float q0 = __shfl_sync(0xffffffffu, sq[0], l0), q1 = __shfl_sync(0xffffffffu, sq[0], l0 + 1);
-                    const float q2 = __shfl_sync(0xffffffffu, sq[0], l0 + 2), q3 = __shfl_sync(0xffffffffu, sq[0], l0 + 3);
+                    const float qpart = sumsq_tree32(v2);
+                    const float q0 = __shfl_sync(0xffffffffu, qpart, l0), q1 = __shfl_sync(0xffffffffu, qpart, l0 + 1);
+                    const float q2 = __shfl_sync(0xffffffffu, qpart, l0 + 2), q3 = __shfl_sync(0xffffffffu, qpart, l0 + 3);
                     const float rms = rsqrt_approx_ftz(fma_ftz(add_ftz(add_ftz(q0, q2), add_ftz(q1, q3)), 1.0f / HEAD_DIM, p.eps));
                     int layer = 0, sq_i = seq, ppos;
                     if (p.step_G > 0) {
@@ -335,8 +395,8 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                         for (int e = 0; e < 4; ++e) {
                             float2 wf = __half22float2(w2[e]);
                             if (p.biased) { wf.x = add_ftz(wf.x, 1.0f); wf.y = add_ftz(wf.y, 1.0f); }
-                            const __half2 h = __floats2half2_rn(mul_ftz(mul_ftz(val[8 * i + 2 * e], rms), wf.x),
-                                                                mul_ftz(mul_ftz(val[8 * i + 2 * e + 1], rms), wf.y));
+                            const __half2 h = __floats2half2_rn(mul_ftz(mul_ftz(v2[4 * i + e].x, rms), wf.x),
+                                                                mul_ftz(mul_ftz(v2[4 * i + e].y, rms), wf.y));
                             nh[4 * i + e] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     }
@@ -368,63 +428,28 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                                     r.y = __half2float(__float2half_rn(fma_ftz(xp.y, sf.y, mul_ftz(xo.y, cf.y))));
                                 }
                             }
-                            val[8 * i + 2 * e] = r.x;
-                            val[8 * i + 2 * e + 1] = r.y;
-                        }
-                    }
-                    if (live) {
-                        uint4* dstp = reinterpret_cast<uint4*>(p.k_post + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * c);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            __half2 o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(val[8 * i + 2 * e], val[8 * i + 2 * e + 1]);
-                            dstp[i] = *reinterpret_cast<const uint4*>(o);
+                            v2[4 * i + e] = r;
                         }
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {  // (the values are fp16 numbers already: the conversion is exact)
                         __half2 o[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(val[8 * i + 2 * e], val[8 * i + 2 * e + 1]);
+                        for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(v2[4 * i + e].x, v2[4 * i + e].y);
                         raw[i] = *reinterpret_cast<const uint4*>(o);
                     }
+                    if (live) {
+                        uint4* dstp = reinterpret_cast<uint4*>(p.k_post + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM + 32 * c);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dstp[i] = raw[i];
+                    }
                 }
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) sq[i] = mul_ftz(val[i], val[i]);
-            // the warp-shuffle tree of the reference (offsets 16, 8, 4, 2, 1), element l taking lane l's place
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                for (int l = 0; l < off; ++l) sq[l] = add_ftz(sq[l], sq[l + off]);
-            const float part = sq[0];
+            // the warp-shuffle tree of the reference (offsets 16, 8, 4, 2, 1) within the chunk, then across the four chunks
+            const float part = sumsq_tree32(v2);
             const float p0 = __shfl_sync(0xffffffffu, part, l0), p1 = __shfl_sync(0xffffffffu, part, l0 + 1);
             const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
-            const float tt = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
-            const float inv = rsqrt_approx_ftz(tt);
-            if (c == 0) {
-                long long row = -1;
-                int layer = 0;
-                const bool abnormal = !(tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
-                if (live) {
-                    int sq = seq, cap = p.capacity_rows;
-                    if (p.step_G > 0) {
-                        layer = seq / p.step_G;
-                        sq = seq - layer * p.step_G;
-                        if (p.seq_capacity) cap = p.seq_capacity[sq];
-                    }
-                    const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
-                    if (pos >= 0 && (cap <= 0 || pos < cap)) {
-                        row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
-                        cn[(size_t)layer * (size_t)p.norm_layer_stride + (size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
-                    } else {
-                        atomicMax(p.status, ST_BAD_POSITION);
-                    }
-                }
-                dst_s[v] = row < 0 ? -1ll : (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
-                inv_s[v] = abnormal ? -1.0f : inv;
-            }
+            if (c == 0) inv_s[v] = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);  // turned into 1/norm below
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // 16-byte chunks: coordinates 32c + 8i .. + 7
                 const uint32_t a = tc_operand_addr(base + TcSmem::A_X, v, 32 * c + 8 * i);
@@ -444,6 +469,35 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             }
             umma_commit(bar);
         }
+        // ---- 2b. while the tensor core works: thread v < 128 settles vector v -- norm out, 1/norm, where its codes go ----
+        if (tid < TC_TILE) {
+            const int v = tid;
+            const bool live = vec0 + v < vec_per_kind;
+            const float tt = inv_s[v];
+            const bool abnormal = !(tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
+            long long row = -1;
+            int layer = 0, head = 0;
+            if (live) {
+                int tok, seq, t;
+                split_vec(v, tok, head);
+                split_tok(tok, seq, t);
+                int sq = seq, cap = p.capacity_rows;
+                if (p.step_G > 0) {
+                    layer = seq / p.step_G;
+                    sq = seq - layer * p.step_G;
+                    if (p.seq_capacity) cap = p.seq_capacity[sq];
+                }
+                const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
+                if (pos >= 0 && (cap <= 0 || pos < cap)) {
+                    row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
+                    cn[(size_t)layer * (size_t)p.norm_layer_stride + (size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
+                } else {
+                    atomicMax(p.status, ST_BAD_POSITION);
+                }
+            }
+            dst_s[v] = row < 0 ? -1ll : (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
+            inv_s[v] = abnormal ? -1.0f : rsqrt_approx_ftz(tt);
+        }
         if (!dead && !mbar_wait_bounded(bar, phase, 1u << 22)) {
             dead = true;
             atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
@@ -460,6 +514,8 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         if (!dead) {
             const float inv = inv_s[ev];
             const bool abn = inv < 0.0f;
+            const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * 256.0f, inv * 256.0f);
+            const float2 magic2 = make_float2(3145728.0f, 3145728.0f);
 #pragma unroll 1
             for (int cc = cc0; cc < cc0 + 2; ++cc) {
                 uint32_t acc_r[32];
@@ -467,29 +523,33 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 tmem_ld32(taddr, acc_r);
                 tmem_ld_wait();
                 uint32_t words[4] = {0u, 0u, 0u, 0u};
-                uint32_t near_mask = 0u;  // queued after the loop: no store may sit between the table look-ups
-                // coordinates in descending order: codes and near-bound flags are shifted in from the right
-                auto one = [&](int i, uint32_t& word, int width) {
-                    const float dval = __uint_as_float(acc_r[i]) * inv;
-                    const uint32_t kb = __float_as_uint(fmaf(dval, 512.0f, 3145728.0f));  // k = rne(2048 x) in the low bits
-                    const uint32_t e = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(grid_s) + (kb & 0x1ffcu));
-                    const float d = dval - __uint_as_float(e);
-                    const uint32_t code = (e & 31u) - (__float_as_uint(d) >> 31);
-                    word = (word << width) + code;
-                    // (the sign bit of |d| - margin, shifted in from the right)
-                    near_mask = __funnelshift_l(__float_as_uint(fabsf(d) - (TC_MARGIN + 1.0e-6f)), near_mask, 1);
+                uint32_t near_rev = 0u;  // bit 31 - i: coordinate i is near a bound (queued after the loop)
+                // Two coordinates at a time, ascending; codes and near-bound flags are shifted in by funnel shifts, which
+                // keep only the bits that count: the entry's four (two) low bits plus one if the value lies above the
+                // entry's bound (the sign of bound - value, added as the high word of twice its bits).
+                auto two = [&](int i, uint32_t& word, int width) {
+                    const float2 a = make_float2(__uint_as_float(acc_r[i]), __uint_as_float(acc_r[i + 1]));
+                    const float2 dval = mul2(a, inv2);
+                    const float2 kf = fma2(a, inv256, magic2);  // k = rne(1024 x) in the low bits
+                    const uint32_t e0 = bucket_entry(__float_as_uint(kf.x)), e1 = bucket_entry(__float_as_uint(kf.y));
+                    const float d0 = __uint_as_float(e0) - dval.x, d1 = __uint_as_float(e1) - dval.y;
+                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(d0), 2u, e0), width);
+                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(d1), 2u, e1), width);
+                    near_rev = __funnelshift_l(__float_as_uint(fabsf(d0) - (TC_MARGIN + 1.0e-6f)), near_rev, 1);
+                    near_rev = __funnelshift_l(__float_as_uint(fabsf(d1) - (TC_MARGIN + 1.0e-6f)), near_rev, 1);
                 };
                 if (bits == 4) {
 #pragma unroll
-                    for (int j = 3; j >= 0; --j)
+                    for (int j = 0; j < 4; ++j)
 #pragma unroll
-                        for (int k = 7; k >= 0; --k) one(8 * j + k, words[j], 4);
+                        for (int k = 0; k < 8; k += 2) two(8 * j + k, words[j], 4);
                 } else {
 #pragma unroll
-                    for (int j = 1; j >= 0; --j)
+                    for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int k = 15; k >= 0; --k) one(16 * j + k, words[j], 2);
+                        for (int k = 0; k < 16; k += 2) two(16 * j + k, words[j], 2);
                 }
+                uint32_t near_mask = __brev(near_rev);
                 if (abn) {  // what the reference's comparisons make of a NaN: the top code at 4 bits, code 0 at 2 bits
                     words[0] = words[1] = words[2] = words[3] = bits == 4 ? 0xffffffffu : 0u;
                     near_mask = 0u;
@@ -510,27 +570,30 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         __syncthreads();
 
         // ---- 4. exact chain for the queued coordinates, patch the packed tile ----
-        auto exact_code = [&](int v, int d) -> int {
+        auto exact_code = [&](int v, int d) -> int {  // one thread, the reference's k-ascending chain
             const int vid = vec0 + v;
             const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
             const bool produced = PRODUCER && kind == 0;
             const uint4* src = reinterpret_cast<const uint4*>((produced ? p.k_post : src_buf) + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM);
             const float inv = inv_s[v];
-            uint4 xall[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) xall[j] = produced ? src[j] : __ldg(src + j);
             float acc = 0.0f;
+#pragma unroll 1
+            for (int j0 = 0; j0 < 16; j0 += 8) {  // eight 16-byte loads in flight at a time
+                uint4 xall[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint4 xv = xall[j];
-                const uint4 rv = *reinterpret_cast<const uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base));
-                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
-                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+                for (int j = 0; j < 8; ++j) xall[j] = produced ? src[j0 + j] : __ldg(src + j0 + j);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
-                    acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
-                    acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+                for (int j = 0; j < 8; ++j) {
+                    const uint4 xv = xall[j];
+                    const uint4 rv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::B_R, d, 8 * (j0 + j)));
+                    const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                    const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                        acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
+                        acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+                    }
                 }
             }
             return quantize_code(acc, bits);
@@ -543,51 +606,15 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             atomicOr(w, (uint32_t)code << sh);
         };
         if (!dead) {
-            // Queued coordinates: 8 lanes per item.  Lane s of the group prepares terms k = 16 s .. 16 s + 15 (R from the
-            // shared-memory operand tile, x from the input, x / norm as the reference forms it); the k-ascending chain
-            // then runs through the lanes in order, the running sum handed on by a shuffle.
+            // Queued coordinates: one lane per item, 32 items per warp and round (a tile queues about 23).
             const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
-            const int sub = lane & 7;
-            for (uint32_t i0 = (uint32_t)warp * 4u; i0 < queued; i0 += (TC_THREADS / 32) * 4) {  // warp-uniform
-                const uint32_t i = i0 + (uint32_t)(lane >> 3);
-                const uint32_t item = i < queued ? list_s[i] : 0u;
-                const int v = (int)(item >> 8), d = (int)(item & 255u);
-                const bool live = i < queued && vec0 + v < vec_per_kind;
-                float xs[16], rr[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) xs[e] = rr[e] = 0.0f;
-                if (live) {
-                    const int vid = vec0 + v;
-                    const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
-                    const bool produced = PRODUCER && kind == 0;
-                    const uint4* src = reinterpret_cast<const uint4*>((produced ? p.k_post : src_buf) + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM) + 2 * sub;
-                    const float inv = inv_s[v];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const uint4 xv = produced ? src[j] : __ldg(src + j);
-                        const uint4 rv = *reinterpret_cast<const uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 16 * sub + 8 * j) - base));
-                        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
-                        const __half2* rh = reinterpret_cast<const __half2*>(&rv);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
-                            xs[8 * j + 2 * e] = mul_ftz(xf.x, inv);
-                            xs[8 * j + 2 * e + 1] = mul_ftz(xf.y, inv);
-                            rr[8 * j + 2 * e] = rf.x;
-                            rr[8 * j + 2 * e + 1] = rf.y;
-                        }
-                    }
+            for (uint32_t i0 = (uint32_t)warp * 32u; i0 < queued; i0 += TC_THREADS) {  // warp-uniform
+                const uint32_t i = i0 + (uint32_t)lane;
+                if (i < queued) {
+                    const uint32_t item = list_s[i];
+                    const int v = (int)(item >> 8), d = (int)(item & 255u);
+                    if (vec0 + v < vec_per_kind) patch(v, d, exact_code(v, d));
                 }
-                float acc = 0.0f;
-#pragma unroll
-                for (int st = 0; st < 8; ++st) {
-                    if (sub == st) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) acc = fma_ftz(rr[e], xs[e], acc);
-                    }
-                    acc = __shfl_sync(0xffffffffu, acc, (lane & ~7) + st);
-                }
-                if (live && sub == 0) patch(v, d, quantize_code(acc, bits));
             }
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
