@@ -294,13 +294,71 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     const bool fast_tok = p.T > TC_TILE + 1;
     const int cpv_shift = bits == 4 ? 2 : 1;  // 16-byte chunks per packed vector, as a shift
 
+    const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
+    const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
+
+    // ---- step 4 of a tile: the exact chain for its queued coordinates (about 23 of 16384), patching the stored codes.
+    // It runs at the start of the NEXT round, after that round's loads have been issued and before the barrier that
+    // lets the operand tile be overwritten: the warps without queued items work on their loads meanwhile.
+    auto exact_code = [&](int v, int d) -> int {  // one thread, the reference's k-ascending chain
+        const float inv = inv_s[v];
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int j = 0; j < 16; ++j) {  // x from the operand tile (the vector as it was rotated), R from its tile
+            const uint4 xv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::A_X, v, 8 * j));
+            const uint4 rv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::B_R, d, 8 * j));
+            const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+            const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
+                acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+            }
+        }
+        return quantize_code(acc, bits);
+    };
+    auto patch = [&](uint8_t* cqp, int v, int d, int code) {  // one code of vector v in the cache (the tile's stores came before)
+        const long long dst = dst_s[v];
+        if (dst < 0) return;
+        uint32_t* w = reinterpret_cast<uint32_t*>(cqp + dst) + (bits == 4 ? d >> 3 : d >> 4);
+        const int sh = bits == 4 ? 4 * (d & 7) : 2 * (d & 15);
+        const uint32_t m = (bits == 4 ? 0xfu : 0x3u) << sh;
+        atomicAnd(w, ~m);
+        atomicOr(w, (uint32_t)code << sh);
+    };
+    auto run_chains = [&](uint8_t* cqp, uint32_t own0, uint32_t own1) {
+        // Queued coordinates: one lane per item, 32 items per warp and round.
+        const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
+        for (uint32_t i0 = (uint32_t)warp * 32u; i0 < queued; i0 += TC_THREADS) {  // warp-uniform
+            const uint32_t i = i0 + (uint32_t)lane;
+            if (i < queued) {
+                const uint32_t item = list_s[i];
+                const int v = (int)(item >> 8), d = (int)(item & 255u);
+                patch(cqp, v, d, exact_code(v, d));
+            }
+        }
+        // ... and those that did not fit the queue, by their owners
+        while (own0) {
+            const int i = __ffs(own0) - 1;
+            own0 &= own0 - 1;
+            patch(cqp, ev, 32 * cc0 + i, exact_code(ev, 32 * cc0 + i));
+        }
+        while (own1) {
+            const int i = __ffs(own1) - 1;
+            own1 &= own1 - 1;
+            patch(cqp, ev, 32 * (cc0 + 1) + i, exact_code(ev, 32 * (cc0 + 1) + i));
+        }
+    };
+    uint8_t* prev_cq = nullptr;  // the previous tile's code array: its exact chains are still to run
+    uint32_t prev_own0 = 0u, prev_own1 = 0u;
+
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
         const int vec0 = (tile - (kind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
         const __half* src_buf = kind == 0 ? p.k_buf : p.v_buf;
         uint8_t* cq = kind == 0 ? p.ck : p.cv;
         __half* cn = kind == 0 ? p.kn : p.vn;
-        if (tid == 0) ctrl[3] = 0;
         const int tok0 = vec0 / p.Hkv, head0 = vec0 - tok0 * p.Hkv;
         const int seq0 = tok0 / p.T, t0 = tok0 - seq0 * p.T;
         auto split_vec = [&](int v, int& tok, int& head) {  // vector vec0 + v of the tile
@@ -325,9 +383,11 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             }
         };
 
-        // ---- 1. load, sum of squares in the reference's order, write the A operand ----
+        // ---- 1. load, sum of squares in the reference's order (registers only: the previous tile's exact chains may
+        //         still be reading its operand rows) ----
         constexpr int PASSES = 4 * TC_TILE / TC_THREADS, VPP = TC_THREADS / 4;  // passes per tile, vectors per pass
         uint4 raw_all[PASSES][4];
+        float tt_all[PASSES];
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {  // every load of the tile goes out before the arithmetic starts
             const int vid = vec0 + pass * VPP + (tid >> 2);
@@ -350,6 +410,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 }
             }
         }
+        if (prev_cq && !dead) run_chains(prev_cq, prev_own0, prev_own1);
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {
             const int v = pass * VPP + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
@@ -449,11 +510,19 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             const float part = sumsq_tree32(v2);
             const float p0 = __shfl_sync(0xffffffffu, part, l0), p1 = __shfl_sync(0xffffffffu, part, l0 + 1);
             const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
-            if (c == 0) inv_s[v] = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);  // turned into 1/norm below
+            tt_all[pass] = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
+        }
+        __syncthreads();  // the previous tile is finished with the operand tile, the queue and the per-vector arrays
+        if (tid == 0) ctrl[3] = 0;
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) {  // the vectors as they are become the A operand
+            const int v = pass * VPP + (tid >> 2), c = tid & 3;
+            if (c == 0) inv_s[v] = tt_all[pass];  // turned into 1/norm below
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // 16-byte chunks: coordinates 32c + 8i .. + 7
                 const uint32_t a = tc_operand_addr(base + TcSmem::A_X, v, 32 * c + 8 * i);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(raw[i].x), "r"(raw[i].y), "r"(raw[i].z), "r"(raw[i].w) : "memory");
+                const uint4 r = raw_all[pass][i];
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
             }
         }
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
@@ -508,11 +577,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
 
         // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
         //         w + 4 share those vectors and take 64 of the 128 coordinates (two blocks of 32 columns) each ----
-        const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
-        const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
         uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
         if (!dead) {
             const float inv = inv_s[ev];
+            const long long ev_dst = dst_s[ev];
             const bool abn = inv < 0.0f;
             const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * 256.0f, inv * 256.0f);
             const float2 magic2 = make_float2(3145728.0f, 3145728.0f);
@@ -554,6 +622,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                     words[0] = words[1] = words[2] = words[3] = bits == 4 ? 0xffffffffu : 0u;
                     near_mask = 0u;
                 }
+                if (ev_dst < 0) near_mask = 0u;  // (a vector past the end of the input is all zeros: every coordinate ON a bound)
                 while (near_mask) {
                     const int i = __ffs(near_mask) - 1;
                     near_mask &= near_mask - 1;
@@ -561,86 +630,22 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                     if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)ev << 8) | (uint32_t)(32 * cc + i);
                     else own_cc[cc - cc0] |= 1u << i;
                 }
-                uint8_t* st = gbase + TcSmem::STAGE + (size_t)ev * bpv;
-                if (bits == 4) *reinterpret_cast<uint4*>(st + 16 * cc) = make_uint4(words[0], words[1], words[2], words[3]);
-                else *reinterpret_cast<uint2*>(st + 8 * cc) = make_uint2(words[0], words[1]);
+                // 32 coordinates' codes go straight to the cache (16 or 8 bytes; the other chunks of the same 32-byte sector
+                // follow from this thread's next block and from the warp that shares the vector)
+                if (ev_dst >= 0) {
+                    if (bits == 4) *reinterpret_cast<uint4*>(cq + ev_dst + 16 * cc) = make_uint4(words[0], words[1], words[2], words[3]);
+                    else *reinterpret_cast<uint2*>(cq + ev_dst + 8 * cc) = make_uint2(words[0], words[1]);
+                }
             }
         }
         tc_fence_before();  // the tensor-memory reads are done before the next tile's mma overwrites the accumulators
-        __syncthreads();
+        __syncthreads();    // ... and the stores above are ordered before the patches below
 
-        // ---- 4. exact chain for the queued coordinates, patch the packed tile ----
-        auto exact_code = [&](int v, int d) -> int {  // one thread, the reference's k-ascending chain
-            const int vid = vec0 + v;
-            const int tok = vid / p.Hkv, head = vid - tok * p.Hkv;
-            const bool produced = PRODUCER && kind == 0;
-            const uint4* src = reinterpret_cast<const uint4*>((produced ? p.k_post : src_buf) + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM);
-            const float inv = inv_s[v];
-            float acc = 0.0f;
-#pragma unroll 1
-            for (int j0 = 0; j0 < 16; j0 += 8) {  // eight 16-byte loads in flight at a time
-                uint4 xall[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) xall[j] = produced ? src[j0 + j] : __ldg(src + j0 + j);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint4 xv = xall[j];
-                    const uint4 rv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::B_R, d, 8 * (j0 + j)));
-                    const __half2* xh = reinterpret_cast<const __half2*>(&xv);
-                    const __half2* rh = reinterpret_cast<const __half2*>(&rv);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
-                        acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
-                        acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
-                    }
-                }
-            }
-            return quantize_code(acc, bits);
-        };
-        auto patch = [&](int v, int d, int code) {
-            uint32_t* w = reinterpret_cast<uint32_t*>(gbase + TcSmem::STAGE + (size_t)v * bpv) + (bits == 4 ? d >> 3 : d >> 4);
-            const int sh = bits == 4 ? 4 * (d & 7) : 2 * (d & 15);
-            const uint32_t m = (bits == 4 ? 0xfu : 0x3u) << sh;
-            atomicAnd(w, ~m);
-            atomicOr(w, (uint32_t)code << sh);
-        };
-        if (!dead) {
-            // Queued coordinates: one lane per item, 32 items per warp and round (a tile queues about 23).
-            const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
-            for (uint32_t i0 = (uint32_t)warp * 32u; i0 < queued; i0 += TC_THREADS) {  // warp-uniform
-                const uint32_t i = i0 + (uint32_t)lane;
-                if (i < queued) {
-                    const uint32_t item = list_s[i];
-                    const int v = (int)(item >> 8), d = (int)(item & 255u);
-                    if (vec0 + v < vec_per_kind) patch(v, d, exact_code(v, d));
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                uint32_t m = own_cc[k];
-                while (m) {
-                    const int i = __ffs(m) - 1;
-                    m &= m - 1;
-                    if (vec0 + ev < vec_per_kind) patch(ev, 32 * (cc0 + k) + i, exact_code(ev, 32 * (cc0 + k) + i));
-                }
-            }
-        }
-        __syncthreads();
-
-        // ---- 5. the packed tile leaves as 16-byte stores; the heads of a token are contiguous in the cache ----
-        if (!dead) {
-            for (int c16 = tid; c16 < (TC_TILE << cpv_shift); c16 += TC_THREADS) {
-                const int v = c16 >> cpv_shift, part = c16 & ((1 << cpv_shift) - 1);
-                const long long dst = dst_s[v];
-                if (dst >= 0) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(gbase + TcSmem::STAGE + (size_t)v * bpv + 16 * part);
-                    *reinterpret_cast<uint4*>(cq + dst + 16 * part) = u;
-                }
-            }
-        }
-        __syncthreads();
+        prev_cq = cq;  // step 4, the exact chains of this tile, runs after the next tile's loads have been issued
+        prev_own0 = own_cc[0];
+        prev_own1 = own_cc[1];
     }
+    if (prev_cq && !dead) run_chains(prev_cq, prev_own0, prev_own1);
 
     tc_fence_before();
     __syncthreads();
