@@ -230,9 +230,34 @@ inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bo
     long long grid = (long long)TC_CTAS_PER_SM * device_props().sm_count;
     if (grid > tiles) grid = tiles;
     if (grid < 1) return TQ_OK;
+#ifdef TQ_TIMING_SWITCHES
+    static unsigned long long* d_stamps = nullptr;
+    static int stamp_calls = 0;
+    PrefillTcParams ts = t;
+    if (getenv("TQ_TC_STAMPS")) {
+        if (!d_stamps) { cudaMalloc(&d_stamps, 256); cudaMemset(d_stamps, 0, 256); }
+        ts.stamps = d_stamps;
+    }
+    if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(ts);
+    else prefill_append_tc_kernel<false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(ts);
+    if (ts.stamps && ++stamp_calls == 40) {
+        unsigned long long h[32];
+        cudaStreamSynchronize(s);
+        cudaMemcpy(h, d_stamps, 256, cudaMemcpyDeviceToHost);
+        for (int w = 0; w < 2; ++w) {
+            const double n = (double)h[16 * w + 15] * (double)((tiles + grid - 1) / grid);
+            fprintf(stderr, "append stamps, warp %d (cycles per tile): top %.0f | loads %.0f | tree %.0f | wait for the chain warp %.0f | operand + barrier B %.0f | "
+                            "mma issue + per-vector %.0f | mma wait + barrier C %.0f | epilogue %.0f | barrier D %.0f\n",
+                    w ? 7 : 0, h[16 * w] / n, h[16 * w + 1] / n, h[16 * w + 2] / n, h[16 * w + 3] / n, h[16 * w + 4] / n, h[16 * w + 5] / n,
+                    h[16 * w + 6] / n, h[16 * w + 7] / n, h[16 * w + 8] / n);
+        }
+    }
+    return cuda_status(cudaGetLastError());
+#else
     if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
     else prefill_append_tc_kernel<false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
     return cuda_status(cudaGetLastError());
+#endif
 }
 
 inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 1, long long seq_stride_rows = 0,

@@ -50,9 +50,6 @@ struct PtcSmem {
 };
 constexpr size_t PTC_DYN_SMEM = PtcSmem::BYTES + 1024;  // + alignment slack
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 // 32 lanes x 32 consecutive 32-bit columns, registers -> tensor memory (the counterpart of tmem_ld32)
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -78,9 +75,6 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void stmatrix_x4(uint32_t addr, const uint32_t (&r)[4]) {
     asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
                  : "memory");
-}
-__device__ __forceinline__ void named_barrier(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 // fp16 x fp16 -> fp32, both operands K-major, M = 128
 constexpr uint32_t PTC_IDESC_N64 = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);

@@ -36,27 +36,32 @@
 namespace tq {
 
 constexpr int TC_TILE = 128;       // head vectors per tile = MMA M
-constexpr int TC_THREADS = 256;
+constexpr int TC_WORKERS = 256;     // eight warps that load, rotate and quantise
+constexpr int TC_THREADS = TC_WORKERS + 32;  // ... and one warp for the exact chains of near-bound coordinates
 constexpr float TC_MARGIN = 1.6e-5f;
 constexpr int TC_LIST_CAP = 96;    // queued near-bound coordinates per tile; the rest is handled by their owners
 
 // Shared memory by ABSOLUTE shared address (the kernel checks that its dynamic shared memory covers the range): the
 // bucket table sits on a 4096-byte boundary so that its look-up address is (bits & 0xffc) plus a constant.
 struct TcSmem {
-    static constexpr uint32_t DST = 0x0800;              // long long[128] byte offset of each vector's codes in the cache (-1: none)
-    static constexpr uint32_t INV = DST + 1024;          // float[128]: sum of squares, then 1/norm per vector; -1: the vector
+    // Per-tile arrays exist twice (tile parity): the chain warp works on a tile's queue while the workers are already
+    // two phases further.
+    static constexpr uint32_t DST0 = 0x0800;             // long long[128] byte offset of each vector's codes in the cache (-1: none)
+    static constexpr uint32_t INV0 = DST0 + 1024;        // float[128]: sum of squares, then 1/norm per vector; -1: the vector
                                                          // holds an infinity or a NaN
-    static constexpr uint32_t LIST = INV + 512;          // uint32[TC_LIST_CAP]
-    static constexpr uint32_t CTRL = LIST + 4 * TC_LIST_CAP;  // mbarrier (8 B), tmem base (4 B), list count (4 B)
+    static constexpr uint32_t CTRL = INV0 + 512;         // mma mbarrier (8 B), tmem base (4 B), pad, full[2], empty[2] mbarriers,
+                                                         // queue counts [2]
     static constexpr uint32_t GRID = 0x1000;             // uint32[1024] bucket table, see the kernel
     static constexpr uint32_t A_X = 0x2000;              // the vectors: 2 K-regions x [128 rows][128 B]
     static constexpr uint32_t B_R = 0xA000;              // R: rows = output coordinate d, K-major
-    static constexpr uint32_t STAGE = A_X;               // packed codes of the tile, 64 B (4-bit) per vector: written after
-                                                         // the MMAs have consumed the operand tile it overlays
-    static constexpr uint32_t END = 0x12000;
+    static constexpr uint32_t DST1 = 0x12000;
+    static constexpr uint32_t INV1 = DST1 + 1024;
+    static constexpr uint32_t LIST0 = INV1 + 512;        // uint32[TC_LIST_CAP] x 2: queued (vector << 8 | coordinate)
+    static constexpr uint32_t LIST1 = LIST0 + 4 * TC_LIST_CAP;
+    static constexpr uint32_t END = LIST1 + 4 * TC_LIST_CAP;
 };
-static_assert(TcSmem::CTRL + 16 <= TcSmem::GRID, "control words run into the bucket table");
-constexpr size_t TC_DYN_SMEM = TcSmem::END;  // enough wherever the dynamic shared memory starts at or below TcSmem::DST
+static_assert(TcSmem::CTRL + 64 <= TcSmem::GRID, "control words run into the bucket table");
+constexpr size_t TC_DYN_SMEM = TcSmem::END;  // enough wherever the dynamic shared memory starts at or below TcSmem::DST0
 constexpr int TC_CTAS_PER_SM = 3;
 static_assert(TC_CTAS_PER_SM * (TC_DYN_SMEM + 1024) <= 228 * 1024, "three CTAs of the tensor-core append must fit one SM");
 
@@ -96,9 +101,18 @@ struct PrefillTcParams {
     int rope_dim;              // 64 or 128
     float eps;
     int biased;
+#ifdef TQ_TIMING_SWITCHES
+    unsigned long long* stamps;  // timing-experiment builds only: [2][16] summed clock deltas of a tile's sections (warps 0, 7)
+#endif
     __half* k_post;            // [vectors][128] like k_buf: receives the produced K vectors (what the reference's k buffer
                                // holds after its two kernels); the exact chains of near-bound coordinates re-read them
 };
+
+#ifdef TQ_TIMING_SWITCHES
+#define TC_STAMP(i) do { const long long _t = clock64(); tc_stamp_acc[i] += _t - tc_stamp_last; tc_stamp_last = _t; } while (0)
+#else
+#define TC_STAMP(i) do { } while (0)
+#endif
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -137,6 +151,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool pred) {  // true if pred holds for any thread
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"((uint32_t)(pred ? 1 : 0))
+        : "memory");
+    return r != 0u;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -193,6 +225,17 @@ __device__ __forceinline__ uint32_t bucket_entry(uint32_t grid_bits) {
     asm("ld.shared.u32 %0, [%1 + %2];" : "=r"(e) : "r"(grid_bits & 0xffcu), "n"(TcSmem::GRID));
     return e;
 }
+// Division of n < 2^31 by a divisor fixed for the launch: q = (n * mul) >> shift with mul = ceil(2^shift / d),
+// shift = 31 + ceil(log2 d); exact because n * (mul * d - 2^shift) < 2^shift.
+struct FastDiv {
+    uint32_t mul, shift;
+    __device__ __forceinline__ explicit FastDiv(uint32_t d) {
+        const uint32_t l = d > 1u ? 32u - (uint32_t)__clz((int)(d - 1u)) : 0u;
+        shift = 31u + l;
+        mul = (uint32_t)((((unsigned long long)1 << shift) + d - 1u) / d);
+    }
+    __device__ __forceinline__ int div(int n) const { return (int)(((unsigned long long)(uint32_t)n * mul) >> shift); }
+};
 __device__ __forceinline__ uint32_t mad_hi_u32(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -221,18 +264,20 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t dyn_base = smem_u32(tc_smem);
-    if (dyn_base > TcSmem::DST || dyn_base + (uint32_t)TC_DYN_SMEM < TcSmem::END) {  // (uniform over the CTA)
+    if (dyn_base > TcSmem::DST0 || dyn_base + (uint32_t)TC_DYN_SMEM < TcSmem::END) {  // (uniform over the CTA)
         if (tid == 0) atomicMax(p.status, ST_SMEM_LAYOUT);
         return;
     }
     constexpr uint32_t base = 0u;                 // TcSmem holds absolute shared addresses
     uint8_t* gbase = tc_smem - dyn_base;          // generic address of shared address 0
-    const uint32_t bar = base + TcSmem::CTRL;
-    volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [3] list count
-    long long* dst_s = reinterpret_cast<long long*>(gbase + TcSmem::DST);
-    float* inv_s = reinterpret_cast<float*>(gbase + TcSmem::INV);
-    uint32_t* list_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::LIST);
+    const uint32_t bar = base + TcSmem::CTRL;       // the tensor core's commits arrive here
+    const uint32_t bar_full = bar + 16u;            // [2]: a tile's queue, per-vector arrays and stored codes are complete
+    const uint32_t bar_empty = bar + 32u;           // [2]: the chain warp is done with them
+    volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [12 + b] queue count
     uint32_t* grid_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::GRID);
+    auto dst_buf = [&](int b) { return reinterpret_cast<long long*>(gbase + (b ? TcSmem::DST1 : TcSmem::DST0)); };
+    auto inv_buf = [&](int b) { return reinterpret_cast<float*>(gbase + (b ? TcSmem::INV1 : TcSmem::INV0)); };
+    auto list_buf = [&](int b) { return reinterpret_cast<uint32_t*>(gbase + (b ? TcSmem::LIST1 : TcSmem::LIST0)); };
 
     const int bits = p.bits;
     const int nb = bits == 4 ? 15 : 3;
@@ -246,6 +291,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     }
     if (tid == 0) {
         mbar_init(bar, 1);
+        mbar_init(bar_full, 1);
+        mbar_init(bar_full + 8u, 1);
+        mbar_init(bar_empty, 1);
+        mbar_init(bar_empty + 8u, 1);
         fence_mbar_init();
     }
     for (int c = tid; c < 2048; c += TC_THREADS) {  // R as the B operand: row d, 16-byte chunk j
@@ -292,82 +341,104 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     const bool fast_head = p.Hkv <= 256;
     const uint32_t hkv_magic = ((1u << 20) + (uint32_t)p.Hkv - 1u) / (uint32_t)p.Hkv;
     const bool fast_tok = p.T > TC_TILE + 1;
-    const int cpv_shift = bits == 4 ? 2 : 1;  // 16-byte chunks per packed vector, as a shift
+    const FastDiv div_hkv((uint32_t)p.Hkv), div_T((uint32_t)p.T), div_G((uint32_t)(p.step_G > 0 ? p.step_G : 1));
 
     const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
-    const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates
+    const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates (warps 0-7)
 
-    // ---- step 4 of a tile: the exact chain for its queued coordinates (about 23 of 16384), patching the stored codes.
-    // It runs at the start of the NEXT round, after that round's loads have been issued and before the barrier that
-    // lets the operand tile be overwritten: the warps without queued items work on their loads meanwhile.
-    auto exact_code = [&](int v, int d) -> int {  // one thread, the reference's k-ascending chain
-        const float inv = inv_s[v];
+    // The reference's k-ascending fp32 chain for coordinate d of one vector (x: its 128 fp16 inputs in global memory),
+    // by one thread; R comes from the operand tile in shared memory.
+    auto exact_code = [&](const __half* x, float inv, int d) -> int {
+        const uint4* src = reinterpret_cast<const uint4*>(x);
         float acc = 0.0f;
-#pragma unroll 4
-        for (int j = 0; j < 16; ++j) {  // x from the operand tile (the vector as it was rotated), R from its tile
-            const uint4 xv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::A_X, v, 8 * j));
-            const uint4 rv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::B_R, d, 8 * j));
-            const __half2* xh = reinterpret_cast<const __half2*>(&xv);
-            const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll 1
+        for (int j0 = 0; j0 < 16; j0 += 8) {  // eight 16-byte loads in flight at a time
+            uint4 xall[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
-                acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
-                acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+            for (int j = 0; j < 8; ++j) xall[j] = src[j0 + j];  // (plain loads: a produced K vector was written by this CTA)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint4 xv = xall[j];
+                const uint4 rv = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::B_R, d, 8 * (j0 + j)));
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 xf = __half22float2(xh[e]), rf = __half22float2(rh[e]);
+                    acc = fma_ftz(rf.x, mul_ftz(xf.x, inv), acc);
+                    acc = fma_ftz(rf.y, mul_ftz(xf.y, inv), acc);
+                }
             }
         }
         return quantize_code(acc, bits);
     };
-    auto patch = [&](uint8_t* cqp, int v, int d, int code) {  // one code of vector v in the cache (the tile's stores came before)
-        const long long dst = dst_s[v];
-        if (dst < 0) return;
-        uint32_t* w = reinterpret_cast<uint32_t*>(cqp + dst) + (bits == 4 ? d >> 3 : d >> 4);
+    auto patch = [&](uint8_t* codes, int d, int code) {  // one code of a vector in the cache (the tile's stores came before)
+        uint32_t* w = reinterpret_cast<uint32_t*>(codes) + (bits == 4 ? d >> 3 : d >> 4);
         const int sh = bits == 4 ? 4 * (d & 7) : 2 * (d & 15);
         const uint32_t m = (bits == 4 ? 0xfu : 0x3u) << sh;
         atomicAnd(w, ~m);
         atomicOr(w, (uint32_t)code << sh);
     };
-    auto run_chains = [&](uint8_t* cqp, uint32_t own0, uint32_t own1) {
-        // Queued coordinates: one lane per item, 32 items per warp and round.
-        const uint32_t queued = min(ctrl[3], (uint32_t)TC_LIST_CAP);
-        for (uint32_t i0 = (uint32_t)warp * 32u; i0 < queued; i0 += TC_THREADS) {  // warp-uniform
-            const uint32_t i = i0 + (uint32_t)lane;
-            if (i < queued) {
+    auto vector_input = [&](int kind, int vid) -> const __half* {  // the 128 inputs of vector vid of a kind, as rotated
+        const int tok = div_hkv.div(vid), head = vid - tok * p.Hkv;
+        const __half* buf = kind == 0 ? (PRODUCER ? p.k_post : p.k_buf) : p.v_buf;
+        return buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM;
+    };
+
+    // ---- the chain warp: step 4 of every tile, one tile behind the workers.  A coordinate within TC_MARGIN of a bound
+    //      (about 23 of a tile's 16384) is queued by the epilogue; here one lane per item runs the exact chain and patches
+    //      the stored code.  None of the workers' barriers waits for it. ----
+    if (warp == TC_WORKERS / 32) {
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int b = (int)(it & 1u);
+            const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
+            const int vec0 = (tile - (kind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
+            uint8_t* cq = kind == 0 ? p.ck : p.cv;
+            if (!mbar_wait_bounded(bar_full + 8u * (uint32_t)b, (it >> 1) & 1u, 1u << 24)) {
+                if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+                return;
+            }
+            const uint32_t queued = min(ctrl[12 + b], (uint32_t)TC_LIST_CAP);
+            const uint32_t* list_s = list_buf(b);
+            const float* inv_s = inv_buf(b);
+            const long long* dst_s = dst_buf(b);
+            for (uint32_t i = (uint32_t)lane; i < queued; i += 32u) {
                 const uint32_t item = list_s[i];
                 const int v = (int)(item >> 8), d = (int)(item & 255u);
-                patch(cqp, v, d, exact_code(v, d));
+                const long long dst = dst_s[v];
+                if (dst >= 0) patch(cq + dst, d, exact_code(vector_input(kind, vec0 + v), inv_s[v], d));
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8u * (uint32_t)b);
         }
-        // ... and those that did not fit the queue, by their owners
-        while (own0) {
-            const int i = __ffs(own0) - 1;
-            own0 &= own0 - 1;
-            patch(cqp, ev, 32 * cc0 + i, exact_code(ev, 32 * cc0 + i));
-        }
-        while (own1) {
-            const int i = __ffs(own1) - 1;
-            own1 &= own1 - 1;
-            patch(cqp, ev, 32 * (cc0 + 1) + i, exact_code(ev, 32 * (cc0 + 1) + i));
-        }
-    };
-    uint8_t* prev_cq = nullptr;  // the previous tile's code array: its exact chains are still to run
-    uint32_t prev_own0 = 0u, prev_own1 = 0u;
+        return;
+    }
 
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+#ifdef TQ_TIMING_SWITCHES
+    long long tc_stamp_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, tc_stamp_last = clock64();
+#endif
+    uint32_t it = 0;  // tiles this CTA has started: parity of the per-tile arrays, phase of their barriers
+
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int b = (int)(it & 1u);
+        long long* const dst_s = dst_buf(b);
+        float* const inv_s = inv_buf(b);
+        uint32_t* const list_s = list_buf(b);
         const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
         const int vec0 = (tile - (kind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
         const __half* src_buf = kind == 0 ? p.k_buf : p.v_buf;
         uint8_t* cq = kind == 0 ? p.ck : p.cv;
         __half* cn = kind == 0 ? p.kn : p.vn;
-        const int tok0 = vec0 / p.Hkv, head0 = vec0 - tok0 * p.Hkv;
-        const int seq0 = tok0 / p.T, t0 = tok0 - seq0 * p.T;
+        const int tok0 = div_hkv.div(vec0), head0 = vec0 - tok0 * p.Hkv;
+        const int seq0 = div_T.div(tok0), t0 = tok0 - seq0 * p.T;
         auto split_vec = [&](int v, int& tok, int& head) {  // vector vec0 + v of the tile
             if (fast_head) {
                 const uint32_t x = (uint32_t)(head0 + v), dq = (x * hkv_magic) >> 20;
                 tok = tok0 + (int)dq;
                 head = (int)(x - dq * (uint32_t)p.Hkv);
             } else {
-                tok = (vec0 + v) / p.Hkv;
+                tok = div_hkv.div(vec0 + v);
                 head = (vec0 + v) - tok * p.Hkv;
             }
         };
@@ -378,14 +449,14 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 seq = seq0 + (wrap ? 1 : 0);
                 t = tt - (wrap ? p.T : 0);
             } else {
-                seq = tok / p.T;
+                seq = div_T.div(tok);
                 t = tok - seq * p.T;
             }
         };
 
-        // ---- 1. load, sum of squares in the reference's order (registers only: the previous tile's exact chains may
-        //         still be reading its operand rows) ----
-        constexpr int PASSES = 4 * TC_TILE / TC_THREADS, VPP = TC_THREADS / 4;  // passes per tile, vectors per pass
+        TC_STAMP(0);
+        // ---- 1. load, sum of squares in the reference's order ----
+        constexpr int PASSES = 4 * TC_TILE / TC_WORKERS, VPP = TC_WORKERS / 4;  // passes per tile, vectors per pass
         uint4 raw_all[PASSES][4];
         float tt_all[PASSES];
 #pragma unroll
@@ -398,19 +469,41 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
 #pragma unroll
             for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
         }
+        // Thread v < 128: where vector v of the tile goes (its position and row base are loads of their own: issued here,
+        // needed only once the operands are with the tensor core)
+        long long my_dst = -1, my_norm_at = 0;  // byte offset of the vector's codes in the cache (-1: none), index of its norm
+        if (tid < TC_TILE && vec0 + tid < vec_per_kind) {
+            int tok, head, seq, t, layer = 0;
+            split_vec(tid, tok, head);
+            split_tok(tok, seq, t);
+            int sq = seq, cap = p.capacity_rows;
+            if (p.step_G > 0) {
+                layer = div_G.div(seq);
+                sq = seq - layer * p.step_G;
+                if (p.seq_capacity) cap = p.seq_capacity[sq];
+            }
+            const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
+            if (pos >= 0 && (cap <= 0 || pos < cap)) {
+                const long long row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
+                my_dst = (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
+                my_norm_at = (long long)layer * p.norm_layer_stride + row * p.Hkv + head;
+            } else {
+                atomicMax(p.status, ST_BAD_POSITION);
+            }
+        }
         {   // the CTA's next tile (same kind or the other one) on its way into L2 while this one is worked on
             const int ntile = tile + (int)gridDim.x;
             if (ntile < total_tiles) {
                 const int nkind = (p.k_buf && ntile < tiles_per_kind) ? 0 : 1;
                 const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + (tid >> 1);
                 if (nvid < vec_per_kind) {  // one 128-byte line per thread
-                    const int ntok = nvid / p.Hkv, nhead = nvid - ntok * p.Hkv;  // (one division per thread and tile)
+                    const int ntok = div_hkv.div(nvid), nhead = nvid - ntok * p.Hkv;
                     const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM + 64 * (tid & 1);
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
                 }
             }
         }
-        if (prev_cq && !dead) run_chains(prev_cq, prev_own0, prev_own1);
+        TC_STAMP(1);
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {
             const int v = pass * VPP + (tid >> 2), c = tid & 3;  // vector within the tile, 32-coordinate chunk
@@ -439,7 +532,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                     const float rms = rsqrt_approx_ftz(fma_ftz(add_ftz(add_ftz(q0, q2), add_ftz(q1, q3)), 1.0f / HEAD_DIM, p.eps));
                     int layer = 0, sq_i = seq, ppos;
                     if (p.step_G > 0) {
-                        layer = seq / p.step_G;
+                        layer = div_G.div(seq);
                         sq_i = seq - layer * p.step_G;
                         ppos = live ? p.positions[sq_i] : 0;
                     } else {
@@ -512,8 +605,15 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
             tt_all[pass] = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
         }
-        __syncthreads();  // the previous tile is finished with the operand tile, the queue and the per-vector arrays
-        if (tid == 0) ctrl[3] = 0;
+        TC_STAMP(2);
+        // The operand tile is free (its MMAs were waited for, and the epilogue reads tensor memory only); the per-vector
+        // arrays and the queue of this parity are free once the chain warp is through with the tile before the last.
+        if (!dead && !mbar_wait_bounded(bar_empty + 8u * (uint32_t)b, ((it >> 1) & 1u) ^ 1u, 1u << 24)) {
+            dead = true;
+            atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+        }
+        TC_STAMP(3);
+        if (tid == 0) ctrl[12 + b] = 0;
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {  // the vectors as they are become the A operand
             const int v = pass * VPP + (tid >> 2), c = tid & 3;
@@ -526,7 +626,8 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             }
         }
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
-        __syncthreads();
+        named_barrier(1, TC_WORKERS);
+        TC_STAMP(4);
 
         // ---- 2. the rotation: 8 K-steps into one accumulator ----
         if (tid == 0 && !dead) {
@@ -540,47 +641,30 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         }
         // ---- 2b. while the tensor core works: thread v < 128 settles vector v -- norm out, 1/norm, where its codes go ----
         if (tid < TC_TILE) {
-            const int v = tid;
-            const bool live = vec0 + v < vec_per_kind;
-            const float tt = inv_s[v];
+            const float tt = inv_s[tid];
             const bool abnormal = !(tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
-            long long row = -1;
-            int layer = 0, head = 0;
-            if (live) {
-                int tok, seq, t;
-                split_vec(v, tok, head);
-                split_tok(tok, seq, t);
-                int sq = seq, cap = p.capacity_rows;
-                if (p.step_G > 0) {
-                    layer = seq / p.step_G;
-                    sq = seq - layer * p.step_G;
-                    if (p.seq_capacity) cap = p.seq_capacity[sq];
-                }
-                const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
-                if (pos >= 0 && (cap <= 0 || pos < cap)) {
-                    row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
-                    cn[(size_t)layer * (size_t)p.norm_layer_stride + (size_t)row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(tt));
-                } else {
-                    atomicMax(p.status, ST_BAD_POSITION);
-                }
-            }
-            dst_s[v] = row < 0 ? -1ll : (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
-            inv_s[v] = abnormal ? -1.0f : rsqrt_approx_ftz(tt);
+            if (my_dst >= 0) cn[my_norm_at] = __float2half_rn(sqrt_approx_ftz(tt));
+            dst_s[tid] = my_dst;
+            inv_s[tid] = abnormal ? -1.0f : rsqrt_approx_ftz(tt);
         }
+        TC_STAMP(5);
         if (!dead && !mbar_wait_bounded(bar, phase, 1u << 22)) {
             dead = true;
             atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
         }
-        dead = __syncthreads_or(dead ? 1 : 0) != 0;
+        dead = named_barrier_or(1, TC_WORKERS, dead);
         phase ^= 1u;
         tc_fence_after();
+        TC_STAMP(6);
 
         // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
         //         w + 4 share those vectors and take 64 of the 128 coordinates (two blocks of 32 columns) each ----
         uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
+        long long ev_dst_keep = -1;
         if (!dead) {
             const float inv = inv_s[ev];
             const long long ev_dst = dst_s[ev];
+            ev_dst_keep = ev_dst;
             const bool abn = inv < 0.0f;
             const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * 256.0f, inv * 256.0f);
             const float2 magic2 = make_float2(3145728.0f, 3145728.0f);
@@ -626,7 +710,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 while (near_mask) {
                     const int i = __ffs(near_mask) - 1;
                     near_mask &= near_mask - 1;
-                    const uint32_t slot = atomicAdd(const_cast<uint32_t*>(&ctrl[3]), 1u);
+                    const uint32_t slot = atomicAdd(const_cast<uint32_t*>(&ctrl[12 + b]), 1u);
                     if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)ev << 8) | (uint32_t)(32 * cc + i);
                     else own_cc[cc - cc0] |= 1u << i;
                 }
@@ -638,17 +722,35 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 }
             }
         }
+        TC_STAMP(7);
         tc_fence_before();  // the tensor-memory reads are done before the next tile's mma overwrites the accumulators
-        __syncthreads();    // ... and the stores above are ordered before the patches below
-
-        prev_cq = cq;  // step 4, the exact chains of this tile, runs after the next tile's loads have been issued
-        prev_own0 = own_cc[0];
-        prev_own1 = own_cc[1];
+        named_barrier(1, TC_WORKERS);  // ... and the queue, the per-vector arrays and the stores above are complete:
+        if (tid == 0) mbar_arrive(bar_full + 8u * (uint32_t)b);  // over to the chain warp
+        TC_STAMP(8);
+        // near-bound coordinates that did not fit the queue (none, ordinarily): their owners run the chains themselves
+        if (!dead && (own_cc[0] | own_cc[1]) != 0u && ev_dst_keep >= 0) {
+            const __half* x = vector_input(kind, vec0 + ev);
+            const float inv = inv_s[ev];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                uint32_t m = own_cc[k];
+                while (m) {
+                    const int i = __ffs(m) - 1;
+                    m &= m - 1;
+                    patch(cq + ev_dst_keep, 32 * (cc0 + k) + i, exact_code(x, inv, 32 * (cc0 + k) + i));
+                }
+            }
+        }
     }
-    if (prev_cq && !dead) run_chains(prev_cq, prev_own0, prev_own1);
+#ifdef TQ_TIMING_SWITCHES
+    if (p.stamps && lane == 0 && (warp == 0 || warp == 7)) {
+        for (int i = 0; i < 10; ++i) atomicAdd(p.stamps + (warp ? 16 : 0) + i, (unsigned long long)tc_stamp_acc[i]);
+        atomicAdd(p.stamps + (warp ? 16 : 0) + 15, 1ull);
+    }
+#endif
 
     tc_fence_before();
-    __syncthreads();
+    named_barrier(1, TC_WORKERS);
     if (warp == 0) tmem_dealloc(tmem, 128u);
 }
 
