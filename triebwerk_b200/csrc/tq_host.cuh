@@ -120,6 +120,26 @@ inline int make_code_map_layers(CUtensorMap* m, const void* base, long long rows
     return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
 }
 
+// fp16 K or V input of an append, [tokens][kv_dim] halves, for prefill_append_tc_kernel's TMA form: one box = the 128 head
+// vectors of a tile (128 / Hkv tokens x Hkv heads), landing in shared memory as [half of the vector][token][head][128 B]
+// with the 128-byte swizzle -- the K-major operand layout of the tensor core, no instruction of the SM involved.
+inline int make_append_input_map(CUtensorMap* m, const void* base, long long tokens, int Hkv, int kv_dim) {
+    auto fn = encode_fn();
+    if (!fn) return TQ_ERR_UNSUPPORTED;
+    const long long row_bytes = (long long)kv_dim * 2;
+    if (((uintptr_t)base & 15u) != 0 || tokens <= 0 || tokens >= (1ll << 31) || Hkv <= 0 || Hkv > TC_TILE || TC_TILE % Hkv != 0 ||
+        row_bytes % 16 != 0 || kv_dim < Hkv * HEAD_DIM)
+        return TQ_ERR_ARG;
+    cuuint64_t dims[4] = {128u, (cuuint64_t)Hkv, (cuuint64_t)tokens, 2u};
+    cuuint64_t strides[3] = {256u, (cuuint64_t)row_bytes, 128u};
+    cuuint32_t box[4] = {128u, (cuuint32_t)Hkv, (cuuint32_t)(TC_TILE / Hkv), 2u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TQ_OK : TQ_ERR_ARG;
+}
+
 // ---- workspace ------------------------------------------------------------------------------------------------------
 // The carve of tq_common.cuh plus two helper arrays used by the prefill form (positions 0..T-1 and a
 // constant row base) and the fp16 twin's ticket/partial area, which aliases the packed path's partials.
@@ -223,23 +243,35 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
 // the fp32-chain kernel.  Both store the same bytes.
 // producer: the form that applies QK-norm and rotary embedding to the K vectors on the way in (PrefillTcParams)
 inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bool producer = false) {
-    int ar = producer ? ensure_dynamic_smem((const void*)prefill_append_tc_kernel<true>, TC_DYN_SMEM)
-                      : ensure_dynamic_smem((const void*)prefill_append_tc_kernel<false>, TC_DYN_SMEM);
-    if (ar != TQ_OK) return ar;
-    const long long tiles = (((long long)t.n_seq * t.T * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
+    const long long tokens = (long long)t.n_seq * t.T;
+    const long long tiles = ((tokens * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
     long long grid = (long long)TC_CTAS_PER_SM * device_props().sm_count;
     if (grid > tiles) grid = tiles;
     if (grid < 1) return TQ_OK;
+    // The vectors reach the operand tile by tensor-map copies where the layout allows it (TQ_PREFILL_TMA=0: through
+    // registers, as in the producer form, whose K vectors are computed on the way in).
+    static const bool tma_allowed = !(getenv("TQ_PREFILL_TMA") && atoi(getenv("TQ_PREFILL_TMA")) == 0);
+    CUtensorMap tmk{}, tmv{};
+    bool tma = !producer && tma_allowed;
+    if (tma && t.k_buf) tma = make_append_input_map(&tmk, t.k_buf, tokens, t.Hkv, t.kv_dim) == TQ_OK;
+    if (tma && t.v_buf) tma = make_append_input_map(&tmv, t.v_buf, tokens, t.Hkv, t.kv_dim) == TQ_OK;
+    const void* kernel = producer ? (const void*)prefill_append_tc_kernel<true, false>
+                                  : (tma ? (const void*)prefill_append_tc_kernel<false, true> : (const void*)prefill_append_tc_kernel<false, false>);
+    int ar = ensure_dynamic_smem(kernel, TC_DYN_SMEM);
+    if (ar != TQ_OK) return ar;
+    PrefillTcParams ts = t;
 #ifdef TQ_TIMING_SWITCHES
     static unsigned long long* d_stamps = nullptr;
     static int stamp_calls = 0;
-    PrefillTcParams ts = t;
     if (getenv("TQ_TC_STAMPS")) {
         if (!d_stamps) { cudaMalloc(&d_stamps, 256); cudaMemset(d_stamps, 0, 256); }
         ts.stamps = d_stamps;
     }
-    if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(ts);
-    else prefill_append_tc_kernel<false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(ts);
+#endif
+    if (producer) prefill_append_tc_kernel<true, false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(tmk, tmv, ts);
+    else if (tma) prefill_append_tc_kernel<false, true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(tmk, tmv, ts);
+    else prefill_append_tc_kernel<false, false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(tmk, tmv, ts);
+#ifdef TQ_TIMING_SWITCHES
     if (ts.stamps && ++stamp_calls == 40) {
         unsigned long long h[32];
         cudaStreamSynchronize(s);
@@ -252,12 +284,8 @@ inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bo
                     h[16 * w + 6] / n, h[16 * w + 7] / n, h[16 * w + 8] / n);
         }
     }
-    return cuda_status(cudaGetLastError());
-#else
-    if (producer) prefill_append_tc_kernel<true><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
-    else prefill_append_tc_kernel<false><<<(unsigned)grid, TC_THREADS, TC_DYN_SMEM, s>>>(t);
-    return cuda_status(cudaGetLastError());
 #endif
+    return cuda_status(cudaGetLastError());
 }
 
 inline int launch_prefill_tc(const AppendParams& p, cudaStream_t s, int n_seq = 1, long long seq_stride_rows = 0,

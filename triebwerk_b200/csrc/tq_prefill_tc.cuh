@@ -259,8 +259,13 @@ __device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int 
     return tile + region * 16384u + (uint32_t)row * 128u + ((((kk >> 3) ^ ((uint32_t)row & 7u))) << 4) + (kk & 7u) * 2u;
 }
 
-template <bool PRODUCER>
-__global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_kernel(const PrefillTcParams p) {
+// TMA_IN: the tile's 128 vectors reach the operand tile by ONE tensor-map copy (issued while the previous tile is being
+// quantised) instead of through registers; the sums of squares are then taken from shared memory while the tensor core
+// already rotates.  Needs a tensor map over the input (make_append_input_map) and Hkv dividing 128; never with PRODUCER.
+template <bool PRODUCER, bool TMA_IN>
+__global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM)
+prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __grid_constant__ CUtensorMap tm_v_in, const PrefillTcParams p) {
+    static_assert(!(PRODUCER && TMA_IN), "the producer form computes its K vectors: they cannot come by a bulk copy");
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t dyn_base = smem_u32(tc_smem);
@@ -273,6 +278,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     const uint32_t bar = base + TcSmem::CTRL;       // the tensor core's commits arrive here
     const uint32_t bar_full = bar + 16u;            // [2]: a tile's queue, per-vector arrays and stored codes are complete
     const uint32_t bar_empty = bar + 32u;           // [2]: the chain warp is done with them
+    const uint32_t bar_ld = bar + 56u;              // TMA_IN: the tile's vectors have arrived in the operand tile
     volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(gbase + TcSmem::CTRL);  // [2] tmem base, [12 + b] queue count
     uint32_t* grid_s = reinterpret_cast<uint32_t*>(gbase + TcSmem::GRID);
     auto dst_buf = [&](int b) { return reinterpret_cast<long long*>(gbase + (b ? TcSmem::DST1 : TcSmem::DST0)); };
@@ -295,6 +301,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         mbar_init(bar_full + 8u, 1);
         mbar_init(bar_empty, 1);
         mbar_init(bar_empty + 8u, 1);
+        mbar_init(bar_ld, 1);
         fence_mbar_init();
     }
     for (int c = tid; c < 2048; c += TC_THREADS) {  // R as the B operand: row d, 16-byte chunk j
@@ -419,6 +426,16 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
     long long tc_stamp_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, tc_stamp_last = clock64();
 #endif
     uint32_t it = 0;  // tiles this CTA has started: parity of the per-tile arrays, phase of their barriers
+    uint32_t ld_phase = 0;
+    auto issue_load = [&](int tile_n) {  // one thread: the 128 vectors of a tile -> operand tile, [half][token][head][128 B]
+        const int kind_n = (p.k_buf && tile_n < tiles_per_kind) ? 0 : 1;
+        const int vec0_n = (tile_n - (kind_n == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
+        mbar_arrive_expect_tx(bar_ld, 2u * 16384u);  // (rows past the end of the input arrive as zeros and count)
+        tma_load_4d(TcSmem::A_X, kind_n == 0 ? &tm_k_in : &tm_v_in, bar_ld, 0, 0, div_hkv.div(vec0_n), 0);
+    };
+    if constexpr (TMA_IN) {
+        if (tid == 0 && (int)blockIdx.x < total_tiles) issue_load((int)blockIdx.x);
+    }
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
         const int b = (int)(it & 1u);
@@ -459,6 +476,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         constexpr int PASSES = 4 * TC_TILE / TC_WORKERS, VPP = TC_WORKERS / 4;  // passes per tile, vectors per pass
         uint4 raw_all[PASSES][4];
         float tt_all[PASSES];
+        if constexpr (!TMA_IN) {
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {  // every load of the tile goes out before the arithmetic starts
             const int vid = vec0 + pass * VPP + (tid >> 2);
@@ -469,12 +487,15 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
 #pragma unroll
             for (int i = 0; i < 4; ++i) raw_all[pass][i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
         }
-        // Thread v < 128: where vector v of the tile goes (its position and row base are loads of their own: issued here,
-        // needed only once the operands are with the tensor core)
+        }
+        // One thread per vector settles it (norm out, 1/norm, where its codes go): thread v < 128, or, in the TMA form, the
+        // lane that ends up holding the vector's sum of squares.  Its position and row base are loads of their own: issued
+        // here, needed only once the operands are with the tensor core.
+        const int settle_v = TMA_IN ? (lane < 16 ? 64 * (lane >> 3) + 8 * warp + (lane & 7) : -1) : (tid < TC_TILE ? tid : -1);
         long long my_dst = -1, my_norm_at = 0;  // byte offset of the vector's codes in the cache (-1: none), index of its norm
-        if (tid < TC_TILE && vec0 + tid < vec_per_kind) {
+        if (settle_v >= 0 && vec0 + settle_v < vec_per_kind) {
             int tok, head, seq, t, layer = 0;
-            split_vec(tid, tok, head);
+            split_vec(settle_v, tok, head);
             split_tok(tok, seq, t);
             int sq = seq, cap = p.capacity_rows;
             if (p.step_G > 0) {
@@ -491,6 +512,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
                 atomicMax(p.status, ST_BAD_POSITION);
             }
         }
+        if constexpr (!TMA_IN) {
         {   // the CTA's next tile (same kind or the other one) on its way into L2 while this one is worked on
             const int ntile = tile + (int)gridDim.x;
             if (ntile < total_tiles) {
@@ -605,6 +627,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             const float p2 = __shfl_sync(0xffffffffu, part, l0 + 2), p3 = __shfl_sync(0xffffffffu, part, l0 + 3);
             tt_all[pass] = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
         }
+        }
         TC_STAMP(2);
         // The operand tile is free (its MMAs were waited for, and the epilogue reads tensor memory only); the per-vector
         // arrays and the queue of this parity are free once the chain warp is through with the tile before the last.
@@ -614,6 +637,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         }
         TC_STAMP(3);
         if (tid == 0) ctrl[12 + b] = 0;
+        if constexpr (!TMA_IN) {
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {  // the vectors as they are become the A operand
             const int v = pass * VPP + (tid >> 2), c = tid & 3;
@@ -627,6 +651,13 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         }
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
         named_barrier(1, TC_WORKERS);
+        } else {
+            if (!dead && !mbar_wait_bounded(bar_ld, ld_phase, 1u << 24)) {
+                dead = true;
+                atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+            }
+            ld_phase ^= 1u;
+        }
         TC_STAMP(4);
 
         // ---- 2. the rotation: 8 K-steps into one accumulator ----
@@ -639,13 +670,38 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
             }
             umma_commit(bar);
         }
-        // ---- 2b. while the tensor core works: thread v < 128 settles vector v -- norm out, 1/norm, where its codes go ----
-        if (tid < TC_TILE) {
-            const float tt = inv_s[tid];
-            const bool abnormal = !(tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
-            if (my_dst >= 0) cn[my_norm_at] = __float2half_rn(sqrt_approx_ftz(tt));
-            dst_s[tid] = my_dst;
-            inv_s[tid] = abnormal ? -1.0f : rsqrt_approx_ftz(tt);
+        // ---- 2b. while the tensor core works ----
+        float my_tt = 0.0f;
+        if constexpr (TMA_IN) {
+            // Sums of squares from the operand tile.  Pass q: lane (r, c) of warp w takes chunk c (32 coordinates) of vector
+            // 64 q + 8 w + r; the eight lanes of a quarter-warp read eight different rows, whose 128-byte swizzle puts their
+            // 16-byte pieces on different banks.  The four chunk sums meet by shuffles, in the reference's order.
+            const int r = lane & 7, c = lane >> 3;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int v = 64 * q + 8 * warp + r;
+                float2 v2[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::A_X, v, 32 * c + 8 * i));
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v2[4 * i + e] = __half22float2(h2[e]);
+                }
+                const float part = sumsq_tree32(v2);
+                const float p0 = __shfl_sync(0xffffffffu, part, r), p1 = __shfl_sync(0xffffffffu, part, r + 8);
+                const float p2 = __shfl_sync(0xffffffffu, part, r + 16), p3 = __shfl_sync(0xffffffffu, part, r + 24);
+                const float tt = add_ftz(add_ftz(add_ftz(p0, p2), add_ftz(p1, p3)), 1e-12f);
+                if (c == q) my_tt = tt;
+            }
+        } else {
+            if (settle_v >= 0) my_tt = inv_s[settle_v];
+        }
+        if (settle_v >= 0) {  // settle the vector: norm out, 1/norm, where its codes go
+            const bool abnormal = !(my_tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
+            if (my_dst >= 0) cn[my_norm_at] = __float2half_rn(sqrt_approx_ftz(my_tt));
+            dst_s[settle_v] = my_dst;
+            inv_s[settle_v] = abnormal ? -1.0f : rsqrt_approx_ftz(my_tt);
         }
         TC_STAMP(5);
         if (!dead && !mbar_wait_bounded(bar, phase, 1u << 22)) {
@@ -655,6 +711,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM) prefill_append_tc_
         dead = named_barrier_or(1, TC_WORKERS, dead);
         phase ^= 1u;
         tc_fence_after();
+        if constexpr (TMA_IN) {  // the operand tile has been read by the tensor core and by every thread: the next tile's vectors
+            if (tid == 0 && !dead && tile + (int)gridDim.x < total_tiles) issue_load(tile + (int)gridDim.x);
+        }
         TC_STAMP(6);
 
         // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
