@@ -227,15 +227,11 @@ __device__ __forceinline__ uint32_t bucket_entry(uint32_t grid_bits) {
 }
 // Division of n < 2^31 by a divisor fixed for the launch: q = (n * mul) >> shift with mul = ceil(2^shift / d),
 // shift = 31 + ceil(log2 d); exact because n * (mul * d - 2^shift) < 2^shift.
-struct FastDiv {
-    uint32_t mul, shift;
-    __device__ __forceinline__ explicit FastDiv(uint32_t d) {
-        const uint32_t l = d > 1u ? 32u - (uint32_t)__clz((int)(d - 1u)) : 0u;
-        shift = 31u + l;
-        mul = (uint32_t)((((unsigned long long)1 << shift) + d - 1u) / d);
-    }
-    __device__ __forceinline__ int div(int n) const { return (int)(((unsigned long long)(uint32_t)n * mul) >> shift); }
-};
+__device__ __forceinline__ uint2 fastdiv_make(uint32_t d) {  // (mul, shift)
+    const uint32_t l = d > 1u ? 32u - (uint32_t)__clz((int)(d - 1u)) : 0u;
+    return make_uint2((uint32_t)((((unsigned long long)1 << (31u + l)) + d - 1u) / d), 31u + l);
+}
+__device__ __forceinline__ int fastdiv(int n, uint2 ms) { return (int)(((unsigned long long)(uint32_t)n * ms.x) >> ms.y); }
 __device__ __forceinline__ uint32_t mad_hi_u32(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -348,7 +344,8 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
     const bool fast_head = p.Hkv <= 256;
     const uint32_t hkv_magic = ((1u << 20) + (uint32_t)p.Hkv - 1u) / (uint32_t)p.Hkv;
     const bool fast_tok = p.T > TC_TILE + 1;
-    const FastDiv div_hkv((uint32_t)p.Hkv), div_T((uint32_t)p.T), div_G((uint32_t)(p.step_G > 0 ? p.step_G : 1));
+    const uint2 div_hkv = fastdiv_make((uint32_t)p.Hkv), div_T = fastdiv_make((uint32_t)p.T),
+                div_G = fastdiv_make((uint32_t)(p.step_G > 0 ? p.step_G : 1));
 
     const int ev = (warp & 3) * 32 + lane;    // this thread's vector in the epilogue
     const int cc0 = (warp >> 2) * 2;          // its first block of 32 coordinates (warps 0-7)
@@ -387,7 +384,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         atomicOr(w, (uint32_t)code << sh);
     };
     auto vector_input = [&](int kind, int vid) -> const __half* {  // the 128 inputs of vector vid of a kind, as rotated
-        const int tok = div_hkv.div(vid), head = vid - tok * p.Hkv;
+        const int tok = fastdiv(vid, div_hkv), head = vid - tok * p.Hkv;
         const __half* buf = kind == 0 ? (PRODUCER ? p.k_post : p.k_buf) : p.v_buf;
         return buf + (size_t)tok * p.kv_dim + (size_t)head * HEAD_DIM;
     };
@@ -431,7 +428,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         const int kind_n = (p.k_buf && tile_n < tiles_per_kind) ? 0 : 1;
         const int vec0_n = (tile_n - (kind_n == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
         mbar_arrive_expect_tx(bar_ld, 2u * 16384u);  // (rows past the end of the input arrive as zeros and count)
-        tma_load_4d(TcSmem::A_X, kind_n == 0 ? &tm_k_in : &tm_v_in, bar_ld, 0, 0, div_hkv.div(vec0_n), 0);
+        tma_load_4d(TcSmem::A_X, kind_n == 0 ? &tm_k_in : &tm_v_in, bar_ld, 0, 0, fastdiv(vec0_n, div_hkv), 0);
     };
     if constexpr (TMA_IN) {
         if (tid == 0 && (int)blockIdx.x < total_tiles) issue_load((int)blockIdx.x);
@@ -447,15 +444,15 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         const __half* src_buf = kind == 0 ? p.k_buf : p.v_buf;
         uint8_t* cq = kind == 0 ? p.ck : p.cv;
         __half* cn = kind == 0 ? p.kn : p.vn;
-        const int tok0 = div_hkv.div(vec0), head0 = vec0 - tok0 * p.Hkv;
-        const int seq0 = div_T.div(tok0), t0 = tok0 - seq0 * p.T;
+        const int tok0 = fastdiv(vec0, div_hkv), head0 = vec0 - tok0 * p.Hkv;
+        const int seq0 = fastdiv(tok0, div_T), t0 = tok0 - seq0 * p.T;
         auto split_vec = [&](int v, int& tok, int& head) {  // vector vec0 + v of the tile
             if (fast_head) {
                 const uint32_t x = (uint32_t)(head0 + v), dq = (x * hkv_magic) >> 20;
                 tok = tok0 + (int)dq;
                 head = (int)(x - dq * (uint32_t)p.Hkv);
             } else {
-                tok = div_hkv.div(vec0 + v);
+                tok = fastdiv(vec0 + v, div_hkv);
                 head = (vec0 + v) - tok * p.Hkv;
             }
         };
@@ -466,7 +463,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                 seq = seq0 + (wrap ? 1 : 0);
                 t = tt - (wrap ? p.T : 0);
             } else {
-                seq = div_T.div(tok);
+                seq = fastdiv(tok, div_T);
                 t = tok - seq * p.T;
             }
         };
@@ -492,25 +489,23 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         // lane that ends up holding the vector's sum of squares.  Its position and row base are loads of their own: issued
         // here, needed only once the operands are with the tensor core.
         const int settle_v = TMA_IN ? (lane < 16 ? 64 * (lane >> 3) + 8 * warp + (lane & 7) : -1) : (tid < TC_TILE ? tid : -1);
-        long long my_dst = -1, my_norm_at = 0;  // byte offset of the vector's codes in the cache (-1: none), index of its norm
+        long long my_row_base = 0;
+        int my_pos = -1, my_head_layer = 0;  // position in the sequence (-1: the vector is not stored), head | layer << 16
         if (settle_v >= 0 && vec0 + settle_v < vec_per_kind) {
             int tok, head, seq, t, layer = 0;
             split_vec(settle_v, tok, head);
             split_tok(tok, seq, t);
             int sq = seq, cap = p.capacity_rows;
             if (p.step_G > 0) {
-                layer = div_G.div(seq);
+                layer = fastdiv(seq, div_G);
                 sq = seq - layer * p.step_G;
                 if (p.seq_capacity) cap = p.seq_capacity[sq];
             }
             const int pos = p.step_G > 0 ? p.positions[sq] : (p.positions ? p.positions[t] : p.pos_value + t);
-            if (pos >= 0 && (cap <= 0 || pos < cap)) {
-                const long long row = (p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows) + pos;
-                my_dst = (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
-                my_norm_at = (long long)layer * p.norm_layer_stride + row * p.Hkv + head;
-            } else {
-                atomicMax(p.status, ST_BAD_POSITION);
-            }
+            my_row_base = p.row_base ? p.row_base[sq] : p.token_row0 + (long long)sq * p.seq_stride_rows;
+            my_head_layer = head | (layer << 16);
+            if (pos >= 0 && (cap <= 0 || pos < cap)) my_pos = pos;
+            else atomicMax(p.status, ST_BAD_POSITION);
         }
         if constexpr (!TMA_IN) {
         {   // the CTA's next tile (same kind or the other one) on its way into L2 while this one is worked on
@@ -519,7 +514,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                 const int nkind = (p.k_buf && ntile < tiles_per_kind) ? 0 : 1;
                 const int nvid = (ntile - (nkind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE + (tid >> 1);
                 if (nvid < vec_per_kind) {  // one 128-byte line per thread
-                    const int ntok = div_hkv.div(nvid), nhead = nvid - ntok * p.Hkv;
+                    const int ntok = fastdiv(nvid, div_hkv), nhead = nvid - ntok * p.Hkv;
                     const __half* a = (nkind == 0 ? p.k_buf : p.v_buf) + (size_t)ntok * p.kv_dim + (size_t)nhead * HEAD_DIM + 64 * (tid & 1);
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
                 }
@@ -554,7 +549,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                     const float rms = rsqrt_approx_ftz(fma_ftz(add_ftz(add_ftz(q0, q2), add_ftz(q1, q3)), 1.0f / HEAD_DIM, p.eps));
                     int layer = 0, sq_i = seq, ppos;
                     if (p.step_G > 0) {
-                        layer = div_G.div(seq);
+                        layer = fastdiv(seq, div_G);
                         sq_i = seq - layer * p.step_G;
                         ppos = live ? p.positions[sq_i] : 0;
                     } else {
@@ -699,7 +694,13 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         }
         if (settle_v >= 0) {  // settle the vector: norm out, 1/norm, where its codes go
             const bool abnormal = !(my_tt < 3.0e38f);  // an infinity or a NaN among the inputs: every coordinate is a NaN
-            if (my_dst >= 0) cn[my_norm_at] = __float2half_rn(sqrt_approx_ftz(my_tt));
+            long long my_dst = -1;  // byte offset of the vector's codes in the cache
+            if (my_pos >= 0) {
+                const long long row = my_row_base + my_pos;
+                const int head = my_head_layer & 65535, layer = my_head_layer >> 16;
+                my_dst = (long long)layer * p.code_layer_stride + row * kvp + (long long)head * bpv;
+                cn[(long long)layer * p.norm_layer_stride + row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(my_tt));
+            }
             dst_s[settle_v] = my_dst;
             inv_s[settle_v] = abnormal ? -1.0f : rsqrt_approx_ftz(my_tt);
         }
@@ -718,7 +719,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
 
         // ---- 3. accumulators -> codes.  A warp reaches the 32 TMEM lanes (vectors) of its rank modulo 4; warps w and
         //         w + 4 share those vectors and take 64 of the 128 coordinates (two blocks of 32 columns) each ----
-        uint32_t own_cc[2] = {0u, 0u};  // near-bound coordinates that did not fit the shared queue
+        uint32_t own0 = 0u, own1 = 0u;  // near-bound coordinates (of this thread's two blocks) that did not fit the shared queue
         long long ev_dst_keep = -1;
         if (!dead) {
             const float inv = inv_s[ev];
@@ -726,7 +727,9 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
             ev_dst_keep = ev_dst;
             const bool abn = inv < 0.0f;
             const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * 256.0f, inv * 256.0f);
-            const float2 magic2 = make_float2(3145728.0f, 3145728.0f);
+            const float2 magic2 = make_float2(3145728.0f, 3145728.0f), minus1 = make_float2(-1.0f, -1.0f);
+            constexpr float kNear = TC_MARGIN + 1.0e-6f;
+            const float2 minus_m2 = make_float2(-kNear * kNear, -kNear * kNear);
 #pragma unroll 1
             for (int cc = cc0; cc < cc0 + 2; ++cc) {
                 uint32_t acc_r[32];
@@ -743,11 +746,12 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                     const float2 dval = mul2(a, inv2);
                     const float2 kf = fma2(a, inv256, magic2);  // k = rne(1024 x) in the low bits
                     const uint32_t e0 = bucket_entry(__float_as_uint(kf.x)), e1 = bucket_entry(__float_as_uint(kf.y));
-                    const float d0 = __uint_as_float(e0) - dval.x, d1 = __uint_as_float(e1) - dval.y;
-                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(d0), 2u, e0), width);
-                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(d1), 2u, e1), width);
-                    near_rev = __funnelshift_l(__float_as_uint(fabsf(d0) - (TC_MARGIN + 1.0e-6f)), near_rev, 1);
-                    near_rev = __funnelshift_l(__float_as_uint(fabsf(d1) - (TC_MARGIN + 1.0e-6f)), near_rev, 1);
+                    const float2 dd = fma2(dval, minus1, make_float2(__uint_as_float(e0), __uint_as_float(e1)));  // bound - value
+                    const float2 nn = fma2(dd, dd, minus_m2);  // negative where |bound - value| < margin
+                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(dd.x), 2u, e0), width);
+                    word = __funnelshift_r(word, mad_hi_u32(__float_as_uint(dd.y), 2u, e1), width);
+                    near_rev = __funnelshift_l(__float_as_uint(nn.x), near_rev, 1);
+                    near_rev = __funnelshift_l(__float_as_uint(nn.y), near_rev, 1);
                 };
                 if (bits == 4) {
 #pragma unroll
@@ -771,7 +775,8 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                     near_mask &= near_mask - 1;
                     const uint32_t slot = atomicAdd(const_cast<uint32_t*>(&ctrl[12 + b]), 1u);
                     if (slot < (uint32_t)TC_LIST_CAP) list_s[slot] = ((uint32_t)ev << 8) | (uint32_t)(32 * cc + i);
-                    else own_cc[cc - cc0] |= 1u << i;
+                    else if (cc == cc0) own0 |= 1u << i;
+                    else own1 |= 1u << i;
                 }
                 // 32 coordinates' codes go straight to the cache (16 or 8 bytes; the other chunks of the same 32-byte sector
                 // follow from this thread's next block and from the warp that shares the vector)
@@ -787,12 +792,12 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         if (tid == 0) mbar_arrive(bar_full + 8u * (uint32_t)b);  // over to the chain warp
         TC_STAMP(8);
         // near-bound coordinates that did not fit the queue (none, ordinarily): their owners run the chains themselves
-        if (!dead && (own_cc[0] | own_cc[1]) != 0u && ev_dst_keep >= 0) {
+        if (!dead && (own0 | own1) != 0u && ev_dst_keep >= 0) {
             const __half* x = vector_input(kind, vec0 + ev);
             const float inv = inv_s[ev];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-                uint32_t m = own_cc[k];
+                uint32_t m = k ? own1 : own0;
                 while (m) {
                     const int i = __ffs(m) - 1;
                     m &= m - 1;
