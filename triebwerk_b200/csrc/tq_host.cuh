@@ -245,7 +245,7 @@ inline int launch_append_t(const AppendParams& p, dim3 grid, cudaStream_t s, boo
 inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bool producer = false) {
     const long long tokens = (long long)t.n_seq * t.T;
     const long long tiles = ((tokens * t.Hkv + TC_TILE - 1) / TC_TILE) * ((t.k_buf ? 1 : 0) + (t.v_buf ? 1 : 0));
-    long long grid = (long long)TC_CTAS_PER_SM * device_props().sm_count;
+    long long grid = (long long)(producer ? 2 : TC_CTAS_PER_SM) * device_props().sm_count;
     if (grid > tiles) grid = tiles;
     if (grid < 1) return TQ_OK;
     // The vectors reach the operand tile by tensor-map copies where the layout allows it (TQ_PREFILL_TMA=0: through
@@ -279,9 +279,9 @@ inline int launch_prefill_tc_params(const PrefillTcParams& t, cudaStream_t s, bo
         for (int w = 0; w < 2; ++w) {
             const double n = (double)h[16 * w + 15] * (double)((tiles + grid - 1) / grid);
             fprintf(stderr, "append stamps, warp %d (cycles per tile): top %.0f | loads %.0f | tree %.0f | wait for the chain warp %.0f | operand + barrier B %.0f | "
-                            "mma issue + per-vector %.0f | mma wait + barrier C %.0f | epilogue %.0f | barrier D %.0f\n",
+                            "mma issue + per-vector %.0f | mma wait + barrier C %.0f | epilogue %.0f | barrier D %.0f | loop back %.0f\n",
                     w ? 7 : 0, h[16 * w] / n, h[16 * w + 1] / n, h[16 * w + 2] / n, h[16 * w + 3] / n, h[16 * w + 4] / n, h[16 * w + 5] / n,
-                    h[16 * w + 6] / n, h[16 * w + 7] / n, h[16 * w + 8] / n);
+                    h[16 * w + 6] / n, h[16 * w + 7] / n, h[16 * w + 8] / n, h[16 * w + 9] / n);
         }
     }
 #endif

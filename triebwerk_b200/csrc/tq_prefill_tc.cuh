@@ -11,24 +11,31 @@
 //     summation errors plus 2^-24 relative for the scaling -- no split of x into a high and a low operand is needed,
 //     and the operand tile is a plain copy of the input;
 //   * a coordinate whose value lies within TC_MARGIN of a decision bound is recomputed with the reference's exact
-//     chain (R read back from the shared-memory operand tile, x rebuilt from the input); everywhere else the
+//     chain (R read back from the shared-memory operand tile, x re-read from the input); everywhere else the
 //     two sums cannot fall on different sides of a bound.  TC_MARGIN (1.6e-5) is twice the textbook bound on the
 //     distance of a 128-term fp32 sum from the exact value when sum|r_k x_k| <= 1 (128 * 2^-24 = 7.6e-6; |x| = 1 and
 //     |R row| = 1): once for the chain, once for the tensor-core sum, with 8e-7 left for the scaling roundings
 //     (1.2e-7 for |x.R| < 2 and 6e-8 for the x_k).  About 1 coordinate in 700 takes the exact path.
 // Sums of squares, rsqrt/sqrt and the norm use the reference's own order and instructions (see tq_append.cuh).
 //
-// One CTA = 256 threads and one tile of 128 head vectors at a time (16 tokens x 8 heads of K or of V), three CTAs per SM
-// (76 KB of shared memory, 128 columns of tensor memory and at most 80 registers per thread each):
-//   1. thread (vector, 32-coordinate chunk) loads 64 bytes, builds the reference's shuffle-tree sum of squares in
-//      registers, the four chunk sums meet by shuffles; the 64 bytes go to shared memory as they are, in the canonical
-//      K-major 128-byte-swizzled operand layout (rows of 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7));
-//   2. one thread issues 8 tcgen05.mma (K-steps of 16) against the resident R tile and commits to an mbarrier; every
-//      wait is bounded;
+// One CTA = eight worker warps + one chain warp (288 threads), one tile of 128 head vectors at a time (16 tokens x 8 heads
+// of K or of V), three CTAs per SM (74 KB of shared memory, 128 columns of tensor memory, 72 registers per thread each):
+//   1. the tile's 128 vectors reach the operand tile -- the canonical K-major 128-byte-swizzled layout: rows of 128
+//      bytes, 16-byte chunk c of row r at chunk c ^ (r & 7) -- by ONE 4-D tensor-map copy [half][token][head][128 B],
+//      issued as soon as the previous tile's MMAs have been waited for, so it lands while that tile is quantised
+//      (TMA form); where the layout does not allow a tensor map, and in the producer form, thread (vector, 32-coordinate
+//      chunk) loads 64 bytes and stores them there;
+//   2. one thread issues 8 tcgen05.mma (K-steps of 16) against the resident R tile and commits to an mbarrier (every
+//      wait is bounded); meanwhile the workers build the reference's shuffle-tree sums of squares (packed fp32
+//      instructions, from shared memory in the TMA form), and one thread per vector settles it: norm out, 1/norm, where
+//      its codes go;
 //   3. each thread reads 64 of ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per
-//      warp and instruction; warps w and w + 4 share a lane quarter), scales by 1/norm, quantises through a 2048-bucket
-//      uniform grid (bucket -> code, or -> the one bound inside it), packs, and queues near-bound coordinates;
-//   4. queued coordinates get the exact chain and patch the packed tile; the tile leaves as coalesced 16-byte stores.
+//      warp and instruction; warps w and w + 4 share a lane quarter), scales by 1/norm, quantises through a 1024-bucket
+//      uniform grid (bucket -> code, or -> the one bound inside it; 13 instructions per two coordinates), stores the
+//      packed codes straight to the cache and queues near-bound coordinates;
+//   4. the chain warp, one tile behind (per-tile arrays exist twice; two mbarrier pairs hand them back and forth),
+//      runs the exact chain of the queued coordinates, one lane per coordinate, and patches the stored codes with
+//      atomics.  None of the workers' barriers waits for it.
 #pragma once
 
 #include "tq_common.cuh"
@@ -259,7 +266,7 @@ __device__ __forceinline__ uint32_t tc_operand_addr(uint32_t tile, int row, int 
 // quantised) instead of through registers; the sums of squares are then taken from shared memory while the tensor core
 // already rotates.  Needs a tensor map over the input (make_append_input_map) and Hkv dividing 128; never with PRODUCER.
 template <bool PRODUCER, bool TMA_IN>
-__global__ void __launch_bounds__(TC_THREADS, TC_CTAS_PER_SM)
+__global__ void __launch_bounds__(TC_THREADS, PRODUCER ? 2 : TC_CTAS_PER_SM)  // (the producer form needs more registers)
 prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __grid_constant__ CUtensorMap tm_v_in, const PrefillTcParams p) {
     static_assert(!(PRODUCER && TMA_IN), "the producer form computes its K vectors: they cannot come by a bulk copy");
     extern __shared__ __align__(1024) uint8_t tc_smem[];
@@ -435,6 +442,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
     }
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        TC_STAMP(9);
         const int b = (int)(it & 1u);
         long long* const dst_s = dst_buf(b);
         float* const inv_s = inv_buf(b);
