@@ -46,6 +46,8 @@ constexpr int TC_TILE = 128;       // head vectors per tile = MMA M
 constexpr int TC_WORKERS = 256;     // eight warps that load, rotate and quantise
 constexpr int TC_THREADS = TC_WORKERS + 32;  // ... and one warp for the exact chains of near-bound coordinates
 constexpr float TC_MARGIN = 1.6e-5f;
+constexpr int TC_BUCKETS = 256;    // entries of the bucket table
+constexpr float TC_BUCKETS_PER_UNIT = 46.0f;  // 1 / bucket width
 constexpr int TC_LIST_CAP = 96;    // queued near-bound coordinates per tile; the rest is handled by their owners
 
 // Shared memory by ABSOLUTE shared address (the kernel checks that its dynamic shared memory covers the range): the
@@ -58,7 +60,7 @@ struct TcSmem {
                                                          // holds an infinity or a NaN
     static constexpr uint32_t CTRL = INV0 + 512;         // mma mbarrier (8 B), tmem base (4 B), pad, full[2], empty[2] mbarriers,
                                                          // queue counts [2]
-    static constexpr uint32_t GRID = 0x1000;             // uint32[1024] bucket table, see the kernel
+    static constexpr uint32_t GRID = 0x1000;             // uint32[TC_BUCKETS] bucket table, see the kernel
     static constexpr uint32_t A_X = 0x2000;              // the vectors: 2 K-regions x [128 rows][128 B]
     static constexpr uint32_t B_R = 0xA000;              // R: rows = output coordinate d, K-major
     static constexpr uint32_t DST1 = 0x12000;
@@ -229,7 +231,7 @@ __device__ __forceinline__ float sumsq_tree32(const float2 (&v)[16]) {
 // One entry of the bucket table (see the kernel), addressed by the low mantissa bits of the grid value.
 __device__ __forceinline__ uint32_t bucket_entry(uint32_t grid_bits) {
     uint32_t e;
-    asm("ld.shared.u32 %0, [%1 + %2];" : "=r"(e) : "r"(grid_bits & 0xffcu), "n"(TcSmem::GRID));
+    asm("ld.shared.u32 %0, [%1 + %2];" : "=r"(e) : "r"(grid_bits & (uint32_t)(4 * TC_BUCKETS - 4)), "n"(TcSmem::GRID));
     return e;
 }
 // Division of n < 2^31 by a divisor fixed for the launch: q = (n * mul) >> shift with mul = ceil(2^shift / d),
@@ -312,23 +314,30 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.rotation + (size_t)d * HEAD_DIM) + j);
         *reinterpret_cast<uint4*>(gbase + (tc_operand_addr(base + TcSmem::B_R, d, 8 * j) - base)) = u;
     }
-    for (int i = tid; i < 1024; i += TC_THREADS) {
-        // Bucket table over the rotated coordinate x.  The epilogue forms k = rne(1024 x) in the low mantissa bits of
-        // fma(x, 256, 1.5 * 2^21) and takes bucket k >> 2 (modulo 1024): bucket n holds x in [(4 n - 0.5) / 1024,
-        // (4 n + 3.5) / 1024], |x| < 2; no two bounds are closer than five buckets.  An entry is ONE float: the decision
+    for (int i = tid; i < TC_BUCKETS; i += TC_THREADS) {
+        // Bucket table over the rotated coordinate x.  The epilogue forms k = rne(4 x / w) in the low mantissa bits of
+        // fma(x, 1 / w, 1.5 * 2^21) and takes bucket k >> 2 (modulo 256): bucket n holds x in [(n - 0.125) w, (n + 0.875) w],
+        // |x| < 2.  The width w = 1/46 is the largest handy one below the smallest distance of two bounds (0.0228 at four
+        // bits), so no bucket holds two -- and the 32 buckets around zero, where a rotated coordinate (sigma = 0.088) falls
+        // with probability 0.9999, sit in 32 different shared-memory banks: the look-ups of a warp rarely collide.  An
+        // entry is ONE float: the decision
         // bound that lies inside the bucket (widened by four margins) with its four lowest mantissa bits replaced by the
         // code a value BELOW the bound gets -- the code is then entry_code + (x > bound) -- or, when no bound is near the
         // bucket, 0x7f000000 (1.7e38: every x is below it) carrying the bucket's code.  The replaced bits move the bound
         // by less than 3e-7; the near-bound test uses a margin wider by more than that, and only coordinates outside it
         // keep the code found here.
-        const int n = i < 512 ? i : i - 1024;
-        const float lo = ((float)(4 * n) - 0.5f) * (1.0f / 1024.0f), hi = lo + (1.0f / 256.0f);
+        const int n = i < TC_BUCKETS / 2 ? i : i - TC_BUCKETS;
+        const float lo = ((float)(4 * n) - 0.5f) * (0.25f / TC_BUCKETS_PER_UNIT), hi = lo + (1.0f / TC_BUCKETS_PER_UNIT);
         int code = 0, amb = -1;
         float ambv = 0.0f;
         for (int b = 0; b < nb; ++b) {
             const float bv = bits == 4 ? kBnd4[b] : kBnd2[b];
             if (bv <= lo) ++code;
-            if (bv >= lo - 4.0f * TC_MARGIN && bv <= hi + 4.0f * TC_MARGIN) { amb = b; ambv = bv; }
+            if (bv >= lo - 4.0f * TC_MARGIN && bv <= hi + 4.0f * TC_MARGIN) {
+                if (amb >= 0) atomicMax(p.status, ST_SMEM_LAYOUT);  // (two bounds in one bucket: the table cannot say which)
+                amb = b;
+                ambv = bv;
+            }
         }
         grid_s[i] = amb >= 0 ? ((__float_as_uint(ambv) & ~15u) | (uint32_t)amb) : (0x7f000000u | (uint32_t)code);
     }
@@ -734,7 +743,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
             const long long ev_dst = dst_s[ev];
             ev_dst_keep = ev_dst;
             const bool abn = inv < 0.0f;
-            const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * 256.0f, inv * 256.0f);
+            const float2 inv2 = make_float2(inv, inv), inv256 = make_float2(inv * TC_BUCKETS_PER_UNIT, inv * TC_BUCKETS_PER_UNIT);
             const float2 magic2 = make_float2(3145728.0f, 3145728.0f), minus1 = make_float2(-1.0f, -1.0f);
             constexpr float kNear = TC_MARGIN + 1.0e-6f;
             const float2 minus_m2 = make_float2(-kNear * kNear, -kNear * kNear);
@@ -752,7 +761,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                 auto two = [&](int i, uint32_t& word, int width) {
                     const float2 a = make_float2(__uint_as_float(acc_r[i]), __uint_as_float(acc_r[i + 1]));
                     const float2 dval = mul2(a, inv2);
-                    const float2 kf = fma2(a, inv256, magic2);  // k = rne(1024 x) in the low bits
+                    const float2 kf = fma2(a, inv256, magic2);  // k = rne(4 * 46 x) in the low bits
                     const uint32_t e0 = bucket_entry(__float_as_uint(kf.x)), e1 = bucket_entry(__float_as_uint(kf.y));
                     const float2 dd = fma2(dval, minus1, make_float2(__uint_as_float(e0), __uint_as_float(e1)));  // bound - value
                     const float2 nn = fma2(dd, dd, minus_m2);  // negative where |bound - value| < margin
