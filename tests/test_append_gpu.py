@@ -243,3 +243,22 @@ def test_batched_prefill_append_equals_per_sequence_calls(bits, ragged):
     assert int(engines[0].layer_cache(0)[0].view(torch.uint8).ne(0).sum()) > 0
     with pytest.raises(tq.TqError):
         engines[0].prefill_append_batch(0, 3, k, v, 0)  # sequences 3, 4, 5: one too many
+
+
+def test_tensor_core_prefill_append_thread_load_form_in_a_child_process():
+    """Where a tensor map over the input can be had, the tcgen05 append takes its vectors by tensor-map copies; the
+    thread-load form (unaligned inputs, a head count that does not divide 128, the producer form) is selected for every
+    call by TQ_PREFILL_TMA=0, which the library reads once per process: the append parity tests of the tensor-core
+    kernel run again in a child with it set."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("TQ_PREFILL_TMA") == "0":
+        pytest.skip("already the child")
+    env = dict(os.environ, TQ_PREFILL_TMA="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_append_gpu.py", "tests/test_engine_gpu.py", "-q", "-x", "-m", "gpu",
+                        "-k", "(tensor_core or batched_prefill or prefill_layer or whole) and not child", "-p", "no:cacheprovider"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
