@@ -224,6 +224,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// The same with a suspend-time hint per poll (nanoseconds): for waits that are expected to last, fewer polls.
+__device__ __forceinline__ bool mbar_wait_bounded_hint(uint32_t bar, uint32_t parity, uint32_t limit, uint32_t hint_ns) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    }
+    return false;
+}
+
 // 2-D tiled TMA load global -> shared of this CTA (no multicast), completion on an mbarrier.
 // x = innermost coordinate in elements (bytes here; must be a multiple of 16), y = row.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y) {

@@ -415,7 +415,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
             const int kind = (p.k_buf && tile < tiles_per_kind) ? 0 : 1;
             const int vec0 = (tile - (kind == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
             uint8_t* cq = kind == 0 ? p.ck : p.cv;
-            if (!mbar_wait_bounded(bar_full + 8u * (uint32_t)b, (it >> 1) & 1u, 1u << 24)) {
+            if (!mbar_wait_bounded_hint(bar_full + 8u * (uint32_t)b, (it >> 1) & 1u, 1u << 18, 4000u)) {
                 if (lane == 0) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
                 return;
             }
@@ -664,7 +664,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
         named_barrier(1, TC_WORKERS);
         } else {
-            if (!dead && !mbar_wait_bounded(bar_ld, ld_phase, 1u << 24)) {
+            if (!dead && !mbar_wait_bounded_hint(bar_ld, ld_phase, 1u << 18, 2000u)) {
                 dead = true;
                 atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
             }
@@ -722,7 +722,7 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
             inv_s[settle_v] = abnormal ? -1.0f : rsqrt_approx_ftz(my_tt);
         }
         TC_STAMP(5);
-        if (!dead && !mbar_wait_bounded(bar, phase, 1u << 22)) {
+        if (!dead && !mbar_wait_bounded_hint(bar, phase, 1u << 18, 2000u)) {
             dead = true;
             atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
         }
