@@ -312,9 +312,9 @@ def build_engine(w, device_seed):
     return eng, gen, scales
 
 
-def run_append_only(args, w, rank, world, local_rank):
+def measure_append(args, w, rank, local_rank):
     """Config 2's shape: whole prompts appended to the packed cache (token-mode append kernel), nothing attended.
-    One step = every sequence's 2048 tokens through the layers of the slice."""
+    One step = every sequence's 2048 tokens through the layers of the slice.  Returns the figures of the timed steps."""
     import torch
     import triebwerk_b200 as tq
     from triebwerk_b200 import synth
@@ -361,17 +361,28 @@ def run_append_only(args, w, rank, world, local_rank):
     vectors = NL * G * T * 2 * Hkv
     vpb = 4 if bits == 2 else 2
     bytes_step = vectors * (256 + D // vpb + 2)
+    del eng, kp, vp
+    torch.cuda.empty_cache()
+    return {"ms": ms, "steps": steps, "warmup": 1 if big else max(3, args.warmup), "vectors": vectors, "bytes_step": bytes_step,
+            "clocks": clocks, "per_sequence": per_sequence, "launches": steps * NL * (G if per_sequence else G // B), "vpb": vpb}
+
+
+def run_append_only(args, w, rank, world, local_rank):
+    r = measure_append(args, w, rank, local_rank)
+    ms, steps, vectors, bytes_step, clocks, per_sequence, vpb = (r[k] for k in ("ms", "steps", "vectors", "bytes_step", "clocks",
+                                                                                "per_sequence", "vpb"))
+    Hkv, bits = w["Hkv"], w["bits"]
     peak, peak_kind = measured_peaks()
     value = bytes_step / (ms * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": 1 if big else max(3, args.warmup),
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": r["warmup"],
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 in, tcgen05 f16 x f16 -> f32 (+ exact f32 chain near bounds), u8 codes", "data": "synthetic",
         "config": {"workload": w["desc"], "kv_bits": bits, "l2": "every step rewrites %.0f MB of cache" % (vectors * (D // vpb + 2) / 1e6)},
         "head_vectors_per_s": vectors / (ms * 1e-3),
         "append_tokens_per_s_28_layers": vectors / (ms * 1e-3) / (28 * 2 * Hkv),
         "fp32_tflops": vectors * 2 * D * D / (ms * 1e-3) / 1e12,
-        "gpu_launches": steps * NL * (G if per_sequence else G // B),
+        "gpu_launches": r["launches"],
         "roofline": {"kernel": "prefill_append_tc_kernel (tcgen05)", "bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s",
                      "frac": value / peak, "peak_kind": peak_kind, "traffic": None,
                      "note": ("one launch per sequence and layer (2048 tokens = 256 tiles = one wave): launch and set-up bound"
@@ -714,6 +725,13 @@ def run_ours(args, w, rank, world, local_rank):
                            "scaling": "strong" if we.get("strong") else "weak", "ms_per_step": r["ms_step"],
                            "ms_per_step_without_gather": r["ms_compute"], "value": val, "unit": "GB/s",
                            "frac_of_measured_hbm_per_gpu": val / world / measured_peaks()[0]}
+        if world == 1:  # the prompt append of config 2 (a slice: 16 prompts x 2048 tokens, 4 layers), tcgen05 kernel
+            wa = WORKLOADS["c2"]
+            ra = measure_append(args, wa, rank, local_rank)
+            val = ra["bytes_step"] / (ra["ms"] * 1e-3) / 1e9
+            extras["c2_prefill_append"] = {"workload": wa["desc"], "kv_bits": wa["bits"], "ms_per_step": ra["ms"], "value": val, "unit": "GB/s",
+                                           "head_vectors_per_s": ra["vectors"] / (ra["ms"] * 1e-3),
+                                           "frac_of_measured_hbm_per_gpu": val / measured_peaks()[0]}
     check = gather_check(rank, world) if world > 1 else None
     if rank != 0:
         return
