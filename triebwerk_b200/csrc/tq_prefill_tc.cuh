@@ -664,11 +664,14 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
         fence_proxy_async_smem();  // generic-proxy writes of the operands before the tensor core reads them
         named_barrier(1, TC_WORKERS);
         } else {
-            if (!dead && !mbar_wait_bounded_hint(bar_ld, ld_phase, 1u << 18, 2000u)) {
-                dead = true;
-                atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+            if (!dead) {
+                if (mbar_wait_bounded_hint(bar_ld, ld_phase, 1u << 18, 2000u)) {
+                    ld_phase ^= 1u;
+                } else {
+                    dead = true;
+                    atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
+                }
             }
-            ld_phase ^= 1u;
         }
         TC_STAMP(4);
 
@@ -830,6 +833,11 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
     }
 #endif
 
+    if constexpr (TMA_IN) {
+        // Given up on a wait: a copy into the operand tile may still be on its way; it must have landed (or never have
+        // been issued: then this runs out) before the CTA's shared memory is handed to another CTA.
+        if (dead && tid == 0) (void)mbar_wait_bounded(bar_ld, ld_phase, 1u << 16);
+    }
     tc_fence_before();
     named_barrier(1, TC_WORKERS);
     if (warp == 0) tmem_dealloc(tmem, 128u);
