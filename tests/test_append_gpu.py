@@ -262,3 +262,26 @@ def test_tensor_core_prefill_append_thread_load_form_in_a_child_process():
                        cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert " passed" in r.stdout
+
+
+@pytest.mark.parametrize("bits,Hkv,T", [(4, 2, 700), (4, 16, 130), (2, 32, 67), (4, 3, 400), (2, 1, 1200)])
+def test_token_append_other_head_counts_vs_oracle(bits, Hkv, T):
+    """The reference's token-form launcher takes any number of KV heads.  Head counts that divide 128 reach the tensor
+    cores' operand tile by tensor-map copies whose box is (128 / Hkv tokens) x (Hkv heads); the others, here 3, through
+    thread loads.  Scattered destinations, ragged last tiles; checked against the oracle."""
+    rng = np.random.default_rng(5 + Hkv)
+    R, _ = tqo.rotation()
+    D = 128
+    k = (rng.standard_normal((T, Hkv * D), dtype=np.float32) * rng.lognormal(0, 0.5, Hkv * D).astype(np.float32)).astype(np.float16)
+    pos = rng.permutation(T).astype(np.int32)
+    cq, cn = gu.gpu_append_tokens(k, R, pos, T, Hkv, D, bits)
+    oq, on = tqo.alloc_cache(1, T, Hkv, D, bits)
+    rot = tqo.append_tokens(oq, on, k, R, pos, T, Hkv, D, bits, want_rot=True)
+    rot_rows = np.zeros_like(rot)
+    rot_rows[pos] = rot
+    a = hp.unpack_codes(cq.reshape(T, Hkv, -1), bits)
+    b = hp.unpack_codes(oq.reshape(T, Hkv, -1), bits)
+    n, worst, n1 = hp.classify_code_mismatches(a, b, rot_rows, bits)
+    print(f"token tq{bits}, {Hkv} heads: {n} of {a.size} coordinates differ; {n1} within 1 ulp; worst {worst:.2f} ulp")
+    assert n <= max(3, a.size // 50000) and worst <= hp.ORACLE_ULP_SLACK
+    assert np.abs(cn.view(np.uint16).astype(np.int32) - on.view(np.uint16).astype(np.int32)).max() <= 1
