@@ -396,12 +396,17 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     }
                 }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
+                for (int e = 0; e < 8; e += 2) {  // (two columns per multiplication: the packed fp32 form)
                     const int c = 8 * c8 + e;
-                    float sv = __uint_as_float(sr[c]) * (BITS != 0 ? kn8[e] : p.score_scale);
-                    if (diagonal && j * PTC_KT + PTC_CPT * part + c > my_tok) sv = -1e30f;
-                    sr[c] = __float_as_uint(sv);
-                    mx = fmaxf(mx, sv);
+                    const float2 sc2 = BITS != 0 ? make_float2(kn8[e], kn8[e + 1]) : make_float2(p.score_scale, p.score_scale);
+                    float2 sv = mul2(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2);
+                    if (diagonal) {
+                        if (j * PTC_KT + PTC_CPT * part + c > my_tok) sv.x = -1e30f;
+                        if (j * PTC_KT + PTC_CPT * part + c + 1 > my_tok) sv.y = -1e30f;
+                    }
+                    sr[c] = __float_as_uint(sv.x);
+                    sr[c + 1] = __float_as_uint(sv.y);
+                    mx = fmaxf(mx, fmaxf(sv.x, sv.y));
                 }
             }
             xch[(j & 1) * PTC_SOFT + tid] = mx;
@@ -434,6 +439,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             }
             // ---- P (times the V norm) as fp16 into the A operand tile ----
             float lsum = 0.0f;
+            float2 lsum2 = make_float2(0.0f, 0.0f);
+            const float2 minus_mn = make_float2(-mn, -mn);
 #pragma unroll
             for (int c8 = 0; c8 < PTC_CPT / 8; ++c8) {
                 float vn8[8];
@@ -459,10 +466,13 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     }
                 } else {  // every row of the tile lies before every query of the block: nothing is masked
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float pe = ex2_approx(__uint_as_float(sr[8 * c8 + e]) - mn);
-                        lsum += pe;
-                        pv[e] = BITS != 0 ? pe * vn8[e] : pe;
+                    for (int e = 0; e < 8; e += 2) {
+                        const float2 d = add2(make_float2(__uint_as_float(sr[8 * c8 + e]), __uint_as_float(sr[8 * c8 + e + 1])), minus_mn);
+                        const float2 pe = make_float2(ex2_approx(d.x), ex2_approx(d.y));
+                        lsum2 = add2(lsum2, pe);
+                        const float2 w = BITS != 0 ? mul2(pe, make_float2(vn8[e], vn8[e + 1])) : pe;
+                        pv[e] = w.x;
+                        pv[e + 1] = w.y;
                     }
                 }
                 uint4 u;
@@ -470,7 +480,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                 u.z = pack_half2(pv[4], pv[5]); u.w = pack_half2(pv[6], pv[7]);
                 *reinterpret_cast<uint4*>(gb + PtcSmem::P + ptc_chunk(0u, srow, (PTC_CPT / 8) * part + c8)) = u;
             }
-            l_run = l_run * corr + lsum;
+            l_run = l_run * corr + (lsum + (lsum2.x + lsum2.y));
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar_pfull);
