@@ -42,8 +42,8 @@ struct PtcSmem {
     static constexpr uint32_t V = K + PTC_STAGES * 16384;   // PTC_STAGES x [128 coordinate rows][128 B = 64 tokens]; at the end: R^T
     static constexpr uint32_t P = V + PTC_STAGES * 16384;   // A operand [128 rows][128 B = 64 tokens]
     static constexpr uint32_t VRM = P + 16384;  // V tile as it lies in the cache, [64 tokens][256 B], chunk c of row r at c ^ (r & 7)
-    static constexpr uint32_t NORM = VRM + 16384;  // [PTC_STAGES][K, V][64] halves
-    static constexpr uint32_t CTRL = NORM + 1024;  // mbarriers and the tensor-memory base
+    static constexpr uint32_t NORM = VRM + 16384;  // [PTC_STAGES][K, V][64] floats (converted once, by the producers)
+    static constexpr uint32_t CTRL = NORM + PTC_STAGES * 512;  // mbarriers and the tensor-memory base
     static constexpr uint32_t XCH = CTRL + 128;   // float[2][PTC_SOFT]: exchange between the threads of a score row (by tile parity)
     static constexpr uint32_t LUT = XCH + 8 * PTC_SOFT;   // 4-bit: [256][32 lanes] half2
     static constexpr uint32_t BYTES = LUT + 32768;
@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
         if (p.status) atomicMax(p.status, ST_TMA_WAIT_TIMEOUT);
     };
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
-        if (!dead && !mbar_wait_bounded(bar, parity, 1u << 17)) give_up();
+        // (a third of this kernel's instructions were polls: each poll may now sleep up to 2 us inside the instruction)
+        if (!dead && !mbar_wait_bounded_hint(bar, parity, 1u << 17, 2000u)) give_up();
     };
 
     // ---- once: tensor memory, barriers, table, this block's queries, R ----
@@ -304,7 +305,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
                     *reinterpret_cast<uint4*>(gb + PtcSmem::VRM + (uint32_t)ktr * 256u + (uint32_t)(((8 * kc + i) ^ (ktr & 7)) << 4)) = w;
                 }
             }
-            if (BITS != 0) reinterpret_cast<__half*>(gb + PtcSmem::NORM)[b * 128 + pt] = nraw;
+            if (BITS != 0) reinterpret_cast<float*>(gb + PtcSmem::NORM)[b * 128 + pt] = __half2float(nraw);
             if (j + 1 < n_tiles) fetch(j + 1);  // on its way during the transposition and the wait for the next stage
             named_barrier(1, 128);  // the row-major V tile is complete
             // V transposed into the B operand [128 coordinate rows][64 tokens]: 8 x 8 blocks through ldmatrix.trans /
@@ -380,20 +381,16 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             tmem_ld_wait();
             // ---- K norm, causal limit, row maximum over both halves ----
             const bool diagonal = j * PTC_KT + PTC_KT - 1 > q0;
-            const uint4* nrm = reinterpret_cast<const uint4*>(gb + PtcSmem::NORM + (uint32_t)st * 256u);
+            const float4* nrm = reinterpret_cast<const float4*>(gb + PtcSmem::NORM + (uint32_t)st * 512u);
             float mx = -1e30f;
 #pragma unroll
             for (int c8 = 0; c8 < PTC_CPT / 8; ++c8) {
                 float kn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[(PTC_CPT / 8) * part + c8];  // (every thread of the warp reads the same words: a broadcast)
-                    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __half22float2(h2[e]);
-                        kn8[2 * e] = f.x;
-                        kn8[2 * e + 1] = f.y;
-                    }
+                    // (every thread of the warp reads the same words: a broadcast)
+                    const float4 n0 = nrm[2 * ((PTC_CPT / 8) * part + c8)], n1 = nrm[2 * ((PTC_CPT / 8) * part + c8) + 1];
+                    kn8[0] = n0.x; kn8[1] = n0.y; kn8[2] = n0.z; kn8[3] = n0.w;
+                    kn8[4] = n1.x; kn8[5] = n1.y; kn8[6] = n1.z; kn8[7] = n1.w;
                 }
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {  // (two columns per multiplication: the packed fp32 form)
@@ -445,14 +442,9 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) prefill_attention_tc_kernel(co
             for (int c8 = 0; c8 < PTC_CPT / 8; ++c8) {
                 float vn8[8];
                 if (BITS != 0) {
-                    const uint4 u = nrm[8 + (PTC_CPT / 8) * part + c8];
-                    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __half22float2(h2[e]);
-                        vn8[2 * e] = f.x;
-                        vn8[2 * e + 1] = f.y;
-                    }
+                    const float4 n0 = nrm[16 + 2 * ((PTC_CPT / 8) * part + c8)], n1 = nrm[16 + 2 * ((PTC_CPT / 8) * part + c8) + 1];
+                    vn8[0] = n0.x; vn8[1] = n0.y; vn8[2] = n0.z; vn8[3] = n0.w;
+                    vn8[4] = n1.x; vn8[5] = n1.y; vn8[6] = n1.z; vn8[7] = n1.w;
                 }
                 float pv[8];
                 if (diagonal) {
