@@ -445,6 +445,8 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
 #endif
     uint32_t it = 0;  // tiles this CTA has started: parity of the per-tile arrays, phase of their barriers
     uint32_t ld_phase = 0;
+    // TMA form: where this lane's 32-coordinate chunk of row 8 * warp + (lane & 7) starts in the operand tile (see 2b)
+    const uint32_t tree_addr = tc_operand_addr(TcSmem::A_X, 8 * warp + (lane & 7), 32 * (lane >> 3));
     auto issue_load = [&](int tile_n) {  // one thread: the 128 vectors of a tile -> operand tile, [half][token][head][128 B]
         const int kind_n = (p.k_buf && tile_n < tiles_per_kind) ? 0 : 1;
         const int vec0_n = (tile_n - (kind_n == 0 || !p.k_buf ? 0 : tiles_per_kind)) * TC_TILE;
@@ -696,14 +698,15 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
             // Sums of squares from the operand tile.  Pass q: lane (r, c) of warp w takes chunk c (32 coordinates) of vector
             // 64 q + 8 w + r; the eight lanes of a quarter-warp read eight different rows, whose 128-byte swizzle puts their
             // 16-byte pieces on different banks.  The four chunk sums meet by shuffles, in the reference's order.
+            // (piece i of the chunk sits at tree_addr ^ (i << 4): the swizzle only exchanges pieces within the chunk's 64 bytes;
+            // pass 1's rows lie 64 rows = 8192 bytes further, with the same swizzle)
             const int r = lane & 7, c = lane >> 3;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                const int v = 64 * q + 8 * warp + r;
                 float2 v2[16];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(gbase + tc_operand_addr(TcSmem::A_X, v, 32 * c + 8 * i));
+                    const uint4 u = *reinterpret_cast<const uint4*>(gbase + ((tree_addr ^ (uint32_t)(i << 4)) + (uint32_t)(q * 8192)));
                     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) v2[4 * i + e] = __half22float2(h2[e]);
