@@ -194,6 +194,8 @@ def test_tensor_core_prefill_append_equals_the_chain_kernel_and_the_oracle(bits,
     k[5, D:2 * D] *= np.float16(300.0)
     v[7, :D] = np.float16(np.nan)
     v[9, :D] = np.float16(6e-8)  # subnormal inputs
+    k[100:140] = 0               # a stretch of padding: all-zero vectors take their constant codes without any exact chain
+    v[120:130, D:] = np.float16(-0.0)
     msl = T + 32
     eng_tc = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)
     eng_ch = tq.Engine(msl, bits, num_layers=1, num_heads=H, num_kv_heads=Hkv, head_dim=D)

@@ -57,7 +57,7 @@ struct TcSmem {
     // two phases further.
     static constexpr uint32_t DST0 = 0x0800;             // long long[128] byte offset of each vector's codes in the cache (-1: none)
     static constexpr uint32_t INV0 = DST0 + 1024;        // float[128]: sum of squares, then 1/norm per vector; -1: the vector
-                                                         // holds an infinity or a NaN
+                                                         // holds an infinity or a NaN; -2: it is all zeros
     static constexpr uint32_t CTRL = INV0 + 512;         // mma mbarrier (8 B), tmem base (4 B), pad, full[2], empty[2] mbarriers,
                                                          // queue counts [2]
     static constexpr uint32_t GRID = 0x1000;             // uint32[TC_BUCKETS] bucket table, see the kernel
@@ -730,7 +730,9 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                 cn[(long long)layer * p.norm_layer_stride + row * p.Hkv + head] = __float2half_rn(sqrt_approx_ftz(my_tt));
             }
             dst_s[settle_v] = my_dst;
-            inv_s[settle_v] = abnormal ? -1.0f : rsqrt_approx_ftz(my_tt);
+            // (an all-zero vector -- padding, say -- has every coordinate ON the bound 0: 128 exact chains, all with the result
+            //  +0; it gets its constant codes directly instead.  The sum of squares of any other fp16 vector is at least 3.6e-15.)
+            inv_s[settle_v] = abnormal ? -1.0f : (my_tt == 1e-12f ? -2.0f : rsqrt_approx_ftz(my_tt));
         }
         TC_STAMP(5);
         if (!dead && !mbar_wait_bounded_hint(bar, phase, 1u << 18, 2000u)) {
@@ -793,8 +795,10 @@ prefill_append_tc_kernel(const __grid_constant__ CUtensorMap tm_k_in, const __gr
                         for (int k = 0; k < 16; k += 2) two(16 * j + k, words[j], 2);
                 }
                 uint32_t near_mask = __brev(near_rev);
-                if (abn) {  // what the reference's comparisons make of a NaN: the top code at 4 bits, code 0 at 2 bits
-                    words[0] = words[1] = words[2] = words[3] = bits == 4 ? 0xffffffffu : 0u;
+                if (abn) {  // what the reference's comparisons make of a NaN: the top code at 4 bits, code 0 at 2 bits;
+                            // of an all-zero vector: the code of +0 everywhere
+                    const uint32_t zero_codes = (uint32_t)quantize_code(0.0f, bits) * (bits == 4 ? 0x11111111u : 0x55555555u);
+                    words[0] = words[1] = words[2] = words[3] = inv == -2.0f ? zero_codes : (bits == 4 ? 0xffffffffu : 0u);
                     near_mask = 0u;
                 }
                 if (ev_dst < 0) near_mask = 0u;  // (a vector past the end of the input is all zeros: every coordinate ON a bound)
