@@ -30,7 +30,7 @@
 //      instructions, from shared memory in the TMA form), and one thread per vector settles it: norm out, 1/norm, where
 //      its codes go;
 //   3. each thread reads 64 of ITS vector's 128 accumulators from tensor memory (tcgen05.ld, 32 lanes x 32 columns per
-//      warp and instruction; warps w and w + 4 share a lane quarter), scales by 1/norm, quantises through a 1024-bucket
+//      warp and instruction; warps w and w + 4 share a lane quarter), scales by 1/norm, quantises through a 256-bucket
 //      uniform grid (bucket -> code, or -> the one bound inside it; 13 instructions per two coordinates), stores the
 //      packed codes straight to the cache and queues near-bound coordinates;
 //   4. the chain warp, one tile behind (per-tile arrays exist twice; two mbarrier pairs hand them back and forth),
@@ -51,7 +51,7 @@ constexpr float TC_BUCKETS_PER_UNIT = 46.0f;  // 1 / bucket width
 constexpr int TC_LIST_CAP = 96;    // queued near-bound coordinates per tile; the rest is handled by their owners
 
 // Shared memory by ABSOLUTE shared address (the kernel checks that its dynamic shared memory covers the range): the
-// bucket table sits on a 4096-byte boundary so that its look-up address is (bits & 0xffc) plus a constant.
+// bucket table sits on a 4096-byte boundary so that its look-up address is (bits & 0x3fc) plus a constant.
 struct TcSmem {
     // Per-tile arrays exist twice (tile parity): the chain warp works on a tile's queue while the workers are already
     // two phases further.
